@@ -1,0 +1,408 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized GEMM hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c1|c3|c5]
+
+One "step" is one pass of the fused NEGEMMLowpMatrixMultiplyCore (+ QUANTIZE_DOWN_FIXEDPOINT output stage)
+over one batch of seeded synthetic input.  The default workload is the configuration the headline metric is
+quoted on: the square QASYMM8_SIGNED x QSYMM8_PER_CHANNEL GEMMLowp with M = N = K = 4096, bias, per-channel
+fixed-point requantisation to QASYMM8_SIGNED.  With N > 1 GPUs (one process per GPU under torchrun) every
+rank owns one 4096-row block of A / dst of an (N*4096) x 4096 x 4096 problem (M-sharding, B replicated, no
+collective): weak scaling.
+
+Prints ONE JSON line (rank 0).  `value` is device-timed with inputs resident in HBM; `e2e` is the same metric
+through the host-buffer C-ABI call (pinned host memory in, pinned host memory out, copies inside the timed
+region); `roofline` is the tensor-core roofline of the GEMM kernel; `cpu_baseline` times the reference's own
+scalar implementation on a bounded row sample on the host cores.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+METRIC = "gemmlowp_int8_tops"
+UNIT = "TOPS"
+NOMINAL_INT8_TOPS = 4500.0
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=20)
+    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c5"])
+    p.add_argument("--size", type=int, default=0, help="override M=N=K of c2 (profiling on a small case)")
+    p.add_argument("--no-cpu-baseline", action="store_true")
+    p.add_argument("--no-e2e", action="store_true")
+    return p.parse_args()
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            d = json.load(f)
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"], source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, source="fallback")
+
+
+class ClockSampler:
+    """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.file = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        if self.proc is not None:
+            self.proc.terminate()  # the exact process started above
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        self.file.flush()
+        self.file.seek(0)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.file.read().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                mx.append(float(parts[1]))
+            except ValueError:
+                continue
+            for name, flag in zip(names, parts[3:7]):
+                if flag.lower().startswith("active"):
+                    reasons.add(name)
+        self.file.close()
+        os.unlink(self.file.name)
+        if sm:
+            # median over the upper half of the samples = the clock while the kernels were running
+            busy = sorted(sm)[len(sm) // 2:]
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        return out
+
+
+# ---------------------------------------------------------------------------------------------------------
+# workloads
+# ---------------------------------------------------------------------------------------------------------
+def make_gemm_workload(name, size):
+    from computelibrary_b200 import capi
+    from computelibrary_b200 import workloads as wl
+    if name == "c1":
+        c = wl.config1()
+        qm, sh = capi.calculate_quantized_multiplier(c["real_multiplier"])
+        mult, shift = np.array([qm], np.int32), np.array([sh], np.int32)
+        label = "config1: QASYMM8 GEMMLowp M=64 N=128 K=256, bias, per-tensor fixed-point requant to QASYMM8"
+    elif name == "c5":
+        c = wl.config5()
+        mult, shift = capi.calculate_quantized_multipliers(c["i_scale"], c["w_scales"], c["o_scale"])
+        label = "config5: s8 linear M=8192 K=4096 N=14336, per-channel requant to s8, no bias"
+    else:
+        n = size or 4096
+        c = wl.config2(M=n, N=n, K=n)
+        mult, shift = capi.calculate_quantized_multipliers(c["i_scale"], c["w_scales"], c["o_scale"])
+        label = (f"config2: QASYMM8_SIGNED x QSYMM8_PER_CHANNEL GEMMLowp M=N=K={n}, bias, per-channel "
+                 "fixed-point requant to QASYMM8_SIGNED")
+    c["mult"], c["shift"], c["label"] = mult, shift, label
+    return c
+
+
+def build_plan(ctx, c):
+    import torch
+    from computelibrary_b200 import capi
+    code = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
+    a, b = c["a"], c["b"]
+    M, K = a.shape
+    N = b.shape[1]
+    pc = c["mult"].size > 1
+    desc, keep = capi.make_gemm_desc(
+        M, N, K, code[a.dtype], code[b.dtype], code[np.dtype(c["out_dtype"])], c["a_off"], c["b_off"],
+        multiplier=int(c["mult"][0]), shift=int(c["shift"][0]), multipliers=c["mult"] if pc else None,
+        shifts=c["shift"] if pc else None, offset=c["offset"], min_bound=c["lo"], max_bound=c["hi"],
+        has_bias=c["bias"] is not None)
+    plan = capi.GemmPlan(ctx, desc, keep)
+    d_b = torch.from_numpy(b.view(np.uint8)).cuda()
+    plan.prepare(d_b)
+    ctx.sync()
+    del d_b  # B may be released after prepare()
+    return plan, (M, N, K)
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import computelibrary_b200 as cl
+
+    rank, world, local = dist_env()
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    ctx = cl.Context(local, torch.cuda.current_stream().cuda_stream)
+    c = make_gemm_workload(args.workload, args.size)
+    if world > 1:
+        # M-sharding: this rank's rows of A are its own seeded block; B / bias / multipliers are replicated
+        from computelibrary_b200 import workloads as wl
+        c["a"] = wl.q8_uniform(np.random.default_rng(1000 + rank), c["a"].shape, c["a"].dtype)
+    plan, (M, N, K) = build_plan(ctx, c)
+    ops = 2.0 * M * N * K
+
+    d_a = torch.from_numpy(c["a"].view(np.uint8)).cuda()
+    d_bias = torch.from_numpy(c["bias"]).cuda() if c["bias"] is not None else None
+    d_dst = torch.empty((M, N), dtype=torch.uint8, device="cuda")
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")  # > 126 MB L2
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-resident timing: per-step CUDA events on the launching stream, L2 flushed in between ----
+    for _ in range(args.warmup):
+        flush.zero_()
+        plan.run(d_a, None, d_bias, d_dst)
+    barrier()
+    sampler = ClockSampler(local) if rank == 0 else None
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    t_wall0 = time.perf_counter()
+    for i in range(args.steps):
+        flush.zero_()
+        starts[i].record()
+        plan.run(d_a, None, d_bias, d_dst)
+        stops[i].record()
+    barrier()
+    t_wall = time.perf_counter() - t_wall0
+    ctx.sync()  # raises if a device-side bounded wait ran out
+    step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
+    total_ms = float(sum(step_ms))
+    clocks = sampler.stop() if sampler is not None else None
+
+    # ---- end to end: pinned host A -> device, run, dst -> pinned host, every step ----
+    e2e = None
+    if not args.no_e2e:
+        a_bytes, d_bytes = M * K, M * N
+        h_a, h_d = ctx.host_alloc(a_bytes), ctx.host_alloc(d_bytes)
+        h_bias = ctx.host_alloc(4 * N) if c["bias"] is not None else 0
+        C.memmove(h_a, c["a"].ctypes.data, a_bytes)
+        if h_bias:
+            C.memmove(h_bias, c["bias"].ctypes.data, 4 * N)
+        for _ in range(max(3, args.warmup)):
+            plan.run_host(h_a, h_bias, h_d)
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            plan.run_host(h_a, h_bias, h_d)  # blocks until dst is valid on the host
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+        got = np.ctypeslib.as_array((C.c_uint8 * d_bytes).from_address(h_d)).reshape(M, N)
+        assert np.array_equal(got, d_dst.cpu().numpy()), "host-buffer path and device path disagree"
+        e2e_ms = e2e_s * 1e3
+        for p in (h_a, h_d, h_bias):
+            if p:
+                ctx.host_free(p)
+    else:
+        e2e_ms = None
+
+    # ---- reduce over ranks: the slowest rank defines the step time ----
+    if world > 1:
+        t = torch.tensor([total_ms, e2e_ms or 0.0], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms, e2e_max = float(t[0]), float(t[1])
+        e2e_ms = e2e_max if e2e_ms is not None else None
+    ms_per_step = total_ms / args.steps
+    value = world * ops / (ms_per_step * 1e-3) / 1e12
+    if e2e_ms is not None:
+        e2e = {"value": world * ops / (e2e_ms / args.steps * 1e-3) / 1e12, "unit": UNIT,
+               "h2d_bytes_per_step": M * K + (4 * N if c["bias"] is not None else 0), "d2h_bytes_per_step": M * N,
+               "ms_per_step": e2e_ms / args.steps}
+
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = load_peaks()
+    kernel_ms = statistics.mean(step_ms)  # the fused GEMM kernel is the only kernel of a step here
+    achieved = ops / (kernel_ms * 1e-3) / 1e12
+    peak = 2.0 * peaks["bf16_tflops"]
+    roofline = {
+        "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TOPS", "frac": achieved / peak,
+        "peak_source": f"2 x {peaks['source']} bf16 cuBLAS burst ({peaks['bf16_tflops']} TFLOP/s): int8 tensor "
+                       "rate is twice the bf16 rate; no int8 figure is recorded in MEASURED_PEAKS.json",
+        "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
+        "traffic": None,
+        "kernel": "gemmlowp_tcgen05_kernel" if plan.kernel == "tcgen05" else "gemmlowp_simt_kernel",
+        "kernel_ms": kernel_ms,
+    }
+    try:  # library int8 GEMM as a yardstick only (never on the product path)
+        ya = torch.from_numpy(c["a"]).cuda()
+        yb = torch.from_numpy(np.ascontiguousarray(c["b"])).cuda().t().contiguous().t()
+        for _ in range(3):
+            torch._int_mm(ya, yb)
+        ts = []
+        for _ in range(10):
+            flush.zero_()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            torch._int_mm(ya, yb)
+            e.record()
+            torch.cuda.synchronize()
+            ts.append(s.elapsed_time(e))
+        roofline["yardstick_torch_int_mm_tops"] = ops / (min(ts) * 1e-3) / 1e12
+    except Exception as ex:  # noqa: BLE001
+        roofline["yardstick_torch_int_mm_tops"] = None
+        roofline["yardstick_error"] = str(ex)[:120]
+
+    line = {
+        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "s8*s8->s32->s8" if c["a"].dtype == np.int8 else "u8*u8->s32->u8", "data": "synthetic",
+        "config": {"workload": c["label"], "per_gpu_shape": [M, N, K], "l2": "flushed between timed steps "
+                   "(256 MB write)", "sharding": "M-sharded, B replicated, no collective" if world > 1 else "single GPU"},
+        "e2e": e2e, "gpu_launches": args.steps * plan.launches, "roofline": roofline, "clocks": clocks,
+        "wall_s_timed_loop": t_wall,
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline(c, ops)
+    print(json.dumps(line), flush=True)
+    plan.close()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the reference's own scalar implementation on the host cores
+# ---------------------------------------------------------------------------------------------------------
+def cpu_reference_step(c, rows, threads):
+    """One pass of the reference's CPU implementation over `rows` rows of A: its scalar GEMMLowp core
+    (tests/validation/reference/GEMMLowp.cpp:202-255, a serial triple loop) + fixed-point output stage.  The
+    rows are split over `threads` host threads the way the NE scheduler splits a window over DimY."""
+    import oracle
+    from concurrent.futures import ThreadPoolExecutor
+    ref = oracle.ref()
+    kind = "reference" if ref is not None else "port"
+    a = c["a"][:rows]
+    pc = c["mult"].size > 1
+
+    if ref is not None:
+        def work(blk):
+            acc = ref.gemmlowp_core(a[blk], c["b"], c["a_off"], c["b_off"])
+            return ref.output_stage(acc, c["bias"], c["mult"] if pc else c["mult"][:1],
+                                    c["shift"] if pc else c["shift"][:1], c["offset"], c["lo"], c["hi"],
+                                    c["out_dtype"])
+        blocks = [slice(i * rows // threads, (i + 1) * rows // threads) for i in range(threads)]
+        blocks = [b for b in blocks if b.stop > b.start]
+        t0 = time.perf_counter()
+        with ThreadPoolExecutor(max_workers=threads) as ex:  # ctypes releases the GIL during the C++ call
+            list(ex.map(work, blocks))
+        return time.perf_counter() - t0, kind, threads
+    port = oracle.port()
+    t0 = time.perf_counter()
+    port.gemmlowp_fused(a, c["b"], c["bias"], c["a_off"], c["b_off"], c["mult"], c["shift"], c["offset"], c["lo"],
+                        c["hi"], c["out_dtype"])
+    return time.perf_counter() - t0, kind, port.num_threads()
+
+
+def cpu_sample_rows(c, threads):
+    M, K = c["a"].shape
+    N = c["b"].shape[1]
+    # the scalar reference sustains roughly 1-2.5 GOP/s per core: aim at about 10 s of work
+    target_ops = 1.5e9 * threads * 10
+    rows = int(max(threads, min(M, target_ops / (2.0 * N * K))))
+    return rows
+
+
+def cpu_baseline(c, ops_full):
+    threads = os.cpu_count() or 1
+    rows = cpu_sample_rows(c, threads)
+    M, K = c["a"].shape
+    N = c["b"].shape[1]
+    secs, kind, used = cpu_reference_step(c, rows, threads)
+    return {"value": 2.0 * rows * N * K / secs / 1e12, "unit": UNIT, "cores": used, "kind": kind,
+            "sample": f"{rows} of {M} rows of A (all of B): {rows}x{N}x{K}, {secs:.2f} s, "
+                      f"{'reference scalar oracle compiled in place, rows split over host threads' if kind == 'reference' else 'C restatement with OpenMP'}"}
+
+
+def run_reference(args):
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    c = make_gemm_workload(args.workload, args.size)
+    M, K = c["a"].shape
+    N = c["b"].shape[1]
+    threads = os.cpu_count() or 1
+    rows = cpu_sample_rows(c, threads)
+    # keep the whole --steps/--warmup run within a few minutes: each step is a bounded row sample
+    per_step_budget = 150.0 / max(1, args.steps + args.warmup)
+    rows = int(max(threads, min(rows, rows * per_step_budget / 10.0)))
+    kind, used = "port", threads
+    for _ in range(args.warmup):
+        _, kind, used = cpu_reference_step(c, rows, threads)
+    t = 0.0
+    for _ in range(args.steps):
+        s, kind, used = cpu_reference_step(c, rows, threads)
+        t += s
+    ms = t / args.steps * 1e3
+    value = 2.0 * rows * N * K / (ms * 1e-3) / 1e12
+    sample = f"each step = {rows} of {M} rows of A against all of B ({rows}x{N}x{K})"
+    line = {
+        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "s8*s8->s32->s8" if c["a"].dtype == np.int8 else "u8*u8->s32->u8", "data": "synthetic",
+        "config": {"workload": c["label"], "per_gpu_shape": [M, N, K], "note": "CPU arm: the NE (Arm) kernels cannot "
+                   "be built on x86_64; this times the reference's own scalar implementation of the path"},
+        "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": kind, "sample": sample},
+        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    args = parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

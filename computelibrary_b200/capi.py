@@ -1,0 +1,424 @@
+"""ctypes binding of include/cugl.h.  Every call goes through libcugl.so; a missing library or a missing
+GPU raises -- nothing here computes on the CPU."""
+from __future__ import annotations
+
+import ctypes as C
+import os
+import re
+
+from . import build as _build
+
+U8, S8, S32 = 0, 1, 2
+STAGE_NONE, STAGE_FIXEDPOINT = 0, 2
+INT32_MIN, INT32_MAX = -(2 ** 31), 2 ** 31 - 1
+
+_vp = C.c_void_p
+_i32 = C.c_int32
+_i64 = C.c_int64
+_pi32 = C.POINTER(C.c_int32)
+
+
+class CuglError(RuntimeError):
+    def __init__(self, status: int, message: str):
+        super().__init__(f"cugl status {status}: {message}")
+        self.status = status
+        self.message = message
+
+
+class GemmDesc(C.Structure):
+    """cugl_gemm_desc"""
+    _fields_ = [
+        ("M", _i32), ("N", _i32), ("K", _i32), ("batch", _i32),
+        ("lda", _i64), ("ldb", _i64), ("ldd", _i64),
+        ("a_batch_stride", _i64), ("b_batch_stride", _i64), ("d_batch_stride", _i64),
+        ("a_dtype", _i32), ("b_dtype", _i32), ("dst_dtype", _i32),
+        ("a_offset", _i32), ("b_offset", _i32),
+        ("stage", _i32), ("is_quantized_per_channel", _i32),
+        ("gemmlowp_multiplier", _i32), ("gemmlowp_shift", _i32),
+        ("h_gemmlowp_multipliers", _pi32), ("h_gemmlowp_shifts", _pi32),
+        ("gemmlowp_offset", _i32), ("gemmlowp_min_bound", _i32), ("gemmlowp_max_bound", _i32),
+        ("has_bias", _i32), ("reshape_b_only_on_first_run", _i32),
+    ]
+
+
+class ConvDesc(C.Structure):
+    """cugl_conv_desc"""
+    _fields_ = [
+        ("B", _i32), ("H", _i32), ("W", _i32), ("C", _i32),
+        ("OFM", _i32), ("kh", _i32), ("kw", _i32),
+        ("stride_x", _i32), ("stride_y", _i32),
+        ("pad_left", _i32), ("pad_right", _i32), ("pad_top", _i32), ("pad_bottom", _i32),
+        ("dil_x", _i32), ("dil_y", _i32),
+        ("src_dtype", _i32), ("w_dtype", _i32),
+        ("src_zero_point", _i32), ("w_zero_point", _i32),
+        ("is_quantized_per_channel", _i32),
+        ("gemmlowp_multiplier", _i32), ("gemmlowp_shift", _i32),
+        ("h_gemmlowp_multipliers", _pi32), ("h_gemmlowp_shifts", _pi32),
+        ("dst_zero_point", _i32), ("min_bound", _i32), ("max_bound", _i32),
+        ("has_bias", _i32),
+    ]
+
+
+_SIGNATURES = {
+    "cugl_context_create": (C.c_int, [C.c_int, _vp, C.POINTER(_vp)]),
+    "cugl_context_destroy": (None, [_vp]),
+    "cugl_last_error_string": (C.c_char_p, [_vp]),
+    "cugl_context_stream": (_vp, [_vp]),
+    "cugl_context_device": (C.c_int, [_vp]),
+    "cugl_context_sm_count": (C.c_int, [_vp]),
+    "cugl_malloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
+    "cugl_free": (C.c_int, [_vp, _vp]),
+    "cugl_host_alloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
+    "cugl_host_free": (C.c_int, [_vp, _vp]),
+    "cugl_memcpy_h2d": (C.c_int, [_vp, _vp, _vp, C.c_size_t]),
+    "cugl_memcpy_d2h": (C.c_int, [_vp, _vp, _vp, C.c_size_t]),
+    "cugl_memcpy2d_h2d": (C.c_int, [_vp, _vp, C.c_size_t, _vp, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "cugl_memcpy2d_d2h": (C.c_int, [_vp, _vp, C.c_size_t, _vp, C.c_size_t, C.c_size_t, C.c_size_t]),
+    "cugl_memset": (C.c_int, [_vp, _vp, C.c_int, C.c_size_t]),
+    "cugl_sync": (C.c_int, [_vp]),
+    "cugl_calculate_quantized_multiplier": (C.c_int, [C.c_float, _pi32, _pi32]),
+    "cugl_calculate_quantized_multipliers": (C.c_int, [C.c_float, C.POINTER(C.c_float), C.c_int, C.c_float, _pi32,
+                                                       _pi32]),
+    "cugl_gemmlowp_validate": (C.c_int, [C.POINTER(GemmDesc), C.POINTER(C.c_char_p)]),
+    "cugl_gemmlowp_plan_create": (C.c_int, [_vp, C.POINTER(GemmDesc), C.POINTER(_vp)]),
+    "cugl_gemmlowp_plan_destroy": (None, [_vp]),
+    "cugl_gemmlowp_prepare": (C.c_int, [_vp, _vp]),
+    "cugl_gemmlowp_run": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
+    "cugl_gemmlowp_run_host": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "cugl_gemmlowp_update_quantization": (C.c_int, [_vp, C.POINTER(GemmDesc)]),
+    "cugl_gemmlowp_plan_kernel": (C.c_char_p, [_vp]),
+    "cugl_gemmlowp_plan_force_simt": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
+    "cugl_reduce_rows": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
+    "cugl_reduce_cols": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
+    "cugl_offset_contribution": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _i32, _i32]),
+    "cugl_output_stage": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32,
+                                    _i32, _i32, _i32]),
+    "cugl_im2col_nhwc": (C.c_int, [_vp, _vp, _vp] + [_i32] * 16 + [_i64]),
+    "cugl_weights_reshape_nhwc": (C.c_int, [_vp, _vp, _vp, _i32, _i32]),
+    "cugl_conv2d_validate": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_char_p)]),
+    "cugl_conv2d_plan_create": (C.c_int, [_vp, C.POINTER(ConvDesc), C.POINTER(_vp)]),
+    "cugl_conv2d_plan_destroy": (None, [_vp]),
+    "cugl_conv2d_prepare": (C.c_int, [_vp, _vp]),
+    "cugl_conv2d_run": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "cugl_conv2d_run_host": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "cugl_conv2d_out_dims": (None, [C.POINTER(ConvDesc), _pi32, _pi32]),
+    "cugl_conv2d_plan_launches": (C.c_int, [_vp]),
+}
+
+_lib = None
+
+
+def header_symbols() -> list[str]:
+    """Every function include/cugl.h declares (parsed from the header text)."""
+    with open(os.path.join(_build.ROOT, "include", "cugl.h")) as f:
+        text = f.read()
+    return sorted(set(re.findall(r"CUGL_API[^;(]*?\b(cugl_\w+)\s*\(", text)))
+
+
+def load_library(build_if_missing: bool = True) -> C.CDLL:
+    """dlopen libcugl.so (building it first when the sources are newer) and type every entry point."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    path = _build.LIB_PATH
+    if build_if_missing:
+        try:
+            path = _build.build()
+        except Exception:
+            if not os.path.exists(path):
+                raise
+    if not os.path.exists(path):
+        raise OSError(f"{path} is missing: run `python -m computelibrary_b200.build`")
+    lib = C.CDLL(path)
+    for name, (restype, argtypes) in _SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError here = header and library disagree
+        fn.restype = restype
+        fn.argtypes = argtypes
+    _lib = lib
+    return lib
+
+
+def _check(status: int, ctx=None):
+    if status != 0:
+        msg = load_library().cugl_last_error_string(ctx)
+        raise CuglError(status, msg.decode() if msg else "")
+
+
+def calculate_quantized_multiplier(multiplier: float):
+    m, s = _i32(0), _i32(0)
+    _check(load_library().cugl_calculate_quantized_multiplier(C.c_float(multiplier), C.byref(m), C.byref(s)))
+    return int(m.value), int(s.value)
+
+
+def calculate_quantized_multipliers(i_scale: float, w_scales, o_scale: float):
+    import numpy as np
+    w = np.ascontiguousarray(np.asarray(w_scales, dtype=np.float32))
+    m = np.zeros(w.size, np.int32)
+    s = np.zeros(w.size, np.int32)
+    _check(load_library().cugl_calculate_quantized_multipliers(
+        C.c_float(i_scale), w.ctypes.data_as(C.POINTER(C.c_float)), int(w.size), C.c_float(o_scale),
+        m.ctypes.data_as(_pi32), s.ctypes.data_as(_pi32)))
+    return m, s
+
+
+def _dptr(t):
+    """Device pointer of a torch tensor / raw int / None."""
+    if t is None:
+        return None
+    if isinstance(t, int):
+        return t
+    return t.data_ptr()
+
+
+class Context:
+    """cugl_context on one device.  stream: raw cudaStream_t (int), e.g. torch's current stream, or None."""
+
+    def __init__(self, device: int = 0, stream: int | None = None):
+        self.lib = load_library()
+        h = _vp()
+        _check(self.lib.cugl_context_create(device, _vp(stream) if stream else None, C.byref(h)))
+        self.handle = h
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.lib.cugl_context_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def check(self, status: int):
+        _check(status, self.handle)
+
+    def sync(self):
+        self.check(self.lib.cugl_sync(self.handle))
+
+    @property
+    def sm_count(self) -> int:
+        return self.lib.cugl_context_sm_count(self.handle)
+
+    @property
+    def stream(self) -> int:
+        return self.lib.cugl_context_stream(self.handle) or 0
+
+    # memory -------------------------------------------------------------------------------------
+    def malloc(self, nbytes: int) -> int:
+        p = _vp()
+        self.check(self.lib.cugl_malloc(self.handle, nbytes, C.byref(p)))
+        return p.value or 0
+
+    def free(self, ptr: int):
+        self.check(self.lib.cugl_free(self.handle, _vp(ptr)))
+
+    def host_alloc(self, nbytes: int) -> int:
+        p = _vp()
+        self.check(self.lib.cugl_host_alloc(self.handle, nbytes, C.byref(p)))
+        return p.value or 0
+
+    def host_free(self, ptr: int):
+        self.check(self.lib.cugl_host_free(self.handle, _vp(ptr)))
+
+    def h2d(self, d_ptr: int, h_ptr: int, nbytes: int):
+        self.check(self.lib.cugl_memcpy_h2d(self.handle, _vp(d_ptr), _vp(h_ptr), nbytes))
+
+    def d2h(self, h_ptr: int, d_ptr: int, nbytes: int):
+        self.check(self.lib.cugl_memcpy_d2h(self.handle, _vp(h_ptr), _vp(d_ptr), nbytes))
+
+    # stand-alone kernels --------------------------------------------------------------------------
+    def reduce_rows(self, a, dtype, M, K, lda, out, scalar=1):
+        self.check(self.lib.cugl_reduce_rows(self.handle, _dptr(a), dtype, M, K, lda, scalar, _dptr(out)))
+
+    def reduce_cols(self, b, dtype, K, N, ldb, out, scalar=1):
+        self.check(self.lib.cugl_reduce_cols(self.handle, _dptr(b), dtype, K, N, ldb, scalar, _dptr(out)))
+
+    def offset_contribution(self, mm, M, N, K, ld_bytes, colsum, rowsum, a_off, b_off):
+        self.check(self.lib.cugl_offset_contribution(self.handle, _dptr(mm), M, N, K, ld_bytes, _dptr(colsum),
+                                                     _dptr(rowsum), a_off, b_off))
+
+    def output_stage(self, src, ld_in, bias, out, ld_out, out_dtype, M, N, mults, shifts, mult, shift, n_mult,
+                     offset, lo, hi):
+        self.check(self.lib.cugl_output_stage(self.handle, _dptr(src), ld_in, _dptr(bias), _dptr(out), ld_out,
+                                              out_dtype, M, N, _dptr(mults), _dptr(shifts), mult, shift, n_mult,
+                                              offset, lo, hi))
+
+    def im2col_nhwc(self, src, dst, C_, W, H, B, kw, kh, sx, sy, pl, pt, dx, dy, Wo, Ho, pad_value, row_stride):
+        self.check(self.lib.cugl_im2col_nhwc(self.handle, _dptr(src), _dptr(dst), C_, W, H, B, kw, kh, sx, sy, pl, pt,
+                                             dx, dy, Wo, Ho, pad_value, row_stride))
+
+    def weights_reshape_nhwc(self, w, dst, K, OFM):
+        self.check(self.lib.cugl_weights_reshape_nhwc(self.handle, _dptr(w), _dptr(dst), K, OFM))
+
+
+def make_gemm_desc(M, N, K, a_dtype, b_dtype, dst_dtype, a_offset=0, b_offset=0, stage=STAGE_FIXEDPOINT,
+                   multiplier=0, shift=0, multipliers=None, shifts=None, offset=0, min_bound=INT32_MIN,
+                   max_bound=INT32_MAX, has_bias=False, batch=1, lda=None, ldb=None, ldd=None,
+                   a_batch_stride=None, b_batch_stride=0, d_batch_stride=None, b_constant=True):
+    """Fill a cugl_gemm_desc for dense row-major operands unless strides are given.  Returns
+    (desc, keepalive) -- keepalive holds the numpy arrays the descriptor points into."""
+    import numpy as np
+    dsz = 4 if dst_dtype == S32 else 1
+    d = GemmDesc()
+    d.M, d.N, d.K, d.batch = M, N, K, batch
+    d.lda = K if lda is None else lda
+    d.ldb = N if ldb is None else ldb
+    d.ldd = N * dsz if ldd is None else ldd
+    d.a_batch_stride = d.lda * M if a_batch_stride is None else a_batch_stride
+    d.b_batch_stride = b_batch_stride
+    d.d_batch_stride = d.ldd * M if d_batch_stride is None else d_batch_stride
+    d.a_dtype, d.b_dtype, d.dst_dtype = a_dtype, b_dtype, dst_dtype
+    d.a_offset, d.b_offset = a_offset, b_offset
+    d.stage = stage
+    keep = []
+    if multipliers is not None:
+        m = np.ascontiguousarray(np.asarray(multipliers, dtype=np.int32))
+        s = np.ascontiguousarray(np.asarray(shifts, dtype=np.int32))
+        keep += [m, s]
+        d.is_quantized_per_channel = 1
+        d.h_gemmlowp_multipliers = m.ctypes.data_as(_pi32)
+        d.h_gemmlowp_shifts = s.ctypes.data_as(_pi32)
+        d.gemmlowp_multiplier, d.gemmlowp_shift = int(m[0]), int(s[0])
+    else:
+        d.is_quantized_per_channel = 0
+        d.gemmlowp_multiplier, d.gemmlowp_shift = multiplier, shift
+    d.gemmlowp_offset = offset
+    d.gemmlowp_min_bound, d.gemmlowp_max_bound = min_bound, max_bound
+    d.has_bias = int(has_bias)
+    d.reshape_b_only_on_first_run = int(b_constant)
+    return d, keep
+
+
+def gemm_validate(desc: GemmDesc):
+    """Returns (status, reason)."""
+    why = C.c_char_p()
+    st = load_library().cugl_gemmlowp_validate(C.byref(desc), C.byref(why))
+    return st, (why.value or b"").decode()
+
+
+def conv_validate(desc: ConvDesc):
+    why = C.c_char_p()
+    st = load_library().cugl_conv2d_validate(C.byref(desc), C.byref(why))
+    return st, (why.value or b"").decode()
+
+
+class GemmPlan:
+    """cugl_gemm_plan: a configured NEGEMMLowpMatrixMultiplyCore."""
+
+    def __init__(self, ctx: Context, desc: GemmDesc, keepalive=None):
+        self.ctx = ctx
+        self.desc = desc
+        self._keep = keepalive
+        h = _vp()
+        ctx.check(ctx.lib.cugl_gemmlowp_plan_create(ctx.handle, C.byref(desc), C.byref(h)))
+        self.handle = h
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx.lib.cugl_gemmlowp_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def prepare(self, b):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_prepare(self.handle, _dptr(b)))
+
+    def run(self, a, b, bias, dst):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_run(self.handle, _dptr(a), _dptr(b), _dptr(bias), _dptr(dst)))
+
+    def run_host(self, h_a: int, h_bias, h_dst: int):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_run_host(self.handle, _vp(h_a), _vp(h_bias) if h_bias else None,
+                                                           _vp(h_dst)))
+
+    def update_quantization(self, desc: GemmDesc, keepalive=None):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_update_quantization(self.handle, C.byref(desc)))
+        self.desc, self._keep = desc, keepalive
+
+    def force_simt(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_force_simt(self.handle, int(on)))
+
+    @property
+    def kernel(self) -> str:
+        return self.ctx.lib.cugl_gemmlowp_plan_kernel(self.handle).decode()
+
+    @property
+    def launches(self) -> int:
+        return self.ctx.lib.cugl_gemmlowp_plan_launches(self.handle)
+
+
+def make_conv_desc(B, H, W, C_, OFM, kh, kw, stride=(1, 1), pad=(0, 0, 0, 0), dilation=(1, 1), src_dtype=U8,
+                   w_dtype=S8, src_zp=0, w_zp=0, multiplier=0, shift=0, multipliers=None, shifts=None, dst_zp=0,
+                   min_bound=INT32_MIN, max_bound=INT32_MAX, has_bias=True):
+    """pad = (left, right, top, bottom); stride / dilation = (x, y).  Returns (desc, keepalive)."""
+    import numpy as np
+    d = ConvDesc()
+    d.B, d.H, d.W, d.C = B, H, W, C_
+    d.OFM, d.kh, d.kw = OFM, kh, kw
+    d.stride_x, d.stride_y = stride
+    d.pad_left, d.pad_right, d.pad_top, d.pad_bottom = pad
+    d.dil_x, d.dil_y = dilation
+    d.src_dtype, d.w_dtype = src_dtype, w_dtype
+    d.src_zero_point, d.w_zero_point = src_zp, w_zp
+    keep = []
+    if multipliers is not None:
+        m = np.ascontiguousarray(np.asarray(multipliers, dtype=np.int32))
+        s = np.ascontiguousarray(np.asarray(shifts, dtype=np.int32))
+        keep += [m, s]
+        d.is_quantized_per_channel = 1
+        d.h_gemmlowp_multipliers = m.ctypes.data_as(_pi32)
+        d.h_gemmlowp_shifts = s.ctypes.data_as(_pi32)
+        d.gemmlowp_multiplier, d.gemmlowp_shift = int(m[0]), int(s[0])
+    else:
+        d.gemmlowp_multiplier, d.gemmlowp_shift = multiplier, shift
+    d.dst_zero_point = dst_zp
+    d.min_bound, d.max_bound = min_bound, max_bound
+    d.has_bias = int(has_bias)
+    return d, keep
+
+
+class ConvPlan:
+    """cugl_conv_plan: a configured NEGEMMConvolutionLayer (NHWC, 8-bit)."""
+
+    def __init__(self, ctx: Context, desc: ConvDesc, keepalive=None):
+        self.ctx = ctx
+        self.desc = desc
+        self._keep = keepalive
+        h = _vp()
+        ctx.check(ctx.lib.cugl_conv2d_plan_create(ctx.handle, C.byref(desc), C.byref(h)))
+        self.handle = h
+
+    def close(self):
+        if getattr(self, "handle", None):
+            self.ctx.lib.cugl_conv2d_plan_destroy(self.handle)
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass
+
+    def out_dims(self):
+        wo, ho = _i32(0), _i32(0)
+        self.ctx.lib.cugl_conv2d_out_dims(C.byref(self.desc), C.byref(wo), C.byref(ho))
+        return int(wo.value), int(ho.value)
+
+    def prepare(self, weights):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_prepare(self.handle, _dptr(weights)))
+
+    def run(self, src, bias, dst):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_run(self.handle, _dptr(src), _dptr(bias), _dptr(dst)))
+
+    def run_host(self, h_src: int, h_bias, h_dst: int):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_run_host(self.handle, _vp(h_src), _vp(h_bias) if h_bias else None,
+                                                         _vp(h_dst)))
+
+    @property
+    def launches(self) -> int:
+        return self.ctx.lib.cugl_conv2d_plan_launches(self.handle)

@@ -1,0 +1,455 @@
+// HBM-bound kernels of the quantized GEMM path: row / column reductions, the B re-layout done in
+// prepare(), the S32 offset contribution, the stand-alone output stage, NHWC im2col and the weights
+// reshape.  All of them move each byte once with 128-bit accesses where the addresses allow it.
+#include "kernels.cuh"
+
+namespace cugl
+{
+namespace
+{
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ int32_t sum4(uint32_t w, bool is_signed, int32_t acc)
+{
+    return is_signed ? __dp4a(static_cast<int32_t>(w), 0x01010101, acc)
+                     : static_cast<int32_t>(__dp4a(w, 0x01010101u, static_cast<uint32_t>(acc)));
+}
+
+__device__ __forceinline__ int32_t warp_sum(int32_t v)
+{
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+    {
+        v += __shfl_xor_sync(0xffffffffu, v, o);
+    }
+    return v;
+}
+
+// ---- rowsum_A[m] = scalar * sum_k A[m,k] -------------------------------------------------------
+// One warp per row: unaligned head bytes, a body of 16-byte vectors, tail bytes; shuffle reduction.
+// CpuGemmLowpMatrixAReductionKernel::run_internal (CpuGemmLowpMatrixReductionKernel.cpp:133-204).
+__global__ void __launch_bounds__(kThreads) reduce_rows_kernel(const uint8_t *__restrict__ a, bool is_signed, int M,
+                                                               int K, int64_t lda, int32_t scalar,
+                                                               int32_t *__restrict__ out)
+{
+    const int lane          = threadIdx.x & 31;
+    const int warps_per_blk = kThreads / 32;
+    for (int m = blockIdx.x * warps_per_blk + (threadIdx.x >> 5); m < M; m += gridDim.x * warps_per_blk)
+    {
+        const uint8_t *row  = a + static_cast<int64_t>(m) * lda;
+        const int      head = min(K, static_cast<int>((16 - (reinterpret_cast<uintptr_t>(row) & 15)) & 15));
+        int32_t        acc  = 0;
+        if (lane < head)
+        {
+            acc += load_q8(row, lane, is_signed);
+        }
+        const int    nvec = (K - head) >> 4;
+        const uint4 *v    = reinterpret_cast<const uint4 *>(row + head);
+        for (int i = lane; i < nvec; i += 32)
+        {
+            const uint4 q = __ldg(v + i);
+            acc           = sum4(q.x, is_signed, acc);
+            acc           = sum4(q.y, is_signed, acc);
+            acc           = sum4(q.z, is_signed, acc);
+            acc           = sum4(q.w, is_signed, acc);
+        }
+        const int tail0 = head + (nvec << 4);
+        if (tail0 + lane < K)
+        {
+            acc += load_q8(row, tail0 + lane, is_signed);
+        }
+        acc = warp_sum(acc);
+        if (lane == 0)
+        {
+            out[m] = acc * scalar;
+        }
+    }
+}
+
+// ---- colsum_B[n] += sum over a K-slab of B[k,n] --------------------------------------------------
+// Thread per group of 4 columns (one 32-bit load per row when aligned), grid.y splits K, integer
+// atomics combine the slabs (exact, order-independent).  out must be zero on entry; the scalar is
+// applied by scale_vector_kernel afterwards.
+// CpuGemmLowpMatrixBReductionKernel::run_internal (CpuGemmLowpMatrixReductionKernel.cpp:273-446).
+__global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const uint8_t *__restrict__ b, bool is_signed, int K,
+                                                               int N, int64_t ldb, int k_per_block,
+                                                               int32_t *__restrict__ out)
+{
+    const int n0 = (blockIdx.x * kThreads + threadIdx.x) * 4;
+    if (n0 >= N)
+    {
+        return;
+    }
+    const int  k0      = blockIdx.y * k_per_block;
+    const int  k1      = min(K, k0 + k_per_block);
+    const bool aligned = ((reinterpret_cast<uintptr_t>(b) | static_cast<uint64_t>(ldb)) & 3) == 0 && n0 + 4 <= N;
+    int32_t    s0 = 0, s1 = 0, s2 = 0, s3 = 0;
+    if (aligned)
+    {
+        for (int k = k0; k < k1; ++k)
+        {
+            const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(b + static_cast<int64_t>(k) * ldb + n0));
+            if (is_signed)
+            {
+                s0 += static_cast<int8_t>(w & 0xff);
+                s1 += static_cast<int8_t>((w >> 8) & 0xff);
+                s2 += static_cast<int8_t>((w >> 16) & 0xff);
+                s3 += static_cast<int8_t>(w >> 24);
+            }
+            else
+            {
+                s0 += w & 0xff;
+                s1 += (w >> 8) & 0xff;
+                s2 += (w >> 16) & 0xff;
+                s3 += w >> 24;
+            }
+        }
+    }
+    else
+    {
+        for (int k = k0; k < k1; ++k)
+        {
+            const uint8_t *row = b + static_cast<int64_t>(k) * ldb;
+            s0 += load_q8(row, n0, is_signed);
+            s1 += (n0 + 1 < N) ? load_q8(row, n0 + 1, is_signed) : 0;
+            s2 += (n0 + 2 < N) ? load_q8(row, n0 + 2, is_signed) : 0;
+            s3 += (n0 + 3 < N) ? load_q8(row, n0 + 3, is_signed) : 0;
+        }
+    }
+    atomicAdd(out + n0, s0);
+    if (n0 + 1 < N) atomicAdd(out + n0 + 1, s1);
+    if (n0 + 2 < N) atomicAdd(out + n0 + 2, s2);
+    if (n0 + 3 < N) atomicAdd(out + n0 + 3, s3);
+}
+
+__global__ void scale_vector_kernel(int32_t *v, int n, int32_t scalar)
+{
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n)
+    {
+        v[i] *= scalar;
+    }
+}
+
+// ---- prepare(): B [K,N] (N contiguous) -> Bt [N, ldbt] (K contiguous) + column sums -------------
+// 64 x 64 byte tiles through shared memory: reads are coalesced along N, writes along K.  Each block
+// also reduces its 64 rows per column and adds the partial sums with integer atomics, so B is read
+// exactly once for both products of prepare().  colsum (when not null) must be zero on entry.
+__global__ void __launch_bounds__(kThreads) transpose_colsum_kernel(const uint8_t *__restrict__ b, bool is_signed,
+                                                                    int K, int N, int64_t ldb,
+                                                                    uint8_t *__restrict__ bt, int64_t ldbt,
+                                                                    int32_t *__restrict__ colsum)
+{
+    __shared__ uint8_t tile[64][64 + 4];
+    const int          k0 = blockIdx.y * 64;
+    const int          n0 = blockIdx.x * 64;
+    const int          tx = threadIdx.x & 63; // fastest index
+    const int          ty = threadIdx.x >> 6; // 0..3
+#pragma unroll 4
+    for (int r = ty; r < 64; r += 4)
+    {
+        const int k = k0 + r, n = n0 + tx;
+        tile[r][tx] = (k < K && n < N) ? b[static_cast<int64_t>(k) * ldb + n] : 0;
+    }
+    __syncthreads();
+#pragma unroll 4
+    for (int r = ty; r < 64; r += 4)
+    {
+        const int n = n0 + r, k = k0 + tx;
+        if (n < N && k < K)
+        {
+            bt[static_cast<int64_t>(n) * ldbt + k] = tile[tx][r];
+        }
+    }
+    if (colsum != nullptr && threadIdx.x < 64)
+    {
+        const int n = n0 + threadIdx.x;
+        if (n < N)
+        {
+            int32_t s = 0;
+#pragma unroll 8
+            for (int r = 0; r < 64; ++r)
+            {
+                const uint8_t v = tile[r][threadIdx.x];
+                s += is_signed ? static_cast<int32_t>(static_cast<int8_t>(v)) : static_cast<int32_t>(v);
+            }
+            atomicAdd(colsum + n, s);
+        }
+    }
+}
+
+// ---- weights reshape: [OFM][K] -> [K][OFM] -------------------------------------------------------
+// CpuWeightsReshapeKernel::run_op (CpuWeightsReshapeKernel.cpp:121-183) for NHWC weights.
+__global__ void __launch_bounds__(kThreads) transpose_bytes_kernel(const uint8_t *__restrict__ src, int rows,
+                                                                   int cols, uint8_t *__restrict__ dst)
+{
+    __shared__ uint8_t tile[64][64 + 4];
+    const int          r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
+    const int          tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    for (int r = ty; r < 64; r += 4)
+    {
+        tile[r][tx] = (r0 + r < rows && c0 + tx < cols) ? src[static_cast<int64_t>(r0 + r) * cols + c0 + tx] : 0;
+    }
+    __syncthreads();
+    for (int c = ty; c < 64; c += 4)
+    {
+        if (c0 + c < cols && r0 + tx < rows)
+        {
+            dst[static_cast<int64_t>(c0 + c) * rows + r0 + tx] = tile[tx][c];
+        }
+    }
+}
+
+// ---- S32 offset contribution (output stage NONE) --------------------------------------------------
+// CpuGemmLowpOffsetContributionKernel (CpuGemmLowpOffsetContributionKernel.cpp:116-229).
+__global__ void __launch_bounds__(kThreads) offset_contribution_kernel(int32_t *__restrict__ mm, int M, int N,
+                                                                       int64_t ld_elems,
+                                                                       const int32_t *__restrict__ colsum,
+                                                                       const int32_t *__restrict__ rowsum,
+                                                                       int32_t a_off, int32_t b_off, int32_t k_term)
+{
+    const int64_t total = static_cast<int64_t>(M) * N;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * kThreads)
+    {
+        const int m = static_cast<int>(i / N), n = static_cast<int>(i % N);
+        int32_t   v = mm[m * ld_elems + n];
+        if (colsum != nullptr) v += a_off * colsum[n];
+        if (rowsum != nullptr) v += b_off * rowsum[m];
+        v += k_term;
+        mm[m * ld_elems + n] = v;
+    }
+}
+
+// ---- stand-alone output stage ---------------------------------------------------------------------
+// CpuGemmLowpQuantizeDownInt32To{Uint8,Int8}ScaleByFixedPointKernel::run_internal
+// (…ToUint8ScaleByFixedPointKernel.cpp:78-186).  Thread per 4 outputs: one 128-bit load, one 32-bit store.
+__global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *__restrict__ in, int64_t ld_in_elems,
+                                                                const int32_t *__restrict__ bias,
+                                                                uint8_t *__restrict__ out, int64_t ld_out, int M,
+                                                                int N, const int32_t *__restrict__ mults,
+                                                                const int32_t *__restrict__ shifts, int32_t mult,
+                                                                int32_t shift, int32_t offset, int32_t lo, int32_t hi,
+                                                                bool vec_ok)
+{
+    const int     groups_per_row = (N + 3) >> 2;
+    const int64_t total          = static_cast<int64_t>(M) * groups_per_row;
+    for (int64_t g = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; g < total;
+         g += static_cast<int64_t>(gridDim.x) * kThreads)
+    {
+        const int      m    = static_cast<int>(g / groups_per_row);
+        const int      n0   = static_cast<int>(g % groups_per_row) * 4;
+        const int32_t *src  = in + m * ld_in_elems + n0;
+        uint8_t       *dst  = out + m * ld_out + n0;
+        const bool     full = n0 + 4 <= N;
+        int32_t        v[4];
+        if (full && vec_ok)
+        {
+            const int4 q = *reinterpret_cast<const int4 *>(src);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = (n0 + j < N) ? src[j] : 0;
+        }
+        uint32_t packed = 0;
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            const int n = min(n0 + j, N - 1);
+            int32_t   x = v[j];
+            if (bias != nullptr) x += bias[n];
+            const int32_t mu = mults != nullptr ? mults[n] : mult;
+            const int32_t sh = shifts != nullptr ? shifts[n] : shift;
+            const int32_t r  = finalize(x, mu, max(-sh, 0), max(sh, 0), offset, lo, hi);
+            packed |= (static_cast<uint32_t>(r) & 0xffu) << (8 * j);
+        }
+        if (full && vec_ok)
+        {
+            *reinterpret_cast<uint32_t *>(dst) = packed;
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+                if (n0 + j < N) dst[j] = static_cast<uint8_t>(packed >> (8 * j));
+        }
+    }
+}
+
+// ---- NHWC im2col ------------------------------------------------------------------------------------
+// dst row m = (b, yo, xo) holds kh*kw taps of C bytes in (ky, kx, c) order; an out-of-image tap is
+// filled with the input zero point (directconv2d/impl.h:333-334).  VEC = bytes moved per thread.
+template <int VEC>
+__global__ void __launch_bounds__(kThreads) im2col_nhwc_kernel(const uint8_t *__restrict__ src,
+                                                               uint8_t *__restrict__ dst, int C, int W, int H,
+                                                               int64_t M, int kw, int kh, int sx, int sy, int pad_l,
+                                                               int pad_t, int dil_x, int dil_y, int Wo, int Ho,
+                                                               uint32_t pad_word, int64_t row_stride)
+{
+    const int     K             = kh * kw * C;
+    const int     units_per_row = static_cast<int>(row_stride / VEC);
+    const int64_t total         = M * units_per_row;
+    for (int64_t u = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; u < total;
+         u += static_cast<int64_t>(gridDim.x) * kThreads)
+    {
+        const int64_t m   = u / units_per_row;
+        const int     off = static_cast<int>(u % units_per_row) * VEC; // byte offset inside the row
+        uint8_t      *d   = dst + m * row_stride + off;
+        if (off >= K)
+        {
+            // zero the K padding that makes the row a multiple of 16 bytes
+            if (VEC == 16) *reinterpret_cast<uint4 *>(d) = make_uint4(0, 0, 0, 0);
+            else *d = 0;
+            continue;
+        }
+        const int tap = off / C, c = off % C;
+        const int ky = tap / kw, kx = tap % kw;
+        const int xo = static_cast<int>(m % Wo);
+        const int yo = static_cast<int>((m / Wo) % Ho);
+        const int64_t b = m / (static_cast<int64_t>(Wo) * Ho);
+        const int yi = yo * sy - pad_t + ky * dil_y;
+        const int xi = xo * sx - pad_l + kx * dil_x;
+        const bool inside = yi >= 0 && yi < H && xi >= 0 && xi < W;
+        if (VEC == 16)
+        {
+            uint4 q = make_uint4(pad_word, pad_word, pad_word, pad_word);
+            if (inside) q = __ldg(reinterpret_cast<const uint4 *>(src + ((b * H + yi) * W + xi) * C + c));
+            *reinterpret_cast<uint4 *>(d) = q;
+        }
+        else
+        {
+            *d = inside ? src[((b * H + yi) * W + xi) * C + c] : static_cast<uint8_t>(pad_word);
+        }
+    }
+}
+
+int grid_for(int64_t work_items, int sm_count, int per_thread = 1)
+{
+    const int64_t blocks = (work_items + static_cast<int64_t>(kThreads) * per_thread - 1) /
+                           (static_cast<int64_t>(kThreads) * per_thread);
+    const int64_t cap    = static_cast<int64_t>(sm_count) * 8; // whole multiples of the SM count
+    return static_cast<int>(blocks < 1 ? 1 : (blocks < cap ? blocks : cap));
+}
+} // namespace
+
+cugl_status launch_reduce_rows(cugl_context *ctx, const void *d_a, bool is_signed, int M, int K, int64_t lda,
+                               int32_t scalar, int32_t *d_out)
+{
+    if (M <= 0) return CUGL_SUCCESS;
+    const int rows_per_block = kThreads / 32;
+    const int blocks         = grid_for(static_cast<int64_t>(M) * 32, ctx->sm_count);
+    (void)rows_per_block;
+    reduce_rows_kernel<<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_a), is_signed, M, K, lda,
+                                                             scalar, d_out);
+    return check_cuda(ctx, cudaGetLastError(), "reduce_rows_kernel");
+}
+
+cugl_status launch_reduce_cols(cugl_context *ctx, const void *d_b, bool is_signed, int K, int N, int64_t ldb,
+                               int32_t scalar, int32_t *d_out)
+{
+    if (N <= 0) return CUGL_SUCCESS;
+    CUGL_CUDA_TRY(ctx, cudaMemsetAsync(d_out, 0, sizeof(int32_t) * N, ctx->stream));
+    if (K > 0)
+    {
+        const int gx = (N + kThreads * 4 - 1) / (kThreads * 4);
+        // enough K slabs to fill the machine a few times over, at least 32 rows each
+        int slabs = (ctx->sm_count * 4 + gx - 1) / gx;
+        slabs     = max(1, min(slabs, (K + 31) / 32));
+        const int k_per_block = (K + slabs - 1) / slabs;
+        slabs                 = (K + k_per_block - 1) / k_per_block;
+        reduce_cols_kernel<<<dim3(gx, slabs), kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_b),
+                                                                          is_signed, K, N, ldb, k_per_block, d_out);
+        CUGL_TRY(check_cuda(ctx, cudaGetLastError(), "reduce_cols_kernel"));
+    }
+    if (scalar != 1)
+    {
+        scale_vector_kernel<<<(N + 255) / 256, 256, 0, ctx->stream>>>(d_out, N, scalar);
+        CUGL_TRY(check_cuda(ctx, cudaGetLastError(), "scale_vector_kernel"));
+    }
+    return CUGL_SUCCESS;
+}
+
+cugl_status launch_transpose_colsum(cugl_context *ctx, const void *d_b, bool is_signed, int K, int N, int64_t ldb,
+                                    void *d_bt, int64_t ldbt, int32_t *d_colsum)
+{
+    if (d_colsum != nullptr)
+    {
+        CUGL_CUDA_TRY(ctx, cudaMemsetAsync(d_colsum, 0, sizeof(int32_t) * N, ctx->stream));
+    }
+    if (K <= 0 || N <= 0) return CUGL_SUCCESS;
+    dim3 grid((N + 63) / 64, (K + 63) / 64);
+    transpose_colsum_kernel<<<grid, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_b), is_signed, K, N,
+                                                                ldb, static_cast<uint8_t *>(d_bt), ldbt, d_colsum);
+    return check_cuda(ctx, cudaGetLastError(), "transpose_colsum_kernel");
+}
+
+cugl_status launch_transpose_bytes(cugl_context *ctx, const void *d_src, int rows, int cols, void *d_dst)
+{
+    if (rows <= 0 || cols <= 0) return CUGL_SUCCESS;
+    dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+    transpose_bytes_kernel<<<grid, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_src), rows, cols,
+                                                               static_cast<uint8_t *>(d_dst));
+    return check_cuda(ctx, cudaGetLastError(), "transpose_bytes_kernel");
+}
+
+cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, int N, int K, int64_t ld_bytes,
+                                       const int32_t *d_colsum, const int32_t *d_rowsum, int32_t a_off,
+                                       int32_t b_off)
+{
+    if (M <= 0 || N <= 0) return CUGL_SUCCESS;
+    const int32_t k_term = (a_off != 0 && b_off != 0)
+                               ? static_cast<int32_t>(static_cast<uint32_t>(a_off) * static_cast<uint32_t>(b_off) *
+                                                      static_cast<uint32_t>(K))
+                               : 0;
+    const int blocks = grid_for(static_cast<int64_t>(M) * N, ctx->sm_count, 4);
+    offset_contribution_kernel<<<blocks, kThreads, 0, ctx->stream>>>(d_mm, M, N, ld_bytes / 4,
+                                                                     a_off != 0 ? d_colsum : nullptr,
+                                                                     b_off != 0 ? d_rowsum : nullptr, a_off, b_off,
+                                                                     k_term);
+    return check_cuda(ctx, cudaGetLastError(), "offset_contribution_kernel");
+}
+
+cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
+                                void *d_out, int64_t ld_out_bytes, int M, int N, const int32_t *d_mults,
+                                const int32_t *d_shifts, int32_t mult, int32_t shift, int32_t offset, int32_t lo,
+                                int32_t hi)
+{
+    if (M <= 0 || N <= 0) return CUGL_SUCCESS;
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(d_in) | static_cast<uint64_t>(ld_in_bytes)) & 15) == 0 &&
+                        ((reinterpret_cast<uintptr_t>(d_out) | static_cast<uint64_t>(ld_out_bytes)) & 3) == 0;
+    const int blocks = grid_for(static_cast<int64_t>(M) * ((N + 3) / 4), ctx->sm_count, 2);
+    output_stage_kernel<<<blocks, kThreads, 0, ctx->stream>>>(d_in, ld_in_bytes / 4, d_bias,
+                                                              static_cast<uint8_t *>(d_out), ld_out_bytes, M, N,
+                                                              d_mults, d_shifts, mult, shift, offset, lo, hi, vec_ok);
+    return check_cuda(ctx, cudaGetLastError(), "output_stage_kernel");
+}
+
+cugl_status launch_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst, int C, int W, int H, int B, int kw,
+                               int kh, int sx, int sy, int pad_l, int pad_t, int dil_x, int dil_y, int Wo, int Ho,
+                               int pad_value, int64_t row_stride)
+{
+    const int64_t M = static_cast<int64_t>(B) * Ho * Wo;
+    if (M <= 0) return CUGL_SUCCESS;
+    const uint32_t pb       = static_cast<uint32_t>(pad_value) & 0xffu;
+    const uint32_t pad_word = pb * 0x01010101u;
+    const bool     vec16    = (C % 16 == 0) && (row_stride % 16 == 0) &&
+                       ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_dst)) & 15) == 0;
+    if (vec16)
+    {
+        const int blocks = grid_for(M * (row_stride / 16), ctx->sm_count, 2);
+        im2col_nhwc_kernel<16><<<blocks, kThreads, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), C, W, H, M, kw, kh, sx, sy, pad_l,
+            pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride);
+    }
+    else
+    {
+        const int blocks = grid_for(M * row_stride, ctx->sm_count, 4);
+        im2col_nhwc_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(
+            static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), C, W, H, M, kw, kh, sx, sy, pad_l,
+            pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride);
+    }
+    return check_cuda(ctx, cudaGetLastError(), "im2col_nhwc_kernel");
+}
+} // namespace cugl

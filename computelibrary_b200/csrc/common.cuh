@@ -1,0 +1,118 @@
+// Shared declarations of the cugl CUDA backend: context object, error plumbing and the integer
+// requantisation primitives every epilogue uses.
+#pragma once
+
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <cstdio>
+#include <string>
+
+#include "cugl.h"
+
+struct cugl_context
+{
+    int          device      = 0;
+    int          sm_count    = 0;
+    cudaStream_t stream      = nullptr;
+    bool         owns_stream = false;
+    int32_t     *d_status    = nullptr; // device word written by kernels whose bounded waits ran out
+    int32_t     *h_status    = nullptr; // pinned mirror read in cugl_sync
+    std::string  last_error;
+};
+
+namespace cugl
+{
+void        set_global_error(const std::string &msg);
+cugl_status fail(cugl_context *ctx, cugl_status code, const std::string &msg);
+cugl_status check_cuda(cugl_context *ctx, cudaError_t e, const char *what);
+
+#define CUGL_CUDA_TRY(ctx, expr)                                     \
+    do                                                               \
+    {                                                                \
+        cudaError_t _e = (expr);                                     \
+        if (_e != cudaSuccess)                                       \
+        {                                                            \
+            return ::cugl::check_cuda((ctx), _e, #expr);             \
+        }                                                            \
+    } while (0)
+
+#define CUGL_TRY(expr)                   \
+    do                                   \
+    {                                    \
+        cugl_status _s = (expr);         \
+        if (_s != CUGL_SUCCESS)          \
+        {                                \
+            return _s;                   \
+        }                                \
+    } while (0)
+
+// Device status codes (written to cugl_context::d_status)
+enum : int32_t
+{
+    DEV_OK               = 0,
+    DEV_TIMEOUT_PRODUCER = 1,
+    DEV_TIMEOUT_MMA      = 2,
+    DEV_TIMEOUT_EPILOGUE = 3,
+    DEV_TIMEOUT_DRAIN    = 4
+};
+
+// Everything an epilogue needs to turn a raw sum_k A*B accumulator into the function's output.
+// Follows CpuGemmLowpOffsetContributionOutputStageKernel.cpp:275-346 (term assembly) and
+// tests/validation/reference/GEMMLowp.cpp:122-157 (requantisation).
+struct EpilogueParams
+{
+    const int32_t *colsum; // [N]  sum_k B[k,n]           (nullptr when a_offset == 0)
+    const int32_t *rowsum; // [M]  sum_k A[m,k]           (nullptr when b_offset == 0)
+    const int32_t *bias;   // [N]                          (nullptr when absent)
+    const int32_t *mults;  // [N] per-channel multipliers  (nullptr: per-tensor)
+    const int32_t *shifts; // [N] per-channel shifts
+    int32_t        mult, shift;
+    int32_t        a_off, b_off;
+    int32_t        k_term;        // K * a_off * b_off
+    int32_t        result_offset; // gemmlowp_offset
+    int32_t        lo, hi;        // bounds already intersected with the 8-bit type range
+    int32_t        stage;         // cugl_stage
+    int32_t        out_signed;    // unused for S32
+};
+
+// SQDMULH: (int64(a) * b * 2) >> 32, i.e. floor(a*b / 2^31); saturates only for INT32_MIN^2.
+// tests/validation/reference/UtilsQuantizedAsymm.h:60-67.
+__device__ __forceinline__ int32_t sqdmulh(int32_t a, int32_t b)
+{
+    const int32_t  hi = __mulhi(a, b);
+    const uint32_t lo = static_cast<uint32_t>(a) * static_cast<uint32_t>(b);
+    int32_t        r  = static_cast<int32_t>(__funnelshift_l(lo, static_cast<uint32_t>(hi), 1));
+    if (a == INT32_MIN && b == INT32_MIN)
+    {
+        r = INT32_MAX;
+    }
+    return r;
+}
+
+// Requantise one accumulator.  left = max(-shift, 0), right = max(shift, 0); exactly one is non-zero,
+// so this single expression covers both branches of the reference:
+//   shift <  0 : sqdmulh(acc * (1 << -shift), mult)
+//   shift >= 0 : (sqdmulh(acc, mult) + (1 << (shift-1))) >> shift      (round-half-up, SRSHL)
+__device__ __forceinline__ int32_t requantize(int32_t acc, int32_t mult, int32_t left, int32_t right)
+{
+    const int32_t  x     = static_cast<int32_t>(static_cast<uint32_t>(acc) << left);
+    const int32_t  q     = sqdmulh(x, mult);
+    const uint32_t round = (1u << right) >> 1; // 0 when right == 0
+    return static_cast<int32_t>(static_cast<uint32_t>(q) + round) >> right;
+}
+
+__device__ __forceinline__ int32_t finalize(int32_t acc, int32_t mult, int32_t left, int32_t right, int32_t offset,
+                                            int32_t lo, int32_t hi)
+{
+    const int32_t r = static_cast<int32_t>(static_cast<uint32_t>(requantize(acc, mult, left, right)) +
+                                           static_cast<uint32_t>(offset));
+    return min(max(r, lo), hi);
+}
+
+__device__ __forceinline__ int32_t load_q8(const void *p, size_t idx, bool is_signed)
+{
+    return is_signed ? static_cast<int32_t>(static_cast<const int8_t *>(p)[idx])
+                     : static_cast<int32_t>(static_cast<const uint8_t *>(p)[idx]);
+}
+} // namespace cugl

@@ -1,0 +1,45 @@
+// Launchers of every CUDA kernel in the library (defined in bandwidth_kernels.cu, gemmlowp_simt.cu
+// and gemmlowp_tcgen05.cu).  All of them enqueue on ctx->stream and return without synchronising.
+#pragma once
+
+#include "common.cuh"
+
+namespace cugl
+{
+cugl_status launch_reduce_rows(cugl_context *ctx, const void *d_a, bool is_signed, int M, int K, int64_t lda,
+                               int32_t scalar, int32_t *d_out);
+cugl_status launch_reduce_cols(cugl_context *ctx, const void *d_b, bool is_signed, int K, int N, int64_t ldb,
+                               int32_t scalar, int32_t *d_out);
+cugl_status launch_transpose_colsum(cugl_context *ctx, const void *d_b, bool is_signed, int K, int N, int64_t ldb,
+                                    void *d_bt, int64_t ldbt, int32_t *d_colsum);
+cugl_status launch_transpose_bytes(cugl_context *ctx, const void *d_src, int rows, int cols, void *d_dst);
+cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, int N, int K, int64_t ld_bytes,
+                                       const int32_t *d_colsum, const int32_t *d_rowsum, int32_t a_off,
+                                       int32_t b_off);
+cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
+                                void *d_out, int64_t ld_out_bytes, int M, int N, const int32_t *d_mults,
+                                const int32_t *d_shifts, int32_t mult, int32_t shift, int32_t offset, int32_t lo,
+                                int32_t hi);
+cugl_status launch_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst, int C, int W, int H, int B, int kw,
+                               int kh, int sx, int sy, int pad_l, int pad_t, int dil_x, int dil_y, int Wo, int Ho,
+                               int pad_value, int64_t row_stride);
+
+// Operand description shared by both GEMM kernels.  B is always given K-major ("Bt": N rows of K
+// contiguous bytes), which is what prepare() produces.
+struct GemmOperands
+{
+    const void *a;   // [M][lda]   K contiguous
+    const void *bt;  // [N][ldbt]  K contiguous
+    void       *dst; // [M][ldd]   8-bit, or int32 when stage == NONE
+    int64_t     lda, ldbt, ldd; // bytes
+    int         M, N, K;
+    bool        a_signed, b_signed;
+};
+
+// Generic CUDA-core kernel: any shape, stride and alignment.
+cugl_status launch_gemmlowp_simt(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep);
+
+// TMA + tcgen05.mma.kind::i8 kernel.  Requires a, bt 16-byte aligned and lda, ldbt multiples of 16.
+bool        gemmlowp_tcgen05_supported(const GemmOperands &op);
+cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep);
+} // namespace cugl

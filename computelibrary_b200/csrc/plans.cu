@@ -1,0 +1,815 @@
+// Plan objects behind the cugl C ABI: the CUDA counterparts of CpuGemmLowpMatrixMultiplyCore
+// (configure / prepare / run with its auxiliary tensors) and CpuGemmConv2d (im2col + GEMMLowp), plus
+// the thin entry points of the stand-alone kernels.
+#include "kernels.cuh"
+
+#include <climits>
+#include <cstring>
+#include <vector>
+
+using namespace cugl;
+
+namespace
+{
+inline int64_t round_up(int64_t v, int64_t m)
+{
+    return (v + m - 1) / m * m;
+}
+inline bool is_q8(int32_t t)
+{
+    return t == CUGL_U8 || t == CUGL_S8;
+}
+
+// Device-side state one quantized GEMM needs besides its operands: the auxiliary tensors of
+// CpuGemmLowpMatrixMultiplyCore.h:144-155 (VectorSumCol, VectorSumRow, TmpB) and the per-channel
+// output-stage vectors.
+struct GemmCore
+{
+    cugl_context *ctx = nullptr;
+    int           M = 0, N = 0, K = 0;
+    bool          a_signed = false, b_signed = false;
+    int32_t       dst_dtype = CUGL_U8;
+    int32_t       a_off = 0, b_off = 0;
+    int32_t       stage = CUGL_STAGE_NONE;
+    bool          per_channel = false;
+    int32_t       mult = 0, shift = 0, result_offset = 0, min_bound = INT32_MIN, max_bound = INT32_MAX;
+    uint8_t      *d_bt     = nullptr; // [N][ldbt], K-major, zero padded
+    int64_t       ldbt     = 0;
+    int32_t      *d_colsum = nullptr; // [N]
+    int32_t      *d_rowsum = nullptr; // [M]
+    int32_t      *d_mults  = nullptr; // [N]
+    int32_t      *d_shifts = nullptr;
+    bool          force_simt = false;
+
+    cugl_status alloc(int n_b_copies, int rowsum_len)
+    {
+        ldbt = round_up(K, 128);
+        CUGL_TRY(cugl_malloc(ctx, static_cast<size_t>(ldbt) * N * n_b_copies, reinterpret_cast<void **>(&d_bt)));
+        CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * N * n_b_copies, reinterpret_cast<void **>(&d_colsum)));
+        CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * rowsum_len, reinterpret_cast<void **>(&d_rowsum)));
+        CUGL_TRY(cugl_memset(ctx, d_bt, 0, static_cast<size_t>(ldbt) * N * n_b_copies));
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status upload_stage_vectors(const int32_t *h_mults, const int32_t *h_shifts)
+    {
+        if (!per_channel)
+        {
+            return CUGL_SUCCESS;
+        }
+        if (d_mults == nullptr)
+        {
+            CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * N, reinterpret_cast<void **>(&d_mults)));
+            CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * N, reinterpret_cast<void **>(&d_shifts)));
+        }
+        // pageable source: the copy is staged before the call returns, so the caller's vectors may die
+        CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(d_mults, h_mults, sizeof(int32_t) * N, cudaMemcpyHostToDevice,
+                                           ctx->stream));
+        CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(d_shifts, h_shifts, sizeof(int32_t) * N, cudaMemcpyHostToDevice,
+                                           ctx->stream));
+        CUGL_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+        return CUGL_SUCCESS;
+    }
+
+    void release()
+    {
+        if (ctx == nullptr)
+        {
+            return;
+        }
+        cugl_free(ctx, d_bt);
+        cugl_free(ctx, d_colsum);
+        cugl_free(ctx, d_rowsum);
+        cugl_free(ctx, d_mults);
+        cugl_free(ctx, d_shifts);
+        d_bt = nullptr;
+        d_colsum = d_rowsum = d_mults = d_shifts = nullptr;
+    }
+
+    EpilogueParams epilogue(const int32_t *bias, int b_copy, int rowsum_off) const
+    {
+        EpilogueParams ep{};
+        ep.colsum = a_off != 0 ? d_colsum + static_cast<size_t>(b_copy) * N : nullptr;
+        ep.rowsum = b_off != 0 ? d_rowsum + rowsum_off : nullptr;
+        ep.bias   = bias;
+        ep.mults  = per_channel ? d_mults : nullptr;
+        ep.shifts = per_channel ? d_shifts : nullptr;
+        ep.mult   = mult;
+        ep.shift  = shift;
+        ep.a_off  = a_off;
+        ep.b_off  = b_off;
+        ep.k_term = (a_off != 0 && b_off != 0)
+                        ? static_cast<int32_t>(static_cast<uint32_t>(a_off) * static_cast<uint32_t>(b_off) *
+                                               static_cast<uint32_t>(K))
+                        : 0;
+        ep.result_offset  = result_offset;
+        const int32_t tlo = dst_dtype == CUGL_S8 ? -128 : 0;
+        const int32_t thi = dst_dtype == CUGL_S8 ? 127 : 255;
+        ep.lo             = min_bound > tlo ? min_bound : tlo;
+        ep.hi             = max_bound < thi ? max_bound : thi;
+        ep.stage          = stage;
+        ep.out_signed     = dst_dtype == CUGL_S8;
+        return ep;
+    }
+
+    bool uses_tcgen05(const GemmOperands &op) const
+    {
+        return !force_simt && gemmlowp_tcgen05_supported(op);
+    }
+
+    // rows x K product against B copy b_copy.
+    cugl_status gemm(const void *d_a, int64_t lda, int rows, void *d_dst, int64_t ldd, const int32_t *d_bias,
+                     int b_copy, int rowsum_off) const
+    {
+        GemmOperands op{};
+        op.a        = d_a;
+        op.bt       = d_bt + static_cast<size_t>(b_copy) * ldbt * N;
+        op.dst      = d_dst;
+        op.lda      = lda;
+        op.ldbt     = ldbt;
+        op.ldd      = ldd;
+        op.M        = rows;
+        op.N        = N;
+        op.K        = K;
+        op.a_signed = a_signed;
+        op.b_signed = b_signed;
+        if (b_off != 0)
+        {
+            CUGL_TRY(launch_reduce_rows(ctx, d_a, a_signed, rows, K, lda, 1, d_rowsum + rowsum_off));
+        }
+        const EpilogueParams ep = epilogue(d_bias, b_copy, rowsum_off);
+        return uses_tcgen05(op) ? launch_gemmlowp_tcgen05(ctx, op, ep) : launch_gemmlowp_simt(ctx, op, ep);
+    }
+};
+
+const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
+{
+    *code = CUGL_INVALID_ARGUMENT;
+    if (d == nullptr) return "descriptor is NULL";
+    if (d->M < 1 || d->N < 1 || d->K < 1 || d->batch < 1) return "M, N, K and batch must be positive";
+    if (!is_q8(d->a_dtype)) return "A must be QASYMM8 or QASYMM8_SIGNED";
+    if (!is_q8(d->b_dtype)) return "B must be QASYMM8, QASYMM8_SIGNED, QSYMM8 or QSYMM8_PER_CHANNEL";
+    if (d->stage != CUGL_STAGE_NONE && d->stage != CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT)
+    {
+        *code = CUGL_UNSUPPORTED_CONFIG;
+        return "only output stages NONE and QUANTIZE_DOWN_FIXEDPOINT are implemented";
+    }
+    if (d->stage == CUGL_STAGE_NONE)
+    {
+        if (d->dst_dtype != CUGL_S32) return "output stage NONE requires an S32 output";
+        if (d->has_bias) return "Bias addition not supported in NEGEMMLowpMatrixMultiplyCore for output S32";
+    }
+    else
+    {
+        if (!is_q8(d->dst_dtype)) return "a quantize-down output stage requires a QASYMM8 / QASYMM8_SIGNED output";
+        if (d->gemmlowp_min_bound > d->gemmlowp_max_bound) return "gemmlowp_min_bound > gemmlowp_max_bound";
+        if (d->is_quantized_per_channel)
+        {
+            if (d->h_gemmlowp_multipliers == nullptr || d->h_gemmlowp_shifts == nullptr)
+                return "per-channel output stage needs N multipliers and shifts";
+            if (d->dst_dtype != CUGL_U8 && d->N > 1 && d->b_offset != 0)
+                return "per-channel requantisation with a non-zero B offset is only defined for QASYMM8 output";
+        }
+    }
+    const int64_t dsz = d->dst_dtype == CUGL_S32 ? 4 : 1;
+    if (d->lda < d->K) return "lda is smaller than a row of A";
+    if (d->ldb < d->N) return "ldb is smaller than a row of B";
+    if (d->ldd < d->N * dsz) return "ldd is smaller than a row of the output";
+    if (d->dst_dtype == CUGL_S32 && (d->ldd % 4) != 0) return "ldd of an S32 output must be a multiple of 4";
+    if (d->batch > 1)
+    {
+        if (d->a_batch_stride < static_cast<int64_t>(d->M) * d->lda) return "a_batch_stride overlaps batches";
+        if (d->d_batch_stride < static_cast<int64_t>(d->M) * d->ldd) return "d_batch_stride overlaps batches";
+        if (d->b_batch_stride != 0 && d->b_batch_stride < static_cast<int64_t>(d->K) * d->ldb)
+            return "b_batch_stride overlaps batches";
+    }
+    *code = CUGL_SUCCESS;
+    return nullptr;
+}
+} // namespace
+
+struct cugl_gemm_plan
+{
+    cugl_context        *ctx = nullptr;
+    cugl_gemm_desc       desc{};
+    std::vector<int32_t> h_mults, h_shifts;
+    GemmCore             core;
+    bool                 collapse_batch = false; // batch folded into M (shared B, dense strides)
+    int                  b_copies       = 1;
+    bool                 prepared       = false;
+    // staging for the host-buffer entry point
+    void    *d_a_stage = nullptr, *d_dst_stage = nullptr;
+    int32_t *d_bias_stage = nullptr;
+};
+
+namespace
+{
+void apply_quant_fields(cugl_gemm_plan *p, const cugl_gemm_desc *d)
+{
+    GemmCore &c     = p->core;
+    c.a_off         = d->a_offset;
+    c.b_off         = d->b_offset;
+    c.stage         = d->stage;
+    c.per_channel   = d->stage != CUGL_STAGE_NONE && d->is_quantized_per_channel != 0;
+    c.mult          = d->gemmlowp_multiplier;
+    c.shift         = d->gemmlowp_shift;
+    c.result_offset = d->gemmlowp_offset;
+    c.min_bound     = d->gemmlowp_min_bound;
+    c.max_bound     = d->gemmlowp_max_bound;
+}
+
+cugl_status relayout_b(cugl_gemm_plan *p, const void *d_b)
+{
+    const cugl_gemm_desc &d = p->desc;
+    for (int i = 0; i < p->b_copies; ++i)
+    {
+        const uint8_t *src = static_cast<const uint8_t *>(d_b) + static_cast<int64_t>(i) * d.b_batch_stride;
+        CUGL_TRY(launch_transpose_colsum(p->ctx, src, p->core.b_signed, d.K, d.N, d.ldb,
+                                         p->core.d_bt + static_cast<size_t>(i) * p->core.ldbt * d.N, p->core.ldbt,
+                                         p->core.d_colsum + static_cast<size_t>(i) * d.N));
+    }
+    return CUGL_SUCCESS;
+}
+} // namespace
+
+extern "C"
+{
+    cugl_status cugl_gemmlowp_validate(const cugl_gemm_desc *desc, const char **reason)
+    {
+        cugl_status code;
+        const char *why = validate_gemm(desc, &code);
+        if (reason != nullptr)
+        {
+            *reason = why != nullptr ? why : "";
+        }
+        if (why != nullptr)
+        {
+            set_global_error(std::string("cugl_gemmlowp_validate: ") + why);
+        }
+        return code;
+    }
+
+    cugl_status cugl_gemmlowp_plan_create(cugl_context *ctx, const cugl_gemm_desc *desc, cugl_gemm_plan **out)
+    {
+        if (ctx == nullptr || out == nullptr)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_create: NULL argument");
+        }
+        *out = nullptr;
+        cugl_status code;
+        const char *why = validate_gemm(desc, &code);
+        if (why != nullptr)
+        {
+            return fail(ctx, code, std::string("cugl_gemmlowp_plan_create: ") + why);
+        }
+        auto *p = new cugl_gemm_plan();
+        p->ctx  = ctx;
+        p->desc = *desc;
+        if (desc->stage != CUGL_STAGE_NONE && desc->is_quantized_per_channel)
+        {
+            p->h_mults.assign(desc->h_gemmlowp_multipliers, desc->h_gemmlowp_multipliers + desc->N);
+            p->h_shifts.assign(desc->h_gemmlowp_shifts, desc->h_gemmlowp_shifts + desc->N);
+        }
+        p->desc.h_gemmlowp_multipliers = nullptr;
+        p->desc.h_gemmlowp_shifts      = nullptr;
+        p->collapse_batch = desc->batch > 1 && desc->b_batch_stride == 0 &&
+                            desc->a_batch_stride == static_cast<int64_t>(desc->M) * desc->lda &&
+                            desc->d_batch_stride == static_cast<int64_t>(desc->M) * desc->ldd;
+        p->b_copies = (desc->batch > 1 && desc->b_batch_stride != 0) ? desc->batch : 1;
+        GemmCore &c = p->core;
+        c.ctx       = ctx;
+        c.M         = desc->M;
+        c.N         = desc->N;
+        c.K         = desc->K;
+        c.a_signed  = desc->a_dtype == CUGL_S8;
+        c.b_signed  = desc->b_dtype == CUGL_S8;
+        c.dst_dtype = desc->dst_dtype;
+        apply_quant_fields(p, desc);
+        cugl_status s = c.alloc(p->b_copies, desc->M * desc->batch);
+        if (s == CUGL_SUCCESS && c.per_channel)
+        {
+            s = c.upload_stage_vectors(p->h_mults.data(), p->h_shifts.data());
+        }
+        if (s != CUGL_SUCCESS)
+        {
+            cugl_gemmlowp_plan_destroy(p);
+            return s;
+        }
+        *out = p;
+        return CUGL_SUCCESS;
+    }
+
+    void cugl_gemmlowp_plan_destroy(cugl_gemm_plan *plan)
+    {
+        if (plan == nullptr)
+        {
+            return;
+        }
+        cudaStreamSynchronize(plan->ctx->stream);
+        plan->core.release();
+        cugl_free(plan->ctx, plan->d_a_stage);
+        cugl_free(plan->ctx, plan->d_dst_stage);
+        cugl_free(plan->ctx, plan->d_bias_stage);
+        delete plan;
+    }
+
+    cugl_status cugl_gemmlowp_prepare(cugl_gemm_plan *plan, const void *d_b)
+    {
+        if (plan == nullptr || d_b == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_prepare: NULL argument");
+        }
+        CUGL_TRY(relayout_b(plan, d_b));
+        plan->prepared = true;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_run(cugl_gemm_plan *plan, const void *d_a, const void *d_b, const int32_t *d_bias,
+                                  void *d_dst)
+    {
+        if (plan == nullptr || d_a == nullptr || d_dst == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run: NULL argument");
+        }
+        const cugl_gemm_desc &d = plan->desc;
+        if (d.has_bias && d_bias == nullptr)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run: plan was configured with a bias");
+        }
+        if (!plan->prepared || !d.reshape_b_only_on_first_run)
+        {
+            if (d_b == nullptr)
+            {
+                return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                            "cugl_gemmlowp_run: B is required (not prepared, or B is not constant)");
+            }
+            CUGL_TRY(relayout_b(plan, d_b));
+            plan->prepared = true;
+        }
+        const int32_t *bias = d.has_bias ? d_bias : nullptr;
+        if (plan->collapse_batch || d.batch == 1)
+        {
+            return plan->core.gemm(d_a, d.lda, d.M * d.batch, d_dst, d.ldd, bias, 0, 0);
+        }
+        for (int i = 0; i < d.batch; ++i)
+        {
+            CUGL_TRY(plan->core.gemm(static_cast<const uint8_t *>(d_a) + i * d.a_batch_stride, d.lda, d.M,
+                                     static_cast<uint8_t *>(d_dst) + i * d.d_batch_stride, d.ldd, bias,
+                                     plan->b_copies > 1 ? i : 0, i * d.M));
+        }
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_run_host(cugl_gemm_plan *plan, const void *h_a, const int32_t *h_bias, void *h_dst)
+    {
+        if (plan == nullptr || h_a == nullptr || h_dst == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_host: NULL argument");
+        }
+        const cugl_gemm_desc &d   = plan->desc;
+        cugl_context         *ctx = plan->ctx;
+        if (!plan->prepared)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_host: call cugl_gemmlowp_prepare first");
+        }
+        const size_t a_bytes =
+            d.batch > 1 ? static_cast<size_t>(d.a_batch_stride) * d.batch : static_cast<size_t>(d.lda) * d.M;
+        const size_t d_bytes =
+            d.batch > 1 ? static_cast<size_t>(d.d_batch_stride) * d.batch : static_cast<size_t>(d.ldd) * d.M;
+        if (plan->d_a_stage == nullptr)
+        {
+            CUGL_TRY(cugl_malloc(ctx, a_bytes, &plan->d_a_stage));
+            CUGL_TRY(cugl_malloc(ctx, d_bytes, &plan->d_dst_stage));
+            CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * d.N, reinterpret_cast<void **>(&plan->d_bias_stage)));
+        }
+        CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_a_stage, h_a, a_bytes));
+        if (d.has_bias)
+        {
+            if (h_bias == nullptr)
+            {
+                return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_host: plan was configured with a bias");
+            }
+            CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_bias_stage, h_bias, sizeof(int32_t) * d.N));
+        }
+        CUGL_TRY(cugl_gemmlowp_run(plan, plan->d_a_stage, nullptr, plan->d_bias_stage, plan->d_dst_stage));
+        CUGL_TRY(cugl_memcpy_d2h(ctx, h_dst, plan->d_dst_stage, d_bytes));
+        return cugl_sync(ctx);
+    }
+
+    cugl_status cugl_gemmlowp_update_quantization(cugl_gemm_plan *plan, const cugl_gemm_desc *desc)
+    {
+        if (plan == nullptr || desc == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
+                        "cugl_gemmlowp_update_quantization: NULL argument");
+        }
+        const cugl_gemm_desc &o = plan->desc;
+        if (desc->M != o.M || desc->N != o.N || desc->K != o.K || desc->batch != o.batch ||
+            desc->a_dtype != o.a_dtype || desc->b_dtype != o.b_dtype || desc->dst_dtype != o.dst_dtype ||
+            desc->stage != o.stage || desc->is_quantized_per_channel != o.is_quantized_per_channel)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                        "cugl_gemmlowp_update_quantization: shapes, types and stage kind must not change");
+        }
+        cugl_status code;
+        const char *why = validate_gemm(desc, &code);
+        if (why != nullptr)
+        {
+            return fail(plan->ctx, code, std::string("cugl_gemmlowp_update_quantization: ") + why);
+        }
+        plan->desc.a_offset            = desc->a_offset;
+        plan->desc.b_offset            = desc->b_offset;
+        plan->desc.gemmlowp_multiplier = desc->gemmlowp_multiplier;
+        plan->desc.gemmlowp_shift      = desc->gemmlowp_shift;
+        plan->desc.gemmlowp_offset     = desc->gemmlowp_offset;
+        plan->desc.gemmlowp_min_bound  = desc->gemmlowp_min_bound;
+        plan->desc.gemmlowp_max_bound  = desc->gemmlowp_max_bound;
+        apply_quant_fields(plan, &plan->desc);
+        if (plan->core.per_channel)
+        {
+            plan->h_mults.assign(desc->h_gemmlowp_multipliers, desc->h_gemmlowp_multipliers + desc->N);
+            plan->h_shifts.assign(desc->h_gemmlowp_shifts, desc->h_gemmlowp_shifts + desc->N);
+            CUGL_TRY(plan->core.upload_stage_vectors(plan->h_mults.data(), plan->h_shifts.data()));
+        }
+        return CUGL_SUCCESS;
+    }
+
+    const char *cugl_gemmlowp_plan_kernel(const cugl_gemm_plan *plan)
+    {
+        if (plan == nullptr)
+        {
+            return "";
+        }
+        // the decision also depends on the alignment of A, only known at run(): assume an aligned base
+        GemmOperands op{};
+        op.a    = reinterpret_cast<const void *>(uintptr_t(256));
+        op.bt   = plan->core.d_bt;
+        op.lda  = plan->desc.lda;
+        op.ldbt = plan->core.ldbt;
+        op.M    = plan->desc.M;
+        op.N    = plan->desc.N;
+        op.K    = plan->desc.K;
+        return plan->core.uses_tcgen05(op) ? "tcgen05" : "simt";
+    }
+
+    cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_force_simt: NULL plan");
+        }
+        plan->core.force_simt = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan)
+    {
+        if (plan == nullptr)
+        {
+            return 0;
+        }
+        const cugl_gemm_desc &d       = plan->desc;
+        const int             n_gemms = (plan->collapse_batch || d.batch == 1) ? 1 : d.batch;
+        int                   n       = n_gemms * (1 + (plan->core.b_off != 0 ? 1 : 0));
+        if (!d.reshape_b_only_on_first_run)
+        {
+            n += plan->b_copies;
+        }
+        return n;
+    }
+
+    // ---- stand-alone kernels ---------------------------------------------------------------------
+    cugl_status cugl_reduce_rows(cugl_context *ctx, const void *d_a, int32_t dtype, int32_t M, int32_t K, int64_t lda,
+                                 int32_t scalar, int32_t *d_out)
+    {
+        if (ctx == nullptr || d_a == nullptr || d_out == nullptr || !is_q8(dtype) || M < 0 || K < 0 || lda < K)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_reduce_rows: bad argument");
+        }
+        return launch_reduce_rows(ctx, d_a, dtype == CUGL_S8, M, K, lda, scalar, d_out);
+    }
+
+    cugl_status cugl_reduce_cols(cugl_context *ctx, const void *d_b, int32_t dtype, int32_t K, int32_t N, int64_t ldb,
+                                 int32_t scalar, int32_t *d_out)
+    {
+        if (ctx == nullptr || d_b == nullptr || d_out == nullptr || !is_q8(dtype) || N < 0 || K < 0 || ldb < N)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_reduce_cols: bad argument");
+        }
+        return launch_reduce_cols(ctx, d_b, dtype == CUGL_S8, K, N, ldb, scalar, d_out);
+    }
+
+    cugl_status cugl_offset_contribution(cugl_context *ctx, int32_t *d_mm, int32_t M, int32_t N, int32_t K,
+                                         int64_t ld_bytes, const int32_t *d_colsum, const int32_t *d_rowsum,
+                                         int32_t a_offset, int32_t b_offset)
+    {
+        if (ctx == nullptr || d_mm == nullptr || M < 0 || N < 0 || ld_bytes < 4ll * N || (ld_bytes & 3) != 0 ||
+            (a_offset != 0 && d_colsum == nullptr) || (b_offset != 0 && d_rowsum == nullptr))
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_offset_contribution: bad argument");
+        }
+        return launch_offset_contribution(ctx, d_mm, M, N, K, ld_bytes, d_colsum, d_rowsum, a_offset, b_offset);
+    }
+
+    cugl_status cugl_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
+                                  void *d_out, int64_t ld_out_bytes, int32_t out_dtype, int32_t M, int32_t N,
+                                  const int32_t *d_multipliers, const int32_t *d_shifts, int32_t multiplier,
+                                  int32_t shift, int32_t n_mult, int32_t result_offset, int32_t min_bound,
+                                  int32_t max_bound)
+    {
+        if (ctx == nullptr || d_in == nullptr || d_out == nullptr || !is_q8(out_dtype) || M < 0 || N < 0 ||
+            ld_in_bytes < 4ll * N || (ld_in_bytes & 3) != 0 || ld_out_bytes < N)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage: bad argument");
+        }
+        if (min_bound > max_bound)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage: min_bound > max_bound");
+        }
+        const bool pc = n_mult > 1;
+        if (pc && (n_mult != N || d_multipliers == nullptr || d_shifts == nullptr))
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage: per-channel needs N multipliers and shifts");
+        }
+        const int32_t tlo = out_dtype == CUGL_S8 ? -128 : 0, thi = out_dtype == CUGL_S8 ? 127 : 255;
+        return launch_output_stage(ctx, d_in, ld_in_bytes, d_bias, d_out, ld_out_bytes, M, N,
+                                   pc ? d_multipliers : nullptr, pc ? d_shifts : nullptr, multiplier, shift,
+                                   result_offset, min_bound > tlo ? min_bound : tlo, max_bound < thi ? max_bound : thi);
+    }
+
+    cugl_status cugl_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst, int32_t C, int32_t W, int32_t H,
+                                 int32_t B, int32_t kw, int32_t kh, int32_t stride_x, int32_t stride_y,
+                                 int32_t pad_left, int32_t pad_top, int32_t dil_x, int32_t dil_y, int32_t Wo,
+                                 int32_t Ho, int32_t pad_value, int64_t row_stride)
+    {
+        if (ctx == nullptr || d_src == nullptr || d_dst == nullptr || C < 1 || W < 1 || H < 1 || B < 1 || kw < 1 ||
+            kh < 1 || stride_x < 1 || stride_y < 1 || dil_x < 1 || dil_y < 1 || Wo < 1 || Ho < 1 ||
+            row_stride < static_cast<int64_t>(kh) * kw * C)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_im2col_nhwc: bad argument");
+        }
+        return launch_im2col_nhwc(ctx, d_src, d_dst, C, W, H, B, kw, kh, stride_x, stride_y, pad_left, pad_top, dil_x,
+                                  dil_y, Wo, Ho, pad_value, row_stride);
+    }
+
+    cugl_status cugl_weights_reshape_nhwc(cugl_context *ctx, const void *d_w, void *d_dst, int32_t K, int32_t OFM)
+    {
+        if (ctx == nullptr || d_w == nullptr || d_dst == nullptr || K < 1 || OFM < 1)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_weights_reshape_nhwc: bad argument");
+        }
+        return launch_transpose_bytes(ctx, d_w, OFM, K, d_dst);
+    }
+}
+
+// ---------------------------------------------------------------------------------------------------
+// Convolution plan
+// ---------------------------------------------------------------------------------------------------
+struct cugl_conv_plan
+{
+    cugl_context        *ctx = nullptr;
+    cugl_conv_desc       desc{};
+    std::vector<int32_t> h_mults, h_shifts;
+    GemmCore             core;
+    int                  Wo = 0, Ho = 0;
+    int64_t              M = 0, K = 0, Kp = 0;
+    bool                 skip_im2col = false;
+    uint8_t             *d_cols      = nullptr; // [M][Kp] im2col matrix
+    bool                 prepared    = false;
+    void                *d_src_stage = nullptr, *d_dst_stage = nullptr;
+    int32_t             *d_bias_stage = nullptr;
+};
+
+namespace
+{
+void conv_out_dims(const cugl_conv_desc *d, int *Wo, int *Ho)
+{
+    // scaled_dimensions with DimensionRoundingType::FLOOR (src/core/Utils.cpp)
+    const int kw_eff = d->dil_x * (d->kw - 1) + 1;
+    const int kh_eff = d->dil_y * (d->kh - 1) + 1;
+    *Wo              = (d->W + d->pad_left + d->pad_right - kw_eff) / d->stride_x + 1;
+    *Ho              = (d->H + d->pad_top + d->pad_bottom - kh_eff) / d->stride_y + 1;
+}
+
+const char *validate_conv(const cugl_conv_desc *d, cugl_status *code)
+{
+    *code = CUGL_INVALID_ARGUMENT;
+    if (d == nullptr) return "descriptor is NULL";
+    if (d->B < 1 || d->H < 1 || d->W < 1 || d->C < 1 || d->OFM < 1 || d->kh < 1 || d->kw < 1)
+        return "tensor dimensions must be positive";
+    if (d->stride_x < 1 || d->stride_y < 1 || d->dil_x < 1 || d->dil_y < 1) return "stride and dilation must be >= 1";
+    if (d->pad_left < 0 || d->pad_right < 0 || d->pad_top < 0 || d->pad_bottom < 0) return "negative padding";
+    if (!is_q8(d->src_dtype) || !is_q8(d->w_dtype)) return "input and weights must be 8-bit quantized";
+    if (d->src_dtype == CUGL_S8 && d->w_dtype == CUGL_U8)
+        return "QASYMM8 weights with a QASYMM8_SIGNED input are not supported";
+    if (d->min_bound > d->max_bound) return "min_bound > max_bound";
+    if (d->is_quantized_per_channel)
+    {
+        if (d->h_gemmlowp_multipliers == nullptr || d->h_gemmlowp_shifts == nullptr)
+            return "per-channel weights need OFM multipliers and shifts";
+        if (d->w_zero_point != 0) return "QSYMM8_PER_CHANNEL weights are symmetric: w_zero_point must be 0";
+    }
+    int Wo, Ho;
+    conv_out_dims(d, &Wo, &Ho);
+    if (Wo < 1 || Ho < 1) return "kernel larger than the padded input";
+    if (static_cast<int64_t>(d->B) * Ho * Wo > INT32_MAX) return "too many output pixels";
+    *code = CUGL_SUCCESS;
+    return nullptr;
+}
+} // namespace
+
+extern "C"
+{
+    void cugl_conv2d_out_dims(const cugl_conv_desc *desc, int32_t *Wo, int32_t *Ho)
+    {
+        int w = 0, h = 0;
+        if (desc != nullptr)
+        {
+            conv_out_dims(desc, &w, &h);
+        }
+        if (Wo != nullptr) *Wo = w;
+        if (Ho != nullptr) *Ho = h;
+    }
+
+    cugl_status cugl_conv2d_validate(const cugl_conv_desc *desc, const char **reason)
+    {
+        cugl_status code;
+        const char *why = validate_conv(desc, &code);
+        if (reason != nullptr)
+        {
+            *reason = why != nullptr ? why : "";
+        }
+        if (why != nullptr)
+        {
+            set_global_error(std::string("cugl_conv2d_validate: ") + why);
+        }
+        return code;
+    }
+
+    cugl_status cugl_conv2d_plan_create(cugl_context *ctx, const cugl_conv_desc *desc, cugl_conv_plan **out)
+    {
+        if (ctx == nullptr || out == nullptr)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_create: NULL argument");
+        }
+        *out = nullptr;
+        cugl_status code;
+        const char *why = validate_conv(desc, &code);
+        if (why != nullptr)
+        {
+            return fail(ctx, code, std::string("cugl_conv2d_plan_create: ") + why);
+        }
+        auto *p = new cugl_conv_plan();
+        p->ctx  = ctx;
+        p->desc = *desc;
+        if (desc->is_quantized_per_channel)
+        {
+            p->h_mults.assign(desc->h_gemmlowp_multipliers, desc->h_gemmlowp_multipliers + desc->OFM);
+            p->h_shifts.assign(desc->h_gemmlowp_shifts, desc->h_gemmlowp_shifts + desc->OFM);
+        }
+        p->desc.h_gemmlowp_multipliers = nullptr;
+        p->desc.h_gemmlowp_shifts      = nullptr;
+        conv_out_dims(desc, &p->Wo, &p->Ho);
+        p->M  = static_cast<int64_t>(desc->B) * p->Ho * p->Wo;
+        p->K  = static_cast<int64_t>(desc->kh) * desc->kw * desc->C;
+        p->Kp = round_up(p->K, 16);
+        // CpuGemmConv2d.cpp:189-191: a 1x1, stride-1, unpadded NHWC convolution is a plain GEMM on the
+        // input tensor.  Kept only when the rows are already 16-byte multiples (TMA stride rule).
+        p->skip_im2col = desc->kw == 1 && desc->kh == 1 && desc->stride_x == 1 && desc->stride_y == 1 &&
+                         desc->pad_left == 0 && desc->pad_right == 0 && desc->pad_top == 0 &&
+                         desc->pad_bottom == 0 && (desc->C % 16) == 0;
+        GemmCore &c     = p->core;
+        c.ctx           = ctx;
+        c.M             = static_cast<int>(p->M);
+        c.N             = desc->OFM;
+        c.K             = static_cast<int>(p->K);
+        c.a_signed      = desc->src_dtype == CUGL_S8;
+        c.b_signed      = desc->w_dtype == CUGL_S8;
+        c.dst_dtype     = desc->src_dtype;
+        c.a_off         = -desc->src_zero_point; // CpuGemmConv2d.cpp:266-280: offsets are negated
+        c.b_off         = -desc->w_zero_point;
+        c.stage         = CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT;
+        c.per_channel   = desc->is_quantized_per_channel != 0;
+        c.mult          = desc->gemmlowp_multiplier;
+        c.shift         = desc->gemmlowp_shift;
+        c.result_offset = desc->dst_zero_point;
+        c.min_bound     = desc->min_bound;
+        c.max_bound     = desc->max_bound;
+        cugl_status s   = c.alloc(1, c.M);
+        if (s == CUGL_SUCCESS && c.per_channel)
+        {
+            s = c.upload_stage_vectors(p->h_mults.data(), p->h_shifts.data());
+        }
+        if (s == CUGL_SUCCESS && !p->skip_im2col)
+        {
+            s = cugl_malloc(ctx, static_cast<size_t>(p->M) * p->Kp, reinterpret_cast<void **>(&p->d_cols));
+        }
+        if (s != CUGL_SUCCESS)
+        {
+            cugl_conv2d_plan_destroy(p);
+            return s;
+        }
+        *out = p;
+        return CUGL_SUCCESS;
+    }
+
+    void cugl_conv2d_plan_destroy(cugl_conv_plan *plan)
+    {
+        if (plan == nullptr)
+        {
+            return;
+        }
+        cudaStreamSynchronize(plan->ctx->stream);
+        plan->core.release();
+        cugl_free(plan->ctx, plan->d_cols);
+        cugl_free(plan->ctx, plan->d_src_stage);
+        cugl_free(plan->ctx, plan->d_dst_stage);
+        cugl_free(plan->ctx, plan->d_bias_stage);
+        delete plan;
+    }
+
+    cugl_status cugl_conv2d_prepare(cugl_conv_plan *plan, const void *d_weights)
+    {
+        if (plan == nullptr || d_weights == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_prepare: NULL argument");
+        }
+        cugl_context *ctx = plan->ctx;
+        GemmCore     &c   = plan->core;
+        // NHWC weights [OFM][kh][kw][C] are already the K-major operand the tensor cores want: the
+        // reshape of CpuWeightsReshapeKernel followed by the pretranspose of the assembly path cancel out.
+        // Copy the rows into the zero-padded buffer and reduce each row (= column of the GEMM's B).
+        CUGL_CUDA_TRY(ctx, cudaMemcpy2DAsync(c.d_bt, c.ldbt, d_weights, plan->K, plan->K, c.N,
+                                             cudaMemcpyDeviceToDevice, ctx->stream));
+        CUGL_TRY(launch_reduce_rows(ctx, c.d_bt, c.b_signed, c.N, c.K, c.ldbt, 1, c.d_colsum));
+        plan->prepared = true;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_run(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias, void *d_dst)
+    {
+        if (plan == nullptr || d_src == nullptr || d_dst == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run: NULL argument");
+        }
+        const cugl_conv_desc &d = plan->desc;
+        if (!plan->prepared)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run: call cugl_conv2d_prepare first");
+        }
+        if (d.has_bias && d_bias == nullptr)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run: plan was configured with a bias");
+        }
+        const void *a   = d_src;
+        int64_t     lda = d.C;
+        if (!plan->skip_im2col)
+        {
+            CUGL_TRY(launch_im2col_nhwc(plan->ctx, d_src, plan->d_cols, d.C, d.W, d.H, d.B, d.kw, d.kh, d.stride_x,
+                                        d.stride_y, d.pad_left, d.pad_top, d.dil_x, d.dil_y, plan->Wo, plan->Ho,
+                                        d.src_zero_point, plan->Kp));
+            a   = plan->d_cols;
+            lda = plan->Kp;
+        }
+        return plan->core.gemm(a, lda, static_cast<int>(plan->M), d_dst, d.OFM, d.has_bias ? d_bias : nullptr, 0, 0);
+    }
+
+    cugl_status cugl_conv2d_run_host(cugl_conv_plan *plan, const void *h_src, const int32_t *h_bias, void *h_dst)
+    {
+        if (plan == nullptr || h_src == nullptr || h_dst == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run_host: NULL argument");
+        }
+        const cugl_conv_desc &d   = plan->desc;
+        cugl_context         *ctx = plan->ctx;
+        const size_t src_bytes    = static_cast<size_t>(d.B) * d.H * d.W * d.C;
+        const size_t dst_bytes    = static_cast<size_t>(plan->M) * d.OFM;
+        if (plan->d_src_stage == nullptr)
+        {
+            CUGL_TRY(cugl_malloc(ctx, src_bytes, &plan->d_src_stage));
+            CUGL_TRY(cugl_malloc(ctx, dst_bytes, &plan->d_dst_stage));
+            CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * d.OFM, reinterpret_cast<void **>(&plan->d_bias_stage)));
+        }
+        CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_src_stage, h_src, src_bytes));
+        if (d.has_bias)
+        {
+            if (h_bias == nullptr)
+            {
+                return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run_host: plan was configured with a bias");
+            }
+            CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_bias_stage, h_bias, sizeof(int32_t) * d.OFM));
+        }
+        CUGL_TRY(cugl_conv2d_run(plan, plan->d_src_stage, plan->d_bias_stage, plan->d_dst_stage));
+        CUGL_TRY(cugl_memcpy_d2h(ctx, h_dst, plan->d_dst_stage, dst_bytes));
+        return cugl_sync(ctx);
+    }
+
+    int cugl_conv2d_plan_launches(const cugl_conv_plan *plan)
+    {
+        if (plan == nullptr)
+        {
+            return 0;
+        }
+        return (plan->skip_im2col ? 0 : 1) + 1 + (plan->core.b_off != 0 ? 1 : 0);
+    }
+}

@@ -1,0 +1,266 @@
+/*
+ * cugl -- C ABI of the B200 (sm_100a) backend for Compute Library's quantized GEMM path.
+ *
+ * This header is the drop-in boundary: host C++ that keeps the arm_compute API
+ * (IFunction::configure/validate/run, ITensor/TensorInfo/QuantizationInfo, GEMMInfo,
+ * GEMMLowpOutputStageInfo) reaches the GPU only through these entry points.  Plain C types only.
+ * Every "d_" pointer is a device pointer on the context's device; every "h_" pointer is host memory.
+ * Work is enqueued on the context's stream and is asynchronous unless the comment says otherwise.
+ * There is no CPU fallback: a call that cannot run on the GPU returns an error.
+ *
+ * Reference citations are paths inside the Compute Library tree.
+ *
+ * Arithmetic contract (all two's-complement int32; identical to tests/validation/reference/GEMMLowp.cpp):
+ *   acc[m,n] = sum_k A[m,k]*B[k,n] + a_offset*colsum_B[n] + b_offset*rowsum_A[m] + K*a_offset*b_offset
+ *            ( == sum_k (A[m,k]+a_offset)*(B[k,n]+b_offset): offsets are ADDED as passed )
+ *   acc     += bias[n]
+ *   r        = shift < 0 ? sqdmulh(acc << -shift, mult) : (sqdmulh(acc, mult) + (1 << (shift-1))) >> shift
+ *              sqdmulh(a,b) = (int64(a)*b*2) >> 32  (floor, saturating only for INT32_MIN*INT32_MIN)
+ *   out      = clamp(r + result_offset, max(min_bound, type_min), min(max_bound, type_max))
+ */
+#ifndef CUGL_H
+#define CUGL_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define CUGL_API
+#else
+#define CUGL_API __attribute__((visibility("default")))
+#endif
+
+/* Status codes; the values mirror AclStatus (arm_compute/AclTypes.h:53-64) where a counterpart exists. */
+typedef enum cugl_status
+{
+    CUGL_SUCCESS            = 0,
+    CUGL_RUNTIME_ERROR      = 1, /* CUDA error or device-side time-out; see cugl_last_error_string */
+    CUGL_OUT_OF_MEMORY      = 2,
+    CUGL_UNIMPLEMENTED      = 3,
+    CUGL_UNSUPPORTED_TARGET = 4, /* no sm_100 device */
+    CUGL_INVALID_ARGUMENT   = 6,
+    CUGL_UNSUPPORTED_CONFIG = 8
+} cugl_status;
+
+/* 8-bit operand / output element types.  QASYMM8 -> U8; QASYMM8_SIGNED, QSYMM8, QSYMM8_PER_CHANNEL -> S8
+ * (arm_compute/core/CoreTypes.h DataType). */
+typedef enum cugl_dtype
+{
+    CUGL_U8  = 0,
+    CUGL_S8  = 1,
+    CUGL_S32 = 2
+} cugl_dtype;
+
+/* GEMMLowpOutputStageType (arm_compute/function_info/GEMMInfo.h:40-46).  Only NONE and
+ * QUANTIZE_DOWN_FIXEDPOINT are on the accelerated path. */
+typedef enum cugl_stage
+{
+    CUGL_STAGE_NONE                     = 0,
+    CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT = 2
+} cugl_stage;
+
+typedef struct cugl_context   cugl_context;   /* one per device + stream; not thread-safe */
+typedef struct cugl_gemm_plan cugl_gemm_plan; /* configured NEGEMMLowpMatrixMultiplyCore instance */
+typedef struct cugl_conv_plan cugl_conv_plan; /* configured NEGEMMConvolutionLayer instance */
+
+/* ------------------------------------------------------------------------------------------------
+ * Context, memory, stream.  Replaces the host TensorAllocator / MemoryManagerOnDemand / NEScheduler
+ * trio (src/runtime/TensorAllocator.cpp:133-146, arm_compute/runtime/IAllocator.h:39-61,
+ * src/runtime/IScheduler.cpp:58-180) by cudaMalloc-backed regions and one CUDA stream.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* stream: a cudaStream_t to enqueue on, or NULL to let the context create and own one. */
+CUGL_API cugl_status cugl_context_create(int device, void *stream, cugl_context **out);
+CUGL_API void        cugl_context_destroy(cugl_context *ctx);
+/* Text of the last error raised through this context (never NULL). ctx may be NULL: global last error. */
+CUGL_API const char *cugl_last_error_string(const cugl_context *ctx);
+CUGL_API void       *cugl_context_stream(const cugl_context *ctx);
+CUGL_API int         cugl_context_device(const cugl_context *ctx);
+CUGL_API int         cugl_context_sm_count(const cugl_context *ctx);
+
+/* IAllocator::allocate / free (arm_compute/runtime/IAllocator.h:39-61): device regions, 256-byte aligned. */
+CUGL_API cugl_status cugl_malloc(cugl_context *ctx, size_t bytes, void **d_ptr);
+CUGL_API cugl_status cugl_free(cugl_context *ctx, void *d_ptr);
+/* Pinned host staging memory for map()/unmap() style access (ICLTensor::map precedent,
+ * arm_compute/core/CL/ICLTensor.h:45-111). */
+CUGL_API cugl_status cugl_host_alloc(cugl_context *ctx, size_t bytes, void **h_ptr);
+CUGL_API cugl_status cugl_host_free(cugl_context *ctx, void *h_ptr);
+CUGL_API cugl_status cugl_memcpy_h2d(cugl_context *ctx, void *d_dst, const void *h_src, size_t bytes);
+CUGL_API cugl_status cugl_memcpy_d2h(cugl_context *ctx, void *h_dst, const void *d_src, size_t bytes);
+/* Strided 2-D copies for host tensors with padding (ITensorInfo strides_in_bytes /
+ * offset_first_element_in_bytes, arm_compute/core/ITensorInfo.h:197-211). */
+CUGL_API cugl_status cugl_memcpy2d_h2d(cugl_context *ctx, void *d_dst, size_t d_pitch, const void *h_src,
+                                       size_t h_pitch, size_t width_bytes, size_t rows);
+CUGL_API cugl_status cugl_memcpy2d_d2h(cugl_context *ctx, void *h_dst, size_t h_pitch, const void *d_src,
+                                       size_t d_pitch, size_t width_bytes, size_t rows);
+CUGL_API cugl_status cugl_memset(cugl_context *ctx, void *d_ptr, int value, size_t bytes);
+/* Blocks until the stream is idle; reports any asynchronous CUDA error or device-side time-out.
+ * (CLScheduler::sync precedent; IFunction::run of a device backend does not block,
+ * arm_compute/runtime/IFunction.h:46-51.) */
+CUGL_API cugl_status cugl_sync(cugl_context *ctx);
+
+/* ------------------------------------------------------------------------------------------------
+ * Host-side quantisation helpers (no GPU work).
+ * ---------------------------------------------------------------------------------------------- */
+
+/* quantization::calculate_quantized_multiplier (src/core/utils/quantization/AsymmHelpers.cpp:43-115).
+ * shift > 0: right shift; shift < 0: left shift. */
+CUGL_API cugl_status cugl_calculate_quantized_multiplier(float multiplier, int32_t *quant_multiplier,
+                                                         int32_t *shift);
+/* quantization::calculate_quantized_multipliers (AsymmHelpers.cpp:117-152): multiplier[i] =
+ * i_scale * w_scales[i] / o_scale in float32. */
+CUGL_API cugl_status cugl_calculate_quantized_multipliers(float i_scale, const float *w_scales, int n,
+                                                          float o_scale, int32_t *multipliers, int32_t *shifts);
+
+/* ------------------------------------------------------------------------------------------------
+ * NEGEMMLowpMatrixMultiplyCore (+ fused NEGEMMLowpOutputStage)
+ *   arm_compute/runtime/NEON/functions/NEGEMMLowpMatrixMultiplyCore.h:54-128
+ *   src/cpu/operators/CpuGemmLowpMatrixMultiplyCore.cpp:116-360 (configure), 362-645 (validate),
+ *   647-811 (run), 813-850 (prepare)
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct cugl_gemm_desc
+{
+    int32_t M, N, K;     /* dst is M x N; A is M x K (K contiguous); B is K x N (N contiguous) */
+    int32_t batch;       /* >= 1; A and dst slide along the batch, B only if b_batch_stride != 0 */
+    int64_t lda;         /* bytes between rows of A  (TensorInfo::strides_in_bytes()[1]) */
+    int64_t ldb;         /* bytes between rows of B */
+    int64_t ldd;         /* bytes between rows of dst */
+    int64_t a_batch_stride, b_batch_stride, d_batch_stride; /* bytes; b_batch_stride 0 = shared B */
+    int32_t a_dtype;     /* CUGL_U8 | CUGL_S8 */
+    int32_t b_dtype;     /* CUGL_U8 | CUGL_S8 */
+    int32_t dst_dtype;   /* CUGL_U8 | CUGL_S8 with a FIXEDPOINT stage, CUGL_S32 with stage NONE */
+    int32_t a_offset;    /* a->quantization_info().uniform().offset AS PASSED to the core (it is added);
+                            library callers pass the negated zero point (CpuGemmConv2d.cpp:266-280) */
+    int32_t b_offset;    /* likewise; must be 0 for per-channel B with a signed dst
+                            (CpuGemmLowpOffsetContributionOutputStageKernel.cpp:832-836) */
+    int32_t stage;       /* cugl_stage */
+    int32_t is_quantized_per_channel; /* GEMMLowpOutputStageInfo::is_quantized_per_channel */
+    int32_t gemmlowp_multiplier;      /* per-tensor multiplier / shift / offset / bounds: */
+    int32_t gemmlowp_shift;           /*   GEMMLowpOutputStageInfo, GEMMInfo.h:49-82 */
+    const int32_t *h_gemmlowp_multipliers; /* per-channel: N host values (read during plan_create / update) */
+    const int32_t *h_gemmlowp_shifts;
+    int32_t gemmlowp_offset;
+    int32_t gemmlowp_min_bound;
+    int32_t gemmlowp_max_bound;
+    int32_t has_bias;                 /* c != nullptr: S32 [N], only with an output stage */
+    int32_t reshape_b_only_on_first_run; /* GEMMInfo flag: B (and its column sums) are constant after prepare */
+} cugl_gemm_desc;
+
+/* static Status validate(a, b, c, output, gemm_info): pure host check, no GPU needed.
+ * Rules: CpuGemmLowpMatrixMultiplyCore.cpp:370-401 and
+ * CpuGemmLowpOffsetContributionOutputStageKernel.cpp:820-906.  reason (optional) receives a pointer to a
+ * static string. */
+CUGL_API cugl_status cugl_gemmlowp_validate(const cugl_gemm_desc *desc, const char **reason);
+/* configure(): validates, sizes the workspace (transposed B, column / row sums, per-channel vectors)
+ * and uploads the output-stage vectors.  Allocates device memory; no kernel is launched. */
+CUGL_API cugl_status cugl_gemmlowp_plan_create(cugl_context *ctx, const cugl_gemm_desc *desc,
+                                               cugl_gemm_plan **out);
+CUGL_API void        cugl_gemmlowp_plan_destroy(cugl_gemm_plan *plan);
+/* prepare(): re-lays B out K-major for the tensor cores and reduces its columns
+ * (CpuGemmLowpMatrixMultiplyCore.cpp:813-846).  After it, d_b may be freed when
+ * reshape_b_only_on_first_run is set. */
+CUGL_API cugl_status cugl_gemmlowp_prepare(cugl_gemm_plan *plan, const void *d_b);
+/* run(): d_b is only read when reshape_b_only_on_first_run == 0 (or prepare has not been called);
+ * d_bias may be NULL when has_bias == 0. */
+CUGL_API cugl_status cugl_gemmlowp_run(cugl_gemm_plan *plan, const void *d_a, const void *d_b,
+                                       const int32_t *d_bias, void *d_dst);
+/* Same function driven from host buffers: copies A (and bias) in, runs, copies dst out, and blocks
+ * until dst is valid.  h_a / h_dst follow lda / ldd of the descriptor. */
+CUGL_API cugl_status cugl_gemmlowp_run_host(cugl_gemm_plan *plan, const void *h_a, const int32_t *h_bias,
+                                            void *h_dst);
+/* update_quantization_parameters() (NEGEMMLowpMatrixMultiplyCore.cpp:118-159): re-reads offsets and the
+ * output-stage fields of desc; shapes and types must be unchanged. */
+CUGL_API cugl_status cugl_gemmlowp_update_quantization(cugl_gemm_plan *plan, const cugl_gemm_desc *desc);
+/* Which kernel the plan will launch: "tcgen05" (TMA + tcgen05.mma.kind::i8) or "simt" (shape / stride
+ * not expressible as a TMA tensor map). */
+CUGL_API const char *cugl_gemmlowp_plan_kernel(const cugl_gemm_plan *plan);
+/* Force the generic kernel (testing aid: both kernels must agree bit for bit). */
+CUGL_API cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on);
+/* Number of kernels one cugl_gemmlowp_run of this plan launches. */
+CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
+
+/* ------------------------------------------------------------------------------------------------
+ * Stand-alone kernels of the path.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* CpuGemmLowpMatrixAReductionKernel (src/cpu/kernels/CpuGemmLowpMatrixReductionKernel.cpp:133-204):
+ * d_out[m] = scalar * sum_k A[m,k]  (scalar 1 when GEMMLowpReductionKernelInfo::mul_by_scalar is false). */
+CUGL_API cugl_status cugl_reduce_rows(cugl_context *ctx, const void *d_a, int32_t dtype, int32_t M, int32_t K,
+                                      int64_t lda, int32_t scalar, int32_t *d_out);
+/* CpuGemmLowpMatrixBReductionKernel (…ReductionKernel.cpp:273-446): d_out[n] = scalar * sum_k B[k,n]. */
+CUGL_API cugl_status cugl_reduce_cols(cugl_context *ctx, const void *d_b, int32_t dtype, int32_t K, int32_t N,
+                                      int64_t ldb, int32_t scalar, int32_t *d_out);
+/* CpuGemmLowpOffsetContributionKernel (src/cpu/kernels/CpuGemmLowpOffsetContributionKernel.cpp:116-229):
+ * in place on an S32 [M,N] product.  d_colsum may be NULL when a_offset == 0, d_rowsum when b_offset == 0. */
+CUGL_API cugl_status cugl_offset_contribution(cugl_context *ctx, int32_t *d_mm, int32_t M, int32_t N, int32_t K,
+                                              int64_t ld_bytes, const int32_t *d_colsum, const int32_t *d_rowsum,
+                                              int32_t a_offset, int32_t b_offset);
+/* NEGEMMLowpOutputStage, QUANTIZE_DOWN_FIXEDPOINT (src/cpu/operators/CpuGemmLowpOutputStage.cpp:41-167,
+ * CpuGemmLowpQuantizeDownInt32ToUint8ScaleByFixedPointKernel.cpp:78-186): S32 [M,N] (+ S32 bias [N])
+ * -> U8 / S8 [M,N].  n_mult == 1: per-tensor (the NE function), n_mult == N: per-column device vectors. */
+CUGL_API cugl_status cugl_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes,
+                                       const int32_t *d_bias, void *d_out, int64_t ld_out_bytes, int32_t out_dtype,
+                                       int32_t M, int32_t N, const int32_t *d_multipliers, const int32_t *d_shifts,
+                                       int32_t multiplier, int32_t shift, int32_t n_mult, int32_t result_offset,
+                                       int32_t min_bound, int32_t max_bound);
+/* CpuIm2ColKernel, NHWC, 8-bit (src/cpu/kernels/CpuIm2ColKernel.cpp:296-420,
+ * src/cpu/kernels/directconv2d/impl.h:148-220,307-388): src [B][H][W][C] -> dst [B*Ho*Wo][row_stride]
+ * with K = kh*kw*C bytes per row in (ky,kx,c) order; out-of-image taps = pad_value (the input zero
+ * point); bytes K..row_stride-1 are zeroed. */
+CUGL_API cugl_status cugl_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst, int32_t C, int32_t W,
+                                      int32_t H, int32_t B, int32_t kw, int32_t kh, int32_t stride_x,
+                                      int32_t stride_y, int32_t pad_left, int32_t pad_top, int32_t dil_x,
+                                      int32_t dil_y, int32_t Wo, int32_t Ho, int32_t pad_value,
+                                      int64_t row_stride);
+/* CpuWeightsReshapeKernel (src/cpu/kernels/CpuWeightsReshapeKernel.cpp:121-183) for NHWC weights
+ * [OFM][kh][kw][C] -> [K][OFM] (row = (ky*kw+kx)*C+c). */
+CUGL_API cugl_status cugl_weights_reshape_nhwc(cugl_context *ctx, const void *d_w, void *d_dst, int32_t K,
+                                               int32_t OFM);
+
+/* ------------------------------------------------------------------------------------------------
+ * NEGEMMConvolutionLayer for 8-bit NHWC tensors
+ *   src/runtime/NEON/functions/NEGEMMConvolutionLayer.cpp:60-145
+ *   src/cpu/operators/CpuGemmConv2d.cpp:243-332 (configure_mm), 461-651 (configure), 910-1009 (run),
+ *   1011-1101 (prepare)
+ * ---------------------------------------------------------------------------------------------- */
+typedef struct cugl_conv_desc
+{
+    int32_t B, H, W, C;     /* src  TensorShape(C, W, H, B), NHWC */
+    int32_t OFM, kh, kw;    /* weights TensorShape(C, kw, kh, OFM) */
+    int32_t stride_x, stride_y;
+    int32_t pad_left, pad_right, pad_top, pad_bottom; /* PadStrideInfo, FLOOR rounding */
+    int32_t dil_x, dil_y;
+    int32_t src_dtype;      /* CUGL_U8 | CUGL_S8; dst has the same type */
+    int32_t w_dtype;        /* CUGL_U8 | CUGL_S8 */
+    int32_t src_zero_point; /* TRUE zero points: the layer negates them itself (CpuGemmConv2d.cpp:266-280) */
+    int32_t w_zero_point;   /* 0 for QSYMM8_PER_CHANNEL */
+    int32_t is_quantized_per_channel;
+    int32_t gemmlowp_multiplier, gemmlowp_shift;
+    const int32_t *h_gemmlowp_multipliers; /* OFM host values when per-channel */
+    const int32_t *h_gemmlowp_shifts;
+    int32_t dst_zero_point; /* gemmlowp_offset */
+    int32_t min_bound, max_bound; /* from get_quantized_activation_min_max (src/core/Utils.cpp:442-460) */
+    int32_t has_bias;
+} cugl_conv_desc;
+
+CUGL_API cugl_status cugl_conv2d_validate(const cugl_conv_desc *desc, const char **reason);
+CUGL_API cugl_status cugl_conv2d_plan_create(cugl_context *ctx, const cugl_conv_desc *desc, cugl_conv_plan **out);
+CUGL_API void        cugl_conv2d_plan_destroy(cugl_conv_plan *plan);
+/* prepare(): weights -> K-major GEMM operand + column sums (weights may be freed afterwards). */
+CUGL_API cugl_status cugl_conv2d_prepare(cugl_conv_plan *plan, const void *d_weights);
+/* run(): im2col (skipped for 1x1 / stride 1 / no pad, CpuGemmConv2d.cpp:189-191) + fused GEMMLowp.
+ * dst is [B][Ho][Wo][OFM]. */
+CUGL_API cugl_status cugl_conv2d_run(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias, void *d_dst);
+CUGL_API cugl_status cugl_conv2d_run_host(cugl_conv_plan *plan, const void *h_src, const int32_t *h_bias,
+                                          void *h_dst);
+CUGL_API void cugl_conv2d_out_dims(const cugl_conv_desc *desc, int32_t *Wo, int32_t *Ho);
+CUGL_API int  cugl_conv2d_plan_launches(const cugl_conv_plan *plan);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CUGL_H */

@@ -1,0 +1,117 @@
+"""Seeded synthetic inputs and small drivers shared by the tests (and by bench.py / smoke())."""
+from __future__ import annotations
+
+import numpy as np
+
+from computelibrary_b200 import capi
+
+NP_OF = {capi.U8: np.uint8, capi.S8: np.int8, capi.S32: np.int32}
+CODE_OF = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8, np.dtype(np.int32): capi.S32}
+
+
+from computelibrary_b200.workloads import (config1, config2, config3, config5, q8_uniform,  # noqa: F401,E402
+                                           type_range)
+
+
+def f32_mults(port, i_scale, w_scales, o_scale):
+    return port.calculate_quantized_multipliers(np.float32(i_scale), np.asarray(w_scales, np.float32),
+                                                np.float32(o_scale))
+
+
+# ---- GPU drivers (torch tensors as device buffers) ------------------------------------------------------
+def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype, force_simt=False,
+                 b_constant=True, runs=1, ldd_pad=0):
+    """Fused NEGEMMLowpMatrixMultiplyCore through the C ABI.  mult/shift scalars -> per-tensor; arrays ->
+    per-channel.  out_dtype np.int32 -> output stage NONE.  Returns (numpy result, kernel name)."""
+    import torch
+    a = np.ascontiguousarray(a)
+    b = np.ascontiguousarray(b)
+    batched = a.ndim == 3
+    batch = a.shape[0] if batched else 1
+    M, K = a.shape[-2:]
+    N = b.shape[-1]
+    out_dtype = np.dtype(out_dtype)
+    dsz = out_dtype.itemsize
+    per_channel = np.ndim(mult) > 0
+    stage = capi.STAGE_NONE if out_dtype == np.int32 else capi.STAGE_FIXEDPOINT
+    ldd = (N + ldd_pad) * dsz
+    desc, keep = capi.make_gemm_desc(
+        M, N, K, CODE_OF[a.dtype], CODE_OF[b.dtype], CODE_OF[out_dtype], a_off, b_off, stage,
+        multiplier=0 if per_channel else int(mult), shift=0 if per_channel else int(shift),
+        multipliers=mult if per_channel else None, shifts=shift if per_channel else None, offset=offset,
+        min_bound=lo, max_bound=hi, has_bias=bias is not None, batch=batch, ldd=ldd,
+        b_batch_stride=(K * N if b.ndim == 3 else 0), b_constant=b_constant)
+    plan = capi.GemmPlan(ctx, desc, keep)
+    if force_simt:
+        plan.force_simt(True)
+    da = torch.from_numpy(a.view(np.uint8)).cuda()
+    db = torch.from_numpy(b.view(np.uint8)).cuda()
+    dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.int32)).cuda() if bias is not None else None
+    canary = 0xA5
+    dd = torch.full((batch * M * ldd,), canary, dtype=torch.uint8, device="cuda")
+    if b_constant:
+        plan.prepare(db)
+    for _ in range(runs):
+        plan.run(da, None if b_constant else db, dbias, dd)
+    ctx.sync()
+    raw = dd.cpu().numpy().reshape(batch, M, ldd)
+    if ldd_pad:
+        assert (raw[:, :, N * dsz:] == canary).all(), "kernel wrote into the row padding"
+    out = np.ascontiguousarray(raw[:, :, :N * dsz]).view(out_dtype).reshape(batch, M, N)
+    kernel = plan.kernel
+    plan.close()
+    return (out if batched else out[0]), kernel
+
+
+# ---- inputs of the committed golden fixtures (outputs live in tests/golden/*.npz) -------------------------
+GOLDEN_GEMM_SHAPES = [(1, 1, 1), (21, 13, 33), (23, 31, 37), (32, 72, 4), (1, 129, 257), (130, 1, 40), (72, 33, 47),
+                      (33, 67, 133)]
+GOLDEN_GEMM_TYPES = [(np.uint8, np.uint8), (np.int8, np.int8), (np.uint8, np.int8)]
+
+
+def golden_gemm_cases():
+    """Yields dicts with the seeded inputs of every GEMMLowp golden case (odd M/N/K as in the reference's
+    Small/LargeGEMMLowpDataset: M=1, N=1, K not a multiple of 16 or 32)."""
+    for si, (M, N, K) in enumerate(GOLDEN_GEMM_SHAPES):
+        for ci, (ad, bd) in enumerate(GOLDEN_GEMM_TYPES):
+            r = np.random.default_rng(1000 + 10 * si + ci)
+            a, b = q8_uniform(r, (M, K), ad), q8_uniform(r, (K, N), bd)
+            ao, bo = int(r.integers(-255, 256)), int(r.integers(-255, 256))
+            bias = r.integers(-3000, 3001, N).astype(np.int32)
+            mult = r.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+            shift = r.integers(0, 14, N).astype(np.int32)
+            od = np.uint8 if ad == np.uint8 else np.int8
+            lo, hi = type_range(od)
+            yield dict(key=f"g{si}_{ci}", a=a, b=b, a_off=ao, b_off=bo, bias=bias, mult=mult, shift=shift,
+                       out_dtype=od, lo=lo, hi=hi, pt_offset=3, pc_offset=-2)
+
+
+GOLDEN_CONV_GEOMS = [(3, 3, 1, 1, (1, 1, 1, 1)), (1, 1, 1, 1, (0, 0, 0, 0)), (3, 2, 2, 1, (0, 1, 1, 0)),
+                     (5, 5, 2, 2, (2, 2, 2, 2)), (3, 3, 2, 2, (0, 1, 0, 1))]
+GOLDEN_CONV_TYPES = [(np.uint8, np.uint8, False), (np.uint8, np.int8, True), (np.int8, np.int8, False),
+                     (np.int8, np.int8, True)]
+GOLDEN_CONV_SCALES = (np.float32(0.03), np.float32(0.4))  # input scale, output scale
+
+
+def golden_conv_cases():
+    """Seeded inputs of the convolution golden cases: NHWC src [2,9,8,C], weights [7,kh,kw,C]."""
+    for ci, (kw, kh, sx, sy, pad) in enumerate(GOLDEN_CONV_GEOMS):
+        for ti, (sd, wd, pc) in enumerate(GOLDEN_CONV_TYPES):
+            r = np.random.default_rng(5000 + 10 * ci + ti)
+            B, H, W, Cc, OFM = 2, 9, 8, (16 if ci % 2 == 0 else 5), 7
+            src = q8_uniform(r, (B, H, W, Cc), sd)
+            wgt = q8_uniform(r, (OFM, kh, kw, Cc), wd, np.iinfo(wd).min + 1)
+            bias = r.integers(-500, 501, OFM).astype(np.int32)
+            ws = r.uniform(2e-3, 8e-3, OFM if pc else 1).astype(np.float32)
+            in_zp = int(r.integers(0, 256)) if sd == np.uint8 else int(r.integers(-128, 128))
+            w_zp = 0 if pc else (int(r.integers(0, 256)) if wd == np.uint8 else int(r.integers(-128, 128)))
+            out_zp = int(r.integers(0, 40)) if sd == np.uint8 else int(r.integers(-20, 20))
+            yield dict(key=f"c{ci}_{ti}", src=src, weights=wgt, bias=bias, w_scales=ws, in_zp=in_zp, w_zp=w_zp,
+                       out_zp=out_zp, stride=(sx, sy), pad=pad, kw=kw, kh=kh, per_channel=pc)
+
+
+def golden_im2col_cases():
+    for ci, (kw, kh, sx, sy, pad) in enumerate(GOLDEN_CONV_GEOMS):
+        r = np.random.default_rng(7000 + ci)
+        src = q8_uniform(r, (2, 9, 8, 16 if ci % 2 == 0 else 5), np.uint8)
+        yield dict(key=f"im2col{ci}", src=src, kw=kw, kh=kh, stride=(sx, sy), pad=pad, zp=77)

@@ -1,0 +1,102 @@
+"""NEGEMMConvolutionLayer on the GPU (im2col + fused GEMMLowp through the C ABI) against the reference-made
+golden fixtures and the oracle: tolerance 0, as tests/validation/NEON/ConvolutionLayer.cpp:102-103."""
+import os
+
+import numpy as np
+import pytest
+
+from computelibrary_b200 import capi
+from helpers import GOLDEN_CONV_SCALES, config3, f32_mults, golden_conv_cases, q8_uniform, type_range
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
+
+
+def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1)):
+    import torch
+    B, H, W, Cc = src.shape
+    OFM, kh, kw, _ = weights.shape
+    pc = np.ndim(mult) > 0 and len(mult) > 1
+    desc, keep = capi.make_conv_desc(B, H, W, Cc, OFM, kh, kw, stride, pad, dilation, CODE[src.dtype],
+                                     CODE[weights.dtype], in_zp, w_zp,
+                                     multiplier=0 if pc else int(np.ravel(mult)[0]),
+                                     shift=0 if pc else int(np.ravel(shift)[0]),
+                                     multipliers=mult if pc else None, shifts=shift if pc else None, dst_zp=out_zp,
+                                     min_bound=lo, max_bound=hi, has_bias=bias is not None)
+    plan = capi.ConvPlan(ctx, desc, keep)
+    wo, ho = plan.out_dims()
+    d_src = torch.from_numpy(src.view(np.uint8)).cuda()
+    d_w = torch.from_numpy(weights.view(np.uint8)).cuda()
+    d_b = torch.from_numpy(bias).cuda() if bias is not None else None
+    d_dst = torch.empty((B, ho, wo, OFM), dtype=torch.uint8, device="cuda")
+    plan.prepare(d_w)
+    del d_w  # weights may be released after prepare()
+    plan.run(d_src, d_b, d_dst)
+    plan.run(d_src, d_b, d_dst)
+    ctx.sync()
+    out = d_dst.cpu().numpy().view(src.dtype)
+    plan.close()
+    return out
+
+
+def test_conv_golden(ctx, port):
+    gold = np.load(os.path.join(GOLDEN, "conv_golden.npz"))
+    i_scale, o_scale = GOLDEN_CONV_SCALES
+    for c in golden_conv_cases():
+        mult, shift = f32_mults(port, i_scale, c["w_scales"], o_scale)
+        lo, hi = type_range(c["src"].dtype)
+        out = gpu_conv(ctx, c["src"], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], c["w_zp"], mult,
+                       shift, c["out_zp"], lo, hi)
+        assert np.array_equal(out, gold[c["key"] + "_out"]), c["key"]
+
+
+@pytest.mark.parametrize("geom", [(3, 1, 1), (1, 1, 0), (3, 2, 1), (7, 2, 3), (1, 2, 0)])
+@pytest.mark.parametrize("act", ["none", "relu", "lu_bounded"])
+def test_conv_vs_oracle(ctx, port, geom, act):
+    """ResNet-like layer shapes with the three activation variants the reference tests."""
+    k, s, p = geom
+    rng = np.random.default_rng(k * 100 + s * 10 + p)
+    Cc = 3 if k == 7 else 64
+    src = q8_uniform(rng, (3, 20, 20, Cc), np.uint8)
+    wgt = q8_uniform(rng, (96, k, k, Cc), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, 96).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), 96)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.03, ws, 0.05)
+    out_zp = 10
+    lo, hi = {"none": (0, 255), "relu": (out_zp, 255), "lu_bounded": (out_zp + 2, out_zp + 120)}[act]
+    got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), 128, 0, mult, shift, out_zp, lo, hi)
+    want = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), 128, 0, mult, shift, out_zp, lo, hi)
+    assert np.array_equal(got, want)
+
+
+def test_conv_asymmetric_weights_and_signed(ctx, port):
+    rng = np.random.default_rng(77)
+    src = q8_uniform(rng, (2, 15, 17, 32), np.int8)
+    wgt = q8_uniform(rng, (40, 3, 3, 32), np.int8)
+    bias = rng.integers(-500, 501, 40).astype(np.int32)
+    mult, shift = f32_mults(port, 0.03, [0.004], 0.3)
+    got = gpu_conv(ctx, src, wgt, bias, (1, 1), (1, 1, 1, 1), -5, 9, mult, shift, -3, -128, 127)
+    want = port.conv2d_nhwc(src, wgt, bias, (1, 1), (1, 1, 1, 1), -5, 9, mult, shift, -3, -128, 127)
+    assert np.array_equal(got, want)
+    srcu = q8_uniform(rng, (2, 15, 17, 32), np.uint8)
+    wgtu = q8_uniform(rng, (40, 3, 3, 32), np.uint8)
+    got = gpu_conv(ctx, srcu, wgtu, bias, (2, 2), (0, 1, 0, 1), 130, 120, mult, shift, 4, 0, 255)
+    want = port.conv2d_nhwc(srcu, wgtu, bias, (2, 2), (0, 1, 0, 1), 130, 120, mult, shift, 4, 0, 255)
+    assert np.array_equal(got, want)
+
+
+def test_config3_full_size(ctx, port):
+    """BASELINE config 3 at full size: batch 32, 56x56x64 -> 64, 3x3 s1 p1, fused ReLU; exact on a batch sample
+    and identical per image whatever the batch it is computed in (batch sharding needs no exchange)."""
+    c = config3()
+    mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])
+    out = gpu_conv(ctx, c["src"], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], 0, mult, shift,
+                   c["out_zp"], c["lo"], c["hi"])
+    want = port.conv2d_nhwc(c["src"][:2], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], 0, mult, shift,
+                            c["out_zp"], c["lo"], c["hi"])
+    assert np.array_equal(out[:2], want)
+    shard = gpu_conv(ctx, c["src"][28:], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], 0, mult, shift,
+                     c["out_zp"], c["lo"], c["hi"])
+    assert np.array_equal(shard, out[28:])
+    assert 0.01 < (out == 0).mean() < 0.99

@@ -1,0 +1,227 @@
+"""Parity of the CUDA GEMMLowp path (through the C ABI) with the oracle: bit-exact, tolerance 0."""
+import os
+
+import numpy as np
+import pytest
+
+from computelibrary_b200 import capi
+from helpers import (config1, config2, config5, f32_mults, golden_gemm_cases, gpu_gemmlowp, q8_uniform, type_range)
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+
+
+@pytest.fixture(scope="module")
+def gemm_golden():
+    return np.load(os.path.join(GOLDEN, "gemmlowp_golden.npz"))
+
+
+@pytest.mark.parametrize("force_simt", [False, True])
+def test_golden_cases(ctx, gemm_golden, force_simt):
+    """Reference-produced outputs on odd shapes (M=1, N=1, K not a multiple of 16): S32 core, per-tensor and
+    per-channel fused output stage, for u8xu8, s8xs8 and u8xs8."""
+    for g in golden_gemm_cases():
+        acc, _ = gpu_gemmlowp(ctx, g["a"], g["b"], None, g["a_off"], g["b_off"], 0, 0, 0, 0, 0, np.int32,
+                              force_simt=force_simt)
+        assert np.array_equal(acc, gemm_golden[g["key"] + "_acc"]), g["key"]
+        pt, _ = gpu_gemmlowp(ctx, g["a"], g["b"], g["bias"], g["a_off"], g["b_off"], int(g["mult"][0]),
+                             int(g["shift"][0]), g["pt_offset"], g["lo"], g["hi"], g["out_dtype"],
+                             force_simt=force_simt)
+        assert np.array_equal(pt, gemm_golden[g["key"] + "_pt"]), g["key"]
+        pc, _ = gpu_gemmlowp(ctx, g["a"], g["b"], g["bias"], g["a_off"], 0, g["mult"], g["shift"], g["pc_offset"],
+                             g["lo"], g["hi"], g["out_dtype"], force_simt=force_simt)
+        assert np.array_equal(pc, gemm_golden[g["key"] + "_pc"]), g["key"]
+
+
+def test_config1_fused_and_two_stage(ctx, port, gemm_golden):
+    """BASELINE config 1 against the reference-produced fixture, fused and as core(S32) + output stage."""
+    import torch
+    c1 = config1()
+    qm, sh = capi.calculate_quantized_multiplier(c1["real_multiplier"])
+    assert (qm, sh) == (1099511552, 8)
+    out, kernel = gpu_gemmlowp(ctx, c1["a"], c1["b"], c1["bias"], c1["a_off"], c1["b_off"], qm, sh, c1["offset"],
+                               c1["lo"], c1["hi"], np.uint8)
+    assert kernel == "tcgen05"
+    assert np.array_equal(out, gemm_golden["c1_out"])
+    acc, _ = gpu_gemmlowp(ctx, c1["a"], c1["b"], None, c1["a_off"], c1["b_off"], 0, 0, 0, 0, 0, np.int32)
+    assert np.array_equal(acc, gemm_golden["c1_acc"])
+    # NEGEMMLowpOutputStage on the S32 result (examples/neon_gemm_qasymm8.cpp:224-239)
+    d_acc = torch.from_numpy(acc).cuda()
+    d_bias = torch.from_numpy(c1["bias"]).cuda()
+    d_out = torch.empty((64, 128), dtype=torch.uint8, device="cuda")
+    ctx.output_stage(d_acc, 128 * 4, d_bias, d_out, 128, capi.U8, 64, 128, None, None, qm, sh, 1, c1["offset"],
+                     c1["lo"], c1["hi"])
+    ctx.sync()
+    assert np.array_equal(d_out.cpu().numpy(), gemm_golden["c1_out"])
+    # as-given (non-negated) offsets are part of the contract too
+    out2, _ = gpu_gemmlowp(ctx, c1["a"], c1["b"], c1["bias"], 128, 120, qm, sh, c1["offset"], 0, 255, np.uint8)
+    want2 = port.gemmlowp_fused(c1["a"], c1["b"], c1["bias"], 128, 120, [qm], [sh], c1["offset"], 0, 255, np.uint8)
+    assert np.array_equal(out2, want2)
+
+
+SHAPES = [(128, 256, 128), (129, 257, 130), (64, 64, 16), (300, 520, 1000), (1, 1000, 2048), (257, 64, 576),
+          (1000, 96, 147), (512, 128, 4608), (37, 1, 5)]
+
+
+@pytest.mark.parametrize("M,N,K", SHAPES)
+@pytest.mark.parametrize("types", ["u8u8", "s8s8", "u8s8"])
+def test_fused_vs_oracle(ctx, port, M, N, K, types):
+    ad = np.uint8 if types[:2] == "u8" else np.int8
+    bd = np.uint8 if types[2:] == "u8" else np.int8
+    rng = np.random.default_rng(M * 131 + N * 17 + K)
+    a, b = q8_uniform(rng, (M, K), ad), q8_uniform(rng, (K, N), bd)
+    bias = rng.integers(-5000, 5001, N).astype(np.int32)
+    lo, hi = type_range(ad)
+    # per-tensor, both offsets
+    ao, bo = int(rng.integers(-200, 200)), int(rng.integers(-200, 200))
+    qm, sh = capi.calculate_quantized_multiplier(np.float32(3.0 / (K * 40.0)))
+    for simt in (False, True):
+        got, kern = gpu_gemmlowp(ctx, a, b, bias, ao, bo, qm, sh, 7, lo, hi, ad, force_simt=simt, ldd_pad=16)
+        want = port.gemmlowp_fused(a, b, bias, ao, bo, [qm], [sh], 7, lo, hi, ad)
+        assert np.array_equal(got, want), (kern, np.argwhere(got != want)[:5])
+    # per-channel (b_offset 0), log-uniform scales as in the benchmark configs
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), N)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.02, ws, 0.02 * 0.005 * K * 30)
+    got, kern = gpu_gemmlowp(ctx, a, b, bias, ao, 0, mult, shift, -3, lo + 2, hi - 3, ad)
+    want = port.gemmlowp_fused(a, b, bias, ao, 0, mult, shift, -3, lo + 2, hi - 3, ad)
+    assert np.array_equal(got, want), kern
+    # S32 core
+    got, _ = gpu_gemmlowp(ctx, a, b, None, ao, bo, 0, 0, 0, 0, 0, np.int32, ldd_pad=4)
+    assert np.array_equal(got, port.gemmlowp_core(a, b, ao, bo))
+
+
+def test_kernel_selection(ctx):
+    rng = np.random.default_rng(0)
+    a, b = q8_uniform(rng, (64, 48), np.uint8), q8_uniform(rng, (48, 32), np.uint8)
+    _, k1 = gpu_gemmlowp(ctx, a, b, None, 0, 0, 2 ** 30, 3, 0, 0, 255, np.uint8)
+    assert k1 == "tcgen05"          # K = 48: row stride is a multiple of 16 bytes
+    a2, b2 = q8_uniform(rng, (64, 50), np.uint8), q8_uniform(rng, (50, 32), np.uint8)
+    _, k2 = gpu_gemmlowp(ctx, a2, b2, None, 0, 0, 2 ** 30, 3, 0, 0, 255, np.uint8)
+    assert k2 == "simt"             # K = 50: TMA cannot address the rows of A
+
+
+def test_negative_shift_and_saturating_multiplier(ctx, port):
+    """Left shifts (multiplier >= 1) and the INT32_MIN * INT32_MIN corner of SQDMULH."""
+    rng = np.random.default_rng(2)
+    M, N, K = 130, 70, 64
+    a, b = q8_uniform(rng, (M, K), np.int8), q8_uniform(rng, (K, N), np.int8)
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+    shift = rng.integers(-3, 4, N).astype(np.int32)
+    mult[5] = -2 ** 31
+    bias = rng.integers(-100, 100, N).astype(np.int32)
+    for simt in (False, True):
+        got, _ = gpu_gemmlowp(ctx, a, b, bias, 3, 0, mult, shift, 1, -128, 127, np.int8, force_simt=simt)
+        assert np.array_equal(got, port.gemmlowp_fused(a, b, bias, 3, 0, mult, shift, 1, -128, 127, np.int8))
+    qm, sh = capi.calculate_quantized_multiplier(np.float32(2.5))
+    assert sh < 0
+    got, _ = gpu_gemmlowp(ctx, a, b, None, 0, 0, qm, sh, 0, -128, 127, np.int8)
+    assert np.array_equal(got, port.gemmlowp_fused(a, b, None, 0, 0, [qm], [sh], 0, -128, 127, np.int8))
+
+
+def test_batched(ctx, port):
+    """BatchedMatMul (tests/validation/NEON/GEMMLowp.cpp:317-359): batched A with shared and batched B."""
+    rng = np.random.default_rng(4)
+    a = q8_uniform(rng, (3, 70, 96), np.int8)
+    b1 = q8_uniform(rng, (96, 40), np.int8)
+    b3 = q8_uniform(rng, (3, 96, 40), np.int8)
+    qm, sh = capi.calculate_quantized_multiplier(np.float32(0.0007))
+    for b in (b1, b3):
+        got, _ = gpu_gemmlowp(ctx, a, b, None, 4, -6, qm, sh, 2, -128, 127, np.int8)
+        for i in range(3):
+            bi = b if b.ndim == 2 else b[i]
+            want = port.gemmlowp_fused(a[i], bi, None, 4, -6, [qm], [sh], 2, -128, 127, np.int8)
+            assert np.array_equal(got[i], want)
+        acc, _ = gpu_gemmlowp(ctx, a, b, None, 4, -6, 0, 0, 0, 0, 0, np.int32)
+        assert np.array_equal(acc, port.gemmlowp_core(a, b, 4, -6))
+
+
+def test_run_twice_and_variable_b(ctx, port):
+    """MultipleExecution (GEMMLowp.cpp:211-297): same plan, same output; B re-laid out per run when it is
+    not constant (reshape_b_only_on_first_run = false)."""
+    rng = np.random.default_rng(6)
+    a, b = q8_uniform(rng, (200, 160), np.uint8), q8_uniform(rng, (160, 300), np.uint8)
+    qm, sh = capi.calculate_quantized_multiplier(np.float32(0.0004))
+    want = port.gemmlowp_fused(a, b, None, -100, -90, [qm], [sh], 5, 0, 255, np.uint8)
+    for const in (True, False):
+        got, _ = gpu_gemmlowp(ctx, a, b, None, -100, -90, qm, sh, 5, 0, 255, np.uint8, b_constant=const, runs=3)
+        assert np.array_equal(got, want)
+
+
+def test_update_quantization_parameters(ctx, port):
+    import torch
+    rng = np.random.default_rng(8)
+    M, N, K = 96, 80, 64
+    a, b = q8_uniform(rng, (M, K), np.int8), q8_uniform(rng, (K, N), np.int8)
+    d1, k1 = capi.make_gemm_desc(M, N, K, capi.S8, capi.S8, capi.S8, 2, 0, multiplier=2 ** 30, shift=6, offset=0,
+                                 min_bound=-128, max_bound=127)
+    plan = capi.GemmPlan(ctx, d1, k1)
+    da, db = torch.from_numpy(a).cuda(), torch.from_numpy(b).cuda()
+    dd = torch.empty((M, N), dtype=torch.int8, device="cuda")
+    plan.prepare(db)
+    plan.run(da, None, None, dd)
+    ctx.sync()
+    assert np.array_equal(dd.cpu().numpy(), port.gemmlowp_fused(a, b, None, 2, 0, [2 ** 30], [6], 0, -128, 127, np.int8))
+    d2, k2 = capi.make_gemm_desc(M, N, K, capi.S8, capi.S8, capi.S8, -9, 4, multiplier=1518500250, shift=5, offset=-4,
+                                 min_bound=-100, max_bound=90)
+    plan.update_quantization(d2, k2)
+    plan.run(da, None, None, dd)
+    ctx.sync()
+    assert np.array_equal(dd.cpu().numpy(),
+                          port.gemmlowp_fused(a, b, None, -9, 4, [1518500250], [5], -4, -100, 90, np.int8))
+    plan.close()
+
+
+def test_run_host_end_to_end(ctx, port):
+    """The host-buffer entry point: pinned buffers in, pinned buffers out."""
+    import ctypes as C
+    rng = np.random.default_rng(10)
+    M, N, K = 256, 192, 128
+    a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), np.int8)
+    bias = rng.integers(-1000, 1000, N).astype(np.int32)
+    import torch
+    desc, keep = capi.make_gemm_desc(M, N, K, capi.U8, capi.S8, capi.U8, -128, 0, multiplier=2 ** 30, shift=9,
+                                     offset=3, min_bound=0, max_bound=255, has_bias=True)
+    plan = capi.GemmPlan(ctx, desc, keep)
+    plan.prepare(torch.from_numpy(b).cuda())
+    h_a, h_d, h_b = ctx.host_alloc(M * K), ctx.host_alloc(M * N), ctx.host_alloc(N * 4)
+    C.memmove(h_a, a.ctypes.data, M * K)
+    C.memmove(h_b, bias.ctypes.data, N * 4)
+    plan.run_host(h_a, h_b, h_d)
+    got = np.ctypeslib.as_array((C.c_uint8 * (M * N)).from_address(h_d)).reshape(M, N).copy()
+    assert np.array_equal(got, port.gemmlowp_fused(a, b, bias, -128, 0, [2 ** 30], [9], 3, 0, 255, np.uint8))
+    for p in (h_a, h_d, h_b):
+        ctx.host_free(p)
+    plan.close()
+
+
+def test_config2_full_size_properties(ctx, port):
+    """4096^3 (BASELINE config 2): exact on a row sample against the oracle, tensor-core and generic kernels
+    agree everywhere, and the result is invariant under a row permutation of A (rows are independent)."""
+    c = config2()
+    mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])
+    out, kern = gpu_gemmlowp(ctx, c["a"], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8)
+    assert kern == "tcgen05"
+    rows = np.r_[0:64, 2000:2064, 4032:4096]
+    want = port.gemmlowp_fused(c["a"][rows], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8)
+    assert np.array_equal(out[rows], want)
+    ref2, _ = gpu_gemmlowp(ctx, c["a"], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8,
+                           force_simt=True)
+    assert np.array_equal(out, ref2)
+    perm = np.random.default_rng(0).permutation(4096)
+    outp, _ = gpu_gemmlowp(ctx, c["a"][perm], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8)
+    assert np.array_equal(outp, out[perm])
+    assert 0.05 < np.mean(np.abs(out.astype(np.int32)) == 127 + (out < 0)) < 0.999  # not all saturated
+
+
+def test_config5_column_shard_property(ctx, port):
+    """Config 5 at reduced M: a column shard of B gives exactly the same columns as the full GEMM (what the
+    N-sharded multi-GPU run relies on), and a row sample matches the oracle."""
+    c = config5(M=512)
+    mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])
+    full, _ = gpu_gemmlowp(ctx, c["a"], c["b"], None, 0, 0, mult, shift, 0, -128, 127, np.int8)
+    want = port.gemmlowp_fused(c["a"][:48], c["b"], None, 0, 0, mult, shift, 0, -128, 127, np.int8)
+    assert np.array_equal(full[:48], want)
+    n0, n1 = 1792 * 3, 1792 * 4
+    shard, _ = gpu_gemmlowp(ctx, c["a"], np.ascontiguousarray(c["b"][:, n0:n1]), None, 0, 0, mult[n0:n1],
+                            shift[n0:n1], 0, -128, 127, np.int8)
+    assert np.array_equal(shard, full[:, n0:n1])
