@@ -40,8 +40,8 @@ NOMINAL_INT8_TOPS = 4500.0
 def parse_args():
     p = argparse.ArgumentParser()
     p.add_argument("--gpus", type=int, default=1)
-    p.add_argument("--steps", type=int, default=20)
-    p.add_argument("--warmup", type=int, default=5)
+    p.add_argument("--steps", type=int, default=2000)
+    p.add_argument("--warmup", type=int, default=200)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c5"])
     p.add_argument("--size", type=int, default=0, help="override M=N=K of c2 (profiling on a small case)")
@@ -68,7 +68,7 @@ def load_peaks():
 
 class ClockSampler:
     """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+    FIELDS = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
@@ -78,12 +78,16 @@ class ClockSampler:
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(gpu_index), f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=self.file, stderr=subprocess.DEVNULL)
+                 "-lms", "20"], stdout=self.file, stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
 
-    def stop(self):
-        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+    def stop(self, t_begin=None, t_end=None):
+        """Summarises the samples taken between the two wall-clock instants (time.time()); when fewer than
+        three fall inside that window every sample of the run (warm-up included) is used and said so."""
+        import datetime
+        out = {"sm_mhz": None, "sm_max_mhz": None, "power_w_max": None, "reasons": [], "samples": 0,
+               "window": "timed region"}
         if self.proc is not None:
             self.proc.terminate()  # the exact process started above
             try:
@@ -92,26 +96,28 @@ class ClockSampler:
                 self.proc.kill()
         self.file.flush()
         self.file.seek(0)
-        sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        rows = []
         for line in self.file.read().splitlines():
             parts = [x.strip() for x in line.split(",")]
-            if len(parts) < 7:
+            if len(parts) < 8:
                 continue
             try:
-                sm.append(float(parts[0]))
-                mx.append(float(parts[1]))
+                ts = datetime.datetime.strptime(parts[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                rows.append((ts, float(parts[1]), float(parts[2]), float(parts[3]),
+                             [n for n, f in zip(names, parts[4:8]) if f.lower().startswith("active")]))
             except ValueError:
                 continue
-            for name, flag in zip(names, parts[3:7]):
-                if flag.lower().startswith("active"):
-                    reasons.add(name)
         self.file.close()
         os.unlink(self.file.name)
-        if sm:
-            # median over the upper half of the samples = the clock while the kernels were running
-            busy = sorted(sm)[len(sm) // 2:]
-            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+        sel = [r for r in rows if t_begin is None or (t_begin <= r[0] <= t_end)]
+        if len(sel) < 3:
+            sel, out["window"] = rows, "whole run incl. warm-up (timed region shorter than three samples)"
+        if sel:
+            busy = sorted(r[1] for r in sel)[len(sel) // 2:]  # upper half = samples taken under load
+            out.update(sm_mhz=statistics.median(busy), sm_max_mhz=max(r[2] for r in sel),
+                       power_w_max=max(r[3] for r in sel), reasons=sorted({n for r in sel for n in r[4]}),
+                       samples=len(sel))
         return out
 
 
@@ -171,6 +177,7 @@ def run_ours(args):
     if args.gpus > 1 and world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
     torch.cuda.set_device(local)
+    sampler = ClockSampler(local) if rank == 0 else None  # started early: nvidia-smi takes a while to come up
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
@@ -198,7 +205,7 @@ def run_ours(args):
         flush.zero_()
         plan.run(d_a, None, d_bias, d_dst)
     barrier()
-    sampler = ClockSampler(local) if rank == 0 else None
+    t_begin = time.time()
     starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     stops = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     t_wall0 = time.perf_counter()
@@ -209,10 +216,11 @@ def run_ours(args):
         stops[i].record()
     barrier()
     t_wall = time.perf_counter() - t_wall0
+    t_end = time.time()
     ctx.sync()  # raises if a device-side bounded wait ran out
     step_ms = [s.elapsed_time(e) for s, e in zip(starts, stops)]
     total_ms = float(sum(step_ms))
-    clocks = sampler.stop() if sampler is not None else None
+    clocks = sampler.stop(t_begin, t_end) if sampler is not None else None
 
     # ---- end to end: pinned host A -> device, run, dst -> pinned host, every step ----
     e2e = None
@@ -226,11 +234,12 @@ def run_ours(args):
         for _ in range(max(3, args.warmup)):
             plan.run_host(h_a, h_bias, h_d)
         barrier()
+        e2e_steps = min(args.steps, 200)
         t0 = time.perf_counter()
-        for _ in range(args.steps):
+        for _ in range(e2e_steps):
             plan.run_host(h_a, h_bias, h_d)  # blocks until dst is valid on the host
         torch.cuda.synchronize()
-        e2e_s = time.perf_counter() - t0
+        e2e_s = (time.perf_counter() - t0) * args.steps / e2e_steps  # scaled to the same step count
         got = np.ctypeslib.as_array((C.c_uint8 * d_bytes).from_address(h_d)).reshape(M, N)
         assert np.array_equal(got, d_dst.cpu().numpy()), "host-buffer path and device path disagree"
         e2e_ms = e2e_s * 1e3

@@ -94,7 +94,7 @@ _SIGNATURES = {
     "cugl_offset_contribution": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _i32, _i32]),
     "cugl_output_stage": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32,
                                     _i32, _i32, _i32]),
-    "cugl_im2col_nhwc": (C.c_int, [_vp, _vp, _vp] + [_i32] * 16 + [_i64]),
+    "cugl_im2col_nhwc": (C.c_int, [_vp, _vp, _vp] + [_i32] * 15 + [_i64]),
     "cugl_weights_reshape_nhwc": (C.c_int, [_vp, _vp, _vp, _i32, _i32]),
     "cugl_conv2d_validate": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_char_p)]),
     "cugl_conv2d_plan_create": (C.c_int, [_vp, C.POINTER(ConvDesc), C.POINTER(_vp)]),
@@ -172,12 +172,14 @@ def _dptr(t):
 
 
 class Context:
-    """cugl_context on one device.  stream: raw cudaStream_t (int), e.g. torch's current stream, or None."""
+    """cugl_context on one device.  stream: raw cudaStream_t as an int (0 = the CUDA default stream, e.g.
+    torch.cuda.current_stream().cuda_stream), or None to let the context create a stream of its own."""
 
     def __init__(self, device: int = 0, stream: int | None = None):
         self.lib = load_library()
         h = _vp()
-        _check(self.lib.cugl_context_create(device, _vp(stream) if stream else None, C.byref(h)))
+        arg = _vp(-1 & (2 ** 64 - 1)) if stream is None else _vp(stream)  # CUGL_STREAM_CREATE
+        _check(self.lib.cugl_context_create(device, arg, C.byref(h)))
         self.handle = h
 
     def close(self):

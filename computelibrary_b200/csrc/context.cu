@@ -76,7 +76,7 @@ extern "C"
         auto *ctx     = new cugl_context();
         ctx->device   = device;
         ctx->sm_count = prop.multiProcessorCount;
-        if (stream != nullptr)
+        if (stream != CUGL_STREAM_CREATE)
         {
             ctx->stream = static_cast<cudaStream_t>(stream);
         }

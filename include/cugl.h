@@ -73,7 +73,9 @@ typedef struct cugl_conv_plan cugl_conv_plan; /* configured NEGEMMConvolutionLay
  * src/runtime/IScheduler.cpp:58-180) by cudaMalloc-backed regions and one CUDA stream.
  * ---------------------------------------------------------------------------------------------- */
 
-/* stream: a cudaStream_t to enqueue on, or NULL to let the context create and own one. */
+/* stream: the cudaStream_t to enqueue on; NULL is the CUDA default stream.  Pass CUGL_STREAM_CREATE to let
+ * the context create (and later destroy) a non-blocking stream of its own. */
+#define CUGL_STREAM_CREATE ((void *)(intptr_t)-1)
 CUGL_API cugl_status cugl_context_create(int device, void *stream, cugl_context **out);
 CUGL_API void        cugl_context_destroy(cugl_context *ctx);
 /* Text of the last error raised through this context (never NULL). ctx may be NULL: global last error. */

@@ -83,7 +83,9 @@ def test_output_stage(ctx, port, out_dtype, M, N):
             assert np.array_equal(out.cpu().numpy().view(out_dtype), want), (qm, sh)
     mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
     shift = rng.integers(-2, 12, N).astype(np.int32)
-    ctx.output_stage(_t(acc), N * 4, _t(bias), out, N, code, M, N, _t(mult), _t(shift), 0, 0, N, -4, lo, hi)
+    # n_mult == 1 means per-tensor in the C ABI, so a single column passes its multiplier by value
+    ctx.output_stage(_t(acc), N * 4, _t(bias), out, N, code, M, N, _t(mult), _t(shift), int(mult[0]), int(shift[0]),
+                     N, -4, lo, hi)
     ctx.sync()
     assert np.array_equal(out.cpu().numpy().view(out_dtype), port.output_stage(acc, bias, mult, shift, -4, lo, hi, out_dtype))
 
