@@ -47,6 +47,7 @@ def parse_args():
     p.add_argument("--size", type=int, default=0, help="override M=N=K of c2 (profiling on a small case)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
+    p.add_argument("--one-cta", action="store_true", help="keep to the one-CTA tensor-core kernel (comparison runs)")
     return p.parse_args()
 
 
@@ -188,6 +189,8 @@ def run_ours(args):
         from computelibrary_b200 import workloads as wl
         c["a"] = wl.q8_uniform(np.random.default_rng(1000 + rank), c["a"].shape, c["a"].dtype)
     plan, (M, N, K) = build_plan(ctx, c)
+    if args.one_cta:
+        plan.allow_pair_kernel(False)
     ops = 2.0 * M * N * K
 
     d_a = torch.from_numpy(c["a"].view(np.uint8)).cuda()
@@ -277,7 +280,8 @@ def run_ours(args):
                        "rate is twice the bf16 rate; no int8 figure is recorded in MEASURED_PEAKS.json",
         "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
         "traffic": None,
-        "kernel": "gemmlowp_tcgen05_kernel" if plan.kernel == "tcgen05" else "gemmlowp_simt_kernel",
+        "kernel": {"tcgen05_2cta": "gemmlowp_tcgen05_2cta_kernel", "tcgen05": "gemmlowp_tcgen05_kernel"}.get(
+            plan.kernel, "gemmlowp_simt_kernel"),
         "kernel_ms": kernel_ms,
     }
     try:  # library int8 GEMM as a yardstick only (never on the product path)

@@ -66,6 +66,7 @@ _SIGNATURES = {
     "cugl_context_stream": (_vp, [_vp]),
     "cugl_context_device": (C.c_int, [_vp]),
     "cugl_context_sm_count": (C.c_int, [_vp]),
+    "cugl_context_set_trace_buffer": (C.c_int, [_vp, _vp]),
     "cugl_malloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "cugl_free": (C.c_int, [_vp, _vp]),
     "cugl_host_alloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
@@ -88,6 +89,7 @@ _SIGNATURES = {
     "cugl_gemmlowp_update_quantization": (C.c_int, [_vp, C.POINTER(GemmDesc)]),
     "cugl_gemmlowp_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_gemmlowp_plan_force_simt": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_allow_pair_kernel": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
     "cugl_reduce_rows": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_reduce_cols": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
@@ -195,6 +197,9 @@ class Context:
 
     def check(self, status: int):
         _check(status, self.handle)
+
+    def set_trace_buffer(self, buf):
+        self.check(self.lib.cugl_context_set_trace_buffer(self.handle, _dptr(buf)))
 
     def sync(self):
         self.check(self.lib.cugl_sync(self.handle))
@@ -344,6 +349,9 @@ class GemmPlan:
 
     def force_simt(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_force_simt(self.handle, int(on)))
+
+    def allow_pair_kernel(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_allow_pair_kernel(self.handle, int(on)))
 
     @property
     def kernel(self) -> str:

@@ -18,6 +18,7 @@ struct cugl_context
     bool         owns_stream = false;
     int32_t     *d_status    = nullptr; // device word written by kernels whose bounded waits ran out
     int32_t     *h_status    = nullptr; // pinned mirror read in cugl_sync
+    long long   *d_trace     = nullptr; // optional event-timestamp buffer for the tensor-core GEMM kernels
     std::string  last_error;
 };
 

@@ -275,6 +275,13 @@ extern "C"
         return CUGL_SUCCESS;
     }
 
+    cugl_status cugl_context_set_trace_buffer(cugl_context *ctx, void *d_buffer)
+    {
+        CUGL_NEED_CTX(ctx);
+        ctx->d_trace = static_cast<long long *>(d_buffer);
+        return CUGL_SUCCESS;
+    }
+
     cugl_status cugl_sync(cugl_context *ctx)
     {
         CUGL_NEED_CTX(ctx);

@@ -6,10 +6,17 @@
 //               into a STAGES-deep ring of 128-byte-swizzled shared-memory buffers
 //   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::i8, M=128, N=BLOCK_N, K=32 per instruction,
 //               int32 accumulators in tensor memory, double buffered (2 x BLOCK_N columns)
-//   warps 2..5  epilogue: tcgen05.ld the accumulator rows, add the offset / bias terms, requantise
+//   warps 2..9  epilogue (two warps per tensor-memory lane quarter, half of the columns each): tcgen05.ld the accumulator rows, add the offset / bias terms, requantise
 //               with the reference's SQDMULH + rounding shift, clamp, and store 8-bit (or int32) rows
 //
 // The epilogue of tile i overlaps the main loop of tile i+1 through the two accumulator buffers.
+//
+// Two kernels share these roles.  gemmlowp_tcgen05_kernel runs one CTA per 128 x BLOCK_N tile.
+// gemmlowp_tcgen05_2cta_kernel runs a cluster of two CTAs (one SM pair) per 256 x 256 tile with
+// tcgen05.mma.cta_group::2: each CTA stages its own 128 rows of A and only HALF of the B tile, the
+// tensor cores of both SMs read both halves, so 64 instead of 96 bytes are fetched from L2 per clock
+// of tensor work and the same shared memory holds six stages instead of four.  No load is multicast.
+//
 // Every wait is bounded: when a limit runs out the kernel raises a flag in shared memory, every role
 // leaves its loop, the producer waits (bounded) for its copies in flight, tensor memory is freed and
 // a status word is written for the host.
@@ -24,8 +31,10 @@ namespace
 constexpr int      BLOCK_M     = 128;
 constexpr int      BLOCK_K     = 128; // bytes == int8 elements: one 128-byte swizzle row
 constexpr int      UMMA_K      = 32;  // K per tcgen05.mma.kind::i8
-constexpr int      kThreads    = 192;
-constexpr int      kEpiThreads = 128;
+constexpr int      kProdLanes  = 4;                        // lanes of the producer warp that issue copies
+constexpr int      kEpiWarps   = 8;                        // two per tensor-memory lane quarter
+constexpr int      kEpiThreads = kEpiWarps * 32;
+constexpr int      kThreads    = 64 + kEpiThreads;          // producer warp + MMA warp + epilogue warps
 constexpr int      A_STAGE     = BLOCK_M * BLOCK_K;
 constexpr long long kSpinLimit = 4000000000ll; // clock64 ticks, about two seconds
 
@@ -166,7 +175,31 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr)
     return d;
 }
 
-// Named barrier over the four epilogue warps that also AND-reduces a predicate, so that the warps
+// Optional tracing: event e of the i-th tile this CTA processes, as a %globaltimer value (ns).
+// Layout: trace[(cta * kTraceTiles + i) * kTraceEvents + e].  Events: 0 producer issued the first copy,
+// 1 MMA issuer owns an accumulator, 2 first operand stage has landed, 3 last MMA issued, 4 epilogue sees the
+// finished accumulator, 5 epilogue has stored the tile; slot 6 = clocks the MMA issuer waited for operands.
+constexpr int kTraceTiles  = 8;
+constexpr int kTraceEvents = 8;
+__device__ __forceinline__ void trace_event(long long *trace, int i, int e)
+{
+    if (trace != nullptr && i < kTraceTiles)
+    {
+        unsigned long long t;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        trace[(static_cast<long long>(blockIdx.x) * kTraceTiles + i) * kTraceEvents + e] = static_cast<long long>(t);
+    }
+}
+
+__device__ __forceinline__ void trace_value(long long *trace, int i, int e, long long v)
+{
+    if (trace != nullptr && i < kTraceTiles)
+    {
+        trace[(static_cast<long long>(blockIdx.x) * kTraceTiles + i) * kTraceEvents + e] = v;
+    }
+}
+
+// Named barrier over the eight epilogue warps that also AND-reduces a predicate, so that the warps
 // take the "carry on / give up" decision together.
 __device__ __forceinline__ bool epi_barrier_and(bool pred)
 {
@@ -174,7 +207,7 @@ __device__ __forceinline__ bool epi_barrier_and(bool pred)
     asm volatile("{\n\t"
                  ".reg .pred p, q;\n\t"
                  "setp.ne.u32 q, %1, 0;\n\t"
-                 "bar.red.and.pred p, 1, 128, q;\n\t"
+                 "bar.red.and.pred p, 1, 256, q;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t"
                  "}"
                  : "=r"(r)
@@ -184,7 +217,7 @@ __device__ __forceinline__ bool epi_barrier_and(bool pred)
 }
 __device__ __forceinline__ void epi_barrier()
 {
-    asm volatile("bar.sync 2, 128;" ::: "memory");
+    asm volatile("bar.sync 2, 256;" ::: "memory");
 }
 
 struct TileParams
@@ -193,13 +226,285 @@ struct TileParams
     int64_t  ldd;
     int      M, N, K;
     uint32_t idesc;
-    int      vec_ok; // dst base and ldd are 16-byte aligned
+    int      vec_ok;  // dst base and ldd are 16-byte aligned
+    int      generic; // some column shifts left or has multiplier INT32_MIN: take the fully general path
+    long long *trace; // optional per-CTA event timestamps (cugl_context_set_trace_buffer), else nullptr
     int32_t *status;
 };
+
+
+// ---- cluster / cta_group::2 primitives ------------------------------------------------------------
+__device__ __forceinline__ uint32_t cluster_ctarank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t cluster_id_x()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%clusterid.x;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t num_clusters_x()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%nclusterid.x;" : "=r"(r));
+    return r;
+}
+// shared::cluster address of the same shared-memory offset in CTA `rank` of this cluster
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank)
+{
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// TMA tile load of a cta_group::2 pipeline: data lands in this CTA's shared memory, the byte count is
+// credited to the barrier at `bar_cluster_addr`, which lives in the leader CTA.  Not a multicast.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap *map, int c0, int c1,
+                                                 uint32_t bar_cluster_addr)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4}], [%2];"
+                 :
+                 : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t cols)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t cols)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(cols) : "memory");
+}
+// 256 x N x 32 across the SM pair: each CTA contributes 128 rows of A and N/2 rows of B.
+__device__ __forceinline__ void umma_i8_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                             uint32_t accumulate)
+{
+    asm volatile("{\n\t"
+                 ".reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t"
+                 "}"
+                 :
+                 : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+                 : "memory");
+}
+// arrives on the barrier at this shared-memory offset in both CTAs of the pair once the MMAs issued so
+// far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar)
+{
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :
+                 : "r"(bar), "h"(mask)
+                 : "memory");
+}
+
+// Requantise + clamp + pack four accumulators of one row (columns c .. c+3 of the tile).
+//   fast path  : every shift is a right shift and no multiplier is INT32_MIN, so the column term holds
+//                {offset+bias term, multiplier, 1 << (shift-1) (0 for shift 0), shift} and the saturating
+//                corner of SQDMULH cannot occur;
+//   generic    : {term, multiplier, right | left << 8, -} and the full reference expression.
+template <bool kGeneric>
+__device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 *col, int32_t row_term, int32_t offset,
+                                                  int32_t lo, int32_t hi)
+{
+    int32_t r[4];
+#pragma unroll
+    for (int b = 0; b < 4; ++b)
+    {
+        const int4    q   = col[b];
+        const int32_t acc = static_cast<int32_t>(v[b]) + q.x + row_term;
+        if (kGeneric)
+        {
+            r[b] = finalize(acc, q.y, q.z >> 8, q.z & 0xff, offset, lo, hi);
+        }
+        else
+        {
+            const int32_t  mh = __mulhi(acc, q.y);
+            const uint32_t ml = static_cast<uint32_t>(acc) * static_cast<uint32_t>(q.y);
+            const uint32_t d  = __funnelshift_l(ml, static_cast<uint32_t>(mh), 1);         // floor(acc*mult / 2^31)
+            const int32_t  t  = static_cast<int32_t>(d + static_cast<uint32_t>(q.z)) >> q.w; // round-half-up shift
+            r[b]              = min(max(t + offset, lo), hi);
+        }
+    }
+    const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
+    const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
+    return __byte_perm(p01, p23, 0x5410);
+}
+
+// Store 32 consecutive outputs of one row held in registers (v: int32 values or w: packed bytes).
+template <bool kS32Out>
+__device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, int nc, bool row_ok, const TileParams &tp)
+{
+    if (!row_ok)
+    {
+        return;
+    }
+    const bool full = nc + 32 <= tp.N;
+    if (kS32Out)
+    {
+        int32_t *o = reinterpret_cast<int32_t *>(drow) + nc;
+        if (full && tp.vec_ok)
+        {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+            {
+                *reinterpret_cast<uint4 *>(o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            }
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+            {
+                if (nc + j < tp.N) o[j] = static_cast<int32_t>(v[j]);
+            }
+        }
+    }
+    else
+    {
+        uint8_t *o = drow + nc;
+        if (full && tp.vec_ok)
+        {
+            *reinterpret_cast<uint4 *>(o)      = make_uint4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<uint4 *>(o + 16) = make_uint4(v[4], v[5], v[6], v[7]);
+        }
+        else
+        {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+            {
+                if (nc + j < tp.N) o[j] = static_cast<uint8_t>(v[j >> 2] >> (8 * (j & 3)));
+            }
+        }
+    }
+}
+
+template <bool kS32Out, bool kGeneric>
+__device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col, int32_t row_term,
+                                              const EpilogueParams &ep)
+{
+    if (kS32Out)
+    {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+        {
+            v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) + col[j].x + row_term);
+        }
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+        {
+            v[j >> 2] = requant_pack4<kGeneric>(v + j, col + j, row_term, ep.result_offset, ep.lo, ep.hi);
+        }
+    }
+}
+
+// Shared epilogue of both kernels: one warp drains NCOLS consecutive columns (a multiple of 32) of its
+// 32 accumulator rows from tensor memory, applies the offset / bias terms and the output stage, and
+// stores.  The tensor-memory load of chunk i+1 is issued before chunk i is processed.
+template <int NCOLS, bool kS32Out, bool kGeneric>
+__device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s_col, const TileParams &tp,
+                                                  const EpilogueParams &ep, int m, int n_first, int32_t row_term)
+{
+    const bool row_ok = m < tp.M;
+    uint8_t   *drow   = tp.dst + static_cast<int64_t>(m) * tp.ldd;
+    uint32_t   va[32], vb[32];
+    tmem_ld_x32(t_addr, va);
+#pragma unroll 1
+    for (int ch = 0; ch < NCOLS / 32; ch += 2)
+    {
+        tmem_ld_wait();
+        if (ch + 1 < NCOLS / 32)
+        {
+            tmem_ld_x32(t_addr + (ch + 1) * 32, vb);
+        }
+        process_chunk<kS32Out, kGeneric>(va, s_col + ch * 32, row_term, ep);
+        store_chunk<kS32Out>(va, drow, n_first + ch * 32, row_ok, tp);
+        if (ch + 1 < NCOLS / 32)
+        {
+            tmem_ld_wait();
+            if (ch + 2 < NCOLS / 32)
+            {
+                tmem_ld_x32(t_addr + (ch + 2) * 32, va);
+            }
+            process_chunk<kS32Out, kGeneric>(vb, s_col + (ch + 1) * 32, row_term, ep);
+            store_chunk<kS32Out>(vb, drow, n_first + (ch + 1) * 32, row_ok, tp);
+        }
+    }
+}
+
+// per-column terms of a tile (see requant_pack4 for the two encodings)
+template <int BLOCK_N>
+__device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, const TileParams &tp,
+                                                  const EpilogueParams &ep)
+{
+    for (int c = et; c < BLOCK_N; c += kEpiThreads)
+    {
+        const int n = n0 + c;
+        int4      q = make_int4(0, 0, 0, 0);
+        if (n < tp.N)
+        {
+            int32_t t = ep.k_term;
+            if (ep.colsum != nullptr) t += ep.a_off * __ldg(ep.colsum + n);
+            if (ep.bias != nullptr) t += __ldg(ep.bias + n);
+            const int32_t sh = ep.shifts != nullptr ? __ldg(ep.shifts + n) : ep.shift;
+            q.x              = t;
+            q.y              = ep.mults != nullptr ? __ldg(ep.mults + n) : ep.mult;
+            if (tp.generic)
+            {
+                q.z = max(sh, 0) | (max(-sh, 0) << 8);
+            }
+            else
+            {
+                q.z = static_cast<int32_t>((1u << sh) >> 1);
+                q.w = sh;
+            }
+        }
+        s_col[c] = q;
+    }
+}
+
+// The part of a tile one epilogue warp owns: lane quarter (warp & 3) and half of the columns.
+template <int BLOCK_N, bool kS32Out>
+__device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4 *s_col, const TileParams &tp,
+                                                   const EpilogueParams &ep, int warp, int lane, int m0, int n0)
+{
+    constexpr int NCOLS    = BLOCK_N / 2;
+    const int     quad     = warp & 3;
+    const int     half     = (warp - 2) >> 2; // warps 2..5 -> 0, 6..9 -> 1
+    const int     m        = m0 + quad * 32 + lane;
+    const int32_t row_term = (ep.rowsum != nullptr && m < tp.M) ? ep.b_off * __ldg(ep.rowsum + m) : 0;
+    const uint32_t t_addr  = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NCOLS;
+    if (tp.generic)
+    {
+        drain_accumulator<NCOLS, kS32Out, true>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term);
+    }
+    else
+    {
+        drain_accumulator<NCOLS, kS32Out, false>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term);
+    }
+}
 
 template <int BLOCK_N, int STAGES>
 struct SmemPlan
 {
+    static_assert(STAGES >= kProdLanes, "the producer lanes of one round must own distinct stages");
     static constexpr int B_STAGE    = BLOCK_N * BLOCK_K;
     static constexpr int STAGE      = A_STAGE + B_STAGE;
     static constexpr int OFF_A      = 0;
@@ -250,7 +555,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int a = 0; a < 2; ++a)
         {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kEpiThreads);
+            mbar_init(tempty_bar(a), kEpiWarps);
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -267,120 +572,152 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == 0)
     {
         // ---------------------------------------------------------------- TMA producer
-        int      s = 0;
-        uint32_t ph = 0, issued = 0, parities = 0;
-        bool     ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
+        // kProdLanes lanes issue copies independently of each other: lane j owns the k-blocks g = j,
+        // j + kProdLanes, ... of this CTA's (tile, k-block) sequence and runs its own wait / issue loop (the
+        // lanes diverge on purpose; nothing inside the loop is warp-collective).  One thread alone sustains
+        // only about one stage per 600 clocks, less than the tensor cores consume.
+        if (lane < kProdLanes)
         {
-            const int m0 = (tile % num_m_blocks) * BLOCK_M;
-            const int n0 = (tile / num_m_blocks) * BLOCK_N;
-            for (int kb = 0; kb < num_kb; ++kb)
+            const int my_tiles = static_cast<int>(blockIdx.x) < num_tiles
+                                     ? (num_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1
+                                     : 0;
+            const int total_kb = my_tiles * num_kb;
+            uint32_t  issued = 0, parities = 0;
+            bool      ok = true;
+            int       ti = 0, kb = lane; // (tile ordinal, k-block) of g, kept incrementally
+            while (kb >= num_kb)
             {
-                ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER));
+                kb -= num_kb;
+                ++ti;
+            }
+            int      st = lane % STAGES;
+            uint32_t ph = static_cast<uint32_t>(lane / STAGES) & 1u;
+            for (int g = lane; g < total_kb; g += kProdLanes)
+            {
+                ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
                 if (!ok)
                 {
                     break;
                 }
-                if (lane == 0)
+                const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
+                const int m0   = (tile % num_m_blocks) * BLOCK_M;
+                const int n0   = (tile / num_m_blocks) * BLOCK_N;
+                if (kb == 0) trace_event(tp.trace, ti, 0);
+                mbar_expect_tx(full_bar(st), P::STAGE);
+                tma_load_2d(sA + st * A_STAGE, &tmap_a, kb * BLOCK_K, m0, full_bar(st));
+                tma_load_2d(sB + st * P::B_STAGE, &tmap_b, kb * BLOCK_K, n0, full_bar(st));
+                issued |= 1u << st;
+                parities = (parities & ~(1u << st)) | (ph << st);
+                // advance g by kProdLanes
+                kb += kProdLanes;
+                while (kb >= num_kb)
                 {
-                    mbar_expect_tx(full_bar(s), P::STAGE);
-                    tma_load_2d(sA + s * A_STAGE, &tmap_a, kb * BLOCK_K, m0, full_bar(s));
-                    tma_load_2d(sB + s * P::B_STAGE, &tmap_b, kb * BLOCK_K, n0, full_bar(s));
+                    kb -= num_kb;
+                    ++ti;
                 }
-                issued |= 1u << s;
-                parities = (parities & ~(1u << s)) | (ph << s);
-                __syncwarp();
-                if (++s == STAGES)
+                st += kProdLanes;
+                if (st >= STAGES)
                 {
-                    s = 0;
+                    st -= STAGES;
                     ph ^= 1;
                 }
             }
-        }
-        if (!ok || *s_abort != 0)
-        {
-            // wait, with a limit of its own, until the copies already issued have landed
-            for (int i = 0; i < STAGES; ++i)
+            if (!ok || *s_abort != 0)
             {
-                if ((issued >> i) & 1u)
+                // wait, with a limit of its own, until the copies this lane issued have landed
+                for (int i = 0; i < STAGES; ++i)
                 {
-                    const long long t0 = clock64();
-                    while (!mbar_try_wait(full_bar(i), (parities >> i) & 1u))
+                    if ((issued >> i) & 1u)
                     {
-                        if (clock64() - t0 > kSpinLimit / 4)
+                        const long long t0 = clock64();
+                        while (!mbar_try_wait(full_bar(i), (parities >> i) & 1u))
                         {
-                            *s_abort = DEV_TIMEOUT_DRAIN;
-                            break;
+                            if (clock64() - t0 > kSpinLimit / 4)
+                            {
+                                *s_abort = DEV_TIMEOUT_DRAIN;
+                                break;
+                            }
                         }
                     }
                 }
             }
         }
+        __syncwarp();
     }
     else if (warp == 1)
     {
         // ---------------------------------------------------------------- MMA issuer
-        int      s = 0, as = 0;
-        uint32_t ph = 0, aph = 0;
-        bool     ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x)
+        // One lane runs the whole loop: tcgen05.mma / commit are single-thread instructions, and 32 lanes
+        // polling the same barrier only slow the hand-over down.
+        if (lane == 0)
         {
-            ok = __all_sync(0xffffffffu, mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA));
-            if (!ok)
+            int      s = 0, as = 0;
+            uint32_t ph = 0, aph = 0;
+            bool     ok = true;
+            int      ti = 0;
+            const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
+            const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
+            for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti)
             {
-                break;
-            }
-            tc_fence_after();
-            const uint32_t d_tmem = tmem_base + as * BLOCK_N;
-            for (int kb = 0; kb < num_kb; ++kb)
-            {
-                ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA));
+                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
                 if (!ok)
                 {
                     break;
                 }
+                trace_event(tp.trace, ti, 1);
                 tc_fence_after();
-                if (lane == 0)
+                const uint32_t d_tmem = tmem_base + as * BLOCK_N;
+                long long      waited = 0;
+                for (int kb = 0; kb < num_kb; ++kb)
                 {
-                    const uint64_t a_desc = make_kmajor_sw128_desc(sA + s * A_STAGE);
-                    const uint64_t b_desc = make_kmajor_sw128_desc(sB + s * P::B_STAGE);
+                    const long long w0 = tp.trace != nullptr ? clock64() : 0;
+                    ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                    if (tp.trace != nullptr) waited += clock64() - w0;
+                    if (!ok)
+                    {
+                        break;
+                    }
+                    tc_fence_after();
+                    if (kb == 0) trace_event(tp.trace, ti, 2);
+                    // stage offset in 16-byte units; advancing K by 32 bytes inside the swizzle row: +2
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * A_STAGE) >> 4);
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
 #pragma unroll
                     for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                     {
-                        // advancing K by 32 bytes inside the swizzle row: +2 in 16-byte units
                         umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, tp.idesc, (kb | k) != 0 ? 1u : 0u);
                     }
                     umma_commit(empty_bar(s)); // frees the smem stage once these MMAs have read it
+                    if (++s == STAGES)
+                    {
+                        s = 0;
+                        ph ^= 1;
+                    }
                 }
-                __syncwarp();
-                if (++s == STAGES)
+                if (ok)
                 {
-                    s = 0;
-                    ph ^= 1;
+                    umma_commit(tfull_bar(as)); // accumulator complete
+                    trace_event(tp.trace, ti, 3);
+                    trace_value(tp.trace, ti, 6, waited); // clocks spent waiting for operands
                 }
-            }
-            if (ok && lane == 0)
-            {
-                umma_commit(tfull_bar(as)); // accumulator complete
-            }
-            __syncwarp();
-            if (++as == 2)
-            {
-                as = 0;
-                aph ^= 1;
+                if (++as == 2)
+                {
+                    as = 0;
+                    aph ^= 1;
+                }
             }
         }
+        __syncwarp();
     }
     else
     {
-        // ---------------------------------------------------------------- epilogue (warps 2..5)
-        const int quad = warp & 3;          // tensor-memory lane quarter this warp may read
-        const int et   = threadIdx.x - 64;  // 0..127
-        const int r_in = quad * 32 + lane;  // row inside the tile
+        // ---------------------------------------------------------------- epilogue (warps 2..9)
+        const int et = threadIdx.x - 64; // 0..255
         int       as = 0;
         uint32_t  aph = 0;
         bool      ok = true;
-        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x)
+        int       ti = 0;
+        for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti)
         {
             if (!epi_barrier_and(ok))
             {
@@ -388,108 +725,21 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const int m0 = (tile % num_m_blocks) * BLOCK_M;
             const int n0 = (tile / num_m_blocks) * BLOCK_N;
-            // per-column terms of this tile: {offset + bias term, multiplier, right | left << 8, 0}
-            for (int c = et; c < BLOCK_N; c += kEpiThreads)
-            {
-                const int n = n0 + c;
-                int4      q = make_int4(0, 0, 0, 0);
-                if (n < tp.N)
-                {
-                    int32_t t = ep.k_term;
-                    if (ep.colsum != nullptr) t += ep.a_off * __ldg(ep.colsum + n);
-                    if (ep.bias != nullptr) t += __ldg(ep.bias + n);
-                    const int32_t sh = ep.shifts != nullptr ? __ldg(ep.shifts + n) : ep.shift;
-                    q.x              = t;
-                    q.y              = ep.mults != nullptr ? __ldg(ep.mults + n) : ep.mult;
-                    q.z              = max(sh, 0) | (max(-sh, 0) << 8);
-                }
-                s_col[c] = q;
-            }
+            fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
             epi_barrier();
-            ok = mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE);
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok)
             {
                 tc_fence_after();
-                const int     m        = m0 + r_in;
-                const bool    row_ok   = m < tp.M;
-                const int32_t row_term = (ep.rowsum != nullptr && row_ok) ? ep.b_off * __ldg(ep.rowsum + m) : 0;
-                const uint32_t t_row   = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + as * BLOCK_N;
-                uint8_t *drow = tp.dst + static_cast<int64_t>(m) * tp.ldd;
-#pragma unroll 1
-                for (int ch = 0; ch < BLOCK_N / 32; ++ch)
-                {
-                    uint32_t v[32];
-                    tmem_ld_x32(t_row + ch * 32, v);
-                    tmem_ld_wait();
-                    const int  nc   = n0 + ch * 32;
-                    const bool full = nc + 32 <= tp.N;
-                    if (kS32Out)
-                    {
-                        int32_t *o = reinterpret_cast<int32_t *>(drow) + nc;
-#pragma unroll
-                        for (int j = 0; j < 32; ++j)
-                        {
-                            v[j] = static_cast<uint32_t>(static_cast<int32_t>(v[j]) + s_col[ch * 32 + j].x + row_term);
-                        }
-                        if (row_ok)
-                        {
-                            if (full && tp.vec_ok)
-                            {
-#pragma unroll
-                                for (int j = 0; j < 32; j += 4)
-                                {
-                                    *reinterpret_cast<uint4 *>(o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                                }
-                            }
-                            else
-                            {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                {
-                                    if (nc + j < tp.N) o[j] = static_cast<int32_t>(v[j]);
-                                }
-                            }
-                        }
-                    }
-                    else
-                    {
-                        uint32_t w[8];
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4)
-                        {
-                            uint32_t packed = 0;
-#pragma unroll
-                            for (int b = 0; b < 4; ++b)
-                            {
-                                const int4    q   = s_col[ch * 32 + j + b];
-                                const int32_t acc = static_cast<int32_t>(v[j + b]) + q.x + row_term;
-                                const int32_t r   = finalize(acc, q.y, q.z >> 8, q.z & 0xff, ep.result_offset, ep.lo,
-                                                             ep.hi);
-                                packed |= (static_cast<uint32_t>(r) & 0xffu) << (8 * b);
-                            }
-                            w[j >> 2] = packed;
-                        }
-                        if (row_ok)
-                        {
-                            uint8_t *o = drow + nc;
-                            if (full && tp.vec_ok)
-                            {
-                                *reinterpret_cast<uint4 *>(o)      = make_uint4(w[0], w[1], w[2], w[3]);
-                                *reinterpret_cast<uint4 *>(o + 16) = make_uint4(w[4], w[5], w[6], w[7]);
-                            }
-                            else
-                            {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j)
-                                {
-                                    if (nc + j < tp.N) o[j] = static_cast<uint8_t>(w[j >> 2] >> (8 * (j & 3)));
-                                }
-                            }
-                        }
-                    }
-                }
+                if (et == 0) trace_event(tp.trace, ti, 4);
+                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0);
                 tc_fence_before();
-                mbar_arrive(tempty_bar(as)); // accumulator buffer may be overwritten
+                __syncwarp();
+                if (et == 0) trace_event(tp.trace, ti, 5);
+                if (lane == 0)
+                {
+                    mbar_arrive(tempty_bar(as)); // accumulator buffer may be overwritten (one arrival per warp)
+                }
             }
             if (++as == 2)
             {
@@ -506,6 +756,258 @@ __global__ void __launch_bounds__(kThreads, 1)
     {
         tc_fence_after();
         tmem_dealloc(tmem_base, P::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *s_abort != 0)
+    {
+        atomicCAS(tp.status, 0, *s_abort);
+    }
+}
+
+
+// ---------------------------------------------------------------------------------------------------
+// Two-CTA kernel: a cluster of two CTAs (an SM pair) per 256 x 256 output tile.
+//   CTA rank r stages rows [m0 + 128 r, +128) of A and rows [n0 + 128 r, +128) of Bt (its half of the
+//   B tile), owns the accumulator rows [m0 + 128 r, +128) x 256 columns in its tensor memory and runs
+//   the epilogue for them.  The MMA issuer of rank 0 drives the tensor cores of both SMs.
+//   Barriers: full[] lives in rank 0 and collects the bytes of both CTAs' copies; empty[] and tfull[]
+//   exist in both CTAs and are signalled together by a multicast tcgen05.commit; tempty[] lives in rank 0
+//   and is arrived on by the sixteen epilogue warps of the pair.
+// ---------------------------------------------------------------------------------------------------
+template <int STAGES>
+struct SmemPlan2
+{
+    static constexpr int BLOCK_N   = 256;
+    static constexpr int B_STAGE   = (BLOCK_N / 2) * BLOCK_K; // this CTA's half of the B tile
+    static constexpr int STAGE     = A_STAGE + B_STAGE;
+    static constexpr int OFF_A     = 0;
+    static constexpr int OFF_B     = STAGES * A_STAGE;
+    static constexpr int OFF_COL   = STAGES * STAGE;
+    static constexpr int OFF_BAR   = OFF_COL + BLOCK_N * 16;
+    static constexpr int OFF_MISC  = OFF_BAR + (2 * STAGES + 4) * 8;
+    static constexpr int TOTAL     = OFF_MISC + 16;
+    static constexpr int DYN_BYTES = TOTAL + 1024;
+    static constexpr int TMEM_COLS = 2 * BLOCK_N;
+};
+
+template <int STAGES, bool kS32Out>
+__global__ void __launch_bounds__(kThreads, 1)
+    gemmlowp_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                 const __grid_constant__ CUtensorMap tmap_b, const TileParams tp,
+                                 const EpilogueParams ep)
+{
+    using P               = SmemPlan2<STAGES>;
+    constexpr int BLOCK_N = P::BLOCK_N;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const uint32_t sA         = smem_u32(smem + P::OFF_A);
+    const uint32_t sB         = smem_u32(smem + P::OFF_B);
+    int4          *s_col      = reinterpret_cast<int4 *>(smem + P::OFF_COL);
+    const uint32_t bar_base   = smem_u32(smem + P::OFF_BAR);
+    auto           full_bar   = [&](int s) { return bar_base + 8u * s; };
+    auto           empty_bar  = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto           tfull_bar  = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto           tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    uint32_t      *s_tmem     = reinterpret_cast<uint32_t *>(smem + P::OFF_MISC);
+    volatile int  *s_abort    = reinterpret_cast<volatile int *>(smem + P::OFF_MISC + 4);
+
+    const int      warp   = threadIdx.x >> 5;
+    const int      lane   = threadIdx.x & 31;
+    const uint32_t rank   = cluster_ctarank();
+    const bool     leader = rank == 0;
+
+    const int num_m_blocks = (tp.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
+    const int num_n_blocks = (tp.N + BLOCK_N - 1) / BLOCK_N;
+    const int num_tiles    = num_m_blocks * num_n_blocks;
+    const int num_kb       = (tp.K + BLOCK_K - 1) / BLOCK_K;
+    const int first_tile   = static_cast<int>(cluster_id_x());
+    const int tile_stride  = static_cast<int>(num_clusters_x());
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < STAGES; ++s)
+        {
+            mbar_init(full_bar(s), 1);  // used in the leader only: its producer's arrive + both CTAs' bytes
+            mbar_init(empty_bar(s), 1); // multicast commit of the leader's MMA issuer
+        }
+        for (int a = 0; a < 2; ++a)
+        {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 2 * kEpiWarps); // used in the leader only: the epilogue warps of both CTAs
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1)
+    {
+        tmem_alloc_pair(smem_u32(s_tmem), P::TMEM_COLS);
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync(); // the peer's barriers are initialised before anything is sent to them
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp == 0)
+    {
+        // ---------------------------------------------------------------- TMA producer (both CTAs)
+        // Same independent-lane issue loops as the one-CTA kernel; the byte counts of both CTAs' copies are
+        // credited to the leader's "full" barrier, whose expected total the leader's lane announces.
+        if (lane < kProdLanes)
+        {
+            const int my_tiles = first_tile < num_tiles ? (num_tiles - 1 - first_tile) / tile_stride + 1 : 0;
+            const int total_kb = my_tiles * num_kb;
+            int       ti = 0, kb = lane;
+            while (kb >= num_kb)
+            {
+                kb -= num_kb;
+                ++ti;
+            }
+            int      st = lane % STAGES;
+            uint32_t ph = static_cast<uint32_t>(lane / STAGES) & 1u;
+            for (int g = lane; g < total_kb; g += kProdLanes)
+            {
+                if (!mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER))
+                {
+                    break;
+                }
+                const int tile = first_tile + ti * tile_stride;
+                const int m0   = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
+                const int n0   = (tile / num_m_blocks) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
+                if (kb == 0) trace_event(tp.trace, ti, 0);
+                const uint32_t leader_full = map_to_cta(full_bar(st), 0);
+                if (leader)
+                {
+                    mbar_expect_tx(full_bar(st), 2 * P::STAGE); // the bytes of both CTAs
+                }
+                tma_load_2d_pair(sA + st * A_STAGE, &tmap_a, kb * BLOCK_K, m0, leader_full);
+                tma_load_2d_pair(sB + st * P::B_STAGE, &tmap_b, kb * BLOCK_K, n0, leader_full);
+                kb += kProdLanes;
+                while (kb >= num_kb)
+                {
+                    kb -= num_kb;
+                    ++ti;
+                }
+                st += kProdLanes;
+                if (st >= STAGES)
+                {
+                    st -= STAGES;
+                    ph ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp == 1)
+    {
+        // ---------------------------------------------------------------- MMA issuer (leader CTA only)
+        if (leader && lane == 0)
+        {
+            int      s = 0, as = 0;
+            uint32_t ph = 0, aph = 0;
+            bool     ok = true;
+            int      ti = 0;
+            const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
+            const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
+            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride, ++ti)
+            {
+                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
+                if (!ok)
+                {
+                    break;
+                }
+                trace_event(tp.trace, ti, 1);
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BLOCK_N;
+                long long      waited = 0;
+                for (int kb = 0; kb < num_kb; ++kb)
+                {
+                    const long long w0 = tp.trace != nullptr ? clock64() : 0;
+                    ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                    if (tp.trace != nullptr) waited += clock64() - w0;
+                    if (!ok)
+                    {
+                        break;
+                    }
+                    tc_fence_after();
+                    if (kb == 0) trace_event(tp.trace, ti, 2);
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * A_STAGE) >> 4);
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                    {
+                        umma_i8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, tp.idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    umma_commit_pair(empty_bar(s)); // frees this stage in both CTAs
+                    if (++s == STAGES)
+                    {
+                        s = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (ok)
+                {
+                    umma_commit_pair(tfull_bar(as)); // accumulator complete, both CTAs
+                    trace_event(tp.trace, ti, 3);
+                    trace_value(tp.trace, ti, 6, waited); // clocks spent waiting for operands
+                }
+                if (++as == 2)
+                {
+                    as = 0;
+                    aph ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else
+    {
+        // ---------------------------------------------------------------- epilogue (warps 2..9, both CTAs)
+        const int et = threadIdx.x - 64; // 0..255
+        int       as = 0;
+        uint32_t  aph = 0;
+        bool      ok = true;
+        int       ti = 0;
+        for (int tile = first_tile; tile < num_tiles; tile += tile_stride, ++ti)
+        {
+            if (!epi_barrier_and(ok))
+            {
+                break;
+            }
+            const int m0 = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
+            const int n0 = (tile / num_m_blocks) * BLOCK_N;
+            fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+            epi_barrier();
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            if (ok)
+            {
+                tc_fence_after();
+                if (et == 0) trace_event(tp.trace, ti, 4);
+                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0);
+                tc_fence_before();
+                __syncwarp();
+                if (et == 0) trace_event(tp.trace, ti, 5);
+                if (lane == 0)
+                {
+                    mbar_arrive_cluster(map_to_cta(tempty_bar(as), 0)); // one arrival per warp, at the leader
+                }
+            }
+            if (++as == 2)
+            {
+                as = 0;
+                aph ^= 1;
+            }
+        }
+    }
+
+    // ---------------------------------------------------------------- teardown
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync(); // neither CTA leaves (or frees tensor memory) while its peer may still touch it
+    if (warp == 1)
+    {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, P::TMEM_COLS);
     }
     if (threadIdx.x == 0 && *s_abort != 0)
     {
@@ -563,11 +1065,11 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
     auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, kS32Out>;
-    static bool attr_set = false; // per instantiation
-    if (!attr_set)
+    static bool attr_set[64] = {}; // per instantiation and device
+    if (!attr_set[ctx->device & 63])
     {
         CUGL_CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::DYN_BYTES));
-        attr_set = true;
+        attr_set[ctx->device & 63] = true;
     }
     TileParams tp;
     tp.dst    = static_cast<uint8_t *>(op.dst);
@@ -578,11 +1080,63 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
-    tp.status = ctx->d_status;
+    tp.status  = ctx->d_status;
+    tp.generic = op.generic_stage ? 1 : 0;
+    tp.trace   = ctx->d_trace;
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, tp, ep);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel");
+}
+
+template <int STAGES, bool kS32Out>
+cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
+{
+    using P = SmemPlan2<STAGES>;
+    static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
+    CUtensorMap map_a, map_b;
+    if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
+        !encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, P::BLOCK_N / 2))
+    {
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
+    }
+    auto kernel = gemmlowp_tcgen05_2cta_kernel<STAGES, kS32Out>;
+    static bool attr_set[64] = {}; // per instantiation and device
+    if (!attr_set[ctx->device & 63])
+    {
+        CUGL_CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::DYN_BYTES));
+        attr_set[ctx->device & 63] = true;
+    }
+    TileParams tp;
+    tp.dst    = static_cast<uint8_t *>(op.dst);
+    tp.ldd    = op.ldd;
+    tp.M      = op.M;
+    tp.N      = op.N;
+    tp.K      = op.K;
+    tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
+               (static_cast<uint32_t>(P::BLOCK_N >> 3) << 17) | (static_cast<uint32_t>((2 * BLOCK_M) >> 4) << 24);
+    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
+    tp.status  = ctx->d_status;
+    tp.generic = op.generic_stage ? 1 : 0;
+    tp.trace   = ctx->d_trace;
+    const int tiles    = ((op.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((op.N + P::BLOCK_N - 1) / P::BLOCK_N);
+    const int pairs    = ctx->sm_count / 2;
+    const int clusters = tiles < pairs ? tiles : pairs;
+
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim          = dim3(2 * clusters, 1, 1);
+    cfg.blockDim         = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = P::DYN_BYTES;
+    cfg.stream           = ctx->stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id               = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs                = attr;
+    cfg.numAttrs             = 1;
+    CUGL_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, tp, ep));
+    return CUGL_SUCCESS;
 }
 } // namespace
 
@@ -597,9 +1151,20 @@ bool gemmlowp_tcgen05_supported(const GemmOperands &op)
     return (bits & 15) == 0 && get_encode_fn() != nullptr;
 }
 
-cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
+// The SM-pair kernel pays off once a tile spans both halves: more than 128 rows and more than 128 columns.
+bool gemmlowp_tcgen05_uses_pair(const GemmOperands &op)
+{
+    return op.N > 128 && op.M > 128;
+}
+
+cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                    bool allow_pair)
 {
     const bool s32 = ep.stage == CUGL_STAGE_NONE;
+    if (allow_pair && gemmlowp_tcgen05_uses_pair(op))
+    {
+        return s32 ? launch_variant_2cta<6, true>(ctx, op, ep) : launch_variant_2cta<6, false>(ctx, op, ep);
+    }
     if (op.N > 128)
     {
         return s32 ? launch_variant<256, 4, true>(ctx, op, ep) : launch_variant<256, 4, false>(ctx, op, ep);

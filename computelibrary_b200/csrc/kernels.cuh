@@ -34,6 +34,7 @@ struct GemmOperands
     int64_t     lda, ldbt, ldd; // bytes
     int         M, N, K;
     bool        a_signed, b_signed;
+    bool        generic_stage; // some shift is negative or some multiplier is INT32_MIN (decided on the host)
 };
 
 // Generic CUDA-core kernel: any shape, stride and alignment.
@@ -41,5 +42,8 @@ cugl_status launch_gemmlowp_simt(cugl_context *ctx, const GemmOperands &op, cons
 
 // TMA + tcgen05.mma.kind::i8 kernel.  Requires a, bt 16-byte aligned and lda, ldbt multiples of 16.
 bool        gemmlowp_tcgen05_supported(const GemmOperands &op);
-cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep);
+bool        gemmlowp_tcgen05_uses_pair(const GemmOperands &op);
+// allow_pair = false keeps to the one-CTA kernels (testing aid; all variants must agree bit for bit).
+cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                    bool allow_pair = true);
 } // namespace cugl

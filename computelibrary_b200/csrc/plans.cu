@@ -40,6 +40,8 @@ struct GemmCore
     int32_t      *d_mults  = nullptr; // [N]
     int32_t      *d_shifts = nullptr;
     bool          force_simt = false;
+    bool          allow_pair = true; // SM-pair (cta_group::2) kernel permitted
+    bool          generic_stage = false; // a left shift or an INT32_MIN multiplier is present
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
@@ -53,9 +55,14 @@ struct GemmCore
 
     cugl_status upload_stage_vectors(const int32_t *h_mults, const int32_t *h_shifts)
     {
+        generic_stage = !per_channel && (shift < 0 || mult == INT32_MIN);
         if (!per_channel)
         {
             return CUGL_SUCCESS;
+        }
+        for (int i = 0; i < N; ++i)
+        {
+            generic_stage = generic_stage || h_shifts[i] < 0 || h_mults[i] == INT32_MIN;
         }
         if (d_mults == nullptr)
         {
@@ -133,12 +140,13 @@ struct GemmCore
         op.K        = K;
         op.a_signed = a_signed;
         op.b_signed = b_signed;
+        op.generic_stage = generic_stage;
         if (b_off != 0)
         {
             CUGL_TRY(launch_reduce_rows(ctx, d_a, a_signed, rows, K, lda, 1, d_rowsum + rowsum_off));
         }
         const EpilogueParams ep = epilogue(d_bias, b_copy, rowsum_off);
-        return uses_tcgen05(op) ? launch_gemmlowp_tcgen05(ctx, op, ep) : launch_gemmlowp_simt(ctx, op, ep);
+        return uses_tcgen05(op) ? launch_gemmlowp_tcgen05(ctx, op, ep, allow_pair) : launch_gemmlowp_simt(ctx, op, ep);
     }
 };
 
@@ -286,7 +294,7 @@ extern "C"
         c.dst_dtype = desc->dst_dtype;
         apply_quant_fields(p, desc);
         cugl_status s = c.alloc(p->b_copies, desc->M * desc->batch);
-        if (s == CUGL_SUCCESS && c.per_channel)
+        if (s == CUGL_SUCCESS)
         {
             s = c.upload_stage_vectors(p->h_mults.data(), p->h_shifts.data());
         }
@@ -429,8 +437,8 @@ extern "C"
         {
             plan->h_mults.assign(desc->h_gemmlowp_multipliers, desc->h_gemmlowp_multipliers + desc->N);
             plan->h_shifts.assign(desc->h_gemmlowp_shifts, desc->h_gemmlowp_shifts + desc->N);
-            CUGL_TRY(plan->core.upload_stage_vectors(plan->h_mults.data(), plan->h_shifts.data()));
         }
+        CUGL_TRY(plan->core.upload_stage_vectors(plan->h_mults.data(), plan->h_shifts.data()));
         return CUGL_SUCCESS;
     }
 
@@ -449,7 +457,12 @@ extern "C"
         op.M    = plan->desc.M;
         op.N    = plan->desc.N;
         op.K    = plan->desc.K;
-        return plan->core.uses_tcgen05(op) ? "tcgen05" : "simt";
+        if (!plan->core.uses_tcgen05(op))
+        {
+            return "simt";
+        }
+        op.M = plan->collapse_batch ? plan->desc.M * plan->desc.batch : plan->desc.M;
+        return (plan->core.allow_pair && gemmlowp_tcgen05_uses_pair(op)) ? "tcgen05_2cta" : "tcgen05";
     }
 
     cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on)
@@ -459,6 +472,16 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_force_simt: NULL plan");
         }
         plan->core.force_simt = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_plan_allow_pair_kernel(cugl_gemm_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_allow_pair_kernel: NULL plan");
+        }
+        plan->core.allow_pair = on != 0;
         return CUGL_SUCCESS;
     }
 
@@ -696,7 +719,7 @@ extern "C"
         c.min_bound     = desc->min_bound;
         c.max_bound     = desc->max_bound;
         cugl_status s   = c.alloc(1, c.M);
-        if (s == CUGL_SUCCESS && c.per_channel)
+        if (s == CUGL_SUCCESS)
         {
             s = c.upload_stage_vectors(p->h_mults.data(), p->h_shifts.data());
         }

@@ -84,6 +84,13 @@ CUGL_API void       *cugl_context_stream(const cugl_context *ctx);
 CUGL_API int         cugl_context_device(const cugl_context *ctx);
 CUGL_API int         cugl_context_sm_count(const cugl_context *ctx);
 
+/* Profiling aid (the role of the reference's scheduler timer, tests/framework/instruments/SchedulerTimer.cpp):
+ * when d_buffer is not NULL every tensor-core GEMM launch records %globaltimer timestamps (ns) of its pipeline
+ * events into it: int64 [grid][8 tiles][8 events]; events 0 first copy issued, 1 accumulator acquired, 2 first
+ * operands landed, 3 last MMA issued, 4 epilogue sees the accumulator, 5 tile stored.  The buffer must hold
+ * 64 * 8 bytes per CTA of the launch (at most 2 * SM count CTAs).  NULL switches tracing off. */
+CUGL_API cugl_status cugl_context_set_trace_buffer(cugl_context *ctx, void *d_buffer);
+
 /* IAllocator::allocate / free (arm_compute/runtime/IAllocator.h:39-61): device regions, 256-byte aligned. */
 CUGL_API cugl_status cugl_malloc(cugl_context *ctx, size_t bytes, void **d_ptr);
 CUGL_API cugl_status cugl_free(cugl_context *ctx, void *d_ptr);
@@ -177,11 +184,14 @@ CUGL_API cugl_status cugl_gemmlowp_run_host(cugl_gemm_plan *plan, const void *h_
 /* update_quantization_parameters() (NEGEMMLowpMatrixMultiplyCore.cpp:118-159): re-reads offsets and the
  * output-stage fields of desc; shapes and types must be unchanged. */
 CUGL_API cugl_status cugl_gemmlowp_update_quantization(cugl_gemm_plan *plan, const cugl_gemm_desc *desc);
-/* Which kernel the plan will launch: "tcgen05" (TMA + tcgen05.mma.kind::i8) or "simt" (shape / stride
- * not expressible as a TMA tensor map). */
+/* Which kernel the plan will launch: "tcgen05_2cta" (TMA + tcgen05.mma.cta_group::2.kind::i8 on SM pairs,
+ * 256 x 256 tiles), "tcgen05" (one CTA per 128 x N tile) or "simt" (shape / stride not expressible as a TMA
+ * tensor map). */
 CUGL_API const char *cugl_gemmlowp_plan_kernel(const cugl_gemm_plan *plan);
 /* Force the generic kernel (testing aid: both kernels must agree bit for bit). */
 CUGL_API cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on);
+/* on = 0 keeps the plan to the one-CTA tensor-core kernels (testing aid). */
+CUGL_API cugl_status cugl_gemmlowp_plan_allow_pair_kernel(cugl_gemm_plan *plan, int on);
 /* Number of kernels one cugl_gemmlowp_run of this plan launches. */
 CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
 

@@ -41,7 +41,7 @@ def test_config1_fused_and_two_stage(ctx, port, gemm_golden):
     assert (qm, sh) == (1099511552, 8)
     out, kernel = gpu_gemmlowp(ctx, c1["a"], c1["b"], c1["bias"], c1["a_off"], c1["b_off"], qm, sh, c1["offset"],
                                c1["lo"], c1["hi"], np.uint8)
-    assert kernel == "tcgen05"
+    assert kernel == "tcgen05"  # 64 rows: one CTA per tile
     assert np.array_equal(out, gemm_golden["c1_out"])
     acc, _ = gpu_gemmlowp(ctx, c1["a"], c1["b"], None, c1["a_off"], c1["b_off"], 0, 0, 0, 0, 0, np.int32)
     assert np.array_equal(acc, gemm_golden["c1_acc"])
@@ -75,9 +75,10 @@ def test_fused_vs_oracle(ctx, port, M, N, K, types):
     # per-tensor, both offsets
     ao, bo = int(rng.integers(-200, 200)), int(rng.integers(-200, 200))
     qm, sh = capi.calculate_quantized_multiplier(np.float32(3.0 / (K * 40.0)))
-    for simt in (False, True):
-        got, kern = gpu_gemmlowp(ctx, a, b, bias, ao, bo, qm, sh, 7, lo, hi, ad, force_simt=simt, ldd_pad=16)
-        want = port.gemmlowp_fused(a, b, bias, ao, bo, [qm], [sh], 7, lo, hi, ad)
+    want = port.gemmlowp_fused(a, b, bias, ao, bo, [qm], [sh], 7, lo, hi, ad)
+    for simt, pair in ((False, True), (False, False), (True, True)):  # SM-pair, one-CTA and generic kernels
+        got, kern = gpu_gemmlowp(ctx, a, b, bias, ao, bo, qm, sh, 7, lo, hi, ad, force_simt=simt, ldd_pad=16,
+                                 pair=pair)
         assert np.array_equal(got, want), (kern, np.argwhere(got != want)[:5])
     # per-channel (b_offset 0), log-uniform scales as in the benchmark configs
     ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), N)).astype(np.float32)
@@ -200,13 +201,16 @@ def test_config2_full_size_properties(ctx, port):
     c = config2()
     mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])
     out, kern = gpu_gemmlowp(ctx, c["a"], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8)
-    assert kern == "tcgen05"
+    assert kern == "tcgen05_2cta"
     rows = np.r_[0:64, 2000:2064, 4032:4096]
     want = port.gemmlowp_fused(c["a"][rows], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8)
     assert np.array_equal(out[rows], want)
     ref2, _ = gpu_gemmlowp(ctx, c["a"], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8,
                            force_simt=True)
     assert np.array_equal(out, ref2)
+    one_cta, kern1 = gpu_gemmlowp(ctx, c["a"], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8,
+                                  pair=False)
+    assert kern1 == "tcgen05" and np.array_equal(out, one_cta)
     perm = np.random.default_rng(0).permutation(4096)
     outp, _ = gpu_gemmlowp(ctx, c["a"][perm], c["b"], c["bias"], c["a_off"], 0, mult, shift, 0, -128, 127, np.int8)
     assert np.array_equal(outp, out[perm])
