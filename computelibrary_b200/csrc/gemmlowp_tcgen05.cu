@@ -31,10 +31,20 @@ namespace
 constexpr int      BLOCK_M     = 128;
 constexpr int      BLOCK_K     = 128; // bytes == int8 elements: one 128-byte swizzle row
 constexpr int      UMMA_K      = 32;  // K per tcgen05.mma.kind::i8
-constexpr int      kProdLanes  = 4;                        // lanes of the producer warp that issue copies
-constexpr int      kEpiWarps   = 8;                        // two per tensor-memory lane quarter
+#ifndef CUGL_PROD_WARPS
+#define CUGL_PROD_WARPS 2
+#endif
+#ifndef CUGL_EPI_WARPS
+#define CUGL_EPI_WARPS 8
+#endif
+constexpr int      kProdWarps  = CUGL_PROD_WARPS;          // producer warps (one issuing lane each)
+constexpr int      kProdLanes  = kProdWarps;               // independent copy issuers per CTA
+constexpr int      kMmaWarp    = kProdWarps;               // index of the MMA-issuing warp
+constexpr int      kFirstEpi   = kProdWarps + 1;           // first epilogue warp
+constexpr int      kEpiWarps   = CUGL_EPI_WARPS;           // a multiple of 4: one or two per tensor-memory lane quarter
 constexpr int      kEpiThreads = kEpiWarps * 32;
-constexpr int      kThreads    = 64 + kEpiThreads;          // producer warp + MMA warp + epilogue warps
+constexpr int      kThreads    = 32 * (kProdWarps + 1) + kEpiThreads;
+static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps: 4 or 8");
 constexpr int      A_STAGE     = BLOCK_M * BLOCK_K;
 constexpr long long kSpinLimit = 4000000000ll; // clock64 ticks, about two seconds
 
@@ -61,7 +71,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile("{\n\t"
                  ".reg .pred p;\n\t"
+#ifdef CUGL_TEST_WAIT
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#else
                  "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+#endif
                  "selp.u32 %0, 1, 0, p;\n\t"
                  "}"
                  : "=r"(ok)
@@ -191,6 +205,21 @@ __device__ __forceinline__ void trace_event(long long *trace, int i, int e)
     }
 }
 
+#ifdef CUGL_KTRACE
+// Development aid: clock64 of per-k-block events of the second tile of each CTA.
+// Layout after the per-tile area: [cta][4 series][64 k-blocks].
+__device__ __forceinline__ void ktrace(long long *trace, int ti, int series, int kb)
+{
+    if (trace != nullptr && ti == 1 && kb < 64)
+    {
+        trace[static_cast<long long>(gridDim.x) * kTraceTiles * kTraceEvents +
+              (static_cast<long long>(blockIdx.x) * 4 + series) * 64 + kb] = clock64();
+    }
+}
+#else
+__device__ __forceinline__ void ktrace(long long *, int, int, int) {}
+#endif
+
 __device__ __forceinline__ void trace_value(long long *trace, int i, int e, long long v)
 {
     if (trace != nullptr && i < kTraceTiles)
@@ -207,17 +236,17 @@ __device__ __forceinline__ bool epi_barrier_and(bool pred)
     asm volatile("{\n\t"
                  ".reg .pred p, q;\n\t"
                  "setp.ne.u32 q, %1, 0;\n\t"
-                 "bar.red.and.pred p, 1, 256, q;\n\t"
+                 "bar.red.and.pred p, 1, %2, q;\n\t"
                  "selp.u32 %0, 1, 0, p;\n\t"
                  "}"
                  : "=r"(r)
-                 : "r"(static_cast<uint32_t>(pred))
+                 : "r"(static_cast<uint32_t>(pred)), "n"(kEpiThreads)
                  : "memory");
     return r != 0;
 }
 __device__ __forceinline__ void epi_barrier()
 {
-    asm volatile("bar.sync 2, 256;" ::: "memory");
+    asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
 }
 
 struct TileParams
@@ -485,9 +514,9 @@ template <int BLOCK_N, bool kS32Out>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4 *s_col, const TileParams &tp,
                                                    const EpilogueParams &ep, int warp, int lane, int m0, int n0)
 {
-    constexpr int NCOLS    = BLOCK_N / 2;
-    const int     quad     = warp & 3;
-    const int     half     = (warp - 2) >> 2; // warps 2..5 -> 0, 6..9 -> 1
+    constexpr int NCOLS    = BLOCK_N / (kEpiWarps / 4);
+    const int     quad     = warp & 3;               // tensor-memory lane quarter this warp may read
+    const int     half     = (warp - kFirstEpi) >> 2; // which share of the columns
     const int     m        = m0 + quad * 32 + lane;
     const int32_t row_term = (ep.rowsum != nullptr && m < tp.M) ? ep.b_off * __ldg(ep.rowsum + m) : 0;
     const uint32_t t_addr  = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NCOLS;
@@ -501,14 +530,20 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
     }
 }
 
-template <int BLOCK_N, int STAGES>
+// KSUB = 128-byte K sub-blocks per pipeline stage.  One barrier hand-over (wait, MMAs, commit) costs the
+// issuing thread about 550 clocks whatever it covers, more than the 512 clocks four MMAs keep the tensor
+// cores busy, so a stage carries two sub-blocks (eight MMAs) wherever shared memory leaves room for three
+// such stages.
+template <int BLOCK_N, int STAGES, int KSUB>
 struct SmemPlan
 {
     static_assert(STAGES >= kProdLanes, "the producer lanes of one round must own distinct stages");
-    static constexpr int B_STAGE    = BLOCK_N * BLOCK_K;
-    static constexpr int STAGE      = A_STAGE + B_STAGE;
+    static constexpr int B_SUB      = BLOCK_N * BLOCK_K;          // one K sub-block of the B tile
+    static constexpr int A_STAGE_K  = KSUB * A_STAGE;
+    static constexpr int B_STAGE    = KSUB * B_SUB;
+    static constexpr int STAGE      = A_STAGE_K + B_STAGE;
     static constexpr int OFF_A      = 0;
-    static constexpr int OFF_B      = STAGES * A_STAGE;
+    static constexpr int OFF_B      = STAGES * A_STAGE_K;
     static constexpr int OFF_COL    = STAGES * STAGE;             // int4 per column
     static constexpr int OFF_BAR    = OFF_COL + BLOCK_N * 16;     // full[S], empty[S], tfull[2], tempty[2]
     static constexpr int OFF_MISC   = OFF_BAR + (2 * STAGES + 4) * 8; // tmem base, abort flag
@@ -517,12 +552,12 @@ struct SmemPlan
     static constexpr int TMEM_COLS  = 2 * BLOCK_N;
 };
 
-template <int BLOCK_N, int STAGES, bool kS32Out>
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                             const TileParams tp, const EpilogueParams ep)
 {
-    using P = SmemPlan<BLOCK_N, STAGES>;
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -543,7 +578,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int num_m_blocks = (tp.M + BLOCK_M - 1) / BLOCK_M;
     const int num_n_blocks = (tp.N + BLOCK_N - 1) / BLOCK_N;
     const int num_tiles    = num_m_blocks * num_n_blocks;
-    const int num_kb       = (tp.K + BLOCK_K - 1) / BLOCK_K;
+    const int num_kb       = (tp.K + KSUB * BLOCK_K - 1) / (KSUB * BLOCK_K); // pipeline stages per tile
 
     if (threadIdx.x == 0)
     {
@@ -560,7 +595,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1)
+    if (warp == kMmaWarp)
     {
         tmem_alloc(smem_u32(s_tmem), P::TMEM_COLS);
     }
@@ -569,43 +604,51 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
-    if (warp == 0)
+    if (warp < kProdWarps)
     {
         // ---------------------------------------------------------------- TMA producer
-        // kProdLanes lanes issue copies independently of each other: lane j owns the k-blocks g = j,
-        // j + kProdLanes, ... of this CTA's (tile, k-block) sequence and runs its own wait / issue loop (the
-        // lanes diverge on purpose; nothing inside the loop is warp-collective).  One thread alone sustains
-        // only about one stage per 600 clocks, less than the tensor cores consume.
-        if (lane < kProdLanes)
+        // kProdWarps warps issue copies independently of each other (one lane each): warp j owns the k-blocks
+        // g = j, j + kProdWarps, ... of this CTA's (tile, k-block) sequence.  One thread alone sustains only
+        // about one stage per 600 clocks (wait + expect_tx + two tensor copies), less than the tensor cores
+        // consume.
+        if (lane == 0)
         {
+            const int issuer   = warp; // this warp's share of the k-block sequence
             const int my_tiles = static_cast<int>(blockIdx.x) < num_tiles
                                      ? (num_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1
                                      : 0;
             const int total_kb = my_tiles * num_kb;
             uint32_t  issued = 0, parities = 0;
             bool      ok = true;
-            int       ti = 0, kb = lane; // (tile ordinal, k-block) of g, kept incrementally
+            int       ti = 0, kb = issuer; // (tile ordinal, k-block) of g, kept incrementally
             while (kb >= num_kb)
             {
                 kb -= num_kb;
                 ++ti;
             }
-            int      st = lane % STAGES;
-            uint32_t ph = static_cast<uint32_t>(lane / STAGES) & 1u;
-            for (int g = lane; g < total_kb; g += kProdLanes)
+            int      st = issuer % STAGES;
+            uint32_t ph = static_cast<uint32_t>(issuer / STAGES) & 1u;
+            for (int g = issuer; g < total_kb; g += kProdLanes)
             {
                 ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
                 if (!ok)
                 {
                     break;
                 }
+                ktrace(tp.trace, ti, 2, kb);
                 const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
                 const int m0   = (tile % num_m_blocks) * BLOCK_M;
                 const int n0   = (tile / num_m_blocks) * BLOCK_N;
                 if (kb == 0) trace_event(tp.trace, ti, 0);
                 mbar_expect_tx(full_bar(st), P::STAGE);
-                tma_load_2d(sA + st * A_STAGE, &tmap_a, kb * BLOCK_K, m0, full_bar(st));
-                tma_load_2d(sB + st * P::B_STAGE, &tmap_b, kb * BLOCK_K, n0, full_bar(st));
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                {
+                    const int k0 = (kb * KSUB + sub) * BLOCK_K; // beyond K: the copy delivers zeros
+                    tma_load_2d(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, full_bar(st));
+                    tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
+                }
+                ktrace(tp.trace, ti, 3, kb);
                 issued |= 1u << st;
                 parities = (parities & ~(1u << st)) | (ph << st);
                 // advance g by kProdLanes
@@ -644,7 +687,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
     }
-    else if (warp == 1)
+    else if (warp == kMmaWarp)
     {
         // ---------------------------------------------------------------- MMA issuer
         // One lane runs the whole loop: tcgen05.mma / commit are single-thread instructions, and 32 lanes
@@ -653,7 +696,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         {
             int      s = 0, as = 0;
             uint32_t ph = 0, aph = 0;
-            bool     ok = true;
+            bool     ok = true, have = false; // have: the current stage's operands are known to have landed
             int      ti = 0;
             const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
@@ -670,29 +713,47 @@ __global__ void __launch_bounds__(kThreads, 1)
                 long long      waited = 0;
                 for (int kb = 0; kb < num_kb; ++kb)
                 {
-                    const long long w0 = tp.trace != nullptr ? clock64() : 0;
-                    ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
-                    if (tp.trace != nullptr) waited += clock64() - w0;
-                    if (!ok)
+                    if (!have)
                     {
-                        break;
+                        const long long w0 = tp.trace != nullptr ? clock64() : 0;
+                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                        if (tp.trace != nullptr) waited += clock64() - w0;
+                        if (!ok)
+                        {
+                            break;
+                        }
                     }
+                    // Ask for the NEXT stage's barrier now: the answer travels while this stage's MMAs and
+                    // commit are being issued, which takes the barrier round trip off the issue path.
+                    int      sn  = s + 1;
+                    uint32_t phn = ph;
+                    if (sn == STAGES)
+                    {
+                        sn = 0;
+                        phn ^= 1;
+                    }
+                    have = mbar_try_wait(full_bar(sn), phn);
                     tc_fence_after();
+                    ktrace(tp.trace, ti, 0, kb);
                     if (kb == 0) trace_event(tp.trace, ti, 2);
                     // stage offset in 16-byte units; advancing K by 32 bytes inside the swizzle row: +2
-                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * A_STAGE) >> 4);
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                    for (int sub = 0; sub < KSUB; ++sub)
                     {
-                        umma_i8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, tp.idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        {
+                            umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                    b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                    (kb | sub | k) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit(empty_bar(s)); // frees the smem stage once these MMAs have read it
-                    if (++s == STAGES)
-                    {
-                        s = 0;
-                        ph ^= 1;
-                    }
+                    ktrace(tp.trace, ti, 1, kb);
+                    s  = sn;
+                    ph = phn;
                 }
                 if (ok)
                 {
@@ -712,7 +773,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     else
     {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
-        const int et = threadIdx.x - 64; // 0..255
+        const int et = threadIdx.x - 32 * kFirstEpi; // 0 .. kEpiThreads-1
         int       as = 0;
         uint32_t  aph = 0;
         bool      ok = true;
@@ -752,7 +813,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // ---------------------------------------------------------------- teardown
     tc_fence_before();
     __syncthreads();
-    if (warp == 1)
+    if (warp == kMmaWarp)
     {
         tc_fence_after();
         tmem_dealloc(tmem_base, P::TMEM_COLS);
@@ -773,14 +834,16 @@ __global__ void __launch_bounds__(kThreads, 1)
 //   exist in both CTAs and are signalled together by a multicast tcgen05.commit; tempty[] lives in rank 0
 //   and is arrived on by the sixteen epilogue warps of the pair.
 // ---------------------------------------------------------------------------------------------------
-template <int STAGES>
+template <int STAGES, int KSUB>
 struct SmemPlan2
 {
     static constexpr int BLOCK_N   = 256;
-    static constexpr int B_STAGE   = (BLOCK_N / 2) * BLOCK_K; // this CTA's half of the B tile
-    static constexpr int STAGE     = A_STAGE + B_STAGE;
+    static constexpr int B_SUB     = (BLOCK_N / 2) * BLOCK_K; // one K sub-block of this CTA's half of the B tile
+    static constexpr int A_STAGE_K = KSUB * A_STAGE;
+    static constexpr int B_STAGE   = KSUB * B_SUB;
+    static constexpr int STAGE     = A_STAGE_K + B_STAGE;
     static constexpr int OFF_A     = 0;
-    static constexpr int OFF_B     = STAGES * A_STAGE;
+    static constexpr int OFF_B     = STAGES * A_STAGE_K;
     static constexpr int OFF_COL   = STAGES * STAGE;
     static constexpr int OFF_BAR   = OFF_COL + BLOCK_N * 16;
     static constexpr int OFF_MISC  = OFF_BAR + (2 * STAGES + 4) * 8;
@@ -789,13 +852,13 @@ struct SmemPlan2
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
 };
 
-template <int STAGES, bool kS32Out>
+template <int STAGES, int KSUB, bool kS32Out>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                  const __grid_constant__ CUtensorMap tmap_b, const TileParams tp,
                                  const EpilogueParams ep)
 {
-    using P               = SmemPlan2<STAGES>;
+    using P               = SmemPlan2<STAGES, KSUB>;
     constexpr int BLOCK_N = P::BLOCK_N;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -819,7 +882,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int num_m_blocks = (tp.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M);
     const int num_n_blocks = (tp.N + BLOCK_N - 1) / BLOCK_N;
     const int num_tiles    = num_m_blocks * num_n_blocks;
-    const int num_kb       = (tp.K + BLOCK_K - 1) / BLOCK_K;
+    const int num_kb       = (tp.K + KSUB * BLOCK_K - 1) / (KSUB * BLOCK_K); // pipeline stages per tile
     const int first_tile   = static_cast<int>(cluster_id_x());
     const int tile_stride  = static_cast<int>(num_clusters_x());
 
@@ -838,7 +901,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    if (warp == 1)
+    if (warp == kMmaWarp)
     {
         tmem_alloc_pair(smem_u32(s_tmem), P::TMEM_COLS);
     }
@@ -848,29 +911,31 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_after();
     const uint32_t tmem_base = *s_tmem;
 
-    if (warp == 0)
+    if (warp < kProdWarps)
     {
         // ---------------------------------------------------------------- TMA producer (both CTAs)
-        // Same independent-lane issue loops as the one-CTA kernel; the byte counts of both CTAs' copies are
+        // Same independent issue loops as the one-CTA kernel; the byte counts of both CTAs' copies are
         // credited to the leader's "full" barrier, whose expected total the leader's lane announces.
-        if (lane < kProdLanes)
+        if (lane == 0)
         {
+            const int issuer   = warp;
             const int my_tiles = first_tile < num_tiles ? (num_tiles - 1 - first_tile) / tile_stride + 1 : 0;
             const int total_kb = my_tiles * num_kb;
-            int       ti = 0, kb = lane;
+            int       ti = 0, kb = issuer;
             while (kb >= num_kb)
             {
                 kb -= num_kb;
                 ++ti;
             }
-            int      st = lane % STAGES;
-            uint32_t ph = static_cast<uint32_t>(lane / STAGES) & 1u;
-            for (int g = lane; g < total_kb; g += kProdLanes)
+            int      st = issuer % STAGES;
+            uint32_t ph = static_cast<uint32_t>(issuer / STAGES) & 1u;
+            for (int g = issuer; g < total_kb; g += kProdLanes)
             {
                 if (!mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER))
                 {
                     break;
                 }
+                ktrace(tp.trace, ti, 2, kb);
                 const int tile = first_tile + ti * tile_stride;
                 const int m0   = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
                 const int n0   = (tile / num_m_blocks) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
@@ -880,8 +945,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     mbar_expect_tx(full_bar(st), 2 * P::STAGE); // the bytes of both CTAs
                 }
-                tma_load_2d_pair(sA + st * A_STAGE, &tmap_a, kb * BLOCK_K, m0, leader_full);
-                tma_load_2d_pair(sB + st * P::B_STAGE, &tmap_b, kb * BLOCK_K, n0, leader_full);
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                {
+                    const int k0 = (kb * KSUB + sub) * BLOCK_K;
+                    tma_load_2d_pair(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, leader_full);
+                    tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, leader_full);
+                }
+                ktrace(tp.trace, ti, 3, kb);
                 kb += kProdLanes;
                 while (kb >= num_kb)
                 {
@@ -898,14 +969,14 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         __syncwarp();
     }
-    else if (warp == 1)
+    else if (warp == kMmaWarp)
     {
         // ---------------------------------------------------------------- MMA issuer (leader CTA only)
         if (leader && lane == 0)
         {
             int      s = 0, as = 0;
             uint32_t ph = 0, aph = 0;
-            bool     ok = true;
+            bool     ok = true, have = false; // have: the current stage's operands are known to have landed
             int      ti = 0;
             const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
@@ -922,28 +993,46 @@ __global__ void __launch_bounds__(kThreads, 1)
                 long long      waited = 0;
                 for (int kb = 0; kb < num_kb; ++kb)
                 {
-                    const long long w0 = tp.trace != nullptr ? clock64() : 0;
-                    ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
-                    if (tp.trace != nullptr) waited += clock64() - w0;
-                    if (!ok)
+                    if (!have)
                     {
-                        break;
+                        const long long w0 = tp.trace != nullptr ? clock64() : 0;
+                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                        if (tp.trace != nullptr) waited += clock64() - w0;
+                        if (!ok)
+                        {
+                            break;
+                        }
                     }
+                    // Ask for the NEXT stage's barrier now: the answer travels while this stage's MMAs and
+                    // commit are being issued, which takes the barrier round trip off the issue path.
+                    int      sn  = s + 1;
+                    uint32_t phn = ph;
+                    if (sn == STAGES)
+                    {
+                        sn = 0;
+                        phn ^= 1;
+                    }
+                    have = mbar_try_wait(full_bar(sn), phn);
                     tc_fence_after();
+                    ktrace(tp.trace, ti, 0, kb);
                     if (kb == 0) trace_event(tp.trace, ti, 2);
-                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * A_STAGE) >> 4);
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                    for (int sub = 0; sub < KSUB; ++sub)
                     {
-                        umma_i8_pair(d_tmem, a_desc + 2u * k, b_desc + 2u * k, tp.idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        {
+                            umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                         (kb | sub | k) != 0 ? 1u : 0u);
+                        }
                     }
                     umma_commit_pair(empty_bar(s)); // frees this stage in both CTAs
-                    if (++s == STAGES)
-                    {
-                        s = 0;
-                        ph ^= 1;
-                    }
+                    ktrace(tp.trace, ti, 1, kb);
+                    s  = sn;
+                    ph = phn;
                 }
                 if (ok)
                 {
@@ -963,7 +1052,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     else
     {
         // ---------------------------------------------------------------- epilogue (warps 2..9, both CTAs)
-        const int et = threadIdx.x - 64; // 0..255
+        const int et = threadIdx.x - 32 * kFirstEpi; // 0 .. kEpiThreads-1
         int       as = 0;
         uint32_t  aph = 0;
         bool      ok = true;
@@ -1004,7 +1093,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     tc_fence_before();
     __syncthreads();
     cluster_sync(); // neither CTA leaves (or frees tensor memory) while its peer may still touch it
-    if (warp == 1)
+    if (warp == kMmaWarp)
     {
         tc_fence_after();
         tmem_dealloc_pair(tmem_base, P::TMEM_COLS);
@@ -1053,10 +1142,10 @@ bool encode_operand_map(CUtensorMap *map, const void *base, int rows, int K, int
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int BLOCK_N, int STAGES, bool kS32Out>
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
 cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
 {
-    using P = SmemPlan<BLOCK_N, STAGES>;
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     CUtensorMap map_a, map_b;
     if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
@@ -1064,7 +1153,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
-    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, kS32Out>;
+    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
     {
@@ -1089,10 +1178,10 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel");
 }
 
-template <int STAGES, bool kS32Out>
+template <int STAGES, int KSUB, bool kS32Out>
 cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
 {
-    using P = SmemPlan2<STAGES>;
+    using P = SmemPlan2<STAGES, KSUB>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     CUtensorMap map_a, map_b;
     if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
@@ -1100,7 +1189,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
-    auto kernel = gemmlowp_tcgen05_2cta_kernel<STAGES, kS32Out>;
+    auto kernel = gemmlowp_tcgen05_2cta_kernel<STAGES, KSUB, kS32Out>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
     {
@@ -1163,16 +1252,16 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
     const bool s32 = ep.stage == CUGL_STAGE_NONE;
     if (allow_pair && gemmlowp_tcgen05_uses_pair(op))
     {
-        return s32 ? launch_variant_2cta<6, true>(ctx, op, ep) : launch_variant_2cta<6, false>(ctx, op, ep);
+        return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);
     }
     if (op.N > 128)
     {
-        return s32 ? launch_variant<256, 4, true>(ctx, op, ep) : launch_variant<256, 4, false>(ctx, op, ep);
+        return s32 ? launch_variant<256, 4, 1, true>(ctx, op, ep) : launch_variant<256, 4, 1, false>(ctx, op, ep);
     }
     if (op.N > 64)
     {
-        return s32 ? launch_variant<128, 6, true>(ctx, op, ep) : launch_variant<128, 6, false>(ctx, op, ep);
+        return s32 ? launch_variant<128, 3, 2, true>(ctx, op, ep) : launch_variant<128, 3, 2, false>(ctx, op, ep);
     }
-    return s32 ? launch_variant<64, 8, true>(ctx, op, ep) : launch_variant<64, 8, false>(ctx, op, ep);
+    return s32 ? launch_variant<64, 4, 2, true>(ctx, op, ep) : launch_variant<64, 4, 2, false>(ctx, op, ep);
 }
 } // namespace cugl

@@ -45,7 +45,11 @@ struct GemmCore
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
+#ifdef CUGL_LDBT_PAD
+        ldbt = round_up(K, 128) + CUGL_LDBT_PAD;
+#else
         ldbt = round_up(K, 128);
+#endif
         CUGL_TRY(cugl_malloc(ctx, static_cast<size_t>(ldbt) * N * n_b_copies, reinterpret_cast<void **>(&d_bt)));
         CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * N * n_b_copies, reinterpret_cast<void **>(&d_colsum)));
         CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * rowsum_len, reinterpret_cast<void **>(&d_rowsum)));
