@@ -2,12 +2,15 @@
 // requantising int8 kernels (src/core/NEON/kernels/arm_gemm/gemm_qint8.cpp, quantized.cpp:55-267) and
 // for CpuGemmLowpOffsetContributionOutputStageKernel, fused into one persistent kernel.
 //
-//   warp 0      TMA producer: cp.async.bulk.tensor tiles of A [128 x 128 B] and Bt [BLOCK_N x 128 B]
-//               into a STAGES-deep ring of 128-byte-swizzled shared-memory buffers
-//   warp 1      MMA issuer: tcgen05.mma.cta_group::1.kind::i8, M=128, N=BLOCK_N, K=32 per instruction,
-//               int32 accumulators in tensor memory, double buffered (2 x BLOCK_N columns)
-//   warps 2..9  epilogue (two warps per tensor-memory lane quarter, half of the columns each): tcgen05.ld the accumulator rows, add the offset / bias terms, requantise
-//               with the reference's SQDMULH + rounding shift, clamp, and store 8-bit (or int32) rows
+//   producer warp(s)  TMA: cp.async.bulk.tensor tiles of A [128 x 128 B] and Bt [BLOCK_N x 128 B] into a
+//                     STAGES-deep ring of 128-byte-swizzled shared-memory buffers (KSUB K sub-blocks per stage)
+//   MMA warp          one lane issues tcgen05.mma.cta_group::1.kind::i8, M=128, N=BLOCK_N, K=32 per
+//                     instruction; int32 accumulators in tensor memory, double buffered (2 x BLOCK_N columns)
+//   epilogue warps    one (or two) per tensor-memory lane quarter: tcgen05.ld the accumulator rows, add the
+//                     offset / bias terms, requantise with the reference's SQDMULH + rounding shift, clamp,
+//                     and store 8-bit (or int32) rows
+// Warp counts are compile-time (CUGL_PROD_WARPS, CUGL_EPI_WARPS); one producer and four epilogue warps
+// measured fastest: every extra resident warp competes for issue slots with the single-thread issue loops.
 //
 // The epilogue of tile i overlaps the main loop of tile i+1 through the two accumulator buffers.
 //
@@ -32,10 +35,10 @@ constexpr int      BLOCK_M     = 128;
 constexpr int      BLOCK_K     = 128; // bytes == int8 elements: one 128-byte swizzle row
 constexpr int      UMMA_K      = 32;  // K per tcgen05.mma.kind::i8
 #ifndef CUGL_PROD_WARPS
-#define CUGL_PROD_WARPS 2
+#define CUGL_PROD_WARPS 1
 #endif
 #ifndef CUGL_EPI_WARPS
-#define CUGL_EPI_WARPS 8
+#define CUGL_EPI_WARPS 4
 #endif
 constexpr int      kProdWarps  = CUGL_PROD_WARPS;          // producer warps (one issuing lane each)
 constexpr int      kProdLanes  = kProdWarps;               // independent copy issuers per CTA
