@@ -91,6 +91,7 @@ _SIGNATURES = {
     "cugl_gemmlowp_plan_force_simt": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_allow_pair_kernel": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
+    "cugl_gemmlowp_run_noalloc": (C.c_int, [_vp, C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp]),
     "cugl_reduce_rows": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_reduce_cols": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_offset_contribution": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _i32, _i32]),
@@ -296,6 +297,12 @@ def make_gemm_desc(M, N, K, a_dtype, b_dtype, dst_dtype, a_offset=0, b_offset=0,
     d.has_bias = int(has_bias)
     d.reshape_b_only_on_first_run = int(b_constant)
     return d, keep
+
+
+def gemmlowp_run_noalloc(stream: int, desc: GemmDesc, a, b, bias, multipliers, shifts, dst):
+    """cugl_gemmlowp_run_noalloc: one fused GEMMLowp on `stream` using the library's fixed workspace."""
+    _check(load_library().cugl_gemmlowp_run_noalloc(_vp(stream) if stream else None, C.byref(desc), _dptr(a), _dptr(b),
+                                                   _dptr(bias), _dptr(multipliers), _dptr(shifts), _dptr(dst)))
 
 
 def gemm_validate(desc: GemmDesc):

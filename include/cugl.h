@@ -195,6 +195,24 @@ CUGL_API cugl_status cugl_gemmlowp_plan_allow_pair_kernel(cugl_gemm_plan *plan, 
 /* Number of kernels one cugl_gemmlowp_run of this plan launches. */
 CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
 
+/* Fused GEMMLowp that allocates nothing.  No counterpart in the reference: Compute Library always lets the
+ * function object own its workspace.  For callers that cannot call cudaMalloc -- a serving loop whose device
+ * memory is fully committed to its own arena, a plugin that may not touch the host's allocator, code inside
+ * a stream capture.  The workspace (K-major copy of B, column sums, row sums) is a fixed array inside the
+ * library image, about 4.3 MB held by every GPU that loads the library until the process exits.
+ *   - Limits: batch == 1, M <= 65536, N <= 8192, N * round_up(K, 128) <= 4 MiB; larger problems are rejected
+ *     with CUGL_INVALID_ARGUMENT (use the planned entry points).
+ *   - Per-channel multipliers / shifts are read from DEVICE vectors (the h_ pointers of desc are ignored).
+ *   - stream is the cudaStream_t to enqueue on (NULL = default stream); the device must be current.
+ *   - The first call on a device resolves the array's device address and clears a status word; make that
+ *     first call outside any stream capture.
+ *   - All calls share the one array, which keeps the previous call's contents (the column sums are cleared
+ *     by the call itself): calls that overlap on the GPU -- different streams, or graph branches -- race.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine; B is re-laid out on every call. */
+CUGL_API cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_desc *desc, const void *d_a,
+                                               const void *d_b, const int32_t *d_bias,
+                                               const int32_t *d_multipliers, const int32_t *d_shifts, void *d_dst);
+
 /* ------------------------------------------------------------------------------------------------
  * Stand-alone kernels of the path.
  * ---------------------------------------------------------------------------------------------- */
