@@ -1,0 +1,29 @@
+// CUDA counterpart of NEGEMMLowpOutputStage (arm_compute/runtime/NEON/functions/NEGEMMLowpOutputStage.h:85-102):
+// S32 [N, M] (+ S32 bias [N]) -> QASYMM8 / QASYMM8_SIGNED with QUANTIZE_DOWN_FIXEDPOINT.
+#pragma once
+#include "arm_compute/core/TensorInfo.h"
+#include "arm_compute/function_info/GEMMInfo.h"
+#include "arm_compute/runtime/IFunction.h"
+
+namespace arm_compute
+{
+class CUGEMMLowpOutputStage : public IFunction
+{
+public:
+    void          configure(const ITensor *input, const ITensor *bias, ITensor *output, const GEMMLowpOutputStageInfo &info);
+    static Status validate(const ITensorInfo *input, const ITensorInfo *bias, const ITensorInfo *output,
+                           const GEMMLowpOutputStageInfo &info);
+    void          run() override;
+
+private:
+    const ITensor          *_input{nullptr};
+    const ITensor          *_bias{nullptr};
+    ITensor                *_output{nullptr};
+    GEMMLowpOutputStageInfo _info{};
+    void                   *_d_mults{nullptr}; // per-channel vectors on the device
+    void                   *_d_shifts{nullptr};
+
+public:
+    ~CUGEMMLowpOutputStage();
+};
+} // namespace arm_compute

@@ -1,0 +1,83 @@
+#include "arm_compute/runtime/CUDA/functions/CUGEMMLowpOutputStage.h"
+
+#include "arm_compute/runtime/CUDA/CUScheduler.h"
+#include "arm_compute/runtime/CUDA/CUTensor.h"
+
+namespace arm_compute
+{
+Status CUGEMMLowpOutputStage::validate(const ITensorInfo *input, const ITensorInfo *bias, const ITensorInfo *output,
+                                       const GEMMLowpOutputStageInfo &info)
+{
+    // CpuGemmLowpOutputStage::validate (src/cpu/operators/CpuGemmLowpOutputStage.cpp:100-161)
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input == nullptr || output == nullptr, "nullptr tensor info");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input->data_type() != DataType::S32, "input must be S32");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() != DataType::QASYMM8 && output->data_type() != DataType::QASYMM8_SIGNED,
+                                    "output must be QASYMM8 or QASYMM8_SIGNED");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT,
+                                    "only QUANTIZE_DOWN_FIXEDPOINT is implemented");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.gemmlowp_min_bound > info.gemmlowp_max_bound, "min bound above max bound");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->tensor_shape() != input->tensor_shape(), "input and output shapes differ");
+    if (bias != nullptr)
+    {
+        ARM_COMPUTE_RETURN_ERROR_ON_MSG(bias->data_type() != DataType::S32, "bias must be S32");
+        ARM_COMPUTE_RETURN_ERROR_ON_MSG(bias->num_dimensions() > 1 || bias->dimension(0) != input->dimension(0),
+                                        "bias must be a vector of N elements");
+    }
+    if (info.is_quantized_per_channel)
+    {
+        ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.gemmlowp_multipliers.size() < input->dimension(0) ||
+                                            info.gemmlowp_shifts.size() < input->dimension(0),
+                                        "per-channel output stage needs N multipliers and shifts");
+    }
+    return Status{};
+}
+
+void CUGEMMLowpOutputStage::configure(const ITensor *input, const ITensor *bias, ITensor *output,
+                                      const GEMMLowpOutputStageInfo &info)
+{
+    ARM_COMPUTE_ERROR_ON_NULLPTR(input, output);
+    ARM_COMPUTE_ERROR_THROW_ON(validate(input->info(), bias != nullptr ? bias->info() : nullptr, output->info(), info));
+    _input  = input;
+    _bias   = bias;
+    _output = output;
+    _info   = info;
+    if (info.is_quantized_per_channel)
+    {
+        cugl_context *ctx = CUScheduler::get().context();
+        const size_t  n   = input->info()->dimension(0);
+        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_malloc(ctx, n * 4, &_d_mults), ctx, "CUGEMMLowpOutputStage::configure"));
+        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_malloc(ctx, n * 4, &_d_shifts), ctx, "CUGEMMLowpOutputStage::configure"));
+        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_memcpy_h2d(ctx, _d_mults, info.gemmlowp_multipliers.data(), n * 4), ctx, "copy"));
+        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_memcpy_h2d(ctx, _d_shifts, info.gemmlowp_shifts.data(), n * 4), ctx, "copy"));
+        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_sync(ctx), ctx, "sync"));
+    }
+}
+
+void CUGEMMLowpOutputStage::run()
+{
+    cugl_context      *ctx = CUScheduler::get().context();
+    const ITensorInfo *in  = _input->info();
+    const int32_t      N   = static_cast<int32_t>(in->dimension(0));
+    const int32_t      M   = static_cast<int32_t>(in->tensor_shape().total_size_upper(1));
+    ARM_COMPUTE_ERROR_THROW_ON(cu_status(
+        cugl_output_stage(ctx, static_cast<const int32_t *>(cu_device_ptr(_input)),
+                          static_cast<int64_t>(in->strides_in_bytes()[1]), static_cast<const int32_t *>(cu_device_ptr(_bias)),
+                          cu_device_ptr(_output), static_cast<int64_t>(_output->info()->strides_in_bytes()[1]),
+                          _output->info()->data_type() == DataType::QASYMM8 ? CUGL_U8 : CUGL_S8, M, N,
+                          static_cast<const int32_t *>(_d_mults), static_cast<const int32_t *>(_d_shifts),
+                          _info.gemmlowp_multiplier, _info.gemmlowp_shift, _info.is_quantized_per_channel ? N : 1,
+                          _info.gemmlowp_offset, _info.gemmlowp_min_bound, _info.gemmlowp_max_bound),
+        ctx, "CUGEMMLowpOutputStage::run"));
+}
+
+CUGEMMLowpOutputStage::~CUGEMMLowpOutputStage()
+{
+    if (_d_mults != nullptr || _d_shifts != nullptr)
+    {
+        cugl_context *ctx = CUScheduler::get().context();
+        cugl_sync(ctx);
+        cugl_free(ctx, _d_mults);
+        cugl_free(ctx, _d_shifts);
+    }
+}
+} // namespace arm_compute
