@@ -86,6 +86,10 @@ _SIGNATURES = {
     "cugl_gemmlowp_prepare": (C.c_int, [_vp, _vp]),
     "cugl_gemmlowp_run": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_run_host": (C.c_int, [_vp, _vp, _vp, _vp]),
+    "cugl_gemmlowp_run_multi": (C.c_int, [_vp, _vp, _vp, C.POINTER(_vp), _i32]),
+    "cugl_ipc_get_handle": (C.c_int, [_vp, _vp, _vp]),
+    "cugl_ipc_open_handle": (C.c_int, [_vp, _vp, C.POINTER(_vp)]),
+    "cugl_ipc_close_handle": (C.c_int, [_vp, _vp]),
     "cugl_gemmlowp_update_quantization": (C.c_int, [_vp, C.POINTER(GemmDesc)]),
     "cugl_gemmlowp_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_gemmlowp_plan_force_simt": (C.c_int, [_vp, C.c_int]),
@@ -107,6 +111,8 @@ _SIGNATURES = {
     "cugl_conv2d_run_host": (C.c_int, [_vp, _vp, _vp, _vp]),
     "cugl_conv2d_out_dims": (None, [C.POINTER(ConvDesc), _pi32, _pi32]),
     "cugl_conv2d_plan_launches": (C.c_int, [_vp]),
+    "cugl_conv2d_plan_kernel": (C.c_char_p, [_vp]),
+    "cugl_conv2d_plan_allow_implicit": (C.c_int, [_vp, C.c_int]),
 }
 
 _lib = None
@@ -236,6 +242,19 @@ class Context:
     def d2h(self, h_ptr: int, d_ptr: int, nbytes: int):
         self.check(self.lib.cugl_memcpy_d2h(self.handle, _vp(h_ptr), _vp(d_ptr), nbytes))
 
+    def ipc_get_handle(self, d_ptr: int) -> bytes:
+        buf = C.create_string_buffer(64)
+        self.check(self.lib.cugl_ipc_get_handle(self.handle, _vp(d_ptr), buf))
+        return buf.raw
+
+    def ipc_open_handle(self, handle: bytes) -> int:
+        p = _vp()
+        self.check(self.lib.cugl_ipc_open_handle(self.handle, C.create_string_buffer(handle, 64), C.byref(p)))
+        return p.value or 0
+
+    def ipc_close_handle(self, d_ptr: int):
+        self.check(self.lib.cugl_ipc_close_handle(self.handle, _vp(d_ptr)))
+
     # stand-alone kernels --------------------------------------------------------------------------
     def reduce_rows(self, a, dtype, M, K, lda, out, scalar=1):
         self.check(self.lib.cugl_reduce_rows(self.handle, _dptr(a), dtype, M, K, lda, scalar, _dptr(out)))
@@ -346,6 +365,11 @@ class GemmPlan:
     def run(self, a, b, bias, dst):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_run(self.handle, _dptr(a), _dptr(b), _dptr(bias), _dptr(dst)))
 
+    def run_multi(self, a, bias, dsts):
+        """dsts: device pointers (ints / tensors) of every destination matrix, this GPU's own first."""
+        arr = (_vp * len(dsts))(*[_dptr(d) for d in dsts])
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_run_multi(self.handle, _dptr(a), _dptr(bias), arr, len(dsts)))
+
     def run_host(self, h_a: int, h_bias, h_dst: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_run_host(self.handle, _vp(h_a), _vp(h_bias) if h_bias else None,
                                                            _vp(h_dst)))
@@ -435,6 +459,13 @@ class ConvPlan:
     def run_host(self, h_src: int, h_bias, h_dst: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_run_host(self.handle, _vp(h_src), _vp(h_bias) if h_bias else None,
                                                          _vp(h_dst)))
+
+    def allow_implicit(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_implicit(self.handle, int(on)))
+
+    @property
+    def kernel(self) -> str:
+        return self.ctx.lib.cugl_conv2d_plan_kernel(self.handle).decode()
 
     @property
     def launches(self) -> int:

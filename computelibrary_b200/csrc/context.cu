@@ -282,6 +282,45 @@ extern "C"
         return CUGL_SUCCESS;
     }
 
+    // ---- peer access to another process's device buffer (CUDA IPC) --------------------------------
+    cugl_status cugl_ipc_get_handle(cugl_context *ctx, void *d_ptr, void *handle64)
+    {
+        CUGL_NEED_CTX(ctx);
+        static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle is 64 bytes");
+        if (d_ptr == nullptr || handle64 == nullptr)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_ipc_get_handle: NULL argument");
+        }
+        cudaIpcMemHandle_t h;
+        CUGL_CUDA_TRY(ctx, cudaIpcGetMemHandle(&h, d_ptr));
+        std::memcpy(handle64, &h, sizeof(h));
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_ipc_open_handle(cugl_context *ctx, const void *handle64, void **d_ptr)
+    {
+        CUGL_NEED_CTX(ctx);
+        if (handle64 == nullptr || d_ptr == nullptr)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_ipc_open_handle: NULL argument");
+        }
+        cudaIpcMemHandle_t h;
+        std::memcpy(&h, handle64, sizeof(h));
+        CUGL_CUDA_TRY(ctx, cudaSetDevice(ctx->device));
+        CUGL_CUDA_TRY(ctx, cudaIpcOpenMemHandle(d_ptr, h, cudaIpcMemLazyEnablePeerAccess));
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_ipc_close_handle(cugl_context *ctx, void *d_ptr)
+    {
+        CUGL_NEED_CTX(ctx);
+        if (d_ptr != nullptr)
+        {
+            CUGL_CUDA_TRY(ctx, cudaIpcCloseMemHandle(d_ptr));
+        }
+        return CUGL_SUCCESS;
+    }
+
     cugl_status cugl_sync(cugl_context *ctx)
     {
         CUGL_NEED_CTX(ctx);

@@ -252,9 +252,13 @@ __device__ __forceinline__ void epi_barrier()
     asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
 }
 
+constexpr int kMaxExtraDst = 7; // push all-gather: this GPU's tile is also stored into up to 7 peers
+
 struct TileParams
 {
     uint8_t *dst;
+    uint8_t *extra_dst[kMaxExtraDst]; // further copies of the output (peer GPUs' buffers), same ldd
+    int      n_extra;
     int64_t  ldd;
     int      M, N, K;
     uint32_t idesc;
@@ -455,7 +459,8 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
                                                   const EpilogueParams &ep, int m, int n_first, int32_t row_term)
 {
     const bool row_ok = m < tp.M;
-    uint8_t   *drow   = tp.dst + static_cast<int64_t>(m) * tp.ldd;
+    const int64_t row_off = static_cast<int64_t>(m) * tp.ldd;
+    uint8_t      *drow    = tp.dst + row_off;
     uint32_t   va[32], vb[32];
     tmem_ld_x32(t_addr, va);
 #pragma unroll 1
@@ -468,6 +473,10 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         }
         process_chunk<kS32Out, kGeneric>(va, s_col + ch * 32, row_term, ep);
         store_chunk<kS32Out>(va, drow, n_first + ch * 32, row_ok, tp);
+        for (int x = 0; x < tp.n_extra; ++x)
+        {
+            store_chunk<kS32Out>(va, tp.extra_dst[x] + row_off, n_first + ch * 32, row_ok, tp);
+        }
         if (ch + 1 < NCOLS / 32)
         {
             tmem_ld_wait();
@@ -477,6 +486,10 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             }
             process_chunk<kS32Out, kGeneric>(vb, s_col + (ch + 1) * 32, row_term, ep);
             store_chunk<kS32Out>(vb, drow, n_first + (ch + 1) * 32, row_ok, tp);
+            for (int x = 0; x < tp.n_extra; ++x)
+            {
+                store_chunk<kS32Out>(vb, tp.extra_dst[x] + row_off, n_first + (ch + 1) * 32, row_ok, tp);
+            }
         }
     }
 }
@@ -558,7 +571,7 @@ struct SmemPlan
 template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const TileParams tp, const EpilogueParams ep)
+                            const __grid_constant__ TileParams tp, const EpilogueParams ep)
 {
     using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
     extern __shared__ uint8_t smem_raw[];
@@ -858,7 +871,7 @@ struct SmemPlan2
 template <int STAGES, int KSUB, bool kS32Out>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                                 const __grid_constant__ CUtensorMap tmap_b, const TileParams tp,
+                                 const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ TileParams tp,
                                  const EpilogueParams ep)
 {
     using P               = SmemPlan2<STAGES, KSUB>;
@@ -1107,6 +1120,320 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------
+// Implicit-GEMM convolution (NHWC, 8-bit): the same one-CTA pipeline, but the A tile (128 output pixels x
+// 128 bytes of the (ky, kx, c) patch axis) is gathered straight from the input tensor by four extra warps
+// instead of being read from a materialised im2col matrix, which is never written.  This is the role of
+// CpuIm2ColKernel + the arm_gemm "indirect" mode (src/cpu/operators/internal/CpuGemmAssemblyDispatch.cpp:396-431).
+// Eight gather threads share one tile row: each loads one 16-byte piece per K sub-block (a piece never straddles
+// a filter tap because C is a multiple of 16) and stores it with the 128-byte swizzle the tensor cores
+// expect (piece j of row r lands at piece j ^ (r & 7)).  The copies are cp.async (global -> shared without
+// registers) and the stage's barrier is told to arrive when they land (cp.async.mbarrier.arrive), so a whole
+// ring of stages is in flight per thread.  Out-of-image taps copy 16 bytes of the input zero point from a small
+// pad buffer, exactly what im2col would have written (the reference's indirect mode points such taps at a
+// zero-point row as well), so the offset terms of the epilogue need no correction.
+// ---------------------------------------------------------------------------------------------------
+struct ConvGeom
+{
+    const uint8_t *src; // [B][H][W][C]
+    const uint8_t *pad; // 16 bytes of the input zero point per gather thread (kConvPadBytes in all)
+    int            C, W, H, kw, kh, sx, sy, pad_l, pad_t, dil_x, dil_y, Wo, Ho;
+};
+
+constexpr int kGatherWarps  = 8;
+static_assert(kConvPadBytes >= 16 * 32 * kGatherWarps, "one pad piece per gather thread");
+constexpr int kFirstGather  = kFirstEpi + kEpiWarps;
+constexpr int kConvThreads  = kThreads + 32 * kGatherWarps;
+
+template <int BLOCK_N, int STAGES, int KSUB>
+__global__ void __launch_bounds__(kConvThreads, 1)
+    gemmlowp_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ TileParams tp,
+                                 const EpilogueParams ep, const ConvGeom cg)
+{
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+    const uint32_t sA         = smem_u32(smem + P::OFF_A);
+    const uint32_t sB         = smem_u32(smem + P::OFF_B);
+    int4          *s_col      = reinterpret_cast<int4 *>(smem + P::OFF_COL);
+    const uint32_t bar_base   = smem_u32(smem + P::OFF_BAR);
+    auto           full_bar   = [&](int s) { return bar_base + 8u * s; };
+    auto           empty_bar  = [&](int s) { return bar_base + 8u * (STAGES + s); };
+    auto           tfull_bar  = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+    auto           tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    uint32_t      *s_tmem     = reinterpret_cast<uint32_t *>(smem + P::OFF_MISC);
+    volatile int  *s_abort    = reinterpret_cast<volatile int *>(smem + P::OFF_MISC + 4);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int num_m_blocks = (tp.M + BLOCK_M - 1) / BLOCK_M;
+    const int num_n_blocks = (tp.N + BLOCK_N - 1) / BLOCK_N;
+    const int num_tiles    = num_m_blocks * num_n_blocks;
+    const int num_kb       = (tp.K + KSUB * BLOCK_K - 1) / (KSUB * BLOCK_K);
+    const int my_tiles     = static_cast<int>(blockIdx.x) < num_tiles
+                                 ? (num_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1
+                                 : 0;
+
+    if (threadIdx.x == 0)
+    {
+        for (int s = 0; s < STAGES; ++s)
+        {
+            mbar_init(full_bar(s), 1 + 32 * kGatherWarps); // B copy (expect_tx arrive) + one deferred arrival per gather thread
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a)
+        {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), kEpiWarps);
+        }
+        *s_abort = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp)
+    {
+        tmem_alloc(smem_u32(s_tmem), P::TMEM_COLS);
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *s_tmem;
+
+    if (warp < kProdWarps)
+    {
+        // ---------------------------------------------------------------- TMA producer: weights only
+        if (warp == 0 && lane == 0)
+        {
+            int      st = 0;
+            uint32_t ph = 0;
+            for (int ti = 0; ti < my_tiles; ++ti)
+            {
+                const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
+                const int n0   = (tile / num_m_blocks) * BLOCK_N;
+                bool      ok   = true;
+                for (int kb = 0; kb < num_kb && ok; ++kb)
+                {
+                    ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(st), P::B_STAGE);
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub)
+                    {
+                        tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, (kb * KSUB + sub) * BLOCK_K, n0,
+                                    full_bar(st));
+                    }
+                    if (++st == STAGES)
+                    {
+                        st = 0;
+                        ph ^= 1;
+                    }
+                }
+                if (!ok) break;
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp == kMmaWarp)
+    {
+        // ---------------------------------------------------------------- MMA issuer (as the GEMM kernel)
+        if (lane == 0)
+        {
+            int      s = 0, as = 0;
+            uint32_t ph = 0, aph = 0;
+            bool     ok = true, have = false;
+            const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
+            const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
+            for (int ti = 0; ti < my_tiles && ok; ++ti)
+            {
+                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + as * BLOCK_N;
+                for (int kb = 0; kb < num_kb; ++kb)
+                {
+                    if (!have)
+                    {
+                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                        if (!ok) break;
+                    }
+                    int      sn  = s + 1;
+                    uint32_t phn = ph;
+                    if (sn == STAGES)
+                    {
+                        sn = 0;
+                        phn ^= 1;
+                    }
+                    have = mbar_try_wait(full_bar(sn), phn);
+                    tc_fence_after();
+                    // the A rows were written by cp.async (generic proxy); the MMA reads through the async proxy
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub)
+                    {
+#pragma unroll
+                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        {
+                            umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                    b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                    (kb | sub | k) != 0 ? 1u : 0u);
+                        }
+                    }
+                    umma_commit(empty_bar(s));
+                    s  = sn;
+                    ph = phn;
+                }
+                if (ok)
+                {
+                    umma_commit(tfull_bar(as));
+                }
+                if (++as == 2)
+                {
+                    as = 0;
+                    aph ^= 1;
+                }
+            }
+        }
+        __syncwarp();
+    }
+    else if (warp < kFirstGather)
+    {
+        // ---------------------------------------------------------------- epilogue
+        const int et = threadIdx.x - 32 * kFirstEpi;
+        int       as = 0;
+        uint32_t  aph = 0;
+        bool      ok = true;
+        for (int ti = 0; ti < my_tiles; ++ti)
+        {
+            if (!epi_barrier_and(ok))
+            {
+                break;
+            }
+            const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
+            const int m0   = (tile % num_m_blocks) * BLOCK_M;
+            const int n0   = (tile / num_m_blocks) * BLOCK_N;
+            fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+            epi_barrier();
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            if (ok)
+            {
+                tc_fence_after();
+                epilogue_warp_tile<BLOCK_N, false>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0);
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0)
+                {
+                    mbar_arrive(tempty_bar(as));
+                }
+            }
+            if (++as == 2)
+            {
+                as = 0;
+                aph ^= 1;
+            }
+        }
+    }
+    else
+    {
+        // ---------------------------------------------------------------- A gather
+        // Thread layout: 8 consecutive threads copy the eight 16-byte pieces of one 128-byte tile row (coalesced
+        // 64..128-byte runs of the input), 32 rows per pass, kRowsPerThread passes per K sub-block.
+        constexpr int kRowsPerThread = BLOCK_M / (kGatherWarps * 4); // 128 rows / (threads / 8)
+        const int     gt             = threadIdx.x - 32 * kFirstGather;
+        const int     piece          = gt & 7;
+        const int     row0           = gt >> 3;
+        const uint8_t *pad_src       = cg.pad + 16 * gt; // every thread its own copy: no single hot line
+        int           st = 0;
+        uint32_t      ph = 0;
+        bool          ok = true;
+        for (int ti = 0; ti < my_tiles && ok; ++ti)
+        {
+            const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
+            const int m0   = (tile % num_m_blocks) * BLOCK_M;
+            int       yi0[kRowsPerThread], xi0[kRowsPerThread];
+            const uint8_t *img[kRowsPerThread];
+#pragma unroll
+            for (int i = 0; i < kRowsPerThread; ++i)
+            {
+                const int m  = min(m0 + row0 + 32 * i, tp.M - 1); // rows beyond M repeat the last pixel (never stored)
+                const int xo = m % cg.Wo, yo = (m / cg.Wo) % cg.Ho, bi = m / (cg.Wo * cg.Ho);
+                yi0[i]       = yo * cg.sy - cg.pad_t;
+                xi0[i]       = xo * cg.sx - cg.pad_l;
+                img[i]       = cg.src + static_cast<long long>(bi) * cg.H * cg.W * cg.C;
+            }
+            for (int kb = 0; kb < num_kb; ++kb)
+            {
+                if (lane == 0)
+                {
+                    ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
+                }
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+#pragma unroll
+                for (int sub = 0; sub < KSUB; ++sub)
+                {
+                    // beyond K the weights are zero (TMA fill), so any finite A bytes do: keep to the last tap
+                    const int kbyte = min((kb * KSUB + sub) * BLOCK_K + piece * 16, tp.K - 16);
+                    const int tap = kbyte / cg.C, c = kbyte - tap * cg.C;
+                    const int ky = tap / cg.kw, kx = tap - ky * cg.kw;
+#pragma unroll
+                    for (int i = 0; i < kRowsPerThread; ++i)
+                    {
+                        const int      yi  = yi0[i] + ky * cg.dil_y, xi = xi0[i] + kx * cg.dil_x;
+                        const bool     in  = yi >= 0 && yi < cg.H && xi >= 0 && xi < cg.W;
+                        const uint8_t *src = in ? img[i] + (static_cast<long long>(yi) * cg.W + xi) * cg.C + c : pad_src;
+                        const int      r   = row0 + 32 * i;
+                        const uint32_t dst = sA + st * P::A_STAGE_K + sub * A_STAGE + r * 128 + ((piece ^ (r & 7)) << 4);
+                        asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+                    }
+                }
+                // this thread's arrival on the stage's barrier happens when its copies above have landed
+                asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(st)) : "memory");
+                if (++st == STAGES)
+                {
+                    st = 0;
+                    ph ^= 1;
+                }
+            }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory"); // nothing of this thread's is in flight when the CTA leaves
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kMmaWarp)
+    {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, P::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *s_abort != 0)
+    {
+        atomicCAS(tp.status, 0, *s_abort);
+    }
+}
+
+void fill_extra_dst(TileParams &tp, const GemmOperands &op)
+{
+    tp.n_extra = op.n_extra_dst;
+    for (int i = 0; i < kMaxExtraDst; ++i)
+    {
+        tp.extra_dst[i] = i < op.n_extra_dst ? static_cast<uint8_t *>(op.extra_dst[i]) : nullptr;
+    }
+}
+
+uint64_t extra_dst_bits(const GemmOperands &op)
+{
+    uint64_t bits = 0;
+    for (int i = 0; i < op.n_extra_dst; ++i)
+    {
+        bits |= reinterpret_cast<uintptr_t>(op.extra_dst[i]);
+    }
+    return bits;
+}
+
 using EncodeTiledFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                    const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                                    CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -1166,12 +1493,13 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     TileParams tp;
     tp.dst    = static_cast<uint8_t *>(op.dst);
     tp.ldd    = op.ldd;
+    fill_extra_dst(tp, op);
     tp.M      = op.M;
     tp.N      = op.N;
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
-    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
+    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
     tp.status  = ctx->d_status;
     tp.generic = op.generic_stage ? 1 : 0;
     tp.trace   = ctx->d_trace;
@@ -1202,12 +1530,13 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     TileParams tp;
     tp.dst    = static_cast<uint8_t *>(op.dst);
     tp.ldd    = op.ldd;
+    fill_extra_dst(tp, op);
     tp.M      = op.M;
     tp.N      = op.N;
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(P::BLOCK_N >> 3) << 17) | (static_cast<uint32_t>((2 * BLOCK_M) >> 4) << 24);
-    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
+    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
     tp.status  = ctx->d_status;
     tp.generic = op.generic_stage ? 1 : 0;
     tp.trace   = ctx->d_trace;
@@ -1229,6 +1558,59 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     cfg.numAttrs             = 1;
     CUGL_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, tp, ep));
     return CUGL_SUCCESS;
+}
+
+template <int BLOCK_N, int STAGES, int KSUB>
+cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                const ConvOperands &cv)
+{
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
+    static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
+    CUtensorMap map_b;
+    if (!encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, BLOCK_N))
+    {
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the weights operand");
+    }
+    auto        kernel = gemmlowp_conv_tcgen05_kernel<BLOCK_N, STAGES, KSUB>;
+    static bool attr_set[64] = {};
+    if (!attr_set[ctx->device & 63])
+    {
+        CUGL_CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::DYN_BYTES));
+        attr_set[ctx->device & 63] = true;
+    }
+    TileParams tp;
+    tp.dst    = static_cast<uint8_t *>(op.dst);
+    tp.ldd    = op.ldd;
+    fill_extra_dst(tp, op);
+    tp.M      = op.M;
+    tp.N      = op.N;
+    tp.K      = op.K;
+    tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
+               (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
+    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
+    tp.status  = ctx->d_status;
+    tp.generic = op.generic_stage ? 1 : 0;
+    tp.trace   = nullptr;
+    ConvGeom cg;
+    cg.src   = static_cast<const uint8_t *>(cv.src);
+    cg.pad   = static_cast<const uint8_t *>(cv.pad);
+    cg.C     = cv.C;
+    cg.W     = cv.W;
+    cg.H     = cv.H;
+    cg.kw    = cv.kw;
+    cg.kh    = cv.kh;
+    cg.sx    = cv.sx;
+    cg.sy    = cv.sy;
+    cg.pad_l = cv.pad_l;
+    cg.pad_t = cv.pad_t;
+    cg.dil_x = cv.dil_x;
+    cg.dil_y = cv.dil_y;
+    cg.Wo    = cv.Wo;
+    cg.Ho    = cv.Ho;
+    const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
+    const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    kernel<<<grid, kConvThreads, P::DYN_BYTES, ctx->stream>>>(map_b, tp, ep, cg);
+    return check_cuda(ctx, cudaGetLastError(), "gemmlowp_conv_tcgen05_kernel");
 }
 } // namespace
 
@@ -1266,5 +1648,34 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
         return s32 ? launch_variant<128, 3, 2, true>(ctx, op, ep) : launch_variant<128, 3, 2, false>(ctx, op, ep);
     }
     return s32 ? launch_variant<64, 4, 2, true>(ctx, op, ep) : launch_variant<64, 4, 2, false>(ctx, op, ep);
+}
+} // namespace cugl
+
+namespace cugl
+{
+bool gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands &cv)
+{
+    const uint64_t bits = reinterpret_cast<uintptr_t>(cv.src) | reinterpret_cast<uintptr_t>(cv.pad) |
+                          reinterpret_cast<uintptr_t>(op.bt) | static_cast<uint64_t>(op.ldbt);
+    return op.M > 0 && op.N > 0 && op.K >= 16 && (bits & 15) == 0 && (cv.C % 16) == 0 && cv.pad != nullptr &&
+           get_encode_fn() != nullptr;
+}
+
+cugl_status launch_gemmlowp_conv_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                         const ConvOperands &cv)
+{
+    if (ep.stage == CUGL_STAGE_NONE)
+    {
+        return fail(ctx, CUGL_UNSUPPORTED_CONFIG, "implicit convolution needs a quantize-down output stage");
+    }
+    if (op.N > 128)
+    {
+        return launch_conv_variant<256, 4, 1>(ctx, op, ep, cv);
+    }
+    if (op.N > 64)
+    {
+        return launch_conv_variant<128, 3, 2>(ctx, op, ep, cv);
+    }
+    return launch_conv_variant<64, 4, 2>(ctx, op, ep, cv);
 }
 } // namespace cugl

@@ -34,8 +34,25 @@ struct GemmOperands
     int64_t     lda, ldbt, ldd; // bytes
     int         M, N, K;
     bool        a_signed, b_signed;
+    void       *extra_dst[7]; // tensor-core kernels only: further destinations that receive the same output
+    int         n_extra_dst;  //   (peer GPUs' buffers in the push all-gather), same ldd as dst
     bool        generic_stage; // some shift is negative or some multiplier is INT32_MIN (decided on the host)
 };
+
+// Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).
+// bytes of the zero-point pad buffer of the implicit convolution: 16 per gather thread
+constexpr int kConvPadBytes = 16 * 256;
+
+struct ConvOperands
+{
+    const void    *src;    // [B][H][W][C]
+    const void    *pad;    // kConvPadBytes holding the input zero point (source of out-of-image taps)
+    int            C, W, H, B, kw, kh, sx, sy, pad_l, pad_t, dil_x, dil_y, Wo, Ho;
+};
+bool        gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands &cv);
+// op.a / op.lda are unused: the A tile comes from cv.src.  M = B*Ho*Wo, K = kh*kw*C.
+cugl_status launch_gemmlowp_conv_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                         const ConvOperands &cv);
 
 // Generic CUDA-core kernel: any shape, stride and alignment.
 cugl_status launch_gemmlowp_simt(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep);

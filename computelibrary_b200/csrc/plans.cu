@@ -130,7 +130,7 @@ struct GemmCore
 
     // rows x K product against B copy b_copy.
     cugl_status gemm(const void *d_a, int64_t lda, int rows, void *d_dst, int64_t ldd, const int32_t *d_bias,
-                     int b_copy, int rowsum_off) const
+                     int b_copy, int rowsum_off, void *const *extra_dst = nullptr, int n_extra = 0) const
     {
         GemmOperands op{};
         op.a        = d_a;
@@ -145,6 +145,16 @@ struct GemmCore
         op.a_signed = a_signed;
         op.b_signed = b_signed;
         op.generic_stage = generic_stage;
+        op.n_extra_dst   = n_extra;
+        for (int i = 0; i < n_extra; ++i)
+        {
+            op.extra_dst[i] = extra_dst[i];
+        }
+        if (n_extra > 0 && !uses_tcgen05(op))
+        {
+            return fail(ctx, CUGL_UNSUPPORTED_CONFIG,
+                        "several destinations need the tensor-core kernel (16-byte aligned A with 16-byte row pitch)");
+        }
         if (b_off != 0)
         {
             CUGL_TRY(launch_reduce_rows(ctx, d_a, a_signed, rows, K, lda, 1, d_rowsum + rowsum_off));
@@ -370,6 +380,33 @@ extern "C"
                                      plan->b_copies > 1 ? i : 0, i * d.M));
         }
         return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_run_multi(cugl_gemm_plan *plan, const void *d_a, const int32_t *d_bias,
+                                        void *const *d_dsts, int32_t n_dsts)
+    {
+        if (plan == nullptr || d_a == nullptr || d_dsts == nullptr || n_dsts < 1 || n_dsts > 8)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_multi: bad argument");
+        }
+        const cugl_gemm_desc &d = plan->desc;
+        if (!plan->prepared || d.batch != 1)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_multi: needs a prepared plan with batch 1");
+        }
+        for (int i = 0; i < n_dsts; ++i)
+        {
+            if (d_dsts[i] == nullptr)
+            {
+                return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_multi: NULL destination");
+            }
+        }
+        if (d.has_bias && d_bias == nullptr)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_multi: plan was configured with a bias");
+        }
+        return plan->core.gemm(d_a, d.lda, d.M, d_dsts[0], d.ldd, d.has_bias ? d_bias : nullptr, 0, 0, d_dsts + 1,
+                               n_dsts - 1);
     }
 
     cugl_status cugl_gemmlowp_run_host(cugl_gemm_plan *plan, const void *h_a, const int32_t *h_bias, void *h_dst)
@@ -601,7 +638,10 @@ struct cugl_conv_plan
     int                  Wo = 0, Ho = 0;
     int64_t              M = 0, K = 0, Kp = 0;
     bool                 skip_im2col = false;
-    uint8_t             *d_cols      = nullptr; // [M][Kp] im2col matrix
+    bool                 implicit    = false;   // gather the patches inside the GEMM kernel, no im2col matrix
+    bool                 allow_implicit = true;
+    uint8_t             *d_cols      = nullptr; // [M][Kp] im2col matrix (allocated on first explicit run)
+    uint8_t             *d_pad       = nullptr; // kConvPadBytes of the input zero point: source of out-of-image taps
     bool                 prepared    = false;
     void                *d_src_stage = nullptr, *d_dst_stage = nullptr;
     int32_t             *d_bias_stage = nullptr;
@@ -727,9 +767,16 @@ extern "C"
         {
             s = c.upload_stage_vectors(p->h_mults.data(), p->h_shifts.data());
         }
-        if (s == CUGL_SUCCESS && !p->skip_im2col)
+        // Implicit GEMM whenever the gather kernel can address the tensors: channel count a multiple of 16 and
+        // symmetric weights (no row-sum term).  Otherwise explicit im2col.
+        p->implicit = !p->skip_im2col && (desc->C % 16) == 0 && desc->w_zero_point == 0;
+        if (s == CUGL_SUCCESS && p->implicit)
         {
-            s = cugl_malloc(ctx, static_cast<size_t>(p->M) * p->Kp, reinterpret_cast<void **>(&p->d_cols));
+            s = cugl_malloc(ctx, kConvPadBytes, reinterpret_cast<void **>(&p->d_pad));
+            if (s == CUGL_SUCCESS)
+            {
+                s = cugl_memset(ctx, p->d_pad, desc->src_zero_point & 0xff, kConvPadBytes);
+            }
         }
         if (s != CUGL_SUCCESS)
         {
@@ -749,6 +796,7 @@ extern "C"
         cudaStreamSynchronize(plan->ctx->stream);
         plan->core.release();
         cugl_free(plan->ctx, plan->d_cols);
+        cugl_free(plan->ctx, plan->d_pad);
         cugl_free(plan->ctx, plan->d_src_stage);
         cugl_free(plan->ctx, plan->d_dst_stage);
         cugl_free(plan->ctx, plan->d_bias_stage);
@@ -788,10 +836,54 @@ extern "C"
         {
             return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run: plan was configured with a bias");
         }
+        if (plan->implicit && plan->allow_implicit && !plan->core.force_simt)
+        {
+            GemmCore    &c = plan->core;
+            GemmOperands op{};
+            op.a             = nullptr;
+            op.bt            = c.d_bt;
+            op.dst           = d_dst;
+            op.lda           = 0;
+            op.ldbt          = c.ldbt;
+            op.ldd           = d.OFM;
+            op.M             = static_cast<int>(plan->M);
+            op.N             = c.N;
+            op.K             = c.K;
+            op.a_signed      = c.a_signed;
+            op.b_signed      = c.b_signed;
+            op.generic_stage = c.generic_stage;
+            op.n_extra_dst   = 0;
+            ConvOperands cv{};
+            cv.src    = d_src;
+            cv.pad    = plan->d_pad;
+            cv.C      = d.C;
+            cv.W      = d.W;
+            cv.H      = d.H;
+            cv.B      = d.B;
+            cv.kw     = d.kw;
+            cv.kh     = d.kh;
+            cv.sx     = d.stride_x;
+            cv.sy     = d.stride_y;
+            cv.pad_l  = d.pad_left;
+            cv.pad_t  = d.pad_top;
+            cv.dil_x  = d.dil_x;
+            cv.dil_y  = d.dil_y;
+            cv.Wo     = plan->Wo;
+            cv.Ho     = plan->Ho;
+            if (gemmlowp_conv_tcgen05_supported(op, cv))
+            {
+                return launch_gemmlowp_conv_tcgen05(plan->ctx, op, c.epilogue(d.has_bias ? d_bias : nullptr, 0, 0), cv);
+            }
+        }
         const void *a   = d_src;
         int64_t     lda = d.C;
         if (!plan->skip_im2col)
         {
+            if (plan->d_cols == nullptr)
+            {
+                CUGL_TRY(cugl_malloc(plan->ctx, static_cast<size_t>(plan->M) * plan->Kp,
+                                     reinterpret_cast<void **>(&plan->d_cols)));
+            }
             CUGL_TRY(launch_im2col_nhwc(plan->ctx, d_src, plan->d_cols, d.C, d.W, d.H, d.B, d.kw, d.kh, d.stride_x,
                                         d.stride_y, d.pad_left, d.pad_top, d.dil_x, d.dil_y, plan->Wo, plan->Ho,
                                         d.src_zero_point, plan->Kp));
@@ -831,11 +923,38 @@ extern "C"
         return cugl_sync(ctx);
     }
 
+    cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_allow_implicit: NULL plan");
+        }
+        plan->allow_implicit = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan)
+    {
+        if (plan == nullptr)
+        {
+            return "";
+        }
+        if (plan->skip_im2col)
+        {
+            return "gemm";
+        }
+        return (plan->implicit && plan->allow_implicit) ? "implicit" : "im2col";
+    }
+
     int cugl_conv2d_plan_launches(const cugl_conv_plan *plan)
     {
         if (plan == nullptr)
         {
             return 0;
+        }
+        if (plan->implicit && plan->allow_implicit)
+        {
+            return 1;
         }
         return (plan->skip_im2col ? 0 : 1) + 1 + (plan->core.b_off != 0 ? 1 : 0);
     }

@@ -106,6 +106,11 @@ CUGL_API cugl_status cugl_memcpy2d_h2d(cugl_context *ctx, void *d_dst, size_t d_
                                        size_t h_pitch, size_t width_bytes, size_t rows);
 CUGL_API cugl_status cugl_memcpy2d_d2h(cugl_context *ctx, void *h_dst, size_t h_pitch, const void *d_src,
                                        size_t d_pitch, size_t width_bytes, size_t rows);
+/* CUDA IPC: export a cugl_malloc'ed buffer to the other single-GPU processes of the node (64-byte handle) and
+ * map a peer's buffer into this process. */
+CUGL_API cugl_status cugl_ipc_get_handle(cugl_context *ctx, void *d_ptr, void *handle64);
+CUGL_API cugl_status cugl_ipc_open_handle(cugl_context *ctx, const void *handle64, void **d_ptr);
+CUGL_API cugl_status cugl_ipc_close_handle(cugl_context *ctx, void *d_ptr);
 CUGL_API cugl_status cugl_memset(cugl_context *ctx, void *d_ptr, int value, size_t bytes);
 /* Blocks until the stream is idle; reports any asynchronous CUDA error or device-side time-out.
  * (CLScheduler::sync precedent; IFunction::run of a device backend does not block,
@@ -177,6 +182,15 @@ CUGL_API cugl_status cugl_gemmlowp_prepare(cugl_gemm_plan *plan, const void *d_b
  * d_bias may be NULL when has_bias == 0. */
 CUGL_API cugl_status cugl_gemmlowp_run(cugl_gemm_plan *plan, const void *d_a, const void *d_b,
                                        const int32_t *d_bias, void *d_dst);
+/* Fused GEMMLowp + push all-gather step for the column-sharded linear layer: the epilogue stores every
+ * finished 8-bit tile into ALL n_dsts (1..8) destination matrices, which share the descriptor's ldd.  Pass this
+ * GPU's own buffer and the peers' buffers (opened with cugl_ipc_open_handle), each already advanced to this
+ * GPU's first column: the output block then crosses NVLink while later tiles are still being computed, and no
+ * separate all-gather runs.  Plain peer stores, no multicast.  Completion on the peers is established by the
+ * caller (stream sync + a host barrier).  Needs the tensor-core kernel; no counterpart in the reference, which
+ * is single-device. */
+CUGL_API cugl_status cugl_gemmlowp_run_multi(cugl_gemm_plan *plan, const void *d_a, const int32_t *d_bias,
+                                             void *const *d_dsts, int32_t n_dsts);
 /* Same function driven from host buffers: copies A (and bias) in, runs, copies dst out, and blocks
  * until dst is valid.  h_a / h_dst follow lda / ldd of the descriptor. */
 CUGL_API cugl_status cugl_gemmlowp_run_host(cugl_gemm_plan *plan, const void *h_a, const int32_t *h_bias,
@@ -289,6 +303,12 @@ CUGL_API cugl_status cugl_conv2d_run_host(cugl_conv_plan *plan, const void *h_sr
                                           void *h_dst);
 CUGL_API void cugl_conv2d_out_dims(const cugl_conv_desc *desc, int32_t *Wo, int32_t *Ho);
 CUGL_API int  cugl_conv2d_plan_launches(const cugl_conv_plan *plan);
+/* How the plan lowers the convolution: "implicit" (patches gathered inside the tensor-core kernel, no im2col
+ * matrix: channel count a multiple of 16, symmetric weights), "im2col" (explicit CpuIm2ColKernel-style matrix +
+ * GEMMLowp) or "gemm" (1x1 / stride 1 / no padding: the input tensor is the A matrix). */
+CUGL_API const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan);
+/* on = 0 forces the explicit im2col lowering (testing aid: both lowerings must agree bit for bit). */
+CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on);
 
 #ifdef __cplusplus
 }

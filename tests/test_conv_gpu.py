@@ -13,7 +13,8 @@ GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
 
 
-def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1)):
+def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1),
+             implicit=True, want_kernel=None):
     import torch
     B, H, W, Cc = src.shape
     OFM, kh, kw, _ = weights.shape
@@ -25,6 +26,10 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
                                      multipliers=mult if pc else None, shifts=shift if pc else None, dst_zp=out_zp,
                                      min_bound=lo, max_bound=hi, has_bias=bias is not None)
     plan = capi.ConvPlan(ctx, desc, keep)
+    if not implicit:
+        plan.allow_implicit(False)
+    if want_kernel is not None:
+        assert plan.kernel == want_kernel, plan.kernel
     wo, ho = plan.out_dims()
     d_src = torch.from_numpy(src.view(np.uint8)).cuda()
     d_w = torch.from_numpy(weights.view(np.uint8)).cuda()
@@ -65,9 +70,11 @@ def test_conv_vs_oracle(ctx, port, geom, act):
     mult, shift = f32_mults(port, 0.03, ws, 0.05)
     out_zp = 10
     lo, hi = {"none": (0, 255), "relu": (out_zp, 255), "lu_bounded": (out_zp + 2, out_zp + 120)}[act]
-    got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), 128, 0, mult, shift, out_zp, lo, hi)
     want = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), 128, 0, mult, shift, out_zp, lo, hi)
-    assert np.array_equal(got, want)
+    for implicit in (True, False):  # gather-in-kernel and explicit im2col lowerings
+        got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), 128, 0, mult, shift, out_zp, lo, hi,
+                       implicit=implicit)
+        assert np.array_equal(got, want), implicit
 
 
 def test_conv_asymmetric_weights_and_signed(ctx, port):
@@ -92,7 +99,10 @@ def test_config3_full_size(ctx, port):
     c = config3()
     mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])
     out = gpu_conv(ctx, c["src"], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], 0, mult, shift,
-                   c["out_zp"], c["lo"], c["hi"])
+                   c["out_zp"], c["lo"], c["hi"], want_kernel="implicit")
+    explicit = gpu_conv(ctx, c["src"], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], 0, mult, shift,
+                        c["out_zp"], c["lo"], c["hi"], implicit=False, want_kernel="im2col")
+    assert np.array_equal(out, explicit)
     want = port.conv2d_nhwc(c["src"][:2], c["weights"], c["bias"], c["stride"], c["pad"], c["in_zp"], 0, mult, shift,
                             c["out_zp"], c["lo"], c["hi"])
     assert np.array_equal(out[:2], want)
@@ -100,3 +110,22 @@ def test_config3_full_size(ctx, port):
                      c["out_zp"], c["lo"], c["hi"])
     assert np.array_equal(shard, out[28:])
     assert 0.01 < (out == 0).mean() < 0.99
+
+
+@pytest.mark.parametrize("geom", [(3, 1, 1, 1, 64, 96), (3, 2, 1, 1, 128, 300), (1, 2, 0, 1, 256, 64), (5, 1, 2, 1, 32, 40),
+                                  (3, 1, 2, 2, 48, 130), (7, 2, 3, 1, 16, 64)])
+@pytest.mark.parametrize("in_zp", [0, 128, 7])
+def test_implicit_conv_vs_oracle(ctx, port, geom, in_zp):
+    """The implicit-GEMM lowering on layer shapes of the ResNet family (3x3 s1/s2, strided 1x1, 5x5, dilated, 7x7)
+    with zero and non-zero input zero points (the latter exercise the per-tap correction on border pixels)."""
+    k, s, p, d, Cc, OFM = geom
+    rng = np.random.default_rng(k * 1000 + s * 100 + Cc + in_zp)
+    src = q8_uniform(rng, (2, 19, 23, Cc), np.uint8)
+    wgt = q8_uniform(rng, (OFM, k, k, Cc), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, OFM).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.03, ws, 0.05 * k)
+    got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, dilation=(d, d),
+                   want_kernel="implicit")
+    want = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, dilation=(d, d))
+    assert np.array_equal(got, want), np.argwhere(got != want)[:5]

@@ -229,3 +229,28 @@ def test_config5_column_shard_property(ctx, port):
     shard, _ = gpu_gemmlowp(ctx, c["a"], np.ascontiguousarray(c["b"][:, n0:n1]), None, 0, 0, mult[n0:n1],
                             shift[n0:n1], 0, -128, 127, np.int8)
     assert np.array_equal(shard, full[:, n0:n1])
+
+
+def test_run_multi_destinations(ctx, port):
+    """The push all-gather epilogue: one launch writes the same column block into several [M, N_total] matrices
+    (here three buffers on one GPU; across GPUs the extra pointers are the peers' buffers)."""
+    import torch
+    rng = np.random.default_rng(21)
+    M, K, n_local, n_total, n0 = 300, 256, 512, 1536, 512
+    a, b = q8_uniform(rng, (M, K), np.int8), q8_uniform(rng, (K, n_local), np.int8, -127, 127)
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, n_local).astype(np.int32)
+    shift = rng.integers(5, 10, n_local).astype(np.int32)
+    desc, keep = capi.make_gemm_desc(M, n_local, K, capi.S8, capi.S8, capi.S8, 0, 0, multipliers=mult, shifts=shift,
+                                     min_bound=-128, max_bound=127, ldd=n_total)
+    plan = capi.GemmPlan(ctx, desc, keep)
+    plan.prepare(torch.from_numpy(b.view(np.uint8)).cuda())
+    d_a = torch.from_numpy(a.view(np.uint8)).cuda()
+    bufs = [torch.full((M, n_total), 0x11, dtype=torch.uint8, device="cuda") for _ in range(3)]
+    plan.run_multi(d_a, None, [t.data_ptr() + n0 for t in bufs])
+    ctx.sync()
+    want = port.gemmlowp_fused(a, b, None, 0, 0, mult, shift, 0, -128, 127, np.int8)
+    for t in bufs:
+        h = t.cpu().numpy()
+        assert np.array_equal(h[:, n0:n0 + n_local].view(np.int8), want)
+        assert (h[:, :n0] == 0x11).all() and (h[:, n0 + n_local:] == 0x11).all()
+    plan.close()
