@@ -195,7 +195,8 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr)
 // Optional tracing: event e of the i-th tile this CTA processes, as a %globaltimer value (ns).
 // Layout: trace[(cta * kTraceTiles + i) * kTraceEvents + e].  Events: 0 producer issued the first copy,
 // 1 MMA issuer owns an accumulator, 2 first operand stage has landed, 3 last MMA issued, 4 epilogue sees the
-// finished accumulator, 5 epilogue has stored the tile; slot 6 = clocks the MMA issuer waited for operands.
+// finished accumulator, 5 epilogue has stored the tile; slot 6 = clocks the MMA issuer waited for operands;
+// 7 (convolution kernel) the gather warps have issued the tile's last copies.
 constexpr int kTraceTiles  = 8;
 constexpr int kTraceEvents = 8;
 __device__ __forceinline__ void trace_event(long long *trace, int i, int e)
@@ -451,16 +452,73 @@ __device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col
     }
 }
 
+// Output staging of the multi-destination (push all-gather) epilogue.  A thread owns one row, so its direct
+// stores are 16-byte pieces 'ldd' apart: harmless in local memory, where L2 merges them, but over NVLink every
+// piece is a packet of its own.  Here a warp first collects 32 rows x 128 columns in shared memory (piece p of
+// row r at p ^ (r & 7): conflict-free both ways) and then stores them with eight lanes per row, 128 contiguous
+// bytes each, to every destination.
+constexpr int kOutStageBytes = 32 * 128;
+
+__device__ __forceinline__ void stage_chunk(uint8_t *stage, const uint32_t *w, int group_chunk, int lane)
+{
+    uint8_t *row = stage + lane * 128;
+    *reinterpret_cast<uint4 *>(row + (((2 * group_chunk) ^ (lane & 7)) << 4))     = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(row + (((2 * group_chunk + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+}
+
+__device__ __forceinline__ void flush_stage(const uint8_t *stage, const TileParams &tp, int m_base, int n_group,
+                                            int ncols_group, int lane)
+{
+    __syncwarp();
+    const int p = lane & 7;
+#pragma unroll 2
+    for (int it = 0; it < 8; ++it)
+    {
+        const int r = it * 4 + (lane >> 3);
+        const int m = m_base + r;
+        const int n = n_group + p * 16;
+        if (p * 16 < ncols_group && m < tp.M && n < tp.N)
+        {
+            const uint4   val = *reinterpret_cast<const uint4 *>(stage + r * 128 + ((p ^ (r & 7)) << 4));
+            const int64_t off = static_cast<int64_t>(m) * tp.ldd + n;
+            if (n + 16 <= tp.N && tp.vec_ok)
+            {
+                *reinterpret_cast<uint4 *>(tp.dst + off) = val;
+                for (int x = 0; x < tp.n_extra; ++x)
+                {
+                    *reinterpret_cast<uint4 *>(tp.extra_dst[x] + off) = val;
+                }
+            }
+            else
+            {
+                const uint32_t w[4] = {val.x, val.y, val.z, val.w};
+                for (int j = 0; j < 16 && n + j < tp.N; ++j)
+                {
+                    const uint8_t b    = static_cast<uint8_t>(w[j >> 2] >> (8 * (j & 3)));
+                    tp.dst[off + j]    = b;
+                    for (int x = 0; x < tp.n_extra; ++x)
+                    {
+                        tp.extra_dst[x][off + j] = b;
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+}
+
 // Shared epilogue of both kernels: one warp drains NCOLS consecutive columns (a multiple of 32) of its
 // 32 accumulator rows from tensor memory, applies the offset / bias terms and the output stage, and
 // stores.  The tensor-memory load of chunk i+1 is issued before chunk i is processed.
 template <int NCOLS, bool kS32Out, bool kGeneric>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s_col, const TileParams &tp,
-                                                  const EpilogueParams &ep, int m, int n_first, int32_t row_term)
+                                                  const EpilogueParams &ep, int m, int n_first, int32_t row_term,
+                                                  uint8_t *stage, int lane)
 {
     const bool row_ok = m < tp.M;
     const int64_t row_off = static_cast<int64_t>(m) * tp.ldd;
     uint8_t      *drow    = tp.dst + row_off;
+    const bool    staged  = !kS32Out && tp.n_extra > 0; // warp-uniform
     uint32_t   va[32], vb[32];
     tmem_ld_x32(t_addr, va);
 #pragma unroll 1
@@ -472,10 +530,21 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             tmem_ld_x32(t_addr + (ch + 1) * 32, vb);
         }
         process_chunk<kS32Out, kGeneric>(va, s_col + ch * 32, row_term, ep);
-        store_chunk<kS32Out>(va, drow, n_first + ch * 32, row_ok, tp);
-        for (int x = 0; x < tp.n_extra; ++x)
+        if (staged)
         {
-            store_chunk<kS32Out>(va, tp.extra_dst[x] + row_off, n_first + ch * 32, row_ok, tp);
+            stage_chunk(stage, va, ch & 3, lane);
+            if (NCOLS / 32 == 1)
+            {
+                flush_stage(stage, tp, m - lane, n_first, 32, lane);
+            }
+        }
+        else
+        {
+            store_chunk<kS32Out>(va, drow, n_first + ch * 32, row_ok, tp);
+            for (int x = 0; x < tp.n_extra; ++x)
+            {
+                store_chunk<kS32Out>(va, tp.extra_dst[x] + row_off, n_first + ch * 32, row_ok, tp);
+            }
         }
         if (ch + 1 < NCOLS / 32)
         {
@@ -485,10 +554,22 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
                 tmem_ld_x32(t_addr + (ch + 2) * 32, va);
             }
             process_chunk<kS32Out, kGeneric>(vb, s_col + (ch + 1) * 32, row_term, ep);
-            store_chunk<kS32Out>(vb, drow, n_first + (ch + 1) * 32, row_ok, tp);
-            for (int x = 0; x < tp.n_extra; ++x)
+            if (staged)
             {
-                store_chunk<kS32Out>(vb, tp.extra_dst[x] + row_off, n_first + (ch + 1) * 32, row_ok, tp);
+                stage_chunk(stage, vb, (ch + 1) & 3, lane);
+                if (((ch + 1) & 3) == 3 || ch + 2 >= NCOLS / 32)
+                {
+                    const int first = (ch + 1) & ~3; // first chunk of this 128-column group
+                    flush_stage(stage, tp, m - lane, n_first + first * 32, (ch + 2 - first) * 32, lane);
+                }
+            }
+            else
+            {
+                store_chunk<kS32Out>(vb, drow, n_first + (ch + 1) * 32, row_ok, tp);
+                for (int x = 0; x < tp.n_extra; ++x)
+                {
+                    store_chunk<kS32Out>(vb, tp.extra_dst[x] + row_off, n_first + (ch + 1) * 32, row_ok, tp);
+                }
             }
         }
     }
@@ -528,9 +609,11 @@ __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, c
 // The part of a tile one epilogue warp owns: lane quarter (warp & 3) and half of the columns.
 template <int BLOCK_N, bool kS32Out>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4 *s_col, const TileParams &tp,
-                                                   const EpilogueParams &ep, int warp, int lane, int m0, int n0)
+                                                   const EpilogueParams &ep, int warp, int lane, int m0, int n0,
+                                                   uint8_t *out_stage)
 {
     constexpr int NCOLS    = BLOCK_N / (kEpiWarps / 4);
+    uint8_t      *stage    = out_stage + (warp - kFirstEpi) * kOutStageBytes;
     const int     quad     = warp & 3;               // tensor-memory lane quarter this warp may read
     const int     half     = (warp - kFirstEpi) >> 2; // which share of the columns
     const int     m        = m0 + quad * 32 + lane;
@@ -538,11 +621,13 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
     const uint32_t t_addr  = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NCOLS;
     if (tp.generic)
     {
-        drain_accumulator<NCOLS, kS32Out, true>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term);
+        drain_accumulator<NCOLS, kS32Out, true>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
+                                                stage, lane);
     }
     else
     {
-        drain_accumulator<NCOLS, kS32Out, false>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term);
+        drain_accumulator<NCOLS, kS32Out, false>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
+                                                 stage, lane);
     }
 }
 
@@ -563,7 +648,8 @@ struct SmemPlan
     static constexpr int OFF_COL    = STAGES * STAGE;             // int4 per column
     static constexpr int OFF_BAR    = OFF_COL + BLOCK_N * 16;     // full[S], empty[S], tfull[2], tempty[2]
     static constexpr int OFF_MISC   = OFF_BAR + (2 * STAGES + 4) * 8; // tmem base, abort flag
-    static constexpr int TOTAL      = OFF_MISC + 16;
+    static constexpr int OFF_OUT    = OFF_MISC + 16;              // per epilogue warp: 32 rows x 128 bytes of output
+    static constexpr int TOTAL      = OFF_OUT + kEpiWarps * kOutStageBytes;
     static constexpr int DYN_BYTES  = TOTAL + 1024;               // slack to align the base to 1024
     static constexpr int TMEM_COLS  = 2 * BLOCK_N;
 };
@@ -809,7 +895,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
-                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0);
+                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
+                                                     smem + P::OFF_OUT);
                 tc_fence_before();
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
@@ -863,7 +950,8 @@ struct SmemPlan2
     static constexpr int OFF_COL   = STAGES * STAGE;
     static constexpr int OFF_BAR   = OFF_COL + BLOCK_N * 16;
     static constexpr int OFF_MISC  = OFF_BAR + (2 * STAGES + 4) * 8;
-    static constexpr int TOTAL     = OFF_MISC + 16;
+    static constexpr int OFF_OUT   = OFF_MISC + 16;
+    static constexpr int TOTAL     = OFF_OUT + kEpiWarps * kOutStageBytes;
     static constexpr int DYN_BYTES = TOTAL + 1024;
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
 };
@@ -1088,7 +1176,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
-                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0);
+                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
+                                                     smem + P::OFF_OUT);
                 tc_fence_before();
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
@@ -1134,12 +1223,52 @@ __global__ void __launch_bounds__(kThreads, 1)
 // pad buffer, exactly what im2col would have written (the reference's indirect mode points such taps at a
 // zero-point row as well), so the offset terms of the epilogue need no correction.
 // ---------------------------------------------------------------------------------------------------
+// Division by a run-time constant as multiply-high and shift (round-up method): with p = 31 + ceil(log2 d),
+// mul = ceil(2^p / d) fits 32 bits and n / d == umulhi(n, mul) >> (p - 32) for every 0 <= n < 2^31.
+struct FastDiv
+{
+    uint32_t mul, shr, d;
+};
+
+inline FastDiv make_fastdiv(int d)
+{
+    FastDiv f;
+    f.d = static_cast<uint32_t>(d);
+    if (d <= 1)
+    {
+        f.mul = 0;
+        f.shr = 0;
+        return f;
+    }
+    int l = 0;
+    while ((1ll << l) < d) ++l;
+    const int p = 31 + l;
+    f.mul       = static_cast<uint32_t>(((1ull << p) + static_cast<uint64_t>(d) - 1) / static_cast<uint64_t>(d));
+    f.shr       = static_cast<uint32_t>(p - 32);
+    return f;
+}
+
+__device__ __forceinline__ int fast_div(int n, const FastDiv &f)
+{
+    return f.d <= 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), f.mul) >> f.shr);
+}
+
 struct ConvGeom
 {
     const uint8_t *src; // [B][H][W][C]
     const uint8_t *pad; // 16 bytes of the input zero point per gather thread (kConvPadBytes in all)
     int            C, W, H, kw, kh, sx, sy, pad_l, pad_t, dil_x, dil_y, Wo, Ho;
+    FastDiv        div_wo, div_ho;
 };
+
+// One entry per 16-byte piece of the patch axis: where the piece lies relative to the top-left tap of an
+// output pixel.  Built once per CTA in shared memory so that the gather loop has no division in it.
+struct TapEntry
+{
+    int32_t  offset; // bytes from the (ky = 0, kx = 0, c = 0) element, in the input tensor
+    uint32_t dydx;   // (ky * dilation_y) << 16 | (kx * dilation_x)
+};
+constexpr int kConvMaxPieces = 1024; // K <= 16384 bytes
 
 constexpr int kGatherWarps  = 8;
 static_assert(kConvPadBytes >= 16 * 32 * kGatherWarps, "one pad piece per gather thread");
@@ -1165,6 +1294,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     auto           tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
     uint32_t      *s_tmem     = reinterpret_cast<uint32_t *>(smem + P::OFF_MISC);
     volatile int  *s_abort    = reinterpret_cast<volatile int *>(smem + P::OFF_MISC + 4);
+    TapEntry      *s_taps     = reinterpret_cast<TapEntry *>(smem + P::TOTAL);
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -1177,6 +1307,16 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                                  ? (num_tiles - 1 - static_cast<int>(blockIdx.x)) / static_cast<int>(gridDim.x) + 1
                                  : 0;
 
+    for (int p = threadIdx.x; p < (tp.K >> 4); p += kConvThreads)
+    {
+        const int kbyte = p << 4;
+        const int tap = kbyte / cg.C, c = kbyte - tap * cg.C;
+        const int ky = tap / cg.kw, kx = tap - ky * cg.kw;
+        TapEntry  e;
+        e.offset  = (ky * cg.dil_y * cg.W + kx * cg.dil_x) * cg.C + c;
+        e.dydx    = (static_cast<uint32_t>(ky * cg.dil_y) << 16) | static_cast<uint32_t>(kx * cg.dil_x);
+        s_taps[p] = e;
+    }
     if (threadIdx.x == 0)
     {
         for (int s = 0; s < STAGES; ++s)
@@ -1250,6 +1390,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
                 if (!ok) break;
                 tc_fence_after();
+                trace_event(tp.trace, ti, 1);
                 const uint32_t d_tmem = tmem_base + as * BLOCK_N;
                 for (int kb = 0; kb < num_kb; ++kb)
                 {
@@ -1258,6 +1399,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                         ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
                         if (!ok) break;
                     }
+                    if (kb == 0) trace_event(tp.trace, ti, 2);
                     int      sn  = s + 1;
                     uint32_t phn = ph;
                     if (sn == STAGES)
@@ -1288,6 +1430,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 }
                 if (ok)
                 {
+                    trace_event(tp.trace, ti, 3);
                     umma_commit(tfull_bar(as));
                 }
                 if (++as == 2)
@@ -1321,7 +1464,10 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             if (ok)
             {
                 tc_fence_after();
-                epilogue_warp_tile<BLOCK_N, false>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0);
+                if (et == 0) trace_event(tp.trace, ti, 4);
+                epilogue_warp_tile<BLOCK_N, false>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
+                                                   smem + P::OFF_OUT);
+                if (et == 0) trace_event(tp.trace, ti, 5);
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0)
@@ -1346,6 +1492,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         const int     piece          = gt & 7;
         const int     row0           = gt >> 3;
         const uint8_t *pad_src       = cg.pad + 16 * gt; // every thread its own copy: no single hot line
+        const int      last_piece    = (tp.K >> 4) - 1;
         int           st = 0;
         uint32_t      ph = 0;
         bool          ok = true;
@@ -1353,16 +1500,19 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         {
             const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
             const int m0   = (tile % num_m_blocks) * BLOCK_M;
-            int       yi0[kRowsPerThread], xi0[kRowsPerThread];
-            const uint8_t *img[kRowsPerThread];
+            int            yi0[kRowsPerThread], xi0[kRowsPerThread];
+            const uint8_t *base[kRowsPerThread];
 #pragma unroll
             for (int i = 0; i < kRowsPerThread; ++i)
             {
                 const int m  = min(m0 + row0 + 32 * i, tp.M - 1); // rows beyond M repeat the last pixel (never stored)
-                const int xo = m % cg.Wo, yo = (m / cg.Wo) % cg.Ho, bi = m / (cg.Wo * cg.Ho);
+                const int q  = fast_div(m, cg.div_wo), xo = m - q * cg.Wo;
+                const int bi = fast_div(q, cg.div_ho), yo = q - bi * cg.Ho;
                 yi0[i]       = yo * cg.sy - cg.pad_t;
                 xi0[i]       = xo * cg.sx - cg.pad_l;
-                img[i]       = cg.src + static_cast<long long>(bi) * cg.H * cg.W * cg.C;
+                // address of tap (0, 0), channel 0 of this pixel; outside the tensor for border pixels, where it is
+                // only ever used after the bounds test below
+                base[i] = cg.src + (static_cast<long long>(bi) * cg.H * cg.W + static_cast<long long>(yi0[i]) * cg.W + xi0[i]) * cg.C;
             }
             for (int kb = 0; kb < num_kb; ++kb)
             {
@@ -1372,19 +1522,19 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
+                if (kb == 0 && gt == 0) trace_event(tp.trace, ti, 0);
 #pragma unroll
                 for (int sub = 0; sub < KSUB; ++sub)
                 {
-                    // beyond K the weights are zero (TMA fill), so any finite A bytes do: keep to the last tap
-                    const int kbyte = min((kb * KSUB + sub) * BLOCK_K + piece * 16, tp.K - 16);
-                    const int tap = kbyte / cg.C, c = kbyte - tap * cg.C;
-                    const int ky = tap / cg.kw, kx = tap - ky * cg.kw;
+                    // beyond K the weights are zero (TMA fill), so any finite A bytes do: repeat the last piece
+                    const TapEntry e  = s_taps[min((kb * KSUB + sub) * 8 + piece, last_piece)];
+                    const int      dy = static_cast<int>(e.dydx >> 16), dx = static_cast<int>(e.dydx & 0xffffu);
 #pragma unroll
                     for (int i = 0; i < kRowsPerThread; ++i)
                     {
-                        const int      yi  = yi0[i] + ky * cg.dil_y, xi = xi0[i] + kx * cg.dil_x;
-                        const bool     in  = yi >= 0 && yi < cg.H && xi >= 0 && xi < cg.W;
-                        const uint8_t *src = in ? img[i] + (static_cast<long long>(yi) * cg.W + xi) * cg.C + c : pad_src;
+                        const bool     in  = static_cast<unsigned>(yi0[i] + dy) < static_cast<unsigned>(cg.H) &&
+                                        static_cast<unsigned>(xi0[i] + dx) < static_cast<unsigned>(cg.W);
+                        const uint8_t *src = in ? base[i] + e.offset : pad_src;
                         const int      r   = row0 + 32 * i;
                         const uint32_t dst = sA + st * P::A_STAGE_K + sub * A_STAGE + r * 128 + ((piece ^ (r & 7)) << 4);
                         asm volatile("cp.async.ca.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -1392,6 +1542,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 }
                 // this thread's arrival on the stage's barrier happens when its copies above have landed
                 asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(full_bar(st)) : "memory");
+                if (kb == num_kb - 1 && gt == 0) trace_event(tp.trace, ti, 7);
                 if (++st == STAGES)
                 {
                     st = 0;
@@ -1565,7 +1716,9 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
                                 const ConvOperands &cv)
 {
     using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
-    static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
+    constexpr int kDynBytes = P::DYN_BYTES + kConvMaxPieces * static_cast<int>(sizeof(TapEntry));
+    static_assert(kDynBytes <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
+    static_assert(P::TOTAL % 8 == 0, "the tap table follows the plan");
     CUtensorMap map_b;
     if (!encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, BLOCK_N))
     {
@@ -1575,7 +1728,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63])
     {
-        CUGL_CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::DYN_BYTES));
+        CUGL_CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDynBytes));
         attr_set[ctx->device & 63] = true;
     }
     TileParams tp;
@@ -1590,7 +1743,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
     tp.status  = ctx->d_status;
     tp.generic = op.generic_stage ? 1 : 0;
-    tp.trace   = nullptr;
+    tp.trace   = ctx->d_trace;
     ConvGeom cg;
     cg.src   = static_cast<const uint8_t *>(cv.src);
     cg.pad   = static_cast<const uint8_t *>(cv.pad);
@@ -1607,9 +1760,11 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     cg.dil_y = cv.dil_y;
     cg.Wo    = cv.Wo;
     cg.Ho    = cv.Ho;
+    cg.div_wo = make_fastdiv(cv.Wo);
+    cg.div_ho = make_fastdiv(cv.Ho);
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kernel<<<grid, kConvThreads, P::DYN_BYTES, ctx->stream>>>(map_b, tp, ep, cg);
+    kernel<<<grid, kConvThreads, kDynBytes, ctx->stream>>>(map_b, tp, ep, cg);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_conv_tcgen05_kernel");
 }
 } // namespace
@@ -1657,7 +1812,10 @@ bool gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands 
 {
     const uint64_t bits = reinterpret_cast<uintptr_t>(cv.src) | reinterpret_cast<uintptr_t>(cv.pad) |
                           reinterpret_cast<uintptr_t>(op.bt) | static_cast<uint64_t>(op.ldbt);
-    return op.M > 0 && op.N > 0 && op.K >= 16 && (bits & 15) == 0 && (cv.C % 16) == 0 && cv.pad != nullptr &&
+    // the tap table holds K / 16 entries with 32-bit offsets inside one image and 16-bit tap displacements
+    const long long image_bytes = static_cast<long long>(cv.H) * cv.W * cv.C;
+    return op.M > 0 && op.N > 0 && op.K >= 16 && op.K <= 16 * kConvMaxPieces && (bits & 15) == 0 && (cv.C % 16) == 0 &&
+           cv.pad != nullptr && image_bytes < (1ll << 31) && cv.kh * cv.dil_y < 65536 && cv.kw * cv.dil_x < 65536 &&
            get_encode_fn() != nullptr;
 }
 
