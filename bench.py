@@ -43,7 +43,9 @@ def parse_args():
     p.add_argument("--steps", type=int, default=2000)
     p.add_argument("--warmup", type=int, default=200)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c5"])
+    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    p.add_argument("--batch", type=int, default=256, help="global batch of c4 (split over the ranks)")
+    p.add_argument("--layers", action="store_true", help="c4: print the per-layer time table to stderr")
     p.add_argument("--size", type=int, default=0, help="override M=N=K of c2 (profiling on a small case)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
@@ -500,6 +502,90 @@ def run_conv(args):
         dist.destroy_process_group()
 
 
+def run_resnet(args):
+    """Config 4: QASYMM8 ResNet-50 v1 (examples/graph_resnet50.cpp topology, batch norm folded, ReLU fused), global
+    batch 256 split over the ranks, weights replicated, no collective.  Reports images/s; the tensor-core roofline
+    uses 6.965 GOP per image."""
+    import torch
+    import torch.distributed as dist
+    import computelibrary_b200 as cl
+    from computelibrary_b200 import resnet50 as rn
+    from computelibrary_b200 import sharding
+    rank, world, local = dist_env()
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    ctx = cl.Context(local, torch.cuda.current_stream().cuda_stream)
+    b0, b1 = sharding.batch_shard(args.batch, world, rank)
+    B = b1 - b0
+    net = rn.ResNet50(ctx, B, seed=1)
+    rng = np.random.default_rng(100 + rank)
+    h_in = torch.from_numpy(rng.integers(0, 256, (B, 224, 224, 3), dtype=np.uint8)).pin_memory()
+    d_in = h_in.cuda()
+    h_out = torch.empty((B, 1, 1, 1000), dtype=torch.uint8).pin_memory()
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local) if rank == 0 else None
+    for _ in range(2):  # first-use costs (lazy workspaces) stay outside the sampled window
+        net.run(d_in)
+    barrier()
+    t_begin = time.time()
+    step_ms = _timed_steps(lambda: net.run(d_in), args.steps, args.warmup, flush, barrier)
+    clocks = sampler.stop(t_begin, time.time()) if sampler else None
+    ctx.sync()
+
+    def e2e_step():
+        d_in.copy_(h_in, non_blocking=True)
+        out = net.run(d_in)
+        h_out.copy_(out, non_blocking=True)
+
+    e2e_ms = [] if args.no_e2e else _timed_steps(e2e_step, max(2, args.steps // 4), 2, flush, barrier)
+    if args.layers and rank == 0:
+        rows = net.run_timed(d_in)
+        tot = sum(r[3] for r in rows)
+        for name, op, kern, ms in rows:
+            print(f"{name:34s} {op:15s} {kern:10s} {ms * 1e3:9.1f} us {100 * ms / tot:5.1f} %", file=sys.stderr)
+        print(f"sum {tot:.3f} ms", file=sys.stderr)
+    t = torch.tensor([float(sum(step_ms)) / args.steps, float(sum(e2e_ms)) / max(1, len(e2e_ms))], device="cuda",
+                     dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank == 0:
+        ms, e2e = float(t[0]), float(t[1])
+        ops_img = rn.graph_ops(net.nodes)
+        peaks = load_peaks()
+        # one rank's tensor-core rate over its own step time against 2 x the measured dense bf16 peak
+        ach = ops_img * B / (statistics.mean(step_ms) * 1e-3) / 1e12
+        peak = 2.0 * peaks["bf16_tflops"]
+        line = {
+            "metric": "resnet50_qasymm8_images_per_s", "value": args.batch / (ms * 1e-3), "unit": "img/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "strong", "vs_baseline": None, "dtype": "u8*s8->s32->u8", "data": "synthetic",
+            "config": {"workload": f"config4: QASYMM8 ResNet-50 v1, 224x224, global batch {args.batch}, per-channel s8 "
+                       "weights, batch norm folded, ReLU fused", "per_gpu_batch": B,
+                       "l2": "flushed between timed steps (256 MB write)",
+                       "sharding": "batch split over ranks, weights replicated, no collective"},
+            "int8_tops": ops_img * args.batch / (ms * 1e-3) / 1e12,
+            "gpu_launches": args.steps * net.launches,
+            "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TOP/s", "frac": ach / peak,
+                         "traffic": None, "peak_source": "2 x " + peaks["source"] + " dense bf16 cuBLAS rate",
+                         "kernel": "whole network (54 convolutions + pooling / addition / softmax kernels)"},
+            "clocks": clocks}
+        if e2e_ms:
+            line["e2e"] = {"value": args.batch / (e2e * 1e-3), "unit": "img/s", "h2d_bytes_per_step": int(h_in.numel()),
+                           "d2h_bytes_per_step": int(h_out.numel())}
+        print(json.dumps(line), flush=True)
+    net.close()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def run_linear_sharded(args):
     """Config 5 on N > 1 GPUs: B is split by columns (multiples of the 256-column tile), every rank computes
     dst[:, n0:n1] with the fused kernel and the int8 column blocks are all-gathered with NCCL."""
@@ -611,6 +697,8 @@ def main():
         run_reference(args)
     elif args.workload == "c3":
         run_conv(args)
+    elif args.workload == "c4":
+        run_resnet(args)
     elif args.workload == "c5" and world > 1:
         run_linear_sharded(args)
     else:

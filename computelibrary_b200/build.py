@@ -17,7 +17,8 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libcugl.so")
-SOURCES = ["context.cu", "bandwidth_kernels.cu", "gemmlowp_simt.cu", "gemmlowp_tcgen05.cu", "plans.cu", "noalloc.cu"]
+SOURCES = ["context.cu", "bandwidth_kernels.cu", "gemmlowp_simt.cu", "gemmlowp_tcgen05.cu", "plans.cu", "noalloc.cu",
+           "layer_kernels.cu"]
 HEADERS = ["common.cuh", "kernels.cuh"]
 
 NVCC_FLAGS = [

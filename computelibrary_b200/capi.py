@@ -59,6 +59,22 @@ class ConvDesc(C.Structure):
     ]
 
 
+class PoolDesc(C.Structure):
+    """cugl_pool_desc"""
+    _fields_ = [
+        ("B", _i32), ("H", _i32), ("W", _i32), ("C", _i32),
+        ("pool_type", _i32), ("pool_w", _i32), ("pool_h", _i32),
+        ("stride_x", _i32), ("stride_y", _i32),
+        ("pad_left", _i32), ("pad_right", _i32), ("pad_top", _i32), ("pad_bottom", _i32),
+        ("exclude_padding", _i32), ("is_global", _i32),
+        ("src_scale", C.c_float), ("src_zero_point", _i32),
+        ("dst_scale", C.c_float), ("dst_zero_point", _i32),
+    ]
+
+
+POOL_MAX, POOL_AVG = 0, 1
+ACT_NONE, ACT_RELU, ACT_BOUNDED_RELU, ACT_LU_BOUNDED_RELU = -1, 0, 1, 2
+
 _SIGNATURES = {
     "cugl_context_create": (C.c_int, [C.c_int, _vp, C.POINTER(_vp)]),
     "cugl_context_destroy": (None, [_vp]),
@@ -113,6 +129,14 @@ _SIGNATURES = {
     "cugl_conv2d_plan_launches": (C.c_int, [_vp]),
     "cugl_conv2d_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_conv2d_plan_allow_implicit": (C.c_int, [_vp, C.c_int]),
+    "cugl_pool2d_out_dims": (None, [C.POINTER(PoolDesc), _pi32, _pi32]),
+    "cugl_pool2d_validate": (C.c_int, [C.POINTER(PoolDesc)]),
+    "cugl_pool2d_nhwc": (C.c_int, [_vp, C.POINTER(PoolDesc), _vp, _vp]),
+    "cugl_add_qasymm8": (C.c_int, [_vp, _vp, _vp, _vp, _i64, C.c_float, _i32, C.c_float, _i32, C.c_float, _i32,
+                                   _i32, C.c_float, C.c_float]),
+    "cugl_activation_qasymm8": (C.c_int, [_vp, _vp, _vp, _i64, _i32, C.c_float, C.c_float, C.c_float, _i32,
+                                          C.c_float, _i32]),
+    "cugl_softmax_qasymm8": (C.c_int, [_vp, _vp, _vp, _i32, _i32, C.c_float, C.c_float, _i32]),
 }
 
 _lib = None
@@ -276,6 +300,22 @@ class Context:
         self.check(self.lib.cugl_im2col_nhwc(self.handle, _dptr(src), _dptr(dst), C_, W, H, B, kw, kh, sx, sy, pl, pt,
                                              dx, dy, Wo, Ho, pad_value, row_stride))
 
+    # QASYMM8 layers: q = (scale, zero point) -------------------------------------------------------------
+    def pool2d_nhwc(self, desc: "PoolDesc", src, dst):
+        self.check(self.lib.cugl_pool2d_nhwc(self.handle, C.byref(desc), _dptr(src), _dptr(dst)))
+
+    def add_qasymm8(self, a, b, dst, n, a_q, b_q, o_q, act=ACT_NONE, act_a=0.0, act_b=0.0):
+        self.check(self.lib.cugl_add_qasymm8(self.handle, _dptr(a), _dptr(b), _dptr(dst), n, a_q[0], a_q[1], b_q[0],
+                                             b_q[1], o_q[0], o_q[1], act, act_a, act_b))
+
+    def activation_qasymm8(self, src, dst, n, act, act_a, act_b, in_q, out_q):
+        self.check(self.lib.cugl_activation_qasymm8(self.handle, _dptr(src), _dptr(dst), n, act, act_a, act_b,
+                                                    in_q[0], in_q[1], out_q[0], out_q[1]))
+
+    def softmax_qasymm8(self, src, dst, rows, cols, beta, in_q):
+        self.check(self.lib.cugl_softmax_qasymm8(self.handle, _dptr(src), _dptr(dst), rows, cols, beta, in_q[0],
+                                                 in_q[1]))
+
     def weights_reshape_nhwc(self, w, dst, K, OFM):
         self.check(self.lib.cugl_weights_reshape_nhwc(self.handle, _dptr(w), _dptr(dst), K, OFM))
 
@@ -329,6 +369,34 @@ def gemm_validate(desc: GemmDesc):
     why = C.c_char_p()
     st = load_library().cugl_gemmlowp_validate(C.byref(desc), C.byref(why))
     return st, (why.value or b"").decode()
+
+
+def make_pool_desc(B, H, W, C_, pool_type, size=(1, 1), stride=(1, 1), pad=(0, 0, 0, 0), in_q=(1.0, 0),
+                   out_q=(1.0, 0), exclude_padding=False, global_pool=False) -> PoolDesc:
+    """pad = (left, right, top, bottom); size = (width, height); q = (scale, zero point)."""
+    d = PoolDesc()
+    d.B, d.H, d.W, d.C = B, H, W, C_
+    d.pool_type = pool_type
+    d.pool_w, d.pool_h = size
+    d.stride_x, d.stride_y = stride
+    d.pad_left, d.pad_right, d.pad_top, d.pad_bottom = pad
+    d.exclude_padding, d.is_global = int(exclude_padding), int(global_pool)
+    d.src_scale, d.src_zero_point = in_q
+    d.dst_scale, d.dst_zero_point = out_q
+    return d
+
+
+def pool_out_dims(desc: PoolDesc):
+    wo, ho = _i32(0), _i32(0)
+    load_library().cugl_pool2d_out_dims(C.byref(desc), C.byref(wo), C.byref(ho))
+    return int(wo.value), int(ho.value)
+
+
+def pool_validate(desc: PoolDesc):
+    lib = load_library()
+    st = lib.cugl_pool2d_validate(C.byref(desc))
+    if st != 0:
+        raise CuglError(st, (lib.cugl_last_error_string(None) or b"").decode())
 
 
 def conv_validate(desc: ConvDesc):

@@ -325,6 +325,66 @@ __global__ void __launch_bounds__(kThreads) im2col_nhwc_kernel(const uint8_t *__
     }
 }
 
+// ---- 2x2 space-to-depth lowering of stride-2 convolutions with at most four input channels -------------
+// A 7x7 / stride 2 convolution over 3 channels has a 147-byte patch row, useless to a 16-byte gather.  Folding
+// every 2x2 pixel block into 16 channels ((dy, dx, c) with c padded to 4) turns it into a 4x4 / stride 1
+// convolution over 16 channels whose folded weights are zero wherever the original kernel has no tap:
+// the sums are the same integers.  fold_input_kernel: dst[b][Y][X][(dy*2+dx)*4 + c] = src[b][2Y+dy][2X+dx][c];
+// pixels beyond an odd edge and the padding channels hold the zero point (their weights are zero).
+__global__ void __launch_bounds__(kThreads) fold_input_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
+                                                              int B, int H, int W, int C, int H2, int W2, uint32_t zp)
+{
+    const int64_t total = static_cast<int64_t>(B) * H2 * W2;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * kThreads)
+    {
+        const int     X = static_cast<int>(i % W2);
+        const int     Y = static_cast<int>((i / W2) % H2);
+        const int64_t b = i / (static_cast<int64_t>(W2) * H2);
+        uint32_t      w[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+        {
+            const int y = 2 * Y + (q >> 1), x = 2 * X + (q & 1);
+            uint32_t  v = zp * 0x01010101u;
+            if (y < H && x < W)
+            {
+                const uint8_t *p = src + ((b * H + y) * W + x) * C;
+                v                = 0;
+                for (int c = 0; c < 4; ++c)
+                {
+                    v |= (c < C ? static_cast<uint32_t>(p[c]) : zp) << (8 * c);
+                }
+            }
+            w[q] = v;
+        }
+        reinterpret_cast<uint4 *>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
+// fold_weights_kernel: bt[n][((ty*kw2 + tx)*4 + dy*2 + dx)*4 + c] = w[n][2ty+dy-oy][2tx+dx-ox][c], zero where the
+// original kernel has no such tap or channel.  (oy, ox) = parity of the top / left padding.
+__global__ void __launch_bounds__(kThreads) fold_weights_kernel(const uint8_t *__restrict__ w, uint8_t *__restrict__ bt,
+                                                                int64_t ldbt, int OFM, int kh, int kw, int C, int kh2,
+                                                                int kw2, int oy, int ox)
+{
+    const int K2    = kh2 * kw2 * 16;
+    const int total = OFM * K2;
+    for (int i = blockIdx.x * kThreads + threadIdx.x; i < total; i += gridDim.x * kThreads)
+    {
+        const int n = i / K2, k = i % K2;
+        const int c = k & 3, dx = (k >> 2) & 1, dy = (k >> 3) & 1, t = k >> 4;
+        const int tx = t % kw2, ty = t / kw2;
+        const int ky = 2 * ty + dy - oy, kx = 2 * tx + dx - ox;
+        uint8_t   v  = 0;
+        if (ky >= 0 && ky < kh && kx >= 0 && kx < kw && c < C)
+        {
+            v = w[((static_cast<int64_t>(n) * kh + ky) * kw + kx) * C + c];
+        }
+        bt[n * ldbt + k] = v;
+    }
+}
+
 int grid_for(int64_t work_items, int sm_count, int per_thread = 1)
 {
     const int64_t blocks = (work_items + static_cast<int64_t>(kThreads) * per_thread - 1) /
@@ -451,5 +511,24 @@ cugl_status launch_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst
             pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride);
     }
     return check_cuda(ctx, cudaGetLastError(), "im2col_nhwc_kernel");
+}
+cugl_status launch_fold_input(cugl_context *ctx, const void *d_src, void *d_dst, int B, int H, int W, int C, int H2,
+                              int W2, int zero_point)
+{
+    const int blocks = grid_for(static_cast<int64_t>(B) * H2 * W2, ctx->sm_count);
+    fold_input_kernel<<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_src),
+                                                            static_cast<uint8_t *>(d_dst), B, H, W, C, H2, W2,
+                                                            static_cast<uint32_t>(zero_point) & 0xffu);
+    return check_cuda(ctx, cudaGetLastError(), "fold_input_kernel");
+}
+
+cugl_status launch_fold_weights(cugl_context *ctx, const void *d_w, void *d_bt, int64_t ldbt, int OFM, int kh, int kw,
+                                int C, int kh2, int kw2, int oy, int ox)
+{
+    const int blocks = grid_for(static_cast<int64_t>(OFM) * kh2 * kw2 * 16, ctx->sm_count);
+    fold_weights_kernel<<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_w),
+                                                              static_cast<uint8_t *>(d_bt), ldbt, OFM, kh, kw, C, kh2,
+                                                              kw2, oy, ox);
+    return check_cuda(ctx, cudaGetLastError(), "fold_weights_kernel");
 }
 } // namespace cugl

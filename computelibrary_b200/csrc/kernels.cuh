@@ -20,6 +20,11 @@ cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t 
                                 void *d_out, int64_t ld_out_bytes, int M, int N, const int32_t *d_mults,
                                 const int32_t *d_shifts, int32_t mult, int32_t shift, int32_t offset, int32_t lo,
                                 int32_t hi);
+// 2x2 space-to-depth lowering of stride-2 convolutions with <= 4 channels (see bandwidth_kernels.cu)
+cugl_status launch_fold_input(cugl_context *ctx, const void *d_src, void *d_dst, int B, int H, int W, int C, int H2,
+                              int W2, int zero_point);
+cugl_status launch_fold_weights(cugl_context *ctx, const void *d_w, void *d_bt, int64_t ldbt, int OFM, int kh, int kw,
+                                int C, int kh2, int kw2, int oy, int ox);
 cugl_status launch_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst, int C, int W, int H, int B, int kw,
                                int kh, int sx, int sy, int pad_l, int pad_t, int dil_x, int dil_y, int Wo, int Ho,
                                int pad_value, int64_t row_stride);

@@ -642,6 +642,12 @@ struct cugl_conv_plan
     bool                 allow_implicit = true;
     uint8_t             *d_cols      = nullptr; // [M][Kp] im2col matrix (allocated on first explicit run)
     uint8_t             *d_pad       = nullptr; // kConvPadBytes of the input zero point: source of out-of-image taps
+    // Geometry the lowerings work on: the descriptor's own, or -- stride 2 with at most four channels -- the
+    // 2x2 space-to-depth form (16 channels, stride 1, zero weights where the original kernel has no tap).
+    bool     fold = false;
+    int      eC = 0, eW = 0, eH = 0, ekw = 0, ekh = 0, esx = 1, esy = 1, epl = 0, ept = 0;
+    int      fold_oy = 0, fold_ox = 0;
+    uint8_t *d_fold = nullptr; // [B][eH][eW][16]
     bool                 prepared    = false;
     void                *d_src_stage = nullptr, *d_dst_stage = nullptr;
     int32_t             *d_bias_stage = nullptr;
@@ -737,8 +743,20 @@ extern "C"
         p->desc.h_gemmlowp_multipliers = nullptr;
         p->desc.h_gemmlowp_shifts      = nullptr;
         conv_out_dims(desc, &p->Wo, &p->Ho);
+        p->eC = desc->C, p->eW = desc->W, p->eH = desc->H, p->ekw = desc->kw, p->ekh = desc->kh;
+        p->esx = desc->stride_x, p->esy = desc->stride_y, p->epl = desc->pad_left, p->ept = desc->pad_top;
+        p->fold = desc->C <= 4 && desc->stride_x == 2 && desc->stride_y == 2 && desc->dil_x == 1 && desc->dil_y == 1 &&
+                  desc->w_zero_point == 0 && desc->kw * desc->kh > 1;
+        if (p->fold)
+        {
+            p->fold_ox = desc->pad_left & 1, p->fold_oy = desc->pad_top & 1;
+            p->eC = 16, p->eW = (desc->W + 1) / 2, p->eH = (desc->H + 1) / 2;
+            p->ekw = (p->fold_ox + desc->kw + 1) / 2, p->ekh = (p->fold_oy + desc->kh + 1) / 2;
+            p->esx = p->esy = 1;
+            p->epl = (desc->pad_left + p->fold_ox) / 2, p->ept = (desc->pad_top + p->fold_oy) / 2;
+        }
         p->M  = static_cast<int64_t>(desc->B) * p->Ho * p->Wo;
-        p->K  = static_cast<int64_t>(desc->kh) * desc->kw * desc->C;
+        p->K  = static_cast<int64_t>(p->ekh) * p->ekw * p->eC;
         p->Kp = round_up(p->K, 16);
         // CpuGemmConv2d.cpp:189-191: a 1x1, stride-1, unpadded NHWC convolution is a plain GEMM on the
         // input tensor.  Kept only when the rows are already 16-byte multiples (TMA stride rule).
@@ -769,7 +787,11 @@ extern "C"
         }
         // Implicit GEMM whenever the gather kernel can address the tensors: channel count a multiple of 16 and
         // symmetric weights (no row-sum term).  Otherwise explicit im2col.
-        p->implicit = !p->skip_im2col && (desc->C % 16) == 0 && desc->w_zero_point == 0;
+        p->implicit = !p->skip_im2col && (p->eC % 16) == 0 && desc->w_zero_point == 0;
+        if (s == CUGL_SUCCESS && p->fold)
+        {
+            s = cugl_malloc(ctx, static_cast<size_t>(desc->B) * p->eH * p->eW * 16, reinterpret_cast<void **>(&p->d_fold));
+        }
         if (s == CUGL_SUCCESS && p->implicit)
         {
             s = cugl_malloc(ctx, kConvPadBytes, reinterpret_cast<void **>(&p->d_pad));
@@ -797,6 +819,7 @@ extern "C"
         plan->core.release();
         cugl_free(plan->ctx, plan->d_cols);
         cugl_free(plan->ctx, plan->d_pad);
+        cugl_free(plan->ctx, plan->d_fold);
         cugl_free(plan->ctx, plan->d_src_stage);
         cugl_free(plan->ctx, plan->d_dst_stage);
         cugl_free(plan->ctx, plan->d_bias_stage);
@@ -814,8 +837,17 @@ extern "C"
         // NHWC weights [OFM][kh][kw][C] are already the K-major operand the tensor cores want: the
         // reshape of CpuWeightsReshapeKernel followed by the pretranspose of the assembly path cancel out.
         // Copy the rows into the zero-padded buffer and reduce each row (= column of the GEMM's B).
-        CUGL_CUDA_TRY(ctx, cudaMemcpy2DAsync(c.d_bt, c.ldbt, d_weights, plan->K, plan->K, c.N,
-                                             cudaMemcpyDeviceToDevice, ctx->stream));
+        if (plan->fold)
+        {
+            const cugl_conv_desc &d = plan->desc;
+            CUGL_TRY(launch_fold_weights(ctx, d_weights, c.d_bt, c.ldbt, c.N, d.kh, d.kw, d.C, plan->ekh, plan->ekw,
+                                         plan->fold_oy, plan->fold_ox));
+        }
+        else
+        {
+            CUGL_CUDA_TRY(ctx, cudaMemcpy2DAsync(c.d_bt, c.ldbt, d_weights, plan->K, plan->K, c.N,
+                                                 cudaMemcpyDeviceToDevice, ctx->stream));
+        }
         CUGL_TRY(launch_reduce_rows(ctx, c.d_bt, c.b_signed, c.N, c.K, c.ldbt, 1, c.d_colsum));
         plan->prepared = true;
         return CUGL_SUCCESS;
@@ -835,6 +867,12 @@ extern "C"
         if (d.has_bias && d_bias == nullptr)
         {
             return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run: plan was configured with a bias");
+        }
+        if (plan->fold)
+        {
+            CUGL_TRY(launch_fold_input(plan->ctx, d_src, plan->d_fold, d.B, d.H, d.W, d.C, plan->eH, plan->eW,
+                                       d.src_zero_point));
+            d_src = plan->d_fold;
         }
         if (plan->implicit && plan->allow_implicit && !plan->core.force_simt)
         {
@@ -856,16 +894,16 @@ extern "C"
             ConvOperands cv{};
             cv.src    = d_src;
             cv.pad    = plan->d_pad;
-            cv.C      = d.C;
-            cv.W      = d.W;
-            cv.H      = d.H;
+            cv.C      = plan->eC;
+            cv.W      = plan->eW;
+            cv.H      = plan->eH;
             cv.B      = d.B;
-            cv.kw     = d.kw;
-            cv.kh     = d.kh;
-            cv.sx     = d.stride_x;
-            cv.sy     = d.stride_y;
-            cv.pad_l  = d.pad_left;
-            cv.pad_t  = d.pad_top;
+            cv.kw     = plan->ekw;
+            cv.kh     = plan->ekh;
+            cv.sx     = plan->esx;
+            cv.sy     = plan->esy;
+            cv.pad_l  = plan->epl;
+            cv.pad_t  = plan->ept;
             cv.dil_x  = d.dil_x;
             cv.dil_y  = d.dil_y;
             cv.Wo     = plan->Wo;
@@ -876,7 +914,7 @@ extern "C"
             }
         }
         const void *a   = d_src;
-        int64_t     lda = d.C;
+        int64_t     lda = plan->eC;
         if (!plan->skip_im2col)
         {
             if (plan->d_cols == nullptr)
@@ -884,9 +922,9 @@ extern "C"
                 CUGL_TRY(cugl_malloc(plan->ctx, static_cast<size_t>(plan->M) * plan->Kp,
                                      reinterpret_cast<void **>(&plan->d_cols)));
             }
-            CUGL_TRY(launch_im2col_nhwc(plan->ctx, d_src, plan->d_cols, d.C, d.W, d.H, d.B, d.kw, d.kh, d.stride_x,
-                                        d.stride_y, d.pad_left, d.pad_top, d.dil_x, d.dil_y, plan->Wo, plan->Ho,
-                                        d.src_zero_point, plan->Kp));
+            CUGL_TRY(launch_im2col_nhwc(plan->ctx, d_src, plan->d_cols, plan->eC, plan->eW, plan->eH, d.B, plan->ekw,
+                                        plan->ekh, plan->esx, plan->esy, plan->epl, plan->ept, d.dil_x, d.dil_y,
+                                        plan->Wo, plan->Ho, d.src_zero_point, plan->Kp));
             a   = plan->d_cols;
             lda = plan->Kp;
         }
@@ -952,10 +990,11 @@ extern "C"
         {
             return 0;
         }
+        const int fold = plan->fold ? 1 : 0;
         if (plan->implicit && plan->allow_implicit)
         {
-            return 1;
+            return fold + 1;
         }
-        return (plan->skip_im2col ? 0 : 1) + 1 + (plan->core.b_off != 0 ? 1 : 0);
+        return fold + (plan->skip_im2col ? 0 : 1) + 1 + (plan->core.b_off != 0 ? 1 : 0);
     }
 }

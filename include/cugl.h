@@ -310,6 +310,69 @@ CUGL_API const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan);
 /* on = 0 forces the explicit im2col lowering (testing aid: both lowerings must agree bit for bit). */
 CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on);
 
+/* ------------------------------------------------------------------------------------------------
+ * QASYMM8 layers between the convolutions of a quantized network (uint8, NHWC).  Each one computes what
+ * Compute Library's scalar oracle computes: dequantize ((q - zero_point) * scale), float operator,
+ * quantize (lround(v / scale) + zero_point, clamped to [0, 255]); results are identical to it bit for bit
+ * except softmax (expf: within +-1, the tolerance of the reference's own tests).
+ *   pooling     NEPoolingLayer          arm_compute/runtime/NEON/functions/NEPoolingLayer.h:48-109;
+ *                                       oracle tests/validation/reference/PoolingLayer.cpp:40-196, 218-230
+ *   addition    NEArithmeticAddition    arm_compute/runtime/NEON/functions/NEArithmeticAddition.h:43-109;
+ *                                       oracle tests/validation/reference/ArithmeticOperations.cpp:124-151
+ *   activation  NEActivationLayer       arm_compute/runtime/NEON/functions/NEActivationLayer.h:48-107;
+ *                                       oracle tests/validation/reference/ActivationLayer.cpp:61-71
+ *   softmax     NESoftmaxLayer          arm_compute/runtime/NEON/functions/NESoftmaxLayer.h:44-99;
+ *                                       oracle tests/validation/reference/SoftmaxLayer.cpp:39-107, 201-213
+ * ---------------------------------------------------------------------------------------------- */
+typedef enum cugl_pool_type
+{
+    CUGL_POOL_MAX = 0,
+    CUGL_POOL_AVG = 1
+} cugl_pool_type;
+
+typedef enum cugl_activation
+{
+    CUGL_ACT_NONE            = -1,
+    CUGL_ACT_RELU            = 0, /* max(0, x)           */
+    CUGL_ACT_BOUNDED_RELU    = 1, /* min(a, max(0, x))   */
+    CUGL_ACT_LU_BOUNDED_RELU = 2  /* min(a, max(b, x))   */
+} cugl_activation;
+
+typedef struct cugl_pool_desc
+{
+    int32_t B, H, W, C;               /* src [B][H][W][C] */
+    int32_t pool_type;                /* cugl_pool_type */
+    int32_t pool_w, pool_h;
+    int32_t stride_x, stride_y;
+    int32_t pad_left, pad_right, pad_top, pad_bottom;
+    int32_t exclude_padding;          /* AVG: divide by the in-image window area only */
+    int32_t is_global;                /* window = whole image; pool_*, stride_*, pad_* ignored */
+    float   src_scale;
+    int32_t src_zero_point;
+    float   dst_scale;
+    int32_t dst_zero_point;
+} cugl_pool_desc;
+
+/* FLOOR rounding of the output size, as arm_compute::scaled_dimensions. */
+CUGL_API void cugl_pool2d_out_dims(const cugl_pool_desc *desc, int32_t *Wo, int32_t *Ho);
+CUGL_API cugl_status cugl_pool2d_validate(const cugl_pool_desc *desc);
+/* dst is [B][Ho][Wo][C]. */
+CUGL_API cugl_status cugl_pool2d_nhwc(cugl_context *ctx, const cugl_pool_desc *desc, const void *d_src, void *d_dst);
+
+/* dst[i] = act(quantize(dequantize(a[i]) + dequantize(b[i]))) over n elements (ConvertPolicy::SATURATE).  The
+ * activation (CUGL_ACT_NONE for none) acts on the quantized sum exactly as a separate NEActivationLayer with
+ * equal input and output quantization would.  a_scale / b_scale must lie within 2^-20 .. 2^20. */
+CUGL_API cugl_status cugl_add_qasymm8(cugl_context *ctx, const void *d_a, const void *d_b, void *d_dst, int64_t n,
+                                      float a_scale, int32_t a_zero_point, float b_scale, int32_t b_zero_point,
+                                      float dst_scale, int32_t dst_zero_point, int32_t activation, float act_a,
+                                      float act_b);
+CUGL_API cugl_status cugl_activation_qasymm8(cugl_context *ctx, const void *d_src, void *d_dst, int64_t n,
+                                             int32_t activation, float act_a, float act_b, float src_scale,
+                                             int32_t src_zero_point, float dst_scale, int32_t dst_zero_point);
+/* rows x cols, contiguous rows; softmax along a row; output quantization is fixed at (1/256, 0). */
+CUGL_API cugl_status cugl_softmax_qasymm8(cugl_context *ctx, const void *d_src, void *d_dst, int32_t rows, int32_t cols,
+                                          float beta, float src_scale, int32_t src_zero_point);
+
 #ifdef __cplusplus
 }
 #endif

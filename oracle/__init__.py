@@ -3,7 +3,8 @@
 Nothing in the shipped package imports this module: it is loaded by ``tests/``, by
 ``__graft_entry__.smoke()`` and by the CPU-baseline leg of ``bench.py``.
 
-``port``  -- ctypes view of ``libgemmlowp_oracle.so`` (the plain-C restatement, ``gemmlowp_oracle.c``).
+``port``  -- ctypes view of ``libgemmlowp_oracle.so`` (the plain-C restatement, ``gemmlowp_oracle.c`` and
+             ``layers_oracle.c``).
 ``ref``   -- ctypes view of ``_ref/libacl_ref.so`` (Compute Library's own scalar test oracle compiled in
              place by ``make -C oracle ref``), or ``None`` when that library has not been built.
 """
@@ -43,7 +44,76 @@ def _i32arr(x) -> np.ndarray:
     return np.ascontiguousarray(np.atleast_1d(np.asarray(x, dtype=np.int32)))
 
 
-class _Port:
+class _Layers:
+    """QASYMM8 layer oracles; `self._pfx` selects the C restatement ("orc_") or the reference ("ref_")."""
+
+    @staticmethod
+    def pool_out_dims(W, H, pw, ph, sx, sy, pl, pr, pt, pb):
+        """FLOOR rounding (arm_compute::scaled_dimensions, src/core/Utils.cpp)."""
+        return (W + pl + pr - pw) // sx + 1, (H + pt + pb - ph) // sy + 1
+
+    def pool_nhwc(self, src, pool_type, size, stride, pad, in_q, out_q, exclude_padding=False, global_pool=False):
+        """src [B,H,W,C] uint8; pool_type "max" | "avg"; size (pw, ph); pad (l, r, t, b); q = (scale, zero point)."""
+        src = np.ascontiguousarray(src)
+        assert src.dtype == np.uint8
+        B, H, W, Cc = src.shape
+        if global_pool:
+            size, stride, pad = (W, H), (1, 1), (0, 0, 0, 0)
+        pw, ph = size
+        sx, sy = stride
+        pl, pr, pt, pb = pad
+        wo, ho = self.pool_out_dims(W, H, pw, ph, sx, sy, pl, pr, pt, pb)
+        dst = np.empty((B, ho, wo, Cc), np.uint8)
+        ptype = 0 if pool_type == "max" else 1
+        if self._pfx == "orc_":
+            self.lib.orc_pool_nhwc_u8(_ptr(src), _ptr(dst), Cc, W, H, B, ptype, pw, ph, sx, sy, pl, pr, pt, pb,
+                                      int(exclude_padding), wo, ho, C.c_float(in_q[0]), C.c_int(in_q[1]),
+                                      C.c_float(out_q[0]), C.c_int(out_q[1]))
+        else:
+            rw, rh = C.c_int(0), C.c_int(0)
+            self.lib.ref_pool_nhwc_u8(_ptr(src), None, Cc, W, H, B, ptype, pw, ph, sx, sy, pl, pr, pt, pb,
+                                      int(exclude_padding), int(global_pool), C.c_float(in_q[0]), C.c_int(in_q[1]),
+                                      C.c_float(out_q[0]), C.c_int(out_q[1]), C.byref(rw), C.byref(rh))
+            assert (rw.value, rh.value) == (wo, ho), "output-shape rule differs from the reference"
+            self.lib.ref_pool_nhwc_u8(_ptr(src), _ptr(dst), Cc, W, H, B, ptype, pw, ph, sx, sy, pl, pr, pt, pb,
+                                      int(exclude_padding), int(global_pool), C.c_float(in_q[0]), C.c_int(in_q[1]),
+                                      C.c_float(out_q[0]), C.c_int(out_q[1]), None, None)
+        return dst
+
+    def add_qasymm8(self, a, b, a_q, b_q, o_q):
+        a = np.ascontiguousarray(a)
+        b = np.ascontiguousarray(b)
+        assert a.dtype == np.uint8 and b.dtype == np.uint8 and a.shape == b.shape
+        dst = np.empty_like(a)
+        getattr(self.lib, self._pfx + "add_qasymm8")(
+            _ptr(a), _ptr(b), _ptr(dst), C.c_longlong(a.size), C.c_float(a_q[0]), C.c_int(a_q[1]), C.c_float(b_q[0]),
+            C.c_int(b_q[1]), C.c_float(o_q[0]), C.c_int(o_q[1]))
+        return dst
+
+    def activation_qasymm8(self, src, act, a, b, in_q, out_q):
+        """act: "relu" | "bounded_relu" (upper a) | "lu_bounded_relu" (upper a, lower b)."""
+        src = np.ascontiguousarray(src)
+        assert src.dtype == np.uint8
+        dst = np.empty_like(src)
+        code = {"relu": 0, "bounded_relu": 1, "lu_bounded_relu": 2}[act]
+        getattr(self.lib, self._pfx + "activation_qasymm8")(
+            _ptr(src), _ptr(dst), C.c_longlong(src.size), code, C.c_float(a), C.c_float(b), C.c_float(in_q[0]),
+            C.c_int(in_q[1]), C.c_float(out_q[0]), C.c_int(out_q[1]))
+        return dst
+
+    def softmax_qasymm8(self, src, beta, in_q):
+        """src [rows, cols] uint8; softmax along cols; output quantization (1/256, 0)."""
+        src = np.ascontiguousarray(src)
+        assert src.dtype == np.uint8 and src.ndim == 2
+        dst = np.empty_like(src)
+        getattr(self.lib, self._pfx + "softmax_qasymm8")(
+            _ptr(src), _ptr(dst), src.shape[0], src.shape[1], C.c_float(beta), C.c_float(in_q[0]), C.c_int(in_q[1]))
+        return dst
+
+
+class _Port(_Layers):
+    _pfx = "orc_"
+
     def __init__(self):
         if not os.path.exists(PORT_SO):
             build(want_ref=False)
@@ -194,8 +264,9 @@ class _Port:
         return dst
 
 
-class _Ref:
+class _Ref(_Layers):
     """Compute Library's own test oracle (tests/validation/reference), compiled in place."""
+    _pfx = "ref_"
 
     def __init__(self):
         self.lib = C.CDLL(REF_SO)

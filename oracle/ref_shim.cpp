@@ -38,30 +38,6 @@ using namespace arm_compute;
 using namespace arm_compute::test;
 using namespace arm_compute::test::validation;
 
-// Only gemmlowp_matrix_multiply_core_accumulate (never called here) needs this symbol; its real
-// definition lives in ArithmeticOperations.cpp, which would pull in the test runner.
-namespace arm_compute
-{
-namespace test
-{
-namespace validation
-{
-namespace reference
-{
-template <>
-SimpleTensor<int32_t> arithmetic_operation<int32_t>(ArithmeticOperation,
-                                                    const SimpleTensor<int32_t> &,
-                                                    const SimpleTensor<int32_t> &,
-                                                    SimpleTensor<int32_t> &,
-                                                    ConvertPolicy)
-{
-    throw std::runtime_error("arithmetic_operation is not part of this oracle build");
-}
-} // namespace reference
-} // namespace validation
-} // namespace test
-} // namespace arm_compute
-
 namespace
 {
 template <typename T>

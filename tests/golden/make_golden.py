@@ -1,10 +1,10 @@
 """Generates the committed golden fixtures of tests/golden/ from Compute Library's OWN scalar test oracle
-(tests/validation/reference/{GEMMLowp.cpp,ConvolutionLayer.cpp,Im2Col.cpp}, UtilsQuantizedAsymm.h and
-AsymmHelpers.cpp), compiled in place into oracle/_ref/libacl_ref.so by `make -C oracle ref`.
+(tests/validation/reference/{GEMMLowp,ConvolutionLayer,Im2Col,PoolingLayer,ArithmeticOperations,ActivationLayer,
+SoftmaxLayer}.cpp, UtilsQuantizedAsymm.h and AsymmHelpers.cpp), compiled in place into oracle/_ref/libacl_ref.so by `make -C oracle ref`.
 
     python tests/golden/make_golden.py        # needs the Compute Library tree; rewrites the fixtures
 
-The fixtures let the CPU-side restatement (oracle/gemmlowp_oracle.c) and the CUDA path be checked against
+The fixtures let the CPU-side restatement (oracle/gemmlowp_oracle.c, oracle/layers_oracle.c) and the CUDA path be checked against
 reference outputs on machines where the reference tree is absent.
 """
 import json
@@ -18,8 +18,9 @@ sys.path.insert(0, os.path.dirname(os.path.dirname(HERE)))
 sys.path.insert(0, os.path.dirname(HERE))
 
 import oracle  # noqa: E402
-from helpers import (GOLDEN_CONV_SCALES, config1, golden_conv_cases, golden_gemm_cases,  # noqa: E402
-                     golden_im2col_cases)
+from helpers import (GOLDEN_CONV_SCALES, config1, golden_act_cases, golden_add_cases,  # noqa: E402
+                     golden_conv_cases, golden_gemm_cases, golden_im2col_cases, golden_pool_cases,
+                     golden_softmax_cases, pool_with)
 
 
 def main():
@@ -86,6 +87,18 @@ def main():
     for c in golden_im2col_cases():
         conv[c["key"]] = ref.im2col_nhwc(c["src"], c["kw"], c["kh"], *c["stride"], *c["pad"], c["zp"])
     np.savez_compressed(os.path.join(HERE, "conv_golden.npz"), **conv)
+
+    # --- QASYMM8 layers: pooling, addition, activation, softmax ------------------------------------
+    layers = {}
+    for c in golden_pool_cases():
+        layers[c["key"]] = pool_with(ref, c)
+    for c in golden_add_cases():
+        layers[c["key"]] = ref.add_qasymm8(c["a"], c["b"], *c["q"])
+    for c in golden_act_cases():
+        layers[c["key"]] = ref.activation_qasymm8(c["src"], c["act"], c["a"], c["b"], c["in_q"], c["out_q"])
+    for c in golden_softmax_cases():
+        layers[c["key"]] = ref.softmax_qasymm8(c["src"], c["beta"], c["q"])
+    np.savez_compressed(os.path.join(HERE, "layers_golden.npz"), **layers)
     print("golden fixtures written to", HERE)
 
 

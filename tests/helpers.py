@@ -117,3 +117,86 @@ def golden_im2col_cases():
         r = np.random.default_rng(7000 + ci)
         src = q8_uniform(r, (2, 9, 8, 16 if ci % 2 == 0 else 5), np.uint8)
         yield dict(key=f"im2col{ci}", src=src, kw=kw, kh=kh, stride=(sx, sy), pad=pad, zp=77)
+
+
+# ---- QASYMM8 layers (pooling / addition / activation / softmax) -----------------------------------------
+# (pool_type, size, stride, pad (l, r, t, b), exclude_padding, global)
+GOLDEN_POOL_GEOMS = [
+    ("max", (3, 3), (2, 2), (0, 1, 0, 1), False, False),   # ResNet-50 pool1
+    ("max", (1, 1), (2, 2), (0, 0, 0, 0), True, False),    # ResNet-50 strided shortcut
+    ("max", (2, 2), (2, 2), (0, 0, 0, 0), False, False),
+    ("max", (3, 3), (1, 1), (1, 1, 1, 1), False, False),
+    ("avg", (3, 3), (1, 1), (1, 1, 1, 1), False, False),
+    ("avg", (3, 3), (2, 2), (1, 1, 1, 1), True, False),
+    ("avg", (2, 2), (2, 1), (0, 1, 1, 0), False, False),
+    ("avg", None, None, None, False, True),                # ResNet-50 pool5
+]
+GOLDEN_LAYER_QINFOS = [((0.05, 0), (0.05, 0)), ((0.03, 10), (0.07, 3)), ((0.5, 128), (0.25, 0))]
+GOLDEN_ADD_QINFOS = [((0.05, 0), (0.05, 0), (0.05, 0)), ((0.03, 5), (0.07, 100), (0.09, 20)),
+                     ((0.5, 128), (0.25, 0), (0.3, 7)), ((0.01, 3), (0.02, 250), (0.004, 128))]
+GOLDEN_ACTS = [("relu", 0.0, 0.0), ("bounded_relu", 6.0, 0.0), ("lu_bounded_relu", 4.0, -2.0)]
+
+
+def golden_pool_cases():
+    for gi, geom in enumerate(GOLDEN_POOL_GEOMS):
+        for si, shape in enumerate([(2, 9, 11, 5), (1, 8, 8, 32), (2, 7, 7, 48)]):
+            for qi, (in_q, out_q) in enumerate(GOLDEN_LAYER_QINFOS):
+                r = np.random.default_rng(9000 + 100 * gi + 10 * si + qi)
+                yield dict(key=f"pool{gi}_{si}_{qi}", src=r.integers(0, 256, shape, dtype=np.uint8), geom=geom,
+                           in_q=in_q, out_q=out_q)
+
+
+def golden_add_cases():
+    for qi, qs in enumerate(GOLDEN_ADD_QINFOS):
+        for ni, n in enumerate([1, 15, 16, 4099, 65536]):
+            r = np.random.default_rng(9500 + 10 * qi + ni)
+            yield dict(key=f"add{qi}_{ni}", a=r.integers(0, 256, n, dtype=np.uint8),
+                       b=r.integers(0, 256, n, dtype=np.uint8), q=qs)
+
+
+def golden_act_cases():
+    for ai, (act, a, b) in enumerate(GOLDEN_ACTS):
+        for qi, (in_q, out_q) in enumerate(GOLDEN_LAYER_QINFOS + [((0.05, 100), (0.03, 80))]):
+            r = np.random.default_rng(9700 + 10 * ai + qi)
+            src = np.concatenate([np.arange(256, dtype=np.uint8), r.integers(0, 256, 4000 + ai, dtype=np.uint8)])
+            yield dict(key=f"act{ai}_{qi}", src=src, act=act, a=a, b=b, in_q=in_q, out_q=out_q)
+
+
+def golden_softmax_cases():
+    for si, (rows, cols, beta, q) in enumerate([(7, 1000, 1.0, (0.05, 0)), (3, 10, 1.0, (0.1, 20)),
+                                                (5, 257, 0.5, (0.02, 128)), (1, 1, 1.0, (0.05, 0))]):
+        r = np.random.default_rng(9900 + si)
+        yield dict(key=f"softmax{si}", src=r.integers(0, 256, (rows, cols), dtype=np.uint8), beta=beta, q=q)
+
+
+def pool_with(oracle_obj, c):
+    pt, size, stride, pad, excl, glob = c["geom"]
+    return oracle_obj.pool_nhwc(c["src"], pt, size, stride, pad, c["in_q"], c["out_q"], exclude_padding=excl,
+                                global_pool=glob)
+
+
+# ---- QASYMM8 ResNet-50: the node list of computelibrary_b200.resnet50 interpreted by the CPU oracle ------
+def run_graph_oracle(port, nodes, params, x, act_q=(0.05, 0)):
+    """x: uint8 [B, image, image, 3].  Returns {node name: uint8 NHWC output}."""
+    out = {"input": x}
+    for n in nodes:
+        src = [out[s] for s in n["inputs"]]
+        if n["op"] == "conv":
+            p = params[n["name"]]
+            out[n["name"]] = port.conv2d_nhwc(src[0], p["weights"], p["bias"], (n["stride"],) * 2, (n["pad"],) * 4,
+                                              act_q[1], 0, p["mult"], p["shift"], act_q[1],
+                                              act_q[1] if n["relu"] else 0, 255)
+        elif n["op"] == "maxpool":
+            out[n["name"]] = port.pool_nhwc(src[0], "max", (n["k"],) * 2, (n["stride"],) * 2, n["pad"], act_q, act_q,
+                                            exclude_padding=True)
+        elif n["op"] == "avgpool_global":
+            out[n["name"]] = port.pool_nhwc(src[0], "avg", None, None, None, act_q, act_q, global_pool=True)
+        elif n["op"] == "add_relu":
+            s = port.add_qasymm8(src[0], src[1], act_q, act_q, act_q)
+            out[n["name"]] = port.activation_qasymm8(s, "relu", 0.0, 0.0, act_q, act_q)
+        elif n["op"] == "softmax":
+            B = src[0].shape[0]
+            out[n["name"]] = port.softmax_qasymm8(src[0].reshape(B, -1), 1.0, act_q).reshape(src[0].shape)
+        else:
+            raise ValueError(n["op"])
+    return out

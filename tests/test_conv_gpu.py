@@ -129,3 +129,24 @@ def test_implicit_conv_vs_oracle(ctx, port, geom, in_zp):
                    want_kernel="implicit")
     want = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, dilation=(d, d))
     assert np.array_equal(got, want), np.argwhere(got != want)[:5]
+
+
+@pytest.mark.parametrize("geom", [(7, 3, 3, 20, 22), (7, 3, 3, 19, 23), (3, 1, 4, 17, 18), (5, 2, 1, 9, 11), (3, 0, 3, 12, 15),
+                                  (2, 1, 2, 10, 10), (4, 2, 4, 21, 16)])
+@pytest.mark.parametrize("in_zp", [0, 77])
+def test_folded_stride2_conv_vs_oracle(ctx, port, geom, in_zp):
+    """Stride-2 convolutions over at most four channels (the 7x7 / 2 stem of ResNet-50 on RGB images) run as a
+    2x2 space-to-depth 16-channel stride-1 convolution: even and odd image sizes, even and odd paddings, kernel
+    sizes 2..7; both the implicit kernel and the explicit im2col lowering of the folded form."""
+    k, p, Cc, H, W = geom
+    rng = np.random.default_rng(k * 100 + p * 10 + Cc + in_zp)
+    src = q8_uniform(rng, (2, H, W, Cc), np.uint8)
+    wgt = q8_uniform(rng, (24, k, k, Cc), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, 24).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), 24)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.05, ws, 0.05)
+    want = port.conv2d_nhwc(src, wgt, bias, (2, 2), (p, p, p, p), in_zp, 0, mult, shift, 0, 0, 255)
+    for implicit in (True, False):
+        got = gpu_conv(ctx, src, wgt, bias, (2, 2), (p, p, p, p), in_zp, 0, mult, shift, 0, 0, 255, implicit=implicit,
+                       want_kernel="implicit" if implicit else "im2col")
+        assert np.array_equal(got, want), (implicit, np.argwhere(got != want)[:5])
