@@ -129,6 +129,11 @@ _SIGNATURES = {
     "cugl_conv2d_plan_launches": (C.c_int, [_vp]),
     "cugl_conv2d_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_conv2d_plan_allow_implicit": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_residual": (C.c_int, [_vp, C.c_float, C.c_float, _i32, C.c_float, _i32, _i32, C.c_float,
+                                                C.c_float]),
+    "cugl_conv2d_run_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
+    "cugl_gemmlowp_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
     "cugl_pool2d_out_dims": (None, [C.POINTER(PoolDesc), _pi32, _pi32]),
     "cugl_pool2d_validate": (C.c_int, [C.POINTER(PoolDesc)]),
     "cugl_pool2d_nhwc": (C.c_int, [_vp, C.POINTER(PoolDesc), _vp, _vp]),
@@ -449,6 +454,9 @@ class GemmPlan:
     def force_simt(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_force_simt(self.handle, int(on)))
 
+    def set_epilogue_warps(self, warps: int):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_epilogue_warps(self.handle, int(warps)))
+
     def allow_pair_kernel(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_allow_pair_kernel(self.handle, int(on)))
 
@@ -524,9 +532,22 @@ class ConvPlan:
     def run(self, src, bias, dst):
         self.ctx.check(self.ctx.lib.cugl_conv2d_run(self.handle, _dptr(src), _dptr(bias), _dptr(dst)))
 
+    def set_residual(self, conv_out_scale, res_q, dst_q, act=ACT_NONE, act_a=0.0, act_b=0.0):
+        """Configure the fused residual addition; raises CuglError (UNSUPPORTED_CONFIG) when the addition is not a
+        saturating byte addition for these quantizations."""
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_residual(self.handle, conv_out_scale, res_q[0], res_q[1],
+                                                                  dst_q[0], dst_q[1], act, act_a, act_b))
+
+    def run_residual(self, src, bias, residual, dst):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_run_residual(self.handle, _dptr(src), _dptr(bias), _dptr(residual),
+                                                             _dptr(dst)))
+
     def run_host(self, h_src: int, h_bias, h_dst: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_run_host(self.handle, _vp(h_src), _vp(h_bias) if h_bias else None,
                                                          _vp(h_dst)))
+
+    def set_epilogue_warps(self, warps: int):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_epilogue_warps(self.handle, int(warps)))
 
     def allow_implicit(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_implicit(self.handle, int(on)))

@@ -40,6 +40,13 @@ constexpr int      UMMA_K      = 32;  // K per tcgen05.mma.kind::i8
 #ifndef CUGL_EPI_WARPS
 #define CUGL_EPI_WARPS 4
 #endif
+// This file is compiled once per epilogue-warp count (gemmlowp_tcgen05_epi8.cu includes it with
+// CUGL_EPI_WARPS = 8): four epilogue warps leave the issue slots to the single-thread producer and MMA loops,
+// which is what long-K GEMMs want; short-K tiles spend their time in the epilogue and want eight.  The
+// entry points carry the count in their names and gemmlowp_dispatch.cu chooses between them.
+#define CUGL_TC_CAT2(a, b) a##_epi##b
+#define CUGL_TC_CAT(a, b) CUGL_TC_CAT2(a, b)
+#define CUGL_TC_NAME(x) CUGL_TC_CAT(x, CUGL_EPI_WARPS)
 constexpr int      kProdWarps  = CUGL_PROD_WARPS;          // producer warps (one issuing lane each)
 constexpr int      kProdLanes  = kProdWarps;               // independent copy issuers per CTA
 constexpr int      kMmaWarp    = kProdWarps;               // index of the MMA-issuing warp
@@ -264,7 +271,9 @@ struct TileParams
     int      M, N, K;
     uint32_t idesc;
     int      vec_ok;  // dst base and ldd are 16-byte aligned
-    int      generic; // some column shifts left or has multiplier INT32_MIN: take the fully general path
+    int      mode;    // kStageGeneric / kStageFast / kStageWide: encoding of the column terms (requant_pack4)
+    const uint8_t *residual; // optional [M][ldd] bytes added to the output with unsigned saturation, then clamped
+    uint32_t res_floor4, res_cap4; // the clamp bounds replicated into four bytes
     long long *trace; // optional per-CTA event timestamps (cugl_context_set_trace_buffer), else nullptr
     int32_t *status;
 };
@@ -349,12 +358,19 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
                  : "memory");
 }
 
-// Requantise + clamp + pack four accumulators of one row (columns c .. c+3 of the tile).
-//   fast path  : every shift is a right shift and no multiplier is INT32_MIN, so the column term holds
-//                {offset+bias term, multiplier, 1 << (shift-1) (0 for shift 0), shift} and the saturating
-//                corner of SQDMULH cannot occur;
-//   generic    : {term, multiplier, right | left << 8, -} and the full reference expression.
-template <bool kGeneric>
+// Requantise + clamp + pack four accumulators of one row (columns c .. c+3 of the tile).  Three encodings of
+// the per-column term, chosen on the host from the multipliers and shifts (TileParams::mode):
+//   kStageGeneric : {term, multiplier, right | left << 8, -} and the full reference expression;
+//   kStageFast    : every shift is a right shift and no multiplier is INT32_MIN, so the saturating corner of
+//                   SQDMULH cannot occur: {term, multiplier, 1 << (shift-1) (0 for shift 0), shift};
+//   kStageWide    : every shift s is >= 2, every multiplier m is in [0, 2^31) and there is no row term.  Then
+//                   ((floor((v+t)*m / 2^31) + 2^(s-1)) >> s equals hi32(v*m + (t*m + 2^(30+s))) >> (s-1): the
+//                   bracket is a 64-bit constant of the column, so one wide multiply-add and one shift replace
+//                   five instructions.  {constant lo, constant hi, multiplier, s-1}.  Equal to the reference
+//                   wherever its own 32-bit sums v+t and x + 2^(s-1) do not overflow.
+constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2;
+
+template <int kMode>
 __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 *col, int32_t row_term, int32_t offset,
                                                   int32_t lo, int32_t hi)
 {
@@ -362,19 +378,30 @@ __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 
 #pragma unroll
     for (int b = 0; b < 4; ++b)
     {
-        const int4    q   = col[b];
-        const int32_t acc = static_cast<int32_t>(v[b]) + q.x + row_term;
-        if (kGeneric)
+        const int4 q = col[b];
+        if (kMode == kStageWide)
         {
-            r[b] = finalize(acc, q.y, q.z >> 8, q.z & 0xff, offset, lo, hi);
+            const long long c64 = static_cast<long long>((static_cast<unsigned long long>(static_cast<uint32_t>(q.y)) << 32) |
+                                                         static_cast<uint32_t>(q.x));
+            const long long p   = static_cast<long long>(static_cast<int32_t>(v[b])) * q.z + c64;
+            const int32_t   t   = static_cast<int32_t>(p >> 32) >> q.w;
+            r[b]                = max(__viaddmin_s32(t, offset, hi), lo);
         }
         else
         {
-            const int32_t  mh = __mulhi(acc, q.y);
-            const uint32_t ml = static_cast<uint32_t>(acc) * static_cast<uint32_t>(q.y);
-            const uint32_t d  = __funnelshift_l(ml, static_cast<uint32_t>(mh), 1);         // floor(acc*mult / 2^31)
-            const int32_t  t  = static_cast<int32_t>(d + static_cast<uint32_t>(q.z)) >> q.w; // round-half-up shift
-            r[b]              = min(max(t + offset, lo), hi);
+            const int32_t acc = static_cast<int32_t>(v[b]) + q.x + row_term;
+            if (kMode == kStageGeneric)
+            {
+                r[b] = finalize(acc, q.y, q.z >> 8, q.z & 0xff, offset, lo, hi);
+            }
+            else
+            {
+                const int32_t  mh = __mulhi(acc, q.y);
+                const uint32_t ml = static_cast<uint32_t>(acc) * static_cast<uint32_t>(q.y);
+                const uint32_t d  = __funnelshift_l(ml, static_cast<uint32_t>(mh), 1);         // floor(acc*mult / 2^31)
+                const int32_t  t  = static_cast<int32_t>(d + static_cast<uint32_t>(q.z)) >> q.w; // round-half-up shift
+                r[b]              = min(max(t + offset, lo), hi);
+            }
         }
     }
     const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
@@ -430,7 +457,7 @@ __device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, in
     }
 }
 
-template <bool kS32Out, bool kGeneric>
+template <bool kS32Out, int kMode>
 __device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col, int32_t row_term,
                                               const EpilogueParams &ep)
 {
@@ -447,39 +474,44 @@ __device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
         {
-            v[j >> 2] = requant_pack4<kGeneric>(v + j, col + j, row_term, ep.result_offset, ep.lo, ep.hi);
+            v[j >> 2] = requant_pack4<kMode>(v + j, col + j, row_term, ep.result_offset, ep.lo, ep.hi);
         }
     }
 }
 
 // Output staging of the multi-destination (push all-gather) epilogue.  A thread owns one row, so its direct
 // stores are 16-byte pieces 'ldd' apart: harmless in local memory, where L2 merges them, but over NVLink every
-// piece is a packet of its own.  Here a warp first collects 32 rows x 128 columns in shared memory (piece p of
-// row r at p ^ (r & 7): conflict-free both ways) and then stores them with eight lanes per row, 128 contiguous
-// bytes each, to every destination.
-constexpr int kOutStageBytes = 32 * 128;
+// piece is a packet of its own.  Here a warp first collects 32 rows x kOutRowBytes columns in shared memory
+// (piece p of row r at p ^ (r & (pieces - 1)): conflict-free both ways) and then stores them with one lane per
+// piece, kOutRowBytes contiguous bytes per row, to every destination.  128 bytes per row with four epilogue
+// warps, 64 with eight (shared memory holds 32 KB of staging at most beside the operand ring).
+constexpr int kOutRowBytes   = kEpiWarps == 4 ? 128 : 64;
+constexpr int kOutPieces     = kOutRowBytes / 16;
+constexpr int kOutChunks     = kOutRowBytes / 32; // 32-column chunks per staged group
+constexpr int kOutStageBytes = 32 * kOutRowBytes;
 
 __device__ __forceinline__ void stage_chunk(uint8_t *stage, const uint32_t *w, int group_chunk, int lane)
 {
-    uint8_t *row = stage + lane * 128;
-    *reinterpret_cast<uint4 *>(row + (((2 * group_chunk) ^ (lane & 7)) << 4))     = make_uint4(w[0], w[1], w[2], w[3]);
-    *reinterpret_cast<uint4 *>(row + (((2 * group_chunk + 1) ^ (lane & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    uint8_t *row = stage + lane * kOutRowBytes;
+    const int sw = lane & (kOutPieces - 1);
+    *reinterpret_cast<uint4 *>(row + (((2 * group_chunk) ^ sw) << 4))     = make_uint4(w[0], w[1], w[2], w[3]);
+    *reinterpret_cast<uint4 *>(row + (((2 * group_chunk + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 __device__ __forceinline__ void flush_stage(const uint8_t *stage, const TileParams &tp, int m_base, int n_group,
                                             int ncols_group, int lane)
 {
     __syncwarp();
-    const int p = lane & 7;
+    const int p = lane & (kOutPieces - 1);
 #pragma unroll 2
-    for (int it = 0; it < 8; ++it)
+    for (int it = 0; it < kOutPieces; ++it)
     {
-        const int r = it * 4 + (lane >> 3);
+        const int r = it * (32 / kOutPieces) + lane / kOutPieces;
         const int m = m_base + r;
         const int n = n_group + p * 16;
         if (p * 16 < ncols_group && m < tp.M && n < tp.N)
         {
-            const uint4   val = *reinterpret_cast<const uint4 *>(stage + r * 128 + ((p ^ (r & 7)) << 4));
+            const uint4   val = *reinterpret_cast<const uint4 *>(stage + r * kOutRowBytes + ((p ^ (r & (kOutPieces - 1))) << 4));
             const int64_t off = static_cast<int64_t>(m) * tp.ldd + n;
             if (n + 16 <= tp.N && tp.vec_ok)
             {
@@ -507,10 +539,45 @@ __device__ __forceinline__ void flush_stage(const uint8_t *stage, const TilePara
     __syncwarp();
 }
 
+// Fused residual addition on 32 packed output bytes of one row: out = min(max(min(out + res, 255), floor), cap),
+// the form the host has proved equal to quantize(dequantize(out) + dequantize(res)) followed by the activation.
+__device__ __forceinline__ void apply_residual(uint32_t *w, const uint8_t *rrow, int nc, bool row_ok, const TileParams &tp)
+{
+    if (!row_ok)
+    {
+        return;
+    }
+    uint32_t r[8];
+    if (nc + 32 <= tp.N && tp.vec_ok)
+    {
+        const uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(rrow + nc));
+        const uint4 r1 = __ldg(reinterpret_cast<const uint4 *>(rrow + nc + 16));
+        r[0] = r0.x, r[1] = r0.y, r[2] = r0.z, r[3] = r0.w, r[4] = r1.x, r[5] = r1.y, r[6] = r1.z, r[7] = r1.w;
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            uint32_t v = 0;
+            for (int b = 0; b < 4; ++b)
+            {
+                if (nc + 4 * j + b < tp.N) v |= static_cast<uint32_t>(rrow[nc + 4 * j + b]) << (8 * b);
+            }
+            r[j] = v;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+    {
+        w[j] = __vminu4(__vmaxu4(__vaddus4(w[j], r[j]), tp.res_floor4), tp.res_cap4);
+    }
+}
+
 // Shared epilogue of both kernels: one warp drains NCOLS consecutive columns (a multiple of 32) of its
 // 32 accumulator rows from tensor memory, applies the offset / bias terms and the output stage, and
 // stores.  The tensor-memory load of chunk i+1 is issued before chunk i is processed.
-template <int NCOLS, bool kS32Out, bool kGeneric>
+template <int NCOLS, bool kS32Out, int kMode>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s_col, const TileParams &tp,
                                                   const EpilogueParams &ep, int m, int n_first, int32_t row_term,
                                                   uint8_t *stage, int lane)
@@ -529,10 +596,14 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         {
             tmem_ld_x32(t_addr + (ch + 1) * 32, vb);
         }
-        process_chunk<kS32Out, kGeneric>(va, s_col + ch * 32, row_term, ep);
+        process_chunk<kS32Out, kMode>(va, s_col + ch * 32, row_term, ep);
+        if (!kS32Out && tp.residual != nullptr)
+        {
+            apply_residual(va, tp.residual + row_off, n_first + ch * 32, row_ok, tp);
+        }
         if (staged)
         {
-            stage_chunk(stage, va, ch & 3, lane);
+            stage_chunk(stage, va, ch & (kOutChunks - 1), lane);
             if (NCOLS / 32 == 1)
             {
                 flush_stage(stage, tp, m - lane, n_first, 32, lane);
@@ -553,13 +624,17 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             {
                 tmem_ld_x32(t_addr + (ch + 2) * 32, va);
             }
-            process_chunk<kS32Out, kGeneric>(vb, s_col + (ch + 1) * 32, row_term, ep);
+            process_chunk<kS32Out, kMode>(vb, s_col + (ch + 1) * 32, row_term, ep);
+            if (!kS32Out && tp.residual != nullptr)
+            {
+                apply_residual(vb, tp.residual + row_off, n_first + (ch + 1) * 32, row_ok, tp);
+            }
             if (staged)
             {
-                stage_chunk(stage, vb, (ch + 1) & 3, lane);
-                if (((ch + 1) & 3) == 3 || ch + 2 >= NCOLS / 32)
+                stage_chunk(stage, vb, (ch + 1) & (kOutChunks - 1), lane);
+                if (((ch + 1) & (kOutChunks - 1)) == kOutChunks - 1 || ch + 2 >= NCOLS / 32)
                 {
-                    const int first = (ch + 1) & ~3; // first chunk of this 128-column group
+                    const int first = (ch + 1) & ~(kOutChunks - 1); // first chunk of this staged group
                     flush_stage(stage, tp, m - lane, n_first + first * 32, (ch + 2 - first) * 32, lane);
                 }
             }
@@ -592,14 +667,22 @@ __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, c
             const int32_t sh = ep.shifts != nullptr ? __ldg(ep.shifts + n) : ep.shift;
             q.x              = t;
             q.y              = ep.mults != nullptr ? __ldg(ep.mults + n) : ep.mult;
-            if (tp.generic)
+            if (tp.mode == kStageGeneric)
             {
                 q.z = max(sh, 0) | (max(-sh, 0) << 8);
             }
-            else
+            else if (tp.mode == kStageFast)
             {
                 q.z = static_cast<int32_t>((1u << sh) >> 1);
                 q.w = sh;
+            }
+            else
+            {
+                const long long c64 = static_cast<long long>(t) * q.y + (1ll << (30 + sh));
+                q.z                 = q.y;
+                q.x                 = static_cast<int32_t>(static_cast<uint32_t>(c64));
+                q.y                 = static_cast<int32_t>(c64 >> 32);
+                q.w                 = sh - 1;
             }
         }
         s_col[c] = q;
@@ -619,15 +702,20 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
     const int     m        = m0 + quad * 32 + lane;
     const int32_t row_term = (ep.rowsum != nullptr && m < tp.M) ? ep.b_off * __ldg(ep.rowsum + m) : 0;
     const uint32_t t_addr  = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NCOLS;
-    if (tp.generic)
+    if (tp.mode == kStageWide && !kS32Out)
     {
-        drain_accumulator<NCOLS, kS32Out, true>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                stage, lane);
+        drain_accumulator<NCOLS, kS32Out, kStageWide>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
+                                                      stage, lane);
+    }
+    else if (tp.mode == kStageGeneric)
+    {
+        drain_accumulator<NCOLS, kS32Out, kStageGeneric>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS,
+                                                         row_term, stage, lane);
     }
     else
     {
-        drain_accumulator<NCOLS, kS32Out, false>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                 stage, lane);
+        drain_accumulator<NCOLS, kS32Out, kStageFast>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
+                                                      stage, lane);
     }
 }
 
@@ -880,6 +968,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t  aph = 0;
         bool      ok = true;
         int       ti = 0;
+        int       filled_n0 = -1;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti)
         {
             if (!epi_barrier_and(ok))
@@ -888,8 +977,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const int m0 = (tile % num_m_blocks) * BLOCK_M;
             const int n0 = (tile / num_m_blocks) * BLOCK_N;
-            fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
-            epi_barrier();
+            if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
+            {
+                fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+                filled_n0 = n0;
+                epi_barrier();
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok)
             {
@@ -1161,6 +1254,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t  aph = 0;
         bool      ok = true;
         int       ti = 0;
+        int       filled_n0 = -1;
         for (int tile = first_tile; tile < num_tiles; tile += tile_stride, ++ti)
         {
             if (!epi_barrier_and(ok))
@@ -1169,8 +1263,12 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const int m0 = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
             const int n0 = (tile / num_m_blocks) * BLOCK_N;
-            fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
-            epi_barrier();
+            if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
+            {
+                fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+                filled_n0 = n0;
+                epi_barrier();
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok)
             {
@@ -1449,6 +1547,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         int       as = 0;
         uint32_t  aph = 0;
         bool      ok = true;
+        int       filled_n0 = -1;
         for (int ti = 0; ti < my_tiles; ++ti)
         {
             if (!epi_barrier_and(ok))
@@ -1458,8 +1557,12 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
             const int m0   = (tile % num_m_blocks) * BLOCK_M;
             const int n0   = (tile / num_m_blocks) * BLOCK_N;
-            fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
-            epi_barrier();
+            if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
+            {
+                fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+                filled_n0 = n0;
+                epi_barrier();
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok)
             {
@@ -1568,7 +1671,10 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 
 void fill_extra_dst(TileParams &tp, const GemmOperands &op)
 {
-    tp.n_extra = op.n_extra_dst;
+    tp.residual   = static_cast<const uint8_t *>(op.residual);
+    tp.res_floor4 = static_cast<uint32_t>(op.res_floor & 0xff) * 0x01010101u;
+    tp.res_cap4   = static_cast<uint32_t>(op.res_cap & 0xff) * 0x01010101u;
+    tp.n_extra    = op.n_extra_dst;
     for (int i = 0; i < kMaxExtraDst; ++i)
     {
         tp.extra_dst[i] = i < op.n_extra_dst ? static_cast<uint8_t *>(op.extra_dst[i]) : nullptr;
@@ -1577,7 +1683,7 @@ void fill_extra_dst(TileParams &tp, const GemmOperands &op)
 
 uint64_t extra_dst_bits(const GemmOperands &op)
 {
-    uint64_t bits = 0;
+    uint64_t bits = reinterpret_cast<uintptr_t>(op.residual);
     for (int i = 0; i < op.n_extra_dst; ++i)
     {
         bits |= reinterpret_cast<uintptr_t>(op.extra_dst[i]);
@@ -1652,7 +1758,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
     tp.status  = ctx->d_status;
-    tp.generic = op.generic_stage ? 1 : 0;
+    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
@@ -1689,7 +1795,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
                (static_cast<uint32_t>(P::BLOCK_N >> 3) << 17) | (static_cast<uint32_t>((2 * BLOCK_M) >> 4) << 24);
     tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
     tp.status  = ctx->d_status;
-    tp.generic = op.generic_stage ? 1 : 0;
+    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
     const int tiles    = ((op.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((op.N + P::BLOCK_N - 1) / P::BLOCK_N);
     const int pairs    = ctx->sm_count / 2;
@@ -1740,9 +1846,9 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
-    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
+    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
     tp.status  = ctx->d_status;
-    tp.generic = op.generic_stage ? 1 : 0;
+    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
     ConvGeom cg;
     cg.src   = static_cast<const uint8_t *>(cv.src);
@@ -1769,7 +1875,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
 }
 } // namespace
 
-bool gemmlowp_tcgen05_supported(const GemmOperands &op)
+bool CUGL_TC_NAME(gemmlowp_tcgen05_supported)(const GemmOperands &op)
 {
     if (op.M <= 0 || op.N <= 0 || op.K <= 0)
     {
@@ -1781,16 +1887,16 @@ bool gemmlowp_tcgen05_supported(const GemmOperands &op)
 }
 
 // The SM-pair kernel pays off once a tile spans both halves: more than 128 rows and more than 128 columns.
-bool gemmlowp_tcgen05_uses_pair(const GemmOperands &op)
+bool CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(const GemmOperands &op)
 {
     return op.N > 128 && op.M > 128;
 }
 
-cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                     bool allow_pair)
 {
     const bool s32 = ep.stage == CUGL_STAGE_NONE;
-    if (allow_pair && gemmlowp_tcgen05_uses_pair(op))
+    if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
     {
         return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);
     }
@@ -1808,7 +1914,7 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
 
 namespace cugl
 {
-bool gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands &cv)
+bool CUGL_TC_NAME(gemmlowp_conv_tcgen05_supported)(const GemmOperands &op, const ConvOperands &cv)
 {
     const uint64_t bits = reinterpret_cast<uintptr_t>(cv.src) | reinterpret_cast<uintptr_t>(cv.pad) |
                           reinterpret_cast<uintptr_t>(op.bt) | static_cast<uint64_t>(op.ldbt);
@@ -1819,7 +1925,7 @@ bool gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands 
            get_encode_fn() != nullptr;
 }
 
-cugl_status launch_gemmlowp_conv_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+cugl_status CUGL_TC_NAME(launch_gemmlowp_conv_tcgen05)(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                          const ConvOperands &cv)
 {
     if (ep.stage == CUGL_STAGE_NONE)

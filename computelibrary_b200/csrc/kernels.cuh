@@ -42,6 +42,13 @@ struct GemmOperands
     void       *extra_dst[7]; // tensor-core kernels only: further destinations that receive the same output
     int         n_extra_dst;  //   (peer GPUs' buffers in the push all-gather), same ldd as dst
     bool        generic_stage; // some shift is negative or some multiplier is INT32_MIN (decided on the host)
+    bool        wide_stage;    // every shift in [2, 31], every multiplier in [0, 2^31), no row-sum term: the
+                               // requantisation can use the one-multiply form (kStageWide)
+    int         epi_warps;     // tensor-core kernels: 4 or 8 forces that build, anything else lets the dispatcher choose
+    // tensor-core kernels, 8-bit unsigned output only: dst = min(max(min(out + residual, 255), res_floor), res_cap)
+    // with residual an [M][ldd] byte matrix (the fused residual addition of a convolution), or nullptr
+    const void *residual;
+    int         res_floor, res_cap;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).
@@ -58,6 +65,21 @@ bool        gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOp
 // op.a / op.lda are unused: the A tile comes from cv.src.  M = B*Ho*Wo, K = kh*kw*C.
 cugl_status launch_gemmlowp_conv_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                          const ConvOperands &cv);
+// the two builds behind the dispatcher (four / eight epilogue warps)
+bool        gemmlowp_conv_tcgen05_supported_epi4(const GemmOperands &op, const ConvOperands &cv);
+bool        gemmlowp_conv_tcgen05_supported_epi8(const GemmOperands &op, const ConvOperands &cv);
+cugl_status launch_gemmlowp_conv_tcgen05_epi4(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                              const ConvOperands &cv);
+cugl_status launch_gemmlowp_conv_tcgen05_epi8(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                              const ConvOperands &cv);
+bool        gemmlowp_tcgen05_supported_epi4(const GemmOperands &op);
+bool        gemmlowp_tcgen05_supported_epi8(const GemmOperands &op);
+bool        gemmlowp_tcgen05_uses_pair_epi4(const GemmOperands &op);
+bool        gemmlowp_tcgen05_uses_pair_epi8(const GemmOperands &op);
+cugl_status launch_gemmlowp_tcgen05_epi4(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                         bool allow_pair);
+cugl_status launch_gemmlowp_tcgen05_epi8(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                         bool allow_pair);
 
 // Generic CUDA-core kernel: any shape, stride and alignment.
 cugl_status launch_gemmlowp_simt(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep);
@@ -68,4 +90,8 @@ bool        gemmlowp_tcgen05_uses_pair(const GemmOperands &op);
 // allow_pair = false keeps to the one-CTA kernels (testing aid; all variants must agree bit for bit).
 cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                     bool allow_pair = true);
+// QASYMM8 addition: true when the oracle's result equals min(max(min(a + b, 255), floor), cap) for every byte pair
+// (proved by enumeration on the host, remembered per parameter set).
+bool classify_add(float a_scale, int a_zp, float b_scale, int b_zp, float o_scale, int o_zp, int act, float act_a,
+                  float act_b, int *floor_out, int *cap_out);
 } // namespace cugl

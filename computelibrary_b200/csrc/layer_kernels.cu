@@ -8,6 +8,12 @@
 // maximum) the 256 possible results are computed once per block into shared memory with that same
 // arithmetic and the kernel becomes a table look-up.
 #include "common.cuh"
+#include "kernels.cuh"
+
+#include <cmath>
+#include <cstring>
+#include <map>
+#include <mutex>
 
 namespace cugl
 {
@@ -149,6 +155,35 @@ __global__ void __launch_bounds__(kThreads)
     for (int64_t i = (nv << 4) + tid; i < n; i += nth)
     {
         dst[i] = static_cast<uint8_t>(add_byte(a[i], b[i], ia, ib, o, post));
+    }
+}
+
+// Saturating form of the addition: for many quantizations (always when the three scales and zero points are
+// equal, as in a residual network whose tensors share one quantization) the oracle's result over all 65536
+// byte pairs is exactly min(max(min(a + b, 255), floor), cap).  The host proves that by enumeration
+// (classify_add, below) and this kernel then needs three byte-parallel instructions per four elements.
+__global__ void __launch_bounds__(kThreads)
+    add_saturating_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ dst,
+                          int64_t n, bool vec, uint32_t floor4, uint32_t cap4)
+{
+    const int64_t tid = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int64_t nth = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    const int64_t nv  = vec ? (n >> 4) : 0;
+    for (int64_t i = tid; i < nv; i += nth)
+    {
+        const uint4 va = __ldg(reinterpret_cast<const uint4 *>(a) + i);
+        const uint4 vb = __ldg(reinterpret_cast<const uint4 *>(b) + i);
+        uint4       r;
+        r.x = __vminu4(__vmaxu4(__vaddus4(va.x, vb.x), floor4), cap4);
+        r.y = __vminu4(__vmaxu4(__vaddus4(va.y, vb.y), floor4), cap4);
+        r.z = __vminu4(__vmaxu4(__vaddus4(va.z, vb.z), floor4), cap4);
+        r.w = __vminu4(__vmaxu4(__vaddus4(va.w, vb.w), floor4), cap4);
+        reinterpret_cast<uint4 *>(dst)[i] = r;
+    }
+    for (int64_t i = (nv << 4) + tid; i < n; i += nth)
+    {
+        const uint32_t v = min(static_cast<uint32_t>(a[i]) + b[i], 255u);
+        dst[i]           = static_cast<uint8_t>(min(max(v, floor4 & 0xffu), cap4 & 0xffu));
     }
 }
 
@@ -294,6 +329,97 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// Host copy of the oracle arithmetic (same expressions, evaluated by the host compiler without contraction:
+// x86-64 baseline has no fused multiply-add) used to classify an addition.
+inline float h_dequantize(int q, float scale, int zp)
+{
+    return static_cast<float>(q - zp) * scale;
+}
+inline int h_quantize_u8(float v, float scale, int zp)
+{
+    const long q = lroundf(v / scale) + zp;
+    return static_cast<int>(q < 0 ? 0 : (q > 255 ? 255 : q));
+}
+inline float h_activate(float x, int act, float a, float b)
+{
+    switch (act)
+    {
+        case CUGL_ACT_RELU:
+            return x > 0.f ? x : 0.f;
+        case CUGL_ACT_BOUNDED_RELU:
+        {
+            const float t = x > 0.f ? x : 0.f;
+            return t < a ? t : a;
+        }
+        case CUGL_ACT_LU_BOUNDED_RELU:
+        {
+            const float t = x > b ? x : b;
+            return t < a ? t : a;
+        }
+        default:
+            return x;
+    }
+}
+} // namespace
+
+// True when act(quantize(dequantize(a) + dequantize(b))) == min(max(min(a + b, 255), floor), cap) for all 65536
+// byte pairs; floor and cap are returned.  Results are remembered per parameter set.
+bool classify_add(float a_scale, int a_zp, float b_scale, int b_zp, float o_scale, int o_zp, int act, float act_a,
+                  float act_b, int *floor_out, int *cap_out)
+{
+    struct Key
+    {
+        float as, bs, os, aa, ab;
+        int   az, bz, oz, act;
+        bool  operator<(const Key &o) const
+        {
+            return std::memcmp(this, &o, sizeof(Key)) < 0;
+        }
+    };
+    struct Form
+    {
+        bool saturating;
+        int  floor, cap;
+    };
+    static std::mutex          mu;
+    static std::map<Key, Form> cache;
+    Key                        key;
+    std::memset(&key, 0, sizeof(key));
+    key.as = a_scale, key.bs = b_scale, key.os = o_scale, key.aa = act_a, key.ab = act_b;
+    key.az = a_zp, key.bz = b_zp, key.oz = o_zp, key.act = act;
+    std::lock_guard<std::mutex> lock(mu);
+    auto                        it = cache.find(key);
+    if (it == cache.end())
+    {
+        auto eval = [&](int qa, int qb)
+        {
+            const double s = static_cast<double>(h_dequantize(qa, a_scale, a_zp)) + static_cast<double>(h_dequantize(qb, b_scale, b_zp));
+            const int    q = h_quantize_u8(static_cast<float>(s), o_scale, o_zp);
+            return act == CUGL_ACT_NONE ? q : h_quantize_u8(h_activate(h_dequantize(q, o_scale, o_zp), act, act_a, act_b), o_scale, o_zp);
+        };
+        Form f{true, eval(0, 0), eval(255, 255)};
+        for (int qa = 0; qa < 256 && f.saturating; ++qa)
+        {
+            for (int qb = 0; qb < 256; ++qb)
+            {
+                const int sum  = qa + qb > 255 ? 255 : qa + qb;
+                const int want = sum < f.floor ? f.floor : (sum > f.cap ? f.cap : sum);
+                if (eval(qa, qb) != want)
+                {
+                    f.saturating = false;
+                    break;
+                }
+            }
+        }
+        it = cache.emplace(key, f).first;
+    }
+    *floor_out = it->second.floor;
+    *cap_out   = it->second.cap;
+    return it->second.saturating;
+}
+
+namespace
+{
 int grid_for(int64_t work_items, int sm_count)
 {
     const int64_t blocks = (work_items + kThreads - 1) / kThreads;
@@ -433,6 +559,14 @@ extern "C"
         }
         if (n == 0) return CUGL_SUCCESS;
         const bool vec = aligned16(d_a) && aligned16(d_b) && aligned16(d_dst);
+        int        floor_q = 0, cap_q = 255;
+        if (classify_add(a_scale, a_zp, b_scale, b_zp, o_scale, o_zp, activation, act_a, act_b, &floor_q, &cap_q))
+        {
+            add_saturating_kernel<<<grid_for((n + 15) / 16, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(d_a), static_cast<const uint8_t *>(d_b), static_cast<uint8_t *>(d_dst), n,
+                vec, static_cast<uint32_t>(floor_q) * 0x01010101u, static_cast<uint32_t>(cap_q) * 0x01010101u);
+            return check_cuda(ctx, cudaGetLastError(), "add_saturating_kernel");
+        }
         add_kernel<<<grid_for((n + 15) / 16, ctx->sm_count), kThreads, 0, ctx->stream>>>(
             static_cast<const uint8_t *>(d_a), static_cast<const uint8_t *>(d_b), static_cast<uint8_t *>(d_dst), n, vec,
             QInfo{a_scale, a_zp}, QInfo{b_scale, b_zp}, QInfo{o_scale, o_zp}, activation, act_a, act_b);

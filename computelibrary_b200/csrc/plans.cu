@@ -42,6 +42,8 @@ struct GemmCore
     bool          force_simt = false;
     bool          allow_pair = true; // SM-pair (cta_group::2) kernel permitted
     bool          generic_stage = false; // a left shift or an INT32_MIN multiplier is present
+    bool          wide_stage    = false; // shifts in [2, 31], multipliers in [0, 2^31), no row-sum term
+    int           epi_warps     = 0;     // 4 / 8 force that build of the tensor-core kernels, 0 = automatic
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
@@ -60,6 +62,8 @@ struct GemmCore
     cugl_status upload_stage_vectors(const int32_t *h_mults, const int32_t *h_shifts)
     {
         generic_stage = !per_channel && (shift < 0 || mult == INT32_MIN);
+        wide_stage    = stage == CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT && b_off == 0 &&
+                     (per_channel || (shift >= 2 && shift <= 31 && mult >= 0));
         if (!per_channel)
         {
             return CUGL_SUCCESS;
@@ -67,6 +71,7 @@ struct GemmCore
         for (int i = 0; i < N; ++i)
         {
             generic_stage = generic_stage || h_shifts[i] < 0 || h_mults[i] == INT32_MIN;
+            wide_stage    = wide_stage && h_shifts[i] >= 2 && h_shifts[i] <= 31 && h_mults[i] >= 0;
         }
         if (d_mults == nullptr)
         {
@@ -130,7 +135,8 @@ struct GemmCore
 
     // rows x K product against B copy b_copy.
     cugl_status gemm(const void *d_a, int64_t lda, int rows, void *d_dst, int64_t ldd, const int32_t *d_bias,
-                     int b_copy, int rowsum_off, void *const *extra_dst = nullptr, int n_extra = 0) const
+                     int b_copy, int rowsum_off, void *const *extra_dst = nullptr, int n_extra = 0,
+                     const void *d_residual = nullptr, int res_floor = 0, int res_cap = 255) const
     {
         GemmOperands op{};
         op.a        = d_a;
@@ -145,15 +151,21 @@ struct GemmCore
         op.a_signed = a_signed;
         op.b_signed = b_signed;
         op.generic_stage = generic_stage;
+        op.wide_stage    = wide_stage;
+        op.epi_warps     = epi_warps;
         op.n_extra_dst   = n_extra;
+        op.residual      = d_residual;
+        op.res_floor     = res_floor;
+        op.res_cap       = res_cap;
         for (int i = 0; i < n_extra; ++i)
         {
             op.extra_dst[i] = extra_dst[i];
         }
-        if (n_extra > 0 && !uses_tcgen05(op))
+        if ((n_extra > 0 || d_residual != nullptr) && !uses_tcgen05(op))
         {
             return fail(ctx, CUGL_UNSUPPORTED_CONFIG,
-                        "several destinations need the tensor-core kernel (16-byte aligned A with 16-byte row pitch)");
+                        "several destinations or a fused residual need the tensor-core kernel (16-byte aligned A "
+                        "with 16-byte row pitch)");
         }
         if (b_off != 0)
         {
@@ -502,8 +514,20 @@ extern "C"
         {
             return "simt";
         }
-        op.M = plan->collapse_batch ? plan->desc.M * plan->desc.batch : plan->desc.M;
+        op.M         = plan->collapse_batch ? plan->desc.M * plan->desc.batch : plan->desc.M;
+        op.epi_warps = plan->core.epi_warps;
         return (plan->core.allow_pair && gemmlowp_tcgen05_uses_pair(op)) ? "tcgen05_2cta" : "tcgen05";
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps)
+    {
+        if (plan == nullptr || (warps != 0 && warps != 4 && warps != 8))
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
+                        "cugl_gemmlowp_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4 or 8");
+        }
+        plan->core.epi_warps = warps;
+        return CUGL_SUCCESS;
     }
 
     cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on)
@@ -648,6 +672,9 @@ struct cugl_conv_plan
     int      eC = 0, eW = 0, eH = 0, ekw = 0, ekh = 0, esx = 1, esy = 1, epl = 0, ept = 0;
     int      fold_oy = 0, fold_ox = 0;
     uint8_t *d_fold = nullptr; // [B][eH][eW][16]
+    // fused residual addition (cugl_conv2d_plan_set_residual): clamp bounds of the saturating form
+    bool residual_set = false;
+    int  res_floor = 0, res_cap = 255;
     bool                 prepared    = false;
     void                *d_src_stage = nullptr, *d_dst_stage = nullptr;
     int32_t             *d_bias_stage = nullptr;
@@ -853,7 +880,62 @@ extern "C"
         return CUGL_SUCCESS;
     }
 
+    cugl_status cugl_conv2d_plan_set_residual(cugl_conv_plan *plan, float conv_out_scale, float residual_scale,
+                                              int32_t residual_zero_point, float dst_scale, int32_t dst_zero_point,
+                                              int32_t activation, float act_a, float act_b)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_residual: NULL plan");
+        }
+        if (plan->desc.src_dtype != CUGL_U8)
+        {
+            return fail(plan->ctx, CUGL_UNSUPPORTED_CONFIG, "fused residual addition needs a QASYMM8 (uint8) output");
+        }
+        if (!(conv_out_scale > 0.f) || !(residual_scale > 0.f) || !(dst_scale > 0.f) || activation < CUGL_ACT_NONE ||
+            activation > CUGL_ACT_LU_BOUNDED_RELU)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_residual: bad scale or activation");
+        }
+        int lo = 0, hi = 255;
+        if (!classify_add(conv_out_scale, plan->desc.dst_zero_point, residual_scale, residual_zero_point, dst_scale,
+                          dst_zero_point, activation, act_a, act_b, &lo, &hi))
+        {
+            return fail(plan->ctx, CUGL_UNSUPPORTED_CONFIG,
+                        "this addition is not a saturating byte addition for every input pair: run cugl_add_qasymm8 "
+                        "after the convolution instead");
+        }
+        plan->residual_set = true;
+        plan->res_floor    = lo;
+        plan->res_cap      = hi;
+        return CUGL_SUCCESS;
+    }
+
+    static cugl_status conv2d_run_impl(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias,
+                                       const void *d_residual, void *d_dst);
+
     cugl_status cugl_conv2d_run(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias, void *d_dst)
+    {
+        return conv2d_run_impl(plan, d_src, d_bias, nullptr, d_dst);
+    }
+
+    cugl_status cugl_conv2d_run_residual(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias,
+                                         const void *d_residual, void *d_dst)
+    {
+        if (plan == nullptr || d_residual == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run_residual: NULL argument");
+        }
+        if (!plan->residual_set)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                        "cugl_conv2d_run_residual: call cugl_conv2d_plan_set_residual first");
+        }
+        return conv2d_run_impl(plan, d_src, d_bias, d_residual, d_dst);
+    }
+
+    static cugl_status conv2d_run_impl(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias,
+                                       const void *d_residual, void *d_dst)
     {
         if (plan == nullptr || d_src == nullptr || d_dst == nullptr)
         {
@@ -890,7 +972,12 @@ extern "C"
             op.a_signed      = c.a_signed;
             op.b_signed      = c.b_signed;
             op.generic_stage = c.generic_stage;
+            op.wide_stage    = c.wide_stage;
+            op.epi_warps     = c.epi_warps;
             op.n_extra_dst   = 0;
+            op.residual      = d_residual;
+            op.res_floor     = plan->res_floor;
+            op.res_cap       = plan->res_cap;
             ConvOperands cv{};
             cv.src    = d_src;
             cv.pad    = plan->d_pad;
@@ -928,7 +1015,8 @@ extern "C"
             a   = plan->d_cols;
             lda = plan->Kp;
         }
-        return plan->core.gemm(a, lda, static_cast<int>(plan->M), d_dst, d.OFM, d.has_bias ? d_bias : nullptr, 0, 0);
+        return plan->core.gemm(a, lda, static_cast<int>(plan->M), d_dst, d.OFM, d.has_bias ? d_bias : nullptr, 0, 0,
+                               nullptr, 0, d_residual, plan->res_floor, plan->res_cap);
     }
 
     cugl_status cugl_conv2d_run_host(cugl_conv_plan *plan, const void *h_src, const int32_t *h_bias, void *h_dst)
@@ -968,6 +1056,17 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_allow_implicit: NULL plan");
         }
         plan->allow_implicit = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_epilogue_warps(cugl_conv_plan *plan, int warps)
+    {
+        if (plan == nullptr || (warps != 0 && warps != 4 && warps != 8))
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
+                        "cugl_conv2d_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4 or 8");
+        }
+        plan->core.epi_warps = warps;
         return CUGL_SUCCESS;
     }
 

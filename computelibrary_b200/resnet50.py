@@ -104,9 +104,12 @@ class ResNet50:
     """One GPU's copy of the network: plans, device weights and activation buffers for a fixed batch."""
 
     def __init__(self, ctx: capi.Context, batch: int, params=None, image: int = 224, num_classes: int = 1000,
-                 seed: int = 1, nodes=None):
+                 seed: int = 1, nodes=None, fuse_residual: bool = True):
+        """``fuse_residual``: compute every ``add_relu`` node inside the epilogue of the convolution that produces
+        its right-hand input (cugl_conv2d_run_residual); the convolution's own buffer is then never written."""
         import torch
         self.ctx, self.batch = ctx, batch
+        self.fuse_residual = fuse_residual
         self.nodes = nodes if nodes is not None else build_graph(image, num_classes)
         self.params = params if params is not None else synthetic_params(self.nodes, seed)
         self.image = self.nodes[0]["in_shape"][0]
@@ -117,7 +120,30 @@ class ResNet50:
         for n in self.nodes:
             H, W, Cc = n["out_shape"]
             self.bufs[n["name"]] = torch.empty((batch, H, W, Cc), dtype=torch.uint8, device=dev)
-        for n in self.nodes:
+        # a convolution whose only consumer is an add_relu node can absorb it, provided the other input of the
+        # addition is produced earlier in the list (the shortcut convolution is moved ahead of it for that)
+        order = list(self.nodes)
+        self.fused = {}
+        if fuse_residual:
+            consumers = {}
+            for n in order:
+                for s in n["inputs"]:
+                    consumers.setdefault(s, []).append(n["name"])
+            by_name = {n["name"]: n for n in order}
+            for add in [n for n in order if n["op"] == "add_relu"]:
+                left, right = add["inputs"]
+                conv = by_name.get(right)
+                if conv is None or conv["op"] != "conv" or consumers[right] != [add["name"]]:
+                    continue
+                li, ci = (order.index(by_name[left]) if left in by_name else -1), order.index(conv)
+                if li > ci:   # shortcut after the convolution: run it first (it does not depend on conv)
+                    ln = order.pop(li)
+                    order.insert(ci, ln)
+                self.fused[conv["name"]] = add
+        self.order = order
+        for n in order:
+            if n["op"] == "add_relu" and any(f is n for f in self.fused.values()):
+                continue
             self._add_step(n, torch, dev)
         ctx.sync()
 
@@ -138,8 +164,21 @@ class ResNet50:
             plan.prepare(d_w)
             self._keep += [plan, d_b]
             is_input = srcs[0] is None
-            self.steps.append((lambda x, plan=plan, d_b=d_b, dst=dst, s=srcs[0], is_input=is_input:
-                               plan.run(x if is_input else s, d_b, dst), plan, n))
+            add = self.fused.get(n["name"])
+            if add is not None:
+                try:
+                    plan.set_residual(ACT_Q[0], ACT_Q, ACT_Q, act=capi.ACT_RELU)
+                except capi.CuglError:
+                    add = None   # not a saturating addition for these quantizations: keep the separate kernel
+                    del self.fused[n["name"]]
+            if add is not None:
+                res = self.bufs[[s for s in add["inputs"] if s != n["name"]][0]]
+                out = self.bufs[add["name"]]
+                self.steps.append((lambda x, plan=plan, d_b=d_b, out=out, s=srcs[0], res=res:
+                                   plan.run_residual(s, d_b, res, out), plan, dict(n, name=n["name"] + "+add")))
+            else:
+                self.steps.append((lambda x, plan=plan, d_b=d_b, dst=dst, s=srcs[0], is_input=is_input:
+                                   plan.run(x if is_input else s, d_b, dst), plan, n))
         elif n["op"] == "maxpool":
             desc = capi.make_pool_desc(B, H, W, Cc, capi.POOL_MAX, (n["k"],) * 2, (n["stride"],) * 2, n["pad"], ACT_Q, ACT_Q,
                                        exclude_padding=True)

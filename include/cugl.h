@@ -208,6 +208,10 @@ CUGL_API cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on)
 CUGL_API cugl_status cugl_gemmlowp_plan_allow_pair_kernel(cugl_gemm_plan *plan, int on);
 /* Number of kernels one cugl_gemmlowp_run of this plan launches. */
 CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
+/* The tensor-core kernels exist with four and with eight epilogue warps; the library picks by K (short K:
+ * eight).  warps = 4 or 8 forces one build, 0 restores the automatic choice (testing / measurement aid: the
+ * results are identical). */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps);
 
 /* Fused GEMMLowp that allocates nothing.  No counterpart in the reference: Compute Library always lets the
  * function object own its workspace.  For callers that cannot call cudaMalloc -- a serving loop whose device
@@ -309,6 +313,23 @@ CUGL_API int  cugl_conv2d_plan_launches(const cugl_conv_plan *plan);
 CUGL_API const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan);
 /* on = 0 forces the explicit im2col lowering (testing aid: both lowerings must agree bit for bit). */
 CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on);
+/* as cugl_gemmlowp_plan_set_epilogue_warps */
+CUGL_API cugl_status cugl_conv2d_plan_set_epilogue_warps(cugl_conv_plan *plan, int warps);
+/* Fused residual addition: dst = act(quantize(dequantize(conv) + dequantize(residual))) computed in the epilogue
+ * of the convolution, i.e. NEGEMMConvolutionLayer followed by NEArithmeticAddition (ConvertPolicy::SATURATE)
+ * and NEActivationLayer (arm_compute/runtime/NEON/functions/NEArithmeticAddition.h:43-109) without the
+ * intermediate tensors.  conv_out_scale with the plan's dst_zero_point is the quantization the convolution
+ * requantizes to; dst_scale / dst_zero_point that of the sum.  QASYMM8 only.  The library enumerates all 65536
+ * input pairs with the reference arithmetic and accepts the configuration when the addition is a saturating
+ * byte addition followed by a clamp (always so when the three quantizations are equal); otherwise
+ * CUGL_UNSUPPORTED_CONFIG is returned and the caller runs cugl_add_qasymm8 after cugl_conv2d_run. */
+CUGL_API cugl_status cugl_conv2d_plan_set_residual(cugl_conv_plan *plan, float conv_out_scale, float residual_scale,
+                                                   int32_t residual_zero_point, float dst_scale,
+                                                   int32_t dst_zero_point, int32_t activation, float act_a,
+                                                   float act_b);
+/* residual and dst are [B][Ho][Wo][OFM]; they may be the same buffer. */
+CUGL_API cugl_status cugl_conv2d_run_residual(cugl_conv_plan *plan, const void *d_src, const int32_t *d_bias,
+                                              const void *d_residual, void *d_dst);
 
 /* ------------------------------------------------------------------------------------------------
  * QASYMM8 layers between the convolutions of a quantized network (uint8, NHWC).  Each one computes what

@@ -150,3 +150,42 @@ def test_folded_stride2_conv_vs_oracle(ctx, port, geom, in_zp):
         got = gpu_conv(ctx, src, wgt, bias, (2, 2), (p, p, p, p), in_zp, 0, mult, shift, 0, 0, 255, implicit=implicit,
                        want_kernel="implicit" if implicit else "im2col")
         assert np.array_equal(got, want), (implicit, np.argwhere(got != want)[:5])
+
+
+@pytest.mark.parametrize("geom", [(1, 1, 0, 64, 256), (3, 1, 1, 32, 40), (3, 2, 1, 16, 130), (1, 1, 0, 24, 20)])
+def test_fused_residual_addition(ctx, port, geom):
+    """cugl_conv2d_run_residual = convolution, QASYMM8 addition and activation in one kernel: against the oracle's
+    three separate layers, on the implicit, the plain-GEMM and (C = 24) the explicit im2col / SIMT-free lowerings."""
+    import torch
+    k, s, p, Cc, OFM = geom
+    rng = np.random.default_rng(k * 100 + Cc + OFM)
+    src = q8_uniform(rng, (2, 14, 15, Cc), np.uint8)
+    wgt = q8_uniform(rng, (OFM, k, k, Cc), np.int8, -127, 127)
+    bias = rng.integers(-3000, 3001, OFM).astype(np.int32)
+    ws = (np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)) / np.sqrt(k * k * Cc) * 8).astype(np.float32)
+    q = (0.05, 0)
+    mult, shift = f32_mults(port, q[0], ws, q[0])
+    conv = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), q[1], 0, mult, shift, q[1], 0, 255)
+    res = q8_uniform(rng, conv.shape, np.uint8)
+    for act, a in (("relu", 0.0), ("bounded_relu", 6.0)):
+        want = port.activation_qasymm8(port.add_qasymm8(conv, res, q, q, q), act, a, 0.0, q, q)
+        desc, keep = capi.make_conv_desc(2, 14, 15, Cc, OFM, k, k, (s, s), (p, p, p, p), (1, 1), capi.U8, capi.S8, q[1], 0,
+                                         multipliers=mult, shifts=shift, dst_zp=q[1], min_bound=0, max_bound=255)
+        plan = capi.ConvPlan(ctx, desc, keep)
+        plan.set_residual(q[0], q, q, act=capi.ACT_RELU if act == "relu" else capi.ACT_BOUNDED_RELU, act_a=a)
+        plan.prepare(torch.from_numpy(wgt.view(np.uint8)).cuda())
+        d_res = torch.from_numpy(res).cuda()
+        d_dst = torch.empty(conv.shape, dtype=torch.uint8, device="cuda")
+        plan.run_residual(torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda(), d_res, d_dst)
+        ctx.sync()
+        assert np.array_equal(d_dst.cpu().numpy(), want), act
+        # in place: the residual buffer is also the destination
+        plan.run_residual(torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda(), d_res, d_res)
+        ctx.sync()
+        assert np.array_equal(d_res.cpu().numpy(), want), act
+        plan.close()
+    # quantizations for which the addition is NOT a saturating byte addition are refused
+    plan = capi.ConvPlan(ctx, desc, keep)
+    with pytest.raises(capi.CuglError):
+        plan.set_residual(0.05, (0.03, 5), (0.07, 9))
+    plan.close()

@@ -254,3 +254,59 @@ def test_run_multi_destinations(ctx, port):
         assert np.array_equal(h[:, n0:n0 + n_local].view(np.int8), want)
         assert (h[:, :n0] == 0x11).all() and (h[:, n0 + n_local:] == 0x11).all()
     plan.close()
+
+
+@pytest.mark.parametrize("epi_warps", [4, 8])
+@pytest.mark.parametrize("shape", [(300, 256, 64), (257, 96, 128), (130, 40, 2048), (515, 520, 320), (128, 64, 16)])
+def test_epilogue_builds_and_stage_encodings(ctx, port, shape, epi_warps):
+    """Both builds of the tensor-core kernels (four / eight epilogue warps) on all three encodings of the output
+    stage: shifts >= 2 with non-negative multipliers (one wide multiply-add per element), shifts 0 and 1 (two
+    half multiplies), and left shifts / INT32_MIN multipliers (the reference expression as written)."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K + epi_warps)
+    a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), np.int8, -127, 127)
+    bias = rng.integers(-20000, 20001, N).astype(np.int32)
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+    for lo_shift, hi_shift, label in [(2, 14, "wide"), (0, 6, "fast"), (-2, 5, "generic")]:
+        shift = rng.integers(lo_shift, hi_shift, N).astype(np.int32)
+        shift[0], shift[-1] = lo_shift, hi_shift - 1
+        want = port.gemmlowp_fused(a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8)
+        for pair in (True, False):
+            got, kern = gpu_gemmlowp(ctx, a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8, pair=pair,
+                                     epi_warps=epi_warps)
+            assert kern.startswith("tcgen05")
+            assert np.array_equal(got, want), (label, pair, np.argwhere(got != want)[:4])
+    # per-tensor wide encoding with a signed output and a lower bound above the type minimum
+    a8 = q8_uniform(rng, (M, K), np.int8)
+    got, _ = gpu_gemmlowp(ctx, a8, b, bias, 5, 0, 1759218688, 13, -3, -100, 90, np.int8, epi_warps=epi_warps)
+    assert np.array_equal(got, port.gemmlowp_fused(a8, b, bias, 5, 0, [1759218688], [13], -3, -100, 90, np.int8))
+    # asymmetric weights (row-sum term present): never the wide encoding
+    bu = q8_uniform(rng, (K, N), np.uint8)
+    got, _ = gpu_gemmlowp(ctx, a, bu, bias, -7, -9, 1099511552, 8, 10, 0, 255, np.uint8, epi_warps=epi_warps)
+    assert np.array_equal(got, port.gemmlowp_fused(a, bu, bias, -7, -9, [1099511552], [8], 10, 0, 255, np.uint8))
+
+
+def test_run_multi_destinations_eight_epilogue_warps(ctx, port):
+    """The staged multi-destination store of the eight-warp build (64-byte row segments), ragged N and M."""
+    import torch
+    rng = np.random.default_rng(22)
+    M, K, n_local, n_total, n0 = 301, 128, 400, 1200, 400
+    a, b = q8_uniform(rng, (M, K), np.int8), q8_uniform(rng, (K, n_local), np.int8, -127, 127)
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, n_local).astype(np.int32)
+    shift = rng.integers(5, 10, n_local).astype(np.int32)
+    want = port.gemmlowp_fused(a, b, None, 0, 0, mult, shift, 0, -128, 127, np.int8)
+    for warps in (4, 8):
+        desc, keep = capi.make_gemm_desc(M, n_local, K, capi.S8, capi.S8, capi.S8, 0, 0, multipliers=mult, shifts=shift,
+                                         min_bound=-128, max_bound=127, ldd=n_total)
+        plan = capi.GemmPlan(ctx, desc, keep)
+        plan.set_epilogue_warps(warps)
+        plan.prepare(torch.from_numpy(b.view(np.uint8)).cuda())
+        d_a = torch.from_numpy(a.view(np.uint8)).cuda()
+        bufs = [torch.full((M, n_total), 0x11, dtype=torch.uint8, device="cuda") for _ in range(2)]
+        plan.run_multi(d_a, None, [t.data_ptr() + n0 for t in bufs])
+        ctx.sync()
+        for t in bufs:
+            h = t.cpu().numpy()
+            assert np.array_equal(h[:, n0:n0 + n_local].view(np.int8), want), warps
+            assert (h[:, :n0] == 0x11).all() and (h[:, n0 + n_local:] == 0x11).all()
+        plan.close()
