@@ -134,6 +134,8 @@ _SIGNATURES = {
                                                 C.c_float]),
     "cugl_conv2d_run_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_set_channel_major": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_channel_major": (C.c_int, [_vp, C.c_int]),
     "cugl_pool2d_out_dims": (None, [C.POINTER(PoolDesc), _pi32, _pi32]),
     "cugl_pool2d_validate": (C.c_int, [C.POINTER(PoolDesc)]),
     "cugl_pool2d_nhwc": (C.c_int, [_vp, C.POINTER(PoolDesc), _vp, _vp]),
@@ -457,6 +459,9 @@ class GemmPlan:
     def set_epilogue_warps(self, warps: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_epilogue_warps(self.handle, int(warps)))
 
+    def set_channel_major(self, mode: int):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_channel_major(self.handle, int(mode)))
+
     def allow_pair_kernel(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_allow_pair_kernel(self.handle, int(on)))
 
@@ -548,6 +553,9 @@ class ConvPlan:
 
     def set_epilogue_warps(self, warps: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_epilogue_warps(self.handle, int(warps)))
+
+    def set_channel_major(self, mode: int):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_channel_major(self.handle, int(mode)))
 
     def allow_implicit(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_implicit(self.handle, int(on)))

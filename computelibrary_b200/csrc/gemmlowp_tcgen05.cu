@@ -371,6 +371,30 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
 constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2;
 
 template <int kMode>
+__device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t row_term, int32_t offset, int32_t lo,
+                                               int32_t hi)
+{
+    if (kMode == kStageWide)
+    {
+        const long long c64 = static_cast<long long>((static_cast<unsigned long long>(static_cast<uint32_t>(q.y)) << 32) |
+                                                     static_cast<uint32_t>(q.x));
+        const long long p   = static_cast<long long>(static_cast<int32_t>(v)) * q.z + c64;
+        const int32_t   t   = static_cast<int32_t>(p >> 32) >> q.w;
+        return max(__viaddmin_s32(t, offset, hi), lo);
+    }
+    const int32_t acc = static_cast<int32_t>(v) + q.x + row_term;
+    if (kMode == kStageGeneric)
+    {
+        return finalize(acc, q.y, q.z >> 8, q.z & 0xff, offset, lo, hi);
+    }
+    const int32_t  mh = __mulhi(acc, q.y);
+    const uint32_t ml = static_cast<uint32_t>(acc) * static_cast<uint32_t>(q.y);
+    const uint32_t d  = __funnelshift_l(ml, static_cast<uint32_t>(mh), 1);         // floor(acc*mult / 2^31)
+    const int32_t  t  = static_cast<int32_t>(d + static_cast<uint32_t>(q.z)) >> q.w; // round-half-up shift
+    return min(max(t + offset, lo), hi);
+}
+
+template <int kMode>
 __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 *col, int32_t row_term, int32_t offset,
                                                   int32_t lo, int32_t hi)
 {
@@ -378,31 +402,7 @@ __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 
 #pragma unroll
     for (int b = 0; b < 4; ++b)
     {
-        const int4 q = col[b];
-        if (kMode == kStageWide)
-        {
-            const long long c64 = static_cast<long long>((static_cast<unsigned long long>(static_cast<uint32_t>(q.y)) << 32) |
-                                                         static_cast<uint32_t>(q.x));
-            const long long p   = static_cast<long long>(static_cast<int32_t>(v[b])) * q.z + c64;
-            const int32_t   t   = static_cast<int32_t>(p >> 32) >> q.w;
-            r[b]                = max(__viaddmin_s32(t, offset, hi), lo);
-        }
-        else
-        {
-            const int32_t acc = static_cast<int32_t>(v[b]) + q.x + row_term;
-            if (kMode == kStageGeneric)
-            {
-                r[b] = finalize(acc, q.y, q.z >> 8, q.z & 0xff, offset, lo, hi);
-            }
-            else
-            {
-                const int32_t  mh = __mulhi(acc, q.y);
-                const uint32_t ml = static_cast<uint32_t>(acc) * static_cast<uint32_t>(q.y);
-                const uint32_t d  = __funnelshift_l(ml, static_cast<uint32_t>(mh), 1);         // floor(acc*mult / 2^31)
-                const int32_t  t  = static_cast<int32_t>(d + static_cast<uint32_t>(q.z)) >> q.w; // round-half-up shift
-                r[b]              = min(max(t + offset, lo), hi);
-            }
-        }
+        r[b] = requant_one<kMode>(v[b], col[b], row_term, offset, lo, hi);
     }
     const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
     const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
@@ -417,6 +417,10 @@ __device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, in
     {
         return;
     }
+#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 11 // row-major: no stores
+    if ((v[0] ^ v[1] ^ v[2] ^ v[3] ^ v[4] ^ v[5] ^ v[6] ^ v[7]) == 0x12345677u) drow[nc] = 1;
+    return;
+#endif
     const bool full = nc + 32 <= tp.N;
     if (kS32Out)
     {
@@ -471,11 +475,23 @@ __device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col
     }
     else
     {
+#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 12 // row-major: no arithmetic, no column terms
+#pragma unroll
+        for (int j = 0; j < 8; ++j) v[j] = v[4 * j] ^ v[4 * j + 1] ^ v[4 * j + 2] ^ v[4 * j + 3];
+#elif defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 14 // row-major: arithmetic with ONE column term per chunk
+        int4 qq[4] = {col[0], col[0], col[0], col[0]};
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+        {
+            v[j >> 2] = requant_pack4<kMode>(v + j, qq, row_term, ep.result_offset, ep.lo, ep.hi);
+        }
+#else
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
         {
             v[j >> 2] = requant_pack4<kMode>(v + j, col + j, row_term, ep.result_offset, ep.lo, ep.hi);
         }
+#endif
     }
 }
 
@@ -650,7 +666,37 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
     }
 }
 
-// per-column terms of a tile (see requant_pack4 for the two encodings)
+// the term of output channel n in the encoding of tp.mode (see requant_pack4)
+__device__ __forceinline__ int4 column_term(int n, const TileParams &tp, const EpilogueParams &ep)
+{
+    int4    q = make_int4(0, 0, 0, 0);
+    int32_t t = ep.k_term;
+    if (ep.colsum != nullptr) t += ep.a_off * __ldg(ep.colsum + n);
+    if (ep.bias != nullptr) t += __ldg(ep.bias + n);
+    const int32_t sh = ep.shifts != nullptr ? __ldg(ep.shifts + n) : ep.shift;
+    q.x              = t;
+    q.y              = ep.mults != nullptr ? __ldg(ep.mults + n) : ep.mult;
+    if (tp.mode == kStageGeneric)
+    {
+        q.z = max(sh, 0) | (max(-sh, 0) << 8);
+    }
+    else if (tp.mode == kStageFast)
+    {
+        q.z = static_cast<int32_t>((1u << sh) >> 1);
+        q.w = sh;
+    }
+    else
+    {
+        const long long c64 = static_cast<long long>(t) * q.y + (1ll << (30 + sh));
+        q.z                 = q.y;
+        q.x                 = static_cast<int32_t>(static_cast<uint32_t>(c64));
+        q.y                 = static_cast<int32_t>(c64 >> 32);
+        q.w                 = sh - 1;
+    }
+    return q;
+}
+
+// per-column terms of a tile
 template <int BLOCK_N>
 __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, const TileParams &tp,
                                                   const EpilogueParams &ep)
@@ -658,34 +704,145 @@ __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, c
     for (int c = et; c < BLOCK_N; c += kEpiThreads)
     {
         const int n = n0 + c;
-        int4      q = make_int4(0, 0, 0, 0);
-        if (n < tp.N)
+        s_col[c]    = n < tp.N ? column_term(n, tp, ep) : make_int4(0, 0, 0, 0);
+    }
+}
+
+// Channel-major epilogue.  The kernel was launched with the operand roles exchanged (weights on the 128-row
+// side, activations on the BLOCK_N side), so a tensor-memory LANE is an output channel and a tensor-memory
+// COLUMN an output row.  A thread then needs the output-stage term of ONE channel, held in four registers for
+// the whole tile, instead of a 16-byte shared-memory read per element -- that read (512 bytes per warp and
+// element column) is what bounds the row-major epilogue on short-K shapes.  The 32 lanes of a warp hold 32
+// consecutive channels of one output row: each store instruction writes one 32-byte segment of dst.
+//   tp.M = number of channels (dst columns), tp.N = number of rows of dst, tp.ldd = dst row pitch in bytes.
+template <bool kS32Out, int kMode>
+__device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const int4 q, const TileParams &tp,
+                                               const EpilogueParams &ep, int ch, int p0)
+{
+    if (ch >= tp.M || p0 >= tp.N)
+    {
+        return;
+    }
+    const int64_t base = static_cast<int64_t>(p0) * tp.ldd;
+    const int     np   = min(32, tp.N - p0);
+    if (kS32Out)
+    {
+        uint8_t *o = tp.dst + base + 4 * static_cast<int64_t>(ch);
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
         {
-            int32_t t = ep.k_term;
-            if (ep.colsum != nullptr) t += ep.a_off * __ldg(ep.colsum + n);
-            if (ep.bias != nullptr) t += __ldg(ep.bias + n);
-            const int32_t sh = ep.shifts != nullptr ? __ldg(ep.shifts + n) : ep.shift;
-            q.x              = t;
-            q.y              = ep.mults != nullptr ? __ldg(ep.mults + n) : ep.mult;
-            if (tp.mode == kStageGeneric)
-            {
-                q.z = max(sh, 0) | (max(-sh, 0) << 8);
-            }
-            else if (tp.mode == kStageFast)
-            {
-                q.z = static_cast<int32_t>((1u << sh) >> 1);
-                q.w = sh;
-            }
-            else
-            {
-                const long long c64 = static_cast<long long>(t) * q.y + (1ll << (30 + sh));
-                q.z                 = q.y;
-                q.x                 = static_cast<int32_t>(static_cast<uint32_t>(c64));
-                q.y                 = static_cast<int32_t>(c64 >> 32);
-                q.w                 = sh - 1;
-            }
+            if (j < np) *reinterpret_cast<int32_t *>(o + j * tp.ldd) = static_cast<int32_t>(v[j]) + q.x;
         }
-        s_col[c] = q;
+    }
+    else if (tp.residual != nullptr)
+    {
+        uint8_t       *o  = tp.dst + base + ch;
+        const uint8_t *r  = tp.residual + base + ch;
+        const int      fl = static_cast<int>(tp.res_floor4 & 0xffu), cp = static_cast<int>(tp.res_cap4 & 0xffu);
+        uint32_t       rs[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+        {
+            rs[j] = j < np ? static_cast<uint32_t>(__ldg(r + j * tp.ldd)) : 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+        {
+            const int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+            if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(min(max(min(y + static_cast<int>(rs[j]), 255), fl), cp));
+        }
+    }
+    else
+    {
+        uint8_t *o = tp.dst + base + ch;
+#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 1 // no stores (result consumed by an impossible branch)
+        int acc = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+        if (acc == 0x7fffffff) o[0] = 1;
+#elif defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 2 // no arithmetic
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+        {
+            if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(v[j]);
+        }
+#elif defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 3 // one store per chunk
+        int acc = 0;
+#pragma unroll
+        for (int j = 0; j < 32; ++j) acc += static_cast<int>(v[j]);
+        o[0] = static_cast<uint8_t>(acc);
+#else
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+        {
+            const int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+            if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(y);
+        }
+#endif
+    }
+}
+
+template <int NPIX, bool kS32Out, int kMode>
+__device__ __forceinline__ void drain_channel_major(uint32_t t_addr, const int4 q, const TileParams &tp,
+                                                    const EpilogueParams &ep, int ch, int p_first)
+{
+    static_assert((NPIX / 32) % 2 == 0 || NPIX == 32, "chunks are drained in pairs");
+    uint32_t va[32], vb[32];
+    tmem_ld_x32(t_addr, va);
+#pragma unroll 1
+    for (int c = 0; c < NPIX / 32; c += 2)
+    {
+        tmem_ld_wait();
+        if (c + 1 < NPIX / 32)
+        {
+            tmem_ld_x32(t_addr + (c + 1) * 32, vb);
+        }
+        store_chunk_cm<kS32Out, kMode>(va, q, tp, ep, ch, p_first + c * 32);
+        if (c + 1 < NPIX / 32)
+        {
+            tmem_ld_wait();
+            if (c + 2 < NPIX / 32)
+            {
+                tmem_ld_x32(t_addr + (c + 2) * 32, va);
+            }
+            store_chunk_cm<kS32Out, kMode>(vb, q, tp, ep, ch, p_first + (c + 1) * 32);
+        }
+    }
+}
+
+template <int BLOCK_N, bool kS32Out>
+__device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const TileParams &tp, const EpilogueParams &ep,
+                                                      int warp, int lane, int m0, int n0)
+{
+    constexpr int NPIX = BLOCK_N / (kEpiWarps / 4);
+    const int     quad = warp & 3;                // tensor-memory lane quarter this warp may read
+    const int     half = (warp - kFirstEpi) >> 2; // which share of the output rows
+    const int     ch   = m0 + quad * 32 + lane;
+    int4          q    = make_int4(0, 0, 0, 0);
+    if (ch < tp.M)
+    {
+        if (kS32Out)
+        {
+            q.x = ep.k_term + (ep.colsum != nullptr ? ep.a_off * __ldg(ep.colsum + ch) : 0); // offset terms only
+        }
+        else
+        {
+            q = column_term(ch, tp, ep);
+        }
+    }
+    const uint32_t t_addr = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NPIX;
+    const int      p0     = n0 + half * NPIX;
+    if (tp.mode == kStageWide && !kS32Out)
+    {
+        drain_channel_major<NPIX, kS32Out, kStageWide>(t_addr, q, tp, ep, ch, p0);
+    }
+    else if (tp.mode == kStageGeneric)
+    {
+        drain_channel_major<NPIX, kS32Out, kStageGeneric>(t_addr, q, tp, ep, ch, p0);
+    }
+    else
+    {
+        drain_channel_major<NPIX, kS32Out, kStageFast>(t_addr, q, tp, ep, ch, p0);
     }
 }
 
@@ -742,7 +899,11 @@ struct SmemPlan
     static constexpr int TMEM_COLS  = 2 * BLOCK_N;
 };
 
-template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
+// kCM (channel-major): the launcher has exchanged the operand roles -- "A" is the weight matrix, "B" the
+// activation matrix, tp.M the number of output channels and tp.N the number of output rows -- so the
+// accumulator holds the transposed output tile and epilogue_warp_tile_cm writes it (see there).  Tiles are then
+// ordered n-fastest, i.e. all row blocks of one channel block in turn.
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kCM>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                             const __grid_constant__ TileParams tp, const EpilogueParams ep)
@@ -827,8 +988,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 ktrace(tp.trace, ti, 2, kb);
                 const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
-                const int m0   = (tile % num_m_blocks) * BLOCK_M;
-                const int n0   = (tile / num_m_blocks) * BLOCK_N;
+                const int m0   = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
+                const int n0   = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
                 if (kb == 0) trace_event(tp.trace, ti, 0);
                 mbar_expect_tx(full_bar(st), P::STAGE);
 #pragma unroll
@@ -975,9 +1136,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 break;
             }
-            const int m0 = (tile % num_m_blocks) * BLOCK_M;
-            const int n0 = (tile / num_m_blocks) * BLOCK_N;
-            if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
+            const int m0 = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
+            const int n0 = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
+            if (!kCM && n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
             {
                 fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
                 filled_n0 = n0;
@@ -988,8 +1149,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
-                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                     smem + P::OFF_OUT);
+                if (kCM)
+                {
+                    epilogue_warp_tile_cm<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, tp, ep, warp, lane, m0, n0);
+                }
+                else
+                {
+                    epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
+                                                         smem + P::OFF_OUT);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
@@ -1740,7 +1908,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
-    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out>;
+    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
     {
@@ -1764,6 +1932,44 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, tp, ep);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel");
+}
+
+// Channel-major launch: weights on the 128-row side of the tile, BLOCK_N rows of the activation matrix on the other.
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
+cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
+{
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
+    static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
+    CUtensorMap map_w, map_x;
+    if (!encode_operand_map(&map_w, op.bt, op.N, op.K, op.ldbt, BLOCK_M) ||
+        !encode_operand_map(&map_x, op.a, op.M, op.K, op.lda, BLOCK_N))
+    {
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
+    }
+    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, true>;
+    static bool attr_set[64] = {}; // per instantiation and device
+    if (!attr_set[ctx->device & 63])
+    {
+        CUGL_CUDA_TRY(ctx, cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, P::DYN_BYTES));
+        attr_set[ctx->device & 63] = true;
+    }
+    TileParams tp;
+    tp.dst    = static_cast<uint8_t *>(op.dst);
+    tp.ldd    = op.ldd;
+    fill_extra_dst(tp, op);
+    tp.M      = op.N; // tensor-memory lanes: output channels
+    tp.N      = op.M; // tensor-memory columns: output rows
+    tp.K      = op.K;
+    tp.idesc  = (2u << 4) | ((op.b_signed ? 1u : 0u) << 7) | ((op.a_signed ? 1u : 0u) << 10) |
+               (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
+    tp.vec_ok  = 0;
+    tp.status  = ctx->d_status;
+    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
+    tp.trace   = ctx->d_trace;
+    const int tiles = ((op.N + BLOCK_M - 1) / BLOCK_M) * ((op.M + BLOCK_N - 1) / BLOCK_N);
+    const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
+    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_w, map_x, tp, ep);
+    return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel (channel-major)");
 }
 
 template <int STAGES, int KSUB, bool kS32Out>
@@ -1896,6 +2102,11 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
                                     bool allow_pair)
 {
     const bool s32 = ep.stage == CUGL_STAGE_NONE;
+    // channel-major accumulators: no row-sum term (it would be a per-column quantity there) and one destination
+    if (op.channel_major > 0 && ep.rowsum == nullptr && op.n_extra_dst == 0)
+    {
+        return s32 ? launch_variant_cm<256, 4, 1, true>(ctx, op, ep) : launch_variant_cm<256, 4, 1, false>(ctx, op, ep);
+    }
     if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
     {
         return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);

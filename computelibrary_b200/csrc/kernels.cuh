@@ -49,6 +49,9 @@ struct GemmOperands
     // with residual an [M][ldd] byte matrix (the fused residual addition of a convolution), or nullptr
     const void *residual;
     int         res_floor, res_cap;
+    // > 0: run the GEMM with the operand roles exchanged (accumulator lanes = output channels); < 0: never;
+    // 0: the dispatcher decides.  Ignored when a row-sum term or several destinations are present.
+    int         channel_major;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).

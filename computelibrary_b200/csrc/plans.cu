@@ -44,6 +44,7 @@ struct GemmCore
     bool          generic_stage = false; // a left shift or an INT32_MIN multiplier is present
     bool          wide_stage    = false; // shifts in [2, 31], multipliers in [0, 2^31), no row-sum term
     int           epi_warps     = 0;     // 4 / 8 force that build of the tensor-core kernels, 0 = automatic
+    int           channel_major = 0;     // > 0 / < 0 force / forbid the channel-major kernel, 0 = automatic
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
@@ -153,6 +154,7 @@ struct GemmCore
         op.generic_stage = generic_stage;
         op.wide_stage    = wide_stage;
         op.epi_warps     = epi_warps;
+        op.channel_major = channel_major;
         op.n_extra_dst   = n_extra;
         op.residual      = d_residual;
         op.res_floor     = res_floor;
@@ -974,6 +976,7 @@ extern "C"
             op.generic_stage = c.generic_stage;
             op.wide_stage    = c.wide_stage;
             op.epi_warps     = c.epi_warps;
+            op.channel_major = c.channel_major;
             op.n_extra_dst   = 0;
             op.residual      = d_residual;
             op.res_floor     = plan->res_floor;
@@ -1056,6 +1059,26 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_allow_implicit: NULL plan");
         }
         plan->allow_implicit = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_channel_major(cugl_gemm_plan *plan, int mode)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_set_channel_major: NULL plan");
+        }
+        plan->core.channel_major = mode;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_channel_major(cugl_conv_plan *plan, int mode)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_channel_major: NULL plan");
+        }
+        plan->core.channel_major = mode;
         return CUGL_SUCCESS;
     }
 

@@ -212,6 +212,11 @@ CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
  * eight).  warps = 4 or 8 forces one build, 0 restores the automatic choice (testing / measurement aid: the
  * results are identical). */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps);
+/* The tensor-core GEMM can also run with the operand roles exchanged, which makes an accumulator lane an output
+ * channel (output-stage terms in registers, byte-wise transposed stores; never with a row-sum term or several
+ * destinations).  mode > 0 requests it, <= 0 keeps the row-major kernel (the default: it is the faster one on
+ * the shapes measured so far).  Testing / measurement aid: the results are identical. */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_channel_major(cugl_gemm_plan *plan, int mode);
 
 /* Fused GEMMLowp that allocates nothing.  No counterpart in the reference: Compute Library always lets the
  * function object own its workspace.  For callers that cannot call cudaMalloc -- a serving loop whose device
@@ -313,8 +318,10 @@ CUGL_API int  cugl_conv2d_plan_launches(const cugl_conv_plan *plan);
 CUGL_API const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan);
 /* on = 0 forces the explicit im2col lowering (testing aid: both lowerings must agree bit for bit). */
 CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on);
-/* as cugl_gemmlowp_plan_set_epilogue_warps */
+/* as cugl_gemmlowp_plan_set_epilogue_warps / cugl_gemmlowp_plan_set_channel_major (the latter acts on the
+ * lowerings that run the plain GEMM kernel: 1x1 convolutions and the explicit im2col path) */
 CUGL_API cugl_status cugl_conv2d_plan_set_epilogue_warps(cugl_conv_plan *plan, int warps);
+CUGL_API cugl_status cugl_conv2d_plan_set_channel_major(cugl_conv_plan *plan, int mode);
 /* Fused residual addition: dst = act(quantize(dequantize(conv) + dequantize(residual))) computed in the epilogue
  * of the convolution, i.e. NEGEMMConvolutionLayer followed by NEArithmeticAddition (ConvertPolicy::SATURATE)
  * and NEActivationLayer (arm_compute/runtime/NEON/functions/NEArithmeticAddition.h:43-109) without the

@@ -167,12 +167,13 @@ def test_fused_residual_addition(ctx, port, geom):
     mult, shift = f32_mults(port, q[0], ws, q[0])
     conv = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), q[1], 0, mult, shift, q[1], 0, 255)
     res = q8_uniform(rng, conv.shape, np.uint8)
-    for act, a in (("relu", 0.0), ("bounded_relu", 6.0)):
+    for act, a, cm in (("relu", 0.0, -1), ("bounded_relu", 6.0, -1), ("relu", 0.0, 1)):
         want = port.activation_qasymm8(port.add_qasymm8(conv, res, q, q, q), act, a, 0.0, q, q)
         desc, keep = capi.make_conv_desc(2, 14, 15, Cc, OFM, k, k, (s, s), (p, p, p, p), (1, 1), capi.U8, capi.S8, q[1], 0,
                                          multipliers=mult, shifts=shift, dst_zp=q[1], min_bound=0, max_bound=255)
         plan = capi.ConvPlan(ctx, desc, keep)
         plan.set_residual(q[0], q, q, act=capi.ACT_RELU if act == "relu" else capi.ACT_BOUNDED_RELU, act_a=a)
+        plan.set_channel_major(cm)
         plan.prepare(torch.from_numpy(wgt.view(np.uint8)).cuda())
         d_res = torch.from_numpy(res).cuda()
         d_dst = torch.empty(conv.shape, dtype=torch.uint8, device="cuda")

@@ -271,15 +271,19 @@ def test_epilogue_builds_and_stage_encodings(ctx, port, shape, epi_warps):
         shift = rng.integers(lo_shift, hi_shift, N).astype(np.int32)
         shift[0], shift[-1] = lo_shift, hi_shift - 1
         want = port.gemmlowp_fused(a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8)
-        for pair in (True, False):
+        for pair, cm in ((True, -1), (False, -1), (False, 1)):
             got, kern = gpu_gemmlowp(ctx, a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8, pair=pair,
-                                     epi_warps=epi_warps)
+                                     epi_warps=epi_warps, channel_major=cm, ldd_pad=5 if cm > 0 else 0)
             assert kern.startswith("tcgen05")
-            assert np.array_equal(got, want), (label, pair, np.argwhere(got != want)[:4])
+            assert np.array_equal(got, want), (label, pair, cm, np.argwhere(got != want)[:4])
     # per-tensor wide encoding with a signed output and a lower bound above the type minimum
     a8 = q8_uniform(rng, (M, K), np.int8)
     got, _ = gpu_gemmlowp(ctx, a8, b, bias, 5, 0, 1759218688, 13, -3, -100, 90, np.int8, epi_warps=epi_warps)
     assert np.array_equal(got, port.gemmlowp_fused(a8, b, bias, 5, 0, [1759218688], [13], -3, -100, 90, np.int8))
+    # raw int32 accumulators with the offset terms, row-major and channel-major kernels
+    for cm in (-1, 1):
+        got, _ = gpu_gemmlowp(ctx, a, b, None, -7, 0, 0, 0, 0, 0, 0, np.int32, epi_warps=epi_warps, channel_major=cm)
+        assert np.array_equal(got, port.gemmlowp_core(a, b, -7, 0)), cm
     # asymmetric weights (row-sum term present): never the wide encoding
     bu = q8_uniform(rng, (K, N), np.uint8)
     got, _ = gpu_gemmlowp(ctx, a, bu, bias, -7, -9, 1099511552, 8, 10, 0, 255, np.uint8, epi_warps=epi_warps)
