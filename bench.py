@@ -46,6 +46,7 @@ def parse_args():
     p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     p.add_argument("--batch", type=int, default=256, help="global batch of c4 (split over the ranks)")
     p.add_argument("--layers", action="store_true", help="c4: print the per-layer time table to stderr")
+    p.add_argument("--no-graph", action="store_true", help="c4: launch every layer eagerly instead of one CUDA graph")
     p.add_argument("--size", type=int, default=0, help="override M=N=K of c2 (profiling on a small case)")
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
@@ -521,7 +522,11 @@ def run_resnet(args):
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    ctx = cl.Context(local, torch.cuda.current_stream().cuda_stream)
+    # a stream of its own: the node list is captured into a CUDA graph on it; torch's current stream is set to
+    # it so that the bench's events, copies and L2 flush are ordered with the network
+    work = torch.cuda.Stream()
+    torch.cuda.set_stream(work)
+    ctx = cl.Context(local, work.cuda_stream)
     b0, b1 = sharding.batch_shard(args.batch, world, rank)
     B = b1 - b0
     net = rn.ResNet50(ctx, B, seed=1)
@@ -540,15 +545,18 @@ def run_resnet(args):
     for _ in range(2):  # first-use costs (lazy workspaces) stay outside the sampled window
         net.run(d_in)
     barrier()
+    graph = None if args.no_graph else net.capture(d_in, work)
+    run_net = (lambda: net.run(d_in)) if graph is None else graph.replay
+    barrier()
     t_begin = time.time()
-    step_ms = _timed_steps(lambda: net.run(d_in), args.steps, args.warmup, flush, barrier)
+    step_ms = _timed_steps(run_net, args.steps, args.warmup, flush, barrier)
     clocks = sampler.stop(t_begin, time.time()) if sampler else None
     ctx.sync()
 
     def e2e_step():
         d_in.copy_(h_in, non_blocking=True)
-        out = net.run(d_in)
-        h_out.copy_(out, non_blocking=True)
+        run_net()
+        h_out.copy_(net.bufs["softmax"], non_blocking=True)
 
     e2e_ms = [] if args.no_e2e else _timed_steps(e2e_step, max(2, args.steps // 4), 2, flush, barrier)
     if args.layers and rank == 0:
@@ -575,7 +583,9 @@ def run_resnet(args):
             "config": {"workload": f"config4: QASYMM8 ResNet-50 v1, 224x224, global batch {args.batch}, per-channel s8 "
                        "weights, batch norm folded, ReLU fused", "per_gpu_batch": B,
                        "l2": "flushed between timed steps (256 MB write)",
-                       "sharding": "batch split over ranks, weights replicated, no collective"},
+                       "sharding": "batch split over ranks, weights replicated, no collective",
+                       "launch": "eager, one C-ABI call per layer" if graph is None else
+                                 "one CUDA graph of the layer calls per step"},
             "int8_tops": ops_img * args.batch / (ms * 1e-3) / 1e12,
             "gpu_launches": args.steps * net.launches,
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TOP/s", "frac": ach / peak,

@@ -208,6 +208,21 @@ class ResNet50:
             fn(d_input)
         return self.bufs["softmax"]
 
+    def capture(self, d_input, torch_stream):
+        """Records one pass over ``d_input`` into a CUDA graph and returns it (``graph.replay()`` re-runs the whole
+        network with one launch; new images are copied into ``d_input`` beforehand).  ``torch_stream`` must be the
+        torch stream the context was created on, and not the default stream.  One eager pass runs first so that
+        nothing allocates or sets kernel attributes while the stream is capturing."""
+        import torch
+        assert torch_stream.cuda_stream == self.ctx.stream and torch_stream.cuda_stream != 0
+        with torch.cuda.stream(torch_stream):
+            self.run(d_input)
+        self.ctx.sync()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=torch_stream):
+            self.run(d_input)
+        return graph
+
     def run_timed(self, d_input, stream=None):
         """Runs once with a CUDA event pair around every node; returns [(name, op, kernel, ms)].  ``stream`` is the
         torch stream the context enqueues on (default: torch's current stream)."""

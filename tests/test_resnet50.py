@@ -60,3 +60,32 @@ def test_reduced_network_vs_oracle(ctx, port, fan_in_scaled, fuse_residual):
         assert 0.02 < np.mean((deep > 0) & (deep < 255))
     assert net.launches >= len(g) - len(net.fused)
     net.close()
+
+
+@pytest.mark.gpu
+def test_graph_replay_equals_eager(port):
+    """The node list captured into one CUDA graph gives the bytes of the eager pass, also on new images."""
+    import torch
+    import computelibrary_b200 as cl
+    from computelibrary_b200 import resnet50 as rn
+    torch.cuda.set_device(0)
+    work = torch.cuda.Stream()
+    ctx = cl.Context(0, work.cuda_stream)
+    g = rn.build_graph(64, 100)
+    params = rn.synthetic_params(g, seed=5, fan_in_scaled=True)
+    rng = np.random.default_rng(23)
+    x0, x1 = (rng.integers(0, 256, (2, 64, 64, 3), dtype=np.uint8) for _ in range(2))
+    with torch.cuda.stream(work):
+        net = rn.ResNet50(ctx, 2, params=params, nodes=g)
+        d_in = torch.from_numpy(x0).cuda()
+        graph = net.capture(d_in, work)
+        for x in (x0, x1):
+            d_in.copy_(torch.from_numpy(x).cuda())
+            graph.replay()
+            ctx.sync()
+            got = {k: net.bufs[k].cpu().numpy() for k in ("block2/unit1/add", "logits")}
+            want = run_graph_oracle(port, g, params, x)
+            for k in got:
+                np.testing.assert_array_equal(got[k], want[k], err_msg=k)
+    net.close()
+    ctx.close()
