@@ -135,6 +135,7 @@ _SIGNATURES = {
     "cugl_conv2d_run_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_channel_major": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_set_tail_split": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_channel_major": (C.c_int, [_vp, C.c_int]),
     "cugl_pool2d_out_dims": (None, [C.POINTER(PoolDesc), _pi32, _pi32]),
     "cugl_pool2d_validate": (C.c_int, [C.POINTER(PoolDesc)]),
@@ -461,6 +462,9 @@ class GemmPlan:
 
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_channel_major(self.handle, int(mode)))
+
+    def set_tail_split(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_tail_split(self.handle, int(on)))
 
     def allow_pair_kernel(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_allow_pair_kernel(self.handle, int(on)))

@@ -272,6 +272,8 @@ struct TileParams
     uint32_t idesc;
     int      vec_ok;  // dst base and ldd are 16-byte aligned
     int      mode;    // kStageGeneric / kStageFast / kStageWide: encoding of the column terms (requant_pack4)
+    uint32_t idesc_half; // SM-pair kernel: instruction descriptor of a half-width (N = 128) tile
+    int      split_tail; // SM-pair kernel: split the tiles of a short last wave in two (see the kernel)
     const uint8_t *residual; // optional [M][ldd] bytes added to the output with unsigned saturation, then clamped
     uint32_t res_floor4, res_cap4; // the clamp bounds replicated into four bytes
     long long *trace; // optional per-CTA event timestamps (cugl_context_set_trace_buffer), else nullptr
@@ -715,6 +717,91 @@ __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, c
 // element column) is what bounds the row-major epilogue on short-K shapes.  The 32 lanes of a warp hold 32
 // consecutive channels of one output row: each store instruction writes one 32-byte segment of dst.
 //   tp.M = number of channels (dst columns), tp.N = number of rows of dst, tp.ldd = dst row pitch in bytes.
+// Channel-major chunk (lane = channel, 32 output rows in registers) written through a 4x4 byte transpose in
+// shared memory: every lane packs four rows of its channel into a word and stores the eight words (pitch 36
+// words: conflict-free both ways); lane (i, g) = (lane / 4, lane % 4) then reads the eight words of channels
+// 8g .. 8g+7 for rows 4i .. 4i+3, transposes two 4x4 byte blocks with eight byte permutes and stores eight
+// contiguous bytes per row: 4 store instructions per lane and chunk instead of 32 byte stores.  The residual
+// is loaded and added in the same shape.  Needs 8-byte aligned rows (tp.vec_ok) and is called by whole warps.
+constexpr int kCmPitchWords = 36;
+constexpr int kCmStageBytes = 8 * kCmPitchWords * 4;
+
+template <int kMode>
+__device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], const int4 q, const TileParams &tp,
+                                                      const EpilogueParams &ep, int ch_base, int p0, int lane,
+                                                      uint32_t *stage)
+{
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+    {
+        int32_t r[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+        {
+            r[b] = requant_one<kMode>(v[4 * i + b], q, 0, ep.result_offset, ep.lo, ep.hi);
+        }
+        const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
+        const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
+        stage[i * kCmPitchWords + lane] = __byte_perm(p01, p23, 0x5410);
+    }
+    __syncwarp();
+    const int   i  = lane >> 2, g = lane & 3;
+    const uint4 lo = *reinterpret_cast<const uint4 *>(stage + i * kCmPitchWords + 8 * g);
+    const uint4 hi = *reinterpret_cast<const uint4 *>(stage + i * kCmPitchWords + 8 * g + 4);
+    __syncwarp(); // the stage may be overwritten by the next chunk
+    uint32_t t[4][2];
+    {
+        const uint32_t x0 = __byte_perm(lo.x, lo.y, 0x5140), x1 = __byte_perm(lo.x, lo.y, 0x7362);
+        const uint32_t y0 = __byte_perm(lo.z, lo.w, 0x5140), y1 = __byte_perm(lo.z, lo.w, 0x7362);
+        t[0][0] = __byte_perm(x0, y0, 0x5410), t[1][0] = __byte_perm(x0, y0, 0x7632);
+        t[2][0] = __byte_perm(x1, y1, 0x5410), t[3][0] = __byte_perm(x1, y1, 0x7632);
+    }
+    {
+        const uint32_t x0 = __byte_perm(hi.x, hi.y, 0x5140), x1 = __byte_perm(hi.x, hi.y, 0x7362);
+        const uint32_t y0 = __byte_perm(hi.z, hi.w, 0x5140), y1 = __byte_perm(hi.z, hi.w, 0x7362);
+        t[0][1] = __byte_perm(x0, y0, 0x5410), t[1][1] = __byte_perm(x0, y0, 0x7632);
+        t[2][1] = __byte_perm(x1, y1, 0x5410), t[3][1] = __byte_perm(x1, y1, 0x7632);
+    }
+    const int ch = ch_base + 8 * g; // first of this lane's eight channels
+    if (ch >= tp.M)
+    {
+        return;
+    }
+    const bool full = ch + 8 <= tp.M;
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+    {
+        const int p = p0 + 4 * i + k;
+        if (p < tp.N)
+        {
+            const int64_t off = static_cast<int64_t>(p) * tp.ldd + ch;
+            uint32_t      w0 = t[k][0], w1 = t[k][1];
+            if (full)
+            {
+                if (tp.residual != nullptr)
+                {
+                    const uint2 r = __ldg(reinterpret_cast<const uint2 *>(tp.residual + off));
+                    w0 = __vminu4(__vmaxu4(__vaddus4(w0, r.x), tp.res_floor4), tp.res_cap4);
+                    w1 = __vminu4(__vmaxu4(__vaddus4(w1, r.y), tp.res_floor4), tp.res_cap4);
+                }
+                *reinterpret_cast<uint2 *>(tp.dst + off) = make_uint2(w0, w1);
+            }
+            else
+            {
+                for (int b = 0; b < 8 && ch + b < tp.M; ++b)
+                {
+                    uint32_t y = ((b < 4 ? w0 : w1) >> (8 * (b & 3))) & 0xffu;
+                    if (tp.residual != nullptr)
+                    {
+                        y = min(max(min(y + tp.residual[off + b], 255u), tp.res_floor4 & 0xffu), tp.res_cap4 & 0xffu);
+                    }
+                    tp.dst[off + b] = static_cast<uint8_t>(y);
+                }
+            }
+        }
+    }
+}
+
 template <bool kS32Out, int kMode>
 __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const int4 q, const TileParams &tp,
                                                const EpilogueParams &ep, int ch, int p0)
@@ -784,11 +871,41 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
 
 template <int NPIX, bool kS32Out, int kMode>
 __device__ __forceinline__ void drain_channel_major(uint32_t t_addr, const int4 q, const TileParams &tp,
-                                                    const EpilogueParams &ep, int ch, int p_first)
+                                                    const EpilogueParams &ep, int ch, int p_first, int lane,
+                                                    uint32_t *stage)
 {
     static_assert((NPIX / 32) % 2 == 0 || NPIX == 32, "chunks are drained in pairs");
     uint32_t va[32], vb[32];
     tmem_ld_x32(t_addr, va);
+    if (!kS32Out && tp.vec_ok) // warp-uniform: rows of dst (and of the residual) are 8-byte aligned
+    {
+#pragma unroll 1
+        for (int c = 0; c < NPIX / 32; c += 2)
+        {
+            tmem_ld_wait();
+            if (c + 1 < NPIX / 32)
+            {
+                tmem_ld_x32(t_addr + (c + 1) * 32, vb);
+            }
+            if (p_first + c * 32 < tp.N)
+            {
+                store_chunk_cm_staged<kMode>(va, q, tp, ep, ch - lane, p_first + c * 32, lane, stage);
+            }
+            if (c + 1 < NPIX / 32)
+            {
+                tmem_ld_wait();
+                if (c + 2 < NPIX / 32)
+                {
+                    tmem_ld_x32(t_addr + (c + 2) * 32, va);
+                }
+                if (p_first + (c + 1) * 32 < tp.N)
+                {
+                    store_chunk_cm_staged<kMode>(vb, q, tp, ep, ch - lane, p_first + (c + 1) * 32, lane, stage);
+                }
+            }
+        }
+        return;
+    }
 #pragma unroll 1
     for (int c = 0; c < NPIX / 32; c += 2)
     {
@@ -812,8 +929,10 @@ __device__ __forceinline__ void drain_channel_major(uint32_t t_addr, const int4 
 
 template <int BLOCK_N, bool kS32Out>
 __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const TileParams &tp, const EpilogueParams &ep,
-                                                      int warp, int lane, int m0, int n0)
+                                                      int warp, int lane, int m0, int n0, uint8_t *out_stage)
 {
+    static_assert(kCmStageBytes <= kOutStageBytes, "the transpose stage lives in the warp's output staging area");
+    uint32_t *stage = reinterpret_cast<uint32_t *>(out_stage + (warp - kFirstEpi) * kOutStageBytes);
     constexpr int NPIX = BLOCK_N / (kEpiWarps / 4);
     const int     quad = warp & 3;                // tensor-memory lane quarter this warp may read
     const int     half = (warp - kFirstEpi) >> 2; // which share of the output rows
@@ -834,15 +953,15 @@ __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const T
     const int      p0     = n0 + half * NPIX;
     if (tp.mode == kStageWide && !kS32Out)
     {
-        drain_channel_major<NPIX, kS32Out, kStageWide>(t_addr, q, tp, ep, ch, p0);
+        drain_channel_major<NPIX, kS32Out, kStageWide>(t_addr, q, tp, ep, ch, p0, lane, stage);
     }
     else if (tp.mode == kStageGeneric)
     {
-        drain_channel_major<NPIX, kS32Out, kStageGeneric>(t_addr, q, tp, ep, ch, p0);
+        drain_channel_major<NPIX, kS32Out, kStageGeneric>(t_addr, q, tp, ep, ch, p0, lane, stage);
     }
     else
     {
-        drain_channel_major<NPIX, kS32Out, kStageFast>(t_addr, q, tp, ep, ch, p0);
+        drain_channel_major<NPIX, kS32Out, kStageFast>(t_addr, q, tp, ep, ch, p0, lane, stage);
     }
 }
 
@@ -1151,7 +1270,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (et == 0) trace_event(tp.trace, ti, 4);
                 if (kCM)
                 {
-                    epilogue_warp_tile_cm<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, tp, ep, warp, lane, m0, n0);
+                    epilogue_warp_tile_cm<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, tp, ep, warp, lane, m0, n0,
+                                                            smem + P::OFF_OUT);
                 }
                 else
                 {
@@ -1220,7 +1340,8 @@ struct SmemPlan2
 template <int STAGES, int KSUB, bool kS32Out>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
-                                 const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ TileParams tp,
+                                 const __grid_constant__ CUtensorMap tmap_b,
+                                 const __grid_constant__ CUtensorMap tmap_bh, const __grid_constant__ TileParams tp,
                                  const EpilogueParams ep)
 {
     using P               = SmemPlan2<STAGES, KSUB>;
@@ -1250,6 +1371,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int num_kb       = (tp.K + KSUB * BLOCK_K - 1) / (KSUB * BLOCK_K); // pipeline stages per tile
     const int first_tile   = static_cast<int>(cluster_id_x());
     const int tile_stride  = static_cast<int>(num_clusters_x());
+    // Tail split.  With T tiles on G SM pairs the last wave holds T mod G tiles and costs as much as a full
+    // one.  When twice that many fit into one wave, each of those tiles is processed as two 256 x 128 halves
+    // (tmap_bh: 64-row boxes of B per CTA, an MMA of N = 128) by two pairs, and the wave takes half the time.
+    // Work items v = 0 .. num_items-1: v < first_split is tile v; above, item first_split + 2j + h is half h of
+    // tile first_split + j.
+    const int tail        = num_tiles % tile_stride;
+    const int n_split     = (tp.split_tail != 0 && tail > 0 && 2 * tail <= tile_stride) ? tail : 0;
+    const int first_split = num_tiles - n_split;
+    const int num_items   = num_tiles + n_split;
+    auto      item_tile   = [&](int v) { return v < first_split ? v : first_split + ((v - first_split) >> 1); };
+    auto      item_half   = [&](int v) { return v < first_split ? -1 : ((v - first_split) & 1); }; // -1: whole tile
 
     if (threadIdx.x == 0)
     {
@@ -1284,7 +1416,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0)
         {
             const int issuer   = warp;
-            const int my_tiles = first_tile < num_tiles ? (num_tiles - 1 - first_tile) / tile_stride + 1 : 0;
+            const int my_tiles = first_tile < num_items ? (num_items - 1 - first_tile) / tile_stride + 1 : 0;
             const int total_kb = my_tiles * num_kb;
             int       ti = 0, kb = issuer;
             while (kb >= num_kb)
@@ -1301,21 +1433,26 @@ __global__ void __launch_bounds__(kThreads, 1)
                     break;
                 }
                 ktrace(tp.trace, ti, 2, kb);
-                const int tile = first_tile + ti * tile_stride;
+                const int item = first_tile + ti * tile_stride;
+                const int tile = item_tile(item), half = item_half(item);
                 const int m0   = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
-                const int n0   = (tile / num_m_blocks) * BLOCK_N + static_cast<int>(rank) * (BLOCK_N / 2);
+                const int n0   = (tile / num_m_blocks) * BLOCK_N +
+                               (half < 0 ? static_cast<int>(rank) * (BLOCK_N / 2)
+                                         : half * (BLOCK_N / 2) + static_cast<int>(rank) * (BLOCK_N / 4));
                 if (kb == 0) trace_event(tp.trace, ti, 0);
                 const uint32_t leader_full = map_to_cta(full_bar(st), 0);
                 if (leader)
                 {
-                    mbar_expect_tx(full_bar(st), 2 * P::STAGE); // the bytes of both CTAs
+                    // the bytes of both CTAs
+                    mbar_expect_tx(full_bar(st), half < 0 ? 2 * P::STAGE : 2 * (P::A_STAGE_K + P::B_STAGE / 2));
                 }
 #pragma unroll
                 for (int sub = 0; sub < KSUB; ++sub)
                 {
                     const int k0 = (kb * KSUB + sub) * BLOCK_K;
                     tma_load_2d_pair(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, leader_full);
-                    tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, leader_full);
+                    tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, half < 0 ? &tmap_b : &tmap_bh, k0, n0,
+                                     leader_full);
                 }
                 ktrace(tp.trace, ti, 3, kb);
                 kb += kProdLanes;
@@ -1345,8 +1482,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             int      ti = 0;
             const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
-            for (int tile = first_tile; tile < num_tiles && ok; tile += tile_stride, ++ti)
+            for (int item = first_tile; item < num_items && ok; item += tile_stride, ++ti)
             {
+                const uint32_t idesc = item_half(item) < 0 ? tp.idesc : tp.idesc_half;
                 ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
                 if (!ok)
                 {
@@ -1390,7 +1528,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                         {
                             umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
-                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, idesc,
                                          (kb | sub | k) != 0 ? 1u : 0u);
                         }
                     }
@@ -1423,14 +1561,15 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool      ok = true;
         int       ti = 0;
         int       filled_n0 = -1;
-        for (int tile = first_tile; tile < num_tiles; tile += tile_stride, ++ti)
+        for (int item = first_tile; item < num_items; item += tile_stride, ++ti)
         {
             if (!epi_barrier_and(ok))
             {
                 break;
             }
-            const int m0 = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
-            const int n0 = (tile / num_m_blocks) * BLOCK_N;
+            const int tile = item_tile(item), half = item_half(item);
+            const int m0   = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
+            const int n0   = (tile / num_m_blocks) * BLOCK_N + (half > 0 ? BLOCK_N / 2 : 0);
             if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
             {
                 fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
@@ -1442,8 +1581,16 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
-                epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                     smem + P::OFF_OUT);
+                if (half < 0)
+                {
+                    epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
+                                                         smem + P::OFF_OUT);
+                }
+                else
+                {
+                    epilogue_warp_tile<BLOCK_N / 2, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
+                                                             smem + P::OFF_OUT);
+                }
                 tc_fence_before();
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
@@ -1928,6 +2075,8 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.idesc_half = 0;
+    tp.split_tail = 0;
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, tp, ep);
@@ -1962,10 +2111,12 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.b_signed ? 1u : 0u) << 7) | ((op.a_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
-    tp.vec_ok  = 0;
+    tp.vec_ok  = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 7) == 0;
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.idesc_half = 0;
+    tp.split_tail = 0;
     const int tiles = ((op.N + BLOCK_M - 1) / BLOCK_M) * ((op.M + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_w, map_x, tp, ep);
@@ -1977,9 +2128,10 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
 {
     using P = SmemPlan2<STAGES, KSUB>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
-    CUtensorMap map_a, map_b;
+    CUtensorMap map_a, map_b, map_bh;
     if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
-        !encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, P::BLOCK_N / 2))
+        !encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, P::BLOCK_N / 2) ||
+        !encode_operand_map(&map_bh, op.bt, op.N, op.K, op.ldbt, P::BLOCK_N / 4))
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
@@ -1999,6 +2151,8 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(P::BLOCK_N >> 3) << 17) | (static_cast<uint32_t>((2 * BLOCK_M) >> 4) << 24);
+    tp.idesc_half = (tp.idesc & ~(0x3fu << 17)) | (static_cast<uint32_t>((P::BLOCK_N / 2) >> 3) << 17);
+    tp.split_tail = op.split_tail >= 0 ? 1 : 0;
     tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
@@ -2019,7 +2173,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs                = attr;
     cfg.numAttrs             = 1;
-    CUGL_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, tp, ep));
+    CUGL_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_bh, tp, ep));
     return CUGL_SUCCESS;
 }
 
@@ -2056,6 +2210,8 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.idesc_half = 0;
+    tp.split_tail = 0;
     ConvGeom cg;
     cg.src   = static_cast<const uint8_t *>(cv.src);
     cg.pad   = static_cast<const uint8_t *>(cv.pad);

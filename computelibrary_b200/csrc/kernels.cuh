@@ -52,6 +52,8 @@ struct GemmOperands
     // > 0: run the GEMM with the operand roles exchanged (accumulator lanes = output channels); < 0: never;
     // 0: the dispatcher decides.  Ignored when a row-sum term or several destinations are present.
     int         channel_major;
+    // SM-pair kernel: < 0 keeps every tile whole; otherwise the tiles of a short last wave are split in two
+    int         split_tail;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).

@@ -45,6 +45,7 @@ struct GemmCore
     bool          wide_stage    = false; // shifts in [2, 31], multipliers in [0, 2^31), no row-sum term
     int           epi_warps     = 0;     // 4 / 8 force that build of the tensor-core kernels, 0 = automatic
     int           channel_major = 0;     // > 0 / < 0 force / forbid the channel-major kernel, 0 = automatic
+    int           split_tail    = 0;     // < 0: the SM-pair kernel keeps the tiles of a short last wave whole
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
@@ -155,6 +156,7 @@ struct GemmCore
         op.wide_stage    = wide_stage;
         op.epi_warps     = epi_warps;
         op.channel_major = channel_major;
+        op.split_tail    = split_tail;
         op.n_extra_dst   = n_extra;
         op.residual      = d_residual;
         op.res_floor     = res_floor;
@@ -1059,6 +1061,16 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_allow_implicit: NULL plan");
         }
         plan->allow_implicit = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_tail_split(cugl_gemm_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_set_tail_split: NULL plan");
+        }
+        plan->core.split_tail = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
     }
 

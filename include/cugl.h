@@ -217,6 +217,10 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan,
  * destinations).  mode > 0 requests it, <= 0 keeps the row-major kernel (the default: it is the faster one on
  * the shapes measured so far).  Testing / measurement aid: the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_channel_major(cugl_gemm_plan *plan, int mode);
+/* SM-pair kernel: when the last wave of 256 x 256 tiles fills at most half of the SM pairs, its tiles are
+ * processed as two 256 x 128 halves each (on by default).  on = 0 keeps them whole.  Testing / measurement aid:
+ * the results are identical. */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_tail_split(cugl_gemm_plan *plan, int on);
 
 /* Fused GEMMLowp that allocates nothing.  No counterpart in the reference: Compute Library always lets the
  * function object own its workspace.  For callers that cannot call cudaMalloc -- a serving loop whose device

@@ -271,11 +271,12 @@ def test_epilogue_builds_and_stage_encodings(ctx, port, shape, epi_warps):
         shift = rng.integers(lo_shift, hi_shift, N).astype(np.int32)
         shift[0], shift[-1] = lo_shift, hi_shift - 1
         want = port.gemmlowp_fused(a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8)
-        for pair, cm in ((True, -1), (False, -1), (False, 1)):
+        # channel-major: 8-byte aligned rows take the shared-memory byte transpose, a pitch of N + 5 the byte stores
+        for pair, cm, pad in ((True, -1, 0), (False, -1, 0), (False, 1, 0), (False, 1, 5), (False, 1, 8)):
             got, kern = gpu_gemmlowp(ctx, a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8, pair=pair,
-                                     epi_warps=epi_warps, channel_major=cm, ldd_pad=5 if cm > 0 else 0)
+                                     epi_warps=epi_warps, channel_major=cm, ldd_pad=pad)
             assert kern.startswith("tcgen05")
-            assert np.array_equal(got, want), (label, pair, cm, np.argwhere(got != want)[:4])
+            assert np.array_equal(got, want), (label, pair, cm, pad, np.argwhere(got != want)[:4])
     # per-tensor wide encoding with a signed output and a lower bound above the type minimum
     a8 = q8_uniform(rng, (M, K), np.int8)
     got, _ = gpu_gemmlowp(ctx, a8, b, bias, 5, 0, 1759218688, 13, -3, -100, 90, np.int8, epi_warps=epi_warps)
@@ -314,3 +315,32 @@ def test_run_multi_destinations_eight_epilogue_warps(ctx, port):
             assert np.array_equal(h[:, n0:n0 + n_local].view(np.int8), want), warps
             assert (h[:, :n0] == 0x11).all() and (h[:, n0 + n_local:] == 0x11).all()
         plan.close()
+
+
+@pytest.mark.parametrize("shape", [(2304, 2304, 1152), (2290, 2200, 1136), (1024, 5000, 1040)])
+def test_pair_kernel_tail_split(ctx, port, shape):
+    """SM-pair kernel with a short last wave (81, 81 and 80 tiles of 256 x 256 on 74 SM pairs): the tail tiles run
+    as two 256 x 128 halves.  Same bytes as the oracle and as the unsplit kernel, ragged edges included."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K)
+    a, b = q8_uniform(rng, (M, K), np.int8), q8_uniform(rng, (K, N), np.int8, -127, 127)
+    bias = rng.integers(-20000, 20001, N).astype(np.int32)
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+    shift = rng.integers(6, 12, N).astype(np.int32)
+    want = port.gemmlowp_fused(a, b, bias, 5, 0, mult, shift, -3, -128, 127, np.int8)
+    outs = []
+    for split in (True, False):
+        import torch
+        desc, keep = capi.make_gemm_desc(M, N, K, capi.S8, capi.S8, capi.S8, 5, 0, multipliers=mult, shifts=shift,
+                                         offset=-3, min_bound=-128, max_bound=127, has_bias=True)
+        plan = capi.GemmPlan(ctx, desc, keep)
+        plan.set_tail_split(split)
+        assert plan.kernel == "tcgen05_2cta"
+        plan.prepare(torch.from_numpy(b.view(np.uint8)).cuda())
+        d_dst = torch.full((M, N), 0x55, dtype=torch.uint8, device="cuda")
+        plan.run(torch.from_numpy(a.view(np.uint8)).cuda(), None, torch.from_numpy(bias).cuda(), d_dst)
+        ctx.sync()
+        outs.append(d_dst.cpu().numpy().view(np.int8))
+        plan.close()
+    assert np.array_equal(outs[0], want), np.argwhere(outs[0] != want)[:5]
+    assert np.array_equal(outs[1], want)
