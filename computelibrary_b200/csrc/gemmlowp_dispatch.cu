@@ -36,11 +36,18 @@ bool gemmlowp_tcgen05_uses_pair(const GemmOperands &op)
 cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                     bool allow_pair)
 {
-    // The channel-major kernel (operand roles exchanged) runs only on request: its per-channel output-stage terms
-    // live in registers, but its byte-wise transposed stores cost more than the shared-memory term reads of the
-    // row-major epilogue save (802816 x 256 x 64: 256 us against 237 us).
-    return eight_epilogue_warps(op) ? launch_gemmlowp_tcgen05_epi8(ctx, op, ep, false)
-                                    : launch_gemmlowp_tcgen05_epi4(ctx, op, ep, allow_pair);
+    // The channel-major kernel (operand roles exchanged, output-stage terms in registers, stores through a byte
+    // transpose in shared memory) wins where the epilogue dominates and whole 128-channel blocks exist: measured
+    // 802816 x 256 x 64: 209 us against 235 us row-major; 200704 x 512 x 128: 113 / 125; 50176 x 1024 x 256:
+    // 63 / 70; 12544 x 2048 x 512: 39 / 47; but N = 64: 110 / 78 (half of the lanes idle).
+    GemmOperands o = op;
+    if (o.channel_major == 0)
+    {
+        // with a fused residual the row-major epilogue stays ahead (block-1 conv3 + add: 344 us against 377 us)
+        o.channel_major = (o.K <= kShortK && o.N >= 256 && o.residual == nullptr) ? 1 : -1;
+    }
+    return eight_epilogue_warps(o) ? launch_gemmlowp_tcgen05_epi8(ctx, o, ep, false)
+                                   : launch_gemmlowp_tcgen05_epi4(ctx, o, ep, allow_pair);
 }
 
 bool gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands &cv)

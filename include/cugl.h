@@ -214,8 +214,8 @@ CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
 CUGL_API cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps);
 /* The tensor-core GEMM can also run with the operand roles exchanged, which makes an accumulator lane an output
  * channel (output-stage terms in registers, byte-wise transposed stores; never with a row-sum term or several
- * destinations).  mode > 0 requests it, <= 0 keeps the row-major kernel (the default: it is the faster one on
- * the shapes measured so far).  Testing / measurement aid: the results are identical. */
+ * destinations).  mode > 0 requests it, < 0 forbids it, 0 lets the library choose (short K with at least 256
+ * output channels).  Testing / measurement aid: the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_channel_major(cugl_gemm_plan *plan, int mode);
 /* SM-pair kernel: when the last wave of 256 x 256 tiles fills at most half of the SM pairs, its tiles are
  * processed as two 256 x 128 halves each (on by default).  on = 0 keeps them whole.  Testing / measurement aid:
