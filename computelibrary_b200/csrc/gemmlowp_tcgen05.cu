@@ -259,6 +259,25 @@ __device__ __forceinline__ void epi_barrier()
 {
     asm volatile("bar.sync 2, %0;" ::"n"(kEpiThreads) : "memory");
 }
+// The same two barriers for one of two epilogue groups of four warps (named barriers 3..6).
+__device__ __forceinline__ bool epi_group_barrier_and(bool pred, int group)
+{
+    uint32_t r;
+    asm volatile("{\n\t"
+                 ".reg .pred p, q;\n\t"
+                 "setp.ne.u32 q, %1, 0;\n\t"
+                 "bar.red.and.pred p, %2, 128, q;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t"
+                 "}"
+                 : "=r"(r)
+                 : "r"(static_cast<uint32_t>(pred)), "r"(3 + group)
+                 : "memory");
+    return r != 0;
+}
+__device__ __forceinline__ void epi_group_barrier(int group)
+{
+    asm volatile("bar.sync %0, 128;" ::"r"(5 + group) : "memory");
+}
 
 constexpr int kMaxExtraDst = 7; // push all-gather: this GPU's tile is also stored into up to 7 peers
 
@@ -701,9 +720,9 @@ __device__ __forceinline__ int4 column_term(int n, const TileParams &tp, const E
 // per-column terms of a tile
 template <int BLOCK_N>
 __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, const TileParams &tp,
-                                                  const EpilogueParams &ep)
+                                                  const EpilogueParams &ep, int n_threads = kEpiThreads)
 {
-    for (int c = et; c < BLOCK_N; c += kEpiThreads)
+    for (int c = et; c < BLOCK_N; c += n_threads)
     {
         const int n = n0 + c;
         s_col[c]    = n < tp.N ? column_term(n, tp, ep) : make_int4(0, 0, 0, 0);
@@ -988,15 +1007,17 @@ __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const T
 }
 
 // The part of a tile one epilogue warp owns: lane quarter (warp & 3) and half of the columns.
-template <int BLOCK_N, bool kS32Out>
+// kGroups = 2: the eight epilogue warps form two groups of four that drain alternate tiles, each warp all columns
+// of its 32 rows (narrow tiles, whose time is latency rather than work).
+template <int BLOCK_N, bool kS32Out, int kGroups = 1>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4 *s_col, const TileParams &tp,
                                                    const EpilogueParams &ep, int warp, int lane, int m0, int n0,
                                                    uint8_t *out_stage)
 {
-    constexpr int NCOLS    = BLOCK_N / (kEpiWarps / 4);
+    constexpr int NCOLS    = BLOCK_N * kGroups / (kEpiWarps / 4);
     uint8_t      *stage    = out_stage + (warp - kFirstEpi) * kOutStageBytes;
     const int     quad     = warp & 3;               // tensor-memory lane quarter this warp may read
-    const int     half     = (warp - kFirstEpi) >> 2; // which share of the columns
+    const int     half     = kGroups == 1 ? (warp - kFirstEpi) >> 2 : 0; // which share of the columns
     const int     m        = m0 + quad * 32 + lane;
     const int32_t row_term = (ep.rowsum != nullptr && m < tp.M) ? ep.b_off * __ldg(ep.rowsum + m) : 0;
     const uint32_t t_addr  = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NCOLS;
@@ -1034,7 +1055,8 @@ struct SmemPlan
     static constexpr int OFF_A      = 0;
     static constexpr int OFF_B      = STAGES * A_STAGE_K;
     static constexpr int OFF_COL    = STAGES * STAGE;             // int4 per column
-    static constexpr int OFF_BAR    = OFF_COL + BLOCK_N * 16;     // full[S], empty[S], tfull[ACC], tempty[ACC]
+    static constexpr int EPI_GROUPS = (kEpiWarps == 8 && BLOCK_N <= 128) ? 2 : 1; // see epilogue_warp_tile
+    static constexpr int OFF_BAR    = OFF_COL + EPI_GROUPS * BLOCK_N * 16; // full[S], empty[S], tfull[ACC], tempty[ACC]
     static constexpr int OFF_MISC   = OFF_BAR + (2 * STAGES + 2 * ACC) * 8; // tmem base, abort flag
     static constexpr int OFF_OUT    = OFF_MISC + 16;              // per epilogue warp: 32 rows x 128 bytes of output
     static constexpr int TOTAL      = OFF_OUT + kEpiWarps * kOutStageBytes;
@@ -1046,12 +1068,12 @@ struct SmemPlan
 // activation matrix, tp.M the number of output channels and tp.N the number of output rows -- so the
 // accumulator holds the transposed output tile and epilogue_warp_tile_cm writes it (see there).  Tiles are then
 // ordered n-fastest, i.e. all row blocks of one channel block in turn.
-template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kCM>
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kCM, int ACC>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                             const __grid_constant__ TileParams tp, const EpilogueParams ep)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -1062,7 +1084,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     auto           full_bar   = [&](int s) { return bar_base + 8u * s; };
     auto           empty_bar  = [&](int s) { return bar_base + 8u * (STAGES + s); };
     auto           tfull_bar  = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
-    auto           tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+    auto           tempty_bar = [&](int a) { return bar_base + 8u * (2 * STAGES + ACC + a); };
     uint32_t      *s_tmem     = reinterpret_cast<uint32_t *>(smem + P::OFF_MISC);
     volatile int  *s_abort    = reinterpret_cast<volatile int *>(smem + P::OFF_MISC + 4);
 
@@ -1081,10 +1103,10 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
         }
-        for (int a = 0; a < 2; ++a)
+        for (int a = 0; a < ACC; ++a)
         {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kEpiWarps);
+            mbar_init(tempty_bar(a), kEpiWarps / (kCM ? 1 : P::EPI_GROUPS)); // the warps of the group that drains it
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1255,7 +1277,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     trace_event(tp.trace, ti, 3);
                     trace_value(tp.trace, ti, 6, waited); // clocks spent waiting for operands
                 }
-                if (++as == 2)
+                if (++as == ACC)
                 {
                     as = 0;
                     aph ^= 1;
@@ -1267,25 +1289,35 @@ __global__ void __launch_bounds__(kThreads, 1)
     else
     {
         // ---------------------------------------------------------------- epilogue (warps 2..9)
-        const int et = threadIdx.x - 32 * kFirstEpi; // 0 .. kEpiThreads-1
-        int       as = 0;
-        uint32_t  aph = 0;
-        bool      ok = true;
-        int       ti = 0;
-        int       filled_n0 = -1;
+        // One group of all epilogue warps, or (narrow tiles, eight warps) two groups of four draining alternate
+        // tiles: accumulator buffer and phase follow from the tile ordinal, so the groups need not talk.
+        constexpr int kGroups = kCM ? 1 : P::EPI_GROUPS;
+        const int     group   = kGroups == 1 ? 0 : (warp - kFirstEpi) >> 2;
+        const int     et      = threadIdx.x - 32 * kFirstEpi - group * 128; // thread index inside the group
+        int4         *g_col   = s_col + group * BLOCK_N;
+        bool          ok      = true;
+        int           ti = 0;
+        int           filled_n0 = -1;
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti)
         {
-            if (!epi_barrier_and(ok))
+            if (kGroups > 1 && (ti & 1) != group)
+            {
+                continue;
+            }
+            if (!(kGroups == 1 ? epi_barrier_and(ok) : epi_group_barrier_and(ok, group)))
             {
                 break;
             }
-            const int m0 = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
-            const int n0 = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
+            const int      as  = ti % ACC;
+            const uint32_t aph = static_cast<uint32_t>(ti / ACC) & 1u;
+            const int      m0  = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
+            const int      n0  = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
             if (!kCM && n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
             {
-                fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+                fill_column_terms<BLOCK_N>(g_col, et, n0, tp, ep, kEpiThreads / kGroups);
                 filled_n0 = n0;
-                epi_barrier();
+                if (kGroups == 1) epi_barrier();
+                else epi_group_barrier(group);
             }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok)
@@ -1299,8 +1331,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 else
                 {
-                    epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                         smem + P::OFF_OUT);
+                    epilogue_warp_tile<BLOCK_N, kS32Out, kGroups>(tmem_base + as * BLOCK_N, g_col, tp, ep, warp, lane,
+                                                                  m0, n0, smem + P::OFF_OUT);
                 }
                 tc_fence_before();
                 __syncwarp();
@@ -1309,11 +1341,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     mbar_arrive(tempty_bar(as)); // accumulator buffer may be overwritten (one arrival per warp)
                 }
-            }
-            if (++as == 2)
-            {
-                as = 0;
-                aph ^= 1;
             }
         }
     }
@@ -1764,7 +1791,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         for (int a = 0; a < ACC; ++a)
         {
             mbar_init(tfull_bar(a), 1);
-            mbar_init(tempty_bar(a), kEpiWarps);
+            mbar_init(tempty_bar(a), kEpiWarps / P::EPI_GROUPS); // the warps of the group that drains it
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1881,34 +1908,42 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     }
     else if (warp < kFirstGather)
     {
-        // ---------------------------------------------------------------- epilogue
-        const int et = threadIdx.x - 32 * kFirstEpi;
-        int       as = 0;
-        uint32_t  aph = 0;
-        bool      ok = true;
-        int       filled_n0 = -1;
+        // ---------------------------------------------------------------- epilogue (groups as in the GEMM kernel)
+        constexpr int kGroups = P::EPI_GROUPS;
+        const int     group   = kGroups == 1 ? 0 : (warp - kFirstEpi) >> 2;
+        const int     et      = threadIdx.x - 32 * kFirstEpi - group * 128;
+        int4         *g_col   = s_col + group * BLOCK_N;
+        bool          ok      = true;
+        int           filled_n0 = -1;
         for (int ti = 0; ti < my_tiles; ++ti)
         {
-            if (!epi_barrier_and(ok))
+            if (kGroups > 1 && (ti & 1) != group)
+            {
+                continue;
+            }
+            if (!(kGroups == 1 ? epi_barrier_and(ok) : epi_group_barrier_and(ok, group)))
             {
                 break;
             }
-            const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
-            const int m0   = (tile % num_m_blocks) * BLOCK_M;
-            const int n0   = (tile / num_m_blocks) * BLOCK_N;
+            const int      as   = ti % ACC;
+            const uint32_t aph  = static_cast<uint32_t>(ti / ACC) & 1u;
+            const int      tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
+            const int      m0   = (tile % num_m_blocks) * BLOCK_M;
+            const int      n0   = (tile / num_m_blocks) * BLOCK_N;
             if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
             {
-                fill_column_terms<BLOCK_N>(s_col, et, n0, tp, ep);
+                fill_column_terms<BLOCK_N>(g_col, et, n0, tp, ep, kEpiThreads / kGroups);
                 filled_n0 = n0;
-                epi_barrier();
+                if (kGroups == 1) epi_barrier();
+                else epi_group_barrier(group);
             }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
-                epilogue_warp_tile<BLOCK_N, false>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                   smem + P::OFF_OUT);
+                epilogue_warp_tile<BLOCK_N, false, kGroups>(tmem_base + as * BLOCK_N, g_col, tp, ep, warp, lane, m0, n0,
+                                                            smem + P::OFF_OUT);
                 if (et == 0) trace_event(tp.trace, ti, 5);
                 tc_fence_before();
                 __syncwarp();
@@ -1916,11 +1951,6 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 {
                     mbar_arrive(tempty_bar(as));
                 }
-            }
-            if (++as == ACC)
-            {
-                as = 0;
-                aph ^= 1;
             }
         }
     }
@@ -2078,7 +2108,8 @@ bool encode_operand_map(CUtensorMap *map, const void *base, int rows, int K, int
 template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
 cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB>;
+    constexpr int ACC = BLOCK_N <= 128 ? 4 : 2; // narrow tiles: four accumulator buffers in the 512 columns
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     CUtensorMap map_a, map_b;
     if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
@@ -2086,7 +2117,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
-    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false>;
+    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false, ACC>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
     {
@@ -2126,7 +2157,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
-    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, true>;
+    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, true, 2>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
     {

@@ -1,5 +1,5 @@
 // Minimal stand-ins for the arm_compute core types the quantized GEMM path touches: DataType, DataLayout,
-// TensorShape, Strides, Size2D, PadStrideInfo, WeightsInfo.  Member names and meanings follow the library
+// TensorShape, Strides, Size2D, PadStrideInfo, WeightsInfo, PoolingLayerInfo, ConvertPolicy.  Member names and meanings follow the library
 // (arm_compute/core/CoreTypes.h, TensorShape.h, Types.h); only what the CUDA functions use is present.
 #pragma once
 #include <array>
@@ -129,6 +129,43 @@ private:
     std::pair<unsigned int, unsigned int> _stride;
     unsigned int                          _l, _t, _r, _b;
     DimensionRoundingType                 _round;
+};
+
+enum class ConvertPolicy
+{
+    WRAP,
+    SATURATE
+};
+enum class PoolingType
+{
+    MAX,
+    AVG,
+    L2
+};
+// arm_compute/core/Types.h (PoolingLayerInfo): global pooling has a zero pool size.
+struct PoolingLayerInfo
+{
+    PoolingLayerInfo() = default;
+    PoolingLayerInfo(PoolingType type, unsigned int size, DataLayout layout, PadStrideInfo psi = PadStrideInfo(),
+                     bool exclude_pad = false)
+        : pool_type(type), pool_size(size, size), data_layout(layout), pad_stride_info(psi), exclude_padding(exclude_pad)
+    {
+    }
+    PoolingLayerInfo(PoolingType type, Size2D size, DataLayout layout, PadStrideInfo psi = PadStrideInfo(),
+                     bool exclude_pad = false)
+        : pool_type(type), pool_size(size), data_layout(layout), pad_stride_info(psi), exclude_padding(exclude_pad)
+    {
+    }
+    PoolingLayerInfo(PoolingType type, DataLayout layout) // global pooling
+        : pool_type(type), pool_size(0, 0), data_layout(layout), is_global_pooling(true)
+    {
+    }
+    PoolingType   pool_type{PoolingType::MAX};
+    Size2D        pool_size{};
+    DataLayout    data_layout{DataLayout::UNKNOWN};
+    PadStrideInfo pad_stride_info{};
+    bool          exclude_padding{false};
+    bool          is_global_pooling{false};
 };
 
 // Convolution weights descriptor; the quantized GEMM path only checks that weights are not pre-reshaped.

@@ -8,8 +8,11 @@
 #include "arm_compute/runtime/CUDA/functions/CUGEMMConvolutionLayer.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMLowpMatrixMultiplyCore.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMLowpOutputStage.h"
+#include "arm_compute/runtime/CUDA/functions/CUQuantizedLayers.h"
 
+#include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <random>
 #include <vector>
@@ -29,6 +32,16 @@ extern "C"
                          int pad_t, int dil_x, int dil_y, int Wo, int Ho, int32_t in_zp, int32_t w_zp,
                          const int32_t *mult, const int32_t *shift, int n_mult, int32_t out_offset, int32_t lo,
                          int32_t hi);
+    // oracle/layers_oracle.c
+    void orc_pool_nhwc_u8(const uint8_t *src, uint8_t *dst, int C, int W, int H, int B, int pool_type, int pw, int ph,
+                          int sx, int sy, int pl, int pr, int pt, int pb, int exclude_padding, int Wo, int Ho,
+                          float in_scale, int in_zp, float out_scale, int out_zp);
+    void orc_add_qasymm8(const uint8_t *a, const uint8_t *b, uint8_t *dst, long long n, float a_scale, int a_zp,
+                         float b_scale, int b_zp, float o_scale, int o_zp);
+    void orc_activation_qasymm8(const uint8_t *src, uint8_t *dst, long long n, int act, float a, float b,
+                                float in_scale, int in_zp, float out_scale, int out_zp);
+    void orc_softmax_qasymm8(const uint8_t *src, uint8_t *dst, int rows, int cols, float beta, float in_scale,
+                             int in_zp);
 }
 
 static int g_failures = 0;
@@ -241,17 +254,111 @@ static void test_convolution()
     CHECK(download<uint8_t>(dst, want.size()) == want);
 }
 
+static TensorInfo u8_nhwc(const TensorShape &shape, float scale, int zp)
+{
+    TensorInfo t(shape, 1, DataType::QASYMM8, QuantizationInfo(scale, zp));
+    t.set_data_layout(DataLayout::NHWC);
+    return t;
+}
+
+static void test_validate_layers()
+{
+    TensorInfo in  = u8_nhwc(TensorShape(64, 112, 112, 2), 0.05f, 0);
+    TensorInfo out = u8_nhwc(TensorShape(64, 56, 56, 2), 0.05f, 0);
+    const PoolingLayerInfo pool1(PoolingType::MAX, 3, DataLayout::NHWC, PadStrideInfo(2, 2, 0, 1, 0, 1, DimensionRoundingType::FLOOR));
+    CHECK(bool(CUPoolingLayer::validate(&in, &out, pool1)));
+    CHECK(!bool(CUPoolingLayer::validate(&in, &in, pool1)));                                   // wrong output shape
+    CHECK(!bool(CUPoolingLayer::validate(&in, &out, PoolingLayerInfo(PoolingType::L2, 3, DataLayout::NHWC,
+                                                                     PadStrideInfo(2, 2, 0, 1, 0, 1, DimensionRoundingType::FLOOR)))));
+    TensorInfo g_out = u8_nhwc(TensorShape(64, 1, 1, 2), 0.05f, 0);
+    CHECK(bool(CUPoolingLayer::validate(&in, &g_out, PoolingLayerInfo(PoolingType::AVG, DataLayout::NHWC))));
+    CHECK(bool(CUArithmeticAddition::validate(&in, &in, &in, ConvertPolicy::SATURATE,
+                                              ActivationLayerInfo(ActivationLayerInfo::ActivationFunction::RELU))));
+    CHECK(!bool(CUArithmeticAddition::validate(&in, &in, &in, ConvertPolicy::WRAP)));
+    CHECK(!bool(CUArithmeticAddition::validate(&in, &out, &in, ConvertPolicy::SATURATE)));      // no broadcasting
+    CHECK(bool(CUActivationLayer::validate(&in, nullptr, ActivationLayerInfo(ActivationLayerInfo::ActivationFunction::BOUNDED_RELU, 6.f))));
+    CHECK(!bool(CUActivationLayer::validate(&in, nullptr, ActivationLayerInfo())));
+    TensorInfo logits(TensorShape(1000, 4), 1, DataType::QASYMM8, QuantizationInfo(0.05f, 0));
+    TensorInfo probs(TensorShape(1000, 4), 1, DataType::QASYMM8, QuantizationInfo(1.f / 256.f, 0));
+    CHECK(bool(CUSoftmaxLayer::validate(&logits, &probs)));
+    CHECK(!bool(CUSoftmaxLayer::validate(&logits, &logits)));                                   // output quantization is fixed
+    CHECK(!bool(CUSoftmaxLayer::validate(&logits, &probs, 1.f, 1)));
+}
+
+// pool1 -> (x + x') -> ReLU -> bounded ReLU -> global average -> softmax, every step against the oracle
+static void test_layers()
+{
+    const int C = 32, W = 20, H = 18, B = 2, Wo = 10, Ho = 9;
+    const float s = 0.05f;
+    CUTensor src, pooled, other, sum, act, avg, probs;
+    src.allocator()->init(u8_nhwc(TensorShape(C, W, H, B), s, 3));
+    pooled.allocator()->init(u8_nhwc(TensorShape(C, Wo, Ho, B), 0.06f, 5));
+    other.allocator()->init(u8_nhwc(TensorShape(C, Wo, Ho, B), 0.04f, 9));
+    sum.allocator()->init(u8_nhwc(TensorShape(C, Wo, Ho, B), 0.07f, 12));
+    act.allocator()->init(u8_nhwc(TensorShape(C, Wo, Ho, B), 0.07f, 12));
+    avg.allocator()->init(u8_nhwc(TensorShape(C, 1, 1, B), 0.07f, 12));
+    TensorInfo pinfo(TensorShape(C, B), 1, DataType::QASYMM8, QuantizationInfo(1.f / 256.f, 0));
+    probs.allocator()->init(pinfo);
+    CUPoolingLayer       pool, gap;
+    CUArithmeticAddition add;
+    CUActivationLayer    relu6;
+    CUSoftmaxLayer       softmax;
+    pool.configure(&src, &pooled, PoolingLayerInfo(PoolingType::MAX, 3, DataLayout::NHWC,
+                                                   PadStrideInfo(2, 2, 0, 1, 0, 1, DimensionRoundingType::FLOOR)));
+    add.configure(&pooled, &other, &sum, ConvertPolicy::SATURATE,
+                  ActivationLayerInfo(ActivationLayerInfo::ActivationFunction::RELU));
+    relu6.configure(&sum, &act, ActivationLayerInfo(ActivationLayerInfo::ActivationFunction::BOUNDED_RELU, 6.f));
+    gap.configure(&act, &avg, PoolingLayerInfo(PoolingType::AVG, DataLayout::NHWC));
+    // softmax over the channels of the pooled vector: view avg [C,1,1,B] as [C,B]
+    CUTensor avg2d;
+    TensorInfo a2(TensorShape(C, B), 1, DataType::QASYMM8, QuantizationInfo(0.07f, 12));
+    avg2d.allocator()->init(a2);
+    for (CUTensor *t : {&src, &pooled, &other, &sum, &act, &avg, &probs}) t->allocator()->allocate();
+    avg2d.allocator()->import_memory(avg.device_ptr());
+    softmax.configure(&avg2d, &probs);
+    std::vector<uint8_t> hsrc(size_t(B) * H * W * C), hother(size_t(B) * Ho * Wo * C);
+    fill_uniform(hsrc, 0, 255, 11);
+    fill_uniform(hother, 0, 255, 12);
+    upload(src, hsrc);
+    upload(other, hother);
+    pool.run();
+    add.run();
+    relu6.run();
+    gap.run();
+    softmax.run();
+    CUScheduler::get().sync();
+
+    const size_t n = size_t(B) * Ho * Wo * C;
+    std::vector<uint8_t> w_pool(n), w_sum(n), w_relu(n), w_act(n), w_avg(size_t(B) * C), w_probs(size_t(B) * C);
+    orc_pool_nhwc_u8(hsrc.data(), w_pool.data(), C, W, H, B, 0, 3, 3, 2, 2, 0, 1, 0, 1, 0, Wo, Ho, s, 3, 0.06f, 5);
+    orc_add_qasymm8(w_pool.data(), hother.data(), w_sum.data(), (long long)n, 0.06f, 5, 0.04f, 9, 0.07f, 12);
+    orc_activation_qasymm8(w_sum.data(), w_relu.data(), (long long)n, 0, 0.f, 0.f, 0.07f, 12, 0.07f, 12);
+    orc_activation_qasymm8(w_relu.data(), w_act.data(), (long long)n, 1, 6.f, 0.f, 0.07f, 12, 0.07f, 12);
+    orc_pool_nhwc_u8(w_act.data(), w_avg.data(), C, Wo, Ho, B, 1, Wo, Ho, 1, 1, 0, 0, 0, 0, 0, 1, 1, 0.07f, 12, 0.07f, 12);
+    orc_softmax_qasymm8(w_avg.data(), w_probs.data(), B, C, 1.f, 0.07f, 12);
+    CHECK(download<uint8_t>(pooled, n) == w_pool);
+    CHECK(download<uint8_t>(sum, n) == w_relu);
+    CHECK(download<uint8_t>(act, n) == w_act);
+    CHECK(download<uint8_t>(avg, w_avg.size()) == w_avg);
+    const std::vector<uint8_t> got = download<uint8_t>(probs, w_probs.size());
+    int worst = 0;
+    for (size_t i = 0; i < got.size(); ++i) worst = std::max(worst, std::abs(int(got[i]) - int(w_probs[i])));
+    CHECK(worst <= 1);
+}
+
 int main(int argc, char **argv)
 {
     const bool validate_only = argc > 1 && std::strcmp(argv[1], "--validate") == 0;
     try
     {
         test_validate();
+        test_validate_layers();
         if (!validate_only)
         {
             CUScheduler::get().default_init(0);
             test_gemmlowp_config1();
             test_convolution();
+            test_layers();
         }
     }
     catch (const std::exception &e)
