@@ -238,10 +238,16 @@ struct cugl_gemm_plan
     // staging for the host-buffer entry point
     void    *d_a_stage = nullptr, *d_dst_stage = nullptr;
     int32_t *d_bias_stage = nullptr;
+    // cugl_gemmlowp_run_host pipelines row blocks over three streams: copies in, GEMM (the context's stream),
+    // copies out
+    cudaStream_t             s_in = nullptr, s_out = nullptr;
+    std::vector<cudaEvent_t> ev_in, ev_done;
 };
 
 namespace
 {
+constexpr int kHostPipelineBlocks = 8;
+
 void apply_quant_fields(cugl_gemm_plan *p, const cugl_gemm_desc *d)
 {
     GemmCore &c     = p->core;
@@ -348,6 +354,10 @@ extern "C"
         cugl_free(plan->ctx, plan->d_a_stage);
         cugl_free(plan->ctx, plan->d_dst_stage);
         cugl_free(plan->ctx, plan->d_bias_stage);
+        for (cudaEvent_t e : plan->ev_in) cudaEventDestroy(e);
+        for (cudaEvent_t e : plan->ev_done) cudaEventDestroy(e);
+        if (plan->s_in != nullptr) cudaStreamDestroy(plan->s_in);
+        if (plan->s_out != nullptr) cudaStreamDestroy(plan->s_out);
         delete plan;
     }
 
@@ -447,13 +457,64 @@ extern "C"
             CUGL_TRY(cugl_malloc(ctx, d_bytes, &plan->d_dst_stage));
             CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * d.N, reinterpret_cast<void **>(&plan->d_bias_stage)));
         }
+        if (d.has_bias && h_bias == nullptr)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_host: plan was configured with a bias");
+        }
+        // Large single-batch products run as a pipeline over row blocks: block i+1 travels to the device while
+        // block i is multiplied and block i-1 travels back (PCIe is full duplex), so the call costs about the
+        // longer of the two copies instead of copy + GEMM + copy.  Pinned host buffers are needed for the overlap;
+        // pageable ones still work, serialised by the driver.
+        const int rows_per = static_cast<int>(round_up((d.M + kHostPipelineBlocks - 1) / kHostPipelineBlocks, 256));
+        if (d.batch == 1 && d.M >= 2048 && d.M > rows_per)
+        {
+            if (plan->s_in == nullptr)
+            {
+                CUGL_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&plan->s_in, cudaStreamNonBlocking));
+                CUGL_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&plan->s_out, cudaStreamNonBlocking));
+                plan->ev_in.resize(kHostPipelineBlocks + 1);
+                plan->ev_done.resize(kHostPipelineBlocks + 1);
+                for (cudaEvent_t &e : plan->ev_in) CUGL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+                for (cudaEvent_t &e : plan->ev_done) CUGL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
+            }
+            const int      n_blocks = (d.M + rows_per - 1) / rows_per;
+            const uint8_t *ha       = static_cast<const uint8_t *>(h_a);
+            uint8_t       *da       = static_cast<uint8_t *>(plan->d_a_stage);
+            uint8_t       *dd       = static_cast<uint8_t *>(plan->d_dst_stage);
+            uint8_t       *hd       = static_cast<uint8_t *>(h_dst);
+            // the staging buffers are free: every earlier call ended with a synchronisation of all three streams
+            if (d.has_bias)
+            {
+                CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(plan->d_bias_stage, h_bias, sizeof(int32_t) * d.N, cudaMemcpyHostToDevice,
+                                                   plan->s_in));
+            }
+            for (int i = 0; i < n_blocks; ++i)
+            {
+                const int    r0   = i * rows_per;
+                const size_t rows = static_cast<size_t>(d.M - r0 < rows_per ? d.M - r0 : rows_per);
+                CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(da + static_cast<size_t>(r0) * d.lda, ha + static_cast<size_t>(r0) * d.lda,
+                                                   rows * d.lda, cudaMemcpyHostToDevice, plan->s_in));
+                CUGL_CUDA_TRY(ctx, cudaEventRecord(plan->ev_in[i], plan->s_in));
+            }
+            for (int i = 0; i < n_blocks; ++i)
+            {
+                const int r0   = i * rows_per;
+                const int rows = d.M - r0 < rows_per ? d.M - r0 : rows_per;
+                CUGL_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, plan->ev_in[i], 0));
+                CUGL_TRY(plan->core.gemm(da + static_cast<size_t>(r0) * d.lda, d.lda, rows, dd + static_cast<size_t>(r0) * d.ldd,
+                                         d.ldd, d.has_bias ? plan->d_bias_stage : nullptr, 0, r0));
+                CUGL_CUDA_TRY(ctx, cudaEventRecord(plan->ev_done[i], ctx->stream));
+                CUGL_CUDA_TRY(ctx, cudaStreamWaitEvent(plan->s_out, plan->ev_done[i], 0));
+                CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(hd + static_cast<size_t>(r0) * d.ldd, dd + static_cast<size_t>(r0) * d.ldd,
+                                                   static_cast<size_t>(rows) * d.ldd, cudaMemcpyDeviceToHost, plan->s_out));
+            }
+            CUGL_CUDA_TRY(ctx, cudaStreamSynchronize(plan->s_out));
+            CUGL_CUDA_TRY(ctx, cudaStreamSynchronize(plan->s_in));
+            return cugl_sync(ctx);
+        }
         CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_a_stage, h_a, a_bytes));
         if (d.has_bias)
         {
-            if (h_bias == nullptr)
-            {
-                return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_run_host: plan was configured with a bias");
-            }
             CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_bias_stage, h_bias, sizeof(int32_t) * d.N));
         }
         CUGL_TRY(cugl_gemmlowp_run(plan, plan->d_a_stage, nullptr, plan->d_bias_stage, plan->d_dst_stage));

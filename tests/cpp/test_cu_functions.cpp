@@ -5,6 +5,7 @@
 //   test_cu_functions              everything, on cuda:0
 #include "arm_compute/runtime/CUDA/CUScheduler.h"
 #include "arm_compute/runtime/CUDA/CUTensor.h"
+#include "arm_compute/runtime/CUDA/functions/CUFullyConnectedLayer.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMConvolutionLayer.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMLowpMatrixMultiplyCore.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMLowpOutputStage.h"
@@ -346,6 +347,53 @@ static void test_layers()
     CHECK(worst <= 1);
 }
 
+// NEFullyConnectedLayer semantics: logits = x * W^T + b on a [num_inputs, batch] input, both weight layouts
+static void test_fully_connected()
+{
+    const int K = 512, N = 200, B = 37;
+    std::vector<uint8_t> hx(size_t(B) * K);
+    std::vector<int8_t>  hw(size_t(N) * K); // one row per output neuron
+    std::vector<int32_t> hb(N);
+    fill_uniform(hx, 0, 255, 21);
+    fill_uniform(hw, -127, 127, 22);
+    fill_uniform(hb, -3000, 3000, 23);
+    std::vector<int8_t> hw_t(size_t(K) * N), b_kn(size_t(K) * N); // [K][N]
+    for (int n = 0; n < N; ++n)
+        for (int k = 0; k < K; ++k) b_kn[size_t(k) * N + n] = hw_t[size_t(k) * N + n] = hw[size_t(n) * K + k];
+    int32_t mult = 0, shift = 0;
+    CHECK(cugl_calculate_quantized_multiplier(0.05f * 0.004f / 0.1f, &mult, &shift) == CUGL_SUCCESS);
+    std::vector<uint8_t> want(size_t(B) * N);
+    // offsets as the operator passes them to the core: negated zero points; ReLU = clamp at the output zero point
+    orc_gemmlowp_fused(hx.data(), 0, b_kn.data(), 1, hb.data(), want.data(), 0, B, N, K, -7, 0, &mult, &shift, 1, 20, 20, 255);
+    for (int transposed = 1; transposed >= 0; --transposed)
+    {
+        CUTensor x, w, b, y;
+        x.allocator()->init(TensorInfo(TensorShape(K, B), 1, DataType::QASYMM8, QuantizationInfo(0.05f, 7)));
+        w.allocator()->init(TensorInfo(transposed ? TensorShape(K, N) : TensorShape(N, K), 1, DataType::QSYMM8,
+                                       QuantizationInfo(0.004f, 0)));
+        b.allocator()->init(TensorInfo(TensorShape(N), 1, DataType::S32));
+        y.allocator()->init(TensorInfo(TensorShape(N, B), 1, DataType::QASYMM8, QuantizationInfo(0.1f, 20)));
+        FullyConnectedLayerInfo info;
+        info.transpose_weights = transposed != 0;
+        info.activation_info   = ActivationLayerInfo(ActivationLayerInfo::ActivationFunction::RELU);
+        CHECK(bool(CUFullyConnectedLayer::validate(x.info(), w.info(), b.info(), y.info(), info)));
+        CUFullyConnectedLayer fc;
+        fc.configure(&x, &w, &b, &y, info);
+        for (CUTensor *t : {&x, &w, &b, &y}) t->allocator()->allocate();
+        upload(x, hx);
+        upload(w, transposed ? hw : hw_t);
+        upload(b, hb);
+        fc.run();
+        fc.run();
+        CUScheduler::get().sync();
+        CHECK(download<uint8_t>(y, want.size()) == want);
+    }
+    TensorInfo bad_w(TensorShape(K + 16, N), 1, DataType::QSYMM8, QuantizationInfo(0.004f, 0));
+    TensorInfo xi(TensorShape(K, B), 1, DataType::QASYMM8, QuantizationInfo(0.05f, 7));
+    TensorInfo yi(TensorShape(N, B), 1, DataType::QASYMM8, QuantizationInfo(0.1f, 20));
+    CHECK(!bool(CUFullyConnectedLayer::validate(&xi, &bad_w, nullptr, &yi)));
+}
+
 int main(int argc, char **argv)
 {
     const bool validate_only = argc > 1 && std::strcmp(argv[1], "--validate") == 0;
@@ -359,6 +407,7 @@ int main(int argc, char **argv)
             test_gemmlowp_config1();
             test_convolution();
             test_layers();
+            test_fully_connected();
         }
     }
     catch (const std::exception &e)

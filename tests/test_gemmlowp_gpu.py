@@ -172,24 +172,30 @@ def test_update_quantization_parameters(ctx, port):
     plan.close()
 
 
-def test_run_host_end_to_end(ctx, port):
-    """The host-buffer entry point: pinned buffers in, pinned buffers out."""
+@pytest.mark.parametrize("shape,b_dtype,b_off", [((256, 192, 128), np.int8, 0), ((2600, 320, 192), np.int8, 0),
+                                                 ((4099, 136, 80), np.uint8, -7)])
+def test_run_host_end_to_end(ctx, port, shape, b_dtype, b_off):
+    """The host-buffer entry point: pinned buffers in, pinned buffers out; from 2048 rows on the call pipelines
+    row blocks (copy in / multiply / copy out) over three streams, with ragged last blocks and row sums."""
     import ctypes as C
     rng = np.random.default_rng(10)
-    M, N, K = 256, 192, 128
-    a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), np.int8)
+    M, N, K = shape
+    a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), b_dtype)
     bias = rng.integers(-1000, 1000, N).astype(np.int32)
     import torch
-    desc, keep = capi.make_gemm_desc(M, N, K, capi.U8, capi.S8, capi.U8, -128, 0, multiplier=2 ** 30, shift=9,
-                                     offset=3, min_bound=0, max_bound=255, has_bias=True)
+    desc, keep = capi.make_gemm_desc(M, N, K, capi.U8, capi.S8 if b_dtype == np.int8 else capi.U8, capi.U8, -128, b_off,
+                                     multiplier=2 ** 30, shift=9, offset=3, min_bound=0, max_bound=255, has_bias=True)
     plan = capi.GemmPlan(ctx, desc, keep)
-    plan.prepare(torch.from_numpy(b).cuda())
+    plan.prepare(torch.from_numpy(b.view(np.uint8)).cuda())
     h_a, h_d, h_b = ctx.host_alloc(M * K), ctx.host_alloc(M * N), ctx.host_alloc(N * 4)
     C.memmove(h_a, a.ctypes.data, M * K)
     C.memmove(h_b, bias.ctypes.data, N * 4)
-    plan.run_host(h_a, h_b, h_d)
-    got = np.ctypeslib.as_array((C.c_uint8 * (M * N)).from_address(h_d)).reshape(M, N).copy()
-    assert np.array_equal(got, port.gemmlowp_fused(a, b, bias, -128, 0, [2 ** 30], [9], 3, 0, 255, np.uint8))
+    want = port.gemmlowp_fused(a, b, bias, -128, b_off, [2 ** 30], [9], 3, 0, 255, np.uint8)
+    for _ in range(2):
+        C.memset(h_d, 0xEE, M * N)
+        plan.run_host(h_a, h_b, h_d)
+        got = np.ctypeslib.as_array((C.c_uint8 * (M * N)).from_address(h_d)).reshape(M, N).copy()
+        assert np.array_equal(got, want)
     for p in (h_a, h_d, h_b):
         ctx.host_free(p)
     plan.close()
