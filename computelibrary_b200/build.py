@@ -18,7 +18,8 @@ CSRC = os.path.join(PKG, "csrc")
 LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libcugl.so")
 SOURCES = ["context.cu", "bandwidth_kernels.cu", "gemmlowp_simt.cu", "gemmlowp_tcgen05.cu", "plans.cu", "noalloc.cu",
-           "layer_kernels.cu", "gemmlowp_tcgen05_epi8.cu", "gemmlowp_dispatch.cu"]
+           "layer_kernels.cu", "gemmlowp_tcgen05_epi8.cu", "gemmlowp_tcgen05_epi16.cu",
+           "gemmlowp_dispatch.cu"]
 HEADERS = ["common.cuh", "kernels.cuh"]
 
 NVCC_FLAGS = [

@@ -1,4 +1,4 @@
-// Chooses between the two builds of the tensor-core kernels (four or eight epilogue warps, see
+// Chooses between the builds of the tensor-core kernels (four, eight or sixteen epilogue warps, see
 // gemmlowp_tcgen05.cu).  The main loop of a 128 x 256 tile takes about 128 clocks per 32 bytes of K; its
 // epilogue takes a fixed few thousand clocks with four warps.  Up to kShortK the epilogue is the longer of the
 // two and gets eight warps; beyond it the main loop is, and extra resident warps only slow its single-thread
@@ -45,6 +45,11 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
     {
         // with a fused residual the row-major epilogue stays ahead (block-1 conv3 + add: 344 us against 377 us)
         o.channel_major = (o.K <= kShortK && o.N >= 256 && o.residual == nullptr) ? 1 : -1;
+    }
+    // sixteen epilogue warps (256-column tiles only) buy another 4 - 7 % on short K with wide outputs
+    if (o.N > 128 && (o.epi_warps == 16 || (o.epi_warps != 4 && o.epi_warps != 8 && o.K <= kShortK)))
+    {
+        return launch_gemmlowp_tcgen05_epi16(ctx, o, ep, false);
     }
     return eight_epilogue_warps(o) ? launch_gemmlowp_tcgen05_epi8(ctx, o, ep, false)
                                    : launch_gemmlowp_tcgen05_epi4(ctx, o, ep, allow_pair);

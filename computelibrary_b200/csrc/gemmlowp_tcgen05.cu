@@ -54,7 +54,10 @@ constexpr int      kFirstEpi   = kProdWarps + 1;           // first epilogue war
 constexpr int      kEpiWarps   = CUGL_EPI_WARPS;           // a multiple of 4: one or two per tensor-memory lane quarter
 constexpr int      kEpiThreads = kEpiWarps * 32;
 constexpr int      kThreads    = 32 * (kProdWarps + 1) + kEpiThreads;
-static_assert(kEpiWarps == 4 || kEpiWarps == 8, "epilogue warps: 4 or 8");
+static_assert(kEpiWarps == 4 || kEpiWarps == 8 || kEpiWarps == 16, "epilogue warps: 4, 8 or 16");
+// The sixteen-warp build holds only the one-CTA GEMM kernels with 256-column tiles (row-major and channel-major):
+// the kernels for short K and wide outputs, whose epilogue wants the most latency hiding.
+#define CUGL_TC_FULL_BUILD (CUGL_EPI_WARPS <= 8)
 constexpr int      A_STAGE     = BLOCK_M * BLOCK_K;
 constexpr long long kSpinLimit = 4000000000ll; // clock64 ticks, about two seconds
 
@@ -522,10 +525,12 @@ __device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col
 // (piece p of row r at p ^ (r & (pieces - 1)): conflict-free both ways) and then stores them with one lane per
 // piece, kOutRowBytes contiguous bytes per row, to every destination.  128 bytes per row with four epilogue
 // warps, 64 with eight (shared memory holds 32 KB of staging at most beside the operand ring).
-constexpr int kOutRowBytes   = kEpiWarps == 4 ? 128 : 64;
+constexpr int kOutRowBytes   = kEpiWarps == 4 ? 128 : (kEpiWarps == 8 ? 64 : 32);
 constexpr int kOutPieces     = kOutRowBytes / 16;
 constexpr int kOutChunks     = kOutRowBytes / 32; // 32-column chunks per staged group
-constexpr int kOutStageBytes = 32 * kOutRowBytes;
+constexpr int kCmPitchWords  = 36;                // channel-major transpose stage (store_chunk_cm_staged)
+constexpr int kCmStageBytes  = 8 * kCmPitchWords * 4;
+constexpr int kOutStageBytes = 32 * kOutRowBytes > kCmStageBytes ? 32 * kOutRowBytes : kCmStageBytes;
 
 __device__ __forceinline__ void stage_chunk(uint8_t *stage, const uint32_t *w, int group_chunk, int lane)
 {
@@ -641,9 +646,9 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         if (staged)
         {
             stage_chunk(stage, va, ch & (kOutChunks - 1), lane);
-            if (NCOLS / 32 == 1)
+            if (NCOLS / 32 == 1 || kOutChunks == 1) // a staged group holds one chunk only
             {
-                flush_stage(stage, tp, m - lane, n_first, 32, lane);
+                flush_stage(stage, tp, m - lane, n_first + ch * 32, 32, lane);
             }
         }
         else
@@ -742,8 +747,6 @@ __device__ __forceinline__ void fill_column_terms(int4 *s_col, int et, int n0, c
 // 8g .. 8g+7 for rows 4i .. 4i+3, transposes two 4x4 byte blocks with eight byte permutes and stores eight
 // contiguous bytes per row: 4 store instructions per lane and chunk instead of 32 byte stores.  The residual
 // is loaded and added in the same shape.  Needs 8-byte aligned rows (tp.vec_ok) and is called by whole warps.
-constexpr int kCmPitchWords = 36;
-constexpr int kCmStageBytes = 8 * kCmPitchWords * 4;
 
 template <int kMode>
 __device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], const int4 q, const TileParams &tp,
@@ -1360,6 +1363,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 }
 
 
+#if CUGL_TC_FULL_BUILD
 // ---------------------------------------------------------------------------------------------------
 // Two-CTA kernel: a cluster of two CTAs (an SM pair) per 256 x 256 output tile.
 //   CTA rank r stages rows [m0 + 128 r, +128) of A and rows [n0 + 128 r, +128) of Bt (its half of the
@@ -2045,6 +2049,8 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     }
 }
 
+#endif // CUGL_TC_FULL_BUILD
+
 void fill_extra_dst(TileParams &tp, const GemmOperands &op)
 {
     tp.residual   = static_cast<const uint8_t *>(op.residual);
@@ -2185,6 +2191,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel (channel-major)");
 }
 
+#if CUGL_TC_FULL_BUILD
 template <int STAGES, int KSUB, bool kS32Out>
 cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
 {
@@ -2297,6 +2304,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     kernel<<<grid, kConvThreads, kDynBytes, ctx->stream>>>(map_b, tp, ep, cg);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_conv_tcgen05_kernel");
 }
+#endif // CUGL_TC_FULL_BUILD
 } // namespace
 
 bool CUGL_TC_NAME(gemmlowp_tcgen05_supported)(const GemmOperands &op)
@@ -2325,22 +2333,29 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
     {
         return s32 ? launch_variant_cm<256, 4, 1, true>(ctx, op, ep) : launch_variant_cm<256, 4, 1, false>(ctx, op, ep);
     }
+#if CUGL_TC_FULL_BUILD
     if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
     {
         return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);
     }
-    if (op.N > 128)
+#else
+    (void)allow_pair;
+#endif
+    if (op.N > 128 || !CUGL_TC_FULL_BUILD)
     {
         return s32 ? launch_variant<256, 4, 1, true>(ctx, op, ep) : launch_variant<256, 4, 1, false>(ctx, op, ep);
     }
+#if CUGL_TC_FULL_BUILD
     if (op.N > 64)
     {
         return s32 ? launch_variant<128, 3, 2, true>(ctx, op, ep) : launch_variant<128, 3, 2, false>(ctx, op, ep);
     }
     return s32 ? launch_variant<64, 4, 2, true>(ctx, op, ep) : launch_variant<64, 4, 2, false>(ctx, op, ep);
+#endif
 }
 } // namespace cugl
 
+#if CUGL_TC_FULL_BUILD
 namespace cugl
 {
 bool CUGL_TC_NAME(gemmlowp_conv_tcgen05_supported)(const GemmOperands &op, const ConvOperands &cv)
@@ -2374,3 +2389,4 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_conv_tcgen05)(cugl_context *ctx, const 
     return launch_conv_variant<64, 4, 2, 4>(ctx, op, ep, cv);
 }
 } // namespace cugl
+#endif // CUGL_TC_FULL_BUILD

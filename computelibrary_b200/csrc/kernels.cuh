@@ -44,7 +44,7 @@ struct GemmOperands
     bool        generic_stage; // some shift is negative or some multiplier is INT32_MIN (decided on the host)
     bool        wide_stage;    // every shift in [2, 31], every multiplier in [0, 2^31), no row-sum term: the
                                // requantisation can use the one-multiply form (kStageWide)
-    int         epi_warps;     // tensor-core kernels: 4 or 8 forces that build, anything else lets the dispatcher choose
+    int         epi_warps;     // tensor-core kernels: 4, 8 or 16 forces that build, anything else lets the dispatcher choose
     // tensor-core kernels, 8-bit unsigned output only: dst = min(max(min(out + residual, 255), res_floor), res_cap)
     // with residual an [M][ldd] byte matrix (the fused residual addition of a convolution), or nullptr
     const void *residual;
@@ -85,6 +85,9 @@ cugl_status launch_gemmlowp_tcgen05_epi4(cugl_context *ctx, const GemmOperands &
                                          bool allow_pair);
 cugl_status launch_gemmlowp_tcgen05_epi8(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                          bool allow_pair);
+// sixteen epilogue warps: 256-column one-CTA tiles only (op.N is not looked at)
+cugl_status launch_gemmlowp_tcgen05_epi16(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
+                                          bool allow_pair);
 
 // Generic CUDA-core kernel: any shape, stride and alignment.
 cugl_status launch_gemmlowp_simt(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep);

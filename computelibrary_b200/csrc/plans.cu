@@ -586,10 +586,10 @@ extern "C"
 
     cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps)
     {
-        if (plan == nullptr || (warps != 0 && warps != 4 && warps != 8))
+        if (plan == nullptr || (warps != 0 && warps != 4 && warps != 8 && warps != 16))
         {
             return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
-                        "cugl_gemmlowp_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4 or 8");
+                        "cugl_gemmlowp_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4, 8 or 16");
         }
         plan->core.epi_warps = warps;
         return CUGL_SUCCESS;
@@ -1157,10 +1157,10 @@ extern "C"
 
     cugl_status cugl_conv2d_plan_set_epilogue_warps(cugl_conv_plan *plan, int warps)
     {
-        if (plan == nullptr || (warps != 0 && warps != 4 && warps != 8))
+        if (plan == nullptr || (warps != 0 && warps != 4 && warps != 8 && warps != 16))
         {
             return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
-                        "cugl_conv2d_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4 or 8");
+                        "cugl_conv2d_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4, 8 or 16");
         }
         plan->core.epi_warps = warps;
         return CUGL_SUCCESS;

@@ -208,9 +208,10 @@ CUGL_API cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on)
 CUGL_API cugl_status cugl_gemmlowp_plan_allow_pair_kernel(cugl_gemm_plan *plan, int on);
 /* Number of kernels one cugl_gemmlowp_run of this plan launches. */
 CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
-/* The tensor-core kernels exist with four and with eight epilogue warps; the library picks by K (short K:
- * eight).  warps = 4 or 8 forces one build, 0 restores the automatic choice (testing / measurement aid: the
- * results are identical). */
+/* The tensor-core kernels exist with four, eight and (256-column one-CTA tiles only) sixteen epilogue warps; the
+ * library picks by K and N (long K: four; short K: eight, sixteen for more than 128 output columns).
+ * warps = 4, 8 or 16 forces one build where it exists, 0 restores the automatic choice (testing / measurement
+ * aid: the results are identical). */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps);
 /* The tensor-core GEMM can also run with the operand roles exchanged, which makes an accumulator lane an output
  * channel (output-stage terms in registers, byte-wise transposed stores; never with a row-sum term or several

@@ -262,7 +262,7 @@ def test_run_multi_destinations(ctx, port):
     plan.close()
 
 
-@pytest.mark.parametrize("epi_warps", [4, 8])
+@pytest.mark.parametrize("epi_warps", [4, 8, 16])
 @pytest.mark.parametrize("shape", [(300, 256, 64), (257, 96, 128), (130, 40, 2048), (515, 520, 320), (128, 64, 16)])
 def test_epilogue_builds_and_stage_encodings(ctx, port, shape, epi_warps):
     """Both builds of the tensor-core kernels (four / eight epilogue warps) on all three encodings of the output
@@ -306,7 +306,7 @@ def test_run_multi_destinations_eight_epilogue_warps(ctx, port):
     mult = rng.integers(2 ** 30, 2 ** 31 - 1, n_local).astype(np.int32)
     shift = rng.integers(5, 10, n_local).astype(np.int32)
     want = port.gemmlowp_fused(a, b, None, 0, 0, mult, shift, 0, -128, 127, np.int8)
-    for warps in (4, 8):
+    for warps in (4, 8, 16):
         desc, keep = capi.make_gemm_desc(M, n_local, K, capi.S8, capi.S8, capi.S8, 0, 0, multipliers=mult, shifts=shift,
                                          min_bound=-128, max_bound=127, ldd=n_total)
         plan = capi.GemmPlan(ctx, desc, keep)
