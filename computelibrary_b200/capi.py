@@ -9,7 +9,7 @@ import re
 from . import build as _build
 
 U8, S8, S32 = 0, 1, 2
-STAGE_NONE, STAGE_FIXEDPOINT = 0, 2
+STAGE_NONE, STAGE_QUANTIZE_DOWN, STAGE_FIXEDPOINT = 0, 1, 2
 INT32_MIN, INT32_MAX = -(2 ** 31), 2 ** 31 - 1
 
 _vp = C.c_void_p
@@ -117,6 +117,8 @@ _SIGNATURES = {
     "cugl_offset_contribution": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _i32, _i32]),
     "cugl_output_stage": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _i32, _i32,
                                     _i32, _i32, _i32]),
+    "cugl_output_stage_quantize_down": (C.c_int, [_vp, _vp, _i64, _vp, _vp, _i64, _i32, _i32, _i32, _vp, _vp, _i32, _i32,
+                                                  _i32, _i32, _i32, _i32]),
     "cugl_im2col_nhwc": (C.c_int, [_vp, _vp, _vp] + [_i32] * 15 + [_i64]),
     "cugl_weights_reshape_nhwc": (C.c_int, [_vp, _vp, _vp, _i32, _i32]),
     "cugl_conv2d_validate": (C.c_int, [C.POINTER(ConvDesc), C.POINTER(C.c_char_p)]),
@@ -303,6 +305,12 @@ class Context:
         self.check(self.lib.cugl_output_stage(self.handle, _dptr(src), ld_in, _dptr(bias), _dptr(out), ld_out,
                                               out_dtype, M, N, _dptr(mults), _dptr(shifts), mult, shift, n_mult,
                                               offset, lo, hi))
+
+    def output_stage_quantize_down(self, src, ld_in, bias, out, ld_out, out_dtype, M, N, mults, shifts, mult, shift,
+                                   n_mult, offset, lo, hi):
+        self.check(self.lib.cugl_output_stage_quantize_down(self.handle, _dptr(src), ld_in, _dptr(bias), _dptr(out),
+                                                            ld_out, out_dtype, M, N, _dptr(mults), _dptr(shifts), mult,
+                                                            shift, n_mult, offset, lo, hi))
 
     def im2col_nhwc(self, src, dst, C_, W, H, B, kw, kh, sx, sy, pl, pt, dx, dy, Wo, Ho, pad_value, row_stride):
         self.check(self.lib.cugl_im2col_nhwc(self.handle, _dptr(src), _dptr(dst), C_, W, H, B, kw, kh, sx, sy, pl, pt,

@@ -230,7 +230,7 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
                                                                 int N, const int32_t *__restrict__ mults,
                                                                 const int32_t *__restrict__ shifts, int32_t mult,
                                                                 int32_t shift, int32_t offset, int32_t lo, int32_t hi,
-                                                                bool vec_ok)
+                                                                bool vec_ok, bool integer_stage)
 {
     const int     groups_per_row = (N + 3) >> 2;
     const int64_t total          = static_cast<int64_t>(M) * groups_per_row;
@@ -262,7 +262,8 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
             if (bias != nullptr) x += bias[n];
             const int32_t mu = mults != nullptr ? mults[n] : mult;
             const int32_t sh = shifts != nullptr ? shifts[n] : shift;
-            const int32_t r  = finalize(x, mu, max(-sh, 0), max(sh, 0), offset, lo, hi);
+            const int32_t r  = integer_stage ? finalize_int(x + offset, mu, sh, lo, hi)
+                                             : finalize(x, mu, max(-sh, 0), max(sh, 0), offset, lo, hi);
             packed |= (static_cast<uint32_t>(r) & 0xffu) << (8 * j);
         }
         if (full && vec_ok)
@@ -474,7 +475,7 @@ cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, 
 cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
                                 void *d_out, int64_t ld_out_bytes, int M, int N, const int32_t *d_mults,
                                 const int32_t *d_shifts, int32_t mult, int32_t shift, int32_t offset, int32_t lo,
-                                int32_t hi)
+                                int32_t hi, bool integer_stage)
 {
     if (M <= 0 || N <= 0) return CUGL_SUCCESS;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(d_in) | static_cast<uint64_t>(ld_in_bytes)) & 15) == 0 &&
@@ -482,7 +483,8 @@ cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t 
     const int blocks = grid_for(static_cast<int64_t>(M) * ((N + 3) / 4), ctx->sm_count, 2);
     output_stage_kernel<<<blocks, kThreads, 0, ctx->stream>>>(d_in, ld_in_bytes / 4, d_bias,
                                                               static_cast<uint8_t *>(d_out), ld_out_bytes, M, N,
-                                                              d_mults, d_shifts, mult, shift, offset, lo, hi, vec_ok);
+                                                              d_mults, d_shifts, mult, shift, offset, lo, hi, vec_ok,
+                                                              integer_stage);
     return check_cuda(ctx, cudaGetLastError(), "output_stage_kernel");
 }
 

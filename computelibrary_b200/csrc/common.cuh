@@ -111,6 +111,14 @@ __device__ __forceinline__ int32_t finalize(int32_t acc, int32_t mult, int32_t l
     return min(max(r, lo), hi);
 }
 
+// Output stage QUANTIZE_DOWN (tests/validation/reference/GEMMLowp.cpp:66-104): x already holds
+// accumulator + offset + bias; wrapping multiply, arithmetic shift, clamp (bounds pre-intersected with the type).
+__device__ __forceinline__ int32_t finalize_int(int32_t x, int32_t mult, int32_t shift, int32_t lo, int32_t hi)
+{
+    const int32_t r = static_cast<int32_t>(static_cast<uint32_t>(x) * static_cast<uint32_t>(mult)) >> shift;
+    return min(max(r, lo), hi);
+}
+
 __device__ __forceinline__ int32_t load_q8(const void *p, size_t idx, bool is_signed)
 {
     return is_signed ? static_cast<int32_t>(static_cast<const int8_t *>(p)[idx])

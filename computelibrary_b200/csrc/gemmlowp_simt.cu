@@ -77,7 +77,9 @@ __global__ void __launch_bounds__(256) gemmlowp_simt_kernel(GemmOperands op, Epi
             {
                 const int32_t mu = ep.mults != nullptr ? ep.mults[n] : ep.mult;
                 const int32_t sh = ep.shifts != nullptr ? ep.shifts[n] : ep.shift;
-                const int32_t r  = finalize(v, mu, max(-sh, 0), max(sh, 0), ep.result_offset, ep.lo, ep.hi);
+                const int32_t r  = ep.stage == CUGL_STAGE_QUANTIZE_DOWN
+                                       ? finalize_int(v + ep.result_offset, mu, sh, ep.lo, ep.hi)
+                                       : finalize(v, mu, max(-sh, 0), max(sh, 0), ep.result_offset, ep.lo, ep.hi);
                 static_cast<uint8_t *>(op.dst)[m * op.ldd + n] = static_cast<uint8_t>(r);
             }
         }

@@ -393,6 +393,7 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
 //                   five instructions.  {constant lo, constant hi, multiplier, s-1}.  Equal to the reference
 //                   wherever its own 32-bit sums v+t and x + 2^(s-1) do not overflow.
 constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2;
+constexpr int kIntegerStageFlag = 1 << 16; // generic encoding, bit of q.z: the integer-multiply stage QUANTIZE_DOWN
 
 template <int kMode>
 __device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t row_term, int32_t offset, int32_t lo,
@@ -409,7 +410,11 @@ __device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t
     const int32_t acc = static_cast<int32_t>(v) + q.x + row_term;
     if (kMode == kStageGeneric)
     {
-        return finalize(acc, q.y, q.z >> 8, q.z & 0xff, offset, lo, hi);
+        if (q.z & kIntegerStageFlag) // QUANTIZE_DOWN: the offset is already part of the column term
+        {
+            return finalize_int(acc, q.y, q.z & 0xff, lo, hi);
+        }
+        return finalize(acc, q.y, (q.z >> 8) & 0xff, q.z & 0xff, offset, lo, hi);
     }
     const int32_t  mh = __mulhi(acc, q.y);
     const uint32_t ml = static_cast<uint32_t>(acc) * static_cast<uint32_t>(q.y);
@@ -583,13 +588,13 @@ __device__ __forceinline__ void flush_stage(const uint8_t *stage, const TilePara
 
 // Fused residual addition on 32 packed output bytes of one row: out = min(max(min(out + res, 255), floor), cap),
 // the form the host has proved equal to quantize(dequantize(out) + dequantize(res)) followed by the activation.
-__device__ __forceinline__ void apply_residual(uint32_t *w, const uint8_t *rrow, int nc, bool row_ok, const TileParams &tp)
+__device__ __forceinline__ void load_residual(uint32_t (&r)[8], const uint8_t *rrow, int nc, bool row_ok,
+                                              const TileParams &tp)
 {
     if (!row_ok)
     {
         return;
     }
-    uint32_t r[8];
     if (nc + 32 <= tp.N && tp.vec_ok)
     {
         const uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(rrow + nc));
@@ -609,6 +614,9 @@ __device__ __forceinline__ void apply_residual(uint32_t *w, const uint8_t *rrow,
             r[j] = v;
         }
     }
+}
+__device__ __forceinline__ void add_residual(uint32_t *w, const uint32_t (&r)[8], const TileParams &tp)
+{
 #pragma unroll
     for (int j = 0; j < 8; ++j)
     {
@@ -638,10 +646,16 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         {
             tmem_ld_x32(t_addr + (ch + 1) * 32, vb);
         }
-        process_chunk<kS32Out, kMode>(va, s_col + ch * 32, row_term, ep);
-        if (!kS32Out && tp.residual != nullptr)
+        uint32_t res[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        const bool with_res = !kS32Out && tp.residual != nullptr; // warp-uniform
+        if (with_res) // requested first: the latency passes while the chunk is requantised
         {
-            apply_residual(va, tp.residual + row_off, n_first + ch * 32, row_ok, tp);
+            load_residual(res, tp.residual + row_off, n_first + ch * 32, row_ok, tp);
+        }
+        process_chunk<kS32Out, kMode>(va, s_col + ch * 32, row_term, ep);
+        if (with_res)
+        {
+            add_residual(va, res, tp);
         }
         if (staged)
         {
@@ -666,10 +680,14 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             {
                 tmem_ld_x32(t_addr + (ch + 2) * 32, va);
             }
-            process_chunk<kS32Out, kMode>(vb, s_col + (ch + 1) * 32, row_term, ep);
-            if (!kS32Out && tp.residual != nullptr)
+            if (with_res)
             {
-                apply_residual(vb, tp.residual + row_off, n_first + (ch + 1) * 32, row_ok, tp);
+                load_residual(res, tp.residual + row_off, n_first + (ch + 1) * 32, row_ok, tp);
+            }
+            process_chunk<kS32Out, kMode>(vb, s_col + (ch + 1) * 32, row_term, ep);
+            if (with_res)
+            {
+                add_residual(vb, res, tp);
             }
             if (staged)
             {
@@ -705,6 +723,11 @@ __device__ __forceinline__ int4 column_term(int n, const TileParams &tp, const E
     if (tp.mode == kStageGeneric)
     {
         q.z = max(sh, 0) | (max(-sh, 0) << 8);
+        if (ep.stage == CUGL_STAGE_QUANTIZE_DOWN)
+        {
+            q.x = static_cast<int32_t>(static_cast<uint32_t>(t) + static_cast<uint32_t>(ep.result_offset));
+            q.z = (sh & 0xff) | kIntegerStageFlag;
+        }
     }
     else if (tp.mode == kStageFast)
     {

@@ -141,6 +141,11 @@ extern "C" cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_d
     const int32_t tlo = desc->dst_dtype == CUGL_S8 ? -128 : 0, thi = desc->dst_dtype == CUGL_S8 ? 127 : 255;
     ep.lo             = desc->gemmlowp_min_bound > tlo ? desc->gemmlowp_min_bound : tlo;
     ep.hi             = desc->gemmlowp_max_bound < thi ? desc->gemmlowp_max_bound : thi;
+    if (desc->stage == CUGL_STAGE_QUANTIZE_DOWN && desc->gemmlowp_min_bound == desc->gemmlowp_max_bound)
+    {
+        ep.lo = tlo; // equal bounds: no bounded ReLU, type range only
+        ep.hi = thi;
+    }
     ep.stage          = desc->stage;
     ep.out_signed     = desc->dst_dtype == CUGL_S8;
 
@@ -158,7 +163,8 @@ extern "C" cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_d
     op.b_signed = b_signed;
     // the per-channel vectors live on the device only, so their signs cannot be inspected here:
     // take the fully general output-stage path for them
-    op.generic_stage = per_channel || desc->gemmlowp_shift < 0 || desc->gemmlowp_multiplier == INT32_MIN;
+    op.generic_stage = per_channel || desc->gemmlowp_shift < 0 || desc->gemmlowp_multiplier == INT32_MIN ||
+                       desc->stage == CUGL_STAGE_QUANTIZE_DOWN;
     return gemmlowp_tcgen05_supported(op) ? launch_gemmlowp_tcgen05(&ctx, op, ep, true)
                                           : launch_gemmlowp_simt(&ctx, op, ep);
 }

@@ -63,7 +63,8 @@ struct GemmCore
 
     cugl_status upload_stage_vectors(const int32_t *h_mults, const int32_t *h_shifts)
     {
-        generic_stage = !per_channel && (shift < 0 || mult == INT32_MIN);
+        // the integer-multiply stage runs on the generic encoding
+        generic_stage = stage == CUGL_STAGE_QUANTIZE_DOWN || (!per_channel && (shift < 0 || mult == INT32_MIN));
         wide_stage    = stage == CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT && b_off == 0 &&
                      (per_channel || (shift >= 2 && shift <= 31 && mult >= 0));
         if (!per_channel)
@@ -125,6 +126,12 @@ struct GemmCore
         const int32_t thi = dst_dtype == CUGL_S8 ? 127 : 255;
         ep.lo             = min_bound > tlo ? min_bound : tlo;
         ep.hi             = max_bound < thi ? max_bound : thi;
+        if (stage == CUGL_STAGE_QUANTIZE_DOWN && min_bound == max_bound)
+        {
+            // tests/validation/reference/GEMMLowp.cpp:93-97: equal bounds mean "no bounded ReLU", type range only
+            ep.lo = tlo;
+            ep.hi = thi;
+        }
         ep.stage          = stage;
         ep.out_signed     = dst_dtype == CUGL_S8;
         return ep;
@@ -187,10 +194,25 @@ const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
     if (d->M < 1 || d->N < 1 || d->K < 1 || d->batch < 1) return "M, N, K and batch must be positive";
     if (!is_q8(d->a_dtype)) return "A must be QASYMM8 or QASYMM8_SIGNED";
     if (!is_q8(d->b_dtype)) return "B must be QASYMM8, QASYMM8_SIGNED, QSYMM8 or QSYMM8_PER_CHANNEL";
-    if (d->stage != CUGL_STAGE_NONE && d->stage != CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT)
+    if (d->stage != CUGL_STAGE_NONE && d->stage != CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT &&
+        d->stage != CUGL_STAGE_QUANTIZE_DOWN)
     {
         *code = CUGL_UNSUPPORTED_CONFIG;
-        return "only output stages NONE and QUANTIZE_DOWN_FIXEDPOINT are implemented";
+        return "only output stages NONE, QUANTIZE_DOWN and QUANTIZE_DOWN_FIXEDPOINT are implemented";
+    }
+    if (d->stage == CUGL_STAGE_QUANTIZE_DOWN)
+    {
+        if (d->is_quantized_per_channel)
+        {
+            for (int i = 0; d->h_gemmlowp_shifts != nullptr && i < d->N; ++i)
+            {
+                if (d->h_gemmlowp_shifts[i] < 0 || d->h_gemmlowp_shifts[i] > 31) return "QUANTIZE_DOWN needs shifts in [0, 31]";
+            }
+        }
+        else if (d->gemmlowp_shift < 0 || d->gemmlowp_shift > 31)
+        {
+            return "QUANTIZE_DOWN needs a shift in [0, 31]";
+        }
     }
     if (d->stage == CUGL_STAGE_NONE)
     {
@@ -688,6 +710,38 @@ extern "C"
         return launch_output_stage(ctx, d_in, ld_in_bytes, d_bias, d_out, ld_out_bytes, M, N,
                                    pc ? d_multipliers : nullptr, pc ? d_shifts : nullptr, multiplier, shift,
                                    result_offset, min_bound > tlo ? min_bound : tlo, max_bound < thi ? max_bound : thi);
+    }
+
+    cugl_status cugl_output_stage_quantize_down(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
+                                  void *d_out, int64_t ld_out_bytes, int32_t out_dtype, int32_t M, int32_t N,
+                                  const int32_t *d_multipliers, const int32_t *d_shifts, int32_t multiplier,
+                                  int32_t shift, int32_t n_mult, int32_t result_offset, int32_t min_bound,
+                                  int32_t max_bound)
+    {
+        if (ctx == nullptr || d_in == nullptr || d_out == nullptr || !is_q8(out_dtype) || M < 0 || N < 0 ||
+            ld_in_bytes < 4ll * N || (ld_in_bytes & 3) != 0 || ld_out_bytes < N)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage_quantize_down: bad argument");
+        }
+        if (min_bound > max_bound)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage_quantize_down: min_bound > max_bound");
+        }
+        const bool pc = n_mult > 1;
+        if (pc && (n_mult != N || d_multipliers == nullptr || d_shifts == nullptr))
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage_quantize_down: per-channel needs N multipliers and shifts");
+        }
+        const int32_t tlo = out_dtype == CUGL_S8 ? -128 : 0, thi = out_dtype == CUGL_S8 ? 127 : 255;
+        if (!pc && (shift < 0 || shift > 31))
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage_quantize_down: shift must lie in [0, 31]");
+        }
+        const bool bounded = min_bound != max_bound; // equal bounds: type range only (GEMMLowp.cpp:93-97)
+        return launch_output_stage(ctx, d_in, ld_in_bytes, d_bias, d_out, ld_out_bytes, M, N,
+                                   pc ? d_multipliers : nullptr, pc ? d_shifts : nullptr, multiplier, shift,
+                                   result_offset, bounded && min_bound > tlo ? min_bound : tlo,
+                                   bounded && max_bound < thi ? max_bound : thi, true);
     }
 
     cugl_status cugl_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst, int32_t C, int32_t W, int32_t H,

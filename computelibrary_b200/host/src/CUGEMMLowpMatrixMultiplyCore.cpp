@@ -84,11 +84,14 @@ Status make_desc(const ITensorInfo *a, const ITensorInfo *b, const ITensorInfo *
         case GEMMLowpOutputStageType::NONE:
             d.stage = CUGL_STAGE_NONE;
             break;
+        case GEMMLowpOutputStageType::QUANTIZE_DOWN:
+            d.stage = CUGL_STAGE_QUANTIZE_DOWN;
+            break;
         case GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT:
             d.stage = CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT;
             break;
         default:
-            return Status(ErrorCode::RUNTIME_ERROR, "only output stages NONE and QUANTIZE_DOWN_FIXEDPOINT are implemented");
+            return Status(ErrorCode::RUNTIME_ERROR, "only output stages NONE, QUANTIZE_DOWN and QUANTIZE_DOWN_FIXEDPOINT are implemented");
     }
     d.is_quantized_per_channel   = s.is_quantized_per_channel ? 1 : 0;
     d.gemmlowp_multiplier        = s.gemmlowp_multiplier;

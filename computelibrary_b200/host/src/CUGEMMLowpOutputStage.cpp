@@ -13,8 +13,9 @@ Status CUGEMMLowpOutputStage::validate(const ITensorInfo *input, const ITensorIn
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(input->data_type() != DataType::S32, "input must be S32");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() != DataType::QASYMM8 && output->data_type() != DataType::QASYMM8_SIGNED,
                                     "output must be QASYMM8 or QASYMM8_SIGNED");
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT,
-                                    "only QUANTIZE_DOWN_FIXEDPOINT is implemented");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT &&
+                                        info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN,
+                                    "only QUANTIZE_DOWN and QUANTIZE_DOWN_FIXEDPOINT are implemented");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.gemmlowp_min_bound > info.gemmlowp_max_bound, "min bound above max bound");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->tensor_shape() != input->tensor_shape(), "input and output shapes differ");
     if (bias != nullptr)
@@ -59,8 +60,9 @@ void CUGEMMLowpOutputStage::run()
     const ITensorInfo *in  = _input->info();
     const int32_t      N   = static_cast<int32_t>(in->dimension(0));
     const int32_t      M   = static_cast<int32_t>(in->tensor_shape().total_size_upper(1));
+    const auto stage_fn = _info.type == GEMMLowpOutputStageType::QUANTIZE_DOWN ? cugl_output_stage_quantize_down : cugl_output_stage;
     ARM_COMPUTE_ERROR_THROW_ON(cu_status(
-        cugl_output_stage(ctx, static_cast<const int32_t *>(cu_device_ptr(_input)),
+        stage_fn(ctx, static_cast<const int32_t *>(cu_device_ptr(_input)),
                           static_cast<int64_t>(in->strides_in_bytes()[1]), static_cast<const int32_t *>(cu_device_ptr(_bias)),
                           cu_device_ptr(_output), static_cast<int64_t>(_output->info()->strides_in_bytes()[1]),
                           _output->info()->data_type() == DataType::QASYMM8 ? CUGL_U8 : CUGL_S8, M, N,

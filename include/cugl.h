@@ -60,6 +60,10 @@ typedef enum cugl_dtype
 typedef enum cugl_stage
 {
     CUGL_STAGE_NONE                     = 0,
+    /* ((acc + gemmlowp_offset + bias) * gemmlowp_multiplier) >> gemmlowp_shift, integer multiply, shift >= 0;
+     * clamp to [min, max] when they differ, saturate to the 8-bit type (GEMMLowpOutputStageType::QUANTIZE_DOWN,
+     * tests/validation/reference/GEMMLowp.cpp:66-104) */
+    CUGL_STAGE_QUANTIZE_DOWN            = 1,
     CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT = 2
 } cugl_stage;
 
@@ -261,6 +265,13 @@ CUGL_API cugl_status cugl_offset_contribution(cugl_context *ctx, int32_t *d_mm, 
  * CpuGemmLowpQuantizeDownInt32ToUint8ScaleByFixedPointKernel.cpp:78-186): S32 [M,N] (+ S32 bias [N])
  * -> U8 / S8 [M,N].  n_mult == 1: per-tensor (the NE function), n_mult == N: per-column device vectors. */
 CUGL_API cugl_status cugl_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes,
+                                       const int32_t *d_bias, void *d_out, int64_t ld_out_bytes, int32_t out_dtype,
+                                       int32_t M, int32_t N, const int32_t *d_multipliers, const int32_t *d_shifts,
+                                       int32_t multiplier, int32_t shift, int32_t n_mult, int32_t result_offset,
+                                       int32_t min_bound, int32_t max_bound);
+/* The same entry point for the QUANTIZE_DOWN (integer multiply) stage: NEGEMMLowpOutputStage with
+ * GEMMLowpOutputStageType::QUANTIZE_DOWN (src/cpu/operators/CpuGemmLowpOutputStage.cpp:41-167). */
+CUGL_API cugl_status cugl_output_stage_quantize_down(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes,
                                        const int32_t *d_bias, void *d_out, int64_t ld_out_bytes, int32_t out_dtype,
                                        int32_t M, int32_t N, const int32_t *d_multipliers, const int32_t *d_shifts,
                                        int32_t multiplier, int32_t shift, int32_t n_mult, int32_t result_offset,

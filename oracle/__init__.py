@@ -205,6 +205,30 @@ class _Port(_Layers):
                                   int(mult.size), _i32(offset), _i32(lo), _i32(hi))
         return out
 
+    def output_stage_int(self, acc, bias, mult, shift, offset, lo, hi, out_dtype):
+        """QUANTIZE_DOWN (integer multiply) stage: ((acc + offset + bias) * mult) >> shift, clamp, saturate."""
+        acc = np.ascontiguousarray(acc, dtype=np.int32)
+        M, N = acc.shape
+        mult, shift = _i32arr(mult), _i32arr(shift)
+        bias = None if bias is None else _i32arr(bias)
+        out = np.empty((M, N), out_dtype)
+        self.lib.orc_output_stage_int(_ptr(acc), _ptr(bias), _ptr(out), _signed(out), M, N, _ptr(mult), _ptr(shift),
+                                      int(mult.size), _i32(offset), _i32(lo), _i32(hi))
+        return out
+
+    def gemmlowp_fused_int(self, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype):
+        a = np.ascontiguousarray(a)
+        b = np.ascontiguousarray(b)
+        M, K = a.shape
+        N = b.shape[1]
+        mult, shift = _i32arr(mult), _i32arr(shift)
+        bias = None if bias is None else _i32arr(bias)
+        out = np.empty((M, N), out_dtype)
+        self.lib.orc_gemmlowp_fused_int(_ptr(a), _signed(a), _ptr(b), _signed(b), _ptr(bias), _ptr(out), _signed(out),
+                                        M, N, K, _i32(a_off), _i32(b_off), _ptr(mult), _ptr(shift), int(mult.size),
+                                        _i32(offset), _i32(lo), _i32(hi))
+        return out
+
     def gemmlowp_fused(self, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype):
         a = np.ascontiguousarray(a)
         b = np.ascontiguousarray(b)
@@ -315,6 +339,17 @@ class _Ref(_Layers):
         bias = None if bias is None else _i32arr(bias)
         out = np.empty((M, N), out_dtype)
         fn = self.lib.ref_quantize_down_fixedpoint_s8 if out.dtype == np.int8 else self.lib.ref_quantize_down_fixedpoint_u8
+        fn(_ptr(acc), _ptr(bias), _ptr(out), M, N, _ptr(mult), _ptr(shift), int(mult.size), _i32(offset), _i32(lo),
+           _i32(hi))
+        return out
+
+    def output_stage_int(self, acc, bias, mult, shift, offset, lo, hi, out_dtype):
+        acc = np.ascontiguousarray(acc, dtype=np.int32)
+        M, N = acc.shape
+        mult, shift = _i32arr(mult), _i32arr(shift)
+        bias = None if bias is None else _i32arr(bias)
+        out = np.empty((M, N), out_dtype)
+        fn = self.lib.ref_quantize_down_scale_s8 if out.dtype == np.int8 else self.lib.ref_quantize_down_scale_u8
         fn(_ptr(acc), _ptr(bias), _ptr(out), M, N, _ptr(mult), _ptr(shift), int(mult.size), _i32(offset), _i32(lo),
            _i32(hi))
         return out

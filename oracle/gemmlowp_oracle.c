@@ -298,6 +298,66 @@ ORC_EXPORT void orc_output_stage(const int32_t *in, const int32_t *bias, void *o
     }
 }
 
+/* Output stage QUANTIZE_DOWN (integer multiply): ((in + offset + bias) * mult) >> shift in wrapping int32 with an
+ * arithmetic shift, clamped to [lo, hi] only when lo != hi, then saturated to the 8-bit type.
+ * tests/validation/reference/GEMMLowp.cpp:66-104.  n_mult == 1: per-tensor, else per-column. */
+ORC_EXPORT void orc_output_stage_int(const int32_t *in, const int32_t *bias, void *out, int out_signed, int M, int N,
+                                     const int32_t *mult, const int32_t *shift, int n_mult, int32_t offset, int32_t lo,
+                                     int32_t hi)
+{
+    const int32_t tmin = out_signed ? -128 : 0;
+    const int32_t tmax = out_signed ? 127 : 255;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static)
+#endif
+    for (int i = 0; i < M; ++i)
+    {
+        for (int j = 0; j < N; ++j)
+        {
+            int32_t v = wrap_add(in[(size_t)i * N + j], offset);
+            if (bias != NULL)
+            {
+                v = wrap_add(v, bias[j]);
+            }
+            v = wrap_mul(v, n_mult > 1 ? mult[j] : mult[0]);
+            v >>= (n_mult > 1 ? shift[j] : shift[0]); /* gcc: arithmetic shift on signed */
+            if (lo != hi)
+            {
+                v = v < lo ? lo : (v > hi ? hi : v);
+            }
+            v = v < tmin ? tmin : (v > tmax ? tmax : v);
+            if (out_signed)
+            {
+                ((int8_t *)out)[(size_t)i * N + j] = (int8_t)v;
+            }
+            else
+            {
+                ((uint8_t *)out)[(size_t)i * N + j] = (uint8_t)v;
+            }
+        }
+    }
+}
+
+/* The fused function with the QUANTIZE_DOWN stage (CpuGemmLowpOffsetContributionOutputStageKernel.cpp with
+ * is_fixed_point == false): raw product + offset contribution, then the stage above. */
+ORC_EXPORT void orc_gemmlowp_fused_int(const void *a, int a_signed, const void *b, int b_signed, const int32_t *bias,
+                                       void *out, int out_signed, int M, int N, int K, int32_t a_off, int32_t b_off,
+                                       const int32_t *mult, const int32_t *shift, int n_mult, int32_t offset,
+                                       int32_t lo, int32_t hi)
+{
+    int32_t *mm     = (int32_t *)malloc((size_t)M * N * sizeof(int32_t));
+    int32_t *colsum = (int32_t *)malloc((size_t)N * sizeof(int32_t));
+    int32_t *rowsum = (int32_t *)malloc((size_t)M * sizeof(int32_t));
+    orc_gemmlowp_core(a, a_signed, b, b_signed, mm, M, N, K, 1, 0, 0, 0);
+    orc_reduce_cols(b, b_signed, K, N, colsum);
+    orc_reduce_rows(a, a_signed, M, K, rowsum);
+    orc_offset_contribution(mm, M, N, K, colsum, rowsum, a_off, b_off);
+    orc_output_stage_int(mm, bias, out, out_signed, M, N, mult, shift, n_mult, offset, lo, hi);
+    free(mm);
+    free(colsum);
+    free(rowsum);
+}
+
 /* The fused function: NEGEMMLowpMatrixMultiplyCore with a QUANTIZE_DOWN_FIXEDPOINT output stage, built
  * the way the library builds it (raw product + offset contribution + bias + requantise):
  * src/cpu/kernels/CpuGemmLowpOffsetContributionOutputStageKernel.cpp:275-346. */

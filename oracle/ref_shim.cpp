@@ -9,6 +9,7 @@
 // Wrapped reference entry points:
 //   reference::gemmlowp_matrix_multiply_core           tests/validation/reference/GEMMLowp.cpp:202-255
 //   reference::gemmlowp_quantize_down_scale_by_fixedpoint  tests/validation/reference/GEMMLowp.cpp:106-158,309-340
+//   reference::gemmlowp_quantize_down_scale            tests/validation/reference/GEMMLowp.cpp:66-104,278-307
 //   reference::convolution_layer (NCHW)                tests/validation/reference/ConvolutionLayer.cpp:43-151
 //   reference::im2col (NHWC / NCHW)                    tests/validation/reference/Im2Col.cpp:40-197
 //   quantization::calculate_quantized_multiplier       src/core/utils/quantization/AsymmHelpers.cpp:43-91
@@ -79,6 +80,27 @@ void qdown(const int32_t *in, const int32_t *bias, void *out, int M, int N, cons
     std::memcpy(out, dst.data(), size_t(M) * N);
 }
 
+template <typename TO>
+void qdown_int(const int32_t *in, const int32_t *bias, void *out, int M, int N, const int32_t *mult, const int32_t *shift,
+               int n_mult, int offset, int lo, int hi)
+{
+    SimpleTensor<int32_t> tin(TensorShape(N, M), DataType::S32);
+    std::memcpy(tin.data(), in, size_t(M) * N * sizeof(int32_t));
+    std::vector<int32_t> vm(mult, mult + n_mult), vs(shift, shift + n_mult);
+    SimpleTensor<TO>     dst;
+    if (bias != nullptr)
+    {
+        SimpleTensor<int32_t> tb(TensorShape(N), DataType::S32);
+        std::memcpy(tb.data(), bias, size_t(N) * sizeof(int32_t));
+        dst = reference::gemmlowp_quantize_down_scale<int32_t, TO>(tin, tb, offset, vm, vs, lo, hi);
+    }
+    else
+    {
+        dst = reference::gemmlowp_quantize_down_scale<int32_t, TO>(tin, offset, vm, vs, lo, hi);
+    }
+    std::memcpy(out, dst.data(), size_t(M) * N);
+}
+
 // NCHW convolution exactly as the conv fixture drives it: src [W,H,C,B], weights [kw,kh,C,OFM].
 template <typename TI, typename TW>
 void conv(const void *src, const void *wgt, const int32_t *bias, void *dst, int W, int H, int C, int B, int kw, int kh,
@@ -141,6 +163,18 @@ extern "C"
                                          int hi)
     {
         qdown<int8_t>(in, bias, out, M, N, mult, shift, n_mult, offset, lo, hi);
+    }
+
+    // reference::gemmlowp_quantize_down_scale (the QUANTIZE_DOWN integer stage), GEMMLowp.cpp:66-104, 278-307
+    void ref_quantize_down_scale_u8(const int32_t *in, const int32_t *bias, uint8_t *out, int M, int N,
+                                    const int32_t *mult, const int32_t *shift, int n_mult, int offset, int lo, int hi)
+    {
+        qdown_int<uint8_t>(in, bias, out, M, N, mult, shift, n_mult, offset, lo, hi);
+    }
+    void ref_quantize_down_scale_s8(const int32_t *in, const int32_t *bias, int8_t *out, int M, int N,
+                                    const int32_t *mult, const int32_t *shift, int n_mult, int offset, int lo, int hi)
+    {
+        qdown_int<int8_t>(in, bias, out, M, N, mult, shift, n_mult, offset, lo, hi);
     }
 
     int ref_quantize_down_scalar(int val, int mult, int shift, int offset, int lo, int hi)

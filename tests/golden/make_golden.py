@@ -19,7 +19,7 @@ sys.path.insert(0, os.path.dirname(HERE))
 
 import oracle  # noqa: E402
 from helpers import (GOLDEN_CONV_SCALES, config1, golden_act_cases, golden_add_cases,  # noqa: E402
-                     golden_conv_cases, golden_gemm_cases, golden_im2col_cases, golden_pool_cases,
+                     golden_conv_cases, golden_gemm_cases, golden_im2col_cases, golden_int_stage, golden_pool_cases,
                      golden_softmax_cases, pool_with)
 
 
@@ -75,6 +75,12 @@ def main():
         acc0 = ref.gemmlowp_core(g["a"], g["b"], g["a_off"], 0)
         out[g["key"] + "_pc"] = ref.output_stage(acc0, g["bias"], g["mult"], g["shift"], g["pc_offset"], g["lo"],
                                                  g["hi"], g["out_dtype"])
+        # QUANTIZE_DOWN (integer multiply) stage: per-tensor on the full accumulators, per-channel on acc0, and
+        # the "equal bounds = no bounded ReLU" rule
+        im, ish, ioff, ilo, ihi = golden_int_stage(g)
+        out[g["key"] + "_int_pt"] = ref.output_stage_int(acc, g["bias"], im[:1], ish[:1], ioff, ilo, ihi, g["out_dtype"])
+        out[g["key"] + "_int_pc"] = ref.output_stage_int(acc0, g["bias"], im, ish, ioff, ilo, ihi, g["out_dtype"])
+        out[g["key"] + "_int_nb"] = ref.output_stage_int(acc0, None, im, ish, ioff, 0, 0, g["out_dtype"])
     np.savez_compressed(os.path.join(HERE, "gemmlowp_golden.npz"), **out)
 
     # --- convolution (NCHW oracle; stored NHWC) and im2col -----------------------------------------

@@ -20,7 +20,7 @@ def f32_mults(port, i_scale, w_scales, o_scale):
 
 # ---- GPU drivers (torch tensors as device buffers) ------------------------------------------------------
 def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype, force_simt=False,
-                 b_constant=True, runs=1, ldd_pad=0, pair=True, epi_warps=0, channel_major=0):
+                 b_constant=True, runs=1, ldd_pad=0, pair=True, epi_warps=0, channel_major=0, integer_stage=False):
     """Fused NEGEMMLowpMatrixMultiplyCore through the C ABI.  mult/shift scalars -> per-tensor; arrays ->
     per-channel.  out_dtype np.int32 -> output stage NONE.  Returns (numpy result, kernel name)."""
     import torch
@@ -33,7 +33,7 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
     out_dtype = np.dtype(out_dtype)
     dsz = out_dtype.itemsize
     per_channel = np.ndim(mult) > 0
-    stage = capi.STAGE_NONE if out_dtype == np.int32 else capi.STAGE_FIXEDPOINT
+    stage = capi.STAGE_NONE if out_dtype == np.int32 else (capi.STAGE_QUANTIZE_DOWN if integer_stage else capi.STAGE_FIXEDPOINT)
     ldd = (N + ldd_pad) * dsz
     desc, keep = capi.make_gemm_desc(
         M, N, K, CODE_OF[a.dtype], CODE_OF[b.dtype], CODE_OF[out_dtype], a_off, b_off, stage,
@@ -90,6 +90,17 @@ def golden_gemm_cases():
             lo, hi = type_range(od)
             yield dict(key=f"g{si}_{ci}", a=a, b=b, a_off=ao, b_off=bo, bias=bias, mult=mult, shift=shift,
                        out_dtype=od, lo=lo, hi=hi, pt_offset=3, pc_offset=-2)
+
+
+def golden_int_stage(g):
+    """Parameters of the QUANTIZE_DOWN (integer multiply) stage derived from a golden GEMM case: small multipliers,
+    shifts in [0, 20), an offset, and bounds inside the type range."""
+    r = np.random.default_rng(int(g["key"][1]) * 7 + 3)
+    N = g["b"].shape[1]
+    mult = r.integers(1, 400, N).astype(np.int32)
+    shift = r.integers(8, 20, N).astype(np.int32)
+    lo, hi = (20, 230) if g["out_dtype"] == np.uint8 else (-100, 110)
+    return mult, shift, 1234, lo, hi
 
 
 GOLDEN_CONV_GEOMS = [(3, 3, 1, 1, (1, 1, 1, 1)), (1, 1, 1, 1, (0, 0, 0, 0)), (3, 2, 2, 1, (0, 1, 1, 0)),

@@ -66,7 +66,8 @@ def test_gemm_validate_rules():
     assert st == 6 and "Bias addition not supported" in why
     assert capi.gemm_validate(_desc(dst_dtype=cl.S32))[0] == 6                      # stage needs 8-bit dst
     assert capi.gemm_validate(_desc(stage=cl.STAGE_NONE))[0] == 6                   # NONE needs S32 dst
-    assert capi.gemm_validate(_desc(stage=1))[0] == 8                               # QUANTIZE_DOWN: unsupported
+    assert capi.gemm_validate(_desc(stage=1))[0] == 0                               # QUANTIZE_DOWN (integer multiply)
+    assert capi.gemm_validate(_desc(stage=3))[0] == 8                               # QUANTIZE_DOWN_FLOAT: unsupported
     assert capi.gemm_validate(_desc(min_bound=10, max_bound=5))[0] == 6
     assert capi.gemm_validate(_desc(K=0))[0] == 6
     assert capi.gemm_validate(_desc(a_dtype=cl.S32))[0] == 6

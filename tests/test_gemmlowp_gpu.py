@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 
 from computelibrary_b200 import capi
-from helpers import (config1, config2, config5, f32_mults, golden_gemm_cases, gpu_gemmlowp, q8_uniform, type_range)
+from helpers import (golden_int_stage, config1, config2, config5, f32_mults, golden_gemm_cases, gpu_gemmlowp, q8_uniform, type_range)
 
 pytestmark = pytest.mark.gpu
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
@@ -350,3 +350,33 @@ def test_pair_kernel_tail_split(ctx, port, shape):
         plan.close()
     assert np.array_equal(outs[0], want), np.argwhere(outs[0] != want)[:5]
     assert np.array_equal(outs[1], want)
+
+
+@pytest.mark.parametrize("force_simt", [False, True])
+def test_fused_quantize_down_stage_golden(ctx, port, gemm_golden, force_simt):
+    """NEGEMMLowpMatrixMultiplyCore with a fused QUANTIZE_DOWN (integer multiply) stage against the reference
+    fixtures: per-channel and per-tensor, tensor-core (where TMA can address the operands) and generic kernels."""
+    for g in golden_gemm_cases():
+        im, ish, ioff, ilo, ihi = golden_int_stage(g)
+        od = g["out_dtype"]
+        got, _ = gpu_gemmlowp(ctx, g["a"], g["b"], g["bias"], g["a_off"], 0, im, ish, ioff, ilo, ihi, od,
+                              force_simt=force_simt, integer_stage=True)
+        assert np.array_equal(got, gemm_golden[g["key"] + "_int_pc"]), g["key"]
+        got, _ = gpu_gemmlowp(ctx, g["a"], g["b"], g["bias"], g["a_off"], g["b_off"], int(im[0]), int(ish[0]), ioff, ilo,
+                              ihi, od, force_simt=force_simt, integer_stage=True)
+        assert np.array_equal(got, gemm_golden[g["key"] + "_int_pt"]), g["key"]
+
+
+def test_fused_quantize_down_stage_tensor_core_shapes(ctx, port):
+    rng = np.random.default_rng(91)
+    for (M, N, K) in [(300, 256, 64), (515, 520, 1088), (130, 40, 2048)]:
+        a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), np.int8, -127, 127)
+        bias = rng.integers(-20000, 20001, N).astype(np.int32)
+        mult = rng.integers(1, 60, N).astype(np.int32)
+        shift = rng.integers(8, 16, N).astype(np.int32)
+        want = port.gemmlowp_fused_int(a, b, bias, -9, 0, mult, shift, 4000, 3, 250, np.uint8)
+        got, kern = gpu_gemmlowp(ctx, a, b, bias, -9, 0, mult, shift, 4000, 3, 250, np.uint8, integer_stage=True)
+        assert kern.startswith("tcgen05") and np.array_equal(got, want), (M, N, K)
+        want = port.gemmlowp_fused_int(a, b, None, -9, 0, mult, shift, 4000, 0, 0, np.uint8)   # equal bounds: type range
+        got, _ = gpu_gemmlowp(ctx, a, b, None, -9, 0, mult, shift, 4000, 0, 0, np.uint8, integer_stage=True)
+        assert np.array_equal(got, want), (M, N, K)

@@ -90,6 +90,35 @@ def test_output_stage(ctx, port, out_dtype, M, N):
     assert np.array_equal(out.cpu().numpy().view(out_dtype), port.output_stage(acc, bias, mult, shift, -4, lo, hi, out_dtype))
 
 
+@pytest.mark.parametrize("out_dtype", [np.uint8, np.int8])
+@pytest.mark.parametrize("M,N", [(1, 1), (37, 53), (300, 1001)])
+def test_output_stage_quantize_down(ctx, port, out_dtype, M, N):
+    """The integer-multiply stage (GEMMLowpOutputStageType::QUANTIZE_DOWN) of the stand-alone output stage."""
+    import torch
+    rng = np.random.default_rng(M * N + 5)
+    acc = rng.integers(-2 ** 22, 2 ** 22, (M, N)).astype(np.int32)
+    acc.flat[:2] = [2 ** 31 - 1, -2 ** 31][:acc.size]
+    bias = rng.integers(-9000, 9001, N).astype(np.int32)
+    lo, hi = type_range(out_dtype)
+    code = capi.U8 if out_dtype == np.uint8 else capi.S8
+    out = torch.empty((M, N), dtype=torch.uint8, device="cuda")
+    for (qm, sh, blo, bhi) in [(3, 5, lo + 1, hi - 1), (-7, 0, 0, 0), (251, 23, lo, hi)]:
+        for b in (None, bias):
+            ctx.output_stage_quantize_down(_t(acc), N * 4, _t(b) if b is not None else None, out, N, code, M, N, None,
+                                           None, qm, sh, 1, 77, blo, bhi)
+            ctx.sync()
+            want = port.output_stage_int(acc, b, [qm], [sh], 77, blo, bhi, out_dtype)
+            assert np.array_equal(out.cpu().numpy().view(out_dtype), want), (qm, sh)
+    if N > 1:
+        mult = rng.integers(1, 400, N).astype(np.int32)
+        shift = rng.integers(0, 20, N).astype(np.int32)
+        ctx.output_stage_quantize_down(_t(acc), N * 4, _t(bias), out, N, code, M, N, _t(mult), _t(shift), 0, 0, N, -4,
+                                       lo + 3, hi - 3)
+        ctx.sync()
+        assert np.array_equal(out.cpu().numpy().view(out_dtype),
+                              port.output_stage_int(acc, bias, mult, shift, -4, lo + 3, hi - 3, out_dtype))
+
+
 def test_im2col_golden_and_oracle(ctx, port):
     import torch
     gold = np.load(os.path.join(GOLDEN, "conv_golden.npz"))

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 from helpers import (GOLDEN_CONV_SCALES, config1, golden_conv_cases, golden_gemm_cases, golden_im2col_cases,
-                     q8_uniform, type_range)
+                     golden_int_stage, q8_uniform, type_range)
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
 
@@ -143,3 +143,37 @@ def test_port_vs_reference_multiplier(port, ref):
     for _ in range(2000):
         m = np.float32(np.exp(rng.uniform(np.log(1e-8), np.log(500.0))))
         assert port.calculate_quantized_multiplier(m) == ref.calculate_quantized_multiplier(float(m))
+
+
+def test_integer_stage_golden(port, gemm_golden):
+    """QUANTIZE_DOWN (integer multiply) stage of the restatement against fixtures made by the reference's
+    gemmlowp_quantize_down_scale: per-tensor, per-channel, and equal bounds (= no bounded ReLU)."""
+    n = 0
+    for g in golden_gemm_cases():
+        im, ish, ioff, ilo, ihi = golden_int_stage(g)
+        acc = port.gemmlowp_core(g["a"], g["b"], g["a_off"], g["b_off"])
+        acc0 = port.gemmlowp_core(g["a"], g["b"], g["a_off"], 0)
+        od = g["out_dtype"]
+        assert np.array_equal(port.output_stage_int(acc, g["bias"], im[:1], ish[:1], ioff, ilo, ihi, od), gemm_golden[g["key"] + "_int_pt"])
+        assert np.array_equal(port.output_stage_int(acc0, g["bias"], im, ish, ioff, ilo, ihi, od), gemm_golden[g["key"] + "_int_pc"])
+        assert np.array_equal(port.output_stage_int(acc0, None, im, ish, ioff, 0, 0, od), gemm_golden[g["key"] + "_int_nb"])
+        assert np.array_equal(port.gemmlowp_fused_int(g["a"], g["b"], g["bias"], g["a_off"], 0, im, ish, ioff, ilo, ihi, od),
+                              gemm_golden[g["key"] + "_int_pc"])
+        n += 1
+    assert n == 24
+
+
+@pytest.mark.parametrize("out_dtype", [np.uint8, np.int8])
+def test_port_vs_reference_integer_stage(port, ref, out_dtype):
+    rng = np.random.default_rng(77)
+    for (M, N) in [(1, 1), (9, 31), (40, 64)]:
+        acc = rng.integers(-2 ** 22, 2 ** 22, (M, N)).astype(np.int32)
+        acc.flat[0] = 2 ** 31 - 1
+        bias = rng.integers(-9000, 9000, N).astype(np.int32)
+        for nm in (1, N):
+            mult = rng.integers(-50, 500, nm).astype(np.int32)
+            shift = rng.integers(0, 24, nm).astype(np.int32)
+            for lo, hi in [(0, 0), (5, 100), (-2 ** 31, 2 ** 31 - 1)]:
+                for b in (None, bias):
+                    assert np.array_equal(port.output_stage_int(acc, b, mult, shift, -321, lo, hi, out_dtype),
+                                          ref.output_stage_int(acc, b, mult, shift, -321, lo, hi, out_dtype))

@@ -89,3 +89,32 @@ def test_graph_replay_equals_eager(port):
                 np.testing.assert_array_equal(got[k], want[k], err_msg=k)
     net.close()
     ctx.close()
+
+
+@pytest.mark.gpu
+def test_full_size_network_vs_oracle_and_batch_invariance(ctx, port):
+    """Config 4 at its real geometry (224x224x3, 1000 classes) on the specified parameter distribution: batch 3
+    against the oracle node by node for the tensors that matter downstream, and the size-independent property
+    the sharding relies on -- an image's result does not depend on which batch (rank) it travels in."""
+    import torch
+    from computelibrary_b200 import resnet50 as rn
+    g = rn.build_graph(224, 1000)
+    params = rn.synthetic_params(g, seed=1)
+    x = np.random.default_rng(31).integers(0, 256, (3, 224, 224, 3), dtype=np.uint8)
+    net = rn.ResNet50(ctx, 3, params=params, nodes=g)
+    net.run(torch.from_numpy(x).cuda())
+    ctx.sync()
+    want = run_graph_oracle(port, g, params, x)
+    for name in ("conv1", "pool1", "block1/unit1/add", "block1/unit3/add", "block2/unit4/add", "block3/unit6/add",
+                 "block4/unit3/add", "pool5", "logits"):
+        np.testing.assert_array_equal(net.bufs[name].cpu().numpy(), want[name], err_msg=name)
+    sm = net.bufs["softmax"].cpu().numpy().astype(np.int32)
+    assert np.abs(sm - want["softmax"].astype(np.int32)).max() <= 1
+    full_logits = net.bufs["logits"].cpu().numpy().copy()
+    net.close()
+    single = rn.ResNet50(ctx, 1, params=params, nodes=g)
+    for i in (0, 2):
+        single.run(torch.from_numpy(x[i:i + 1]).cuda())
+        ctx.sync()
+        np.testing.assert_array_equal(single.bufs["logits"].cpu().numpy()[0], full_logits[i])
+    single.close()
