@@ -646,15 +646,14 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         {
             tmem_ld_x32(t_addr + (ch + 1) * 32, vb);
         }
-        uint32_t res[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         const bool with_res = !kS32Out && tp.residual != nullptr; // warp-uniform
-        if (with_res) // requested first: the latency passes while the chunk is requantised
-        {
-            load_residual(res, tp.residual + row_off, n_first + ch * 32, row_ok, tp);
-        }
         process_chunk<kS32Out, kMode>(va, s_col + ch * 32, row_term, ep);
         if (with_res)
         {
+            // loaded after the arithmetic: requesting the bytes before it (eight more live registers) measured
+            // slower in the sixteen-warp build, whose threads have 96 registers (305 -> 365 us on 802816 x 256 x 64)
+            uint32_t res[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            load_residual(res, tp.residual + row_off, n_first + ch * 32, row_ok, tp);
             add_residual(va, res, tp);
         }
         if (staged)
@@ -680,13 +679,11 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             {
                 tmem_ld_x32(t_addr + (ch + 2) * 32, va);
             }
-            if (with_res)
-            {
-                load_residual(res, tp.residual + row_off, n_first + (ch + 1) * 32, row_ok, tp);
-            }
             process_chunk<kS32Out, kMode>(vb, s_col + (ch + 1) * 32, row_term, ep);
             if (with_res)
             {
+                uint32_t res[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                load_residual(res, tp.residual + row_off, n_first + (ch + 1) * 32, row_ok, tp);
                 add_residual(vb, res, tp);
             }
             if (staged)
