@@ -132,6 +132,10 @@ _SIGNATURES = {
     "cugl_conv2d_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_conv2d_plan_allow_implicit": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_residual": (C.c_int, [_vp, C.c_float, C.c_float, _i32, C.c_float, _i32, _i32, C.c_float,
                                                 C.c_float]),
     "cugl_conv2d_run_residual": (C.c_int, [_vp, _vp, _vp, _vp, _vp]),
@@ -468,6 +472,12 @@ class GemmPlan:
     def set_epilogue_warps(self, warps: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_epilogue_warps(self.handle, int(warps)))
 
+    def set_tile_columns(self, columns: int):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_tile_columns(self.handle, int(columns)))
+
+    def set_paired_drain(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_paired_drain(self.handle, int(on)))
+
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_channel_major(self.handle, int(mode)))
 
@@ -565,6 +575,12 @@ class ConvPlan:
 
     def set_epilogue_warps(self, warps: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_epilogue_warps(self.handle, int(warps)))
+
+    def set_tile_columns(self, columns: int):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_tile_columns(self.handle, int(columns)))
+
+    def set_paired_drain(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_paired_drain(self.handle, int(on)))
 
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_channel_major(self.handle, int(mode)))

@@ -19,6 +19,49 @@ bool eight_epilogue_warps(const GemmOperands &op)
     }
     return op.K <= kShortK;
 }
+
+// Tile width of the one-CTA kernels.  The widest tile N calls for moves the fewest operand bytes per output, but
+// an output of fewer such tiles than SMs leaves SMs idle while each busy one walks all of K for a wide tile.
+// Then the width is the one that minimises (waves of tiles over the SMs) x (128 + width), the operand bytes a
+// CTA stages per K step; ties go to the wider tile.
+int pick_block_n(const cugl_context *ctx, const GemmOperands &op)
+{
+    const int widest = op.N > 128 ? 256 : (op.N > 64 ? 128 : 64);
+    if (op.block_n > 0)
+    {
+        return op.block_n < widest ? op.block_n : widest;
+    }
+    if (op.epi_warps == 16 || op.channel_major > 0)
+    {
+        return widest; // kernels the caller asked for by name: 256-column tiles only
+    }
+    const long long sms     = ctx->sm_count > 0 ? ctx->sm_count : 1;
+    const long long m_tiles = (op.M + 127) / 128;
+    if (m_tiles * ((op.N + widest - 1) / widest) >= sms)
+    {
+        return widest;
+    }
+    int       best      = widest;
+    long long best_cost = -1;
+    for (int bn = widest; bn >= 64; bn >>= 1)
+    {
+        const long long tiles = m_tiles * ((op.N + bn - 1) / bn);
+        const long long cost  = ((tiles + sms - 1) / sms) * (128 + bn);
+        if (best_cost < 0 || cost < best_cost)
+        {
+            best      = bn;
+            best_cost = cost;
+        }
+    }
+    return best;
+}
+
+// the SM-pair kernel works on 256 x 256 tiles, one per pair of SMs
+bool pair_fills_the_device(const cugl_context *ctx, const GemmOperands &op)
+{
+    const long long tiles = static_cast<long long>((op.M + 255) / 256) * ((op.N + 255) / 256);
+    return tiles >= ctx->sm_count / 2;
+}
 } // namespace
 
 bool gemmlowp_tcgen05_supported(const GemmOperands &op)
@@ -26,11 +69,12 @@ bool gemmlowp_tcgen05_supported(const GemmOperands &op)
     return gemmlowp_tcgen05_supported_epi4(op);
 }
 
-// The SM-pair kernel pays off once a tile spans both halves (more than 128 rows and more than 128 columns) and
-// the main loop is long enough to matter.
-bool gemmlowp_tcgen05_uses_pair(const GemmOperands &op)
+// The SM-pair kernel pays off once a tile spans both halves (more than 128 rows and more than 128 columns), the
+// main loop is long enough to matter and there is a 256 x 256 tile for every pair of SMs.
+bool gemmlowp_tcgen05_uses_pair(const cugl_context *ctx, const GemmOperands &op)
 {
-    return gemmlowp_tcgen05_uses_pair_epi4(op) && !eight_epilogue_warps(op);
+    return gemmlowp_tcgen05_uses_pair_epi4(op) && !eight_epilogue_warps(op) && pair_fills_the_device(ctx, op) &&
+           (op.block_n == 0 || op.block_n == 256);
 }
 
 cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
@@ -40,12 +84,22 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
     // transpose in shared memory) wins where the epilogue dominates and whole 128-channel blocks exist: measured
     // 802816 x 256 x 64: 209 us against 235 us row-major; 200704 x 512 x 128: 113 / 125; 50176 x 1024 x 256:
     // 63 / 70; 12544 x 2048 x 512: 39 / 47; but N = 64: 110 / 78 (half of the lanes idle).
-    GemmOperands o = op;
+    GemmOperands o   = op;
+    o.block_n        = pick_block_n(ctx, op); // before the automatic channel-major choice below
     if (o.channel_major == 0)
     {
         // with a fused residual the row-major epilogue stays ahead (block-1 conv3 + add: 344 us against 377 us)
         o.channel_major = (o.K <= kShortK && o.N >= 256 && o.residual == nullptr) ? 1 : -1;
     }
+    const int widest = o.N > 128 ? 256 : (o.N > 64 ? 128 : 64);
+    if (o.block_n < widest)
+    {
+        // a small output: narrower tiles on more SMs (the kernels of the complete builds only)
+        o.channel_major = -1;
+        return eight_epilogue_warps(o) ? launch_gemmlowp_tcgen05_epi8(ctx, o, ep, false)
+                                       : launch_gemmlowp_tcgen05_epi4(ctx, o, ep, false);
+    }
+    allow_pair = allow_pair && pair_fills_the_device(ctx, o);
     // sixteen epilogue warps (256-column tiles only) buy another 4 - 7 % on short K with wide outputs
     if (o.N > 128 && (o.epi_warps == 16 || (o.epi_warps != 4 && o.epi_warps != 8 && o.K <= kShortK)))
     {
@@ -63,7 +117,9 @@ bool gemmlowp_conv_tcgen05_supported(const GemmOperands &op, const ConvOperands 
 cugl_status launch_gemmlowp_conv_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                          const ConvOperands &cv)
 {
-    return eight_epilogue_warps(op) ? launch_gemmlowp_conv_tcgen05_epi8(ctx, op, ep, cv)
-                                    : launch_gemmlowp_conv_tcgen05_epi4(ctx, op, ep, cv);
+    GemmOperands o = op;
+    o.block_n      = pick_block_n(ctx, o);
+    return eight_epilogue_warps(o) ? launch_gemmlowp_conv_tcgen05_epi8(ctx, o, ep, cv)
+                                   : launch_gemmlowp_conv_tcgen05_epi4(ctx, o, ep, cv);
 }
 } // namespace cugl

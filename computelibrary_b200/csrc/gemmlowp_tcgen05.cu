@@ -298,6 +298,7 @@ struct TileParams
     int      split_tail; // SM-pair kernel: split the tiles of a short last wave in two (see the kernel)
     const uint8_t *residual; // optional [M][ldd] bytes added to the output with unsigned saturation, then clamped
     uint32_t res_floor4, res_cap4; // the clamp bounds replicated into four bytes
+    int      pair_drain; // one-CTA kernel, two accumulator buffers: drain two tiles of one column block together
     long long *trace; // optional per-CTA event timestamps (cugl_context_set_trace_buffer), else nullptr
     int32_t *status;
 };
@@ -705,6 +706,71 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             }
         }
     }
+}
+
+// Two accumulator buffers that hold tiles of the same column block (rows ma and mb of this thread) drained
+// together, kStageWide encoding only.  Every lane of a warp needs the 16-byte term of every column, so the
+// per-element term read from shared memory is what the load/store pipe spends most of a short-K epilogue on
+// (802816 x 256 x 64: 235 us, 134 us with one term read per 32 columns instead of 32).  Here a term is read
+// once for two elements; both residual rows are requested together.
+template <int NCOLS>
+__device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
+                                                       const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
+                                                       int n_first)
+{
+    const bool    ok_a   = ma < tp.M, ok_b = mb < tp.M;
+    const int64_t off_a  = static_cast<int64_t>(ma) * tp.ldd;
+    const int64_t off_b  = static_cast<int64_t>(mb) * tp.ldd;
+    const bool with_res  = tp.residual != nullptr; // warp-uniform
+    uint32_t   va[32], vb[32];
+#pragma unroll 1
+    for (int ch = 0; ch < NCOLS / 32; ++ch)
+    {
+        const int4 *col = s_col + ch * 32;
+        tmem_ld_x32(t_a + ch * 32, va);
+        tmem_ld_x32(t_b + ch * 32, vb);
+        tmem_ld_wait();
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+        {
+            int32_t ra[4], rb[4];
+#pragma unroll
+            for (int b = 0; b < 4; ++b)
+            {
+                const int4 q = col[j + b];
+                ra[b]        = requant_one<kStageWide>(va[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
+                rb[b]        = requant_one<kStageWide>(vb[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
+            }
+            va[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(ra[0]), static_cast<uint32_t>(ra[1]), 0x0040),
+                                     __byte_perm(static_cast<uint32_t>(ra[2]), static_cast<uint32_t>(ra[3]), 0x0040), 0x5410);
+            vb[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(rb[0]), static_cast<uint32_t>(rb[1]), 0x0040),
+                                     __byte_perm(static_cast<uint32_t>(rb[2]), static_cast<uint32_t>(rb[3]), 0x0040), 0x5410);
+        }
+        const int nc = n_first + ch * 32;
+        if (with_res)
+        {
+            uint32_t res_a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, res_b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            load_residual(res_a, tp.residual + off_a, nc, ok_a, tp);
+            load_residual(res_b, tp.residual + off_b, nc, ok_b, tp);
+            add_residual(va, res_a, tp);
+            add_residual(vb, res_b, tp);
+        }
+        store_chunk<false>(va, tp.dst + off_a, nc, ok_a, tp);
+        store_chunk<false>(vb, tp.dst + off_b, nc, ok_b, tp);
+    }
+}
+
+template <int BLOCK_N>
+__device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_t tmem_b, const int4 *s_col,
+                                                        const TileParams &tp, const EpilogueParams &ep, int warp,
+                                                        int lane, int m0a, int m0b, int n0)
+{
+    constexpr int  NCOLS = BLOCK_N / (kEpiWarps / 4);
+    const int      quad  = warp & 3;                 // tensor-memory lane quarter this warp may read
+    const int      half  = (warp - kFirstEpi) >> 2;  // which share of the columns
+    const uint32_t lanes = static_cast<uint32_t>(quad * 32) << 16;
+    drain_accumulator_pair<NCOLS>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS, s_col + half * NCOLS, tp,
+                                  ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane, n0 + half * NCOLS);
 }
 
 // the term of output channel n in the encoding of tp.mode (see requant_pack4)
@@ -1342,7 +1408,20 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (kGroups == 1) epi_barrier();
                 else epi_group_barrier(group);
             }
+            // Paired drain (see drain_accumulator_pair): at buffer 0, when this CTA's next tile lies in the same
+            // column block, wait for both accumulators and drain them together.  The MMA warp is untouched: it
+            // fills buffer 1 while buffer 0 waits here, and meets the two released buffers afterwards.
+            bool pair_now = false;
+            if (!kCM && !kS32Out && kGroups == 1 && ACC == 2 && tp.pair_drain != 0 && tp.mode == kStageWide && as == 0)
+            {
+                const int next = tile + static_cast<int>(gridDim.x);
+                pair_now       = next < num_tiles && next / num_m_blocks == tile / num_m_blocks;
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            if (ok && pair_now)
+            {
+                ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(1), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            }
             if (ok)
             {
                 tc_fence_after();
@@ -1351,6 +1430,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     epilogue_warp_tile_cm<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, tp, ep, warp, lane, m0, n0,
                                                             smem + P::OFF_OUT);
+                }
+                else if (!kS32Out && kGroups == 1 && ACC == 2 && pair_now)
+                {
+                    const int m0b = ((tile + static_cast<int>(gridDim.x)) % num_m_blocks) * BLOCK_M;
+                    epilogue_warp_tile_pair<BLOCK_N>(tmem_base, tmem_base + BLOCK_N, g_col, tp, ep, warp, lane, m0, m0b, n0);
                 }
                 else
                 {
@@ -1363,6 +1447,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (lane == 0)
                 {
                     mbar_arrive(tempty_bar(as)); // accumulator buffer may be overwritten (one arrival per warp)
+                    if (pair_now)
+                    {
+                        mbar_arrive(tempty_bar(1));
+                    }
+                }
+                if (pair_now) // two tiles consumed
+                {
+                    tile += static_cast<int>(gridDim.x);
+                    ++ti;
                 }
             }
         }
@@ -2077,6 +2170,7 @@ void fill_extra_dst(TileParams &tp, const GemmOperands &op)
     tp.res_floor4 = static_cast<uint32_t>(op.res_floor & 0xff) * 0x01010101u;
     tp.res_cap4   = static_cast<uint32_t>(op.res_cap & 0xff) * 0x01010101u;
     tp.n_extra    = op.n_extra_dst;
+    tp.pair_drain = (op.pair_drain >= 0 && op.n_extra_dst == 0 && op.wide_stage && !op.generic_stage) ? 1 : 0;
     for (int i = 0; i < kMaxExtraDst; ++i)
     {
         tp.extra_dst[i] = i < op.n_extra_dst ? static_cast<uint8_t *>(op.extra_dst[i]) : nullptr;
@@ -2361,12 +2455,13 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
 #else
     (void)allow_pair;
 #endif
-    if (op.N > 128 || !CUGL_TC_FULL_BUILD)
+    const int block_n = op.block_n > 0 ? op.block_n : (op.N > 128 ? 256 : (op.N > 64 ? 128 : 64));
+    if (block_n > 128 || !CUGL_TC_FULL_BUILD)
     {
         return s32 ? launch_variant<256, 4, 1, true>(ctx, op, ep) : launch_variant<256, 4, 1, false>(ctx, op, ep);
     }
 #if CUGL_TC_FULL_BUILD
-    if (op.N > 64)
+    if (block_n > 64)
     {
         return s32 ? launch_variant<128, 3, 2, true>(ctx, op, ep) : launch_variant<128, 3, 2, false>(ctx, op, ep);
     }
@@ -2396,11 +2491,12 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_conv_tcgen05)(cugl_context *ctx, const 
     {
         return fail(ctx, CUGL_UNSUPPORTED_CONFIG, "implicit convolution needs a quantize-down output stage");
     }
-    if (op.N > 128)
+    const int block_n = op.block_n > 0 ? op.block_n : (op.N > 128 ? 256 : (op.N > 64 ? 128 : 64));
+    if (block_n > 128)
     {
         return launch_conv_variant<256, 4, 1, 2>(ctx, op, ep, cv);
     }
-    if (op.N > 64)
+    if (block_n > 64)
     {
         return launch_conv_variant<128, 3, 2, 4>(ctx, op, ep, cv);
     }

@@ -54,6 +54,12 @@ struct GemmOperands
     int         channel_major;
     // SM-pair kernel: < 0 keeps every tile whole; otherwise the tiles of a short last wave are split in two
     int         split_tail;
+    // one-CTA tensor-core kernels: tile width in columns (256, 128 or 64); 0 = the widest that N calls for.  Set by the
+    // dispatcher, which narrows the tiles of an output too small to give every SM a wide one.
+    int         block_n;
+    // one-CTA tensor-core kernels with 256-column tiles: < 0 drains every accumulator buffer on its own; otherwise two
+    // tiles of one column block are drained together wherever the output stage allows (see drain_accumulator_pair)
+    int         pair_drain;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).
@@ -94,7 +100,7 @@ cugl_status launch_gemmlowp_simt(cugl_context *ctx, const GemmOperands &op, cons
 
 // TMA + tcgen05.mma.kind::i8 kernel.  Requires a, bt 16-byte aligned and lda, ldbt multiples of 16.
 bool        gemmlowp_tcgen05_supported(const GemmOperands &op);
-bool        gemmlowp_tcgen05_uses_pair(const GemmOperands &op);
+bool        gemmlowp_tcgen05_uses_pair(const cugl_context *ctx, const GemmOperands &op);
 // allow_pair = false keeps to the one-CTA kernels (testing aid; all variants must agree bit for bit).
 cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                     bool allow_pair = true);

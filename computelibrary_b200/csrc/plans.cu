@@ -46,6 +46,8 @@ struct GemmCore
     int           epi_warps     = 0;     // 4 / 8 force that build of the tensor-core kernels, 0 = automatic
     int           channel_major = 0;     // > 0 / < 0 force / forbid the channel-major kernel, 0 = automatic
     int           split_tail    = 0;     // < 0: the SM-pair kernel keeps the tiles of a short last wave whole
+    int           block_n       = 0;     // 64 / 128 / 256 force that tile width of the one-CTA kernels, 0 = automatic
+    int           pair_drain    = 0;     // < 0: every accumulator buffer is drained on its own
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
@@ -164,6 +166,8 @@ struct GemmCore
         op.epi_warps     = epi_warps;
         op.channel_major = channel_major;
         op.split_tail    = split_tail;
+        op.block_n       = block_n;
+        op.pair_drain    = pair_drain;
         op.n_extra_dst   = n_extra;
         op.residual      = d_residual;
         op.res_floor     = res_floor;
@@ -603,7 +607,8 @@ extern "C"
         }
         op.M         = plan->collapse_batch ? plan->desc.M * plan->desc.batch : plan->desc.M;
         op.epi_warps = plan->core.epi_warps;
-        return (plan->core.allow_pair && gemmlowp_tcgen05_uses_pair(op)) ? "tcgen05_2cta" : "tcgen05";
+        op.block_n   = plan->core.block_n;
+        return (plan->core.allow_pair && gemmlowp_tcgen05_uses_pair(plan->ctx, op)) ? "tcgen05_2cta" : "tcgen05";
     }
 
     cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan, int warps)
@@ -614,6 +619,27 @@ extern "C"
                         "cugl_gemmlowp_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4, 8 or 16");
         }
         plan->core.epi_warps = warps;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_tile_columns(cugl_gemm_plan *plan, int columns)
+    {
+        if (plan == nullptr || (columns != 0 && columns != 64 && columns != 128 && columns != 256))
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
+                        "cugl_gemmlowp_plan_set_tile_columns: plan is NULL or columns is not 0, 64, 128 or 256");
+        }
+        plan->core.block_n = columns;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_paired_drain(cugl_gemm_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_set_paired_drain: NULL plan");
+        }
+        plan->core.pair_drain = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
     }
 
@@ -1094,6 +1120,8 @@ extern "C"
             op.wide_stage    = c.wide_stage;
             op.epi_warps     = c.epi_warps;
             op.channel_major = c.channel_major;
+            op.block_n       = c.block_n;
+            op.pair_drain    = c.pair_drain;
             op.n_extra_dst   = 0;
             op.residual      = d_residual;
             op.res_floor     = plan->res_floor;
@@ -1217,6 +1245,27 @@ extern "C"
                         "cugl_conv2d_plan_set_epilogue_warps: plan is NULL or warps is not 0, 4, 8 or 16");
         }
         plan->core.epi_warps = warps;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_tile_columns(cugl_conv_plan *plan, int columns)
+    {
+        if (plan == nullptr || (columns != 0 && columns != 64 && columns != 128 && columns != 256))
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
+                        "cugl_conv2d_plan_set_tile_columns: plan is NULL or columns is not 0, 64, 128 or 256");
+        }
+        plan->core.block_n = columns;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_paired_drain(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_paired_drain: NULL plan");
+        }
+        plan->core.pair_drain = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
     }
 

@@ -226,6 +226,17 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_channel_major(cugl_gemm_plan *plan, 
  * processed as two 256 x 128 halves each (on by default).  on = 0 keeps them whole.  Testing / measurement aid:
  * the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_tail_split(cugl_gemm_plan *plan, int on);
+/* Tile width of the one-CTA tensor-core kernels, in output columns.  By default (0) the widest tile N calls for
+ * (256 above 128 columns, 128 above 64, else 64) unless the output then has fewer tiles than the device has
+ * SMs: a small output gets narrower tiles so that more SMs share its K loop (and is kept off the SM-pair and
+ * sixteen-warp kernels, which exist for 256 columns only).  columns = 64, 128 or 256 forces a width (capped at
+ * the widest N calls for).  Testing / measurement aid: the results are identical. */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_tile_columns(cugl_gemm_plan *plan, int columns);
+/* One-CTA kernel, 256-column tiles, 8-bit output with shifts >= 2 and non-negative multipliers: two consecutive
+ * tiles of one column block are drained from their two accumulator buffers together, so that each per-column
+ * output-stage term is read from shared memory once for two elements (on by default).  on = 0 drains every
+ * tile on its own.  Testing / measurement aid: the results are identical. */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_paired_drain(cugl_gemm_plan *plan, int on);
 
 /* Fused GEMMLowp that allocates nothing.  No counterpart in the reference: Compute Library always lets the
  * function object own its workspace.  For callers that cannot call cudaMalloc -- a serving loop whose device
@@ -338,6 +349,10 @@ CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int o
  * lowerings that run the plain GEMM kernel: 1x1 convolutions and the explicit im2col path) */
 CUGL_API cugl_status cugl_conv2d_plan_set_epilogue_warps(cugl_conv_plan *plan, int warps);
 CUGL_API cugl_status cugl_conv2d_plan_set_channel_major(cugl_conv_plan *plan, int mode);
+/* as cugl_gemmlowp_plan_set_tile_columns, for every lowering of the convolution */
+CUGL_API cugl_status cugl_conv2d_plan_set_tile_columns(cugl_conv_plan *plan, int columns);
+/* as cugl_gemmlowp_plan_set_paired_drain, for the lowerings that run the plain GEMM kernel */
+CUGL_API cugl_status cugl_conv2d_plan_set_paired_drain(cugl_conv_plan *plan, int on);
 /* Fused residual addition: dst = act(quantize(dequantize(conv) + dequantize(residual))) computed in the epilogue
  * of the convolution, i.e. NEGEMMConvolutionLayer followed by NEArithmeticAddition (ConvertPolicy::SATURATE)
  * and NEActivationLayer (arm_compute/runtime/NEON/functions/NEArithmeticAddition.h:43-109) without the

@@ -14,7 +14,7 @@ CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
 
 
 def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1),
-             implicit=True, want_kernel=None):
+             implicit=True, want_kernel=None, tile_columns=0):
     import torch
     B, H, W, Cc = src.shape
     OFM, kh, kw, _ = weights.shape
@@ -28,6 +28,8 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
     plan = capi.ConvPlan(ctx, desc, keep)
     if not implicit:
         plan.allow_implicit(False)
+    if tile_columns:
+        plan.set_tile_columns(tile_columns)
     if want_kernel is not None:
         assert plan.kernel == want_kernel, plan.kernel
     wo, ho = plan.out_dims()
@@ -125,10 +127,12 @@ def test_implicit_conv_vs_oracle(ctx, port, geom, in_zp):
     bias = rng.integers(-5000, 5001, OFM).astype(np.int32)
     ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)).astype(np.float32)
     mult, shift = f32_mults(port, 0.03, ws, 0.05 * k)
-    got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, dilation=(d, d),
-                   want_kernel="implicit")
     want = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, dilation=(d, d))
-    assert np.array_equal(got, want), np.argwhere(got != want)[:5]
+    # 0: the library's own choice (narrow tiles here, the outputs are small); then every tile width by name
+    for cols in (0, 256, 128, 64):
+        got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, dilation=(d, d),
+                       want_kernel="implicit", tile_columns=cols)
+        assert np.array_equal(got, want), (cols, np.argwhere(got != want)[:5])
 
 
 @pytest.mark.parametrize("geom", [(7, 3, 3, 20, 22), (7, 3, 3, 19, 23), (3, 1, 4, 17, 18), (5, 2, 1, 9, 11), (3, 0, 3, 12, 15),
@@ -189,4 +193,37 @@ def test_fused_residual_addition(ctx, port, geom):
     plan = capi.ConvPlan(ctx, desc, keep)
     with pytest.raises(capi.CuglError):
         plan.set_residual(0.05, (0.03, 5), (0.07, 9))
+    plan.close()
+
+
+@pytest.mark.parametrize("paired", [True, False])
+def test_fused_residual_addition_many_tiles(ctx, port, paired):
+    """1x1 convolution 64 -> 256 with a fused residual on 39200 output rows: 307 tiles of 128 x 256 for 148 CTAs,
+    so the paired drain of the epilogue (two tiles, one term read) runs with the residual rows of both tiles."""
+    import torch
+    rng = np.random.default_rng(99)
+    B, H, W, Cc, OFM = 8, 70, 70, 64, 256
+    src = q8_uniform(rng, (B, H, W, Cc), np.uint8)
+    wgt = q8_uniform(rng, (OFM, 1, 1, Cc), np.int8, -127, 127)
+    bias = rng.integers(-3000, 3001, OFM).astype(np.int32)
+    ws = (np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)) / np.sqrt(Cc) * 8).astype(np.float32)
+    q = (0.05, 0)
+    mult, shift = f32_mults(port, q[0], ws, q[0])
+    conv = port.conv2d_nhwc(src, wgt, bias, (1, 1), (0, 0, 0, 0), q[1], 0, mult, shift, q[1], 0, 255)
+    res = q8_uniform(rng, conv.shape, np.uint8)
+    want = port.activation_qasymm8(port.add_qasymm8(conv, res, q, q, q), "relu", 0.0, 0.0, q, q)
+    desc, keep = capi.make_conv_desc(B, H, W, Cc, OFM, 1, 1, (1, 1), (0, 0, 0, 0), (1, 1), capi.U8, capi.S8, q[1], 0,
+                                     multipliers=mult, shifts=shift, dst_zp=q[1], min_bound=0, max_bound=255)
+    plan = capi.ConvPlan(ctx, desc, keep)
+    plan.set_residual(q[0], q, q, act=capi.ACT_RELU, act_a=0.0)
+    plan.set_paired_drain(paired)
+    plan.prepare(torch.from_numpy(wgt.view(np.uint8)).cuda())
+    d_res = torch.from_numpy(res).cuda()
+    d_dst = torch.empty(conv.shape, dtype=torch.uint8, device="cuda")
+    plan.run_residual(torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda(), d_res, d_dst)
+    ctx.sync()
+    assert np.array_equal(d_dst.cpu().numpy(), want)
+    plan.run_residual(torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda(), d_res, d_res)  # in place
+    ctx.sync()
+    assert np.array_equal(d_res.cpu().numpy(), want)
     plan.close()

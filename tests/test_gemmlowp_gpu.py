@@ -283,6 +283,13 @@ def test_epilogue_builds_and_stage_encodings(ctx, port, shape, epi_warps):
                                      epi_warps=epi_warps, channel_major=cm, ldd_pad=pad)
             assert kern.startswith("tcgen05")
             assert np.array_equal(got, want), (label, pair, cm, pad, np.argwhere(got != want)[:4])
+        # these outputs have fewer tiles than the device has SMs, so the library narrows the tiles by itself; the
+        # forced widths cover every tile variant of the build (256 is the only one of the sixteen-warp build)
+        for cols in (256, 128, 64):
+            got, kern = gpu_gemmlowp(ctx, a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8, epi_warps=epi_warps,
+                                     channel_major=-1, tile_columns=cols)
+            assert kern.startswith("tcgen05")
+            assert np.array_equal(got, want), (label, cols, np.argwhere(got != want)[:4])
     # per-tensor wide encoding with a signed output and a lower bound above the type minimum
     a8 = q8_uniform(rng, (M, K), np.int8)
     got, _ = gpu_gemmlowp(ctx, a8, b, bias, 5, 0, 1759218688, 13, -3, -100, 90, np.int8, epi_warps=epi_warps)
@@ -380,3 +387,23 @@ def test_fused_quantize_down_stage_tensor_core_shapes(ctx, port):
         want = port.gemmlowp_fused_int(a, b, None, -9, 0, mult, shift, 4000, 0, 0, np.uint8)   # equal bounds: type range
         got, _ = gpu_gemmlowp(ctx, a, b, None, -9, 0, mult, shift, 4000, 0, 0, np.uint8, integer_stage=True)
         assert np.array_equal(got, want), (M, N, K)
+
+
+@pytest.mark.parametrize("epi_warps", [4, 8, 16])
+@pytest.mark.parametrize("shape", [(38477, 256, 64), (20000, 520, 96), (37900, 300, 1104)])
+def test_paired_drain(ctx, port, shape, epi_warps):
+    """More 128 x 256 tiles than SMs, so a CTA owns several: consecutive tiles of one column block are drained from
+    the two accumulator buffers together (one term read for two elements), with single tiles left over where the
+    column block changes or the count is odd.  Same bytes as the oracle and as the unpaired epilogue."""
+    M, N, K = shape
+    rng = np.random.default_rng(M + N + K + epi_warps)
+    a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), np.int8, -127, 127)
+    bias = rng.integers(-20000, 20001, N).astype(np.int32)
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+    shift = rng.integers(2, 12, N).astype(np.int32)
+    want = port.gemmlowp_fused(a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8)
+    for paired in (True, False):
+        got, kern = gpu_gemmlowp(ctx, a, b, bias, -7, 0, mult, shift, 3, 0, 255, np.uint8, pair=False,
+                                 epi_warps=epi_warps, channel_major=-1, paired_drain=paired)
+        assert kern == "tcgen05"
+        assert np.array_equal(got, want), (paired, np.argwhere(got != want)[:4])
