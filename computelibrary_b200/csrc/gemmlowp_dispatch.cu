@@ -81,15 +81,15 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
                                     bool allow_pair)
 {
     // The channel-major kernel (operand roles exchanged, output-stage terms in registers, stores through a byte
-    // transpose in shared memory) wins where the epilogue dominates and whole 128-channel blocks exist: measured
-    // 802816 x 256 x 64: 209 us against 235 us row-major; 200704 x 512 x 128: 113 / 125; 50176 x 1024 x 256:
-    // 63 / 70; 12544 x 2048 x 512: 39 / 47; but N = 64: 110 / 78 (half of the lanes idle).
+    // transpose in shared memory) against the row-major one with sixteen epilogue warps, paired drain and 256-bit
+    // stores, measured: 802816 x 256 x 64: 189 us against 170 us; 200704 x 512 x 128: 102 / 94; 50176 x 1024 x 256:
+    // 57 / 60; 12544 x 2048 x 512: 37 / 43.  It needs whole 128-channel blocks (N = 64: 110 / 78).
     GemmOperands o   = op;
     o.block_n        = pick_block_n(ctx, op); // before the automatic channel-major choice below
     if (o.channel_major == 0)
     {
         // with a fused residual the row-major epilogue stays ahead (block-1 conv3 + add: 344 us against 377 us)
-        o.channel_major = (o.K <= kShortK && o.N >= 256 && o.residual == nullptr) ? 1 : -1;
+        o.channel_major = (o.K >= 256 && o.K <= kShortK && o.N >= 256 && o.residual == nullptr) ? 1 : -1;
     }
     const int widest = o.N > 128 ? 256 : (o.N > 64 ? 128 : 64);
     if (o.block_n < widest)

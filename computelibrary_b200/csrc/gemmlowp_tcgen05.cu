@@ -292,7 +292,7 @@ struct TileParams
     int64_t  ldd;
     int      M, N, K;
     uint32_t idesc;
-    int      vec_ok;  // dst base and ldd are 16-byte aligned
+    int      vec_ok;  // row-major: vector_flags() of dst base, ldd and residual; channel-major: rows 8-byte aligned
     int      mode;    // kStageGeneric / kStageFast / kStageWide: encoding of the column terms (requant_pack4)
     uint32_t idesc_half; // SM-pair kernel: instruction descriptor of a half-width (N = 128) tile
     int      split_tail; // SM-pair kernel: split the tiles of a short last wave in two (see the kernel)
@@ -475,7 +475,14 @@ __device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, in
     else
     {
         uint8_t *o = drow + nc;
-        if (full && tp.vec_ok)
+        if (full && (tp.vec_ok & 2))
+        {
+            // one 256-bit store: the lane writes a whole 32-byte sector instead of two halves
+            asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o), "r"(v[0]), "r"(v[1]),
+                         "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                         : "memory");
+        }
+        else if (full && tp.vec_ok)
         {
             *reinterpret_cast<uint4 *>(o)      = make_uint4(v[0], v[1], v[2], v[3]);
             *reinterpret_cast<uint4 *>(o + 16) = make_uint4(v[4], v[5], v[6], v[7]);
@@ -596,7 +603,13 @@ __device__ __forceinline__ void load_residual(uint32_t (&r)[8], const uint8_t *r
     {
         return;
     }
-    if (nc + 32 <= tp.N && tp.vec_ok)
+    if (nc + 32 <= tp.N && (tp.vec_ok & 2))
+    {
+        asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "l"(rrow + nc));
+    }
+    else if (nc + 32 <= tp.N && tp.vec_ok)
     {
         const uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(rrow + nc));
         const uint4 r1 = __ldg(reinterpret_cast<const uint4 *>(rrow + nc + 16));
@@ -622,6 +635,20 @@ __device__ __forceinline__ void add_residual(uint32_t *w, const uint32_t (&r)[8]
     for (int j = 0; j < 8; ++j)
     {
         w[j] = __vminu4(__vmaxu4(__vaddus4(w[j], r[j]), tp.res_floor4), tp.res_cap4);
+    }
+}
+
+// Asks L2 for the residual bytes this thread will add to row m, columns [n_first, n_first + ncols): issued before the
+// wait for the accumulator, so the DRAM latency passes behind the MMA and the requantisation.
+__device__ __forceinline__ void prefetch_residual(const TileParams &tp, int m, int n_first, int ncols)
+{
+    if (m < tp.M)
+    {
+        const uint8_t *p = tp.residual + static_cast<int64_t>(m) * tp.ldd + n_first;
+        for (int c = 0; c < ncols && n_first + c < tp.N; c += 128)
+        {
+            asm volatile("prefetch.global.L2 [%0];" ::"l"(p + c));
+        }
     }
 }
 
@@ -1417,6 +1444,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int next = tile + static_cast<int>(gridDim.x);
                 pair_now       = next < num_tiles && next / num_m_blocks == tile / num_m_blocks;
             }
+            if (!kCM && !kS32Out && kGroups == 1 && tp.residual != nullptr)
+            {
+                constexpr int NCOLS = BLOCK_N / (kEpiWarps / 4);
+                const int     row   = (warp & 3) * 32 + lane;
+                const int     first = n0 + ((warp - kFirstEpi) >> 2) * NCOLS;
+                prefetch_residual(tp, m0 + row, first, NCOLS);
+                if (pair_now)
+                {
+                    prefetch_residual(tp, ((tile + static_cast<int>(gridDim.x)) % num_m_blocks) * BLOCK_M + row, first, NCOLS);
+                }
+            }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok && pair_now)
             {
@@ -2177,6 +2215,13 @@ void fill_extra_dst(TileParams &tp, const GemmOperands &op)
     }
 }
 
+// TileParams::vec_ok of a row-major output: 0 = byte stores; bit 0 = every row piece is 16-byte aligned; bit 1 = 32-byte
+// aligned as well (one 256-bit access per 32 output bytes, i.e. a whole DRAM sector per lane)
+int vector_flags(uint64_t address_bits)
+{
+    return (address_bits & 15) != 0 ? 0 : ((address_bits & 31) != 0 ? 1 : 3);
+}
+
 uint64_t extra_dst_bits(const GemmOperands &op)
 {
     uint64_t bits = reinterpret_cast<uintptr_t>(op.residual);
@@ -2253,7 +2298,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
-    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
+    tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
@@ -2336,7 +2381,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
                (static_cast<uint32_t>(P::BLOCK_N >> 3) << 17) | (static_cast<uint32_t>((2 * BLOCK_M) >> 4) << 24);
     tp.idesc_half = (tp.idesc & ~(0x3fu << 17)) | (static_cast<uint32_t>((P::BLOCK_N / 2) >> 3) << 17);
     tp.split_tail = op.split_tail >= 0 ? 1 : 0;
-    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
+    tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
@@ -2389,7 +2434,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     tp.K      = op.K;
     tp.idesc  = (2u << 4) | ((op.a_signed ? 1u : 0u) << 7) | ((op.b_signed ? 1u : 0u) << 10) |
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
-    tp.vec_ok = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 15) == 0;
+    tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
