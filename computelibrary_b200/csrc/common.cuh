@@ -111,6 +111,25 @@ __device__ __forceinline__ int32_t finalize(int32_t acc, int32_t mult, int32_t l
     return min(max(r, lo), hi);
 }
 
+// Four unsigned bytes at once: min(max(min(a + b, 255), floor), cap) with floor <= cap <= 255, floor4 / cap4 holding the
+// bound in every byte.  The byte-wise SIMD intrinsics (__vaddus4, __vmaxu4, __vminu4) have no instruction on
+// sm_100 and expand to about seven instructions per element; the 16-bit pair forms of add-then-min and max do, so
+// the bytes are widened into two words of halfword pairs (four byte permutes), added and bounded there (two or
+// four instructions) and narrowed again (one permute).
+__device__ __forceinline__ uint32_t add_clamp_u8x4(uint32_t a, uint32_t b, uint32_t floor4, uint32_t cap4)
+{
+    const uint32_t cap2 = cap4 & 0x00ff00ffu;
+    uint32_t lo = __viaddmin_u16x2(__byte_perm(a, 0, 0x4140), __byte_perm(b, 0, 0x4140), cap2);
+    uint32_t hi = __viaddmin_u16x2(__byte_perm(a, 0, 0x4342), __byte_perm(b, 0, 0x4342), cap2);
+    if (floor4 != 0) // uniform over the launch
+    {
+        const uint32_t floor2 = floor4 & 0x00ff00ffu;
+        lo = __vimax3_u16x2(lo, floor2, floor2);
+        hi = __vimax3_u16x2(hi, floor2, floor2);
+    }
+    return __byte_perm(lo, hi, 0x6420);
+}
+
 // Output stage QUANTIZE_DOWN (tests/validation/reference/GEMMLowp.cpp:66-104): x already holds
 // accumulator + offset + bias; wrapping multiply, arithmetic shift, clamp (bounds pre-intersected with the type).
 __device__ __forceinline__ int32_t finalize_int(int32_t x, int32_t mult, int32_t shift, int32_t lo, int32_t hi)

@@ -634,7 +634,7 @@ __device__ __forceinline__ void add_residual(uint32_t *w, const uint32_t (&r)[8]
 #pragma unroll
     for (int j = 0; j < 8; ++j)
     {
-        w[j] = __vminu4(__vmaxu4(__vaddus4(w[j], r[j]), tp.res_floor4), tp.res_cap4);
+        w[j] = add_clamp_u8x4(w[j], r[j], tp.res_floor4, tp.res_cap4);
     }
 }
 
@@ -938,8 +938,8 @@ __device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], c
             {
                 if (tp.residual != nullptr)
                 {
-                    w0 = __vminu4(__vmaxu4(__vaddus4(w0, res[k].x), tp.res_floor4), tp.res_cap4);
-                    w1 = __vminu4(__vmaxu4(__vaddus4(w1, res[k].y), tp.res_floor4), tp.res_cap4);
+                    w0 = add_clamp_u8x4(w0, res[k].x, tp.res_floor4, tp.res_cap4);
+                    w1 = add_clamp_u8x4(w1, res[k].y, tp.res_floor4, tp.res_cap4);
                 }
                 *reinterpret_cast<uint2 *>(tp.dst + off) = make_uint2(w0, w1);
             }

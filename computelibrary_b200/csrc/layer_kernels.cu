@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(kThreads)
 // Saturating form of the addition: for many quantizations (always when the three scales and zero points are
 // equal, as in a residual network whose tensors share one quantization) the oracle's result over all 65536
 // byte pairs is exactly min(max(min(a + b, 255), floor), cap).  The host proves that by enumeration
-// (classify_add, below) and this kernel then needs three byte-parallel instructions per four elements.
+// (classify_add, below) and this kernel then needs seven to nine instructions per four elements (add_clamp_u8x4).
 __global__ void __launch_bounds__(kThreads)
     add_saturating_kernel(const uint8_t *__restrict__ a, const uint8_t *__restrict__ b, uint8_t *__restrict__ dst,
                           int64_t n, bool vec, uint32_t floor4, uint32_t cap4)
@@ -174,10 +174,10 @@ __global__ void __launch_bounds__(kThreads)
         const uint4 va = __ldg(reinterpret_cast<const uint4 *>(a) + i);
         const uint4 vb = __ldg(reinterpret_cast<const uint4 *>(b) + i);
         uint4       r;
-        r.x = __vminu4(__vmaxu4(__vaddus4(va.x, vb.x), floor4), cap4);
-        r.y = __vminu4(__vmaxu4(__vaddus4(va.y, vb.y), floor4), cap4);
-        r.z = __vminu4(__vmaxu4(__vaddus4(va.z, vb.z), floor4), cap4);
-        r.w = __vminu4(__vmaxu4(__vaddus4(va.w, vb.w), floor4), cap4);
+        r.x = add_clamp_u8x4(va.x, vb.x, floor4, cap4);
+        r.y = add_clamp_u8x4(va.y, vb.y, floor4, cap4);
+        r.z = add_clamp_u8x4(va.z, vb.z, floor4, cap4);
+        r.w = add_clamp_u8x4(va.w, vb.w, floor4, cap4);
         reinterpret_cast<uint4 *>(dst)[i] = r;
     }
     for (int64_t i = (nv << 4) + tid; i < n; i += nth)
@@ -217,18 +217,29 @@ __global__ void __launch_bounds__(kThreads)
         const int hs = max(h * g.sy - g.pt, 0), he = min(h * g.sy - g.pt + g.ph, g.H);
         if (kVec)
         {
-            uint4 m = make_uint4(0, 0, 0, 0);
+            // running maxima as halfword pairs (even bytes / odd bytes of each word): the 16-bit pair maximum is one
+            // instruction, the byte-wise __vmaxu4 is not
+            uint32_t me[4] = {0, 0, 0, 0}, mo[4] = {0, 0, 0, 0};
             for (int y = hs; y < he; ++y)
             {
                 for (int x = ws; x < we; ++x)
                 {
                     const uint4 v = __ldg(reinterpret_cast<const uint4 *>(src + ((static_cast<int64_t>(b) * g.H + y) * g.W + x) * g.C) + c);
-                    m.x = __vmaxu4(m.x, v.x);
-                    m.y = __vmaxu4(m.y, v.y);
-                    m.z = __vmaxu4(m.z, v.z);
-                    m.w = __vmaxu4(m.w, v.w);
+                    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                    {
+                        const uint32_t e = __byte_perm(w[k], 0, 0x4240), o = __byte_perm(w[k], 0, 0x4341);
+                        me[k]            = __vimax3_u16x2(me[k], e, e);
+                        mo[k]            = __vimax3_u16x2(mo[k], o, o);
+                    }
                 }
             }
+            uint4 m;
+            m.x = __byte_perm(me[0], mo[0], 0x6240);
+            m.y = __byte_perm(me[1], mo[1], 0x6240);
+            m.z = __byte_perm(me[2], mo[2], 0x6240);
+            m.w = __byte_perm(me[3], mo[3], 0x6240);
             m.x = map4(table, m.x);
             m.y = map4(table, m.y);
             m.z = map4(table, m.z);
