@@ -787,14 +787,14 @@ __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_
     }
 }
 
-template <int BLOCK_N>
+template <int BLOCK_N, int kGroups>
 __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_t tmem_b, const int4 *s_col,
                                                         const TileParams &tp, const EpilogueParams &ep, int warp,
                                                         int lane, int m0a, int m0b, int n0)
 {
-    constexpr int  NCOLS = BLOCK_N / (kEpiWarps / 4);
-    const int      quad  = warp & 3;                 // tensor-memory lane quarter this warp may read
-    const int      half  = (warp - kFirstEpi) >> 2;  // which share of the columns
+    constexpr int  NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
+    const int      quad  = warp & 3;                                      // tensor-memory lane quarter this warp may read
+    const int      half  = kGroups == 1 ? (warp - kFirstEpi) >> 2 : 0;    // which share of the columns
     const uint32_t lanes = static_cast<uint32_t>(quad * 32) << 16;
     drain_accumulator_pair<NCOLS>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS, s_col + half * NCOLS, tp,
                                   ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane, n0 + half * NCOLS);
@@ -1414,9 +1414,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         bool          ok      = true;
         int           ti = 0;
         int           filled_n0 = -1;
+        // Paired drain (see drain_accumulator_pair): the tile this group drains next (kStride ordinals on) is drained
+        // together with the current one when it lies in the same column block and its accumulator buffer belongs
+        // to the same phase.  The MMA warp is untouched: it fills the partner buffer while the first one waits
+        // here, and meets both released afterwards.
+        // Only the 256-column tiles with their two buffers: with four buffers and two epilogue groups, and in the
+        // implicit convolution, pairing measured slower (the MMA warp can no longer run two tiles ahead).
+        constexpr int  kStride  = 1;
+        constexpr bool kCanPair = !kCM && !kS32Out && ACC == 2 && kGroups == 1;
+        int            skip     = -1; // ordinal of a tile already drained as the partner of an earlier one
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti)
         {
-            if (kGroups > 1 && (ti & 1) != group)
+            if ((kGroups > 1 && (ti & 1) != group) || ti == skip)
             {
                 continue;
             }
@@ -1435,30 +1444,28 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (kGroups == 1) epi_barrier();
                 else epi_group_barrier(group);
             }
-            // Paired drain (see drain_accumulator_pair): at buffer 0, when this CTA's next tile lies in the same
-            // column block, wait for both accumulators and drain them together.  The MMA warp is untouched: it
-            // fills buffer 1 while buffer 0 waits here, and meets the two released buffers afterwards.
-            bool pair_now = false;
-            if (!kCM && !kS32Out && kGroups == 1 && ACC == 2 && tp.pair_drain != 0 && tp.mode == kStageWide && as == 0)
+            const int tile_b   = tile + kStride * static_cast<int>(gridDim.x);
+            bool      pair_now = false;
+            if (kCanPair && tp.pair_drain != 0 && tp.mode == kStageWide && as < kStride)
             {
-                const int next = tile + static_cast<int>(gridDim.x);
-                pair_now       = next < num_tiles && next / num_m_blocks == tile / num_m_blocks;
+                pair_now = tile_b < num_tiles && tile_b / num_m_blocks == tile / num_m_blocks;
             }
-            if (!kCM && !kS32Out && kGroups == 1 && tp.residual != nullptr)
+            const int m0b = kCanPair ? (tile_b % num_m_blocks) * BLOCK_M : 0;
+            if (!kCM && !kS32Out && tp.residual != nullptr)
             {
-                constexpr int NCOLS = BLOCK_N / (kEpiWarps / 4);
+                constexpr int NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
                 const int     row   = (warp & 3) * 32 + lane;
-                const int     first = n0 + ((warp - kFirstEpi) >> 2) * NCOLS;
+                const int     first = n0 + (kGroups == 1 ? (warp - kFirstEpi) >> 2 : 0) * NCOLS;
                 prefetch_residual(tp, m0 + row, first, NCOLS);
                 if (pair_now)
                 {
-                    prefetch_residual(tp, ((tile + static_cast<int>(gridDim.x)) % num_m_blocks) * BLOCK_M + row, first, NCOLS);
+                    prefetch_residual(tp, m0b + row, first, NCOLS);
                 }
             }
             ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             if (ok && pair_now)
             {
-                ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(1), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+                ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as + kStride), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
             }
             if (ok)
             {
@@ -1469,10 +1476,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                     epilogue_warp_tile_cm<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, tp, ep, warp, lane, m0, n0,
                                                             smem + P::OFF_OUT);
                 }
-                else if (!kS32Out && kGroups == 1 && ACC == 2 && pair_now)
+                else if (kCanPair && pair_now)
                 {
-                    const int m0b = ((tile + static_cast<int>(gridDim.x)) % num_m_blocks) * BLOCK_M;
-                    epilogue_warp_tile_pair<BLOCK_N>(tmem_base, tmem_base + BLOCK_N, g_col, tp, ep, warp, lane, m0, m0b, n0);
+                    epilogue_warp_tile_pair<BLOCK_N, kGroups>(tmem_base + as * BLOCK_N, tmem_base + (as + kStride) * BLOCK_N,
+                                                              g_col, tp, ep, warp, lane, m0, m0b, n0);
                 }
                 else
                 {
@@ -1487,13 +1494,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                     mbar_arrive(tempty_bar(as)); // accumulator buffer may be overwritten (one arrival per warp)
                     if (pair_now)
                     {
-                        mbar_arrive(tempty_bar(1));
+                        mbar_arrive(tempty_bar(as + kStride));
                     }
                 }
-                if (pair_now) // two tiles consumed
+                if (pair_now)
                 {
-                    tile += static_cast<int>(gridDim.x);
-                    ++ti;
+                    skip = ti + kStride;
                 }
             }
         }
@@ -2208,7 +2214,9 @@ void fill_extra_dst(TileParams &tp, const GemmOperands &op)
     tp.res_floor4 = static_cast<uint32_t>(op.res_floor & 0xff) * 0x01010101u;
     tp.res_cap4   = static_cast<uint32_t>(op.res_cap & 0xff) * 0x01010101u;
     tp.n_extra    = op.n_extra_dst;
-    tp.pair_drain = (op.pair_drain >= 0 && op.n_extra_dst == 0 && op.wide_stage && !op.generic_stage) ? 1 : 0;
+    // paired drain: where the tile's time is its epilogue (K = 64: 227 -> 173 us, 128: 120 -> 96, 256: 67 -> 61,
+    // 512: 43 -> 43); with a longer main loop the MMA of the next tile should overlap the drain instead
+    tp.pair_drain = (op.pair_drain >= 0 && op.K <= 512 && op.n_extra_dst == 0 && op.wide_stage && !op.generic_stage) ? 1 : 0;
     for (int i = 0; i < kMaxExtraDst; ++i)
     {
         tp.extra_dst[i] = i < op.n_extra_dst ? static_cast<uint8_t *>(op.extra_dst[i]) : nullptr;

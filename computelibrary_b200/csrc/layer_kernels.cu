@@ -207,12 +207,26 @@ __global__ void __launch_bounds__(kThreads)
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x)
     {
-        const int     c  = static_cast<int>(i % cv);
-        int64_t       p  = i / cv;
-        const int     w  = static_cast<int>(p % g.Wo);
-        p /= g.Wo;
-        const int h = static_cast<int>(p % g.Ho);
-        const int b = static_cast<int>(p / g.Ho);
+        int c, w, h, b;
+        if (total <= 0x7fffffff) // 32-bit divisions: a 64-bit one costs more than the whole pooling window
+        {
+            uint32_t q = static_cast<uint32_t>(i);
+            c          = static_cast<int>(q % static_cast<uint32_t>(cv));
+            q /= static_cast<uint32_t>(cv);
+            w = static_cast<int>(q % static_cast<uint32_t>(g.Wo));
+            q /= static_cast<uint32_t>(g.Wo);
+            h = static_cast<int>(q % static_cast<uint32_t>(g.Ho));
+            b = static_cast<int>(q / static_cast<uint32_t>(g.Ho));
+        }
+        else
+        {
+            c         = static_cast<int>(i % cv);
+            int64_t p = i / cv;
+            w         = static_cast<int>(p % g.Wo);
+            p /= g.Wo;
+            h = static_cast<int>(p % g.Ho);
+            b = static_cast<int>(p / g.Ho);
+        }
         const int ws = max(w * g.sx - g.pl, 0), we = min(w * g.sx - g.pl + g.pw, g.W);
         const int hs = max(h * g.sy - g.pt, 0), he = min(h * g.sy - g.pt + g.ph, g.H);
         if (kVec)

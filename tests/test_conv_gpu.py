@@ -14,7 +14,7 @@ CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
 
 
 def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1),
-             implicit=True, want_kernel=None, tile_columns=0):
+             implicit=True, want_kernel=None, tile_columns=0, paired_drain=True):
     import torch
     B, H, W, Cc = src.shape
     OFM, kh, kw, _ = weights.shape
@@ -30,6 +30,8 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
         plan.allow_implicit(False)
     if tile_columns:
         plan.set_tile_columns(tile_columns)
+    if not paired_drain:
+        plan.set_paired_drain(False)
     if want_kernel is not None:
         assert plan.kernel == want_kernel, plan.kernel
     wo, ho = plan.out_dims()

@@ -390,7 +390,7 @@ def test_fused_quantize_down_stage_tensor_core_shapes(ctx, port):
 
 
 @pytest.mark.parametrize("epi_warps", [4, 8, 16])
-@pytest.mark.parametrize("shape", [(38477, 256, 64), (20000, 520, 96), (37900, 300, 1104)])
+@pytest.mark.parametrize("shape", [(38477, 256, 64), (20000, 520, 96), (37900, 300, 496)])
 def test_paired_drain(ctx, port, shape, epi_warps):
     """More 128 x 256 tiles than SMs, so a CTA owns several: consecutive tiles of one column block are drained from
     the two accumulator buffers together (one term read for two elements), with single tiles left over where the
