@@ -45,6 +45,8 @@ def parse_args():
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
     p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
     p.add_argument("--batch", type=int, default=256, help="global batch of c4 (split over the ranks)")
+    p.add_argument("--weak", action="store_true",
+                   help="c4: every rank runs a whole --batch (weak scaling) instead of its share of one global batch")
     p.add_argument("--layers", action="store_true", help="c4: print the per-layer time table to stderr")
     p.add_argument("--no-graph", action="store_true", help="c4: launch every layer eagerly instead of one CUDA graph")
     p.add_argument("--size", type=int, default=0, help="override M=N=K of c2 (profiling on a small case)")
@@ -527,7 +529,8 @@ def run_resnet(args):
     work = torch.cuda.Stream()
     torch.cuda.set_stream(work)
     ctx = cl.Context(local, work.cuda_stream)
-    b0, b1 = sharding.batch_shard(args.batch, world, rank)
+    global_batch = args.batch * world if args.weak else args.batch
+    b0, b1 = sharding.batch_shard(global_batch, world, rank)
     B = b1 - b0
     net = rn.ResNet50(ctx, B, seed=1)
     rng = np.random.default_rng(100 + rank)
@@ -577,25 +580,25 @@ def run_resnet(args):
         ach = ops_img * B / (statistics.mean(step_ms) * 1e-3) / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
         line = {
-            "metric": "resnet50_qasymm8_images_per_s", "value": args.batch / (ms * 1e-3), "unit": "img/s",
+            "metric": "resnet50_qasymm8_images_per_s", "value": global_batch / (ms * 1e-3), "unit": "img/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "strong", "vs_baseline": None, "dtype": "u8*s8->s32->u8", "data": "synthetic",
-            "config": {"workload": f"config4: QASYMM8 ResNet-50 v1, 224x224, global batch {args.batch}, per-channel s8 "
+            "scaling": "weak" if args.weak else "strong", "vs_baseline": None, "dtype": "u8*s8->s32->u8", "data": "synthetic",
+            "config": {"workload": f"config4: QASYMM8 ResNet-50 v1, 224x224, global batch {global_batch}, per-channel s8 "
                        "weights, batch norm folded, ReLU fused", "per_gpu_batch": B,
                        "l2": "flushed between timed steps (256 MB write)",
                        "sharding": "batch split over ranks, weights replicated, no collective",
                        "launch": "eager, one C-ABI call per layer" if graph is None else
                                  "one CUDA graph of the layer calls per step"},
-            "int8_tops": ops_img * args.batch / (ms * 1e-3) / 1e12,
+            "int8_tops": ops_img * global_batch / (ms * 1e-3) / 1e12,
             "gpu_launches": args.steps * net.launches,
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TOP/s", "frac": ach / peak,
                          "traffic": None, "peak_source": "2 x " + peaks["source"] + " dense bf16 cuBLAS rate",
                          "kernel": "whole network (54 convolutions + pooling / addition / softmax kernels)"},
             "clocks": clocks}
         if e2e_ms:
-            line["e2e"] = {"value": args.batch / (e2e * 1e-3), "unit": "img/s",
-                           "h2d_bytes_per_step": int(args.batch * 224 * 224 * 3),   # all ranks together
-                           "d2h_bytes_per_step": int(args.batch * 1000)}
+            line["e2e"] = {"value": global_batch / (e2e * 1e-3), "unit": "img/s",
+                           "h2d_bytes_per_step": int(global_batch * 224 * 224 * 3),   # all ranks together
+                           "d2h_bytes_per_step": int(global_batch * 1000)}
         print(json.dumps(line), flush=True)
     net.close()
     ctx.close()
