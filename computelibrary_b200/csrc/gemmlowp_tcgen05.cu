@@ -739,7 +739,8 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
 // together, kStageWide encoding only.  Every lane of a warp needs the 16-byte term of every column, so the
 // per-element term read from shared memory is what the load/store pipe spends most of a short-K epilogue on
 // (802816 x 256 x 64: 235 us, 134 us with one term read per 32 columns instead of 32).  Here a term is read
-// once for two elements; both residual rows are requested together.
+// once for two elements; both residual rows are requested together, after the arithmetic (requesting them while the
+// tensor-memory loads travel measured slower: block-1 conv3 + add 238 -> 284 us).
 template <int NCOLS>
 __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
                                                        const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
