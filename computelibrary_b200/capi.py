@@ -8,7 +8,7 @@ import re
 
 from . import build as _build
 
-U8, S8, S32 = 0, 1, 2
+U8, S8, S32, S16 = 0, 1, 2, 3  # S16: QSYMM16 destination of the stand-alone fixed-point output stage
 STAGE_NONE, STAGE_QUANTIZE_DOWN, STAGE_FIXEDPOINT = 0, 1, 2
 INT32_MIN, INT32_MAX = -(2 ** 31), 2 ** 31 - 1
 

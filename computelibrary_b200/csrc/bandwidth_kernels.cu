@@ -224,6 +224,7 @@ __global__ void __launch_bounds__(kThreads) offset_contribution_kernel(int32_t *
 // ---- stand-alone output stage ---------------------------------------------------------------------
 // CpuGemmLowpQuantizeDownInt32To{Uint8,Int8}ScaleByFixedPointKernel::run_internal
 // (…ToUint8ScaleByFixedPointKernel.cpp:78-186).  Thread per 4 outputs: one 128-bit load, one 32-bit store.
+template <bool kOut16>
 __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *__restrict__ in, int64_t ld_in_elems,
                                                                 const int32_t *__restrict__ bias,
                                                                 uint8_t *__restrict__ out, int64_t ld_out, int M,
@@ -240,7 +241,7 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
         const int      m    = static_cast<int>(g / groups_per_row);
         const int      n0   = static_cast<int>(g % groups_per_row) * 4;
         const int32_t *src  = in + m * ld_in_elems + n0;
-        uint8_t       *dst  = out + m * ld_out + n0;
+        uint8_t       *dst  = out + m * ld_out + n0 * (kOut16 ? 2 : 1);
         const bool     full = n0 + 4 <= N;
         int32_t        v[4];
         if (full && vec_ok)
@@ -253,7 +254,7 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
 #pragma unroll
             for (int j = 0; j < 4; ++j) v[j] = (n0 + j < N) ? src[j] : 0;
         }
-        uint32_t packed = 0;
+        uint32_t packed = 0, packed_hi = 0; // 8-bit: four bytes in packed; 16-bit: two halfwords in each
 #pragma unroll
         for (int j = 0; j < 4; ++j)
         {
@@ -264,9 +265,30 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
             const int32_t sh = shifts != nullptr ? shifts[n] : shift;
             const int32_t r  = integer_stage ? finalize_int(x + offset, mu, sh, lo, hi)
                                              : finalize(x, mu, max(-sh, 0), max(sh, 0), offset, lo, hi);
-            packed |= (static_cast<uint32_t>(r) & 0xffu) << (8 * j);
+            if (kOut16)
+            {
+                (j < 2 ? packed : packed_hi) |= (static_cast<uint32_t>(r) & 0xffffu) << (16 * (j & 1));
+            }
+            else
+            {
+                packed |= (static_cast<uint32_t>(r) & 0xffu) << (8 * j);
+            }
         }
-        if (full && vec_ok)
+        if (kOut16)
+        {
+            if (full && vec_ok)
+            {
+                *reinterpret_cast<uint2 *>(dst) = make_uint2(packed, packed_hi);
+            }
+            else
+            {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (n0 + j < N)
+                        reinterpret_cast<uint16_t *>(dst)[j] = static_cast<uint16_t>((j < 2 ? packed : packed_hi) >> (16 * (j & 1)));
+            }
+        }
+        else if (full && vec_ok)
         {
             *reinterpret_cast<uint32_t *>(dst) = packed;
         }
@@ -475,16 +497,24 @@ cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, 
 cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
                                 void *d_out, int64_t ld_out_bytes, int M, int N, const int32_t *d_mults,
                                 const int32_t *d_shifts, int32_t mult, int32_t shift, int32_t offset, int32_t lo,
-                                int32_t hi, bool integer_stage)
+                                int32_t hi, bool integer_stage, bool out16)
 {
     if (M <= 0 || N <= 0) return CUGL_SUCCESS;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(d_in) | static_cast<uint64_t>(ld_in_bytes)) & 15) == 0 &&
-                        ((reinterpret_cast<uintptr_t>(d_out) | static_cast<uint64_t>(ld_out_bytes)) & 3) == 0;
+                        ((reinterpret_cast<uintptr_t>(d_out) | static_cast<uint64_t>(ld_out_bytes)) & (out16 ? 7 : 3)) == 0;
     const int blocks = grid_for(static_cast<int64_t>(M) * ((N + 3) / 4), ctx->sm_count, 2);
-    output_stage_kernel<<<blocks, kThreads, 0, ctx->stream>>>(d_in, ld_in_bytes / 4, d_bias,
-                                                              static_cast<uint8_t *>(d_out), ld_out_bytes, M, N,
-                                                              d_mults, d_shifts, mult, shift, offset, lo, hi, vec_ok,
-                                                              integer_stage);
+    if (out16)
+    {
+        output_stage_kernel<true><<<blocks, kThreads, 0, ctx->stream>>>(
+            d_in, ld_in_bytes / 4, d_bias, static_cast<uint8_t *>(d_out), ld_out_bytes, M, N, d_mults, d_shifts, mult,
+            shift, offset, lo, hi, vec_ok, integer_stage);
+    }
+    else
+    {
+        output_stage_kernel<false><<<blocks, kThreads, 0, ctx->stream>>>(
+            d_in, ld_in_bytes / 4, d_bias, static_cast<uint8_t *>(d_out), ld_out_bytes, M, N, d_mults, d_shifts, mult,
+            shift, offset, lo, hi, vec_ok, integer_stage);
+    }
     return check_cuda(ctx, cudaGetLastError(), "output_stage_kernel");
 }
 

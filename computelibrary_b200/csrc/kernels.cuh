@@ -19,7 +19,7 @@ cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, 
 cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,
                                 void *d_out, int64_t ld_out_bytes, int M, int N, const int32_t *d_mults,
                                 const int32_t *d_shifts, int32_t mult, int32_t shift, int32_t offset, int32_t lo,
-                                int32_t hi, bool integer_stage = false);
+                                int32_t hi, bool integer_stage = false, bool out16 = false);
 // 2x2 space-to-depth lowering of stride-2 convolutions with <= 4 channels (see bandwidth_kernels.cu)
 cugl_status launch_fold_input(cugl_context *ctx, const void *d_src, void *d_dst, int B, int H, int W, int C, int H2,
                               int W2, int zero_point);

@@ -718,8 +718,10 @@ extern "C"
                                   int32_t shift, int32_t n_mult, int32_t result_offset, int32_t min_bound,
                                   int32_t max_bound)
     {
-        if (ctx == nullptr || d_in == nullptr || d_out == nullptr || !is_q8(out_dtype) || M < 0 || N < 0 ||
-            ld_in_bytes < 4ll * N || (ld_in_bytes & 3) != 0 || ld_out_bytes < N)
+        const bool out16 = out_dtype == CUGL_S16; // QSYMM16 (CpuGemmLowpQuantizeDownInt32ToInt16ScaleByFixedPointKernel)
+        if (ctx == nullptr || d_in == nullptr || d_out == nullptr || !(is_q8(out_dtype) || out16) || M < 0 || N < 0 ||
+            ld_in_bytes < 4ll * N || (ld_in_bytes & 3) != 0 || ld_out_bytes < (out16 ? 2ll : 1ll) * N ||
+            (out16 && (((reinterpret_cast<uintptr_t>(d_out) | static_cast<uint64_t>(ld_out_bytes)) & 1) != 0)))
         {
             return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage: bad argument");
         }
@@ -732,10 +734,12 @@ extern "C"
         {
             return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_output_stage: per-channel needs N multipliers and shifts");
         }
-        const int32_t tlo = out_dtype == CUGL_S8 ? -128 : 0, thi = out_dtype == CUGL_S8 ? 127 : 255;
+        const int32_t tlo = out16 ? -32768 : (out_dtype == CUGL_S8 ? -128 : 0);
+        const int32_t thi = out16 ? 32767 : (out_dtype == CUGL_S8 ? 127 : 255);
         return launch_output_stage(ctx, d_in, ld_in_bytes, d_bias, d_out, ld_out_bytes, M, N,
                                    pc ? d_multipliers : nullptr, pc ? d_shifts : nullptr, multiplier, shift,
-                                   result_offset, min_bound > tlo ? min_bound : tlo, max_bound < thi ? max_bound : thi);
+                                   result_offset, min_bound > tlo ? min_bound : tlo, max_bound < thi ? max_bound : thi,
+                                   false, out16);
     }
 
     cugl_status cugl_output_stage_quantize_down(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes, const int32_t *d_bias,

@@ -52,7 +52,8 @@ typedef enum cugl_dtype
 {
     CUGL_U8  = 0,
     CUGL_S8  = 1,
-    CUGL_S32 = 2
+    CUGL_S32 = 2,
+    CUGL_S16 = 3 /* QSYMM16: destination of the stand-alone fixed-point output stage only */
 } cugl_dtype;
 
 /* GEMMLowpOutputStageType (arm_compute/function_info/GEMMInfo.h:40-46).  Only NONE and
@@ -274,7 +275,10 @@ CUGL_API cugl_status cugl_offset_contribution(cugl_context *ctx, int32_t *d_mm, 
                                               int32_t a_offset, int32_t b_offset);
 /* NEGEMMLowpOutputStage, QUANTIZE_DOWN_FIXEDPOINT (src/cpu/operators/CpuGemmLowpOutputStage.cpp:41-167,
  * CpuGemmLowpQuantizeDownInt32ToUint8ScaleByFixedPointKernel.cpp:78-186): S32 [M,N] (+ S32 bias [N])
- * -> U8 / S8 [M,N].  n_mult == 1: per-tensor (the NE function), n_mult == N: per-column device vectors. */
+ * -> U8 / S8 [M,N].  n_mult == 1: per-tensor (the NE function), n_mult == N: per-column device vectors.
+ * out_dtype CUGL_S16 is the QSYMM16 variant (CpuGemmLowpOutputStage.cpp:73-80,
+ * CpuGemmLowpQuantizeDownInt32ToInt16ScaleByFixedPointKernel): the same arithmetic saturated to int16, rows of
+ * ld_out_bytes >= 2 N bytes, 2-byte aligned; the NE kernel has no offset, pass result_offset = 0 for it. */
 CUGL_API cugl_status cugl_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t ld_in_bytes,
                                        const int32_t *d_bias, void *d_out, int64_t ld_out_bytes, int32_t out_dtype,
                                        int32_t M, int32_t N, const int32_t *d_multipliers, const int32_t *d_shifts,

@@ -201,6 +201,10 @@ class _Port(_Layers):
         mult, shift = _i32arr(mult), _i32arr(shift)
         bias = None if bias is None else _i32arr(bias)
         out = np.empty((M, N), out_dtype)
+        if out.dtype == np.int16:  # QSYMM16 destination
+            self.lib.orc_output_stage_s16(_ptr(acc), _ptr(bias), _ptr(out), M, N, _ptr(mult), _ptr(shift),
+                                          int(mult.size), _i32(offset), _i32(lo), _i32(hi))
+            return out
         self.lib.orc_output_stage(_ptr(acc), _ptr(bias), _ptr(out), _signed(out), M, N, _ptr(mult), _ptr(shift),
                                   int(mult.size), _i32(offset), _i32(lo), _i32(hi))
         return out
@@ -338,7 +342,9 @@ class _Ref(_Layers):
         mult, shift = _i32arr(mult), _i32arr(shift)
         bias = None if bias is None else _i32arr(bias)
         out = np.empty((M, N), out_dtype)
-        fn = self.lib.ref_quantize_down_fixedpoint_s8 if out.dtype == np.int8 else self.lib.ref_quantize_down_fixedpoint_u8
+        fn = {np.dtype(np.int8): self.lib.ref_quantize_down_fixedpoint_s8,
+              np.dtype(np.int16): self.lib.ref_quantize_down_fixedpoint_s16,
+              np.dtype(np.uint8): self.lib.ref_quantize_down_fixedpoint_u8}[out.dtype]
         fn(_ptr(acc), _ptr(bias), _ptr(out), M, N, _ptr(mult), _ptr(shift), int(mult.size), _i32(offset), _i32(lo),
            _i32(hi))
         return out

@@ -298,6 +298,34 @@ ORC_EXPORT void orc_output_stage(const int32_t *in, const int32_t *bias, void *o
     }
 }
 
+/* The same stage with a QSYMM16 destination (CpuGemmLowpQuantizeDownInt32ToInt16ScaleByFixedPointKernel;
+ * tests/validation/reference/GEMMLowp.cpp:106-157 instantiated for int16_t, :423-436): identical arithmetic,
+ * bounds intersected with the int16 range. */
+ORC_EXPORT void orc_output_stage_s16(const int32_t *in, const int32_t *bias, int16_t *out, int M, int N,
+                                     const int32_t *mult, const int32_t *shift, int n_mult, int32_t offset, int32_t lo,
+                                     int32_t hi)
+{
+    const int32_t l = lo > -32768 ? lo : -32768;
+    const int32_t h = hi < 32767 ? hi : 32767;
+#if defined(_OPENMP)
+#pragma omp parallel for schedule(static)
+#endif
+    for (int i = 0; i < M; ++i)
+    {
+        for (int j = 0; j < N; ++j)
+        {
+            int32_t v = in[(size_t)i * N + j];
+            if (bias != NULL)
+            {
+                v = wrap_add(v, bias[j]);
+            }
+            const int32_t m = n_mult > 1 ? mult[j] : mult[0];
+            const int32_t s = n_mult > 1 ? shift[j] : shift[0];
+            out[(size_t)i * N + j] = (int16_t)orc_quantize_down_fixedpoint(v, m, s, offset, l, h);
+        }
+    }
+}
+
 /* Output stage QUANTIZE_DOWN (integer multiply): ((in + offset + bias) * mult) >> shift in wrapping int32 with an
  * arithmetic shift, clamped to [lo, hi] only when lo != hi, then saturated to the 8-bit type.
  * tests/validation/reference/GEMMLowp.cpp:66-104.  n_mult == 1: per-tensor, else per-column. */

@@ -77,7 +77,7 @@ void qdown(const int32_t *in, const int32_t *bias, void *out, int M, int N, cons
     {
         dst = reference::gemmlowp_quantize_down_scale_by_fixedpoint<int32_t, TO>(tin, vm, vs, offset, lo, hi);
     }
-    std::memcpy(out, dst.data(), size_t(M) * N);
+    std::memcpy(out, dst.data(), size_t(M) * N * sizeof(TO));
 }
 
 template <typename TO>
@@ -163,6 +163,14 @@ extern "C"
                                          int hi)
     {
         qdown<int8_t>(in, bias, out, M, N, mult, shift, n_mult, offset, lo, hi);
+    }
+
+    // QSYMM16 destination: the int16_t instantiation of the same reference template (GEMMLowp.cpp:423-436)
+    void ref_quantize_down_fixedpoint_s16(const int32_t *in, const int32_t *bias, int16_t *out, int M, int N,
+                                          const int32_t *mult, const int32_t *shift, int n_mult, int offset, int lo,
+                                          int hi)
+    {
+        qdown<int16_t>(in, bias, out, M, N, mult, shift, n_mult, offset, lo, hi);
     }
 
     // reference::gemmlowp_quantize_down_scale (the QUANTIZE_DOWN integer stage), GEMMLowp.cpp:66-104, 278-307

@@ -81,6 +81,10 @@ def main():
         out[g["key"] + "_int_pt"] = ref.output_stage_int(acc, g["bias"], im[:1], ish[:1], ioff, ilo, ihi, g["out_dtype"])
         out[g["key"] + "_int_pc"] = ref.output_stage_int(acc0, g["bias"], im, ish, ioff, ilo, ihi, g["out_dtype"])
         out[g["key"] + "_int_nb"] = ref.output_stage_int(acc0, None, im, ish, ioff, 0, 0, g["out_dtype"])
+        # QSYMM16 destination of the fixed-point stage: per-tensor with bounds, per-channel over the whole int16 range
+        out[g["key"] + "_s16_pt"] = ref.output_stage(acc, g["bias"], g["mult"][:1], g["shift"][:1] - 6, 0, -20000, 25000,
+                                                     np.int16)
+        out[g["key"] + "_s16_pc"] = ref.output_stage(acc0, None, g["mult"], g["shift"] - 6, 0, -32768, 32767, np.int16)
     np.savez_compressed(os.path.join(HERE, "gemmlowp_golden.npz"), **out)
 
     # --- convolution (NCHW oracle; stored NHWC) and im2col -----------------------------------------

@@ -119,6 +119,32 @@ def test_output_stage_quantize_down(ctx, port, out_dtype, M, N):
                               port.output_stage_int(acc, bias, mult, shift, -4, lo + 3, hi - 3, out_dtype))
 
 
+@pytest.mark.parametrize("M,N", [(1, 1), (37, 53), (300, 1000)])
+def test_output_stage_qsymm16(ctx, port, M, N):
+    """NEGEMMLowpOutputStage with a QSYMM16 destination (cugl_output_stage, out_dtype CUGL_S16): per-tensor and
+    per-channel, with and without bias, odd and 8-byte aligned rows, bounded and whole-range."""
+    import torch
+    rng = np.random.default_rng(M * N + 16)
+    acc = rng.integers(-2 ** 24, 2 ** 24, (M, N)).astype(np.int32)
+    acc.flat[:2] = [2 ** 31 - 1, -2 ** 31][:acc.size]
+    bias = rng.integers(-9000, 9001, N).astype(np.int32)
+    out = torch.empty((M, N), dtype=torch.int16, device="cuda")
+    for (qm, sh, lo, hi) in [(1759218688, 9, -32768, 32767), (1234567890, -1, -1000, 2000), (2 ** 31 - 1, 3, 0, 0)]:
+        for b in (None, bias):
+            ctx.output_stage(_t(acc), N * 4, _t(b) if b is not None else None, out, N * 2, capi.S16, M, N, None, None,
+                             qm, sh, 1, 0, lo, hi)
+            ctx.sync()
+            want = port.output_stage(acc, b, [qm], [sh], 0, lo, hi, np.int16)
+            assert np.array_equal(out.cpu().numpy(), want), (qm, sh, lo, hi)
+    if N > 1:
+        mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+        shift = rng.integers(-1, 14, N).astype(np.int32)
+        ctx.output_stage(_t(acc), N * 4, _t(bias), out, N * 2, capi.S16, M, N, _t(mult), _t(shift), 0, 0, N, 5, -30000,
+                         31000)
+        ctx.sync()
+        assert np.array_equal(out.cpu().numpy(), port.output_stage(acc, bias, mult, shift, 5, -30000, 31000, np.int16))
+
+
 def test_im2col_golden_and_oracle(ctx, port):
     import torch
     gold = np.load(os.path.join(GOLDEN, "conv_golden.npz"))

@@ -163,6 +163,32 @@ def test_integer_stage_golden(port, gemm_golden):
     assert n == 24
 
 
+def test_qsymm16_stage_golden_and_reference(port, ref, gemm_golden):
+    """Fixed-point output stage with a QSYMM16 destination: the restatement against fixtures made by the int16_t
+    instantiation of the reference's gemmlowp_quantize_down_scale_by_fixedpoint, and against that code directly on
+    random accumulators (left shifts, INT32 extremes, equal bounds)."""
+    for g in golden_gemm_cases():
+        acc = port.gemmlowp_core(g["a"], g["b"], g["a_off"], g["b_off"])
+        acc0 = port.gemmlowp_core(g["a"], g["b"], g["a_off"], 0)
+        assert np.array_equal(port.output_stage(acc, g["bias"], g["mult"][:1], g["shift"][:1] - 6, 0, -20000, 25000, np.int16),
+                              gemm_golden[g["key"] + "_s16_pt"])
+        assert np.array_equal(port.output_stage(acc0, None, g["mult"], g["shift"] - 6, 0, -32768, 32767, np.int16),
+                              gemm_golden[g["key"] + "_s16_pc"])
+    if ref is None:
+        return
+    rng = np.random.default_rng(5)
+    acc = rng.integers(-2 ** 24, 2 ** 24, (37, 53)).astype(np.int32)
+    acc.flat[:2] = [2 ** 31 - 1, -2 ** 31]
+    bias = rng.integers(-10000, 10000, 53).astype(np.int32)
+    for nm in (1, 53):
+        mult = rng.integers(2 ** 30, 2 ** 31 - 1, nm).astype(np.int32)
+        shift = rng.integers(-1, 12, nm).astype(np.int32)
+        for lo, hi in ((-32768, 32767), (-1000, 2000), (0, 0)):
+            for b in (None, bias):
+                assert np.array_equal(port.output_stage(acc, b, mult, shift, 0, lo, hi, np.int16),
+                                      ref.output_stage(acc, b, mult, shift, 0, lo, hi, np.int16)), (nm, lo, hi)
+
+
 @pytest.mark.parametrize("out_dtype", [np.uint8, np.int8])
 def test_port_vs_reference_integer_stage(port, ref, out_dtype):
     rng = np.random.default_rng(77)
