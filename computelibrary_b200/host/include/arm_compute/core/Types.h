@@ -19,6 +19,7 @@ enum class DataType
     QASYMM8,
     QASYMM8_SIGNED,
     QSYMM8_PER_CHANNEL,
+    QSYMM16,
     S32,
     F32
 };
@@ -36,7 +37,7 @@ enum class DimensionRoundingType
 
 inline size_t element_size_from_data_type(DataType dt)
 {
-    return (dt == DataType::S32 || dt == DataType::F32) ? 4 : 1;
+    return (dt == DataType::S32 || dt == DataType::F32) ? 4 : (dt == DataType::QSYMM16 ? 2 : 1);
 }
 inline bool is_data_type_quantized_per_channel(DataType dt)
 {

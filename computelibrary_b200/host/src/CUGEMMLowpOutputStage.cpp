@@ -11,8 +11,13 @@ Status CUGEMMLowpOutputStage::validate(const ITensorInfo *input, const ITensorIn
     // CpuGemmLowpOutputStage::validate (src/cpu/operators/CpuGemmLowpOutputStage.cpp:100-161)
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(input == nullptr || output == nullptr, "nullptr tensor info");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(input->data_type() != DataType::S32, "input must be S32");
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() != DataType::QASYMM8 && output->data_type() != DataType::QASYMM8_SIGNED,
-                                    "output must be QASYMM8 or QASYMM8_SIGNED");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() != DataType::QASYMM8 && output->data_type() != DataType::QASYMM8_SIGNED &&
+                                        output->data_type() != DataType::QSYMM16,
+                                    "output must be QASYMM8, QASYMM8_SIGNED or QSYMM16");
+    // QSYMM16 exists for the fixed-point stage only (CpuGemmLowpOutputStage.cpp:73-80)
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() == DataType::QSYMM16 &&
+                                        info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT,
+                                    "a QSYMM16 output needs QUANTIZE_DOWN_FIXEDPOINT");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT &&
                                         info.type != GEMMLowpOutputStageType::QUANTIZE_DOWN,
                                     "only QUANTIZE_DOWN and QUANTIZE_DOWN_FIXEDPOINT are implemented");
@@ -65,7 +70,10 @@ void CUGEMMLowpOutputStage::run()
         stage_fn(ctx, static_cast<const int32_t *>(cu_device_ptr(_input)),
                           static_cast<int64_t>(in->strides_in_bytes()[1]), static_cast<const int32_t *>(cu_device_ptr(_bias)),
                           cu_device_ptr(_output), static_cast<int64_t>(_output->info()->strides_in_bytes()[1]),
-                          _output->info()->data_type() == DataType::QASYMM8 ? CUGL_U8 : CUGL_S8, M, N,
+                          _output->info()->data_type() == DataType::QASYMM8
+                              ? CUGL_U8
+                              : (_output->info()->data_type() == DataType::QSYMM16 ? CUGL_S16 : CUGL_S8),
+                          M, N,
                           static_cast<const int32_t *>(_d_mults), static_cast<const int32_t *>(_d_shifts),
                           _info.gemmlowp_multiplier, _info.gemmlowp_shift, _info.is_quantized_per_channel ? N : 1,
                           _info.gemmlowp_offset, _info.gemmlowp_min_bound, _info.gemmlowp_max_bound),

@@ -28,6 +28,8 @@ extern "C"
     void orc_gemmlowp_fused(const void *a, int a_signed, const void *b, int b_signed, const int32_t *bias, void *out,
                             int out_signed, int M, int N, int K, int32_t a_off, int32_t b_off, const int32_t *mult,
                             const int32_t *shift, int n_mult, int32_t offset, int32_t lo, int32_t hi);
+    void orc_output_stage_s16(const int32_t *in, const int32_t *bias, int16_t *out, int M, int N, const int32_t *mult,
+                              const int32_t *shift, int n_mult, int32_t offset, int32_t lo, int32_t hi);
     void orc_conv2d_nhwc(const void *src, int src_signed, const void *weights, int w_signed, const int32_t *bias,
                          void *dst, int C, int W, int H, int B, int kw, int kh, int OFM, int sx, int sy, int pad_l,
                          int pad_t, int dil_x, int dil_y, int Wo, int Ho, int32_t in_zp, int32_t w_zp,
@@ -166,22 +168,38 @@ static void test_gemmlowp_config1()
     stage.gemmlowp_max_bound  = 255;
     stage.output_data_type    = DataType::QASYMM8;
 
+    // the same accumulators through the QSYMM16 variant of the stage (no offset, whole int16 range)
+    CUTensor out16;
+    out16.allocator()->init(TensorInfo(TensorShape(N, M), 1, DataType::QSYMM16, QuantizationInfo(0.001f, 0)));
+    GEMMLowpOutputStageInfo stage16 = stage;
+    stage16.gemmlowp_shift          = 2;
+    stage16.gemmlowp_offset         = 0;
+    stage16.gemmlowp_min_bound      = -32768;
+    stage16.gemmlowp_max_bound      = 32767;
+    stage16.output_data_type        = DataType::QSYMM16;
+    GEMMLowpOutputStageInfo bad16   = stage16;
+    bad16.type                      = GEMMLowpOutputStageType::QUANTIZE_DOWN;
+    CHECK(bool(CUGEMMLowpOutputStage::validate(acc.info(), bias.info(), out16.info(), stage16)));
+    CHECK(!bool(CUGEMMLowpOutputStage::validate(acc.info(), bias.info(), out16.info(), bad16)));
+
     CUGEMMLowpMatrixMultiplyCore core;
     core.configure(&a, &b, nullptr, &acc);
-    CUGEMMLowpOutputStage os;
+    CUGEMMLowpOutputStage os, os16;
     os.configure(&acc, &bias, &out, stage);
+    os16.configure(&acc, &bias, &out16, stage16);
     CUGEMMLowpMatrixMultiplyCore fused;
     GEMMInfo                     info;
     info.set_gemmlowp_output_stage(stage);
     fused.configure(&a, &b, &bias, &out_fused, info);
 
     // allocation after configure, as the library requires
-    for (CUTensor *t : {&a, &b, &bias, &acc, &out, &out_fused}) t->allocator()->allocate();
+    for (CUTensor *t : {&a, &b, &bias, &acc, &out, &out_fused, &out16}) t->allocator()->allocate();
     upload(a, ha);
     upload(b, hb);
     upload(bias, hbias);
     core.run();
     os.run();
+    os16.run();
     fused.run();
     fused.run(); // MultipleExecution: same output
     CUScheduler::get().sync();
@@ -194,6 +212,10 @@ static void test_gemmlowp_config1()
     CHECK(download<int32_t>(acc, want_acc.size()) == want_acc);
     CHECK(download<uint8_t>(out, want.size()) == want);
     CHECK(download<uint8_t>(out_fused, want.size()) == want);
+    std::vector<int16_t> want16(size_t(M) * N);
+    const int32_t        shift16 = 2;
+    orc_output_stage_s16(want_acc.data(), hbias.data(), want16.data(), M, N, &mult, &shift16, 1, 0, -32768, 32767);
+    CHECK(download<int16_t>(out16, want16.size()) == want16);
 
     // update_quantization_parameters: new scales / offsets, recomputed stage
     a.info()->set_quantization_info(QuantizationInfo(0.03f, -100));
