@@ -278,15 +278,18 @@ __global__ void __launch_bounds__(kThreads)
 // AVG (tests/validation/reference/PoolingLayer.cpp:137-172): float sum in window order (y outer, x inner),
 // divided by the window area with or without the padding.  One thread per output element; consecutive
 // threads take consecutive channels.
+// kVec = channels per thread (4: one 32-bit load per tap; every channel keeps its own sum in window order).
+template <int kVec>
 __global__ void __launch_bounds__(kThreads)
     avgpool_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst, PoolGeom g, QInfo in, QInfo out)
 {
-    const int64_t total = static_cast<int64_t>(g.B) * g.Ho * g.Wo * g.C;
+    const int     cv    = g.C / kVec;
+    const int64_t total = static_cast<int64_t>(g.B) * g.Ho * g.Wo * cv;
     for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * blockDim.x)
     {
-        const int c = static_cast<int>(i % g.C);
-        int64_t   p = i / g.C;
+        const int c = static_cast<int>(i % cv) * kVec;
+        int64_t   p = i / cv;
         const int w = static_cast<int>(p % g.Wo);
         p /= g.Wo;
         const int h = static_cast<int>(p % g.Ho);
@@ -299,15 +302,44 @@ __global__ void __launch_bounds__(kThreads)
         we = min(we, g.W);
         he = min(he, g.H);
         if (g.exclude_padding) pool = (he - hs) * (we - ws);
-        float sum = 0.f;
+        float sum[kVec];
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) sum[k] = 0.f;
         for (int y = hs; y < he; ++y)
         {
             for (int x = ws; x < we; ++x)
             {
-                sum = __fadd_rn(sum, dequantize(src[((static_cast<int64_t>(b) * g.H + y) * g.W + x) * g.C + c], in.scale, in.zp));
+                const uint8_t *px = src + ((static_cast<int64_t>(b) * g.H + y) * g.W + x) * g.C + c;
+                if (kVec == 4)
+                {
+                    const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(px));
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                    {
+                        sum[k] = __fadd_rn(sum[k], dequantize(static_cast<uint8_t>(v >> (8 * k)), in.scale, in.zp));
+                    }
+                }
+                else
+                {
+                    sum[0] = __fadd_rn(sum[0], dequantize(px[0], in.scale, in.zp));
+                }
             }
         }
-        dst[i] = static_cast<uint8_t>(quantize_u8(__fdiv_rn(sum, static_cast<float>(pool)), out.scale, out.zp));
+        uint8_t *o = dst + ((static_cast<int64_t>(b) * g.Ho + h) * g.Wo + w) * g.C + c;
+        if (kVec == 4)
+        {
+            uint32_t r = 0;
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+            {
+                r |= static_cast<uint32_t>(quantize_u8(__fdiv_rn(sum[k], static_cast<float>(pool)), out.scale, out.zp) & 0xff) << (8 * k);
+            }
+            *reinterpret_cast<uint32_t *>(o) = r;
+        }
+        else
+        {
+            o[0] = static_cast<uint8_t>(quantize_u8(__fdiv_rn(sum[0], static_cast<float>(pool)), out.scale, out.zp));
+        }
     }
 }
 
@@ -563,8 +595,18 @@ extern "C"
             }
             return check_cuda(ctx, cudaGetLastError(), "maxpool_kernel");
         }
-        avgpool_kernel<<<grid_for(pixels * g.C, ctx->sm_count), kThreads, 0, ctx->stream>>>(
-            static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), g, in, out);
+        const bool vec4 = (g.C % 4) == 0 &&
+                          ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_dst)) & 3) == 0;
+        if (vec4)
+        {
+            avgpool_kernel<4><<<grid_for(pixels * (g.C / 4), ctx->sm_count), kThreads, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), g, in, out);
+        }
+        else
+        {
+            avgpool_kernel<1><<<grid_for(pixels * g.C, ctx->sm_count), kThreads, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), g, in, out);
+        }
         return check_cuda(ctx, cudaGetLastError(), "avgpool_kernel");
     }
 
