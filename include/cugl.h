@@ -221,7 +221,7 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_epilogue_warps(cugl_gemm_plan *plan,
 /* The tensor-core GEMM can also run with the operand roles exchanged, which makes an accumulator lane an output
  * channel (output-stage terms in registers, byte-wise transposed stores; never with a row-sum term or several
  * destinations).  mode > 0 requests it, < 0 forbids it, 0 lets the library choose (K from 256 to 1024 with at
- * least 256 output channels and no fused residual).  Testing / measurement aid: the results are identical. */
+ * least 256 output channels).  Testing / measurement aid: the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_channel_major(cugl_gemm_plan *plan, int mode);
 /* SM-pair kernel: when the last wave of 256 x 256 tiles fills at most half of the SM pairs, its tiles are
  * processed as two 256 x 128 halves each (on by default).  on = 0 keeps them whole.  Testing / measurement aid:
