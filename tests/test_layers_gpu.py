@@ -44,7 +44,12 @@ def test_pool_resnet_shapes(ctx, port):
     r = np.random.default_rng(21)
     for shape, geom in [((2, 112, 112, 64), ("max", (3, 3), (2, 2), (0, 1, 0, 1), False, False)),
                         ((2, 56, 56, 256), ("max", (1, 1), (2, 2), (0, 0, 0, 0), True, False)),
-                        ((4, 7, 7, 2048), ("avg", None, None, None, False, True))]:
+                        ((4, 7, 7, 2048), ("avg", None, None, None, False, True)),
+                        # enough outputs for the four-channels-per-thread average kernel (a whole batch of 256 at the
+                        # end of ResNet-50 has them too), padded and unpadded windows, both area rules
+                        ((2, 40, 40, 128), ("avg", (3, 3), (1, 1), (1, 1, 1, 1), False, False)),
+                        ((2, 40, 40, 128), ("avg", (3, 3), (1, 1), (1, 1, 1, 1), True, False)),
+                        ((160, 7, 7, 2048), ("avg", None, None, None, False, True))]:
         c = dict(src=r.integers(0, 256, shape, dtype=np.uint8), geom=geom, in_q=(0.05, 0), out_q=(0.05, 0))
         np.testing.assert_array_equal(gpu_pool(ctx, c), pool_with(port, c))
 
