@@ -22,12 +22,13 @@ SOURCES = ["context.cu", "bandwidth_kernels.cu", "gemmlowp_simt.cu", "gemmlowp_t
            "gemmlowp_dispatch.cu"]
 HEADERS = ["common.cuh", "kernels.cuh"]
 
-NVCC_FLAGS = [
+OBJ_DIR = os.path.join(LIB_DIR, "obj")
+NVCC_COMPILE_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
     "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC,-fvisibility=hidden,-Wall",
-    "-shared", "-cudart", "static",
 ]
+NVCC_LINK_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-cudart", "static"]
 
 
 def _nvcc() -> str:
@@ -37,31 +38,47 @@ def _nvcc() -> str:
     raise RuntimeError("nvcc not found: the cugl library cannot be built")
 
 
-def _stale() -> bool:
-    if not os.path.exists(LIB_PATH):
-        return True
-    t = os.path.getmtime(LIB_PATH)
-    deps = [os.path.join(CSRC, f) for f in SOURCES + HEADERS] + [os.path.join(ROOT, "include", "cugl.h")]
-    return any(os.path.getmtime(d) > t for d in deps)
+def _includes() -> list[str]:
+    return ["-I", os.path.join(ROOT, "include"), "-I", CSRC]
 
 
-def build(force: bool = False, verbose: bool = False) -> str:
-    """Compile every CUDA source into one shared library; returns its path."""
-    if not force and not _stale():
-        return LIB_PATH
-    os.makedirs(LIB_DIR, exist_ok=True)
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", os.path.join(ROOT, "include"), "-I", CSRC]
+def _compile_one(src: str, verbose: bool) -> str:
+    """One translation unit -> lib/obj/<name>.o, skipped when the object is newer than the source and headers."""
+    obj = os.path.join(OBJ_DIR, os.path.splitext(src)[0] + ".o")
+    deps = [os.path.join(CSRC, src)] + [os.path.join(CSRC, h) for h in HEADERS] + [os.path.join(ROOT, "include", "cugl.h")]
+    if src.startswith("gemmlowp_tcgen05_epi"):
+        deps.append(os.path.join(CSRC, "gemmlowp_tcgen05.cu"))  # these units re-include it with another warp count
+    if os.path.exists(obj) and all(os.path.getmtime(d) <= os.path.getmtime(obj) for d in deps):
+        return obj
+    cmd = [_nvcc(), *NVCC_COMPILE_FLAGS, *_includes(), "-ccbin", shutil.which("g++") or "g++"]
     if verbose:
         cmd += ["-Xptxas", "-v"]
-    cmd += [os.path.join(CSRC, s) for s in SOURCES] + ["-o", LIB_PATH]
-    env = dict(os.environ)
-    # the image exports CC/CXX pointing at a toolchain without libgomp; nvcc must use the system g++
-    cmd += ["-ccbin", shutil.which("g++") or "g++"]
-    res = subprocess.run(cmd, capture_output=True, text=True, env=env)
+    cmd += ["-c", os.path.join(CSRC, src), "-o", obj]
+    res = subprocess.run(cmd, capture_output=True, text=True)
     if verbose or res.returncode != 0:
         sys.stderr.write(res.stdout + res.stderr)
     if res.returncode != 0:
-        raise RuntimeError("nvcc failed building libcugl.so")
+        raise RuntimeError(f"nvcc failed on {src}")
+    return obj
+
+
+def build(force: bool = False, verbose: bool = False) -> str:
+    """Compile every CUDA source (in parallel, one object each) and link one shared library; returns its path."""
+    from concurrent.futures import ThreadPoolExecutor
+    os.makedirs(OBJ_DIR, exist_ok=True)
+    if force:
+        for f in os.listdir(OBJ_DIR):
+            os.remove(os.path.join(OBJ_DIR, f))
+    with ThreadPoolExecutor(max_workers=min(len(SOURCES), os.cpu_count() or 1)) as pool:
+        objs = list(pool.map(lambda s: _compile_one(s, verbose), SOURCES))
+    if not force and os.path.exists(LIB_PATH) and all(os.path.getmtime(o) <= os.path.getmtime(LIB_PATH) for o in objs):
+        return LIB_PATH
+    # the image exports CC/CXX pointing at a toolchain without libgomp; nvcc must use the system g++
+    cmd = [_nvcc(), *NVCC_LINK_FLAGS, "-ccbin", shutil.which("g++") or "g++", *objs, "-o", LIB_PATH]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed linking libcugl.so")
     return LIB_PATH
 
 

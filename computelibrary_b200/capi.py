@@ -112,6 +112,7 @@ _SIGNATURES = {
     "cugl_gemmlowp_plan_allow_pair_kernel": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
     "cugl_gemmlowp_run_noalloc": (C.c_int, [_vp, C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp]),
+    "cugl_gemmlowp_noalloc_status": (C.c_int, [_vp]),
     "cugl_reduce_rows": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_reduce_cols": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_offset_contribution": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _i32, _i32]),
@@ -382,6 +383,11 @@ def gemmlowp_run_noalloc(stream: int, desc: GemmDesc, a, b, bias, multipliers, s
     """cugl_gemmlowp_run_noalloc: one fused GEMMLowp on `stream` using the library's fixed workspace."""
     _check(load_library().cugl_gemmlowp_run_noalloc(_vp(stream) if stream else None, C.byref(desc), _dptr(a), _dptr(b),
                                                    _dptr(bias), _dptr(multipliers), _dptr(shifts), _dptr(dst)))
+
+
+def gemmlowp_noalloc_status(stream: int):
+    """cugl_gemmlowp_noalloc_status: waits for `stream`; raises CuglError if an allocation-free call timed out."""
+    _check(load_library().cugl_gemmlowp_noalloc_status(_vp(stream) if stream else None))
 
 
 def gemm_validate(desc: GemmDesc):

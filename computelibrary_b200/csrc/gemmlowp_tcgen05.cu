@@ -84,11 +84,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     uint32_t ok;
     asm volatile("{\n\t"
                  ".reg .pred p;\n\t"
-#ifdef CUGL_TEST_WAIT
-                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#else
                  "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-#endif
                  "selp.u32 %0, 1, 0, p;\n\t"
                  "}"
                  : "=r"(ok)
@@ -218,21 +214,6 @@ __device__ __forceinline__ void trace_event(long long *trace, int i, int e)
         trace[(static_cast<long long>(blockIdx.x) * kTraceTiles + i) * kTraceEvents + e] = static_cast<long long>(t);
     }
 }
-
-#ifdef CUGL_KTRACE
-// Development aid: clock64 of per-k-block events of the second tile of each CTA.
-// Layout after the per-tile area: [cta][4 series][64 k-blocks].
-__device__ __forceinline__ void ktrace(long long *trace, int ti, int series, int kb)
-{
-    if (trace != nullptr && ti == 1 && kb < 64)
-    {
-        trace[static_cast<long long>(gridDim.x) * kTraceTiles * kTraceEvents +
-              (static_cast<long long>(blockIdx.x) * 4 + series) * 64 + kb] = clock64();
-    }
-}
-#else
-__device__ __forceinline__ void ktrace(long long *, int, int, int) {}
-#endif
 
 __device__ __forceinline__ void trace_value(long long *trace, int i, int e, long long v)
 {
@@ -447,10 +428,6 @@ __device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, in
     {
         return;
     }
-#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 11 // row-major: no stores
-    if ((v[0] ^ v[1] ^ v[2] ^ v[3] ^ v[4] ^ v[5] ^ v[6] ^ v[7]) == 0x12345677u) drow[nc] = 1;
-    return;
-#endif
     const bool full = nc + 32 <= tp.N;
     if (kS32Out)
     {
@@ -512,23 +489,11 @@ __device__ __forceinline__ void process_chunk(uint32_t (&v)[32], const int4 *col
     }
     else
     {
-#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 12 // row-major: no arithmetic, no column terms
-#pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = v[4 * j] ^ v[4 * j + 1] ^ v[4 * j + 2] ^ v[4 * j + 3];
-#elif defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 14 // row-major: arithmetic with ONE column term per chunk
-        int4 qq[4] = {col[0], col[0], col[0], col[0]};
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-        {
-            v[j >> 2] = requant_pack4<kMode>(v + j, qq, row_term, ep.result_offset, ep.lo, ep.hi);
-        }
-#else
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
         {
             v[j >> 2] = requant_pack4<kMode>(v + j, col + j, row_term, ep.result_offset, ep.lo, ep.hi);
         }
-#endif
     }
 }
 
@@ -892,11 +857,7 @@ __device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], c
 #pragma unroll
         for (int b = 0; b < 4; ++b)
         {
-#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 23 // staged: no requantisation
-            r[b] = static_cast<int32_t>(v[4 * j + b]);
-#else
             r[b] = requant_one<kMode>(v[4 * j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
-#endif
         }
         const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
         const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
@@ -923,10 +884,6 @@ __device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], c
     {
         return;
     }
-#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 21 // staged: no global stores
-    if ((t[0][0] ^ t[1][0] ^ t[2][0] ^ t[3][0] ^ t[0][1] ^ t[1][1] ^ t[2][1] ^ t[3][1]) == 0x12345677u) tp.dst[p0] = 1;
-    return;
-#endif
 #pragma unroll
     for (int k = 0; k < 4; ++k)
     {
@@ -1000,30 +957,12 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
     else
     {
         uint8_t *o = tp.dst + base + ch;
-#if defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 1 // no stores (result consumed by an impossible branch)
-        int acc = 0;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc += requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
-        if (acc == 0x7fffffff) o[0] = 1;
-#elif defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 2 // no arithmetic
-#pragma unroll
-        for (int j = 0; j < 32; ++j)
-        {
-            if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(v[j]);
-        }
-#elif defined(CUGL_EPI_EXPERIMENT) && CUGL_EPI_EXPERIMENT == 3 // one store per chunk
-        int acc = 0;
-#pragma unroll
-        for (int j = 0; j < 32; ++j) acc += static_cast<int>(v[j]);
-        o[0] = static_cast<uint8_t>(acc);
-#else
 #pragma unroll
         for (int j = 0; j < 32; ++j)
         {
             const int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
             if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(y);
         }
-#endif
     }
 }
 
@@ -1268,7 +1207,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     break;
                 }
-                ktrace(tp.trace, ti, 2, kb);
                 const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
                 const int m0   = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
                 const int n0   = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
@@ -1281,7 +1219,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tma_load_2d(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, full_bar(st));
                     tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
                 }
-                ktrace(tp.trace, ti, 3, kb);
                 issued |= 1u << st;
                 parities = (parities & ~(1u << st)) | (ph << st);
                 // advance g by kProdLanes
@@ -1367,7 +1304,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     have = mbar_try_wait(full_bar(sn), phn);
                     tc_fence_after();
-                    ktrace(tp.trace, ti, 0, kb);
                     if (kb == 0) trace_event(tp.trace, ti, 2);
                     // stage offset in 16-byte units; advancing K by 32 bytes inside the swizzle row: +2
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
@@ -1384,7 +1320,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                         }
                     }
                     umma_commit(empty_bar(s)); // frees the smem stage once these MMAs have read it
-                    ktrace(tp.trace, ti, 1, kb);
                     s  = sn;
                     ph = phn;
                 }
@@ -1645,7 +1580,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     break;
                 }
-                ktrace(tp.trace, ti, 2, kb);
                 const int item = first_tile + ti * tile_stride;
                 const int tile = item_tile(item), half = item_half(item);
                 const int m0   = (tile % num_m_blocks) * 2 * BLOCK_M + static_cast<int>(rank) * BLOCK_M;
@@ -1667,7 +1601,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, half < 0 ? &tmap_b : &tmap_bh, k0, n0,
                                      leader_full);
                 }
-                ktrace(tp.trace, ti, 3, kb);
                 kb += kProdLanes;
                 while (kb >= num_kb)
                 {
@@ -1730,7 +1663,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                     have = mbar_try_wait(full_bar(sn), phn);
                     tc_fence_after();
-                    ktrace(tp.trace, ti, 0, kb);
                     if (kb == 0) trace_event(tp.trace, ti, 2);
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
@@ -1746,7 +1678,6 @@ __global__ void __launch_bounds__(kThreads, 1)
                         }
                     }
                     umma_commit_pair(empty_bar(s)); // frees this stage in both CTAs
-                    ktrace(tp.trace, ti, 1, kb);
                     s  = sn;
                     ph = phn;
                 }

@@ -104,6 +104,8 @@ bool        gemmlowp_tcgen05_uses_pair(const cugl_context *ctx, const GemmOperan
 // allow_pair = false keeps to the one-CTA kernels (testing aid; all variants must agree bit for bit).
 cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                     bool allow_pair = true);
+// The rules of cugl_gemmlowp_validate; returns nullptr (and *code = CUGL_SUCCESS) or the reason.
+const char *validate_gemm_desc(const cugl_gemm_desc *d, cugl_status *code, bool need_host_vectors);
 // QASYMM8 addition: true when the oracle's result equals min(max(min(a + b, 255), floor), cap) for every byte pair
 // (proved by enumeration on the host, remembered per parameter set).
 bool classify_add(float a_scale, int a_zp, float b_scale, int b_zp, float o_scale, int o_zp, int act, float act_a,

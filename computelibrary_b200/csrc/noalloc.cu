@@ -49,10 +49,12 @@ extern "C" cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_d
                                                  void *d_dst)
 {
     using namespace cugl;
-    const char *why = nullptr;
-    if (cugl_gemmlowp_validate(desc, &why) != CUGL_SUCCESS)
+    // the per-channel vectors are device memory here: the h_ pointers of desc are neither needed nor read
+    cugl_status code = CUGL_SUCCESS;
+    const char *why  = validate_gemm_desc(desc, &code, false);
+    if (why != nullptr)
     {
-        return fail(nullptr, CUGL_INVALID_ARGUMENT, std::string("cugl_gemmlowp_run_noalloc: ") + why);
+        return fail(nullptr, code, std::string("cugl_gemmlowp_run_noalloc: ") + why);
     }
     if (d_a == nullptr || d_b == nullptr || d_dst == nullptr)
     {
@@ -96,8 +98,9 @@ extern "C" cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_d
             CUGL_CUDA_TRY(nullptr, cudaGetSymbolAddress(&p, g_scratch));
             CUGL_CUDA_TRY(nullptr, cudaDeviceGetAttribute(&su.sm_count, cudaDevAttrMultiProcessorCount, device));
             su.scratch = static_cast<unsigned char *>(p);
-            // the status word the kernels may write must start at zero
-            CUGL_CUDA_TRY(nullptr, cudaMemsetAsync(su.scratch + kOffStatus, 0, 256, static_cast<cudaStream_t>(stream)));
+            // the status word the kernels may write must start at zero; blocking, so that it is clear for every
+            // stream and not only for the one this first call happens to use
+            CUGL_CUDA_TRY(nullptr, cudaMemset(su.scratch + kOffStatus, 0, 256));
             su.ready = true;
         }
     }
@@ -167,4 +170,38 @@ extern "C" cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_d
                        desc->stage == CUGL_STAGE_QUANTIZE_DOWN;
     return gemmlowp_tcgen05_supported(op) ? launch_gemmlowp_tcgen05(&ctx, op, ep, true)
                                           : launch_gemmlowp_simt(&ctx, op, ep);
+}
+
+// The tensor-core kernels bound every wait; when one runs out they record which role gave up in a status word
+// inside the fixed array and return.  The planned entry points report that word through cugl_sync; this path
+// has no context, so the word is read here: waits for `stream`, copies the word to the host, clears it for
+// the next call and answers CUGL_RUNTIME_ERROR when it was set (dst of the affected call is then invalid).
+// Allocates nothing.
+extern "C" cugl_status cugl_gemmlowp_noalloc_status(void *stream)
+{
+    using namespace cugl;
+    int device = 0;
+    CUGL_CUDA_TRY(nullptr, cudaGetDevice(&device));
+    unsigned char *scratch = nullptr;
+    {
+        std::lock_guard<std::mutex> lock(g_setup_mutex);
+        if (device < 0 || device >= 64 || !g_setup[device].ready)
+        {
+            return CUGL_SUCCESS; // nothing has run on this device yet
+        }
+        scratch = g_setup[device].scratch;
+    }
+    cudaStream_t st   = static_cast<cudaStream_t>(stream);
+    int32_t      word = 0;
+    CUGL_CUDA_TRY(nullptr, cudaMemcpyAsync(&word, scratch + kOffStatus, sizeof(word), cudaMemcpyDeviceToHost, st));
+    CUGL_CUDA_TRY(nullptr, cudaStreamSynchronize(st));
+    if (word == 0)
+    {
+        return CUGL_SUCCESS;
+    }
+    CUGL_CUDA_TRY(nullptr, cudaMemsetAsync(scratch + kOffStatus, 0, sizeof(word), st));
+    CUGL_CUDA_TRY(nullptr, cudaStreamSynchronize(st));
+    return fail(nullptr, CUGL_RUNTIME_ERROR,
+                "cugl_gemmlowp_run_noalloc: a bounded device wait ran out (role code " + std::to_string(word) +
+                    ": 1 producer, 2 MMA issuer, 3 epilogue, 4 drain); the output of that call is invalid");
 }

@@ -51,11 +51,7 @@ struct GemmCore
 
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
-#ifdef CUGL_LDBT_PAD
-        ldbt = round_up(K, 128) + CUGL_LDBT_PAD;
-#else
         ldbt = round_up(K, 128);
-#endif
         CUGL_TRY(cugl_malloc(ctx, static_cast<size_t>(ldbt) * N * n_b_copies, reinterpret_cast<void **>(&d_bt)));
         CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * N * n_b_copies, reinterpret_cast<void **>(&d_colsum)));
         CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * rowsum_len, reinterpret_cast<void **>(&d_rowsum)));
@@ -191,7 +187,11 @@ struct GemmCore
     }
 };
 
-const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
+} // namespace
+
+// need_host_vectors = false: the per-channel multipliers and shifts live in device memory only (the
+// allocation-free entry point), so their host copies are neither required nor read.
+const char *cugl::validate_gemm_desc(const cugl_gemm_desc *d, cugl_status *code, bool need_host_vectors)
 {
     *code = CUGL_INVALID_ARGUMENT;
     if (d == nullptr) return "descriptor is NULL";
@@ -208,7 +208,7 @@ const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
     {
         if (d->is_quantized_per_channel)
         {
-            for (int i = 0; d->h_gemmlowp_shifts != nullptr && i < d->N; ++i)
+            for (int i = 0; need_host_vectors && d->h_gemmlowp_shifts != nullptr && i < d->N; ++i)
             {
                 if (d->h_gemmlowp_shifts[i] < 0 || d->h_gemmlowp_shifts[i] > 31) return "QUANTIZE_DOWN needs shifts in [0, 31]";
             }
@@ -229,7 +229,7 @@ const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
         if (d->gemmlowp_min_bound > d->gemmlowp_max_bound) return "gemmlowp_min_bound > gemmlowp_max_bound";
         if (d->is_quantized_per_channel)
         {
-            if (d->h_gemmlowp_multipliers == nullptr || d->h_gemmlowp_shifts == nullptr)
+            if (need_host_vectors && (d->h_gemmlowp_multipliers == nullptr || d->h_gemmlowp_shifts == nullptr))
                 return "per-channel output stage needs N multipliers and shifts";
             if (d->dst_dtype != CUGL_U8 && d->N > 1 && d->b_offset != 0)
                 return "per-channel requantisation with a non-zero B offset is only defined for QASYMM8 output";
@@ -249,6 +249,13 @@ const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
     }
     *code = CUGL_SUCCESS;
     return nullptr;
+}
+
+namespace
+{
+const char *validate_gemm(const cugl_gemm_desc *d, cugl_status *code)
+{
+    return cugl::validate_gemm_desc(d, code, true);
 }
 } // namespace
 
@@ -477,10 +484,11 @@ extern "C"
             d.batch > 1 ? static_cast<size_t>(d.a_batch_stride) * d.batch : static_cast<size_t>(d.lda) * d.M;
         const size_t d_bytes =
             d.batch > 1 ? static_cast<size_t>(d.d_batch_stride) * d.batch : static_cast<size_t>(d.ldd) * d.M;
-        if (plan->d_a_stage == nullptr)
+        // each buffer on its own: a failed allocation must not leave the plan believing that all three exist
+        if (plan->d_a_stage == nullptr) CUGL_TRY(cugl_malloc(ctx, a_bytes, &plan->d_a_stage));
+        if (plan->d_dst_stage == nullptr) CUGL_TRY(cugl_malloc(ctx, d_bytes, &plan->d_dst_stage));
+        if (plan->d_bias_stage == nullptr)
         {
-            CUGL_TRY(cugl_malloc(ctx, a_bytes, &plan->d_a_stage));
-            CUGL_TRY(cugl_malloc(ctx, d_bytes, &plan->d_dst_stage));
             CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * d.N, reinterpret_cast<void **>(&plan->d_bias_stage)));
         }
         if (d.has_bias && h_bias == nullptr)
@@ -1181,10 +1189,10 @@ extern "C"
         cugl_context         *ctx = plan->ctx;
         const size_t src_bytes    = static_cast<size_t>(d.B) * d.H * d.W * d.C;
         const size_t dst_bytes    = static_cast<size_t>(plan->M) * d.OFM;
-        if (plan->d_src_stage == nullptr)
+        if (plan->d_src_stage == nullptr) CUGL_TRY(cugl_malloc(ctx, src_bytes, &plan->d_src_stage));
+        if (plan->d_dst_stage == nullptr) CUGL_TRY(cugl_malloc(ctx, dst_bytes, &plan->d_dst_stage));
+        if (plan->d_bias_stage == nullptr)
         {
-            CUGL_TRY(cugl_malloc(ctx, src_bytes, &plan->d_src_stage));
-            CUGL_TRY(cugl_malloc(ctx, dst_bytes, &plan->d_dst_stage));
             CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * d.OFM, reinterpret_cast<void **>(&plan->d_bias_stage)));
         }
         CUGL_TRY(cugl_memcpy_h2d(ctx, plan->d_src_stage, h_src, src_bytes));

@@ -18,7 +18,7 @@ def type_range(dtype):
     return int(info.min), int(info.max)
 
 
-# ---- the five benchmark configurations (seeded stand-ins; shapes / distributions of BASELINE.json) ----
+# ---- the five benchmark configurations (seeded stand-ins; shapes / distributions of the benchmark specification) ----
 def config1(seed=1):
     """examples/neon_gemm_qasymm8-style: u8 [64,256] x u8 [256,128], bias, fixed-point stage to u8."""
     rng = np.random.default_rng(seed)

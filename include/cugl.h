@@ -252,10 +252,16 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_paired_drain(cugl_gemm_plan *plan, i
  *     first call outside any stream capture.
  *   - All calls share the one array, which keeps the previous call's contents (the column sums are cleared
  *     by the call itself): calls that overlap on the GPU -- different streams, or graph branches -- race.
- *   - It calls no cudaMalloc / cudaFree and no allocating library routine; B is re-laid out on every call. */
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine; B is re-laid out on every call.
+ *   - The call is asynchronous.  A device-side time-out (every wait of the kernels is bounded) cannot be reported
+ *     by the call itself: ask cugl_gemmlowp_noalloc_status afterwards. */
 CUGL_API cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_desc *desc, const void *d_a,
                                                const void *d_b, const int32_t *d_bias,
                                                const int32_t *d_multipliers, const int32_t *d_shifts, void *d_dst);
+/* Companion of cugl_gemmlowp_run_noalloc (no counterpart in the reference either): waits for `stream`, then
+ * returns CUGL_RUNTIME_ERROR if a kernel of an earlier allocation-free call on the current device gave up a bounded
+ * wait (and clears that record), else CUGL_SUCCESS.  Allocates nothing; the role of cugl_sync for this path. */
+CUGL_API cugl_status cugl_gemmlowp_noalloc_status(void *stream);
 
 /* ------------------------------------------------------------------------------------------------
  * Stand-alone kernels of the path.

@@ -24,10 +24,19 @@ _i32 = C.c_int32
 _p = C.c_void_p
 
 
-def build(want_ref: bool = True, acl_root: str = "/root/reference") -> None:
+def find_acl_root() -> str | None:
+    """An unmodified Compute Library tree: $ACL_ROOT, else a directory named "reference" beside this repository."""
+    for cand in (os.environ.get("ACL_ROOT"), os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")):
+        if cand and os.path.isdir(os.path.join(cand, "tests", "validation", "reference")):
+            return cand
+    return None
+
+
+def build(want_ref: bool = True, acl_root: str | None = None) -> None:
     """Compile the C restatement and, when a Compute Library tree is present, the in-place reference."""
     subprocess.run(["make", "-C", _HERE, "port"], check=True, capture_output=True)
-    if want_ref and os.path.isdir(os.path.join(acl_root, "tests", "validation", "reference")):
+    acl_root = acl_root or find_acl_root()
+    if want_ref and acl_root is not None:
         subprocess.run(["make", "-C", _HERE, "ref", f"ACL_ROOT={acl_root}"], check=True, capture_output=True)
 
 

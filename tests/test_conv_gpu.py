@@ -98,7 +98,7 @@ def test_conv_asymmetric_weights_and_signed(ctx, port):
 
 
 def test_config3_full_size(ctx, port):
-    """BASELINE config 3 at full size: batch 32, 56x56x64 -> 64, 3x3 s1 p1, fused ReLU; exact on a batch sample
+    """Configuration 3 of the benchmark at full size: batch 32, 56x56x64 -> 64, 3x3 s1 p1, fused ReLU; exact on a batch sample
     and identical per image whatever the batch it is computed in (batch sharding needs no exchange)."""
     c = config3()
     mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])

@@ -34,7 +34,7 @@ def test_golden_cases(ctx, gemm_golden, force_simt):
 
 
 def test_config1_fused_and_two_stage(ctx, port, gemm_golden):
-    """BASELINE config 1 against the reference-produced fixture, fused and as core(S32) + output stage."""
+    """Configuration 1 of the benchmark against the reference-produced fixture, fused and as core(S32) + output stage."""
     import torch
     c1 = config1()
     qm, sh = capi.calculate_quantized_multiplier(c1["real_multiplier"])
@@ -202,7 +202,7 @@ def test_run_host_end_to_end(ctx, port, shape, b_dtype, b_off):
 
 
 def test_config2_full_size_properties(ctx, port):
-    """4096^3 (BASELINE config 2): exact on a row sample against the oracle, tensor-core and generic kernels
+    """4096^3 (configuration 2 of the benchmark): exact on a row sample against the oracle, tensor-core and generic kernels
     agree everywhere, and the result is invariant under a row permutation of A (rows are independent)."""
     c = config2()
     mult, shift = f32_mults(port, c["i_scale"], c["w_scales"], c["o_scale"])
