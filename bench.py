@@ -43,7 +43,9 @@ def parse_args():
     p.add_argument("--steps", type=int, default=2000)
     p.add_argument("--warmup", type=int, default=200)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5"])
+    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "bw"])
+    p.add_argument("--only", default="", help="bw: run only the kernels whose name contains this text")
+    p.add_argument("--small", action="store_true", help="bw: the reduced sizes used for ncu captures (a few hundred MB)")
     p.add_argument("--batch", type=int, default=256, help="global batch of c4 (split over the ranks)")
     p.add_argument("--weak", action="store_true",
                    help="c4: every rank runs a whole --batch (weak scaling) instead of its share of one global batch")
@@ -710,11 +712,90 @@ def run_linear_sharded(args):
     dist.destroy_process_group()
 
 
+def run_bandwidth(args):
+    """The HBM-bound kernels of the path, each on one shape, timed alone with the L2 flushed before every launch.
+    One JSON line: per kernel the algorithmic bytes, the time and the achieved GB/s against the measured copy peak."""
+    import torch
+    import computelibrary_b200 as cl
+    from computelibrary_b200 import capi
+    torch.cuda.set_device(0)
+    ctx = cl.Context(0, torch.cuda.current_stream().cuda_stream)
+    flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    peaks = load_peaks()
+    g = torch.Generator(device="cuda").manual_seed(1)
+    sc = 4 if args.small else 1  # divisor of the leading dimension
+
+    def rnd8(*shape):
+        return torch.randint(0, 256, shape, dtype=torch.uint8, device="cuda", generator=g)
+
+    cases = []
+
+    def case(name, nbytes, fn, note):
+        if args.only and args.only not in name:
+            return
+        ms = _timed_steps(fn, args.steps, args.warmup, flush, torch.cuda.synchronize)
+        ctx.sync()
+        t = statistics.mean(ms)
+        cases.append({"kernel": name, "case": note, "bytes": int(nbytes), "us": t * 1e3,
+                      "gbs": nbytes / (t * 1e-3) / 1e9, "frac_of_measured_copy": nbytes / (t * 1e-3) / 1e9 / peaks["hbm_gbs"]})
+
+    M, K = 32768 // sc, 8192
+    a, out = rnd8(M, K), torch.empty(M, dtype=torch.int32, device="cuda")
+    case("reduce_rows_kernel", M * K + 4 * M, lambda: ctx.reduce_rows(a, capi.S8, M, K, K, out), f"A s8 [{M}][{K}]")
+    K, N = 16384 // sc, 14336
+    b, out = rnd8(K, N), torch.empty(N, dtype=torch.int32, device="cuda")
+    case("reduce_cols_kernel", K * N + 4 * N, lambda: ctx.reduce_cols(b, capi.S8, K, N, N, out), f"B s8 [{K}][{N}]")
+    del a, b
+    K, N = 4096, 14336 // sc
+    desc, keep = capi.make_gemm_desc(128, N, K, capi.S8, capi.S8, capi.S8, 5, 0, multiplier=2 ** 30, shift=8,
+                                     min_bound=-128, max_bound=127)
+    plan, b = capi.GemmPlan(ctx, desc, keep), rnd8(K, N)
+    case("transpose_colsum_kernel", 2 * K * N + 4 * N, lambda: plan.prepare(b), f"B s8 [{K}][{N}] -> Bt + column sums")
+    plan.close()
+    del b
+    M, N = 8192 // sc, 8192
+    acc = torch.randint(-2 ** 20, 2 ** 20, (M, N), dtype=torch.int32, device="cuda", generator=g)
+    bias = torch.randint(-5000, 5000, (N,), dtype=torch.int32, device="cuda", generator=g)
+    o8 = torch.empty((M, N), dtype=torch.uint8, device="cuda")
+    case("output_stage_kernel", 5 * M * N + 4 * N,
+         lambda: ctx.output_stage(acc, 4 * N, bias, o8, N, capi.U8, M, N, None, None, 1099511552, 8, 1, 10, 0, 255),
+         f"S32 [{M}][{N}] + bias -> u8, per-tensor")
+    cs, rs = bias, torch.randint(-5000, 5000, (M,), dtype=torch.int32, device="cuda", generator=g)
+    case("offset_contribution_kernel", 8 * M * N + 4 * (M + N),
+         lambda: ctx.offset_contribution(acc, M, N, 4096, 4 * N, cs, rs, 3, -7), f"S32 [{M}][{N}] in place, both offsets")
+    del acc, o8
+    for B in ([32] if args.small else [32, 256]):
+        H = W = 56
+        Cc, Kp = 64, 576
+        src, dst = rnd8(B, H, W, Cc), torch.empty((B * H * W, Kp), dtype=torch.uint8, device="cuda")
+        case("im2col_nhwc_kernel", B * H * W * (Cc + Kp),
+             lambda: ctx.im2col_nhwc(src, dst, Cc, W, H, B, 3, 3, 1, 1, 1, 1, 1, 1, W, H, 128, Kp),
+             f"batch {B}, 56x56x64, 3x3 s1 p1")
+        del src, dst
+    B = 256 // sc
+    pd = capi.make_pool_desc(B, 112, 112, 64, capi.POOL_MAX, (3, 3), (2, 2), (0, 1, 0, 1), (0.05, 0), (0.05, 0))
+    wo, ho = capi.pool_out_dims(pd)
+    src, dst = rnd8(B, 112, 112, 64), torch.empty((B, ho, wo, 64), dtype=torch.uint8, device="cuda")
+    case("maxpool_kernel", B * 64 * (112 * 112 + ho * wo), lambda: ctx.pool2d_nhwc(pd, src, dst),
+         f"batch {B}, 112x112x64, 3x3 s2")
+    del src, dst
+    n = (256 // sc) * 56 * 56 * 256
+    x, y, z = rnd8(n), rnd8(n), torch.empty(n, dtype=torch.uint8, device="cuda")
+    case("add_saturating_kernel", 3 * n, lambda: ctx.add_qasymm8(x, y, z, n, (0.05, 0), (0.05, 0), (0.05, 0), capi.ACT_RELU),
+         f"{n} elements, equal quantizations + ReLU")
+    print(json.dumps({"metric": "hbm_kernel_gbs", "unit": "GB/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
+                      "peak_measured_copy_gbs": peaks["hbm_gbs"], "peak_source": peaks["source"],
+                      "l2": "flushed before every timed launch (256 MB write)", "kernels": cases}), flush=True)
+    ctx.close()
+
+
 def main():
     args = parse_args()
     _, world, _ = dist_env()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "bw":
+        run_bandwidth(args)
     elif args.workload == "c3":
         run_conv(args)
     elif args.workload == "c4":

@@ -113,6 +113,10 @@ _SIGNATURES = {
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
     "cugl_gemmlowp_run_noalloc": (C.c_int, [_vp, C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_noalloc_status": (C.c_int, [_vp]),
+    "cugl_gemmlowp_plan_temp_bytes": (C.c_size_t, [_vp]),
+    "cugl_gemmlowp_plan_bind_temp": (C.c_int, [_vp, _vp, C.c_size_t]),
+    "cugl_conv2d_plan_temp_bytes": (C.c_size_t, [_vp]),
+    "cugl_conv2d_plan_bind_temp": (C.c_int, [_vp, _vp, C.c_size_t]),
     "cugl_reduce_rows": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_reduce_cols": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
     "cugl_offset_contribution": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _vp, _vp, _i32, _i32]),

@@ -45,7 +45,21 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_kernel(const uint8_t *__
         }
         const int    nvec = (K - head) >> 4;
         const uint4 *v    = reinterpret_cast<const uint4 *>(row + head);
-        for (int i = lane; i < nvec; i += 32)
+        int i = lane;
+        for (; i + 96 < nvec; i += 128) // four independent 16-byte loads in flight per lane
+        {
+            const uint4 q0 = __ldg(v + i), q1 = __ldg(v + i + 32), q2 = __ldg(v + i + 64), q3 = __ldg(v + i + 96);
+            int32_t     a0 = sum4(q0.x, is_signed, 0), a1 = sum4(q1.x, is_signed, 0);
+            int32_t     a2 = sum4(q2.x, is_signed, 0), a3 = sum4(q3.x, is_signed, 0);
+            a0 = sum4(q0.y, is_signed, a0), a1 = sum4(q1.y, is_signed, a1);
+            a2 = sum4(q2.y, is_signed, a2), a3 = sum4(q3.y, is_signed, a3);
+            a0 = sum4(q0.z, is_signed, a0), a1 = sum4(q1.z, is_signed, a1);
+            a2 = sum4(q2.z, is_signed, a2), a3 = sum4(q3.z, is_signed, a3);
+            a0 = sum4(q0.w, is_signed, a0), a1 = sum4(q1.w, is_signed, a1);
+            a2 = sum4(q2.w, is_signed, a2), a3 = sum4(q3.w, is_signed, a3);
+            acc += (a0 + a1) + (a2 + a3);
+        }
+        for (; i < nvec; i += 32)
         {
             const uint4 q = __ldg(v + i);
             acc           = sum4(q.x, is_signed, acc);
@@ -67,59 +81,70 @@ __global__ void __launch_bounds__(kThreads) reduce_rows_kernel(const uint8_t *__
 }
 
 // ---- colsum_B[n] += sum over a K-slab of B[k,n] --------------------------------------------------
-// Thread per group of 4 columns (one 32-bit load per row when aligned), grid.y splits K, integer
-// atomics combine the slabs (exact, order-independent).  out must be zero on entry; the scalar is
-// applied by scale_vector_kernel afterwards.
+// A thread owns 16 consecutive columns and reads them with one 128-bit load per row, so a warp reads 512
+// contiguous bytes of a row.  The bytes are summed as packed 16-bit pairs (signed bytes are biased by 128 first,
+// the bias leaves again at the end): two adds per four columns and row.  A slab is at most 256 rows, which a
+// 16-bit lane holds without overflow (256 * 255 < 2^16).  grid.y splits K; integer atomics combine the slabs
+// (exact, order-independent).  out must be zero on entry; the scalar is applied by scale_vector_kernel.
+// Needs B and ldb 16-byte aligned; reduce_cols_generic_kernel covers the rest and the ragged last columns.
 // CpuGemmLowpMatrixBReductionKernel::run_internal (CpuGemmLowpMatrixReductionKernel.cpp:273-446).
+constexpr int kColSlabRows = 256;
 __global__ void __launch_bounds__(kThreads) reduce_cols_kernel(const uint8_t *__restrict__ b, bool is_signed, int K,
-                                                               int N, int64_t ldb, int k_per_block,
+                                                               int n_vec, int64_t ldb, int k_per_block,
                                                                int32_t *__restrict__ out)
 {
-    const int n0 = (blockIdx.x * kThreads + threadIdx.x) * 4;
-    if (n0 >= N)
+    const int unit = blockIdx.x * kThreads + threadIdx.x; // 16 columns
+    if (unit >= n_vec)
     {
         return;
     }
-    const int  k0      = blockIdx.y * k_per_block;
-    const int  k1      = min(K, k0 + k_per_block);
-    const bool aligned = ((reinterpret_cast<uintptr_t>(b) | static_cast<uint64_t>(ldb)) & 3) == 0 && n0 + 4 <= N;
-    int32_t    s0 = 0, s1 = 0, s2 = 0, s3 = 0;
-    if (aligned)
+    const int      k0   = blockIdx.y * k_per_block;
+    const int      k1   = min(K, k0 + k_per_block);
+    const uint32_t flip = is_signed ? 0x80808080u : 0u;
+    uint32_t       even[4] = {0, 0, 0, 0}, odd[4] = {0, 0, 0, 0}; // columns 4w, 4w+2 | 4w+1, 4w+3 as 16-bit pairs
+    const uint8_t *p = b + static_cast<int64_t>(k0) * ldb + 16 * static_cast<int64_t>(unit);
+#pragma unroll 4
+    for (int k = k0; k < k1; ++k, p += ldb)
     {
-        for (int k = k0; k < k1; ++k)
+        const uint4    q    = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint32_t w[4] = {q.x ^ flip, q.y ^ flip, q.z ^ flip, q.w ^ flip};
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
         {
-            const uint32_t w = __ldg(reinterpret_cast<const uint32_t *>(b + static_cast<int64_t>(k) * ldb + n0));
-            if (is_signed)
-            {
-                s0 += static_cast<int8_t>(w & 0xff);
-                s1 += static_cast<int8_t>((w >> 8) & 0xff);
-                s2 += static_cast<int8_t>((w >> 16) & 0xff);
-                s3 += static_cast<int8_t>(w >> 24);
-            }
-            else
-            {
-                s0 += w & 0xff;
-                s1 += (w >> 8) & 0xff;
-                s2 += (w >> 16) & 0xff;
-                s3 += w >> 24;
-            }
+            even[j] += w[j] & 0x00ff00ffu;
+            odd[j] += (w[j] >> 8) & 0x00ff00ffu;
         }
     }
-    else
+    const int32_t bias = is_signed ? 128 * (k1 - k0) : 0;
+    int32_t      *o    = out + 16 * unit;
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
     {
-        for (int k = k0; k < k1; ++k)
-        {
-            const uint8_t *row = b + static_cast<int64_t>(k) * ldb;
-            s0 += load_q8(row, n0, is_signed);
-            s1 += (n0 + 1 < N) ? load_q8(row, n0 + 1, is_signed) : 0;
-            s2 += (n0 + 2 < N) ? load_q8(row, n0 + 2, is_signed) : 0;
-            s3 += (n0 + 3 < N) ? load_q8(row, n0 + 3, is_signed) : 0;
-        }
+        atomicAdd(o + 4 * j + 0, static_cast<int32_t>(even[j] & 0xffffu) - bias);
+        atomicAdd(o + 4 * j + 1, static_cast<int32_t>(odd[j] & 0xffffu) - bias);
+        atomicAdd(o + 4 * j + 2, static_cast<int32_t>(even[j] >> 16) - bias);
+        atomicAdd(o + 4 * j + 3, static_cast<int32_t>(odd[j] >> 16) - bias);
     }
-    atomicAdd(out + n0, s0);
-    if (n0 + 1 < N) atomicAdd(out + n0 + 1, s1);
-    if (n0 + 2 < N) atomicAdd(out + n0 + 2, s2);
-    if (n0 + 3 < N) atomicAdd(out + n0 + 3, s3);
+}
+
+// any alignment: one thread per column of [n_first, N)
+__global__ void __launch_bounds__(kThreads) reduce_cols_generic_kernel(const uint8_t *__restrict__ b, bool is_signed,
+                                                                       int K, int n_first, int N, int64_t ldb,
+                                                                       int k_per_block, int32_t *__restrict__ out)
+{
+    const int n = n_first + blockIdx.x * kThreads + threadIdx.x;
+    if (n >= N)
+    {
+        return;
+    }
+    const int k0 = blockIdx.y * k_per_block;
+    const int k1 = min(K, k0 + k_per_block);
+    int32_t   s  = 0;
+    for (int k = k0; k < k1; ++k)
+    {
+        s += load_q8(b + static_cast<int64_t>(k) * ldb, n, is_signed);
+    }
+    atomicAdd(out + n, s);
 }
 
 __global__ void scale_vector_kernel(int32_t *v, int n, int32_t scalar)
@@ -206,24 +231,45 @@ __global__ void __launch_bounds__(kThreads) offset_contribution_kernel(int32_t *
                                                                        int64_t ld_elems,
                                                                        const int32_t *__restrict__ colsum,
                                                                        const int32_t *__restrict__ rowsum,
-                                                                       int32_t a_off, int32_t b_off, int32_t k_term)
+                                                                       int32_t a_off, int32_t b_off, int32_t k_term,
+                                                                       bool vec_ok)
 {
-    const int64_t total = static_cast<int64_t>(M) * N;
-    for (int64_t i = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; i < total;
-         i += static_cast<int64_t>(gridDim.x) * kThreads)
+    // blockIdx.y strides over rows, x over groups of four columns: no division anywhere
+    const int groups = (N + 3) >> 2;
+    for (int m = blockIdx.y; m < M; m += gridDim.y)
     {
-        const int m = static_cast<int>(i / N), n = static_cast<int>(i % N);
-        int32_t   v = mm[m * ld_elems + n];
-        if (colsum != nullptr) v += a_off * colsum[n];
-        if (rowsum != nullptr) v += b_off * rowsum[m];
-        v += k_term;
-        mm[m * ld_elems + n] = v;
+        int32_t      *row   = mm + m * ld_elems;
+        const int32_t rterm = k_term + (rowsum != nullptr ? b_off * __ldg(rowsum + m) : 0);
+        for (int g = blockIdx.x * kThreads + threadIdx.x; g < groups; g += gridDim.x * kThreads)
+        {
+            const int n0 = g * 4;
+            if (vec_ok && n0 + 4 <= N)
+            {
+                int4 v = *reinterpret_cast<int4 *>(row + n0);
+                if (colsum != nullptr)
+                {
+                    const int4 c = __ldg(reinterpret_cast<const int4 *>(colsum + n0));
+                    v.x += a_off * c.x, v.y += a_off * c.y, v.z += a_off * c.z, v.w += a_off * c.w;
+                }
+                v.x += rterm, v.y += rterm, v.z += rterm, v.w += rterm;
+                *reinterpret_cast<int4 *>(row + n0) = v;
+            }
+            else
+            {
+                for (int n = n0; n < min(n0 + 4, N); ++n)
+                {
+                    row[n] += rterm + (colsum != nullptr ? a_off * colsum[n] : 0);
+                }
+            }
+        }
     }
 }
 
 // ---- stand-alone output stage ---------------------------------------------------------------------
 // CpuGemmLowpQuantizeDownInt32To{Uint8,Int8}ScaleByFixedPointKernel::run_internal
-// (…ToUint8ScaleByFixedPointKernel.cpp:78-186).  Thread per 4 outputs: one 128-bit load, one 32-bit store.
+// (…ToUint8ScaleByFixedPointKernel.cpp:78-186).  A thread owns four consecutive columns -- their bias, multipliers and
+// shifts stay in registers -- and walks down the rows (blockIdx.y strides over them): one 128-bit load and one 32-bit
+// (8-bit output) or 64-bit (16-bit output) store per row, a warp covering 512 contiguous input bytes; no division.
 template <bool kOut16>
 __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *__restrict__ in, int64_t ld_in_elems,
                                                                 const int32_t *__restrict__ bias,
@@ -233,20 +279,31 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
                                                                 int32_t shift, int32_t offset, int32_t lo, int32_t hi,
                                                                 bool vec_ok, bool integer_stage)
 {
-    const int     groups_per_row = (N + 3) >> 2;
-    const int64_t total          = static_cast<int64_t>(M) * groups_per_row;
-    for (int64_t g = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; g < total;
-         g += static_cast<int64_t>(gridDim.x) * kThreads)
+    const int n0 = (blockIdx.x * kThreads + threadIdx.x) * 4;
+    if (n0 >= N)
     {
-        const int      m    = static_cast<int>(g / groups_per_row);
-        const int      n0   = static_cast<int>(g % groups_per_row) * 4;
-        const int32_t *src  = in + m * ld_in_elems + n0;
-        uint8_t       *dst  = out + m * ld_out + n0 * (kOut16 ? 2 : 1);
-        const bool     full = n0 + 4 <= N;
+        return;
+    }
+    const bool full = n0 + 4 <= N;
+    int32_t    cb[4], cm[4], cl[4], cr[4]; // bias, multiplier, left and right shift of this thread's columns
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+    {
+        const int     n  = min(n0 + j, N - 1);
+        const int32_t sh = shifts != nullptr ? shifts[n] : shift;
+        cb[j]            = bias != nullptr ? bias[n] : 0;
+        cm[j]            = mults != nullptr ? mults[n] : mult;
+        cl[j]            = max(-sh, 0);
+        cr[j]            = integer_stage ? sh : max(sh, 0);
+    }
+    for (int m = blockIdx.y; m < M; m += gridDim.y)
+    {
+        const int32_t *src = in + m * ld_in_elems + n0;
+        uint8_t       *dst = out + m * ld_out + n0 * (kOut16 ? 2 : 1);
         int32_t        v[4];
         if (full && vec_ok)
         {
-            const int4 q = *reinterpret_cast<const int4 *>(src);
+            const int4 q = __ldcs(reinterpret_cast<const int4 *>(src)); // read once: streaming
             v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
         }
         else
@@ -258,13 +315,11 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
 #pragma unroll
         for (int j = 0; j < 4; ++j)
         {
-            const int n = min(n0 + j, N - 1);
-            int32_t   x = v[j];
-            if (bias != nullptr) x += bias[n];
-            const int32_t mu = mults != nullptr ? mults[n] : mult;
-            const int32_t sh = shifts != nullptr ? shifts[n] : shift;
-            const int32_t r  = integer_stage ? finalize_int(x + offset, mu, sh, lo, hi)
-                                             : finalize(x, mu, max(-sh, 0), max(sh, 0), offset, lo, hi);
+            const int32_t x = static_cast<int32_t>(static_cast<uint32_t>(v[j]) + static_cast<uint32_t>(cb[j]));
+            const int32_t r = integer_stage
+                                  ? finalize_int(static_cast<int32_t>(static_cast<uint32_t>(x) + static_cast<uint32_t>(offset)),
+                                                 cm[j], cr[j], lo, hi)
+                                  : finalize(x, cm[j], cl[j], cr[j], offset, lo, hi);
             if (kOut16)
             {
                 (j < 2 ? packed : packed_hi) |= (static_cast<uint32_t>(r) & 0xffffu) << (16 * (j & 1));
@@ -303,47 +358,64 @@ __global__ void __launch_bounds__(kThreads) output_stage_kernel(const int32_t *_
 
 // ---- NHWC im2col ------------------------------------------------------------------------------------
 // dst row m = (b, yo, xo) holds kh*kw taps of C bytes in (ky, kx, c) order; an out-of-image tap is
-// filled with the input zero point (directconv2d/impl.h:333-334).  VEC = bytes moved per thread.
+// filled with the input zero point (directconv2d/impl.h:333-334).  VEC = bytes moved per thread and step.
+// A block takes `rows_per_iter` consecutive output rows per step and spreads their VEC-byte units over its
+// threads (consecutive threads write consecutive units: whole 128-byte lines); every index split is a 32-bit
+// multiply-high division by a launch constant.
+struct Im2colDivs
+{
+    FastDiv units, c, kw, wo, ho;
+};
+
 template <int VEC>
 __global__ void __launch_bounds__(kThreads) im2col_nhwc_kernel(const uint8_t *__restrict__ src,
                                                                uint8_t *__restrict__ dst, int C, int W, int H,
-                                                               int64_t M, int kw, int kh, int sx, int sy, int pad_l,
+                                                               int M, int kw, int kh, int sx, int sy, int pad_l,
                                                                int pad_t, int dil_x, int dil_y, int Wo, int Ho,
-                                                               uint32_t pad_word, int64_t row_stride)
+                                                               uint32_t pad_word, int64_t row_stride,
+                                                               int rows_per_iter, const Im2colDivs dv)
 {
-    const int     K             = kh * kw * C;
-    const int     units_per_row = static_cast<int>(row_stride / VEC);
-    const int64_t total         = M * units_per_row;
-    for (int64_t u = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; u < total;
-         u += static_cast<int64_t>(gridDim.x) * kThreads)
+    const int K             = kh * kw * C;
+    const int units_per_row = static_cast<int>(row_stride / VEC);
+    const int per_iter      = rows_per_iter * units_per_row;
+    for (int64_t m0 = static_cast<int64_t>(blockIdx.x) * rows_per_iter; m0 < M;
+         m0 += static_cast<int64_t>(gridDim.x) * rows_per_iter)
     {
-        const int64_t m   = u / units_per_row;
-        const int     off = static_cast<int>(u % units_per_row) * VEC; // byte offset inside the row
-        uint8_t      *d   = dst + m * row_stride + off;
-        if (off >= K)
+        for (int i = threadIdx.x; i < per_iter; i += kThreads)
         {
-            // zero the K padding that makes the row a multiple of 16 bytes
-            if (VEC == 16) *reinterpret_cast<uint4 *>(d) = make_uint4(0, 0, 0, 0);
-            else *d = 0;
-            continue;
-        }
-        const int tap = off / C, c = off % C;
-        const int ky = tap / kw, kx = tap % kw;
-        const int xo = static_cast<int>(m % Wo);
-        const int yo = static_cast<int>((m / Wo) % Ho);
-        const int64_t b = m / (static_cast<int64_t>(Wo) * Ho);
-        const int yi = yo * sy - pad_t + ky * dil_y;
-        const int xi = xo * sx - pad_l + kx * dil_x;
-        const bool inside = yi >= 0 && yi < H && xi >= 0 && xi < W;
-        if (VEC == 16)
-        {
-            uint4 q = make_uint4(pad_word, pad_word, pad_word, pad_word);
-            if (inside) q = __ldg(reinterpret_cast<const uint4 *>(src + ((b * H + yi) * W + xi) * C + c));
-            *reinterpret_cast<uint4 *>(d) = q;
-        }
-        else
-        {
-            *d = inside ? src[((b * H + yi) * W + xi) * C + c] : static_cast<uint8_t>(pad_word);
+            const int r = fast_div(i, dv.units);
+            const int m = static_cast<int>(m0) + r;
+            if (m >= M)
+            {
+                break;
+            }
+            const int off = (i - r * units_per_row) * VEC; // byte offset inside the row
+            uint8_t  *d   = dst + static_cast<int64_t>(m) * row_stride + off;
+            if (off >= K)
+            {
+                // zero the K padding that makes the row a multiple of 16 bytes
+                if (VEC == 16) *reinterpret_cast<uint4 *>(d) = make_uint4(0, 0, 0, 0);
+                else *d = 0;
+                continue;
+            }
+            const int tap = fast_div(off, dv.c), c = off - tap * C;
+            const int ky = fast_div(tap, dv.kw), kx = tap - ky * kw;
+            const int q  = fast_div(m, dv.wo), xo = m - q * Wo;
+            const int b  = fast_div(q, dv.ho), yo = q - b * Ho;
+            const int yi = yo * sy - pad_t + ky * dil_y;
+            const int xi = xo * sx - pad_l + kx * dil_x;
+            const bool     inside = yi >= 0 && yi < H && xi >= 0 && xi < W;
+            const uint8_t *sp     = src + ((static_cast<int64_t>(b) * H + yi) * W + xi) * C + c;
+            if (VEC == 16)
+            {
+                uint4 v = make_uint4(pad_word, pad_word, pad_word, pad_word);
+                if (inside) v = __ldg(reinterpret_cast<const uint4 *>(sp));
+                *reinterpret_cast<uint4 *>(d) = v;
+            }
+            else
+            {
+                *d = inside ? *sp : static_cast<uint8_t>(pad_word);
+            }
         }
     }
 }
@@ -436,15 +508,30 @@ cugl_status launch_reduce_cols(cugl_context *ctx, const void *d_b, bool is_signe
     CUGL_CUDA_TRY(ctx, cudaMemsetAsync(d_out, 0, sizeof(int32_t) * N, ctx->stream));
     if (K > 0)
     {
-        const int gx = (N + kThreads * 4 - 1) / (kThreads * 4);
-        // enough K slabs to fill the machine a few times over, at least 32 rows each
-        int slabs = (ctx->sm_count * 4 + gx - 1) / gx;
-        slabs     = max(1, min(slabs, (K + 31) / 32));
-        const int k_per_block = (K + slabs - 1) / slabs;
-        slabs                 = (K + k_per_block - 1) / k_per_block;
-        reduce_cols_kernel<<<dim3(gx, slabs), kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_b),
-                                                                          is_signed, K, N, ldb, k_per_block, d_out);
-        CUGL_TRY(check_cuda(ctx, cudaGetLastError(), "reduce_cols_kernel"));
+        const bool aligned = ((reinterpret_cast<uintptr_t>(d_b) | static_cast<uint64_t>(ldb)) & 15) == 0;
+        const int  n_vec   = aligned ? N / 16 : 0; // 16-column units read with 128-bit loads
+        // enough K slabs to fill the machine a few times over, at least 32 rows each, at most kColSlabRows
+        auto slab_rows = [&](int gx) {
+            int slabs = (ctx->sm_count * 4 + gx - 1) / gx;
+            slabs     = max(1, min(slabs, (K + 31) / 32));
+            return min(kColSlabRows, (K + slabs - 1) / slabs);
+        };
+        if (n_vec > 0)
+        {
+            const int gx          = (n_vec + kThreads - 1) / kThreads;
+            const int k_per_block = slab_rows(gx);
+            reduce_cols_kernel<<<dim3(gx, (K + k_per_block - 1) / k_per_block), kThreads, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(d_b), is_signed, K, n_vec, ldb, k_per_block, d_out);
+            CUGL_TRY(check_cuda(ctx, cudaGetLastError(), "reduce_cols_kernel"));
+        }
+        if (16 * n_vec < N)
+        {
+            const int gx          = (N - 16 * n_vec + kThreads - 1) / kThreads;
+            const int k_per_block = slab_rows(gx);
+            reduce_cols_generic_kernel<<<dim3(gx, (K + k_per_block - 1) / k_per_block), kThreads, 0, ctx->stream>>>(
+                static_cast<const uint8_t *>(d_b), is_signed, K, 16 * n_vec, N, ldb, k_per_block, d_out);
+            CUGL_TRY(check_cuda(ctx, cudaGetLastError(), "reduce_cols_generic_kernel"));
+        }
     }
     if (scalar != 1)
     {
@@ -486,11 +573,15 @@ cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, 
                                ? static_cast<int32_t>(static_cast<uint32_t>(a_off) * static_cast<uint32_t>(b_off) *
                                                       static_cast<uint32_t>(K))
                                : 0;
-    const int blocks = grid_for(static_cast<int64_t>(M) * N, ctx->sm_count, 4);
-    offset_contribution_kernel<<<blocks, kThreads, 0, ctx->stream>>>(d_mm, M, N, ld_bytes / 4,
-                                                                     a_off != 0 ? d_colsum : nullptr,
-                                                                     b_off != 0 ? d_rowsum : nullptr, a_off, b_off,
-                                                                     k_term);
+    const int  groups = (N + 3) / 4;
+    const int  gx     = max(1, min((groups + kThreads - 1) / kThreads, 8));
+    const int  gy     = max(1, min(M, ctx->sm_count * 16 / gx));
+    const bool vec_ok = ((reinterpret_cast<uintptr_t>(d_mm) | static_cast<uint64_t>(ld_bytes) |
+                          reinterpret_cast<uintptr_t>(d_colsum)) & 15) == 0;
+    offset_contribution_kernel<<<dim3(gx, gy), kThreads, 0, ctx->stream>>>(d_mm, M, N, ld_bytes / 4,
+                                                                           a_off != 0 ? d_colsum : nullptr,
+                                                                           b_off != 0 ? d_rowsum : nullptr, a_off, b_off,
+                                                                           k_term, vec_ok);
     return check_cuda(ctx, cudaGetLastError(), "offset_contribution_kernel");
 }
 
@@ -502,7 +593,9 @@ cugl_status launch_output_stage(cugl_context *ctx, const int32_t *d_in, int64_t 
     if (M <= 0 || N <= 0) return CUGL_SUCCESS;
     const bool vec_ok = ((reinterpret_cast<uintptr_t>(d_in) | static_cast<uint64_t>(ld_in_bytes)) & 15) == 0 &&
                         ((reinterpret_cast<uintptr_t>(d_out) | static_cast<uint64_t>(ld_out_bytes)) & (out16 ? 7 : 3)) == 0;
-    const int blocks = grid_for(static_cast<int64_t>(M) * ((N + 3) / 4), ctx->sm_count, 2);
+    const int  gx = ((N + 3) / 4 + kThreads - 1) / kThreads;
+    const int  gy = max(1, min(M, (ctx->sm_count * 16 + gx - 1) / gx));
+    const dim3 blocks(gx, gy);
     if (out16)
     {
         output_stage_kernel<true><<<blocks, kThreads, 0, ctx->stream>>>(
@@ -522,25 +615,39 @@ cugl_status launch_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst
                                int kh, int sx, int sy, int pad_l, int pad_t, int dil_x, int dil_y, int Wo, int Ho,
                                int pad_value, int64_t row_stride)
 {
-    const int64_t M = static_cast<int64_t>(B) * Ho * Wo;
-    if (M <= 0) return CUGL_SUCCESS;
+    const int64_t M64 = static_cast<int64_t>(B) * Ho * Wo;
+    if (M64 <= 0) return CUGL_SUCCESS;
+    if (M64 >= (1ll << 31) || row_stride >= (1ll << 24))
+    {
+        return fail(ctx, CUGL_UNSUPPORTED_CONFIG, "im2col: more than 2^31 output rows or rows of 16 MB and more");
+    }
+    const int      M        = static_cast<int>(M64);
     const uint32_t pb       = static_cast<uint32_t>(pad_value) & 0xffu;
     const uint32_t pad_word = pb * 0x01010101u;
     const bool     vec16    = (C % 16 == 0) && (row_stride % 16 == 0) &&
                        ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_dst)) & 15) == 0;
+    const int vec   = vec16 ? 16 : 1;
+    const int units = static_cast<int>(row_stride / vec);
+    // about four units per thread and step, whole rows
+    const int rows_per_iter = max(1, min(M, (4 * kThreads + units - 1) / units));
+    Im2colDivs dv;
+    dv.units = make_fastdiv(units);
+    dv.c     = make_fastdiv(C);
+    dv.kw    = make_fastdiv(kw);
+    dv.wo    = make_fastdiv(Wo);
+    dv.ho    = make_fastdiv(Ho);
+    const int blocks = grid_for((static_cast<int64_t>(M) + rows_per_iter - 1) / rows_per_iter * kThreads, ctx->sm_count);
     if (vec16)
     {
-        const int blocks = grid_for(M * (row_stride / 16), ctx->sm_count, 2);
         im2col_nhwc_kernel<16><<<blocks, kThreads, 0, ctx->stream>>>(
             static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), C, W, H, M, kw, kh, sx, sy, pad_l,
-            pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride);
+            pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride, rows_per_iter, dv);
     }
     else
     {
-        const int blocks = grid_for(M * row_stride, ctx->sm_count, 4);
         im2col_nhwc_kernel<1><<<blocks, kThreads, 0, ctx->stream>>>(
             static_cast<const uint8_t *>(d_src), static_cast<uint8_t *>(d_dst), C, W, H, M, kw, kh, sx, sy, pad_l,
-            pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride);
+            pad_t, dil_x, dil_y, Wo, Ho, pad_word, row_stride, rows_per_iter, dv);
     }
     return check_cuda(ctx, cudaGetLastError(), "im2col_nhwc_kernel");
 }

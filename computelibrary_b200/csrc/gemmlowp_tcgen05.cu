@@ -1780,36 +1780,6 @@ __global__ void __launch_bounds__(kThreads, 1)
 // pad buffer, exactly what im2col would have written (the reference's indirect mode points such taps at a
 // zero-point row as well), so the offset terms of the epilogue need no correction.
 // ---------------------------------------------------------------------------------------------------
-// Division by a run-time constant as multiply-high and shift (round-up method): with p = 31 + ceil(log2 d),
-// mul = ceil(2^p / d) fits 32 bits and n / d == umulhi(n, mul) >> (p - 32) for every 0 <= n < 2^31.
-struct FastDiv
-{
-    uint32_t mul, shr, d;
-};
-
-inline FastDiv make_fastdiv(int d)
-{
-    FastDiv f;
-    f.d = static_cast<uint32_t>(d);
-    if (d <= 1)
-    {
-        f.mul = 0;
-        f.shr = 0;
-        return f;
-    }
-    int l = 0;
-    while ((1ll << l) < d) ++l;
-    const int p = 31 + l;
-    f.mul       = static_cast<uint32_t>(((1ull << p) + static_cast<uint64_t>(d) - 1) / static_cast<uint64_t>(d));
-    f.shr       = static_cast<uint32_t>(p - 32);
-    return f;
-}
-
-__device__ __forceinline__ int fast_div(int n, const FastDiv &f)
-{
-    return f.d <= 1 ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), f.mul) >> f.shr);
-}
-
 struct ConvGeom
 {
     const uint8_t *src; // [B][H][W][C]

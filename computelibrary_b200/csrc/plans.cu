@@ -36,7 +36,9 @@ struct GemmCore
     uint8_t      *d_bt     = nullptr; // [N][ldbt], K-major, zero padded
     int64_t       ldbt     = 0;
     int32_t      *d_colsum = nullptr; // [N]
-    int32_t      *d_rowsum = nullptr; // [M]
+    int32_t      *d_rowsum = nullptr; // [M]; plan-owned, allocated when first needed unless a temporary workspace is bound
+    int32_t      *d_rowsum_bound = nullptr; // row sums inside the caller's temporary workspace
+    int           rowsum_len = 0;
     int32_t      *d_mults  = nullptr; // [N]
     int32_t      *d_shifts = nullptr;
     bool          force_simt = false;
@@ -49,12 +51,35 @@ struct GemmCore
     int           block_n       = 0;     // 64 / 128 / 256 force that tile width of the one-CTA kernels, 0 = automatic
     int           pair_drain    = 0;     // < 0: every accumulator buffer is drained on its own
 
+    // bytes of the row-sum vector as a share of a temporary workspace (none without a B offset)
+    size_t rowsum_bytes() const
+    {
+        return b_off != 0 ? static_cast<size_t>(round_up(sizeof(int32_t) * static_cast<int64_t>(rowsum_len), 256)) : 0;
+    }
+
+    // the row sums live in the bound workspace, else in plan-owned memory allocated on first use
+    cugl_status rowsum_buffer(int32_t **out)
+    {
+        if (d_rowsum_bound != nullptr)
+        {
+            *out = d_rowsum_bound;
+            return CUGL_SUCCESS;
+        }
+        if (d_rowsum == nullptr)
+        {
+            CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * static_cast<size_t>(rowsum_len > 0 ? rowsum_len : 1),
+                                 reinterpret_cast<void **>(&d_rowsum)));
+        }
+        *out = d_rowsum;
+        return CUGL_SUCCESS;
+    }
+
     cugl_status alloc(int n_b_copies, int rowsum_len)
     {
         ldbt = round_up(K, 128);
         CUGL_TRY(cugl_malloc(ctx, static_cast<size_t>(ldbt) * N * n_b_copies, reinterpret_cast<void **>(&d_bt)));
         CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * N * n_b_copies, reinterpret_cast<void **>(&d_colsum)));
-        CUGL_TRY(cugl_malloc(ctx, sizeof(int32_t) * rowsum_len, reinterpret_cast<void **>(&d_rowsum)));
+        this->rowsum_len = rowsum_len;
         CUGL_TRY(cugl_memset(ctx, d_bt, 0, static_cast<size_t>(ldbt) * N * n_b_copies));
         return CUGL_SUCCESS;
     }
@@ -103,11 +128,11 @@ struct GemmCore
         d_colsum = d_rowsum = d_mults = d_shifts = nullptr;
     }
 
-    EpilogueParams epilogue(const int32_t *bias, int b_copy, int rowsum_off) const
+    EpilogueParams epilogue(const int32_t *bias, int b_copy, const int32_t *rowsum = nullptr) const
     {
         EpilogueParams ep{};
         ep.colsum = a_off != 0 ? d_colsum + static_cast<size_t>(b_copy) * N : nullptr;
-        ep.rowsum = b_off != 0 ? d_rowsum + rowsum_off : nullptr;
+        ep.rowsum = b_off != 0 ? rowsum : nullptr;
         ep.bias   = bias;
         ep.mults  = per_channel ? d_mults : nullptr;
         ep.shifts = per_channel ? d_shifts : nullptr;
@@ -143,7 +168,7 @@ struct GemmCore
     // rows x K product against B copy b_copy.
     cugl_status gemm(const void *d_a, int64_t lda, int rows, void *d_dst, int64_t ldd, const int32_t *d_bias,
                      int b_copy, int rowsum_off, void *const *extra_dst = nullptr, int n_extra = 0,
-                     const void *d_residual = nullptr, int res_floor = 0, int res_cap = 255) const
+                     const void *d_residual = nullptr, int res_floor = 0, int res_cap = 255)
     {
         GemmOperands op{};
         op.a        = d_a;
@@ -178,11 +203,14 @@ struct GemmCore
                         "several destinations or a fused residual need the tensor-core kernel (16-byte aligned A "
                         "with 16-byte row pitch)");
         }
+        int32_t *rowsum = nullptr;
         if (b_off != 0)
         {
-            CUGL_TRY(launch_reduce_rows(ctx, d_a, a_signed, rows, K, lda, 1, d_rowsum + rowsum_off));
+            CUGL_TRY(rowsum_buffer(&rowsum));
+            rowsum += rowsum_off;
+            CUGL_TRY(launch_reduce_rows(ctx, d_a, a_signed, rows, K, lda, 1, rowsum));
         }
-        const EpilogueParams ep = epilogue(d_bias, b_copy, rowsum_off);
+        const EpilogueParams ep = epilogue(d_bias, b_copy, rowsum);
         return uses_tcgen05(op) ? launch_gemmlowp_tcgen05(ctx, op, ep, allow_pair) : launch_gemmlowp_simt(ctx, op, ep);
     }
 };
@@ -828,7 +856,27 @@ struct cugl_conv_plan
     bool     fold = false;
     int      eC = 0, eW = 0, eH = 0, ekw = 0, ekh = 0, esx = 1, esy = 1, epl = 0, ept = 0;
     int      fold_oy = 0, fold_ox = 0;
-    uint8_t *d_fold = nullptr; // [B][eH][eW][16]
+    uint8_t *d_fold = nullptr; // [B][eH][eW][16]; plan-owned, allocated on first use unless a workspace is bound
+    // temporary workspace handed in by the caller (cugl_conv2d_plan_bind_temp): row sums | folded input | im2col matrix
+    uint8_t *d_temp = nullptr;
+    size_t   temp_bound_bytes = 0;
+
+    size_t fold_bytes() const
+    {
+        return fold ? static_cast<size_t>(round_up(static_cast<int64_t>(desc.B) * eH * eW * 16, 256)) : 0;
+    }
+    bool explicit_lowering() const
+    {
+        return !skip_im2col && !(implicit && allow_implicit && !core.force_simt);
+    }
+    size_t cols_bytes() const
+    {
+        return explicit_lowering() ? static_cast<size_t>(round_up(M * Kp, 256)) : 0;
+    }
+    size_t temp_bytes() const
+    {
+        return core.rowsum_bytes() + fold_bytes() + cols_bytes();
+    }
     // fused residual addition (cugl_conv2d_plan_set_residual): clamp bounds of the saturating form
     bool residual_set = false;
     int  res_floor = 0, res_cap = 255;
@@ -972,10 +1020,6 @@ extern "C"
         // Implicit GEMM whenever the gather kernel can address the tensors: channel count a multiple of 16 and
         // symmetric weights (no row-sum term).  Otherwise explicit im2col.
         p->implicit = !p->skip_im2col && (p->eC % 16) == 0 && desc->w_zero_point == 0;
-        if (s == CUGL_SUCCESS && p->fold)
-        {
-            s = cugl_malloc(ctx, static_cast<size_t>(desc->B) * p->eH * p->eW * 16, reinterpret_cast<void **>(&p->d_fold));
-        }
         if (s == CUGL_SUCCESS && p->implicit)
         {
             s = cugl_malloc(ctx, kConvPadBytes, reinterpret_cast<void **>(&p->d_pad));
@@ -1107,11 +1151,23 @@ extern "C"
         {
             return fail(plan->ctx, CUGL_INVALID_ARGUMENT, "cugl_conv2d_run: plan was configured with a bias");
         }
+        const bool bound = plan->d_temp != nullptr;
+        if (bound && plan->temp_bound_bytes < plan->temp_bytes())
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                        "cugl_conv2d_run: the bound temporary workspace is smaller than cugl_conv2d_plan_temp_bytes");
+        }
         if (plan->fold)
         {
-            CUGL_TRY(launch_fold_input(plan->ctx, d_src, plan->d_fold, d.B, d.H, d.W, d.C, plan->eH, plan->eW,
+            uint8_t *fold_buf = bound ? plan->d_temp + plan->core.rowsum_bytes() : plan->d_fold;
+            if (fold_buf == nullptr)
+            {
+                CUGL_TRY(cugl_malloc(plan->ctx, plan->fold_bytes(), reinterpret_cast<void **>(&plan->d_fold)));
+                fold_buf = plan->d_fold;
+            }
+            CUGL_TRY(launch_fold_input(plan->ctx, d_src, fold_buf, d.B, d.H, d.W, d.C, plan->eH, plan->eW,
                                        d.src_zero_point));
-            d_src = plan->d_fold;
+            d_src = fold_buf;
         }
         if (plan->implicit && plan->allow_implicit && !plan->core.force_simt)
         {
@@ -1157,22 +1213,24 @@ extern "C"
             cv.Ho     = plan->Ho;
             if (gemmlowp_conv_tcgen05_supported(op, cv))
             {
-                return launch_gemmlowp_conv_tcgen05(plan->ctx, op, c.epilogue(d.has_bias ? d_bias : nullptr, 0, 0), cv);
+                return launch_gemmlowp_conv_tcgen05(plan->ctx, op, c.epilogue(d.has_bias ? d_bias : nullptr, 0), cv);
             }
         }
         const void *a   = d_src;
         int64_t     lda = plan->eC;
         if (!plan->skip_im2col)
         {
-            if (plan->d_cols == nullptr)
+            uint8_t *cols = bound ? plan->d_temp + plan->core.rowsum_bytes() + plan->fold_bytes() : plan->d_cols;
+            if (cols == nullptr)
             {
                 CUGL_TRY(cugl_malloc(plan->ctx, static_cast<size_t>(plan->M) * plan->Kp,
                                      reinterpret_cast<void **>(&plan->d_cols)));
+                cols = plan->d_cols;
             }
-            CUGL_TRY(launch_im2col_nhwc(plan->ctx, d_src, plan->d_cols, plan->eC, plan->eW, plan->eH, d.B, plan->ekw,
+            CUGL_TRY(launch_im2col_nhwc(plan->ctx, d_src, cols, plan->eC, plan->eW, plan->eH, d.B, plan->ekw,
                                         plan->ekh, plan->esx, plan->esy, plan->epl, plan->ept, d.dil_x, d.dil_y,
                                         plan->Wo, plan->Ho, d.src_zero_point, plan->Kp));
-            a   = plan->d_cols;
+            a   = cols;
             lda = plan->Kp;
         }
         return plan->core.gemm(a, lda, static_cast<int>(plan->M), d_dst, d.OFM, d.has_bias ? d_bias : nullptr, 0, 0,
@@ -1306,5 +1364,47 @@ extern "C"
             return fold + 1;
         }
         return fold + (plan->skip_im2col ? 0 : 1) + 1 + (plan->core.b_off != 0 ? 1 : 0);
+    }
+    // ---- temporary workspaces (MemoryRequirements with lifetime Temporary, arm_compute/core/experimental/Types.h:89-125)
+    size_t cugl_gemmlowp_plan_temp_bytes(const cugl_gemm_plan *plan)
+    {
+        return plan != nullptr ? plan->core.rowsum_bytes() : 0;
+    }
+
+    cugl_status cugl_gemmlowp_plan_bind_temp(cugl_gemm_plan *plan, void *d_ws, size_t bytes)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_bind_temp: NULL plan");
+        }
+        if (d_ws != nullptr && ((reinterpret_cast<uintptr_t>(d_ws) & 255) != 0 || bytes < plan->core.rowsum_bytes()))
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                        "cugl_gemmlowp_plan_bind_temp: workspace must be 256-byte aligned and hold cugl_gemmlowp_plan_temp_bytes");
+        }
+        plan->core.d_rowsum_bound = static_cast<int32_t *>(d_ws);
+        return CUGL_SUCCESS;
+    }
+
+    size_t cugl_conv2d_plan_temp_bytes(const cugl_conv_plan *plan)
+    {
+        return plan != nullptr ? plan->temp_bytes() : 0;
+    }
+
+    cugl_status cugl_conv2d_plan_bind_temp(cugl_conv_plan *plan, void *d_ws, size_t bytes)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_bind_temp: NULL plan");
+        }
+        if (d_ws != nullptr && ((reinterpret_cast<uintptr_t>(d_ws) & 255) != 0 || bytes < plan->temp_bytes()))
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                        "cugl_conv2d_plan_bind_temp: workspace must be 256-byte aligned and hold cugl_conv2d_plan_temp_bytes");
+        }
+        plan->d_temp              = static_cast<uint8_t *>(d_ws);
+        plan->temp_bound_bytes    = d_ws != nullptr ? bytes : 0;
+        plan->core.d_rowsum_bound = plan->core.b_off != 0 ? static_cast<int32_t *>(d_ws) : nullptr;
+        return CUGL_SUCCESS;
     }
 }

@@ -239,6 +239,15 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_tile_columns(cugl_gemm_plan *plan, i
  * tile on its own.  Testing / measurement aid: the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_paired_drain(cugl_gemm_plan *plan, int on);
 
+/* MemoryRequirements of the operator with lifetime Temporary (arm_compute/core/experimental/Types.h:89-125; the
+ * VectorSumRow slot of src/cpu/operators/CpuGemmLowpMatrixMultiplyCore.h:144-155): bytes of device memory a run of the
+ * plan needs that hold nothing between runs (the row sums of A, only with a non-zero B offset).  By default the plan
+ * allocates them itself on first use.  cugl_gemmlowp_plan_bind_temp makes later runs use [d_ws, d_ws + bytes)
+ * instead (256-byte aligned, at least _temp_bytes), so that a host-side memory manager (MemoryGroup /
+ * MemoryManagerOnDemand) can hand the same bytes to other functions between runs; d_ws = NULL unbinds. */
+CUGL_API size_t      cugl_gemmlowp_plan_temp_bytes(const cugl_gemm_plan *plan);
+CUGL_API cugl_status cugl_gemmlowp_plan_bind_temp(cugl_gemm_plan *plan, void *d_ws, size_t bytes);
+
 /* Fused GEMMLowp that allocates nothing.  No counterpart in the reference: Compute Library always lets the
  * function object own its workspace.  For callers that cannot call cudaMalloc -- a serving loop whose device
  * memory is fully committed to its own arena, a plugin that may not touch the host's allocator, code inside
@@ -363,6 +372,10 @@ CUGL_API cugl_status cugl_conv2d_plan_set_channel_major(cugl_conv_plan *plan, in
 CUGL_API cugl_status cugl_conv2d_plan_set_tile_columns(cugl_conv_plan *plan, int columns);
 /* as cugl_gemmlowp_plan_set_paired_drain, for the lowerings that run the plain GEMM kernel */
 CUGL_API cugl_status cugl_conv2d_plan_set_paired_drain(cugl_conv_plan *plan, int on);
+/* As cugl_gemmlowp_plan_temp_bytes / _bind_temp for the convolution: row sums, the folded stem input and -- explicit
+ * lowering only -- the im2col matrix (the Im2ColOutput slot of CpuGemmConv2d, src/cpu/operators/CpuGemmConv2d.h). */
+CUGL_API size_t      cugl_conv2d_plan_temp_bytes(const cugl_conv_plan *plan);
+CUGL_API cugl_status cugl_conv2d_plan_bind_temp(cugl_conv_plan *plan, void *d_ws, size_t bytes);
 /* Fused residual addition: dst = act(quantize(dequantize(conv) + dequantize(residual))) computed in the epilogue
  * of the convolution, i.e. NEGEMMConvolutionLayer followed by NEArithmeticAddition (ConvertPolicy::SATURATE)
  * and NEActivationLayer (arm_compute/runtime/NEON/functions/NEArithmeticAddition.h:43-109) without the
