@@ -8,7 +8,7 @@ import re
 
 from . import build as _build
 
-U8, S8, S32, S16 = 0, 1, 2, 3  # S16: QSYMM16 destination of the stand-alone fixed-point output stage
+U8, S8, S32, S16, F32 = 0, 1, 2, 3, 4  # S16: QSYMM16 (stand-alone stage only); F32: dequantized GEMM output
 STAGE_NONE, STAGE_QUANTIZE_DOWN, STAGE_FIXEDPOINT = 0, 1, 2
 INT32_MIN, INT32_MAX = -(2 ** 31), 2 ** 31 - 1
 
@@ -38,6 +38,7 @@ class GemmDesc(C.Structure):
         ("h_gemmlowp_multipliers", _pi32), ("h_gemmlowp_shifts", _pi32),
         ("gemmlowp_offset", _i32), ("gemmlowp_min_bound", _i32), ("gemmlowp_max_bound", _i32),
         ("has_bias", _i32), ("reshape_b_only_on_first_run", _i32),
+        ("accumulate", _i32), ("dequantize_scale", C.c_float),
     ]
 
 
@@ -115,6 +116,8 @@ _SIGNATURES = {
     "cugl_gemmlowp_noalloc_status": (C.c_int, [_vp]),
     "cugl_gemmlowp_plan_temp_bytes": (C.c_size_t, [_vp]),
     "cugl_gemmlowp_plan_bind_temp": (C.c_int, [_vp, _vp, C.c_size_t]),
+    "cugl_conv2d_update_quantization": (C.c_int, [_vp, C.POINTER(ConvDesc)]),
+    "cugl_transpose_batched": (C.c_int, [_vp, _vp, _vp, _i32, _i32, _i32]),
     "cugl_conv2d_plan_temp_bytes": (C.c_size_t, [_vp]),
     "cugl_conv2d_plan_bind_temp": (C.c_int, [_vp, _vp, C.c_size_t]),
     "cugl_reduce_rows": (C.c_int, [_vp, _vp, _i32, _i32, _i32, _i64, _i32, _vp]),
@@ -341,6 +344,9 @@ class Context:
         self.check(self.lib.cugl_softmax_qasymm8(self.handle, _dptr(src), _dptr(dst), rows, cols, beta, in_q[0],
                                                  in_q[1]))
 
+    def transpose_batched(self, src, dst, rows, cols, batch):
+        self.check(self.lib.cugl_transpose_batched(self.handle, _dptr(src), _dptr(dst), rows, cols, batch))
+
     def weights_reshape_nhwc(self, w, dst, K, OFM):
         self.check(self.lib.cugl_weights_reshape_nhwc(self.handle, _dptr(w), _dptr(dst), K, OFM))
 
@@ -348,11 +354,12 @@ class Context:
 def make_gemm_desc(M, N, K, a_dtype, b_dtype, dst_dtype, a_offset=0, b_offset=0, stage=STAGE_FIXEDPOINT,
                    multiplier=0, shift=0, multipliers=None, shifts=None, offset=0, min_bound=INT32_MIN,
                    max_bound=INT32_MAX, has_bias=False, batch=1, lda=None, ldb=None, ldd=None,
-                   a_batch_stride=None, b_batch_stride=0, d_batch_stride=None, b_constant=True):
+                   a_batch_stride=None, b_batch_stride=0, d_batch_stride=None, b_constant=True, accumulate=False,
+                   dequantize_scale=0.0):
     """Fill a cugl_gemm_desc for dense row-major operands unless strides are given.  Returns
     (desc, keepalive) -- keepalive holds the numpy arrays the descriptor points into."""
     import numpy as np
-    dsz = 4 if dst_dtype == S32 else 1
+    dsz = 4 if dst_dtype in (S32, F32) else 1
     d = GemmDesc()
     d.M, d.N, d.K, d.batch = M, N, K, batch
     d.lda = K if lda is None else lda
@@ -380,6 +387,8 @@ def make_gemm_desc(M, N, K, a_dtype, b_dtype, dst_dtype, a_offset=0, b_offset=0,
     d.gemmlowp_min_bound, d.gemmlowp_max_bound = min_bound, max_bound
     d.has_bias = int(has_bias)
     d.reshape_b_only_on_first_run = int(b_constant)
+    d.accumulate = int(accumulate)
+    d.dequantize_scale = float(dequantize_scale)
     return d, keep
 
 
@@ -498,6 +507,13 @@ class GemmPlan:
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_allow_pair_kernel(self.handle, int(on)))
 
     @property
+    def temp_bytes(self) -> int:
+        return int(self.ctx.lib.cugl_gemmlowp_plan_temp_bytes(self.handle))
+
+    def bind_temp(self, ws, nbytes: int):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_bind_temp(self.handle, _dptr(ws), nbytes))
+
+    @property
     def kernel(self) -> str:
         return self.ctx.lib.cugl_gemmlowp_plan_kernel(self.handle).decode()
 
@@ -569,6 +585,10 @@ class ConvPlan:
     def run(self, src, bias, dst):
         self.ctx.check(self.ctx.lib.cugl_conv2d_run(self.handle, _dptr(src), _dptr(bias), _dptr(dst)))
 
+    def update_quantization(self, desc: "ConvDesc", keepalive=None):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_update_quantization(self.handle, C.byref(desc)))
+        self.desc, self._keep = desc, keepalive
+
     def set_residual(self, conv_out_scale, res_q, dst_q, act=ACT_NONE, act_a=0.0, act_b=0.0):
         """Configure the fused residual addition; raises CuglError (UNSUPPORTED_CONFIG) when the addition is not a
         saturating byte addition for these quantizations."""
@@ -597,6 +617,13 @@ class ConvPlan:
 
     def allow_implicit(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_implicit(self.handle, int(on)))
+
+    @property
+    def temp_bytes(self) -> int:
+        return int(self.ctx.lib.cugl_conv2d_plan_temp_bytes(self.handle))
+
+    def bind_temp(self, ws, nbytes: int):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_bind_temp(self.handle, _dptr(ws), nbytes))
 
     @property
     def kernel(self) -> str:

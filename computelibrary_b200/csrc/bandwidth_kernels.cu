@@ -211,6 +211,8 @@ __global__ void __launch_bounds__(kThreads) transpose_bytes_kernel(const uint8_t
     __shared__ uint8_t tile[64][64 + 4];
     const int          r0 = blockIdx.y * 64, c0 = blockIdx.x * 64;
     const int          tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+    src += static_cast<int64_t>(blockIdx.z) * rows * cols; // blockIdx.z: which matrix of the batch
+    dst += static_cast<int64_t>(blockIdx.z) * rows * cols;
     for (int r = ty; r < 64; r += 4)
     {
         tile[r][tx] = (r0 + r < rows && c0 + tx < cols) ? src[static_cast<int64_t>(r0 + r) * cols + c0 + tx] : 0;
@@ -555,10 +557,10 @@ cugl_status launch_transpose_colsum(cugl_context *ctx, const void *d_b, bool is_
     return check_cuda(ctx, cudaGetLastError(), "transpose_colsum_kernel");
 }
 
-cugl_status launch_transpose_bytes(cugl_context *ctx, const void *d_src, int rows, int cols, void *d_dst)
+cugl_status launch_transpose_bytes(cugl_context *ctx, const void *d_src, int rows, int cols, void *d_dst, int batch)
 {
-    if (rows <= 0 || cols <= 0) return CUGL_SUCCESS;
-    dim3 grid((cols + 63) / 64, (rows + 63) / 64);
+    if (rows <= 0 || cols <= 0 || batch <= 0) return CUGL_SUCCESS;
+    dim3 grid((cols + 63) / 64, (rows + 63) / 64, batch);
     transpose_bytes_kernel<<<grid, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_src), rows, cols,
                                                                static_cast<uint8_t *>(d_dst));
     return check_cuda(ctx, cudaGetLastError(), "transpose_bytes_kernel");

@@ -75,7 +75,27 @@ struct EpilogueParams
     int32_t        lo, hi;        // bounds already intersected with the 8-bit type range
     int32_t        stage;         // cugl_stage
     int32_t        out_signed;    // unused for S32
+    // stage NONE only: out_f32 != 0 writes float(result) * dq_scale instead of the int32 result; accumulate != 0 adds
+    // the value to what dst holds (int32 addition, or one float addition for a float destination)
+    int32_t        out_f32;
+    int32_t        accumulate;
+    float          dq_scale;
 };
+
+// The 32-bit word a stage-NONE epilogue stores for the int32 result v, given the word dst holds now.
+__device__ __forceinline__ uint32_t raw_result_word(int32_t v, uint32_t old, const EpilogueParams &ep)
+{
+    if (ep.out_f32 != 0)
+    {
+        float f = __fmul_rn(__int2float_rn(v), ep.dq_scale);
+        if (ep.accumulate != 0)
+        {
+            f = __fadd_rn(__uint_as_float(old), f);
+        }
+        return __float_as_uint(f);
+    }
+    return ep.accumulate != 0 ? old + static_cast<uint32_t>(v) : static_cast<uint32_t>(v);
+}
 
 // SQDMULH: (int64(a) * b * 2) >> 32, i.e. floor(a*b / 2^31); saturates only for INT32_MIN^2.
 // tests/validation/reference/UtilsQuantizedAsymm.h:60-67.

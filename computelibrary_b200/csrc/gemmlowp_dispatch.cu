@@ -86,6 +86,10 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
     // 57 / 60; 12544 x 2048 x 512: 37 / 43.  It needs whole 128-channel blocks (N = 64: 110 / 78).
     GemmOperands o   = op;
     o.block_n        = pick_block_n(ctx, op); // before the automatic channel-major choice below
+    if (ep.stage == CUGL_STAGE_NONE && (ep.out_f32 != 0 || ep.accumulate != 0) && o.channel_major == 0)
+    {
+        o.channel_major = -1; // read-modify-write of dst rows: the row-major epilogue does it with 128-bit accesses
+    }
     if (o.channel_major == 0)
     {
         // with a fused residual too: 50176 x 1024 x 256 + residual 69 us against 79 us row-major, 12544 x 2048 x 512

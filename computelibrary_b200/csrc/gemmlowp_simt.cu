@@ -71,7 +71,8 @@ __global__ void __launch_bounds__(256) gemmlowp_simt_kernel(GemmOperands op, Epi
             if (ep.bias != nullptr) v += ep.bias[n];
             if (ep.stage == CUGL_STAGE_NONE)
             {
-                *reinterpret_cast<int32_t *>(static_cast<uint8_t *>(op.dst) + m * op.ldd + n * 4) = v;
+                uint32_t *o = reinterpret_cast<uint32_t *>(static_cast<uint8_t *>(op.dst) + m * op.ldd + n * 4);
+                *o          = raw_result_word(v, ep.accumulate != 0 ? *o : 0u, ep);
             }
             else
             {

@@ -282,6 +282,8 @@ struct TileParams
     int      pair_drain; // one-CTA kernel, two accumulator buffers: drain two tiles of one column block together
     long long *trace; // optional per-CTA event timestamps (cugl_context_set_trace_buffer), else nullptr
     int32_t *status;
+    int      raw_f32, raw_accumulate; // stage NONE: float destination / dst += result (EpilogueParams::out_f32, accumulate)
+    float    raw_scale;               // dequantization scale of a float destination
 };
 
 
@@ -431,13 +433,29 @@ __device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, in
     const bool full = nc + 32 <= tp.N;
     if (kS32Out)
     {
-        int32_t *o = reinterpret_cast<int32_t *>(drow) + nc;
+        // v holds the int32 results; float conversion and accumulation into dst happen here (raw_result_word)
+        uint32_t  *o     = reinterpret_cast<uint32_t *>(drow) + nc;
+        const bool plain = tp.raw_f32 == 0 && tp.raw_accumulate == 0; // uniform over the launch
+        EpilogueParams rp{};
+        rp.out_f32    = tp.raw_f32;
+        rp.accumulate = tp.raw_accumulate;
+        rp.dq_scale   = tp.raw_scale;
         if (full && tp.vec_ok)
         {
 #pragma unroll
             for (int j = 0; j < 32; j += 4)
             {
-                *reinterpret_cast<uint4 *>(o + j) = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                uint4 w = make_uint4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                if (!plain)
+                {
+                    uint4 old = make_uint4(0, 0, 0, 0);
+                    if (tp.raw_accumulate != 0) old = *reinterpret_cast<const uint4 *>(o + j);
+                    w.x = raw_result_word(static_cast<int32_t>(w.x), old.x, rp);
+                    w.y = raw_result_word(static_cast<int32_t>(w.y), old.y, rp);
+                    w.z = raw_result_word(static_cast<int32_t>(w.z), old.z, rp);
+                    w.w = raw_result_word(static_cast<int32_t>(w.w), old.w, rp);
+                }
+                *reinterpret_cast<uint4 *>(o + j) = w;
             }
         }
         else
@@ -445,7 +463,10 @@ __device__ __forceinline__ void store_chunk(const uint32_t *v, uint8_t *drow, in
 #pragma unroll
             for (int j = 0; j < 32; ++j)
             {
-                if (nc + j < tp.N) o[j] = static_cast<int32_t>(v[j]);
+                if (nc + j < tp.N)
+                {
+                    o[j] = plain ? v[j] : raw_result_word(static_cast<int32_t>(v[j]), tp.raw_accumulate != 0 ? o[j] : 0u, rp);
+                }
             }
         }
     }
@@ -933,7 +954,11 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
 #pragma unroll
         for (int j = 0; j < 32; ++j)
         {
-            if (j < np) *reinterpret_cast<int32_t *>(o + j * tp.ldd) = static_cast<int32_t>(v[j]) + q.x;
+            if (j < np)
+            {
+                uint32_t *w = reinterpret_cast<uint32_t *>(o + j * tp.ldd);
+                *w          = raw_result_word(static_cast<int32_t>(v[j]) + q.x, ep.accumulate != 0 ? *w : 0u, ep);
+            }
         }
     }
     else if (tp.residual != nullptr)
@@ -2212,6 +2237,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     tp.idesc_half = 0;
     tp.split_tail = 0;
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
@@ -2252,6 +2278,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     tp.idesc_half = 0;
     tp.split_tail = 0;
     const int tiles = ((op.N + BLOCK_M - 1) / BLOCK_M) * ((op.M + BLOCK_N - 1) / BLOCK_N);
@@ -2295,6 +2322,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     const int tiles    = ((op.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((op.N + P::BLOCK_N - 1) / P::BLOCK_N);
     const int pairs    = ctx->sm_count / 2;
     const int clusters = tiles < pairs ? tiles : pairs;
@@ -2348,6 +2376,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     tp.status  = ctx->d_status;
     tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
     tp.trace   = ctx->d_trace;
+    tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     tp.idesc_half = 0;
     tp.split_tail = 0;
     ConvGeom cg;

@@ -12,7 +12,8 @@ cugl_status launch_reduce_cols(cugl_context *ctx, const void *d_b, bool is_signe
                                int32_t scalar, int32_t *d_out);
 cugl_status launch_transpose_colsum(cugl_context *ctx, const void *d_b, bool is_signed, int K, int N, int64_t ldb,
                                     void *d_bt, int64_t ldbt, int32_t *d_colsum);
-cugl_status launch_transpose_bytes(cugl_context *ctx, const void *d_src, int rows, int cols, void *d_dst);
+// batch matrices of rows x cols bytes, each transposed on its own (dense, back to back)
+cugl_status launch_transpose_bytes(cugl_context *ctx, const void *d_src, int rows, int cols, void *d_dst, int batch = 1);
 cugl_status launch_offset_contribution(cugl_context *ctx, int32_t *d_mm, int M, int N, int K, int64_t ld_bytes,
                                        const int32_t *d_colsum, const int32_t *d_rowsum, int32_t a_off,
                                        int32_t b_off);

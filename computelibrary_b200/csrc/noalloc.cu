@@ -151,6 +151,9 @@ extern "C" cugl_status cugl_gemmlowp_run_noalloc(void *stream, const cugl_gemm_d
     }
     ep.stage          = desc->stage;
     ep.out_signed     = desc->dst_dtype == CUGL_S8;
+    ep.out_f32        = desc->dst_dtype == CUGL_F32 ? 1 : 0;
+    ep.accumulate     = desc->accumulate != 0 ? 1 : 0;
+    ep.dq_scale       = desc->dequantize_scale;
 
     GemmOperands op{};
     op.a        = d_a;

@@ -33,12 +33,22 @@ struct GemmCore
     int32_t       stage = CUGL_STAGE_NONE;
     bool          per_channel = false;
     int32_t       mult = 0, shift = 0, result_offset = 0, min_bound = INT32_MIN, max_bound = INT32_MAX;
+    bool          accumulate = false; // stage NONE: dst += result
+    float         dq_scale   = 0.f;   // F32 destination: result * dq_scale
     uint8_t      *d_bt     = nullptr; // [N][ldbt], K-major, zero padded
     int64_t       ldbt     = 0;
     int32_t      *d_colsum = nullptr; // [N]
     int32_t      *d_rowsum = nullptr; // [M]; plan-owned, allocated when first needed unless a temporary workspace is bound
     int32_t      *d_rowsum_bound = nullptr; // row sums inside the caller's temporary workspace
     int           rowsum_len = 0;
+    // A whose base or row pitch is not a multiple of 16 bytes cannot be described to the TMA engine.  A copy with
+    // rows of round_up(K, 16) bytes in temporary memory keeps such products on the tensor cores (the role of the
+    // TmpA slot of CpuGemmLowpMatrixMultiplyCore.h:144-155, there an interleaved copy of A).
+    uint8_t      *d_tmp_a = nullptr;       // plan-owned copy, allocated on first use unless a workspace is bound
+    size_t        tmp_a_capacity = 0;
+    uint8_t      *d_tmp_a_bound = nullptr; // inside the caller's temporary workspace
+    int64_t       lda_hint = 0;            // row pitch of A announced at configure time (sizes the workspace share)
+    int           tmp_a_rows = 0;          // rows one launch copies at most
     int32_t      *d_mults  = nullptr; // [N]
     int32_t      *d_shifts = nullptr;
     bool          force_simt = false;
@@ -55,6 +65,33 @@ struct GemmCore
     size_t rowsum_bytes() const
     {
         return b_off != 0 ? static_cast<size_t>(round_up(sizeof(int32_t) * static_cast<int64_t>(rowsum_len), 256)) : 0;
+    }
+
+    size_t tmp_a_bytes() const
+    {
+        return (lda_hint & 15) != 0 ? static_cast<size_t>(round_up(round_up(K, 16) * static_cast<int64_t>(tmp_a_rows), 256)) : 0;
+    }
+
+    cugl_status tmp_a_buffer(size_t bytes, uint8_t **out)
+    {
+        if (d_tmp_a_bound != nullptr && bytes <= tmp_a_bytes())
+        {
+            *out = d_tmp_a_bound;
+            return CUGL_SUCCESS;
+        }
+        if (d_tmp_a == nullptr || tmp_a_capacity < bytes)
+        {
+            if (d_tmp_a != nullptr)
+            {
+                CUGL_CUDA_TRY(ctx, cudaStreamSynchronize(ctx->stream));
+                cugl_free(ctx, d_tmp_a);
+                d_tmp_a = nullptr;
+            }
+            CUGL_TRY(cugl_malloc(ctx, bytes, reinterpret_cast<void **>(&d_tmp_a)));
+            tmp_a_capacity = bytes;
+        }
+        *out = d_tmp_a;
+        return CUGL_SUCCESS;
     }
 
     // the row sums live in the bound workspace, else in plan-owned memory allocated on first use
@@ -122,6 +159,8 @@ struct GemmCore
         cugl_free(ctx, d_bt);
         cugl_free(ctx, d_colsum);
         cugl_free(ctx, d_rowsum);
+        cugl_free(ctx, d_tmp_a);
+        d_tmp_a = nullptr;
         cugl_free(ctx, d_mults);
         cugl_free(ctx, d_shifts);
         d_bt = nullptr;
@@ -157,6 +196,9 @@ struct GemmCore
         }
         ep.stage          = stage;
         ep.out_signed     = dst_dtype == CUGL_S8;
+        ep.out_f32        = dst_dtype == CUGL_F32 ? 1 : 0;
+        ep.accumulate     = accumulate ? 1 : 0;
+        ep.dq_scale       = dq_scale;
         return ep;
     }
 
@@ -197,6 +239,15 @@ struct GemmCore
         {
             op.extra_dst[i] = extra_dst[i];
         }
+        if (!force_simt && ((reinterpret_cast<uintptr_t>(d_a) | static_cast<uint64_t>(lda)) & 15) != 0)
+        {
+            const int64_t kp  = round_up(K, 16);
+            uint8_t      *tmp = nullptr;
+            CUGL_TRY(tmp_a_buffer(static_cast<size_t>(kp) * rows, &tmp));
+            CUGL_CUDA_TRY(ctx, cudaMemcpy2DAsync(tmp, kp, d_a, lda, K, rows, cudaMemcpyDeviceToDevice, ctx->stream));
+            op.a   = tmp; // bytes K .. kp-1 of a row are never read: the tensor map ends at K
+            op.lda = kp;
+        }
         if ((n_extra > 0 || d_residual != nullptr) && !uses_tcgen05(op))
         {
             return fail(ctx, CUGL_UNSUPPORTED_CONFIG,
@@ -208,7 +259,7 @@ struct GemmCore
         {
             CUGL_TRY(rowsum_buffer(&rowsum));
             rowsum += rowsum_off;
-            CUGL_TRY(launch_reduce_rows(ctx, d_a, a_signed, rows, K, lda, 1, rowsum));
+            CUGL_TRY(launch_reduce_rows(ctx, op.a, a_signed, rows, K, op.lda, 1, rowsum));
         }
         const EpilogueParams ep = epilogue(d_bias, b_copy, rowsum);
         return uses_tcgen05(op) ? launch_gemmlowp_tcgen05(ctx, op, ep, allow_pair) : launch_gemmlowp_simt(ctx, op, ep);
@@ -248,12 +299,14 @@ const char *cugl::validate_gemm_desc(const cugl_gemm_desc *d, cugl_status *code,
     }
     if (d->stage == CUGL_STAGE_NONE)
     {
-        if (d->dst_dtype != CUGL_S32) return "output stage NONE requires an S32 output";
+        if (d->dst_dtype != CUGL_S32 && d->dst_dtype != CUGL_F32) return "output stage NONE requires an S32 or F32 output";
         if (d->has_bias) return "Bias addition not supported in NEGEMMLowpMatrixMultiplyCore for output S32";
+        if (d->dst_dtype == CUGL_F32 && !(d->dequantize_scale > 0.f)) return "an F32 output needs a positive dequantize_scale";
     }
     else
     {
         if (!is_q8(d->dst_dtype)) return "a quantize-down output stage requires a QASYMM8 / QASYMM8_SIGNED output";
+        if (d->accumulate) return "Accumulation is not supported for output QASYMM8/QASYMM8_SIGNED";
         if (d->gemmlowp_min_bound > d->gemmlowp_max_bound) return "gemmlowp_min_bound > gemmlowp_max_bound";
         if (d->is_quantized_per_channel)
         {
@@ -263,11 +316,11 @@ const char *cugl::validate_gemm_desc(const cugl_gemm_desc *d, cugl_status *code,
                 return "per-channel requantisation with a non-zero B offset is only defined for QASYMM8 output";
         }
     }
-    const int64_t dsz = d->dst_dtype == CUGL_S32 ? 4 : 1;
+    const int64_t dsz = (d->dst_dtype == CUGL_S32 || d->dst_dtype == CUGL_F32) ? 4 : 1;
     if (d->lda < d->K) return "lda is smaller than a row of A";
     if (d->ldb < d->N) return "ldb is smaller than a row of B";
     if (d->ldd < d->N * dsz) return "ldd is smaller than a row of the output";
-    if (d->dst_dtype == CUGL_S32 && (d->ldd % 4) != 0) return "ldd of an S32 output must be a multiple of 4";
+    if (dsz == 4 && (d->ldd % 4) != 0) return "ldd of an S32 / F32 output must be a multiple of 4";
     if (d->batch > 1)
     {
         if (d->a_batch_stride < static_cast<int64_t>(d->M) * d->lda) return "a_batch_stride overlaps batches";
@@ -321,6 +374,8 @@ void apply_quant_fields(cugl_gemm_plan *p, const cugl_gemm_desc *d)
     c.result_offset = d->gemmlowp_offset;
     c.min_bound     = d->gemmlowp_min_bound;
     c.max_bound     = d->gemmlowp_max_bound;
+    c.accumulate    = d->accumulate != 0;
+    c.dq_scale      = d->dequantize_scale;
 }
 
 cugl_status relayout_b(cugl_gemm_plan *p, const void *d_b)
@@ -390,6 +445,8 @@ extern "C"
         c.b_signed  = desc->b_dtype == CUGL_S8;
         c.dst_dtype = desc->dst_dtype;
         apply_quant_fields(p, desc);
+        c.lda_hint   = desc->lda;
+        c.tmp_a_rows = p->collapse_batch ? desc->M * desc->batch : desc->M;
         cugl_status s = c.alloc(p->b_copies, desc->M * desc->batch);
         if (s == CUGL_SUCCESS)
         {
@@ -612,6 +669,7 @@ extern "C"
         plan->desc.gemmlowp_offset     = desc->gemmlowp_offset;
         plan->desc.gemmlowp_min_bound  = desc->gemmlowp_min_bound;
         plan->desc.gemmlowp_max_bound  = desc->gemmlowp_max_bound;
+        plan->desc.dequantize_scale    = desc->dequantize_scale;
         apply_quant_fields(plan, &plan->desc);
         if (plan->core.per_channel)
         {
@@ -632,7 +690,7 @@ extern "C"
         GemmOperands op{};
         op.a    = reinterpret_cast<const void *>(uintptr_t(256));
         op.bt   = plan->core.d_bt;
-        op.lda  = plan->desc.lda;
+        op.lda  = round_up(plan->desc.lda, 16); // an unaligned pitch runs on a 16-byte-pitch copy of A
         op.ldbt = plan->core.ldbt;
         op.M    = plan->desc.M;
         op.N    = plan->desc.N;
@@ -1365,10 +1423,80 @@ extern "C"
         }
         return fold + (plan->skip_im2col ? 0 : 1) + 1 + (plan->core.b_off != 0 ? 1 : 0);
     }
+    cugl_status cugl_conv2d_update_quantization(cugl_conv_plan *plan, const cugl_conv_desc *desc)
+    {
+        if (plan == nullptr || desc == nullptr)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_update_quantization: NULL argument");
+        }
+        const cugl_conv_desc &o = plan->desc;
+        if (desc->B != o.B || desc->H != o.H || desc->W != o.W || desc->C != o.C || desc->OFM != o.OFM || desc->kh != o.kh ||
+            desc->kw != o.kw || desc->stride_x != o.stride_x || desc->stride_y != o.stride_y ||
+            desc->pad_left != o.pad_left || desc->pad_right != o.pad_right || desc->pad_top != o.pad_top ||
+            desc->pad_bottom != o.pad_bottom || desc->dil_x != o.dil_x || desc->dil_y != o.dil_y ||
+            desc->src_dtype != o.src_dtype || desc->w_dtype != o.w_dtype ||
+            desc->is_quantized_per_channel != o.is_quantized_per_channel || desc->has_bias != o.has_bias)
+        {
+            return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
+                        "cugl_conv2d_update_quantization: geometry, types and per-channel kind must not change");
+        }
+        cugl_status code;
+        const char *why = validate_conv(desc, &code);
+        if (why != nullptr)
+        {
+            return fail(plan->ctx, code, std::string("cugl_conv2d_update_quantization: ") + why);
+        }
+        // the lowering was chosen for symmetric or asymmetric weights; a weights zero point appearing later would
+        // need the row sums the implicit kernel does not compute
+        if ((desc->w_zero_point != 0) != (o.w_zero_point != 0))
+        {
+            return fail(plan->ctx, CUGL_UNSUPPORTED_CONFIG,
+                        "cugl_conv2d_update_quantization: the weights zero point may not change between zero and non-zero");
+        }
+        const bool zp_changed = desc->src_zero_point != o.src_zero_point;
+        plan->desc.src_zero_point      = desc->src_zero_point;
+        plan->desc.w_zero_point        = desc->w_zero_point;
+        plan->desc.gemmlowp_multiplier = desc->gemmlowp_multiplier;
+        plan->desc.gemmlowp_shift      = desc->gemmlowp_shift;
+        plan->desc.dst_zero_point      = desc->dst_zero_point;
+        plan->desc.min_bound           = desc->min_bound;
+        plan->desc.max_bound           = desc->max_bound;
+        GemmCore &c     = plan->core;
+        c.a_off         = -desc->src_zero_point;
+        c.b_off         = -desc->w_zero_point;
+        c.mult          = desc->gemmlowp_multiplier;
+        c.shift         = desc->gemmlowp_shift;
+        c.result_offset = desc->dst_zero_point;
+        c.min_bound     = desc->min_bound;
+        c.max_bound     = desc->max_bound;
+        if (c.per_channel)
+        {
+            plan->h_mults.assign(desc->h_gemmlowp_multipliers, desc->h_gemmlowp_multipliers + desc->OFM);
+            plan->h_shifts.assign(desc->h_gemmlowp_shifts, desc->h_gemmlowp_shifts + desc->OFM);
+        }
+        CUGL_TRY(c.upload_stage_vectors(plan->h_mults.data(), plan->h_shifts.data()));
+        if (zp_changed && plan->d_pad != nullptr)
+        {
+            // out-of-image taps read the input zero point from the pad buffer
+            CUGL_TRY(cugl_memset(plan->ctx, plan->d_pad, desc->src_zero_point & 0xff, kConvPadBytes));
+        }
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_transpose_batched(cugl_context *ctx, const void *d_src, void *d_dst, int32_t rows, int32_t cols,
+                                       int32_t batch)
+    {
+        if (ctx == nullptr || d_src == nullptr || d_dst == nullptr || rows < 1 || cols < 1 || batch < 1 || batch > 65535)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_transpose_batched: bad argument");
+        }
+        return launch_transpose_bytes(ctx, d_src, rows, cols, d_dst, batch);
+    }
+
     // ---- temporary workspaces (MemoryRequirements with lifetime Temporary, arm_compute/core/experimental/Types.h:89-125)
     size_t cugl_gemmlowp_plan_temp_bytes(const cugl_gemm_plan *plan)
     {
-        return plan != nullptr ? plan->core.rowsum_bytes() : 0;
+        return plan != nullptr ? plan->core.rowsum_bytes() + plan->core.tmp_a_bytes() : 0;
     }
 
     cugl_status cugl_gemmlowp_plan_bind_temp(cugl_gemm_plan *plan, void *d_ws, size_t bytes)
@@ -1377,12 +1505,16 @@ extern "C"
         {
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_bind_temp: NULL plan");
         }
-        if (d_ws != nullptr && ((reinterpret_cast<uintptr_t>(d_ws) & 255) != 0 || bytes < plan->core.rowsum_bytes()))
+        if (d_ws != nullptr && ((reinterpret_cast<uintptr_t>(d_ws) & 255) != 0 ||
+                                bytes < plan->core.rowsum_bytes() + plan->core.tmp_a_bytes()))
         {
             return fail(plan->ctx, CUGL_INVALID_ARGUMENT,
                         "cugl_gemmlowp_plan_bind_temp: workspace must be 256-byte aligned and hold cugl_gemmlowp_plan_temp_bytes");
         }
-        plan->core.d_rowsum_bound = static_cast<int32_t *>(d_ws);
+        plan->core.d_rowsum_bound = (d_ws != nullptr && plan->core.rowsum_bytes() != 0) ? static_cast<int32_t *>(d_ws) : nullptr;
+        plan->core.d_tmp_a_bound  = (d_ws != nullptr && plan->core.tmp_a_bytes() != 0)
+                                        ? static_cast<uint8_t *>(d_ws) + plan->core.rowsum_bytes()
+                                        : nullptr;
         return CUGL_SUCCESS;
     }
 

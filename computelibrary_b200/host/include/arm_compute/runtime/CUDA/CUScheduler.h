@@ -24,4 +24,17 @@ private:
 
 // cugl status -> arm_compute::Status (text from cugl_last_error_string)
 Status cu_status(cugl_status s, cugl_context *ctx, const char *where);
+
+// ARM_COMPUTE_ERROR_THROW_ON / ARM_COMPUTE_ERROR_ON_MSG are compiled out of builds without asserts
+// (arm_compute/core/Error.h:407-460) together with their argument.  Calls into the C ABI have side effects and CUDA
+// errors must surface in every build, so the CUDA functions use these always-active forms.
+#define CU_THROW_ON(status) (status).throw_if_error()
+#define CU_ERROR_IF(cond, msg)      \
+    do                              \
+    {                               \
+        if (cond)                   \
+        {                           \
+            ARM_COMPUTE_ERROR(msg); \
+        }                           \
+    } while (0)
 } // namespace arm_compute

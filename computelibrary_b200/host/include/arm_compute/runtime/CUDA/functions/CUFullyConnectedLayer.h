@@ -10,28 +10,25 @@
 // A fully connected layer is the 1x1 convolution of a 1x1 image with num_inputs channels, so the function runs on
 // the convolution plan of the C ABI (plain-GEMM lowering).
 #pragma once
-#include "arm_compute/core/TensorInfo.h"
+#include "arm_compute/core/ITensor.h"
+#include "arm_compute/core/Types.h"
+#include "arm_compute/function_info/ActivationLayerInfo.h"
+#include "arm_compute/function_info/FullyConnectedLayerInfo.h"
 #include "arm_compute/function_info/GEMMInfo.h"
 #include "arm_compute/runtime/IFunction.h"
+#include "arm_compute/runtime/IMemoryManager.h"
+#include "arm_compute/runtime/IWeightsManager.h"
 
 #include <memory>
 
 namespace arm_compute
 {
-struct FullyConnectedLayerInfo
-{
-    DataLayout          weights_trained_layout{DataLayout::NHWC};
-    bool                transpose_weights{true};
-    bool                are_weights_reshaped{false};
-    bool                retain_internal_weights{false};
-    bool                enable_fast_math{false};
-    ActivationLayerInfo activation_info{};
-};
-
 class CUFullyConnectedLayer : public IFunction
 {
 public:
-    CUFullyConnectedLayer();
+    CUFullyConnectedLayer(std::shared_ptr<IMemoryManager> memory_manager = nullptr, IWeightsManager *weights_manager = nullptr);
+    CUFullyConnectedLayer(const CUFullyConnectedLayer &)            = delete;
+    CUFullyConnectedLayer &operator=(const CUFullyConnectedLayer &) = delete;
     ~CUFullyConnectedLayer();
     void          configure(const ITensor *input, const ITensor *weights, const ITensor *biases, ITensor *output,
                             FullyConnectedLayerInfo fc_info = FullyConnectedLayerInfo(),

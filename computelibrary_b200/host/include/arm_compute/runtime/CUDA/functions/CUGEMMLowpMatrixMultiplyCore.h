@@ -5,9 +5,13 @@
 // QSYMM8, QSYMM8_PER_CHANNEL; src2 S32 or none; dst QASYMM8 / QASYMM8_SIGNED (QUANTIZE_DOWN_FIXEDPOINT stage) or
 // S32 (stage NONE).  The F32 / F16 dequantising rows are not implemented.
 #pragma once
-#include "arm_compute/core/TensorInfo.h"
+#include "arm_compute/core/ITensor.h"
+#include "arm_compute/core/Types.h"
+#include "arm_compute/function_info/ActivationLayerInfo.h"
 #include "arm_compute/function_info/GEMMInfo.h"
 #include "arm_compute/runtime/IFunction.h"
+#include "arm_compute/runtime/IMemoryManager.h"
+#include "arm_compute/runtime/IWeightsManager.h"
 
 #include <memory>
 
@@ -15,9 +19,6 @@ struct cugl_gemm_plan;
 
 namespace arm_compute
 {
-class IMemoryManager;
-class IWeightsManager;
-
 class CUGEMMLowpMatrixMultiplyCore : public IFunction
 {
 public:

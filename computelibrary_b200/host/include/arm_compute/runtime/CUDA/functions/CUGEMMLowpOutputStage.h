@@ -1,9 +1,14 @@
 // CUDA counterpart of NEGEMMLowpOutputStage (arm_compute/runtime/NEON/functions/NEGEMMLowpOutputStage.h:85-102):
 // S32 [N, M] (+ S32 bias [N]) -> QASYMM8 / QASYMM8_SIGNED with QUANTIZE_DOWN_FIXEDPOINT.
 #pragma once
-#include "arm_compute/core/TensorInfo.h"
+#include "arm_compute/core/ITensor.h"
+#include "arm_compute/core/Types.h"
+#include "arm_compute/function_info/ActivationLayerInfo.h"
 #include "arm_compute/function_info/GEMMInfo.h"
 #include "arm_compute/runtime/IFunction.h"
+#include "arm_compute/runtime/IMemoryManager.h"
+#include "arm_compute/runtime/IWeightsManager.h"
+#include "arm_compute/runtime/CUDA/CUTensor.h"
 
 namespace arm_compute
 {
@@ -16,9 +21,7 @@ public:
     void          run() override;
 
 private:
-    const ITensor          *_input{nullptr};
-    const ITensor          *_bias{nullptr};
-    ITensor                *_output{nullptr};
+    CUOperand               _input{}, _bias{}, _output{};
     GEMMLowpOutputStageInfo _info{};
     void                   *_d_mults{nullptr}; // per-channel vectors on the device
     void                   *_d_shifts{nullptr};

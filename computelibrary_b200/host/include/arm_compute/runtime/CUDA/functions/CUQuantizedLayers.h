@@ -7,9 +7,13 @@
 // QASYMM8 (uint8), NHWC only; results equal the library's scalar oracle (dequantize, float operator, quantize)
 // bit for bit, softmax within one step.  run() enqueues on the scheduler's stream and does not block.
 #pragma once
-#include "arm_compute/core/TensorInfo.h"
+#include "arm_compute/core/ITensor.h"
+#include "arm_compute/core/Types.h"
+#include "arm_compute/function_info/ActivationLayerInfo.h"
 #include "arm_compute/function_info/GEMMInfo.h"
 #include "arm_compute/runtime/IFunction.h"
+#include "arm_compute/runtime/IMemoryManager.h"
+#include "arm_compute/runtime/IWeightsManager.h"
 
 namespace arm_compute
 {

@@ -1,8 +1,9 @@
 #include "arm_compute/runtime/CUDA/functions/CUFullyConnectedLayer.h"
 
-#include "arm_compute/runtime/CUDA/CUScheduler.h"
-#include "arm_compute/runtime/CUDA/CUTensor.h"
-#include "arm_compute/runtime/CUDA/functions/CUGEMMConvolutionLayer.h"
+#include "arm_compute/core/Utils.h"
+#include "arm_compute/core/utils/quantization/AsymmHelpers.h"
+
+#include "CUHelpers.h"
 
 #include <tuple>
 #include <vector>
@@ -13,9 +14,9 @@ namespace
 {
 struct FcSetup
 {
-    cugl_conv_desc       desc{};
-    std::vector<int32_t> mults, shifts;
-    size_t               num_inputs{0}, num_outputs{0};
+    cugl_conv_desc          desc{};
+    GEMMLowpOutputStageInfo stage{}; // owns the per-channel vectors the descriptor points into
+    size_t                  num_inputs{0}, num_outputs{0};
 };
 
 Status make_fc(const ITensorInfo *input, const ITensorInfo *weights, const ITensorInfo *biases, const ITensorInfo *output,
@@ -37,6 +38,14 @@ Status make_fc(const ITensorInfo *input, const ITensorInfo *weights, const ITens
     const size_t flat          = is_conv_input ? input->dimension(0) * input->dimension(1) * input->dimension(2) : input->dimension(0);
     const size_t batch         = is_conv_input ? input->tensor_shape().total_size_upper(3) : input->tensor_shape().total_size_upper(1);
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(flat != out.num_inputs, "input features and weights rows differ");
+    // CpuFullyConnected.cpp:290-304: when a convolution output with more than one pixel feeds the layer and the
+    // weights were trained in the other layout, the reference permutes the weights (CpuConvertFullyConnectedWeights)
+    const size_t pixels = !is_conv_input ? 1
+                          : (input->data_layout() == DataLayout::NHWC ? input->dimension(1) * input->dimension(2)
+                                                                      : input->dimension(0) * input->dimension(1));
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(pixels > 1 && fc.weights_trained_layout != input->data_layout(),
+                                    "weights trained in another layout than the 4-D input's: the weight permutation of "
+                                    "CpuConvertFullyConnectedWeights is not implemented (set weights_trained_layout)");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->dimension(0) != out.num_outputs || output->tensor_shape().total_size_upper(1) != batch,
                                     "output must be [num_outputs, batch]");
     if (biases != nullptr)
@@ -61,19 +70,15 @@ Status make_fc(const ITensorInfo *input, const ITensorInfo *weights, const ITens
     d.src_zero_point           = iq.uniform().offset; // true zero points; the plan negates them (CpuFullyConnected.cpp:97-102)
     d.w_zero_point             = per_channel ? 0 : wq.uniform().offset;
     d.is_quantized_per_channel = per_channel ? 1 : 0;
-    const size_t n_scales      = per_channel ? out.num_outputs : 1;
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(wq.scale().size() < n_scales, "per-channel weights need num_outputs scales");
-    out.mults.resize(n_scales);
-    out.shifts.resize(n_scales);
-    if (cugl_calculate_quantized_multipliers(iq.scale()[0], wq.scale().data(), static_cast<int>(n_scales), oq.scale()[0],
-                                             out.mults.data(), out.shifts.data()) != CUGL_SUCCESS)
-    {
-        return Status(ErrorCode::RUNTIME_ERROR, cugl_last_error_string(nullptr));
-    }
-    d.gemmlowp_multiplier    = out.mults[0];
-    d.gemmlowp_shift         = out.shifts[0];
-    d.h_gemmlowp_multipliers = out.mults.data();
-    d.h_gemmlowp_shifts      = out.shifts.data();
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(per_channel && wq.scale().size() < out.num_outputs, "per-channel weights need num_outputs scales");
+    out.stage.type                     = GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT;
+    out.stage.is_quantized_per_channel = per_channel;
+    out.stage.gemmlowp_offset          = oq.uniform().offset;
+    ARM_COMPUTE_RETURN_ON_ERROR(quantization::calculate_quantized_multipliers(iq, wq, oq, out.stage)); // CpuFullyConnected.cpp:165-170
+    d.gemmlowp_multiplier    = out.stage.gemmlowp_multiplier;
+    d.gemmlowp_shift         = out.stage.gemmlowp_shift;
+    d.h_gemmlowp_multipliers = out.stage.gemmlowp_multipliers.data();
+    d.h_gemmlowp_shifts      = out.stage.gemmlowp_shifts.data();
     d.dst_zero_point         = oq.uniform().offset;
     int32_t lo = dt == DataType::QASYMM8 ? 0 : -128, hi = dt == DataType::QASYMM8 ? 255 : 127;
     if (fc.activation_info.enabled())
@@ -82,7 +87,7 @@ Status make_fc(const ITensorInfo *input, const ITensorInfo *weights, const ITens
         const F f = fc.activation_info.activation();
         ARM_COMPUTE_RETURN_ERROR_ON_MSG(f != F::RELU && f != F::BOUNDED_RELU && f != F::LU_BOUNDED_RELU,
                                         "only RELU, BOUNDED_RELU and LU_BOUNDED_RELU can be fused");
-        std::tie(lo, hi) = cu_quantized_activation_min_max(fc.activation_info, dt, oq.uniform());
+        std::tie(lo, hi) = get_quantized_activation_min_max(fc.activation_info, dt, oq.uniform());
     }
     d.min_bound = lo;
     d.max_bound = hi;
@@ -98,18 +103,19 @@ Status make_fc(const ITensorInfo *input, const ITensorInfo *weights, const ITens
 
 struct CUFullyConnectedLayer::Impl
 {
-    const ITensor          *input{nullptr};
-    const ITensor          *weights{nullptr};
-    const ITensor          *biases{nullptr};
-    ITensor                *output{nullptr};
+    CUOperand               input{}, weights{}, biases{}, output{};
     cugl_conv_plan         *plan{nullptr};
     FullyConnectedLayerInfo fc{};
     size_t                  num_inputs{0}, num_outputs{0};
     bool                    is_prepared{false};
 };
 
-CUFullyConnectedLayer::CUFullyConnectedLayer() : _impl(std::make_unique<Impl>())
+CUFullyConnectedLayer::CUFullyConnectedLayer(std::shared_ptr<IMemoryManager> memory_manager, IWeightsManager *weights_manager)
+    : _impl(std::make_unique<Impl>())
 {
+    // a fully connected layer on the plain-GEMM lowering needs no temporary memory (symmetric or per-tensor
+    // weights alike: the row sums of a [batch, num_inputs] input are a few KB owned by the plan)
+    ARM_COMPUTE_UNUSED(memory_manager, weights_manager);
 }
 
 CUFullyConnectedLayer::~CUFullyConnectedLayer()
@@ -133,23 +139,23 @@ void CUFullyConnectedLayer::configure(const ITensor *input, const ITensor *weigh
 {
     ARM_COMPUTE_ERROR_ON_NULLPTR(input, weights, output);
     FcSetup s;
-    ARM_COMPUTE_ERROR_THROW_ON(make_fc(input->info(), weights->info(), biases != nullptr ? biases->info() : nullptr,
+    CU_THROW_ON(make_fc(input->info(), weights->info(), biases != nullptr ? biases->info() : nullptr,
                                        output->info(), fc_info, weights_info, s));
     if (_impl->plan != nullptr)
     {
         cugl_conv2d_plan_destroy(_impl->plan);
         _impl->plan = nullptr;
     }
-    _impl->input       = input;
-    _impl->weights     = weights;
-    _impl->biases      = biases;
-    _impl->output      = output;
+    _impl->input.set(input);
+    _impl->weights.set(weights);
+    _impl->biases.set(biases);
+    _impl->output.set(output);
     _impl->fc          = fc_info;
     _impl->num_inputs  = s.num_inputs;
     _impl->num_outputs = s.num_outputs;
     _impl->is_prepared = false;
     cugl_context *ctx  = CUScheduler::get().context();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_conv2d_plan_create(ctx, &s.desc, &_impl->plan), ctx, "CUFullyConnectedLayer::configure"));
+    CU_THROW_ON(cu_status(cugl_conv2d_plan_create(ctx, &s.desc, &_impl->plan), ctx, "CUFullyConnectedLayer::configure"));
 }
 
 void CUFullyConnectedLayer::prepare()
@@ -158,27 +164,28 @@ void CUFullyConnectedLayer::prepare()
     {
         return;
     }
-    ARM_COMPUTE_ERROR_ON_MSG(_impl->plan == nullptr, "prepare before configure");
+    CU_ERROR_IF(_impl->plan == nullptr, "prepare before configure");
     cugl_context *ctx = CUScheduler::get().context();
-    const void   *w   = cu_device_ptr(_impl->weights);
+    CU_ERROR_IF(!cu::is_dense(*_impl->weights.tensor()->info()), "CUFullyConnectedLayer: the weights tensor must be dense (no padding)");
+    const void   *w   = _impl->weights.device(true);
     void         *tmp = nullptr;
     if (!_impl->fc.transpose_weights)
     {
         // weights arrive as [num_inputs][num_outputs] (num_outputs contiguous): bring them to one row per output
         const size_t bytes = _impl->num_inputs * _impl->num_outputs;
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_malloc(ctx, bytes, &tmp), ctx, "CUFullyConnectedLayer::prepare"));
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_weights_reshape_nhwc(ctx, w, tmp, static_cast<int32_t>(_impl->num_outputs),
+        CU_THROW_ON(cu_status(cugl_malloc(ctx, bytes, &tmp), ctx, "CUFullyConnectedLayer::prepare"));
+        CU_THROW_ON(cu_status(cugl_weights_reshape_nhwc(ctx, w, tmp, static_cast<int32_t>(_impl->num_outputs),
                                                                        static_cast<int32_t>(_impl->num_inputs)),
                                              ctx, "CUFullyConnectedLayer::prepare"));
         w = tmp;
     }
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_conv2d_prepare(_impl->plan, w), ctx, "CUFullyConnectedLayer::prepare"));
+    CU_THROW_ON(cu_status(cugl_conv2d_prepare(_impl->plan, w), ctx, "CUFullyConnectedLayer::prepare"));
     if (tmp != nullptr)
     {
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_sync(ctx), ctx, "CUFullyConnectedLayer::prepare"));
+        CU_THROW_ON(cu_status(cugl_sync(ctx), ctx, "CUFullyConnectedLayer::prepare"));
         cugl_free(ctx, tmp);
     }
-    _impl->weights->mark_as_unused();
+    _impl->weights.tensor()->mark_as_unused();
     _impl->is_prepared = true;
 }
 
@@ -186,9 +193,13 @@ void CUFullyConnectedLayer::run()
 {
     prepare();
     cugl_context *ctx = CUScheduler::get().context();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_conv2d_run(_impl->plan, cu_device_ptr(_impl->input),
-                                                         static_cast<const int32_t *>(cu_device_ptr(_impl->biases)),
-                                                         cu_device_ptr(_impl->output)),
-                                         ctx, "CUFullyConnectedLayer::run"));
+    CU_ERROR_IF(!cu::is_dense(*_impl->input.tensor()->info()) || !cu::is_dense(*_impl->output.tensor()->info()) ||
+                    (_impl->biases.tensor() != nullptr && !cu::is_dense(*_impl->biases.tensor()->info())),
+                "CUFullyConnectedLayer: input, biases and output must be dense (no padding)");
+    void *dst = _impl->output.device(false);
+    CU_THROW_ON(cu_status(cugl_conv2d_run(_impl->plan, _impl->input.device(true),
+                                          static_cast<const int32_t *>(_impl->biases.device(true)), dst),
+                          ctx, "CUFullyConnectedLayer::run"));
+    _impl->output.download();
 }
 } // namespace arm_compute

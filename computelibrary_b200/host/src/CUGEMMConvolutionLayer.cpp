@@ -1,64 +1,68 @@
 #include "arm_compute/runtime/CUDA/functions/CUGEMMConvolutionLayer.h"
 
-#include "arm_compute/runtime/CUDA/CUScheduler.h"
-#include "arm_compute/runtime/CUDA/CUTensor.h"
+#include "arm_compute/core/Utils.h"
+#include "arm_compute/core/utils/quantization/AsymmHelpers.h"
+
+#include "CUHelpers.h"
 
 #include <algorithm>
+#include <tuple>
 #include <vector>
 
 namespace arm_compute
 {
-std::pair<int32_t, int32_t> cu_quantized_activation_min_max(const ActivationLayerInfo &act, DataType dt,
-                                                            UniformQuantizationInfo oq)
-{
-    const bool    is_signed = dt == DataType::QASYMM8_SIGNED;
-    const int     a_int     = is_signed ? quantize_qasymm8_signed(act.a(), oq) : quantize_qasymm8(act.a(), oq);
-    const int     b_int     = is_signed ? quantize_qasymm8_signed(act.b(), oq) : quantize_qasymm8(act.b(), oq);
-    const int32_t type_max  = is_signed ? 127 : 255;
-    const int32_t lo = act.activation() != ActivationLayerInfo::ActivationFunction::LU_BOUNDED_RELU
-                           ? std::min(oq.offset, type_max)
-                           : b_int;
-    const int32_t hi = act.activation() == ActivationLayerInfo::ActivationFunction::RELU ? type_max : a_int;
-    return {lo, hi};
-}
-
 namespace
 {
 struct ConvSetup
 {
-    cugl_conv_desc       desc{};
-    std::vector<int32_t> mults, shifts;
+    cugl_conv_desc          desc{};
+    GEMMLowpOutputStageInfo stage{}; // owns the per-channel vectors the descriptor points into
+    bool                    nchw{false};
 };
+
+// Index of the width / height / channel dimension for the tensor's layout (get_data_layout_dimension_index)
+struct Dims
+{
+    size_t w, h, c;
+};
+Dims dims_of(DataLayout layout)
+{
+    return layout == DataLayout::NHWC ? Dims{1, 2, 0} : Dims{0, 1, 2};
+}
 
 Status make_conv(const ITensorInfo *input, const ITensorInfo *weights, const ITensorInfo *biases,
                  const ITensorInfo *output, const PadStrideInfo &conv_info, const WeightsInfo &weights_info,
                  const Size2D &dilation, const ActivationLayerInfo &act_info, unsigned int num_groups, ConvSetup &out)
 {
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input == nullptr || weights == nullptr || output == nullptr, "nullptr tensor info");
+    ARM_COMPUTE_RETURN_ERROR_ON_NULLPTR(input, weights, output);
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(weights_info.are_reshaped(), "Weights already reshaped are not supported!");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(num_groups != 1, "Grouping (num_groups != 1) is not supported");
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input->data_layout() != DataLayout::NHWC, "the CUDA backend implements the NHWC layout");
+    const DataLayout layout = input->data_layout();
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(layout != DataLayout::NHWC && layout != DataLayout::NCHW, "layout must be NHWC or NCHW");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(weights->data_layout() != layout, "weights and input layouts differ");
+    const Dims     ix = dims_of(layout);
     const DataType dt = input->data_type();
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(dt != DataType::QASYMM8 && dt != DataType::QASYMM8_SIGNED, "input must be 8-bit quantized");
+    ARM_COMPUTE_RETURN_ERROR_ON_DATA_TYPE_CHANNEL_NOT_IN(input, 1, DataType::QASYMM8, DataType::QASYMM8_SIGNED);
     const DataType wdt = weights->data_type();
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(!is_data_type_quantized(wdt), "weights must be 8-bit quantized");
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() != dt, "output must have the input's data type");
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(weights->dimension(0) != input->dimension(0), "weights and input channel counts differ");
+    ARM_COMPUTE_RETURN_ERROR_ON_DATA_TYPE_CHANNEL_NOT_IN(weights, 1, DataType::QASYMM8, DataType::QASYMM8_SIGNED,
+                                                         DataType::QSYMM8_PER_CHANNEL);
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(weights->dimension(ix.c) != input->dimension(ix.c), "weights and input channel counts differ");
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(conv_info.round() != DimensionRoundingType::FLOOR, "only FLOOR rounding is implemented");
     if (biases != nullptr)
     {
-        ARM_COMPUTE_RETURN_ERROR_ON_MSG(biases->data_type() != DataType::S32, "biases must be S32 for quantized convolution");
+        ARM_COMPUTE_RETURN_ERROR_ON_DATA_TYPE_CHANNEL_NOT_IN(biases, 1, DataType::S32);
         ARM_COMPUTE_RETURN_ERROR_ON_MSG(biases->num_dimensions() > 1 || biases->dimension(0) != weights->dimension(3),
                                         "biases must be a vector of OFM elements");
     }
+    out.nchw          = layout == DataLayout::NCHW;
     cugl_conv_desc &d = out.desc;
     d                 = cugl_conv_desc{};
-    d.C               = static_cast<int32_t>(input->dimension(0));
-    d.W               = static_cast<int32_t>(input->dimension(1));
-    d.H               = static_cast<int32_t>(input->dimension(2));
+    d.C               = static_cast<int32_t>(input->dimension(ix.c));
+    d.W               = static_cast<int32_t>(input->dimension(ix.w));
+    d.H               = static_cast<int32_t>(input->dimension(ix.h));
     d.B               = static_cast<int32_t>(input->tensor_shape().total_size_upper(3));
-    d.kw              = static_cast<int32_t>(weights->dimension(1));
-    d.kh              = static_cast<int32_t>(weights->dimension(2));
+    d.kw              = static_cast<int32_t>(weights->dimension(ix.w));
+    d.kh              = static_cast<int32_t>(weights->dimension(ix.h));
     d.OFM             = static_cast<int32_t>(weights->dimension(3));
     d.stride_x        = static_cast<int32_t>(conv_info.stride().first);
     d.stride_y        = static_cast<int32_t>(conv_info.stride().second);
@@ -73,32 +77,30 @@ Status make_conv(const ITensorInfo *input, const ITensorInfo *weights, const ITe
     const QuantizationInfo iq = input->quantization_info(), wq = weights->quantization_info();
     const QuantizationInfo oq = output->total_size() == 0 ? iq : output->quantization_info();
     ARM_COMPUTE_RETURN_ERROR_ON_MSG(iq.scale().empty() || wq.scale().empty() || oq.scale().empty(), "missing quantization scale");
-    const bool per_channel = is_data_type_quantized_per_channel(wdt);
-    d.src_zero_point       = iq.uniform().offset; // true zero points: negated inside the plan (CpuGemmConv2d.cpp:266-280)
-    d.w_zero_point         = per_channel ? 0 : wq.uniform().offset;
+    const bool per_channel     = is_data_type_quantized_per_channel(wdt);
+    d.src_zero_point           = iq.uniform().offset; // true zero points: negated inside the plan (CpuGemmConv2d.cpp:266-280)
+    d.w_zero_point             = per_channel ? 0 : wq.uniform().offset;
     d.is_quantized_per_channel = per_channel ? 1 : 0;
-    const size_t n_scales      = per_channel ? static_cast<size_t>(d.OFM) : 1;
-    ARM_COMPUTE_RETURN_ERROR_ON_MSG(wq.scale().size() < n_scales, "per-channel weights need OFM scales");
-    out.mults.resize(n_scales);
-    out.shifts.resize(n_scales);
-    if (cugl_calculate_quantized_multipliers(iq.scale()[0], wq.scale().data(), static_cast<int>(n_scales), oq.scale()[0],
-                                             out.mults.data(), out.shifts.data()) != CUGL_SUCCESS)
-    {
-        return Status(ErrorCode::RUNTIME_ERROR, cugl_last_error_string(nullptr));
-    }
-    d.gemmlowp_multiplier    = out.mults[0];
-    d.gemmlowp_shift         = out.shifts[0];
-    d.h_gemmlowp_multipliers = out.mults.data();
-    d.h_gemmlowp_shifts      = out.shifts.data();
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(per_channel && wq.scale().size() < static_cast<size_t>(d.OFM),
+                                    "per-channel weights need OFM scales");
+    // the library's own multiplier derivation (src/core/utils/quantization/AsymmHelpers.cpp:117-152)
+    out.stage.type                     = GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT;
+    out.stage.is_quantized_per_channel = per_channel;
+    out.stage.gemmlowp_offset          = oq.uniform().offset;
+    ARM_COMPUTE_RETURN_ON_ERROR(quantization::calculate_quantized_multipliers(iq, wq, oq, out.stage));
+    d.gemmlowp_multiplier    = out.stage.gemmlowp_multiplier;
+    d.gemmlowp_shift         = out.stage.gemmlowp_shift;
+    d.h_gemmlowp_multipliers = out.stage.gemmlowp_multipliers.data();
+    d.h_gemmlowp_shifts      = out.stage.gemmlowp_shifts.data();
     d.dst_zero_point         = oq.uniform().offset;
     int32_t lo = dt == DataType::QASYMM8 ? 0 : -128, hi = dt == DataType::QASYMM8 ? 255 : 127;
     if (act_info.enabled())
     {
-        using F = ActivationLayerInfo::ActivationFunction;
+        using F   = ActivationLayerInfo::ActivationFunction;
         const F f = act_info.activation();
         ARM_COMPUTE_RETURN_ERROR_ON_MSG(f != F::RELU && f != F::BOUNDED_RELU && f != F::LU_BOUNDED_RELU,
                                         "only RELU, BOUNDED_RELU and LU_BOUNDED_RELU can be fused");
-        std::tie(lo, hi) = cu_quantized_activation_min_max(act_info, dt, oq.uniform());
+        std::tie(lo, hi) = get_quantized_activation_min_max(act_info, dt, oq.uniform()); // src/core/Utils.cpp:442-460
     }
     d.min_bound = lo;
     d.max_bound = hi;
@@ -112,10 +114,12 @@ Status make_conv(const ITensorInfo *input, const ITensorInfo *weights, const ITe
     cugl_conv2d_out_dims(&d, &wo, &ho);
     if (output->total_size() != 0)
     {
-        ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->dimension(0) != static_cast<size_t>(d.OFM) ||
-                                            output->dimension(1) != static_cast<size_t>(wo) ||
-                                            output->dimension(2) != static_cast<size_t>(ho),
-                                        "output shape must be [OFM, Wo, Ho, B]");
+        ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_type() != dt, "output must have the input's data type");
+        ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->data_layout() != layout, "output and input layouts differ");
+        ARM_COMPUTE_RETURN_ERROR_ON_MSG(output->dimension(ix.c) != static_cast<size_t>(d.OFM) ||
+                                            output->dimension(ix.w) != static_cast<size_t>(wo) ||
+                                            output->dimension(ix.h) != static_cast<size_t>(ho),
+                                        "output shape does not match the convolution");
     }
     return Status{};
 }
@@ -123,19 +127,27 @@ Status make_conv(const ITensorInfo *input, const ITensorInfo *weights, const ITe
 
 struct CUGEMMConvolutionLayer::Impl
 {
-    const ITensor  *input{nullptr};
-    const ITensor  *weights{nullptr};
-    const ITensor  *biases{nullptr};
-    ITensor        *output{nullptr};
-    cugl_conv_plan *plan{nullptr};
-    bool            is_prepared{false};
+    explicit Impl(std::shared_ptr<IMemoryManager> mm) : memory_group(std::move(mm)) {}
+    MemoryGroup            memory_group;
+    CUOperand              input{}, weights{}, biases{}, output{};
+    PadStrideInfo          conv_info{};
+    Size2D                 dilation{1U, 1U};
+    ActivationLayerInfo    act_info{};
+    cugl_conv_plan        *plan{nullptr};
+    cu::TemporaryWorkspace workspace{};
+    // NCHW: the plan works on NHWC copies of the input and of the output that live in the workspace, behind the
+    // plan's own temporaries
+    bool   nchw{false};
+    size_t plan_temp{0}, in_bytes{0}, out_bytes{0};
+    int    B{0}, C{0}, HW{0}, OFM{0}, HoWo{0}, khkw{0};
+    bool   is_prepared{false};
 };
 
 CUGEMMConvolutionLayer::CUGEMMConvolutionLayer(const std::shared_ptr<IMemoryManager> &memory_manager,
                                                IWeightsManager                       *weights_manager)
-    : _impl(std::make_unique<Impl>())
+    : _impl(std::make_unique<Impl>(memory_manager))
 {
-    ARM_COMPUTE_UNUSED(memory_manager, weights_manager);
+    ARM_COMPUTE_UNUSED(weights_manager); // the weights are re-laid out on the device inside the plan
 }
 
 CUGEMMConvolutionLayer::~CUGEMMConvolutionLayer()
@@ -163,20 +175,50 @@ void CUGEMMConvolutionLayer::configure(const ITensor *input, const ITensor *weig
     ARM_COMPUTE_UNUSED(enable_fast_math);
     ARM_COMPUTE_ERROR_ON_NULLPTR(input, weights, output);
     ConvSetup s;
-    ARM_COMPUTE_ERROR_THROW_ON(make_conv(input->info(), weights->info(), biases != nullptr ? biases->info() : nullptr,
-                                         output->info(), conv_info, weights_info, dilation, act_info, num_groups, s));
+    CU_THROW_ON(make_conv(input->info(), weights->info(), biases != nullptr ? biases->info() : nullptr, output->info(),
+                          conv_info, weights_info, dilation, act_info, num_groups, s));
     if (_impl->plan != nullptr)
     {
         cugl_conv2d_plan_destroy(_impl->plan);
         _impl->plan = nullptr;
     }
-    _impl->input       = input;
-    _impl->weights     = weights;
-    _impl->biases      = biases;
-    _impl->output      = output;
+    _impl->input.set(input);
+    _impl->weights.set(weights);
+    _impl->biases.set(biases);
+    _impl->output.set(output);
+    _impl->conv_info   = conv_info;
+    _impl->dilation    = dilation;
+    _impl->act_info    = act_info;
     _impl->is_prepared = false;
     cugl_context *ctx  = CUScheduler::get().context();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_conv2d_plan_create(ctx, &s.desc, &_impl->plan), ctx, "CUGEMMConvolutionLayer::configure"));
+    CU_THROW_ON(cu_status(cugl_conv2d_plan_create(ctx, &s.desc, &_impl->plan), ctx, "CUGEMMConvolutionLayer::configure"));
+    int32_t wo = 0, ho = 0;
+    cugl_conv2d_out_dims(&s.desc, &wo, &ho);
+    _impl->nchw      = s.nchw;
+    _impl->B         = s.desc.B;
+    _impl->C         = s.desc.C;
+    _impl->HW        = s.desc.H * s.desc.W;
+    _impl->OFM       = s.desc.OFM;
+    _impl->HoWo      = wo * ho;
+    _impl->khkw      = s.desc.kh * s.desc.kw;
+    _impl->plan_temp = (cugl_conv2d_plan_temp_bytes(_impl->plan) + 255) / 256 * 256;
+    _impl->in_bytes  = s.nchw ? (static_cast<size_t>(_impl->B) * _impl->C * _impl->HW + 255) / 256 * 256 : 0;
+    _impl->out_bytes = s.nchw ? (static_cast<size_t>(_impl->B) * _impl->OFM * _impl->HoWo + 255) / 256 * 256 : 0;
+    // Temporary-lifetime memory (im2col matrix, folded input, row sums, NHWC copies): one slot managed by the
+    // memory group, the protocol of CpuGemmConv2d's Im2ColOutput / GemmOutput workspace slots
+    _impl->workspace.configure(_impl->memory_group, _impl->plan_temp + _impl->in_bytes + _impl->out_bytes);
+}
+
+void CUGEMMConvolutionLayer::update_quantization_parameters()
+{
+    CU_ERROR_IF(_impl->plan == nullptr, "update_quantization_parameters before configure");
+    ConvSetup s;
+    CU_THROW_ON(make_conv(_impl->input.tensor()->info(), _impl->weights.tensor()->info(),
+                          _impl->biases.tensor() != nullptr ? _impl->biases.tensor()->info() : nullptr,
+                          _impl->output.tensor()->info(), _impl->conv_info, WeightsInfo(), _impl->dilation, _impl->act_info, 1, s));
+    cugl_context *ctx = CUScheduler::get().context();
+    CU_THROW_ON(cu_status(cugl_conv2d_update_quantization(_impl->plan, &s.desc), ctx,
+                          "CUGEMMConvolutionLayer::update_quantization_parameters"));
 }
 
 void CUGEMMConvolutionLayer::prepare()
@@ -185,20 +227,60 @@ void CUGEMMConvolutionLayer::prepare()
     {
         return;
     }
-    ARM_COMPUTE_ERROR_ON_MSG(_impl->plan == nullptr, "prepare before configure");
+    CU_ERROR_IF(_impl->plan == nullptr, "prepare before configure");
+    CU_ERROR_IF(!cu::is_dense(*_impl->weights.tensor()->info()), "CUGEMMConvolutionLayer: the weights tensor must be dense (no padding)");
     cugl_context *ctx = CUScheduler::get().context();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_conv2d_prepare(_impl->plan, cu_device_ptr(_impl->weights)), ctx, "CUGEMMConvolutionLayer::prepare"));
-    _impl->weights->mark_as_unused();
+    const void   *w   = _impl->weights.device(true);
+    void         *tmp = nullptr;
+    if (_impl->nchw)
+    {
+        // [OFM][C][kh*kw] -> [OFM][kh*kw][C]: the K-major operand the plan expects
+        const size_t bytes = static_cast<size_t>(_impl->OFM) * _impl->C * _impl->khkw;
+        CU_THROW_ON(cu_status(cugl_malloc(ctx, bytes, &tmp), ctx, "CUGEMMConvolutionLayer::prepare"));
+        CU_THROW_ON(cu_status(cugl_transpose_batched(ctx, w, tmp, _impl->C, _impl->khkw, _impl->OFM), ctx,
+                              "CUGEMMConvolutionLayer::prepare"));
+        w = tmp;
+    }
+    CU_THROW_ON(cu_status(cugl_conv2d_prepare(_impl->plan, w), ctx, "CUGEMMConvolutionLayer::prepare"));
+    if (tmp != nullptr)
+    {
+        CU_THROW_ON(cu_status(cugl_sync(ctx), ctx, "CUGEMMConvolutionLayer::prepare"));
+        cugl_free(ctx, tmp);
+    }
+    _impl->weights.tensor()->mark_as_unused();
     _impl->is_prepared = true;
 }
 
 void CUGEMMConvolutionLayer::run()
 {
     prepare();
+    // the plan reads and writes dense tensors; padded ones (extend_padding after configure) are refused loudly
+    CU_ERROR_IF(!cu::is_dense(*_impl->input.tensor()->info()) || !cu::is_dense(*_impl->output.tensor()->info()) ||
+                    (_impl->biases.tensor() != nullptr && !cu::is_dense(*_impl->biases.tensor()->info())),
+                "CUGEMMConvolutionLayer: input, biases and output must be dense (no padding)");
+    MemoryGroupResourceScope scope_mg(_impl->memory_group);
     cugl_context *ctx = CUScheduler::get().context();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_conv2d_run(_impl->plan, cu_device_ptr(_impl->input),
-                                                         static_cast<const int32_t *>(cu_device_ptr(_impl->biases)),
-                                                         cu_device_ptr(_impl->output)),
-                                         ctx, "CUGEMMConvolutionLayer::run"));
+    uint8_t      *ws  = static_cast<uint8_t *>(_impl->workspace.device_ptr());
+    if (ws != nullptr && _impl->plan_temp != 0)
+    {
+        CU_THROW_ON(cu_status(cugl_conv2d_plan_bind_temp(_impl->plan, ws, _impl->plan_temp), ctx, "CUGEMMConvolutionLayer::run"));
+    }
+    const void *src = _impl->input.device(true);
+    void       *dst = _impl->output.device(false);
+    if (_impl->nchw)
+    {
+        CU_ERROR_IF(ws == nullptr, "CUGEMMConvolutionLayer: NCHW workspace missing");
+        uint8_t *in_nhwc = ws + _impl->plan_temp, *out_nhwc = in_nhwc + _impl->in_bytes;
+        CU_THROW_ON(cu_status(cugl_transpose_batched(ctx, src, in_nhwc, _impl->C, _impl->HW, _impl->B), ctx, "NCHW -> NHWC"));
+        CU_THROW_ON(cu_status(cugl_conv2d_run(_impl->plan, in_nhwc, static_cast<const int32_t *>(_impl->biases.device(true)), out_nhwc),
+                              ctx, "CUGEMMConvolutionLayer::run"));
+        CU_THROW_ON(cu_status(cugl_transpose_batched(ctx, out_nhwc, dst, _impl->HoWo, _impl->OFM, _impl->B), ctx, "NHWC -> NCHW"));
+    }
+    else
+    {
+        CU_THROW_ON(cu_status(cugl_conv2d_run(_impl->plan, src, static_cast<const int32_t *>(_impl->biases.device(true)), dst), ctx,
+                              "CUGEMMConvolutionLayer::run"));
+    }
+    _impl->output.download();
 }
 } // namespace arm_compute

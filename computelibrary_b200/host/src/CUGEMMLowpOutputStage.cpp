@@ -1,7 +1,6 @@
 #include "arm_compute/runtime/CUDA/functions/CUGEMMLowpOutputStage.h"
 
-#include "arm_compute/runtime/CUDA/CUScheduler.h"
-#include "arm_compute/runtime/CUDA/CUTensor.h"
+#include "CUHelpers.h"
 
 namespace arm_compute
 {
@@ -42,42 +41,42 @@ void CUGEMMLowpOutputStage::configure(const ITensor *input, const ITensor *bias,
                                       const GEMMLowpOutputStageInfo &info)
 {
     ARM_COMPUTE_ERROR_ON_NULLPTR(input, output);
-    ARM_COMPUTE_ERROR_THROW_ON(validate(input->info(), bias != nullptr ? bias->info() : nullptr, output->info(), info));
-    _input  = input;
-    _bias   = bias;
-    _output = output;
-    _info   = info;
+    CU_THROW_ON(validate(input->info(), bias != nullptr ? bias->info() : nullptr, output->info(), info));
+    _input.set(input);
+    _bias.set(bias);
+    _output.set(output);
+    _info = info;
     if (info.is_quantized_per_channel)
     {
         cugl_context *ctx = CUScheduler::get().context();
         const size_t  n   = input->info()->dimension(0);
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_malloc(ctx, n * 4, &_d_mults), ctx, "CUGEMMLowpOutputStage::configure"));
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_malloc(ctx, n * 4, &_d_shifts), ctx, "CUGEMMLowpOutputStage::configure"));
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_memcpy_h2d(ctx, _d_mults, info.gemmlowp_multipliers.data(), n * 4), ctx, "copy"));
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_memcpy_h2d(ctx, _d_shifts, info.gemmlowp_shifts.data(), n * 4), ctx, "copy"));
-        ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_sync(ctx), ctx, "sync"));
+        CU_THROW_ON(cu_status(cugl_malloc(ctx, n * 4, &_d_mults), ctx, "CUGEMMLowpOutputStage::configure"));
+        CU_THROW_ON(cu_status(cugl_malloc(ctx, n * 4, &_d_shifts), ctx, "CUGEMMLowpOutputStage::configure"));
+        CU_THROW_ON(cu_status(cugl_memcpy_h2d(ctx, _d_mults, info.gemmlowp_multipliers.data(), n * 4), ctx, "copy"));
+        CU_THROW_ON(cu_status(cugl_memcpy_h2d(ctx, _d_shifts, info.gemmlowp_shifts.data(), n * 4), ctx, "copy"));
+        CU_THROW_ON(cu_status(cugl_sync(ctx), ctx, "sync"));
     }
 }
 
 void CUGEMMLowpOutputStage::run()
 {
     cugl_context      *ctx = CUScheduler::get().context();
-    const ITensorInfo *in  = _input->info();
+    const ITensorInfo *in  = _input.tensor()->info();
+    const ITensorInfo *out = _output.tensor()->info();
+    void              *dst = _output.device(false);
     const int32_t      N   = static_cast<int32_t>(in->dimension(0));
     const int32_t      M   = static_cast<int32_t>(in->tensor_shape().total_size_upper(1));
     const auto stage_fn = _info.type == GEMMLowpOutputStageType::QUANTIZE_DOWN ? cugl_output_stage_quantize_down : cugl_output_stage;
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(
-        stage_fn(ctx, static_cast<const int32_t *>(cu_device_ptr(_input)),
-                          static_cast<int64_t>(in->strides_in_bytes()[1]), static_cast<const int32_t *>(cu_device_ptr(_bias)),
-                          cu_device_ptr(_output), static_cast<int64_t>(_output->info()->strides_in_bytes()[1]),
-                          _output->info()->data_type() == DataType::QASYMM8
-                              ? CUGL_U8
-                              : (_output->info()->data_type() == DataType::QSYMM16 ? CUGL_S16 : CUGL_S8),
+    CU_THROW_ON(cu_status(
+        stage_fn(ctx, static_cast<const int32_t *>(_input.device(true)),
+                          static_cast<int64_t>(in->strides_in_bytes()[1]), static_cast<const int32_t *>(_bias.device(true)),
+                          dst, static_cast<int64_t>(out->strides_in_bytes()[1]), cu::to_cugl_dtype(out->data_type()),
                           M, N,
                           static_cast<const int32_t *>(_d_mults), static_cast<const int32_t *>(_d_shifts),
                           _info.gemmlowp_multiplier, _info.gemmlowp_shift, _info.is_quantized_per_channel ? N : 1,
                           _info.gemmlowp_offset, _info.gemmlowp_min_bound, _info.gemmlowp_max_bound),
         ctx, "CUGEMMLowpOutputStage::run"));
+    _output.download();
 }
 
 CUGEMMLowpOutputStage::~CUGEMMLowpOutputStage()

@@ -85,7 +85,7 @@ Status CUPoolingLayer::validate(const ITensorInfo *input, const ITensorInfo *out
 void CUPoolingLayer::configure(ITensor *input, ITensor *output, const PoolingLayerInfo &pool_info, ITensor *indices)
 {
     ARM_COMPUTE_ERROR_ON_NULLPTR(input, output);
-    ARM_COMPUTE_ERROR_THROW_ON(validate(input->info(), output->info(), pool_info, indices != nullptr ? indices->info() : nullptr));
+    CU_THROW_ON(validate(input->info(), output->info(), pool_info, indices != nullptr ? indices->info() : nullptr));
     _input  = input;
     _output = output;
     _info   = pool_info;
@@ -95,7 +95,7 @@ void CUPoolingLayer::run()
 {
     cugl_context        *ctx = CUScheduler::get().context();
     const cugl_pool_desc d   = make_pool_desc(_input->info(), _output->info(), _info);
-    ARM_COMPUTE_ERROR_THROW_ON(
+    CU_THROW_ON(
         cu_status(cugl_pool2d_nhwc(ctx, &d, cu_device_ptr(_input), cu_device_ptr(_output)), ctx, "CUPoolingLayer::run"));
 }
 
@@ -127,7 +127,7 @@ void CUArithmeticAddition::configure(const ITensor *input1, const ITensor *input
                                      const ActivationLayerInfo &act_info)
 {
     ARM_COMPUTE_ERROR_ON_NULLPTR(input1, input2, output);
-    ARM_COMPUTE_ERROR_THROW_ON(validate(input1->info(), input2->info(), output->info(), policy, act_info));
+    CU_THROW_ON(validate(input1->info(), input2->info(), output->info(), policy, act_info));
     _input1 = input1;
     _input2 = input2;
     _output = output;
@@ -140,7 +140,7 @@ void CUArithmeticAddition::run()
     const UniformQuantizationInfo q1  = _input1->info()->quantization_info().uniform();
     const UniformQuantizationInfo q2  = _input2->info()->quantization_info().uniform();
     const UniformQuantizationInfo qo  = _output->info()->quantization_info().uniform();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(
+    CU_THROW_ON(cu_status(
         cugl_add_qasymm8(ctx, cu_device_ptr(_input1), cu_device_ptr(_input2), cu_device_ptr(_output),
                          static_cast<int64_t>(_output->info()->tensor_shape().total_size()), q1.scale, q1.offset, q2.scale,
                          q2.offset, qo.scale, qo.offset, to_cugl_activation(_act), _act.a(), _act.b()),
@@ -167,7 +167,7 @@ Status CUActivationLayer::validate(const ITensorInfo *input, const ITensorInfo *
 void CUActivationLayer::configure(ITensor *input, ITensor *output, ActivationLayerInfo activation_info)
 {
     ARM_COMPUTE_ERROR_ON_NULLPTR(input);
-    ARM_COMPUTE_ERROR_THROW_ON(validate(input->info(), output != nullptr ? output->info() : nullptr, activation_info));
+    CU_THROW_ON(validate(input->info(), output != nullptr ? output->info() : nullptr, activation_info));
     _input  = input;
     _output = output != nullptr ? output : input;
     _act    = activation_info;
@@ -178,7 +178,7 @@ void CUActivationLayer::run()
     cugl_context                 *ctx = CUScheduler::get().context();
     const UniformQuantizationInfo qi  = _input->info()->quantization_info().uniform();
     const UniformQuantizationInfo qo  = _output->info()->quantization_info().uniform();
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(
+    CU_THROW_ON(cu_status(
         cugl_activation_qasymm8(ctx, cu_device_ptr(_input), cu_device_ptr(_output),
                                 static_cast<int64_t>(_input->info()->tensor_shape().total_size()), to_cugl_activation(_act),
                                 _act.a(), _act.b(), qi.scale, qi.offset, qo.scale, qo.offset),
@@ -204,7 +204,7 @@ Status CUSoftmaxLayer::validate(const ITensorInfo *input, const ITensorInfo *out
 void CUSoftmaxLayer::configure(ITensor *input, ITensor *output, float beta, int32_t axis)
 {
     ARM_COMPUTE_ERROR_ON_NULLPTR(input, output);
-    ARM_COMPUTE_ERROR_THROW_ON(validate(input->info(), output->info(), beta, axis));
+    CU_THROW_ON(validate(input->info(), output->info(), beta, axis));
     _input  = input;
     _output = output;
     _beta   = beta;
@@ -216,7 +216,7 @@ void CUSoftmaxLayer::run()
     const UniformQuantizationInfo qi   = _input->info()->quantization_info().uniform();
     const int32_t                 cols = static_cast<int32_t>(_input->info()->dimension(0));
     const int32_t                 rows = static_cast<int32_t>(_input->info()->tensor_shape().total_size_upper(1));
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(
+    CU_THROW_ON(cu_status(
         cugl_softmax_qasymm8(ctx, cu_device_ptr(_input), cu_device_ptr(_output), rows, cols, _beta, qi.scale, qi.offset), ctx,
         "CUSoftmaxLayer::run"));
 }

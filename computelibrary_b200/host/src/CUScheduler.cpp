@@ -29,7 +29,7 @@ void CUScheduler::default_init(int device, void *stream)
     }
     cugl_context *ctx = nullptr;
     const cugl_status s = cugl_context_create(device, stream != nullptr ? stream : CUGL_STREAM_CREATE, &ctx);
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(s, nullptr, "CUScheduler::default_init"));
+    CU_THROW_ON(cu_status(s, nullptr, "CUScheduler::default_init"));
     _ctx = ctx;
 }
 
@@ -44,7 +44,7 @@ cugl_context *CUScheduler::context()
 
 void CUScheduler::sync()
 {
-    ARM_COMPUTE_ERROR_THROW_ON(cu_status(cugl_sync(context()), _ctx, "CUScheduler::sync"));
+    CU_THROW_ON(cu_status(cugl_sync(context()), _ctx, "CUScheduler::sync"));
 }
 
 CUScheduler::~CUScheduler()

@@ -53,7 +53,8 @@ typedef enum cugl_dtype
     CUGL_U8  = 0,
     CUGL_S8  = 1,
     CUGL_S32 = 2,
-    CUGL_S16 = 3 /* QSYMM16: destination of the stand-alone fixed-point output stage only */
+    CUGL_S16 = 3, /* QSYMM16: destination of the stand-alone fixed-point output stage only */
+    CUGL_F32 = 4  /* destination of the GEMM with stage NONE: the int32 result times dequantize_scale */
 } cugl_dtype;
 
 /* GEMMLowpOutputStageType (arm_compute/function_info/GEMMInfo.h:40-46).  Only NONE and
@@ -151,7 +152,7 @@ typedef struct cugl_gemm_desc
     int64_t a_batch_stride, b_batch_stride, d_batch_stride; /* bytes; b_batch_stride 0 = shared B */
     int32_t a_dtype;     /* CUGL_U8 | CUGL_S8 */
     int32_t b_dtype;     /* CUGL_U8 | CUGL_S8 */
-    int32_t dst_dtype;   /* CUGL_U8 | CUGL_S8 with a FIXEDPOINT stage, CUGL_S32 with stage NONE */
+    int32_t dst_dtype;   /* CUGL_U8 | CUGL_S8 with a quantize-down stage; CUGL_S32 or CUGL_F32 with stage NONE */
     int32_t a_offset;    /* a->quantization_info().uniform().offset AS PASSED to the core (it is added);
                             library callers pass the negated zero point (CpuGemmConv2d.cpp:266-280) */
     int32_t b_offset;    /* likewise; must be 0 for per-channel B with a signed dst
@@ -167,6 +168,11 @@ typedef struct cugl_gemm_desc
     int32_t gemmlowp_max_bound;
     int32_t has_bias;                 /* c != nullptr: S32 [N], only with an output stage */
     int32_t reshape_b_only_on_first_run; /* GEMMInfo flag: B (and its column sums) are constant after prepare */
+    int32_t accumulate;  /* GEMMInfo::accumulate(): stage NONE only, dst += result instead of dst = result
+                            (CpuGemmLowpMatrixMultiplyCore.cpp:393-401) */
+    float   dequantize_scale; /* dst_dtype CUGL_F32: dst = float(int32 result) * dequantize_scale, the product of the
+                            two operand scales (the s8 -> f32 rows of NEGEMMLowpMatrixMultiplyCore.h:72-90;
+                            CpuGemmLowpMatrixMultiplyCore.cpp:305-320); float(x) rounds to nearest, one float multiply */
 } cugl_gemm_desc;
 
 /* static Status validate(a, b, c, output, gemm_info): pure host check, no GPU needed.
@@ -320,6 +326,12 @@ CUGL_API cugl_status cugl_im2col_nhwc(cugl_context *ctx, const void *d_src, void
 CUGL_API cugl_status cugl_weights_reshape_nhwc(cugl_context *ctx, const void *d_w, void *d_dst, int32_t K,
                                                int32_t OFM);
 
+/* batch dense matrices of rows x cols bytes, back to back, each transposed into cols x rows (blockwise through shared
+ * memory).  With rows = C, cols = H*W this is the NCHW -> NHWC permute of 8-bit images (NEPermute with
+ * PermutationVector(2, 0, 1), as CpuGemmConv2d's callers use it), with rows = H*W, cols = C the way back. */
+CUGL_API cugl_status cugl_transpose_batched(cugl_context *ctx, const void *d_src, void *d_dst, int32_t rows,
+                                            int32_t cols, int32_t batch);
+
 /* ------------------------------------------------------------------------------------------------
  * NEGEMMConvolutionLayer for 8-bit NHWC tensors
  *   src/runtime/NEON/functions/NEGEMMConvolutionLayer.cpp:60-145
@@ -372,6 +384,10 @@ CUGL_API cugl_status cugl_conv2d_plan_set_channel_major(cugl_conv_plan *plan, in
 CUGL_API cugl_status cugl_conv2d_plan_set_tile_columns(cugl_conv_plan *plan, int columns);
 /* as cugl_gemmlowp_plan_set_paired_drain, for the lowerings that run the plain GEMM kernel */
 CUGL_API cugl_status cugl_conv2d_plan_set_paired_drain(cugl_conv_plan *plan, int on);
+/* NEGEMMConvolutionLayer::update_quantization_parameters (src/runtime/NEON/functions/NEGEMMConvolutionLayer.cpp:129-131,
+ * src/cpu/operators/CpuGemmConv2d.cpp:858-908): re-reads the zero points, the multipliers / shifts, the output zero
+ * point and the clamp bounds of desc; geometry and types must be unchanged.  The prepared weights stay valid. */
+CUGL_API cugl_status cugl_conv2d_update_quantization(cugl_conv_plan *plan, const cugl_conv_desc *desc);
 /* As cugl_gemmlowp_plan_temp_bytes / _bind_temp for the convolution: row sums, the folded stem input and -- explicit
  * lowering only -- the im2col matrix (the Im2ColOutput slot of CpuGemmConv2d, src/cpu/operators/CpuGemmConv2d.h). */
 CUGL_API size_t      cugl_conv2d_plan_temp_bytes(const cugl_conv_plan *plan);

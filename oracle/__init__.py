@@ -229,6 +229,13 @@ class _Port(_Layers):
                                       int(mult.size), _i32(offset), _i32(lo), _i32(hi))
         return out
 
+    @staticmethod
+    def dequantize_s32(acc, scale, previous=None):
+        """Restates dequantize_s32 (arm_compute/core/QuantizationInfo.h:639-642) on an int32 array:
+        float32(acc) * float32(scale), one rounding each; plus one float32 addition when accumulating."""
+        r = np.asarray(acc, dtype=np.int32).astype(np.float32) * np.float32(scale)
+        return r if previous is None else (np.asarray(previous, np.float32) + r).astype(np.float32)
+
     def gemmlowp_fused_int(self, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype):
         a = np.ascontiguousarray(a)
         b = np.ascontiguousarray(b)
@@ -367,6 +374,14 @@ class _Ref(_Layers):
         fn = self.lib.ref_quantize_down_scale_s8 if out.dtype == np.int8 else self.lib.ref_quantize_down_scale_u8
         fn(_ptr(acc), _ptr(bias), _ptr(out), M, N, _ptr(mult), _ptr(shift), int(mult.size), _i32(offset), _i32(lo),
            _i32(hi))
+        return out
+
+    def dequantize_s32(self, acc, scale, previous=None):
+        """The dequantised GEMMLowp output: float(acc) * scale, added to `previous` when given."""
+        acc = np.ascontiguousarray(acc, dtype=np.int32)
+        out = np.zeros(acc.shape, np.float32) if previous is None else np.array(previous, dtype=np.float32, copy=True)
+        self.lib.ref_dequantize_s32_f32(_ptr(acc), _ptr(out), C.c_longlong(acc.size), C.c_float(scale),
+                                        0 if previous is None else 1)
         return out
 
     def conv_nchw(self, src, weights, bias, stride, pad, in_scale, in_zp, w_scales, w_zp, out_scale, out_zp):

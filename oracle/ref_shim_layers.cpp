@@ -34,6 +34,7 @@
 #include "tests/validation/Helpers.cpp"                        // NOLINT: in-place inclusion on purpose
 #include "tests/validation/reference/ActivationLayer.cpp"      // NOLINT
 #include "tests/validation/reference/ArithmeticOperations.cpp" // NOLINT
+#include "tests/validation/reference/DequantizationLayer.cpp"  // NOLINT
 #include "tests/validation/reference/PoolingLayer.cpp"         // NOLINT
 #include "tests/validation/reference/SoftmaxLayer.cpp"         // NOLINT
 
@@ -149,5 +150,27 @@ extern "C"
         std::memcpy(ts.data(), src, size_t(rows) * cols);
         SimpleTensor<uint8_t> td = reference::softmax_layer<uint8_t>(ts, beta, 0, false);
         std::memcpy(dst, td.data(), size_t(rows) * cols);
+    }
+    // The dequantised GEMMLowp output as the reference's fixture computes it (GEMMLowpFixture.h:898-921):
+    // reference::dequantization_layer<float, int32_t> of the S32 result carrying (scale, 0), then -- accumulate != 0 --
+    // reference::arithmetic_operation<float>(ADD, previous, result, SATURATE).  inout holds the previous output on
+    // entry when accumulating and the result on return.
+    void ref_dequantize_s32_f32(const int32_t *acc, float *inout, long long n, float scale, int accumulate)
+    {
+        SimpleTensor<int32_t> in{TensorShape(static_cast<size_t>(n)), DataType::S32, 1, QuantizationInfo(scale, 0)};
+        std::memcpy(in.data(), acc, sizeof(int32_t) * n);
+        SimpleTensor<float> deq = reference::dequantization_layer<float, int32_t>(in);
+        if (accumulate != 0)
+        {
+            SimpleTensor<float> prev{TensorShape(static_cast<size_t>(n)), DataType::F32, 1};
+            std::memcpy(prev.data(), inout, sizeof(float) * n);
+            SimpleTensor<float> sum{TensorShape(static_cast<size_t>(n)), DataType::F32, 1};
+            reference::arithmetic_operation<float>(reference::ArithmeticOperation::ADD, prev, deq, sum, ConvertPolicy::SATURATE);
+            std::memcpy(inout, sum.data(), sizeof(float) * n);
+        }
+        else
+        {
+            std::memcpy(inout, deq.data(), sizeof(float) * n);
+        }
     }
 }

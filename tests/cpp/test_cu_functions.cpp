@@ -3,8 +3,12 @@
 // configure -> allocate -> fill (std::mt19937) -> run -> compare with the CPU oracle (oracle/gemmlowp_oracle.c).
 //   test_cu_functions --validate   host-only checks of validate() (no GPU needed)
 //   test_cu_functions              everything, on cuda:0
+#include "arm_compute/core/Utils.h"
+#include "arm_compute/runtime/CUDA/CUAllocator.h"
 #include "arm_compute/runtime/CUDA/CUScheduler.h"
 #include "arm_compute/runtime/CUDA/CUTensor.h"
+#include "arm_compute/runtime/MemoryGroup.h"
+#include "arm_compute/runtime/Tensor.h"
 #include "arm_compute/runtime/CUDA/functions/CUFullyConnectedLayer.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMConvolutionLayer.h"
 #include "arm_compute/runtime/CUDA/functions/CUGEMMLowpMatrixMultiplyCore.h"
@@ -98,8 +102,7 @@ static void test_validate()
     const TensorInfo b_bad(TensorShape(128U, 255U), 1, DataType::QASYMM8);
     CHECK(!bool(CUGEMMLowpMatrixMultiplyCore::validate(&a, &b_bad, nullptr, &out_s32, plain)));
     // reshaped operands are refused
-    GEMMInfo reshaped;
-    reshaped.set_is_a_reshaped(true);
+    const GEMMInfo reshaped(true, false, false);
     CHECK(!bool(CUGEMMLowpMatrixMultiplyCore::validate(&a, &b, nullptr, &out_s32, reshaped)));
     // fused stage
     GEMMLowpOutputStageInfo stage;
@@ -132,7 +135,7 @@ static void test_validate()
     CHECK(!bool(CUGEMMConvolutionLayer::validate(&src, &wgt, &cb, &dst, PadStrideInfo(1, 1, 0, 0)))); // wrong out shape
     CHECK(!bool(CUGEMMConvolutionLayer::validate(&src, &wgt, &cb, &dst, PadStrideInfo(1, 1, 1, 1), WeightsInfo(),
                                                  Size2D(1U, 1U), ActivationLayerInfo(), false, 2))); // groups
-    const auto mm = cu_quantized_activation_min_max(
+    const auto mm = get_quantized_activation_min_max(
         ActivationLayerInfo(ActivationLayerInfo::ActivationFunction::LU_BOUNDED_RELU, 6.f, 1.f), DataType::QASYMM8,
         UniformQuantizationInfo(0.05f, 10));
     CHECK(mm.first == 30 && mm.second == 130);
@@ -416,6 +419,253 @@ static void test_fully_connected()
     CHECK(!bool(CUFullyConnectedLayer::validate(&xi, &bad_w, nullptr, &yi)));
 }
 
+
+// ---- host tensors with padding: the fixtures add padding after configure() (GEMMLowpFixture.h:302) -----------------
+// element (x, y) of a 2-D host tensor
+template <typename T>
+static T &at(Tensor &t, int x, int y)
+{
+    return *reinterpret_cast<T *>(t.ptr_to_element(Coordinates(x, y)));
+}
+
+static void test_host_tensors_with_padding()
+{
+    const int            M = 37, N = 72, K = 96;
+    std::vector<uint8_t> ha(size_t(M) * K), hb(size_t(K) * N);
+    std::vector<int32_t> hbias(N);
+    fill_uniform(ha, 0, 255, 31);
+    fill_uniform(hb, 0, 255, 32);
+    fill_uniform(hbias, -2000, 2000, 33);
+    GEMMLowpOutputStageInfo stage;
+    stage.type                = GEMMLowpOutputStageType::QUANTIZE_DOWN_FIXEDPOINT;
+    stage.gemmlowp_multiplier = 1099511552;
+    stage.gemmlowp_shift      = 8;
+    stage.gemmlowp_offset     = 10;
+    stage.gemmlowp_min_bound  = 0;
+    stage.gemmlowp_max_bound  = 255;
+    stage.output_data_type    = DataType::QASYMM8;
+    Tensor a, b, bias, out; // plain host tensors: the function stages them
+    a.allocator()->init(TensorInfo(TensorShape(K, M), 1, DataType::QASYMM8, QuantizationInfo(0.02f, -128)));
+    b.allocator()->init(TensorInfo(TensorShape(N, K), 1, DataType::QASYMM8, QuantizationInfo(0.005f, -120)));
+    bias.allocator()->init(TensorInfo(TensorShape(N), 1, DataType::S32));
+    out.allocator()->init(TensorInfo(TensorShape(N, M), 1, DataType::QASYMM8, QuantizationInfo(0.05f, 10)));
+    CUGEMMLowpMatrixMultiplyCore fused;
+    GEMMInfo                     info;
+    info.set_gemmlowp_output_stage(stage);
+    fused.configure(&a, &b, &bias, &out, info);
+    // padding appears after configure, as in the validation fixtures: row pitches and the first-element offset change
+    a.info()->extend_padding(PaddingSize(0, 5, 0, 3));
+    b.info()->extend_padding(PaddingSize(0, 11, 0, 0));
+    out.info()->extend_padding(PaddingSize(0, 7, 0, 2));
+    for (Tensor *t : {&a, &b, &bias, &out}) t->allocator()->allocate();
+    std::memset(out.buffer(), 0xEE, out.info()->total_size());
+    for (int m = 0; m < M; ++m)
+        for (int k = 0; k < K; ++k) at<uint8_t>(a, k, m) = ha[size_t(m) * K + k];
+    for (int k = 0; k < K; ++k)
+        for (int n = 0; n < N; ++n) at<uint8_t>(b, n, k) = hb[size_t(k) * N + n];
+    std::memcpy(bias.buffer(), hbias.data(), hbias.size() * 4);
+    fused.run(); // blocks for a host output
+    std::vector<uint8_t> want(size_t(M) * N);
+    const int32_t        mult = 1099511552, shift = 8;
+    orc_gemmlowp_fused(ha.data(), 0, hb.data(), 0, hbias.data(), want.data(), 0, M, N, K, -128, -120, &mult, &shift, 1,
+                       10, 0, 255);
+    bool equal = true;
+    for (int m = 0; m < M && equal; ++m)
+        for (int n = 0; n < N; ++n) equal = equal && at<uint8_t>(out, n, m) == want[size_t(m) * N + n];
+    CHECK(equal);
+    // the padding bytes of the host output were left alone
+    const size_t pitch = out.info()->strides_in_bytes()[1], off0 = out.info()->offset_first_element_in_bytes();
+    bool padding_untouched = true;
+    for (size_t i = 0; i < off0; ++i) padding_untouched = padding_untouched && out.buffer()[i] == 0xEE;
+    for (int m = 0; m + 1 < M; ++m)
+        for (size_t x = N; x < pitch; ++x) padding_untouched = padding_untouched && out.buffer()[off0 + m * pitch + x] == 0xEE;
+    CHECK(padding_untouched);
+}
+
+// ---- rest of the function's type table: S32 accumulation, F32 dequantised output, 3-D reinterpretation, odd K -------
+static void test_type_table()
+{
+    const int           M = 70, N = 130, K = 221; // K and the row pitch are no multiples of 16
+    std::vector<int8_t> ha(size_t(M) * K), hb(size_t(K) * N);
+    fill_uniform(ha, -128, 127, 41);
+    fill_uniform(hb, -128, 127, 42);
+    std::vector<int32_t> want(size_t(M) * N);
+    orc_gemmlowp_core(ha.data(), 1, hb.data(), 1, want.data(), M, N, K, 1, 0, 3, -4);
+    CUTensor a, b, acc, accf;
+    a.allocator()->init(TensorInfo(TensorShape(K, M), 1, DataType::QASYMM8_SIGNED, QuantizationInfo(1.f / 255, 3)));
+    b.allocator()->init(TensorInfo(TensorShape(N, K), 1, DataType::QASYMM8_SIGNED, QuantizationInfo(5.f / 255, -4)));
+    acc.allocator()->init(TensorInfo(TensorShape(N, M), 1, DataType::S32));
+    accf.allocator()->init(TensorInfo(TensorShape(N, M), 1, DataType::F32));
+    // GEMMInfo(..., accumulate = true): dst += A * B (CpuGemmLowpMatrixMultiplyCore.cpp:393-401)
+    const GEMMInfo accumulate(false, false, false, 0, false, false, GEMMLowpOutputStageInfo(), false, false, false,
+                              ActivationLayerInfo(), false, arm_compute::WeightFormat::UNSPECIFIED, false, true);
+    CUGEMMLowpMatrixMultiplyCore plain, acc_fn, f32_fn, f32_acc_fn;
+    plain.configure(&a, &b, nullptr, &acc);
+    acc_fn.configure(&a, &b, nullptr, &acc, accumulate);
+    f32_fn.configure(&a, &b, nullptr, &accf);
+    f32_acc_fn.configure(&a, &b, nullptr, &accf, accumulate);
+    for (CUTensor *t : {&a, &b, &acc, &accf}) t->allocator()->allocate();
+    upload(a, ha);
+    upload(b, hb);
+    plain.run();
+    CUScheduler::get().sync();
+    CHECK(download<int32_t>(acc, want.size()) == want);
+    acc_fn.run();
+    acc_fn.run();
+    CUScheduler::get().sync();
+    std::vector<int32_t> want3(want);
+    for (auto &v : want3) v *= 3;
+    CHECK(download<int32_t>(acc, want.size()) == want3);
+    // dequantised output (the s8 -> f32 rows of the type table): float(int32) * (scale_a * scale_b), as
+    // dequantize_s32 of arm_compute/core/QuantizationInfo.h:639-642 computes it
+    f32_fn.run();
+    CUScheduler::get().sync();
+    const float        scale = (1.f / 255) * (5.f / 255);
+    std::vector<float> wantf(want.size());
+    for (size_t i = 0; i < want.size(); ++i) wantf[i] = static_cast<float>(want[i]) * scale;
+    CHECK(download<float>(accf, wantf.size()) == wantf);
+    f32_acc_fn.run();
+    CUScheduler::get().sync();
+    for (size_t i = 0; i < want.size(); ++i) wantf[i] = wantf[i] + static_cast<float>(want[i]) * scale;
+    CHECK(download<float>(accf, wantf.size()) == wantf);
+
+    // reinterpret_input_as_3d + depth_output_gemm3d: A [K, 7, 10, 2] is a batch of two 70-row matrices
+    CUTensor a3, o3;
+    a3.allocator()->init(TensorInfo(TensorShape(K, 7, 10, 2), 1, DataType::QASYMM8_SIGNED, QuantizationInfo(1.f / 255, 3)));
+    o3.allocator()->init(TensorInfo(TensorShape(N, 7, 10, 2), 1, DataType::S32));
+    const GEMMInfo               as3d(false, false, false, 10, true);
+    CUGEMMLowpMatrixMultiplyCore fn3d;
+    fn3d.configure(&a3, &b, nullptr, &o3, as3d);
+    a3.allocator()->allocate();
+    o3.allocator()->allocate();
+    std::vector<int8_t> ha2(ha);
+    ha2.insert(ha2.end(), ha.rbegin(), ha.rend()); // second batch: other data
+    upload(a3, ha2);
+    fn3d.run();
+    CUScheduler::get().sync();
+    std::vector<int32_t> want2(2 * want.size());
+    orc_gemmlowp_core(ha2.data(), 1, hb.data(), 1, want2.data(), M, N, K, 2, 0, 3, -4);
+    CHECK(download<int32_t>(o3, want2.size()) == want2);
+}
+
+// ---- NCHW convolution and update_quantization_parameters --------------------------------------------------------------
+static void test_convolution_nchw_and_requantisation()
+{
+    const int            B = 2, H = 11, W = 13, C = 16, OFM = 24, k = 3;
+    std::vector<uint8_t> nhwc(size_t(B) * H * W * C), nchw(nhwc.size());
+    std::vector<int8_t>  w_nhwc(size_t(OFM) * k * k * C), w_nchw(w_nhwc.size());
+    std::vector<int32_t> hbias(OFM);
+    std::vector<float>   scales(OFM);
+    fill_uniform(nhwc, 0, 255, 51);
+    fill_uniform(w_nhwc, -127, 127, 52);
+    fill_uniform(hbias, -3000, 3000, 53);
+    std::mt19937                          gen(54);
+    std::uniform_real_distribution<float> sd(2e-3f, 8e-3f);
+    for (auto &s : scales) s = sd(gen);
+    for (int b = 0; b < B; ++b)
+        for (int y = 0; y < H; ++y)
+            for (int x = 0; x < W; ++x)
+                for (int c = 0; c < C; ++c)
+                    nchw[((size_t(b) * C + c) * H + y) * W + x] = nhwc[((size_t(b) * H + y) * W + x) * C + c];
+    for (int o = 0; o < OFM; ++o)
+        for (int y = 0; y < k; ++y)
+            for (int x = 0; x < k; ++x)
+                for (int c = 0; c < C; ++c)
+                    w_nchw[((size_t(o) * C + c) * k + y) * k + x] = w_nhwc[((size_t(o) * k + y) * k + x) * C + c];
+    const int Wo = (W + 2 - k) / 2 + 1, Ho = (H + 2 - k) / 2 + 1;
+    CUTensor   src, wgt, bias, dst;
+    TensorInfo si(TensorShape(W, H, C, B), 1, DataType::QASYMM8, QuantizationInfo(0.03f, 128));
+    TensorInfo wi(TensorShape(k, k, C, OFM), 1, DataType::QSYMM8_PER_CHANNEL, QuantizationInfo(scales));
+    TensorInfo di(TensorShape(Wo, Ho, OFM, B), 1, DataType::QASYMM8, QuantizationInfo(0.05f, 4));
+    si.set_data_layout(DataLayout::NCHW);
+    wi.set_data_layout(DataLayout::NCHW);
+    di.set_data_layout(DataLayout::NCHW);
+    src.allocator()->init(si);
+    wgt.allocator()->init(wi);
+    bias.allocator()->init(TensorInfo(TensorShape(OFM), 1, DataType::S32));
+    dst.allocator()->init(di);
+    CUGEMMConvolutionLayer conv;
+    conv.configure(&src, &wgt, &bias, &dst, PadStrideInfo(2, 2, 1, 1));
+    for (CUTensor *t : {&src, &wgt, &bias, &dst}) t->allocator()->allocate();
+    upload(src, nchw);
+    upload(wgt, w_nchw);
+    upload(bias, hbias);
+    conv.run();
+    CUScheduler::get().sync();
+    auto check = [&](float in_scale, int in_zp, float out_scale, int out_zp) {
+        std::vector<int32_t> mult(OFM), shift(OFM);
+        cugl_calculate_quantized_multipliers(in_scale, scales.data(), OFM, out_scale, mult.data(), shift.data());
+        std::vector<uint8_t> want(size_t(B) * Ho * Wo * OFM), want_nchw(want.size());
+        orc_conv2d_nhwc(nhwc.data(), 0, w_nhwc.data(), 1, hbias.data(), want.data(), C, W, H, B, k, k, OFM, 2, 2, 1, 1, 1,
+                        1, Wo, Ho, in_zp, 0, mult.data(), shift.data(), OFM, out_zp, 0, 255);
+        for (int b = 0; b < B; ++b)
+            for (int p = 0; p < Ho * Wo; ++p)
+                for (int o = 0; o < OFM; ++o) want_nchw[(size_t(b) * OFM + o) * Ho * Wo + p] = want[(size_t(b) * Ho * Wo + p) * OFM + o];
+        CHECK(download<uint8_t>(dst, want_nchw.size()) == want_nchw);
+    };
+    check(0.03f, 128, 0.05f, 4);
+    // NEGEMMConvolutionLayer::update_quantization_parameters: new input / output quantization, same prepared weights
+    src.info()->set_quantization_info(QuantizationInfo(0.02f, 100));
+    dst.info()->set_quantization_info(QuantizationInfo(0.04f, 9));
+    conv.update_quantization_parameters();
+    conv.run();
+    CUScheduler::get().sync();
+    check(0.02f, 100, 0.04f, 9);
+}
+
+// ---- memory manager: two convolutions on the explicit lowering share one pool ----------------------------------------
+static size_t run_two_convolutions(std::shared_ptr<IMemoryManager> mm, std::vector<uint8_t> &result)
+{
+    // C = 3 keeps both layers on the explicit im2col lowering: each needs a [M][Kp] patch matrix per run
+    const int  B = 4, H = 40, W = 40, C = 3, OFM = 3, k = 5;
+    CUAllocator allocator;
+    const size_t before = CUAllocator::bytes_in_use();
+    CUAllocator::reset_peak();
+    {
+        CUTensor   x, w1, w2, mid, y;
+        TensorInfo xi(TensorShape(C, W, H, B), 1, DataType::QASYMM8, QuantizationInfo(0.03f, 120));
+        TensorInfo wi(TensorShape(C, k, k, OFM), 1, DataType::QASYMM8, QuantizationInfo(0.004f, 130));
+        TensorInfo yi(TensorShape(OFM, W, H, B), 1, DataType::QASYMM8, QuantizationInfo(0.1f, 12));
+        xi.set_data_layout(DataLayout::NHWC), wi.set_data_layout(DataLayout::NHWC), yi.set_data_layout(DataLayout::NHWC);
+        x.allocator()->init(xi), w1.allocator()->init(wi), w2.allocator()->init(wi), mid.allocator()->init(yi), y.allocator()->init(yi);
+        CUGEMMConvolutionLayer c1(mm), c2(mm);
+        c1.configure(&x, &w1, nullptr, &mid, PadStrideInfo(1, 1, 2, 2));
+        c2.configure(&mid, &w2, nullptr, &y, PadStrideInfo(1, 1, 2, 2));
+        for (CUTensor *t : {&x, &w1, &w2, &mid, &y}) t->allocator()->allocate();
+        if (mm)
+        {
+            mm->populate(allocator, 1); // one pool: the two workspaces never live at the same time
+        }
+        std::vector<uint8_t> hx(size_t(B) * H * W * C), hw(size_t(OFM) * k * k * C);
+        fill_uniform(hx, 0, 255, 61);
+        fill_uniform(hw, 100, 160, 62);
+        upload(x, hx);
+        upload(w1, hw);
+        upload(w2, hw);
+        c1.run();
+        c2.run();
+        CUScheduler::get().sync();
+        result = download<uint8_t>(y, size_t(B) * H * W * OFM);
+    }
+    if (mm)
+    {
+        mm->clear();
+    }
+    return CUAllocator::peak_bytes() - before;
+}
+
+static void test_memory_manager()
+{
+    std::vector<uint8_t> plain, managed;
+    const size_t         peak_plain   = run_two_convolutions(nullptr, plain);
+    const size_t         peak_managed = run_two_convolutions(cu_create_memory_manager(), managed);
+    CHECK(plain == managed);
+    // without a manager each function holds its own patch matrix (4*40*40 rows x 80 bytes = 512 KB each)
+    std::printf("peak device bytes of the tensors and workspaces: %zu without a memory manager, %zu with one\n", peak_plain,
+                peak_managed);
+    CHECK(peak_managed + 400 * 1024 < peak_plain);
+}
+
 int main(int argc, char **argv)
 {
     const bool validate_only = argc > 1 && std::strcmp(argv[1], "--validate") == 0;
@@ -430,6 +680,10 @@ int main(int argc, char **argv)
             test_convolution();
             test_layers();
             test_fully_connected();
+            test_host_tensors_with_padding();
+            test_type_table();
+            test_convolution_nchw_and_requantisation();
+            test_memory_manager();
         }
     }
     catch (const std::exception &e)

@@ -5,8 +5,9 @@ import numpy as np
 
 from computelibrary_b200 import capi
 
-NP_OF = {capi.U8: np.uint8, capi.S8: np.int8, capi.S32: np.int32}
-CODE_OF = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8, np.dtype(np.int32): capi.S32}
+NP_OF = {capi.U8: np.uint8, capi.S8: np.int8, capi.S32: np.int32, capi.F32: np.float32}
+CODE_OF = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8, np.dtype(np.int32): capi.S32,
+           np.dtype(np.float32): capi.F32}
 
 
 from computelibrary_b200.workloads import (config1, config2, config3, config5, q8_uniform,  # noqa: F401,E402
@@ -21,7 +22,8 @@ def f32_mults(port, i_scale, w_scales, o_scale):
 # ---- GPU drivers (torch tensors as device buffers) ------------------------------------------------------
 def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype, force_simt=False,
                  b_constant=True, runs=1, ldd_pad=0, pair=True, epi_warps=0, channel_major=0, integer_stage=False,
-                 tile_columns=0, paired_drain=True):
+                 tile_columns=0, paired_drain=True, accumulate=False, dequantize_scale=0.0, dst_init=None,
+                 temp_workspace=False):
     """Fused NEGEMMLowpMatrixMultiplyCore through the C ABI.  mult/shift scalars -> per-tensor; arrays ->
     per-channel.  out_dtype np.int32 -> output stage NONE.  Returns (numpy result, kernel name)."""
     import torch
@@ -34,15 +36,22 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
     out_dtype = np.dtype(out_dtype)
     dsz = out_dtype.itemsize
     per_channel = np.ndim(mult) > 0
-    stage = capi.STAGE_NONE if out_dtype == np.int32 else (capi.STAGE_QUANTIZE_DOWN if integer_stage else capi.STAGE_FIXEDPOINT)
+    raw = out_dtype in (np.dtype(np.int32), np.dtype(np.float32))  # output stage NONE
+    stage = capi.STAGE_NONE if raw else (capi.STAGE_QUANTIZE_DOWN if integer_stage else capi.STAGE_FIXEDPOINT)
     ldd = (N + ldd_pad) * dsz
     desc, keep = capi.make_gemm_desc(
         M, N, K, CODE_OF[a.dtype], CODE_OF[b.dtype], CODE_OF[out_dtype], a_off, b_off, stage,
         multiplier=0 if per_channel else int(mult), shift=0 if per_channel else int(shift),
         multipliers=mult if per_channel else None, shifts=shift if per_channel else None, offset=offset,
         min_bound=lo, max_bound=hi, has_bias=bias is not None, batch=batch, ldd=ldd,
-        b_batch_stride=(K * N if b.ndim == 3 else 0), b_constant=b_constant)
+        b_batch_stride=(K * N if b.ndim == 3 else 0), b_constant=b_constant, accumulate=accumulate,
+        dequantize_scale=dequantize_scale)
     plan = capi.GemmPlan(ctx, desc, keep)
+    ws = None
+    if temp_workspace:  # the caller owns the temporary memory (what a MemoryGroup does for the C++ functions)
+        nbytes = plan.temp_bytes
+        ws = torch.full((max(nbytes, 1) + 64,), 0x77, dtype=torch.uint8, device="cuda")
+        plan.bind_temp(ws, nbytes)
     if force_simt:
         plan.force_simt(True)
     if not pair:
@@ -60,6 +69,9 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
     dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.int32)).cuda() if bias is not None else None
     canary = 0xA5
     dd = torch.full((batch * M * ldd,), canary, dtype=torch.uint8, device="cuda")
+    if dst_init is not None:  # accumulation starts from these values
+        init = np.ascontiguousarray(dst_init, dtype=out_dtype).reshape(batch * M, N).view(np.uint8)
+        dd.view(batch * M, ldd)[:, :N * dsz] = torch.from_numpy(init).cuda()
     if b_constant:
         plan.prepare(db)
     for _ in range(runs):
@@ -70,6 +82,8 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
         assert (raw[:, :, N * dsz:] == canary).all(), "kernel wrote into the row padding"
     out = np.ascontiguousarray(raw[:, :, :N * dsz]).view(out_dtype).reshape(batch, M, N)
     kernel = plan.kernel
+    if ws is not None:
+        assert (ws[plan.temp_bytes:] == 0x77).all(), "the plan wrote past the bound temporary workspace"
     plan.close()
     return (out if batched else out[0]), kernel
 

@@ -20,8 +20,9 @@ def test_library_exports_every_declared_symbol():
 
 
 def test_struct_layout_matches_header():
-    # natural C layout: 4 x i32, 6 x i64, 9 x i32 (+pad), 2 x ptr, 5 x i32 (+pad)
-    assert C.sizeof(capi.GemmDesc) == 16 + 48 + 40 + 16 + 24
+    # natural C layout: 4 x i32, 6 x i64, 9 x i32 (+pad), 2 x ptr, 6 x i32 + 1 x f32 (+pad)
+    assert C.sizeof(capi.GemmDesc) == 16 + 48 + 40 + 16 + 32
+    assert capi.GemmDesc.dequantize_scale.offset == 16 + 48 + 40 + 16 + 24
     assert capi.GemmDesc.h_gemmlowp_multipliers.offset == 104
     assert capi.ConvDesc.h_gemmlowp_multipliers.offset == 88
 

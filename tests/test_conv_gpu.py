@@ -229,3 +229,52 @@ def test_fused_residual_addition_many_tiles(ctx, port, paired):
     ctx.sync()
     assert np.array_equal(d_res.cpu().numpy(), want)
     plan.close()
+
+
+def test_conv_update_quantization_and_bound_workspace(ctx, port):
+    """cugl_conv2d_update_quantization (NEGEMMConvolutionLayer::update_quantization_parameters): new input zero
+    point, multipliers, output zero point and bounds on prepared weights; on the explicit lowering with its im2col
+    matrix in a workspace the caller owns."""
+    import torch
+    rng = np.random.default_rng(5)
+    B, H, W, C_, OFM = 2, 9, 10, 16, 24
+    src = q8_uniform(rng, (B, H, W, C_), np.uint8)
+    wgt = q8_uniform(rng, (OFM, 3, 3, C_), np.int8, -127, 127)
+    bias = rng.integers(-3000, 3001, OFM).astype(np.int32)
+    ws = rng.uniform(2e-3, 8e-3, OFM).astype(np.float32)
+    d_src, d_w, d_b = torch.from_numpy(src).cuda(), torch.from_numpy(wgt.view(np.uint8)).cuda(), torch.from_numpy(bias).cuda()
+    for implicit in (True, False):
+        def desc_for(i_scale, i_zp, o_scale, o_zp, lo, hi):
+            mult, shift = capi.calculate_quantized_multipliers(np.float32(i_scale), ws, np.float32(o_scale))
+            return capi.make_conv_desc(B, H, W, C_, OFM, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1), capi.U8, capi.S8, i_zp, 0,
+                                       multipliers=mult, shifts=shift, dst_zp=o_zp, min_bound=lo, max_bound=hi), (mult, shift)
+        (desc, keep), (mult, shift) = desc_for(0.03, 128, 0.05, 0, 0, 255)
+        plan = capi.ConvPlan(ctx, desc, keep)
+        plan.allow_implicit(implicit)
+        nbytes = plan.temp_bytes
+        assert (nbytes > 0) == (not implicit)
+        wsbuf = torch.full((nbytes + 64,), 0x77, dtype=torch.uint8, device="cuda")
+        plan.bind_temp(wsbuf, nbytes)
+        d_dst = torch.empty((B, H, W, OFM), dtype=torch.uint8, device="cuda")
+        plan.prepare(d_w)
+        plan.run(d_src, d_b, d_dst)
+        ctx.sync()
+        assert np.array_equal(d_dst.cpu().numpy(), port.conv2d_nhwc(src, wgt, bias, (1, 1), (1, 1, 1, 1), 128, 0, mult, shift, 0, 0, 255))
+        (desc2, keep2), (mult2, shift2) = desc_for(0.02, 100, 0.04, 9, 9, 200)
+        plan.update_quantization(desc2, keep2)
+        plan.run(d_src, d_b, d_dst)
+        ctx.sync()
+        assert np.array_equal(d_dst.cpu().numpy(), port.conv2d_nhwc(src, wgt, bias, (1, 1), (1, 1, 1, 1), 100, 0, mult2, shift2, 9, 9, 200))
+        assert (wsbuf[nbytes:] == 0x77).all()
+        plan.close()
+
+
+def test_transpose_batched_is_the_nchw_nhwc_permute(ctx):
+    import torch
+    rng = np.random.default_rng(6)
+    x = rng.integers(0, 256, (3, 37, 11 * 13), dtype=np.uint8)  # [B][C][H*W]
+    d_x = torch.from_numpy(x).cuda()
+    d_y = torch.empty((3, 11 * 13, 37), dtype=torch.uint8, device="cuda")
+    ctx.transpose_batched(d_x, d_y, 37, 11 * 13, 3)
+    ctx.sync()
+    assert np.array_equal(d_y.cpu().numpy(), x.transpose(0, 2, 1))

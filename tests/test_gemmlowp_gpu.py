@@ -97,8 +97,11 @@ def test_kernel_selection(ctx):
     _, k1 = gpu_gemmlowp(ctx, a, b, None, 0, 0, 2 ** 30, 3, 0, 0, 255, np.uint8)
     assert k1 == "tcgen05"          # K = 48: row stride is a multiple of 16 bytes
     a2, b2 = q8_uniform(rng, (64, 50), np.uint8), q8_uniform(rng, (50, 32), np.uint8)
-    _, k2 = gpu_gemmlowp(ctx, a2, b2, None, 0, 0, 2 ** 30, 3, 0, 0, 255, np.uint8)
-    assert k2 == "simt"             # K = 50: TMA cannot address the rows of A
+    got, k2 = gpu_gemmlowp(ctx, a2, b2, None, 0, 0, 2 ** 30, 3, 0, 0, 255, np.uint8)
+    # K = 50: TMA cannot address these rows of A, so the plan multiplies a copy of A with a 64-byte row pitch
+    assert k2 == "tcgen05"
+    _, k3 = gpu_gemmlowp(ctx, a2, b2, None, 0, 0, 2 ** 30, 3, 0, 0, 255, np.uint8, force_simt=True)
+    assert k3 == "simt" and np.array_equal(got, _)
 
 
 def test_negative_shift_and_saturating_multiplier(ctx, port):
@@ -407,3 +410,56 @@ def test_paired_drain(ctx, port, shape, epi_warps):
                                  epi_warps=epi_warps, channel_major=-1, paired_drain=paired)
         assert kern == "tcgen05"
         assert np.array_equal(got, want), (paired, np.argwhere(got != want)[:4])
+
+
+# Shapes of tests/datasets/SmallGEMMLowpDataset.h:43-52 and LargeGEMMLowpDataset.h:43-52 as (M, N, K, a_offset, b_offset)
+REFERENCE_DATASET_SHAPES = [(13, 33, 21, 0, 0), (13, 33, 52, 0, 4), (27, 23, 31, 18, 23), (72, 17, 32, -9, 1),
+                            (1, 33, 21, 0, 0), (13, 1, 21, 5, 13), (973, 221, 1021, 10, 2), (1123, 213, 941, -3, -2),
+                            (429, 71, 1021, 1, -1), (1023, 171, 1, 1, 3)]
+
+
+@pytest.mark.parametrize("M,N,K,ao,bo", REFERENCE_DATASET_SHAPES)
+def test_reference_dataset_shapes_run_on_the_tensor_cores(ctx, port, M, N, K, ao, bo):
+    """Every shape of the reference's Small / Large GEMMLowp datasets -- K and row pitches that are no multiples of 16
+    among them -- runs on the tcgen05 kernel (through a 16-byte-pitch copy of A where needed) and is exact."""
+    rng = np.random.default_rng(M * 7 + K)
+    a, b = q8_uniform(rng, (M, K), np.uint8), q8_uniform(rng, (K, N), np.uint8)
+    got, kern = gpu_gemmlowp(ctx, a, b, None, ao, bo, 0, 0, 0, 0, 0, np.int32)
+    assert kern.startswith("tcgen05"), kern
+    assert np.array_equal(got, port.gemmlowp_core(a, b, ao, bo))
+    bias = rng.integers(-3000, 3001, N).astype(np.int32)
+    mult, shift = 1518500250, int(np.ceil(np.log2(max(K, 2) * 255 * 255 / 200)))
+    got, kern = gpu_gemmlowp(ctx, a, b, bias, ao, bo, mult, shift, 7, 0, 255, np.uint8, temp_workspace=True)
+    assert kern.startswith("tcgen05"), kern
+    assert np.array_equal(got, port.gemmlowp_fused(a, b, bias, ao, bo, [mult], [shift], 7, 0, 255, np.uint8))
+
+
+@pytest.mark.parametrize("M,N,K", [(70, 130, 221), (256, 512, 1040), (300, 64, 96)])
+@pytest.mark.parametrize("force_simt", [False, True])
+def test_accumulate_and_dequantized_output(ctx, port, M, N, K, force_simt):
+    """GEMMInfo::accumulate (dst += A * B, S32) and the s8 x s8 -> F32 rows of the type table: float(int32) * scale with
+    one rounding each, identical to the reference's dequantization of the S32 result bit for bit."""
+    rng = np.random.default_rng(M + N + K)
+    a, b = q8_uniform(rng, (M, K), np.int8), q8_uniform(rng, (K, N), np.int8)
+    acc = port.gemmlowp_core(a, b, 3, -4)
+    start = rng.integers(-2 ** 20, 2 ** 20, (M, N)).astype(np.int32)
+    got, _ = gpu_gemmlowp(ctx, a, b, None, 3, -4, 0, 0, 0, 0, 0, np.int32, accumulate=True, dst_init=start, runs=2,
+                          force_simt=force_simt, ldd_pad=4)
+    assert np.array_equal(got, start + 2 * acc)
+    scale = float(np.float32(1 / 255) * np.float32(5 / 255))
+    got, _ = gpu_gemmlowp(ctx, a, b, None, 3, -4, 0, 0, 0, 0, 0, np.float32, dequantize_scale=scale, force_simt=force_simt)
+    want = port.dequantize_s32(acc, scale)
+    assert got.dtype == np.float32 and np.array_equal(got, want)
+    prev = rng.uniform(-100, 100, (M, N)).astype(np.float32)
+    got, _ = gpu_gemmlowp(ctx, a, b, None, 3, -4, 0, 0, 0, 0, 0, np.float32, dequantize_scale=scale, accumulate=True,
+                          dst_init=prev, force_simt=force_simt)
+    assert np.array_equal(got, port.dequantize_s32(acc, scale, prev))
+
+
+def test_validate_rules_of_the_raw_outputs():
+    d, keep = capi.make_gemm_desc(8, 8, 8, capi.S8, capi.S8, capi.F32, stage=capi.STAGE_NONE)
+    assert capi.gemm_validate(d)[0] == 6            # an F32 output needs a scale
+    d, keep = capi.make_gemm_desc(8, 8, 8, capi.S8, capi.S8, capi.F32, stage=capi.STAGE_NONE, dequantize_scale=0.1)
+    assert capi.gemm_validate(d)[0] == 0
+    d, keep = capi.make_gemm_desc(8, 8, 8, capi.S8, capi.S8, capi.S8, multiplier=2 ** 30, shift=1, accumulate=True)
+    assert capi.gemm_validate(d)[0] == 6            # accumulation only without an output stage

@@ -203,3 +203,14 @@ def test_port_vs_reference_integer_stage(port, ref, out_dtype):
                 for b in (None, bias):
                     assert np.array_equal(port.output_stage_int(acc, b, mult, shift, -321, lo, hi, out_dtype),
                                           ref.output_stage_int(acc, b, mult, shift, -321, lo, hi, out_dtype))
+
+
+def test_port_vs_reference_dequantized_output(port, ref):
+    """The dequantised (F32) GEMMLowp output and its accumulating form against reference::dequantization_layer /
+    reference::arithmetic_operation compiled in place."""
+    rng = np.random.default_rng(77)
+    acc = rng.integers(-2 ** 31, 2 ** 31, 50000, dtype=np.int64).astype(np.int32)
+    prev = rng.uniform(-2e4, 2e4, acc.size).astype(np.float32)
+    for scale in (np.float32(1 / 255) * np.float32(5 / 255), np.float32(0.37), np.float32(3e-7)):
+        assert np.array_equal(ref.dequantize_s32(acc, scale), port.dequantize_s32(acc, scale))
+        assert np.array_equal(ref.dequantize_s32(acc, scale, prev), port.dequantize_s32(acc, scale, prev))
