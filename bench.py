@@ -35,6 +35,8 @@ sys.path.insert(0, ROOT)
 METRIC = "gemmlowp_int8_tops"
 UNIT = "TOPS"
 NOMINAL_INT8_TOPS = 4500.0
+# DRAM bytes (read + write) ncu counted for one launch of the fused GEMM, keyed by (M, N, K); see profiles/
+NCU_TRAFFIC_BYTES = {(4096, 4096, 4096): 33.7e6}
 
 
 def parse_args():
@@ -55,6 +57,10 @@ def parse_args():
     p.add_argument("--no-cpu-baseline", action="store_true")
     p.add_argument("--no-e2e", action="store_true")
     p.add_argument("--one-cta", action="store_true", help="keep to the one-CTA tensor-core kernel (comparison runs)")
+    p.add_argument("--headline-only", action="store_true",
+                   help="c2: skip the ResNet-50 and sharded-linear-layer blocks that follow the headline measurement")
+    p.add_argument("--net-steps", type=int, default=20,
+                   help="cap on the timed steps of the ResNet-50 / sharded-linear blocks (each step is milliseconds)")
     return p.parse_args()
 
 
@@ -132,22 +138,42 @@ class ClockSampler:
 # ---------------------------------------------------------------------------------------------------------
 # workloads
 # ---------------------------------------------------------------------------------------------------------
-def make_gemm_workload(name, size):
+def _product_multipliers():
     from computelibrary_b200 import capi
+    return capi.calculate_quantized_multiplier, capi.calculate_quantized_multipliers
+
+
+def _reference_multipliers():
+    """The reference arm derives its output stage with the reference's own AsymmHelpers (oracle/_ref, else the C
+    restatement), so that its process never maps the library under test."""
+    import oracle
+    impl = oracle.ref() or oracle.port()
+
+    def many(i_scale, w_scales, o_scale):
+        w = np.asarray(w_scales, np.float32)
+        if hasattr(impl, "calculate_quantized_multipliers"):
+            return impl.calculate_quantized_multipliers(np.float32(i_scale), w, np.float32(o_scale))
+        pairs = [impl.calculate_quantized_multiplier(float(np.float32(i_scale) * ws / np.float32(o_scale))) for ws in w]
+        return np.array([p[0] for p in pairs], np.int32), np.array([p[1] for p in pairs], np.int32)
+    return impl.calculate_quantized_multiplier, many
+
+
+def make_gemm_workload(name, size, derive=None):
     from computelibrary_b200 import workloads as wl
+    one, many = derive or _product_multipliers()
     if name == "c1":
         c = wl.config1()
-        qm, sh = capi.calculate_quantized_multiplier(c["real_multiplier"])
+        qm, sh = one(c["real_multiplier"])
         mult, shift = np.array([qm], np.int32), np.array([sh], np.int32)
         label = "config1: QASYMM8 GEMMLowp M=64 N=128 K=256, bias, per-tensor fixed-point requant to QASYMM8"
     elif name == "c5":
         c = wl.config5()
-        mult, shift = capi.calculate_quantized_multipliers(c["i_scale"], c["w_scales"], c["o_scale"])
+        mult, shift = many(c["i_scale"], c["w_scales"], c["o_scale"])
         label = "config5: s8 linear M=8192 K=4096 N=14336, per-channel requant to s8, no bias"
     else:
         n = size or 4096
         c = wl.config2(M=n, N=n, K=n)
-        mult, shift = capi.calculate_quantized_multipliers(c["i_scale"], c["w_scales"], c["o_scale"])
+        mult, shift = many(c["i_scale"], c["w_scales"], c["o_scale"])
         label = (f"config2: QASYMM8_SIGNED x QSYMM8_PER_CHANNEL GEMMLowp M=N=K={n}, bias, per-channel "
                  "fixed-point requant to QASYMM8_SIGNED")
     c["mult"], c["shift"], c["label"] = mult, shift, label
@@ -175,19 +201,28 @@ def build_plan(ctx, c):
     return plan, (M, N, K)
 
 
+def init_dist(args):
+    """One process per GPU (torchrun); NCCL carries the barriers and the max-reduce of the timings only."""
+    import torch
+    import torch.distributed as dist
+    rank, world, local = dist_env()
+    if args.gpus > 1 and world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, world, local
+
+
 def run_ours(args):
+    """The headline line: config 2 (or c1 / c5 on one GPU).  Returns the JSON line as a dict on rank 0, else None."""
     import torch
     import torch.distributed as dist
 
     import computelibrary_b200 as cl
 
-    rank, world, local = dist_env()
-    if args.gpus > 1 and world != args.gpus:
-        raise SystemExit(f"--gpus {args.gpus} needs torchrun with {args.gpus} ranks (WORLD_SIZE={world})")
-    torch.cuda.set_device(local)
+    rank, world, local = init_dist(args)
     sampler = ClockSampler(local) if rank == 0 else None  # started early: nvidia-smi takes a while to come up
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     ctx = cl.Context(local, torch.cuda.current_stream().cuda_stream)
     c = make_gemm_workload(args.workload, args.size)
@@ -272,10 +307,16 @@ def run_ours(args):
                "h2d_bytes_per_step": M * K + (4 * N if c["bias"] is not None else 0), "d2h_bytes_per_step": M * N,
                "ms_per_step": e2e_ms / args.steps}
 
+    # per-rank copy rates of the end-to-end call: what the host side sustains while every rank copies at once
+    if e2e is not None:
+        e2e["h2d_gbs_per_rank"] = e2e["h2d_bytes_per_step"] / (e2e["ms_per_step"] * 1e-3) / 1e9
+        e2e["d2h_gbs_per_rank"] = e2e["d2h_bytes_per_step"] / (e2e["ms_per_step"] * 1e-3) / 1e9
+        e2e["note"] = ("copies in and out overlap the GEMM in eight row blocks; the step costs about the longer copy, "
+                       "so the rate above is what one rank's PCIe / host-memory path delivered with all ranks active")
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        plan.close()
+        ctx.close()
+        return None
 
     peaks = load_peaks()
     kernel_ms = statistics.mean(step_ms)  # the fused GEMM kernel is the only kernel of a step here
@@ -286,7 +327,11 @@ def run_ours(args):
         "peak_source": f"2 x {peaks['source']} bf16 cuBLAS burst ({peaks['bf16_tflops']} TFLOP/s): int8 tensor "
                        "rate is twice the bf16 rate; no int8 figure is recorded in MEASURED_PEAKS.json",
         "frac_of_nominal_4500": achieved / NOMINAL_INT8_TOPS,
-        "traffic": None,
+        # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu capture of this kernel
+        # (profiles/): the 4096^3 operands are read once, the 16.8 MB output stays in L2 within the capture window
+        "traffic": NCU_TRAFFIC_BYTES.get((M, N, K)),
+        "traffic_source": "ncu capture summarised under profiles/" if (M, N, K) in NCU_TRAFFIC_BYTES else None,
+        "algorithmic_bytes": M * K + N * K + M * N + 16 * N,
         "kernel": {"tcgen05_2cta": "gemmlowp_tcgen05_2cta_kernel", "tcgen05": "gemmlowp_tcgen05_kernel"}.get(
             plan.kernel, "gemmlowp_simt_kernel"),
         "kernel_ms": kernel_ms,
@@ -321,11 +366,9 @@ def run_ours(args):
     }
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline(c, ops)
-    print(json.dumps(line), flush=True)
     plan.close()
     ctx.close()
-    if world > 1:
-        dist.destroy_process_group()
+    return line
 
 
 # ---------------------------------------------------------------------------------------------------------
@@ -385,15 +428,17 @@ def run_reference(args):
     rank, world, _ = dist_env()
     if rank != 0:
         return
-    c = make_gemm_workload(args.workload, args.size)
+    c = make_gemm_workload(args.workload if args.workload in ("c1", "c2", "c5") else "c2", args.size,
+                           derive=_reference_multipliers())
     M, K = c["a"].shape
     N = c["b"].shape[1]
     threads = os.cpu_count() or 1
-    rows = cpu_sample_rows(c, threads)
-    # keep the whole --steps/--warmup run within a few minutes: each step is a bounded row sample
+    # keep the whole --steps/--warmup run within a few minutes: a short calibration pass gives this machine's
+    # rate, each step then takes as many rows of A as fit its share of about 150 s -- all of them when they fit
     per_step_budget = 150.0 / max(1, args.steps + args.warmup)
-    rows = int(max(threads, min(rows, rows * per_step_budget / 10.0)))
-    kind, used = "port", threads
+    cal_rows = min(M, 16 * threads)
+    cal_s, kind, used = cpu_reference_step(c, cal_rows, threads)
+    rows = int(max(threads, min(M, cal_rows * per_step_budget / max(cal_s, 1e-6) * 0.8)))
     for _ in range(args.warmup):
         _, kind, used = cpu_reference_step(c, rows, threads)
     t = 0.0
@@ -402,7 +447,10 @@ def run_reference(args):
         t += s
     ms = t / args.steps * 1e3
     value = 2.0 * rows * N * K / (ms * 1e-3) / 1e12
-    sample = f"each step = {rows} of {M} rows of A against all of B ({rows}x{N}x{K})"
+    sample = (f"each step = {rows} of {M} rows of A against all of B ({rows}x{N}x{K})" +
+              (": the whole problem" if rows == M else ""))
+    with open("/proc/self/maps") as f:
+        native = sorted({ln.split()[-1] for ln in f if ".so" in ln and ("/oracle/" in ln or "computelibrary_b200" in ln)})
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
@@ -411,7 +459,7 @@ def run_reference(args):
                    "be built on x86_64; this times the reference's own scalar implementation of the path"},
         "cpu_baseline": {"value": value, "unit": UNIT, "cores": used, "kind": kind, "sample": sample},
         "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
-        "gpu_launches": 0,
+        "gpu_launches": 0, "same_config": rows == M, "native_libraries_mapped": native,
     }
     print(json.dumps(line), flush=True)
 
@@ -444,10 +492,7 @@ def run_conv(args):
     import computelibrary_b200 as cl
     from computelibrary_b200 import capi, sharding
     from computelibrary_b200 import workloads as wl
-    rank, world, local = dist_env()
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world, local = init_dist(args)
     ctx = cl.Context(local, torch.cuda.current_stream().cuda_stream)
     c = wl.config3()
     b0, b1 = sharding.batch_shard(c["src"].shape[0], world, rank)
@@ -509,29 +554,25 @@ def run_conv(args):
                          "lowering": plan.kernel}}), flush=True)
     plan.close()
     ctx.close()
-    if world > 1:
-        dist.destroy_process_group()
 
 
-def run_resnet(args):
-    """Config 4: QASYMM8 ResNet-50 v1 (examples/graph_resnet50.cpp topology, batch norm folded, ReLU fused), global
-    batch 256 split over the ranks, weights replicated, no collective.  Reports images/s; the tensor-core roofline
-    uses 6.965 GOP per image."""
+def measure_resnet(args, weak):
+    """Config 4: QASYMM8 ResNet-50 v1 (examples/graph_resnet50.cpp topology, batch norm folded, ReLU fused), batch split
+    over the ranks (strong scaling: one global batch of --batch; weak: --batch per rank), weights replicated, no
+    collective.  Every rank takes part; rank 0 gets the result, the others None."""
     import torch
     import torch.distributed as dist
     import computelibrary_b200 as cl
     from computelibrary_b200 import resnet50 as rn
     from computelibrary_b200 import sharding
-    rank, world, local = dist_env()
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world, local = init_dist(args)
     # a stream of its own: the node list is captured into a CUDA graph on it; torch's current stream is set to
     # it so that the bench's events, copies and L2 flush are ordered with the network
+    prev_stream = torch.cuda.current_stream()
     work = torch.cuda.Stream()
     torch.cuda.set_stream(work)
     ctx = cl.Context(local, work.cuda_stream)
-    global_batch = args.batch * world if args.weak else args.batch
+    global_batch = args.batch * world if weak else args.batch
     b0, b1 = sharding.batch_shard(global_batch, world, rank)
     B = b1 - b0
     net = rn.ResNet50(ctx, B, seed=1)
@@ -540,6 +581,7 @@ def run_resnet(args):
     d_in = h_in.cuda()
     h_out = torch.empty((B, 1, 1, 1000), dtype=torch.uint8).pin_memory()
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
+    steps, warmup = min(args.steps, args.net_steps), max(3, min(args.warmup, 5))
 
     def barrier():
         if world > 1:
@@ -554,7 +596,7 @@ def run_resnet(args):
     run_net = (lambda: net.run(d_in)) if graph is None else graph.replay
     barrier()
     t_begin = time.time()
-    step_ms = _timed_steps(run_net, args.steps, args.warmup, flush, barrier)
+    step_ms = _timed_steps(run_net, steps, warmup, flush, barrier)
     clocks = sampler.stop(t_begin, time.time()) if sampler else None
     ctx.sync()
 
@@ -563,28 +605,32 @@ def run_resnet(args):
         run_net()
         h_out.copy_(net.bufs["softmax"], non_blocking=True)
 
-    e2e_ms = [] if args.no_e2e else _timed_steps(e2e_step, max(2, args.steps // 4), 2, flush, barrier)
+    e2e_ms = [] if args.no_e2e else _timed_steps(e2e_step, max(3, steps // 2), 3, flush, barrier)
     if args.layers and rank == 0:
         rows = net.run_timed(d_in)
         tot = sum(r[3] for r in rows)
         for name, op, kern, ms in rows:
             print(f"{name:34s} {op:15s} {kern:10s} {ms * 1e3:9.1f} us {100 * ms / tot:5.1f} %", file=sys.stderr)
         print(f"sum {tot:.3f} ms", file=sys.stderr)
-    t = torch.tensor([float(sum(step_ms)) / args.steps, float(sum(e2e_ms)) / max(1, len(e2e_ms))], device="cuda",
+    t = torch.tensor([float(sum(step_ms)) / steps, float(sum(e2e_ms)) / max(1, len(e2e_ms))], device="cuda",
                      dtype=torch.float64)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    out = None
     if rank == 0:
         ms, e2e = float(t[0]), float(t[1])
-        ops_img = rn.graph_ops(net.nodes)
+        ops_img, bytes_img = rn.graph_ops(net.nodes), rn.graph_bytes(net.nodes)
         peaks = load_peaks()
-        # one rank's tensor-core rate over its own step time against 2 x the measured dense bf16 peak
-        ach = ops_img * B / (statistics.mean(step_ms) * 1e-3) / 1e12
+        # one rank's rates over its own step time: tensor-core rate against 2 x the measured dense bf16 peak, and the
+        # bytes a layer-by-layer run must move at least against the measured copy bandwidth
+        own_s = statistics.mean(step_ms) * 1e-3
+        ach = ops_img * B / own_s / 1e12
         peak = 2.0 * peaks["bf16_tflops"]
-        line = {
+        gbs = bytes_img * B / own_s / 1e9
+        out = {
             "metric": "resnet50_qasymm8_images_per_s", "value": global_batch / (ms * 1e-3), "unit": "img/s",
-            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-            "scaling": "weak" if args.weak else "strong", "vs_baseline": None, "dtype": "u8*s8->s32->u8", "data": "synthetic",
+            "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": ms, "higher_is_better": True,
+            "scaling": "weak" if weak else "strong", "dtype": "u8*s8->s32->u8", "data": "synthetic",
             "config": {"workload": f"config4: QASYMM8 ResNet-50 v1, 224x224, global batch {global_batch}, per-channel s8 "
                        "weights, batch norm folded, ReLU fused", "per_gpu_batch": B,
                        "l2": "flushed between timed steps (256 MB write)",
@@ -592,32 +638,40 @@ def run_resnet(args):
                        "launch": "eager, one C-ABI call per layer" if graph is None else
                                  "one CUDA graph of the layer calls per step"},
             "int8_tops": ops_img * global_batch / (ms * 1e-3) / 1e12,
-            "gpu_launches": args.steps * net.launches,
+            "gpu_launches": steps * net.launches,
             "roofline": {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TOP/s", "frac": ach / peak,
                          "traffic": None, "peak_source": "2 x " + peaks["source"] + " dense bf16 cuBLAS rate",
-                         "kernel": "whole network (54 convolutions + pooling / addition / softmax kernels)"},
+                         "kernel": "whole network (54 convolutions + pooling / addition / softmax kernels)",
+                         "hbm": {"achieved": gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": gbs / peaks["hbm_gbs"],
+                                 "bytes_counted": "inputs read + output written once per layer, 8-bit activations "
+                                                  f"({bytes_img / 1e6:.1f} MB per image unfused)"}},
             "clocks": clocks}
         if e2e_ms:
-            line["e2e"] = {"value": global_batch / (e2e * 1e-3), "unit": "img/s",
-                           "h2d_bytes_per_step": int(global_batch * 224 * 224 * 3),   # all ranks together
-                           "d2h_bytes_per_step": int(global_batch * 1000)}
-        print(json.dumps(line), flush=True)
+            out["e2e"] = {"value": global_batch / (e2e * 1e-3), "unit": "img/s", "ms_per_step": e2e,
+                          "h2d_bytes_per_step": int(global_batch * 224 * 224 * 3),   # all ranks together
+                          "d2h_bytes_per_step": int(global_batch * 1000)}
     net.close()
     ctx.close()
-    if world > 1:
-        dist.destroy_process_group()
+    torch.cuda.set_stream(prev_stream)
+    return out
 
 
-def run_linear_sharded(args):
+def run_resnet(args):
+    line = measure_resnet(args, args.weak)
+    if line is not None:
+        line["vs_baseline"] = None
+        print(json.dumps(line), flush=True)
+
+
+def measure_linear_sharded(args):
     """Config 5 on N > 1 GPUs: B is split by columns (multiples of the 256-column tile), every rank computes
-    dst[:, n0:n1] with the fused kernel and the int8 column blocks are all-gathered with NCCL."""
+    dst[:, n0:n1]; the int8 column blocks reach every rank either through ncclAllGather (baseline) or by the fused
+    kernel's epilogue storing each tile into all ranks' buffers (push all-gather).  Rank 0 gets the result."""
     import torch
     import torch.distributed as dist
     import computelibrary_b200 as cl
     from computelibrary_b200 import capi, sharding
-    rank, world, local = dist_env()
-    torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    rank, world, local = init_dist(args)
     ctx = cl.Context(local, torch.cuda.current_stream().cuda_stream)
     c = make_gemm_workload("c5", 0)
     M, K = c["a"].shape
@@ -631,6 +685,7 @@ def run_linear_sharded(args):
     d_local = torch.empty((M, n1 - n0), dtype=torch.uint8, device="cuda")
     flush = torch.empty(256 * 1024 * 1024, dtype=torch.uint8, device="cuda")
     full = [None]
+    steps, warmup = min(args.steps, args.net_steps), max(3, min(args.warmup, 5))
 
     def step():
         plan.run(d_a, None, None, d_local)
@@ -640,15 +695,14 @@ def run_linear_sharded(args):
         dist.barrier()
         torch.cuda.synchronize()
 
-    step_ms = _timed_steps(step, args.steps, args.warmup, flush, barrier)
-    gemm_ms = _timed_steps(lambda: plan.run(d_a, None, None, d_local), args.steps, args.warmup, flush, barrier)
+    step_ms = _timed_steps(step, steps, warmup, flush, barrier)
+    gemm_ms = _timed_steps(lambda: plan.run(d_a, None, None, d_local), steps, warmup, flush, barrier)
 
     # ---- fused push all-gather: the epilogue stores each tile into every rank's [M, N] buffer over NVLink ----
-    from computelibrary_b200 import capi as _capi
-    desc_push, keep_push = _capi.make_gemm_desc(
-        M, n1 - n0, K, _capi.S8, _capi.S8, _capi.S8, c["a_off"], c["b_off"], multipliers=cs["mult"],
+    desc_push, keep_push = capi.make_gemm_desc(
+        M, n1 - n0, K, capi.S8, capi.S8, capi.S8, c["a_off"], c["b_off"], multipliers=cs["mult"],
         shifts=cs["shift"], offset=c["offset"], min_bound=c["lo"], max_bound=c["hi"], has_bias=False, ldd=N)
-    plan_push = _capi.GemmPlan(ctx, desc_push, keep_push)
+    plan_push = capi.GemmPlan(ctx, desc_push, keep_push)
     d_bs = torch.from_numpy(cs["b"].view(np.uint8)).cuda()
     plan_push.prepare(d_bs)
     ctx.sync()
@@ -657,17 +711,16 @@ def run_linear_sharded(args):
     dist.all_gather_object(handles, ctx.ipc_get_handle(full_ptr))
     peers = {r: ctx.ipc_open_handle(handles[r]) for r in range(world) if r != rank}
     dsts = [full_ptr + n0] + [peers[r] + n0 for r in sorted(peers)]
-    push_ms = _timed_steps(lambda: plan_push.run_multi(d_a, None, dsts), args.steps, args.warmup, flush, barrier)
+    push_ms = _timed_steps(lambda: plan_push.run_multi(d_a, None, dsts), steps, warmup, flush, barrier)
     ctx.sync()
     barrier()
     # wall time of push steps including the completion barrier a consumer needs
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         plan_push.run_multi(d_a, None, dsts)
         torch.cuda.synchronize()
         dist.barrier()
-    push_wall_ms = (time.perf_counter() - t0) * 1e3 / args.steps
-    import ctypes as _C
+    push_wall_ms = (time.perf_counter() - t0) * 1e3 / steps
     host = np.empty((M, N), np.uint8)
     ctx.d2h(host.ctypes.data, full_ptr, M * N)
     ctx.sync()
@@ -679,28 +732,35 @@ def run_linear_sharded(args):
     lo, hi = chk.clone(), chk.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+    out = None
     if rank == 0:
         ops = 2.0 * M * N * K
-        ms = float(t[2]) / args.steps
-        nccl_ms = float(t[0]) / args.steps
-        recv = (world - 1) * M * (n1 - n0)
-        print(json.dumps({
-            "metric": METRIC, "value": ops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "s8*s8->s32->s8", "data": "synthetic",
+        ms = float(t[2]) / steps
+        nccl_ms = float(t[0]) / steps
+        gemm_only = float(t[1]) / steps
+        sent = (world - 1) * M * (n1 - n0)
+        peaks = load_peaks()
+        # the step cannot be faster than its GEMM share on the tensor cores nor than its bytes over one direction of
+        # this GPU's NVLink ports (measured peer-copy rate of this pool: 770 GB/s)
+        floor_ms = max(ops / world / (2.0 * peaks["bf16_tflops"] * 1e12), sent / 770e9) * 1e3
+        out = {
+            "metric": METRIC, "value": ops / (ms * 1e-3) / 1e12, "unit": UNIT, "n_gpus": world, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong",
+            "dtype": "s8*s8->s32->s8", "data": "synthetic",
             "config": {"workload": c["label"], "sharding": f"columns of B split over {world} ranks "
                        f"({n1 - n0} per rank); fused kernel stores every tile into all ranks' [M,N] buffers "
                        "(push all-gather over NVLink peer stores)",
                        "l2": "flushed between timed steps (256 MB write)"},
+            "push_ms": ms, "nccl_ms": nccl_ms, "gemm_only_ms": gemm_only,
             "push_wall_ms_per_step_incl_sync_and_barrier": float(t[3]),
             "nccl_baseline": {"ms_per_step": nccl_ms, "value": ops / (nccl_ms * 1e-3) / 1e12,
                               "what": "same GEMM + ncclAllGather of the column blocks + re-tile copy"},
-            "gemm_only_ms_per_step": float(t[1]) / args.steps,
-            "nvlink": {"bytes_sent_per_rank": recv, "achieved_gbs_per_direction": recv / (ms * 1e-3) / 1e9,
+            "nvlink": {"bytes_sent_per_rank": sent, "achieved_gbs_per_direction": sent / (ms * 1e-3) / 1e9,
                        "measured_peer_copy_gbs": 770.0},
-            "push_equals_nccl_result": bool(float(t[4]) == 0.0),
+            "roofline": {"bound": "max(tensor, nvlink)", "floor_ms": floor_ms, "frac": floor_ms / ms},
+            "push_equals_nccl": bool(float(t[4]) == 0.0),
             "ranks_agree": bool(int(lo) == int(hi)),
-            "gpu_launches": args.steps * plan_push.launches}), flush=True)
+            "gpu_launches": steps * plan_push.launches}
     barrier()
     for pptr in peers.values():
         ctx.ipc_close_handle(pptr)
@@ -709,7 +769,14 @@ def run_linear_sharded(args):
     plan_push.close()
     plan.close()
     ctx.close()
-    dist.destroy_process_group()
+    return out
+
+
+def run_linear_sharded(args):
+    line = measure_linear_sharded(args)
+    if line is not None:
+        line["vs_baseline"] = None
+        print(json.dumps(line), flush=True)
 
 
 def run_bandwidth(args):
@@ -794,7 +861,8 @@ def main():
     _, world, _ = dist_env()
     if args.impl == "reference":
         run_reference(args)
-    elif args.workload == "bw":
+        return
+    if args.workload == "bw":
         run_bandwidth(args)
     elif args.workload == "c3":
         run_conv(args)
@@ -803,7 +871,33 @@ def main():
     elif args.workload == "c5" and world > 1:
         run_linear_sharded(args)
     else:
-        run_ours(args)
+        line = run_ours(args)
+        if args.workload == "c2" and not args.headline_only and not args.size:
+            # the second half of the metric and the one configuration with a collective, measured in the same
+            # process after the headline: ResNet-50 images/s (strong and weak scaling) and, on several GPUs, the
+            # column-sharded linear layer with its all-gather
+            strong = measure_resnet(args, weak=False)
+            weak = measure_resnet(args, weak=True) if world > 1 else strong
+            linear = measure_linear_sharded(args) if world > 1 else None
+            if line is not None:
+                def brief(r):
+                    return {k: r[k] for k in ("value", "unit", "ms_per_step", "scaling", "int8_tops", "roofline", "e2e",
+                                              "clocks", "gpu_launches", "steps", "warmup") if k in r} | {
+                                                  "batch_per_gpu": r["config"]["per_gpu_batch"], "launch": r["config"]["launch"]}
+                line["resnet50"] = {"metric": "resnet50_qasymm8_images_per_s",
+                                    "workload": strong["config"]["workload"].replace(f"global batch {args.batch}", "batch 256"),
+                                    "strong": brief(strong), "weak": brief(weak),
+                                    "img_per_s": strong["value"], "img_per_s_weak": weak["value"]}
+                if linear is not None:
+                    line["linear_c5"] = {k: linear[k] for k in ("value", "unit", "push_ms", "nccl_ms", "gemm_only_ms",
+                                                                "nvlink", "roofline", "push_equals_nccl", "ranks_agree",
+                                                                "push_wall_ms_per_step_incl_sync_and_barrier")}
+                    line["linear_c5"]["workload"] = linear["config"]["workload"]
+        if line is not None:
+            print(json.dumps(line), flush=True)
+    import torch.distributed as dist
+    if dist.is_available() and dist.is_initialized():
+        dist.destroy_process_group()
 
 
 if __name__ == "__main__":

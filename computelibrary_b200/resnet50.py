@@ -79,6 +79,18 @@ def graph_ops(nodes) -> float:
                      for n in nodes if n["op"] == "conv"))
 
 
+def graph_bytes(nodes) -> float:
+    """Bytes per image a layer-by-layer run has to move at least: every node reads its inputs and writes its output
+    once (8-bit activations), the convolutions also read their weights once per batch (not counted per image)."""
+    total = 0.0
+    for n in nodes:
+        ho, wo, co = n["out_shape"]
+        hi, wi, ci = n["in_shape"]
+        total += ho * wo * co                      # output written
+        total += hi * wi * ci * len(n["inputs"])   # inputs read (the two operands of an addition have equal shapes)
+    return float(total)
+
+
 def synthetic_params(nodes, seed: int = 1, scale_range=(1e-3, 1e-2), bias_range: int = 5000, fan_in_scaled=False):
     """Seeded random parameters per convolution: int8 weights U[-127,127] [OFM,kh,kw,C], per-channel scales
     log-uniform in ``scale_range``, int32 bias U[-bias_range, bias_range].  ``fan_in_scaled`` divides the scales
