@@ -114,6 +114,8 @@ _SIGNATURES = {
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
     "cugl_gemmlowp_run_noalloc": (C.c_int, [_vp, C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_noalloc_status": (C.c_int, [_vp]),
+    "cugl_gemmlowp_plan_set_saturating_pack": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_saturating_pack": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_temp_bytes": (C.c_size_t, [_vp]),
     "cugl_gemmlowp_plan_bind_temp": (C.c_int, [_vp, _vp, C.c_size_t]),
     "cugl_conv2d_update_quantization": (C.c_int, [_vp, C.POINTER(ConvDesc)]),
@@ -494,6 +496,9 @@ class GemmPlan:
     def set_tile_columns(self, columns: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_tile_columns(self.handle, int(columns)))
 
+    def set_saturating_pack(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_saturating_pack(self.handle, int(on)))
+
     def set_paired_drain(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_paired_drain(self.handle, int(on)))
 
@@ -608,6 +613,9 @@ class ConvPlan:
 
     def set_tile_columns(self, columns: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_tile_columns(self.handle, int(columns)))
+
+    def set_saturating_pack(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_saturating_pack(self.handle, int(on)))
 
     def set_paired_drain(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_paired_drain(self.handle, int(on)))

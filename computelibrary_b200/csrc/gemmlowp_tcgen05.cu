@@ -376,19 +376,30 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
 //                   bracket is a 64-bit constant of the column, so one wide multiply-add and one shift replace
 //                   five instructions.  {constant lo, constant hi, multiplier, s-1}.  Equal to the reference
 //                   wherever its own 32-bit sums v+t and x + 2^(s-1) do not overflow.
-constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2;
+//   kStagePack    : kStageWide whose clamp bounds are the whole range of the 8-bit output type (no activation bound
+//                   tighter than the type, the case of every ReLU at zero point 0 and of every plain requantisation).
+//                   The output offset joins the 64-bit column constant -- adding offset * 2^(s-1) before the final
+//                   shift by s-1 equals adding offset after it -- and the clamp becomes the saturation of the
+//                   instruction that packs two results into bytes (cvt.pack.sat): per element one wide multiply-add
+//                   and one shift, per four elements two packs.  Needs s <= 22 with a non-zero offset so that the
+//                   constant stays inside 64 bits.
+constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2, kStagePack = 3;
 constexpr int kIntegerStageFlag = 1 << 16; // generic encoding, bit of q.z: the integer-multiply stage QUANTIZE_DOWN
 
 template <int kMode>
 __device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t row_term, int32_t offset, int32_t lo,
                                                int32_t hi)
 {
-    if (kMode == kStageWide)
+    if (kMode == kStageWide || kMode == kStagePack)
     {
         const long long c64 = static_cast<long long>((static_cast<unsigned long long>(static_cast<uint32_t>(q.y)) << 32) |
                                                      static_cast<uint32_t>(q.x));
         const long long p   = static_cast<long long>(static_cast<int32_t>(v)) * q.z + c64;
         const int32_t   t   = static_cast<int32_t>(p >> 32) >> q.w;
+        if (kMode == kStagePack)
+        {
+            return t; // offset already inside c64; the caller saturates while packing (pack4_sat)
+        }
         return max(__viaddmin_s32(t, offset, hi), lo);
     }
     const int32_t acc = static_cast<int32_t>(v) + q.x + row_term;
@@ -407,6 +418,24 @@ __device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t
     return min(max(t + offset, lo), hi);
 }
 
+// Four int32 results saturated to the 8-bit output type and packed, r0 in the lowest byte.  cvt.pack.sat puts
+// sat(a) into bits 15..8, sat(b) into bits 7..0 and the low half of c into the upper half of the result.
+__device__ __forceinline__ uint32_t pack4_sat(int32_t r0, int32_t r1, int32_t r2, int32_t r3, bool out_signed)
+{
+    uint32_t hi2, w;
+    if (out_signed)
+    {
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(hi2) : "r"(r3), "r"(r2), "r"(0));
+        asm("cvt.pack.sat.s8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi2));
+    }
+    else
+    {
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(hi2) : "r"(r3), "r"(r2), "r"(0));
+        asm("cvt.pack.sat.u8.s32.b32 %0, %1, %2, %3;" : "=r"(w) : "r"(r1), "r"(r0), "r"(hi2));
+    }
+    return w;
+}
+
 template <int kMode>
 __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 *col, int32_t row_term, int32_t offset,
                                                   int32_t lo, int32_t hi)
@@ -416,6 +445,10 @@ __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 
     for (int b = 0; b < 4; ++b)
     {
         r[b] = requant_one<kMode>(v[b], col[b], row_term, offset, lo, hi);
+    }
+    if (kMode == kStagePack)
+    {
+        return pack4_sat(r[0], r[1], r[2], r[3], lo < 0); // lo is the minimum of the output type in this mode
     }
     const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
     const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
@@ -727,7 +760,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
 // (802816 x 256 x 64: 235 us, 134 us with one term read per 32 columns instead of 32).  Here a term is read
 // once for two elements; both residual rows are requested together, after the arithmetic (requesting them while the
 // tensor-memory loads travel measured slower: block-1 conv3 + add 238 -> 284 us).
-template <int NCOLS>
+template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
                                                        const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
                                                        int n_first)
@@ -752,13 +785,21 @@ __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_
             for (int b = 0; b < 4; ++b)
             {
                 const int4 q = col[j + b];
-                ra[b]        = requant_one<kStageWide>(va[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
-                rb[b]        = requant_one<kStageWide>(vb[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
+                ra[b]        = requant_one<kMode>(va[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
+                rb[b]        = requant_one<kMode>(vb[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
             }
-            va[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(ra[0]), static_cast<uint32_t>(ra[1]), 0x0040),
-                                     __byte_perm(static_cast<uint32_t>(ra[2]), static_cast<uint32_t>(ra[3]), 0x0040), 0x5410);
-            vb[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(rb[0]), static_cast<uint32_t>(rb[1]), 0x0040),
-                                     __byte_perm(static_cast<uint32_t>(rb[2]), static_cast<uint32_t>(rb[3]), 0x0040), 0x5410);
+            if (kMode == kStagePack)
+            {
+                va[j >> 2] = pack4_sat(ra[0], ra[1], ra[2], ra[3], ep.lo < 0);
+                vb[j >> 2] = pack4_sat(rb[0], rb[1], rb[2], rb[3], ep.lo < 0);
+            }
+            else
+            {
+                va[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(ra[0]), static_cast<uint32_t>(ra[1]), 0x0040),
+                                         __byte_perm(static_cast<uint32_t>(ra[2]), static_cast<uint32_t>(ra[3]), 0x0040), 0x5410);
+                vb[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(rb[0]), static_cast<uint32_t>(rb[1]), 0x0040),
+                                         __byte_perm(static_cast<uint32_t>(rb[2]), static_cast<uint32_t>(rb[3]), 0x0040), 0x5410);
+            }
         }
         const int nc = n_first + ch * 32;
         if (with_res)
@@ -783,8 +824,18 @@ __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_
     const int      quad  = warp & 3;                                      // tensor-memory lane quarter this warp may read
     const int      half  = kGroups == 1 ? (warp - kFirstEpi) >> 2 : 0;    // which share of the columns
     const uint32_t lanes = static_cast<uint32_t>(quad * 32) << 16;
-    drain_accumulator_pair<NCOLS>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS, s_col + half * NCOLS, tp,
-                                  ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane, n0 + half * NCOLS);
+    if (tp.mode == kStagePack)
+    {
+        drain_accumulator_pair<NCOLS, kStagePack>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
+                                                  s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
+                                                  n0 + half * NCOLS);
+    }
+    else
+    {
+        drain_accumulator_pair<NCOLS, kStageWide>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
+                                                  s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
+                                                  n0 + half * NCOLS);
+    }
 }
 
 // the term of output channel n in the encoding of tp.mode (see requant_pack4)
@@ -813,7 +864,11 @@ __device__ __forceinline__ int4 column_term(int n, const TileParams &tp, const E
     }
     else
     {
-        const long long c64 = static_cast<long long>(t) * q.y + (1ll << (30 + sh));
+        long long c64 = static_cast<long long>(t) * q.y + (1ll << (30 + sh));
+        if (tp.mode == kStagePack)
+        {
+            c64 += static_cast<long long>(ep.result_offset) << (31 + sh); // offset * 2^(s-1), in units of 2^32
+        }
         q.z                 = q.y;
         q.x                 = static_cast<int32_t>(static_cast<uint32_t>(c64));
         q.y                 = static_cast<int32_t>(c64 >> 32);
@@ -880,9 +935,16 @@ __device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], c
         {
             r[b] = requant_one<kMode>(v[4 * j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
         }
-        const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
-        const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
-        stage[j * kCmPitchWords + lane] = __byte_perm(p01, p23, 0x5410);
+        if (kMode == kStagePack)
+        {
+            stage[j * kCmPitchWords + lane] = pack4_sat(r[0], r[1], r[2], r[3], ep.lo < 0);
+        }
+        else
+        {
+            const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
+            const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
+            stage[j * kCmPitchWords + lane] = __byte_perm(p01, p23, 0x5410);
+        }
     }
     __syncwarp();
     const uint4 lo = *reinterpret_cast<const uint4 *>(stage + i * kCmPitchWords + 8 * g);
@@ -975,7 +1037,8 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
 #pragma unroll
         for (int j = 0; j < 32; ++j)
         {
-            const int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+            int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+            if (kMode == kStagePack) y = min(max(y, ep.lo), ep.hi); // no packing instruction here to saturate
             if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(min(max(min(y + static_cast<int>(rs[j]), 255), fl), cp));
         }
     }
@@ -985,7 +1048,8 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
 #pragma unroll
         for (int j = 0; j < 32; ++j)
         {
-            const int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+            int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
+            if (kMode == kStagePack) y = min(max(y, ep.lo), ep.hi); // no packing instruction here to saturate
             if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(y);
         }
     }
@@ -1073,7 +1137,11 @@ __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const T
     }
     const uint32_t t_addr = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NPIX;
     const int      p0     = n0 + half * NPIX;
-    if (tp.mode == kStageWide && !kS32Out)
+    if (tp.mode == kStagePack && !kS32Out)
+    {
+        drain_channel_major<NPIX, kS32Out, kStagePack>(t_addr, q, tp, ep, ch, p0, lane, stage);
+    }
+    else if (tp.mode == kStageWide && !kS32Out)
     {
         drain_channel_major<NPIX, kS32Out, kStageWide>(t_addr, q, tp, ep, ch, p0, lane, stage);
     }
@@ -1102,7 +1170,12 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
     const int     m        = m0 + quad * 32 + lane;
     const int32_t row_term = (ep.rowsum != nullptr && m < tp.M) ? ep.b_off * __ldg(ep.rowsum + m) : 0;
     const uint32_t t_addr  = tmem_acc + (static_cast<uint32_t>(quad * 32) << 16) + half * NCOLS;
-    if (tp.mode == kStageWide && !kS32Out)
+    if (tp.mode == kStagePack && !kS32Out)
+    {
+        drain_accumulator<NCOLS, kS32Out, kStagePack>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
+                                                      stage, lane);
+    }
+    else if (tp.mode == kStageWide && !kS32Out)
     {
         drain_accumulator<NCOLS, kS32Out, kStageWide>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
                                                       stage, lane);
@@ -1407,7 +1480,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const int tile_b   = tile + kStride * static_cast<int>(gridDim.x);
             bool      pair_now = false;
-            if (kCanPair && tp.pair_drain != 0 && tp.mode == kStageWide && as < kStride)
+            if (kCanPair && tp.pair_drain != 0 && (tp.mode == kStageWide || tp.mode == kStagePack) && as < kStride)
             {
                 pair_now = tile_b < num_tiles && tile_b / num_m_blocks == tile / num_m_blocks;
             }
@@ -2135,6 +2208,22 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 
 #endif // CUGL_TC_FULL_BUILD
 
+// encoding of the output stage for this launch (see requant_pack4)
+int stage_mode(const GemmOperands &op, const EpilogueParams &ep)
+{
+    if (op.generic_stage)
+    {
+        return kStageGeneric;
+    }
+    if (!op.wide_stage)
+    {
+        return kStageFast;
+    }
+    const int32_t tlo = ep.out_signed != 0 ? -128 : 0, thi = ep.out_signed != 0 ? 127 : 255;
+    const bool    whole_range = ep.lo == tlo && ep.hi == thi;
+    return (op.pack_stage >= 0 && whole_range && (ep.result_offset == 0 || op.max_shift <= 22)) ? kStagePack : kStageWide;
+}
+
 void fill_extra_dst(TileParams &tp, const GemmOperands &op)
 {
     tp.residual   = static_cast<const uint8_t *>(op.residual);
@@ -2235,7 +2324,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
-    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
+    tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     tp.idesc_half = 0;
@@ -2276,7 +2365,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok  = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 7) == 0;
     tp.status  = ctx->d_status;
-    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
+    tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     tp.idesc_half = 0;
@@ -2320,7 +2409,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.split_tail = op.split_tail >= 0 ? 1 : 0;
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
-    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
+    tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     const int tiles    = ((op.M + 2 * BLOCK_M - 1) / (2 * BLOCK_M)) * ((op.N + P::BLOCK_N - 1) / P::BLOCK_N);
@@ -2374,7 +2463,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
-    tp.mode    = op.generic_stage ? kStageGeneric : (op.wide_stage ? kStageWide : kStageFast);
+    tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
     tp.idesc_half = 0;

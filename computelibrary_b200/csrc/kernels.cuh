@@ -45,6 +45,8 @@ struct GemmOperands
     bool        generic_stage; // some shift is negative or some multiplier is INT32_MIN (decided on the host)
     bool        wide_stage;    // every shift in [2, 31], every multiplier in [0, 2^31), no row-sum term: the
                                // requantisation can use the one-multiply form (kStageWide)
+    int         max_shift;     // largest right shift of the output stage (decides whether the offset fits kStagePack)
+    int         pack_stage;    // < 0: never use the saturating-pack encoding (testing aid); else where it applies
     int         epi_warps;     // tensor-core kernels: 4, 8 or 16 forces that build, anything else lets the dispatcher choose
     // tensor-core kernels, 8-bit unsigned output only: dst = min(max(min(out + residual, 255), res_floor), res_cap)
     // with residual an [M][ldd] byte matrix (the fused residual addition of a convolution), or nullptr

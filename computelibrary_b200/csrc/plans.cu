@@ -55,6 +55,8 @@ struct GemmCore
     bool          allow_pair = true; // SM-pair (cta_group::2) kernel permitted
     bool          generic_stage = false; // a left shift or an INT32_MIN multiplier is present
     bool          wide_stage    = false; // shifts in [2, 31], multipliers in [0, 2^31), no row-sum term
+    int           max_shift     = 0;     // largest right shift of the stage
+    int           pack_stage    = 0;     // < 0: keep off the saturating-pack encoding of the output stage
     int           epi_warps     = 0;     // 4 / 8 force that build of the tensor-core kernels, 0 = automatic
     int           channel_major = 0;     // > 0 / < 0 force / forbid the channel-major kernel, 0 = automatic
     int           split_tail    = 0;     // < 0: the SM-pair kernel keeps the tiles of a short last wave whole
@@ -127,12 +129,14 @@ struct GemmCore
         generic_stage = stage == CUGL_STAGE_QUANTIZE_DOWN || (!per_channel && (shift < 0 || mult == INT32_MIN));
         wide_stage    = stage == CUGL_STAGE_QUANTIZE_DOWN_FIXEDPOINT && b_off == 0 &&
                      (per_channel || (shift >= 2 && shift <= 31 && mult >= 0));
+        max_shift = shift;
         if (!per_channel)
         {
             return CUGL_SUCCESS;
         }
         for (int i = 0; i < N; ++i)
         {
+            max_shift     = h_shifts[i] > max_shift || i == 0 ? h_shifts[i] : max_shift;
             generic_stage = generic_stage || h_shifts[i] < 0 || h_mults[i] == INT32_MIN;
             wide_stage    = wide_stage && h_shifts[i] >= 2 && h_shifts[i] <= 31 && h_mults[i] >= 0;
         }
@@ -226,6 +230,8 @@ struct GemmCore
         op.b_signed = b_signed;
         op.generic_stage = generic_stage;
         op.wide_stage    = wide_stage;
+        op.max_shift     = max_shift;
+        op.pack_stage    = pack_stage;
         op.epi_warps     = epi_warps;
         op.channel_major = channel_major;
         op.split_tail    = split_tail;
@@ -1244,6 +1250,8 @@ extern "C"
             op.b_signed      = c.b_signed;
             op.generic_stage = c.generic_stage;
             op.wide_stage    = c.wide_stage;
+            op.max_shift     = c.max_shift;
+            op.pack_stage    = c.pack_stage;
             op.epi_warps     = c.epi_warps;
             op.channel_major = c.channel_major;
             op.block_n       = c.block_n;
@@ -1491,6 +1499,26 @@ extern "C"
             return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_transpose_batched: bad argument");
         }
         return launch_transpose_bytes(ctx, d_src, rows, cols, d_dst, batch);
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_saturating_pack(cugl_gemm_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_set_saturating_pack: NULL plan");
+        }
+        plan->core.pack_stage = on != 0 ? 0 : -1;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_saturating_pack(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_saturating_pack: NULL plan");
+        }
+        plan->core.pack_stage = on != 0 ? 0 : -1;
+        return CUGL_SUCCESS;
     }
 
     // ---- temporary workspaces (MemoryRequirements with lifetime Temporary, arm_compute/core/experimental/Types.h:89-125)

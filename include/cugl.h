@@ -245,6 +245,12 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_tile_columns(cugl_gemm_plan *plan, i
  * tile on its own.  Testing / measurement aid: the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_paired_drain(cugl_gemm_plan *plan, int on);
 
+/* Output stages whose clamp bounds are the whole range of the 8-bit output type (every shift in [2, 31], or [2, 22]
+ * with a non-zero output offset; non-negative multipliers; no B offset) fold the offset into the per-column constant
+ * and clamp by the saturation of the byte-packing instruction: fewer instructions per output (on by default).
+ * on = 0 keeps the explicit add / min / max form.  Testing / measurement aid: the results are identical. */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_saturating_pack(cugl_gemm_plan *plan, int on);
+
 /* MemoryRequirements of the operator with lifetime Temporary (arm_compute/core/experimental/Types.h:89-125; the
  * VectorSumRow slot of src/cpu/operators/CpuGemmLowpMatrixMultiplyCore.h:144-155): bytes of device memory a run of the
  * plan needs that hold nothing between runs (the row sums of A, only with a non-zero B offset).  By default the plan
@@ -392,6 +398,8 @@ CUGL_API cugl_status cugl_conv2d_update_quantization(cugl_conv_plan *plan, const
  * lowering only -- the im2col matrix (the Im2ColOutput slot of CpuGemmConv2d, src/cpu/operators/CpuGemmConv2d.h). */
 CUGL_API size_t      cugl_conv2d_plan_temp_bytes(const cugl_conv_plan *plan);
 CUGL_API cugl_status cugl_conv2d_plan_bind_temp(cugl_conv_plan *plan, void *d_ws, size_t bytes);
+/* as cugl_gemmlowp_plan_set_saturating_pack, for every lowering of the convolution */
+CUGL_API cugl_status cugl_conv2d_plan_set_saturating_pack(cugl_conv_plan *plan, int on);
 /* Fused residual addition: dst = act(quantize(dequantize(conv) + dequantize(residual))) computed in the epilogue
  * of the convolution, i.e. NEGEMMConvolutionLayer followed by NEArithmeticAddition (ConvertPolicy::SATURATE)
  * and NEActivationLayer (arm_compute/runtime/NEON/functions/NEArithmeticAddition.h:43-109) without the

@@ -463,3 +463,25 @@ def test_validate_rules_of_the_raw_outputs():
     assert capi.gemm_validate(d)[0] == 0
     d, keep = capi.make_gemm_desc(8, 8, 8, capi.S8, capi.S8, capi.S8, multiplier=2 ** 30, shift=1, accumulate=True)
     assert capi.gemm_validate(d)[0] == 6            # accumulation only without an output stage
+
+
+@pytest.mark.parametrize("out_dtype,offset", [(np.uint8, 0), (np.uint8, 7), (np.int8, 0), (np.int8, -11)])
+@pytest.mark.parametrize("M,N,K,epi", [(300, 256, 64, 0), (257, 512, 192, 0), (520, 320, 2048, 0), (130, 64, 96, 8), (1000, 256, 512, 1)])
+def test_saturating_pack_encoding(ctx, port, out_dtype, offset, M, N, K, epi):
+    """Whole-type-range clamps run on the saturating-pack encoding of the output stage (offset folded into the column
+    constant, cvt.pack.sat as the clamp): identical to the explicit encoding and to the oracle, for results far
+    outside the type range on both sides, shifts up to the limit of the encoding and beyond it."""
+    rng = np.random.default_rng(M + N + K + offset)
+    a_dt = np.uint8 if out_dtype == np.uint8 else np.int8
+    a, b = q8_uniform(rng, (M, K), a_dt), q8_uniform(rng, (K, N), np.int8, -127, 127)
+    bias = rng.integers(-400000, 400001, N).astype(np.int32)   # drives many results beyond both ends of the range
+    mult = rng.integers(2 ** 30, 2 ** 31 - 1, N).astype(np.int32)
+    lo, hi = type_range(out_dtype)
+    for max_shift in (12, 22, 24):
+        shift = rng.integers(2, max_shift + 1, N).astype(np.int32)
+        shift[0] = max_shift
+        want = port.gemmlowp_fused(a, b, bias, 3, 0, mult, shift, offset, lo, hi, out_dtype)
+        kw = dict(channel_major=1) if epi == 1 else dict(epi_warps=epi)
+        got, _ = gpu_gemmlowp(ctx, a, b, bias, 3, 0, mult, shift, offset, lo, hi, out_dtype, **kw)
+        ref, _ = gpu_gemmlowp(ctx, a, b, bias, 3, 0, mult, shift, offset, lo, hi, out_dtype, saturating_pack=False, **kw)
+        assert np.array_equal(got, want) and np.array_equal(ref, want), max_shift
