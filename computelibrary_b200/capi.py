@@ -3,6 +3,7 @@ GPU raises -- nothing here computes on the CPU."""
 from __future__ import annotations
 
 import ctypes as C
+import weakref
 import os
 import re
 
@@ -10,6 +11,8 @@ from . import build as _build
 
 U8, S8, S32, S16, F32 = 0, 1, 2, 3, 4  # S16: QSYMM16 (stand-alone stage only); F32: dequantized GEMM output
 STAGE_NONE, STAGE_QUANTIZE_DOWN, STAGE_FIXEDPOINT = 0, 1, 2
+# cugl_status values the tests name
+SUCCESS, RUNTIME_ERROR, INVALID_ARGUMENT = 0, 1, 6
 INT32_MIN, INT32_MAX = -(2 ** 31), 2 ** 31 - 1
 
 _vp = C.c_void_p
@@ -84,6 +87,8 @@ _SIGNATURES = {
     "cugl_context_device": (C.c_int, [_vp]),
     "cugl_context_sm_count": (C.c_int, [_vp]),
     "cugl_context_set_trace_buffer": (C.c_int, [_vp, _vp]),
+    "cugl_context_set_wait_limit_us": (C.c_int, [_vp, C.c_uint64]),
+    "cugl_context_withhold_copy_once": (C.c_int, [_vp, C.c_int]),
     "cugl_malloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "cugl_free": (C.c_int, [_vp, _vp]),
     "cugl_host_alloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
@@ -114,6 +119,7 @@ _SIGNATURES = {
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
     "cugl_gemmlowp_run_noalloc": (C.c_int, [_vp, C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_noalloc_status": (C.c_int, [_vp]),
+    "cugl_memcpy_d2d": (C.c_int, [_vp, _vp, _vp, C.c_size_t]),
     "cugl_gemmlowp_plan_set_saturating_pack": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_saturating_pack": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_temp_bytes": (C.c_size_t, [_vp]),
@@ -237,10 +243,15 @@ class Context:
         h = _vp()
         arg = _vp(-1 & (2 ** 64 - 1)) if stream is None else _vp(stream)  # CUGL_STREAM_CREATE
         _check(self.lib.cugl_context_create(device, arg, C.byref(h)))
+        self._plans = weakref.WeakSet()  # live GemmPlan / ConvPlan objects of this context, see close()
         self.handle = h
 
     def close(self):
         if getattr(self, "handle", None):
+            # plans hold a pointer to the context: destroy the ones still alive first, whatever order the garbage
+            # collector would have picked
+            for plan in list(getattr(self, "_plans", ())):
+                plan.close()
             self.lib.cugl_context_destroy(self.handle)
             self.handle = None
 
@@ -255,6 +266,14 @@ class Context:
 
     def set_trace_buffer(self, buf):
         self.check(self.lib.cugl_context_set_trace_buffer(self.handle, _dptr(buf)))
+
+    def set_wait_limit_us(self, microseconds: int):
+        """Bound of every device-side barrier wait of the tensor-core kernels (0: the two-second default)."""
+        self.check(self.lib.cugl_context_set_wait_limit_us(self.handle, int(microseconds)))
+
+    def withhold_copy_once(self, k_block: int):
+        """Test instrument: the next tensor-core GEMM launch leaves out one operand copy in CTA 0."""
+        self.check(self.lib.cugl_context_withhold_copy_once(self.handle, int(k_block)))
 
     def sync(self):
         self.check(self.lib.cugl_sync(self.handle))
@@ -456,6 +475,7 @@ class GemmPlan:
         h = _vp()
         ctx.check(ctx.lib.cugl_gemmlowp_plan_create(ctx.handle, C.byref(desc), C.byref(h)))
         self.handle = h
+        ctx._plans.add(self)
 
     def close(self):
         if getattr(self, "handle", None):
@@ -567,6 +587,7 @@ class ConvPlan:
         h = _vp()
         ctx.check(ctx.lib.cugl_conv2d_plan_create(ctx.handle, C.byref(desc), C.byref(h)))
         self.handle = h
+        ctx._plans.add(self)
 
     def close(self):
         if getattr(self, "handle", None):

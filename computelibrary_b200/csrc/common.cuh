@@ -19,6 +19,8 @@ struct cugl_context
     int32_t     *d_status    = nullptr; // device word written by kernels whose bounded waits ran out
     int32_t     *h_status    = nullptr; // pinned mirror read in cugl_sync
     long long   *d_trace     = nullptr; // optional event-timestamp buffer for the tensor-core GEMM kernels
+    long long    spin_limit  = 4000000000ll; // clock64 ticks a device-side wait may last (about two seconds)
+    int          withhold_kb = -1;      // one-shot test instrument, see cugl_context_withhold_copy_once
     std::string  last_error;
 };
 

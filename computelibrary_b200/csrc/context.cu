@@ -238,6 +238,17 @@ extern "C"
         return CUGL_SUCCESS;
     }
 
+    cugl_status cugl_memcpy_d2d(cugl_context *ctx, void *d_dst, const void *d_src, size_t bytes)
+    {
+        CUGL_NEED_CTX(ctx);
+        if (bytes == 0)
+        {
+            return CUGL_SUCCESS;
+        }
+        CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(d_dst, d_src, bytes, cudaMemcpyDeviceToDevice, ctx->stream));
+        return CUGL_SUCCESS;
+    }
+
     cugl_status cugl_memcpy2d_h2d(cugl_context *ctx, void *d_dst, size_t d_pitch, const void *h_src, size_t h_pitch,
                                   size_t width_bytes, size_t rows)
     {
@@ -279,6 +290,31 @@ extern "C"
     {
         CUGL_NEED_CTX(ctx);
         ctx->d_trace = static_cast<long long *>(d_buffer);
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_context_set_wait_limit_us(cugl_context *ctx, uint64_t microseconds)
+    {
+        CUGL_NEED_CTX(ctx);
+        if (microseconds == 0)
+        {
+            ctx->spin_limit = cugl_context{}.spin_limit;
+            return CUGL_SUCCESS;
+        }
+        int khz = 0; // clock64 counts SM clocks: convert at the device's peak rate, the limit is an upper bound
+        CUGL_CUDA_TRY(ctx, cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->device));
+        ctx->spin_limit = static_cast<long long>(microseconds) * khz / 1000;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_context_withhold_copy_once(cugl_context *ctx, int k_block)
+    {
+        CUGL_NEED_CTX(ctx);
+        if (k_block < 0)
+        {
+            return fail(ctx, CUGL_INVALID_ARGUMENT, "cugl_context_withhold_copy_once: k_block must be >= 0");
+        }
+        ctx->withhold_kb = k_block;
         return CUGL_SUCCESS;
     }
 

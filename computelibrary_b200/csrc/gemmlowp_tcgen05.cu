@@ -59,7 +59,6 @@ static_assert(kEpiWarps == 4 || kEpiWarps == 8 || kEpiWarps == 16, "epilogue war
 // the kernels for short K and wide outputs, whose epilogue wants the most latency hiding.
 #define CUGL_TC_FULL_BUILD (CUGL_EPI_WARPS <= 8)
 constexpr int      A_STAGE     = BLOCK_M * BLOCK_K;
-constexpr long long kSpinLimit = 4000000000ll; // clock64 ticks, about two seconds
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p)
 {
@@ -93,7 +92,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return ok != 0;
 }
 // Bounded wait.  Returns false when the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code)
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code, long long limit)
 {
     if (mbar_try_wait(bar, parity))
     {
@@ -109,7 +108,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
             {
                 return false;
             }
-            if (clock64() - t0 > kSpinLimit)
+            if (clock64() - t0 > limit)
             {
                 *abort_flag = code;
                 return false;
@@ -284,6 +283,9 @@ struct TileParams
     int32_t *status;
     int      raw_f32, raw_accumulate; // stage NONE: float destination / dst += result (EpilogueParams::out_f32, accumulate)
     float    raw_scale;               // dequantization scale of a float destination
+    long long spin_limit;             // clock64 ticks a wait on a barrier may last before the kernel gives up
+    int      withhold_kb;             // >= 0: CTA 0 leaves out the copies of this k-block ordinal (test instrument
+                                      // of the give-up path, cugl_context_withhold_copy_once); -1 otherwise
 };
 
 
@@ -383,20 +385,20 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t bar)
 //                   instruction that packs two results into bytes (cvt.pack.sat): per element one wide multiply-add
 //                   and one shift, per four elements two packs.  Needs s <= 22 with a non-zero offset so that the
 //                   constant stays inside 64 bits.
-constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2, kStagePack = 3;
+constexpr int kStageGeneric = 0, kStageFast = 1, kStageWide = 2, kStagePack = 3, kStagePackS = 4; // 3: uint8, 4: int8 output
 constexpr int kIntegerStageFlag = 1 << 16; // generic encoding, bit of q.z: the integer-multiply stage QUANTIZE_DOWN
 
 template <int kMode>
 __device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t row_term, int32_t offset, int32_t lo,
                                                int32_t hi)
 {
-    if (kMode == kStageWide || kMode == kStagePack)
+    if (kMode == kStageWide || kMode == kStagePack || kMode == kStagePackS)
     {
         const long long c64 = static_cast<long long>((static_cast<unsigned long long>(static_cast<uint32_t>(q.y)) << 32) |
                                                      static_cast<uint32_t>(q.x));
         const long long p   = static_cast<long long>(static_cast<int32_t>(v)) * q.z + c64;
         const int32_t   t   = static_cast<int32_t>(p >> 32) >> q.w;
-        if (kMode == kStagePack)
+        if (kMode == kStagePack || kMode == kStagePackS)
         {
             return t; // offset already inside c64; the caller saturates while packing (pack4_sat)
         }
@@ -420,7 +422,8 @@ __device__ __forceinline__ int32_t requant_one(uint32_t v, const int4 q, int32_t
 
 // Four int32 results saturated to the 8-bit output type and packed, r0 in the lowest byte.  cvt.pack.sat puts
 // sat(a) into bits 15..8, sat(b) into bits 7..0 and the low half of c into the upper half of the result.
-__device__ __forceinline__ uint32_t pack4_sat(int32_t r0, int32_t r1, int32_t r2, int32_t r3, bool out_signed)
+template <bool out_signed>
+__device__ __forceinline__ uint32_t pack4_sat(int32_t r0, int32_t r1, int32_t r2, int32_t r3)
 {
     uint32_t hi2, w;
     if (out_signed)
@@ -446,9 +449,9 @@ __device__ __forceinline__ uint32_t requant_pack4(const uint32_t *v, const int4 
     {
         r[b] = requant_one<kMode>(v[b], col[b], row_term, offset, lo, hi);
     }
-    if (kMode == kStagePack)
+    if (kMode == kStagePack || kMode == kStagePackS)
     {
-        return pack4_sat(r[0], r[1], r[2], r[3], lo < 0); // lo is the minimum of the output type in this mode
+        return pack4_sat<kMode == kStagePackS>(r[0], r[1], r[2], r[3]);
     }
     const uint32_t p01 = __byte_perm(static_cast<uint32_t>(r[0]), static_cast<uint32_t>(r[1]), 0x0040);
     const uint32_t p23 = __byte_perm(static_cast<uint32_t>(r[2]), static_cast<uint32_t>(r[3]), 0x0040);
@@ -671,13 +674,40 @@ __device__ __forceinline__ void prefetch_residual(const TileParams &tp, int m, i
     }
 }
 
+// Hand-back of accumulator buffers to the MMA issuer.  A warp may give its share of a buffer back as soon as its last
+// tcgen05.ld from it has completed -- the values are in registers then -- so the arithmetic and the stores of the last
+// chunk overlap the MMAs of the tile that reuses the buffer.  bar_a / bar_b: shared::cta addresses of the buffers'
+// "empty" barriers (0: none); cluster: bar_a is a shared::cluster address (the leader CTA's barrier, SM-pair kernel).
+struct AccRelease
+{
+    uint32_t bar_a, bar_b;
+    bool     cluster;
+};
+__device__ __forceinline__ void release_accumulators(const AccRelease &r, int lane)
+{
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0)
+    {
+        if (r.cluster)
+        {
+            mbar_arrive_cluster(r.bar_a);
+        }
+        else
+        {
+            if (r.bar_a != 0) mbar_arrive(r.bar_a);
+            if (r.bar_b != 0) mbar_arrive(r.bar_b);
+        }
+    }
+}
+
 // Shared epilogue of both kernels: one warp drains NCOLS consecutive columns (a multiple of 32) of its
 // 32 accumulator rows from tensor memory, applies the offset / bias terms and the output stage, and
 // stores.  The tensor-memory load of chunk i+1 is issued before chunk i is processed.
 template <int NCOLS, bool kS32Out, int kMode>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s_col, const TileParams &tp,
                                                   const EpilogueParams &ep, int m, int n_first, int32_t row_term,
-                                                  uint8_t *stage, int lane)
+                                                  uint8_t *stage, int lane, const AccRelease &rel)
 {
     const bool row_ok = m < tp.M;
     const int64_t row_off = static_cast<int64_t>(m) * tp.ldd;
@@ -692,6 +722,10 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         if (ch + 1 < NCOLS / 32)
         {
             tmem_ld_x32(t_addr + (ch + 1) * 32, vb);
+        }
+        else
+        {
+            release_accumulators(rel, lane); // nothing more to read from tensor memory
         }
         const bool with_res = !kS32Out && tp.residual != nullptr; // warp-uniform
         process_chunk<kS32Out, kMode>(va, s_col + ch * 32, row_term, ep);
@@ -725,6 +759,10 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             if (ch + 2 < NCOLS / 32)
             {
                 tmem_ld_x32(t_addr + (ch + 2) * 32, va);
+            }
+            else
+            {
+                release_accumulators(rel, lane);
             }
             process_chunk<kS32Out, kMode>(vb, s_col + (ch + 1) * 32, row_term, ep);
             if (with_res)
@@ -763,7 +801,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
 template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
                                                        const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
-                                                       int n_first)
+                                                       int n_first, int lane, const AccRelease &rel)
 {
     const bool    ok_a   = ma < tp.M, ok_b = mb < tp.M;
     const int64_t off_a  = static_cast<int64_t>(ma) * tp.ldd;
@@ -777,6 +815,10 @@ __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_
         tmem_ld_x32(t_a + ch * 32, va);
         tmem_ld_x32(t_b + ch * 32, vb);
         tmem_ld_wait();
+        if (ch == NCOLS / 32 - 1)
+        {
+            release_accumulators(rel, lane); // both buffers: the MMAs of the next two tiles overlap this last chunk
+        }
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
         {
@@ -788,10 +830,10 @@ __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_
                 ra[b]        = requant_one<kMode>(va[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
                 rb[b]        = requant_one<kMode>(vb[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
             }
-            if (kMode == kStagePack)
+            if (kMode == kStagePack || kMode == kStagePackS)
             {
-                va[j >> 2] = pack4_sat(ra[0], ra[1], ra[2], ra[3], ep.lo < 0);
-                vb[j >> 2] = pack4_sat(rb[0], rb[1], rb[2], rb[3], ep.lo < 0);
+                va[j >> 2] = pack4_sat<kMode == kStagePackS>(ra[0], ra[1], ra[2], ra[3]);
+                vb[j >> 2] = pack4_sat<kMode == kStagePackS>(rb[0], rb[1], rb[2], rb[3]);
             }
             else
             {
@@ -818,7 +860,7 @@ __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_
 template <int BLOCK_N, int kGroups>
 __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_t tmem_b, const int4 *s_col,
                                                         const TileParams &tp, const EpilogueParams &ep, int warp,
-                                                        int lane, int m0a, int m0b, int n0)
+                                                        int lane, int m0a, int m0b, int n0, const AccRelease &rel)
 {
     constexpr int  NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
     const int      quad  = warp & 3;                                      // tensor-memory lane quarter this warp may read
@@ -828,13 +870,19 @@ __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_
     {
         drain_accumulator_pair<NCOLS, kStagePack>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                  n0 + half * NCOLS);
+                                                  n0 + half * NCOLS, lane, rel);
+    }
+    else if (tp.mode == kStagePackS)
+    {
+        drain_accumulator_pair<NCOLS, kStagePackS>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
+                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
+                                                   n0 + half * NCOLS, lane, rel);
     }
     else
     {
         drain_accumulator_pair<NCOLS, kStageWide>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                  n0 + half * NCOLS);
+                                                  n0 + half * NCOLS, lane, rel);
     }
 }
 
@@ -865,7 +913,7 @@ __device__ __forceinline__ int4 column_term(int n, const TileParams &tp, const E
     else
     {
         long long c64 = static_cast<long long>(t) * q.y + (1ll << (30 + sh));
-        if (tp.mode == kStagePack)
+        if (tp.mode == kStagePack || tp.mode == kStagePackS)
         {
             c64 += static_cast<long long>(ep.result_offset) << (31 + sh); // offset * 2^(s-1), in units of 2^32
         }
@@ -935,9 +983,9 @@ __device__ __forceinline__ void store_chunk_cm_staged(const uint32_t (&v)[32], c
         {
             r[b] = requant_one<kMode>(v[4 * j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
         }
-        if (kMode == kStagePack)
+        if (kMode == kStagePack || kMode == kStagePackS)
         {
-            stage[j * kCmPitchWords + lane] = pack4_sat(r[0], r[1], r[2], r[3], ep.lo < 0);
+            stage[j * kCmPitchWords + lane] = pack4_sat<kMode == kStagePackS>(r[0], r[1], r[2], r[3]);
         }
         else
         {
@@ -1038,7 +1086,7 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
         for (int j = 0; j < 32; ++j)
         {
             int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
-            if (kMode == kStagePack) y = min(max(y, ep.lo), ep.hi); // no packing instruction here to saturate
+            if (kMode == kStagePack || kMode == kStagePackS) y = min(max(y, ep.lo), ep.hi); // no packing instruction here to saturate
             if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(min(max(min(y + static_cast<int>(rs[j]), 255), fl), cp));
         }
     }
@@ -1049,7 +1097,7 @@ __device__ __forceinline__ void store_chunk_cm(const uint32_t (&v)[32], const in
         for (int j = 0; j < 32; ++j)
         {
             int y = requant_one<kMode>(v[j], q, 0, ep.result_offset, ep.lo, ep.hi);
-            if (kMode == kStagePack) y = min(max(y, ep.lo), ep.hi); // no packing instruction here to saturate
+            if (kMode == kStagePack || kMode == kStagePackS) y = min(max(y, ep.lo), ep.hi); // no packing instruction here to saturate
             if (j < np) o[j * tp.ldd] = static_cast<uint8_t>(y);
         }
     }
@@ -1141,6 +1189,10 @@ __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const T
     {
         drain_channel_major<NPIX, kS32Out, kStagePack>(t_addr, q, tp, ep, ch, p0, lane, stage);
     }
+    else if (tp.mode == kStagePackS && !kS32Out)
+    {
+        drain_channel_major<NPIX, kS32Out, kStagePackS>(t_addr, q, tp, ep, ch, p0, lane, stage);
+    }
     else if (tp.mode == kStageWide && !kS32Out)
     {
         drain_channel_major<NPIX, kS32Out, kStageWide>(t_addr, q, tp, ep, ch, p0, lane, stage);
@@ -1161,7 +1213,7 @@ __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const T
 template <int BLOCK_N, bool kS32Out, int kGroups = 1>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4 *s_col, const TileParams &tp,
                                                    const EpilogueParams &ep, int warp, int lane, int m0, int n0,
-                                                   uint8_t *out_stage)
+                                                   uint8_t *out_stage, const AccRelease &rel)
 {
     constexpr int NCOLS    = BLOCK_N * kGroups / (kEpiWarps / 4);
     uint8_t      *stage    = out_stage + (warp - kFirstEpi) * kOutStageBytes;
@@ -1173,22 +1225,27 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
     if (tp.mode == kStagePack && !kS32Out)
     {
         drain_accumulator<NCOLS, kS32Out, kStagePack>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                      stage, lane);
+                                                      stage, lane, rel);
+    }
+    else if (tp.mode == kStagePackS && !kS32Out)
+    {
+        drain_accumulator<NCOLS, kS32Out, kStagePackS>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
+                                                       stage, lane, rel);
     }
     else if (tp.mode == kStageWide && !kS32Out)
     {
         drain_accumulator<NCOLS, kS32Out, kStageWide>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                      stage, lane);
+                                                      stage, lane, rel);
     }
     else if (tp.mode == kStageGeneric)
     {
         drain_accumulator<NCOLS, kS32Out, kStageGeneric>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS,
-                                                         row_term, stage, lane);
+                                                         row_term, stage, lane, rel);
     }
     else
     {
         drain_accumulator<NCOLS, kS32Out, kStageFast>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                      stage, lane);
+                                                      stage, lane, rel);
     }
 }
 
@@ -1229,7 +1286,10 @@ __global__ void __launch_bounds__(kThreads, 1)
 {
     using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the 1024-byte aligned start of the dynamic shared memory, derived by pointer arithmetic on the __shared__ array
+    // itself: a pointer rebuilt from an integer loses its address space and every access through it becomes a
+    // generic load / store (slower, and tracked like a global access) instead of LDS / STS
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const uint32_t sA       = smem_u32(smem + P::OFF_A);
     const uint32_t sB       = smem_u32(smem + P::OFF_B);
@@ -1300,7 +1360,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t ph = static_cast<uint32_t>(issuer / STAGES) & 1u;
             for (int g = issuer; g < total_kb; g += kProdLanes)
             {
-                ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
+                ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER, tp.spin_limit);
                 if (!ok)
                 {
                     break;
@@ -1309,16 +1369,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int m0   = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
                 const int n0   = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
                 if (kb == 0) trace_event(tp.trace, ti, 0);
-                mbar_expect_tx(full_bar(st), P::STAGE);
-#pragma unroll
-                for (int sub = 0; sub < KSUB; ++sub)
+                if (g != tp.withhold_kb || blockIdx.x != 0)
                 {
-                    const int k0 = (kb * KSUB + sub) * BLOCK_K; // beyond K: the copy delivers zeros
-                    tma_load_2d(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, full_bar(st));
-                    tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
+                    mbar_expect_tx(full_bar(st), P::STAGE);
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub)
+                    {
+                        const int k0 = (kb * KSUB + sub) * BLOCK_K; // beyond K: the copy delivers zeros
+                        tma_load_2d(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, full_bar(st));
+                        tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
+                    }
+                    issued |= 1u << st;
+                    parities = (parities & ~(1u << st)) | (ph << st);
                 }
-                issued |= 1u << st;
-                parities = (parities & ~(1u << st)) | (ph << st);
                 // advance g by kProdLanes
                 kb += kProdLanes;
                 while (kb >= num_kb)
@@ -1343,7 +1406,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         const long long t0 = clock64();
                         while (!mbar_try_wait(full_bar(i), (parities >> i) & 1u))
                         {
-                            if (clock64() - t0 > kSpinLimit / 4)
+                            if (clock64() - t0 > tp.spin_limit)
                             {
                                 *s_abort = DEV_TIMEOUT_DRAIN;
                                 break;
@@ -1370,7 +1433,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti)
             {
-                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
+                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
                 if (!ok)
                 {
                     break;
@@ -1384,7 +1447,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (!have)
                     {
                         const long long w0 = tp.trace != nullptr ? clock64() : 0;
-                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
                         if (tp.trace != nullptr) waited += clock64() - w0;
                         if (!ok)
                         {
@@ -1480,7 +1543,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const int tile_b   = tile + kStride * static_cast<int>(gridDim.x);
             bool      pair_now = false;
-            if (kCanPair && tp.pair_drain != 0 && (tp.mode == kStageWide || tp.mode == kStagePack) && as < kStride)
+            if (kCanPair && tp.pair_drain != 0 && (tp.mode == kStageWide || tp.mode == kStagePack || tp.mode == kStagePackS) && as < kStride)
             {
                 pair_now = tile_b < num_tiles && tile_b / num_m_blocks == tile / num_m_blocks;
             }
@@ -1496,41 +1559,35 @@ __global__ void __launch_bounds__(kThreads, 1)
                     prefetch_residual(tp, m0b + row, first, NCOLS);
                 }
             }
-            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE, tp.spin_limit));
             if (ok && pair_now)
             {
-                ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as + kStride), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+                ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as + kStride), aph, s_abort, DEV_TIMEOUT_EPILOGUE, tp.spin_limit));
             }
             if (ok)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
+                // one arrival per warp and buffer, made inside the drain as soon as the warp's last load has landed
+                const AccRelease rel{tempty_bar(as), pair_now ? tempty_bar(as + kStride) : 0u, false};
                 if (kCM)
                 {
                     epilogue_warp_tile_cm<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, tp, ep, warp, lane, m0, n0,
                                                             smem + P::OFF_OUT);
+                    release_accumulators(rel, lane);
                 }
                 else if (kCanPair && pair_now)
                 {
                     epilogue_warp_tile_pair<BLOCK_N, kGroups>(tmem_base + as * BLOCK_N, tmem_base + (as + kStride) * BLOCK_N,
-                                                              g_col, tp, ep, warp, lane, m0, m0b, n0);
+                                                              g_col, tp, ep, warp, lane, m0, m0b, n0, rel);
                 }
                 else
                 {
                     epilogue_warp_tile<BLOCK_N, kS32Out, kGroups>(tmem_base + as * BLOCK_N, g_col, tp, ep, warp, lane,
-                                                                  m0, n0, smem + P::OFF_OUT);
+                                                                  m0, n0, smem + P::OFF_OUT, rel);
                 }
-                tc_fence_before();
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
-                if (lane == 0)
-                {
-                    mbar_arrive(tempty_bar(as)); // accumulator buffer may be overwritten (one arrival per warp)
-                    if (pair_now)
-                    {
-                        mbar_arrive(tempty_bar(as + kStride));
-                    }
-                }
                 if (pair_now)
                 {
                     skip = ti + kStride;
@@ -1593,7 +1650,10 @@ __global__ void __launch_bounds__(kThreads, 1)
     using P               = SmemPlan2<STAGES, KSUB>;
     constexpr int BLOCK_N = P::BLOCK_N;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the 1024-byte aligned start of the dynamic shared memory, derived by pointer arithmetic on the __shared__ array
+    // itself: a pointer rebuilt from an integer loses its address space and every access through it becomes a
+    // generic load / store (slower, and tracked like a global access) instead of LDS / STS
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const uint32_t sA         = smem_u32(smem + P::OFF_A);
     const uint32_t sB         = smem_u32(smem + P::OFF_B);
@@ -1674,7 +1734,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t ph = static_cast<uint32_t>(issuer / STAGES) & 1u;
             for (int g = issuer; g < total_kb; g += kProdLanes)
             {
-                if (!mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER))
+                if (!mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER, tp.spin_limit))
                 {
                     break;
                 }
@@ -1686,13 +1746,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                                          : half * (BLOCK_N / 2) + static_cast<int>(rank) * (BLOCK_N / 4));
                 if (kb == 0) trace_event(tp.trace, ti, 0);
                 const uint32_t leader_full = map_to_cta(full_bar(st), 0);
-                if (leader)
+                const bool     withheld    = g == tp.withhold_kb && blockIdx.x == 0; // the leader of cluster 0
+                if (leader && !withheld)
                 {
                     // the bytes of both CTAs
                     mbar_expect_tx(full_bar(st), half < 0 ? 2 * P::STAGE : 2 * (P::A_STAGE_K + P::B_STAGE / 2));
                 }
 #pragma unroll
-                for (int sub = 0; sub < KSUB; ++sub)
+                for (int sub = 0; sub < KSUB && !withheld; ++sub)
                 {
                     const int k0 = (kb * KSUB + sub) * BLOCK_K;
                     tma_load_2d_pair(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, leader_full);
@@ -1729,7 +1790,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             for (int item = first_tile; item < num_items && ok; item += tile_stride, ++ti)
             {
                 const uint32_t idesc = item_half(item) < 0 ? tp.idesc : tp.idesc_half;
-                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
+                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
                 if (!ok)
                 {
                     break;
@@ -1743,7 +1804,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (!have)
                     {
                         const long long w0 = tp.trace != nullptr ? clock64() : 0;
-                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
                         if (tp.trace != nullptr) waited += clock64() - w0;
                         if (!ok)
                         {
@@ -1818,28 +1879,24 @@ __global__ void __launch_bounds__(kThreads, 1)
                 filled_n0 = n0;
                 epi_barrier();
             }
-            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE, tp.spin_limit));
             if (ok)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
+                const AccRelease rel{map_to_cta(tempty_bar(as), 0), 0u, true}; // one arrival per warp, at the leader
                 if (half < 0)
                 {
                     epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                         smem + P::OFF_OUT);
+                                                         smem + P::OFF_OUT, rel);
                 }
                 else
                 {
                     epilogue_warp_tile<BLOCK_N / 2, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                             smem + P::OFF_OUT);
+                                                             smem + P::OFF_OUT, rel);
                 }
-                tc_fence_before();
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
-                if (lane == 0)
-                {
-                    mbar_arrive_cluster(map_to_cta(tempty_bar(as), 0)); // one arrival per warp, at the leader
-                }
             }
             if (++as == 2)
             {
@@ -1907,7 +1964,10 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 {
     using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
     extern __shared__ uint8_t smem_raw[];
-    uint8_t *smem = reinterpret_cast<uint8_t *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    // the 1024-byte aligned start of the dynamic shared memory, derived by pointer arithmetic on the __shared__ array
+    // itself: a pointer rebuilt from an integer loses its address space and every access through it becomes a
+    // generic load / store (slower, and tracked like a global access) instead of LDS / STS
+    uint8_t *smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
     const uint32_t sA         = smem_u32(smem + P::OFF_A);
     const uint32_t sB         = smem_u32(smem + P::OFF_B);
@@ -1980,7 +2040,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 bool      ok   = true;
                 for (int kb = 0; kb < num_kb && ok; ++kb)
                 {
-                    ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
+                    ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER, tp.spin_limit);
                     if (!ok) break;
                     mbar_expect_tx(full_bar(st), P::B_STAGE);
 #pragma unroll
@@ -2012,7 +2072,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
             for (int ti = 0; ti < my_tiles && ok; ++ti)
             {
-                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA);
+                ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
                 if (!ok) break;
                 tc_fence_after();
                 trace_event(tp.trace, ti, 1);
@@ -2021,7 +2081,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 {
                     if (!have)
                     {
-                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA);
+                        ok = mbar_wait(full_bar(s), ph, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
                         if (!ok) break;
                     }
                     if (kb == 0) trace_event(tp.trace, ti, 2);
@@ -2098,20 +2158,16 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 if (kGroups == 1) epi_barrier();
                 else epi_group_barrier(group);
             }
-            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE));
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE, tp.spin_limit));
             if (ok)
             {
                 tc_fence_after();
                 if (et == 0) trace_event(tp.trace, ti, 4);
+                const AccRelease rel{tempty_bar(as), 0u, false};
                 epilogue_warp_tile<BLOCK_N, false, kGroups>(tmem_base + as * BLOCK_N, g_col, tp, ep, warp, lane, m0, n0,
-                                                            smem + P::OFF_OUT);
+                                                            smem + P::OFF_OUT, rel);
                 if (et == 0) trace_event(tp.trace, ti, 5);
-                tc_fence_before();
                 __syncwarp();
-                if (lane == 0)
-                {
-                    mbar_arrive(tempty_bar(as));
-                }
             }
         }
     }
@@ -2151,7 +2207,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             {
                 if (lane == 0)
                 {
-                    ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER);
+                    ok = mbar_wait(empty_bar(st), ph ^ 1, s_abort, DEV_TIMEOUT_PRODUCER, tp.spin_limit);
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
                 if (!ok) break;
@@ -2221,7 +2277,11 @@ int stage_mode(const GemmOperands &op, const EpilogueParams &ep)
     }
     const int32_t tlo = ep.out_signed != 0 ? -128 : 0, thi = ep.out_signed != 0 ? 127 : 255;
     const bool    whole_range = ep.lo == tlo && ep.hi == thi;
-    return (op.pack_stage >= 0 && whole_range && (ep.result_offset == 0 || op.max_shift <= 22)) ? kStagePack : kStageWide;
+    if (op.pack_stage >= 0 && whole_range && (ep.result_offset == 0 || op.max_shift <= 22))
+    {
+        return ep.out_signed != 0 ? kStagePackS : kStagePack;
+    }
+    return kStageWide;
 }
 
 void fill_extra_dst(TileParams &tp, const GemmOperands &op)
@@ -2324,6 +2384,9 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.spin_limit  = ctx->spin_limit;
+    tp.withhold_kb = ctx->withhold_kb;
+    ctx->withhold_kb = -1;
     tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
@@ -2365,6 +2428,9 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok  = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 7) == 0;
     tp.status  = ctx->d_status;
+    tp.spin_limit  = ctx->spin_limit;
+    tp.withhold_kb = ctx->withhold_kb;
+    ctx->withhold_kb = -1;
     tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
@@ -2409,6 +2475,9 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.split_tail = op.split_tail >= 0 ? 1 : 0;
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.spin_limit  = ctx->spin_limit;
+    tp.withhold_kb = ctx->withhold_kb;
+    ctx->withhold_kb = -1;
     tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;
@@ -2463,6 +2532,9 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.spin_limit  = ctx->spin_limit;
+    tp.withhold_kb = ctx->withhold_kb;
+    ctx->withhold_kb = -1;
     tp.mode    = stage_mode(op, ep);
     tp.trace   = ctx->d_trace;
     tp.raw_f32 = ep.out_f32, tp.raw_accumulate = ep.accumulate, tp.raw_scale = ep.dq_scale;

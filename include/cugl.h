@@ -97,6 +97,18 @@ CUGL_API int         cugl_context_sm_count(const cugl_context *ctx);
  * 64 * 8 bytes per CTA of the launch (at most 2 * SM count CTAs).  NULL switches tracing off. */
 CUGL_API cugl_status cugl_context_set_trace_buffer(cugl_context *ctx, void *d_buffer);
 
+/* Every wait of a tensor-core kernel on a barrier (operands landed, stage free, accumulator complete / drained) is
+ * bounded: when it has lasted longer than the limit the kernel stops issuing work, waits for the copies it has in
+ * flight, frees its tensor memory, returns, and the next cugl_sync() reports CUGL_RUNTIME_ERROR; the context stays
+ * usable.  The limit is two seconds unless set here, in microseconds (0 restores the default).  It is the
+ * counterpart of the scheduler-side run-time checks of the reference (IScheduler::schedule errors); the reference
+ * has no device waits. */
+CUGL_API cugl_status cugl_context_set_wait_limit_us(cugl_context *ctx, uint64_t microseconds);
+/* Test instrument of that path, no reference counterpart: in the NEXT tensor-core GEMM launch of this context the
+ * producer of CTA 0 leaves out the operand copies of k-block ordinal `k_block` (counted over the CTA's tile
+ * sequence), so that the wait for them runs out.  One shot: the launch after it is normal again. */
+CUGL_API cugl_status cugl_context_withhold_copy_once(cugl_context *ctx, int k_block);
+
 /* IAllocator::allocate / free (arm_compute/runtime/IAllocator.h:39-61): device regions, 256-byte aligned. */
 CUGL_API cugl_status cugl_malloc(cugl_context *ctx, size_t bytes, void **d_ptr);
 CUGL_API cugl_status cugl_free(cugl_context *ctx, void *d_ptr);
@@ -106,6 +118,9 @@ CUGL_API cugl_status cugl_host_alloc(cugl_context *ctx, size_t bytes, void **h_p
 CUGL_API cugl_status cugl_host_free(cugl_context *ctx, void *h_ptr);
 CUGL_API cugl_status cugl_memcpy_h2d(cugl_context *ctx, void *d_dst, const void *h_src, size_t bytes);
 CUGL_API cugl_status cugl_memcpy_d2h(cugl_context *ctx, void *h_dst, const void *d_src, size_t bytes);
+/* Device-to-device copy on the context's stream (the reshape-type layers that only re-label a dense tensor:
+ * NEFlattenLayer / NEReshapeLayer, src/cpu/operators/CpuFlatten.cpp). */
+CUGL_API cugl_status cugl_memcpy_d2d(cugl_context *ctx, void *d_dst, const void *d_src, size_t bytes);
 /* Strided 2-D copies for host tensors with padding (ITensorInfo strides_in_bytes /
  * offset_first_element_in_bytes, arm_compute/core/ITensorInfo.h:197-211). */
 CUGL_API cugl_status cugl_memcpy2d_h2d(cugl_context *ctx, void *d_dst, size_t d_pitch, const void *h_src,

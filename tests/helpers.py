@@ -47,46 +47,48 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
         b_batch_stride=(K * N if b.ndim == 3 else 0), b_constant=b_constant, accumulate=accumulate,
         dequantize_scale=dequantize_scale)
     plan = capi.GemmPlan(ctx, desc, keep)
-    ws = None
-    if temp_workspace:  # the caller owns the temporary memory (what a MemoryGroup does for the C++ functions)
-        nbytes = plan.temp_bytes
-        ws = torch.full((max(nbytes, 1) + 64,), 0x77, dtype=torch.uint8, device="cuda")
-        plan.bind_temp(ws, nbytes)
-    if force_simt:
-        plan.force_simt(True)
-    if not pair:
-        plan.allow_pair_kernel(False)
-    if epi_warps:
-        plan.set_epilogue_warps(epi_warps)
-    if channel_major:
-        plan.set_channel_major(channel_major)
-    if tile_columns:
-        plan.set_tile_columns(tile_columns)
-    if not paired_drain:
-        plan.set_paired_drain(False)
-    if not saturating_pack:
-        plan.set_saturating_pack(False)
-    da = torch.from_numpy(a.view(np.uint8)).cuda()
-    db = torch.from_numpy(b.view(np.uint8)).cuda()
-    dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.int32)).cuda() if bias is not None else None
-    canary = 0xA5
-    dd = torch.full((batch * M * ldd,), canary, dtype=torch.uint8, device="cuda")
-    if dst_init is not None:  # accumulation starts from these values
-        init = np.ascontiguousarray(dst_init, dtype=out_dtype).reshape(batch * M, N).view(np.uint8)
-        dd.view(batch * M, ldd)[:, :N * dsz] = torch.from_numpy(init).cuda()
-    if b_constant:
-        plan.prepare(db)
-    for _ in range(runs):
-        plan.run(da, None if b_constant else db, dbias, dd)
-    ctx.sync()
-    raw = dd.cpu().numpy().reshape(batch, M, ldd)
-    if ldd_pad:
-        assert (raw[:, :, N * dsz:] == canary).all(), "kernel wrote into the row padding"
-    out = np.ascontiguousarray(raw[:, :, :N * dsz]).view(out_dtype).reshape(batch, M, N)
-    kernel = plan.kernel
-    if ws is not None:
-        assert (ws[plan.temp_bytes:] == 0x77).all(), "the plan wrote past the bound temporary workspace"
-    plan.close()
+    try:
+        ws = None
+        if temp_workspace:  # the caller owns the temporary memory (what a MemoryGroup does for the C++ functions)
+            nbytes = plan.temp_bytes
+            ws = torch.full((max(nbytes, 1) + 64,), 0x77, dtype=torch.uint8, device="cuda")
+            plan.bind_temp(ws, nbytes)
+        if force_simt:
+            plan.force_simt(True)
+        if not pair:
+            plan.allow_pair_kernel(False)
+        if epi_warps:
+            plan.set_epilogue_warps(epi_warps)
+        if channel_major:
+            plan.set_channel_major(channel_major)
+        if tile_columns:
+            plan.set_tile_columns(tile_columns)
+        if not paired_drain:
+            plan.set_paired_drain(False)
+        if not saturating_pack:
+            plan.set_saturating_pack(False)
+        da = torch.from_numpy(a.view(np.uint8)).cuda()
+        db = torch.from_numpy(b.view(np.uint8)).cuda()
+        dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.int32)).cuda() if bias is not None else None
+        canary = 0xA5
+        dd = torch.full((batch * M * ldd,), canary, dtype=torch.uint8, device="cuda")
+        if dst_init is not None:  # accumulation starts from these values
+            init = np.ascontiguousarray(dst_init, dtype=out_dtype).reshape(batch * M, N).view(np.uint8)
+            dd.view(batch * M, ldd)[:, :N * dsz] = torch.from_numpy(init).cuda()
+        if b_constant:
+            plan.prepare(db)
+        for _ in range(runs):
+            plan.run(da, None if b_constant else db, dbias, dd)
+        ctx.sync()
+        raw = dd.cpu().numpy().reshape(batch, M, ldd)
+        if ldd_pad:
+            assert (raw[:, :, N * dsz:] == canary).all(), "kernel wrote into the row padding"
+        out = np.ascontiguousarray(raw[:, :, :N * dsz]).view(out_dtype).reshape(batch, M, N)
+        kernel = plan.kernel
+        if ws is not None:
+            assert (ws[plan.temp_bytes:] == 0x77).all(), "the plan wrote past the bound temporary workspace"
+    finally:
+        plan.close()
     return (out if batched else out[0]), kernel
 
 
