@@ -2,7 +2,7 @@
 
     python -m computelibrary_b200.host.build [--force] [ACL_ROOT=<tree>]
 
-Two shared libraries land in computelibrary_b200/lib/ (git-ignored; they travel with the source tree):
+Three shared libraries land in computelibrary_b200/lib/ (git-ignored; they travel with the source tree):
 
   libarm_compute_host.so  Compute Library's own host-side core and runtime sources -- TensorInfo, Tensor,
                           TensorAllocator, MemoryGroup / MemoryManagerOnDemand / BlobLifetimeManager / PoolManager,
@@ -13,6 +13,10 @@ Two shared libraries land in computelibrary_b200/lib/ (git-ignored; they travel 
                           CUGEMMLowpMatrixMultiplyCore, CUGEMMLowpOutputStage, CUGEMMConvolutionLayer, ...),
                           compiled against the reference's own headers (-I$ACL_ROOT -I$ACL_ROOT/include) and linked
                           to libarm_compute_host.so and libcugl.so.
+  libarm_compute_graph_cuda.so  Compute Library's graph frontend and IR (src/graph/**, without its NEON and CL
+                          backends), compiled in place, together with this repository's graph backend
+                          (host/src/graph/: CUDeviceBackend, CUTensorHandle, CUFunctionFactory), which registers itself
+                          when the library is loaded.
 
 Inside Compute Library itself the second set of sources would simply be added to the library's source list
 (SConscript / filelist.json) next to src/runtime/NEON and src/runtime/CL.
@@ -34,6 +38,7 @@ LIB_DIR = os.path.join(PKG, "lib")
 OBJ_DIR = os.path.join(LIB_DIR, "obj_host")
 ACL_HOST_LIB = os.path.join(LIB_DIR, "libarm_compute_host.so")
 LIB_PATH = os.path.join(LIB_DIR, "libarm_compute_cuda.so")
+GRAPH_LIB = os.path.join(LIB_DIR, "libarm_compute_graph_cuda.so")
 
 # The reference's host sources behind the API types of the path (relative to the tree).  Left out on purpose:
 # src/core/GPUTarget.cpp (OpenCL), src/core/Version.cpp (needs a generated header), src/core/utils/ScaleUtils.cpp
@@ -44,6 +49,8 @@ ACL_RUNTIME = ["Allocator", "BlobLifetimeManager", "BlobMemoryPool", "ISimpleLif
                "IWeightsManager", "Memory", "MemoryManagerOnDemand", "OffsetLifetimeManager", "OffsetMemoryPool",
                "PoolManager", "SubTensor", "Tensor", "TensorAllocator"]
 ACL_DEFINES = ["-DARM_COMPUTE_CPU_ENABLED", "-DARM_COMPUTE_ASSERTS_ENABLED"]
+# the graph library: everything under src/graph except the two device backends of the reference
+ACL_GRAPH_GLOBS = ["src/graph/*.cpp", "src/graph/*/*.cpp", "src/graph/backends/BackendRegistry.cpp"]
 
 
 def find_acl_root() -> str | None:
@@ -63,6 +70,13 @@ def acl_sources(acl_root: str) -> list[str]:
     return rel
 
 
+def acl_graph_sources(acl_root: str) -> list[str]:
+    rel = []
+    for g in ACL_GRAPH_GLOBS:
+        rel += [os.path.relpath(p, acl_root) for p in glob.glob(os.path.join(acl_root, g))]
+    return sorted(r for r in set(rel) if "/backends/NEON/" not in r and "/backends/CL/" not in r)
+
+
 def include_flags(acl_root: str) -> list[str]:
     return [f"-I{acl_root}", f"-I{acl_root}/include", f"-I{acl_root}/src/cpu/kernels/assembly",
             f"-I{os.path.join(HERE, 'include')}", f"-I{os.path.join(HERE, 'src')}", f"-I{os.path.join(ROOT, 'include')}"]
@@ -72,8 +86,8 @@ def compile_flags(acl_root: str) -> list[str]:
     return ["-std=c++17", "-O2", "-fPIC", *ACL_DEFINES, *include_flags(acl_root)]
 
 
-def link_flags() -> list[str]:
-    return [f"-L{LIB_DIR}", "-larm_compute_cuda", "-larm_compute_host", "-lcugl", f"-Wl,-rpath,{LIB_DIR}", "-Wl,-rpath,$ORIGIN",
+def link_flags(graph: bool = False) -> list[str]:
+    return [f"-L{LIB_DIR}", *(["-larm_compute_graph_cuda"] if graph else []), "-larm_compute_cuda", "-larm_compute_host", "-lcugl", f"-Wl,-rpath,{LIB_DIR}", "-Wl,-rpath,$ORIGIN",
             "-lpthread"]
 
 
@@ -106,7 +120,7 @@ def build(force: bool = False, acl_root: str | None = None) -> str:
     cuda_build.build()
     acl_root = acl_root or find_acl_root()
     if acl_root is None:
-        if os.path.exists(LIB_PATH) and os.path.exists(ACL_HOST_LIB):
+        if os.path.exists(LIB_PATH) and os.path.exists(ACL_HOST_LIB) and os.path.exists(GRAPH_LIB):
             return LIB_PATH  # prebuilt libraries travel with the tree
         raise RuntimeError("no Compute Library tree (set ACL_ROOT) and no prebuilt libarm_compute_cuda.so")
     os.makedirs(OBJ_DIR, exist_ok=True)
@@ -131,6 +145,17 @@ def build(force: bool = False, acl_root: str | None = None) -> str:
                                                    compile_flags(acl_root) + ["-Wall", "-Wextra"], headers), srcs))
     _link(cu_objs, LIB_PATH, [f"-L{LIB_DIR}", "-larm_compute_host", "-lcugl", f"-Wl,-rpath,{LIB_DIR}", "-Wl,-rpath,$ORIGIN",
                               "-Wl,--no-undefined", "-lpthread"])
+    # 3. the reference's graph library + the CUDA graph backend
+    gsrc = acl_graph_sources(acl_root)
+    bsrc = sorted(glob.glob(os.path.join(HERE, "src", "graph", "*.cpp")))
+    with ThreadPoolExecutor(max_workers=workers) as pool:
+        g_objs = list(pool.map(lambda r: _compile(os.path.join(acl_root, r),
+                                                  os.path.join(OBJ_DIR, "aclg_" + r.replace("/", "_")[:-4] + ".o"),
+                                                  compile_flags(acl_root) + warn_off, []), gsrc))
+        g_objs += list(pool.map(lambda s: _compile(s, os.path.join(OBJ_DIR, "cug_" + os.path.basename(s)[:-4] + ".o"),
+                                                   compile_flags(acl_root) + ["-Wall", "-Wextra"], headers), bsrc))
+    _link(g_objs, GRAPH_LIB, [f"-L{LIB_DIR}", "-larm_compute_cuda", "-larm_compute_host", "-lcugl", f"-Wl,-rpath,{LIB_DIR}",
+                              "-Wl,-rpath,$ORIGIN", "-Wl,--no-undefined", "-lpthread"])
     return LIB_PATH
 
 

@@ -15,6 +15,8 @@
 #include "arm_compute/runtime/IMemoryManager.h"
 #include "arm_compute/runtime/IWeightsManager.h"
 
+#include <memory>
+
 namespace arm_compute
 {
 class CUPoolingLayer : public IFunction
@@ -64,6 +66,8 @@ private:
 class CUSoftmaxLayer : public IFunction
 {
 public:
+    // the softmax kernel keeps its row in registers and shared memory: no workspace for a memory manager to hold
+    explicit CUSoftmaxLayer(std::shared_ptr<IMemoryManager> memory_manager = nullptr) { ARM_COMPUTE_UNUSED(memory_manager); }
     void          configure(ITensor *input, ITensor *output, float beta = 1.0f, int32_t axis = 0);
     static Status validate(const ITensorInfo *input, const ITensorInfo *output, float beta = 1.0f, int32_t axis = 0);
     void          run() override;
@@ -72,5 +76,19 @@ private:
     const ITensor *_input{nullptr};
     ITensor       *_output{nullptr};
     float          _beta{1.f};
+};
+
+// NEFlattenLayer (arm_compute/runtime/NEON/functions/NEFlattenLayer.h:41-78): [d0, d1, d2, batch] -> [d0*d1*d2, batch].
+// The elements keep their order, so for dense tensors the layer is one device-to-device copy.
+class CUFlattenLayer : public IFunction
+{
+public:
+    void          configure(const ITensor *input, ITensor *output);
+    static Status validate(const ITensorInfo *input, const ITensorInfo *output);
+    void          run() override;
+
+private:
+    const ITensor *_input{nullptr};
+    ITensor       *_output{nullptr};
 };
 } // namespace arm_compute

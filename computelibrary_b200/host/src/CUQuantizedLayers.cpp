@@ -220,4 +220,31 @@ void CUSoftmaxLayer::run()
         cugl_softmax_qasymm8(ctx, cu_device_ptr(_input), cu_device_ptr(_output), rows, cols, _beta, qi.scale, qi.offset), ctx,
         "CUSoftmaxLayer::run"));
 }
+
+// ---- flatten (src/cpu/operators/CpuFlatten.cpp) ------------------------------------------------------------------
+Status CUFlattenLayer::validate(const ITensorInfo *input, const ITensorInfo *output)
+{
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input == nullptr || output == nullptr, "nullptr tensor info");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input->data_type() != output->data_type(), "input and output data types differ");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(input->tensor_shape().total_size() != output->tensor_shape().total_size(),
+                                    "input and output hold different numbers of elements");
+    ARM_COMPUTE_RETURN_ERROR_ON_MSG(!dense(input) || !dense(output), "padded tensors are not supported");
+    return Status{};
+}
+
+void CUFlattenLayer::configure(const ITensor *input, ITensor *output)
+{
+    ARM_COMPUTE_ERROR_ON_NULLPTR(input, output);
+    CU_THROW_ON(validate(input->info(), output->info()));
+    _input  = input;
+    _output = output;
+}
+
+void CUFlattenLayer::run()
+{
+    cugl_context *ctx = CUScheduler::get().context();
+    CU_THROW_ON(cu_status(cugl_memcpy_d2d(ctx, cu_device_ptr(_output), cu_device_ptr(_input),
+                                          _input->info()->tensor_shape().total_size() * _input->info()->element_size()),
+                          ctx, "CUFlattenLayer::run"));
+}
 } // namespace arm_compute

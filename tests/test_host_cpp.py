@@ -86,6 +86,42 @@ def build_fixture_exe():
     return FIXTURE_EXE
 
 
+GRAPH_TEST_EXE = os.path.join(ROOT, "tests", "cpp", "test_graph_backend")
+GRAPH_EXAMPLE_EXE = os.path.join(ROOT, "tests", "cpp", "graph_resnet50")
+
+
+def _build_graph_program(exe, sources, acl_sources=()):
+    """A program on the graph frontend + the CUDA graph backend.  `acl_sources` are files of the Compute Library tree
+    compiled where they lie (the example itself and the utilities it uses)."""
+    from computelibrary_b200.host import build as hb
+    import oracle
+    acl_root = hb.find_acl_root()
+    if acl_root is None:
+        assert os.path.exists(exe), f"no Compute Library tree and no prebuilt {os.path.relpath(exe, ROOT)}"
+        return exe
+    hb.build()
+    if not os.path.exists(oracle.PORT_SO):
+        oracle.build(want_ref=False)
+    deps = list(sources) + [hb.GRAPH_LIB, hb.LIB_PATH]
+    if os.path.exists(exe) and all(os.path.getmtime(d) <= os.path.getmtime(exe) for d in deps):
+        return exe
+    odir = os.path.dirname(oracle.PORT_SO)
+    cmd = [shutil.which("g++") or "g++", *hb.compile_flags(acl_root), f"-I{ROOT}", "-w", *sources,
+           *[os.path.join(acl_root, r) for r in acl_sources], "-o", exe, *hb.link_flags(graph=True), f"-L{odir}",
+           "-lgemmlowp_oracle", f"-Wl,-rpath,{odir}"]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    assert res.returncode == 0, res.stderr
+    return exe
+
+
+def build_graph_exes():
+    t = _build_graph_program(GRAPH_TEST_EXE, [GRAPH_TEST_EXE + ".cpp"])
+    # the reference's own example, unmodified, on the graph frontend
+    e = _build_graph_program(GRAPH_EXAMPLE_EXE, [], ["examples/graph_resnet50.cpp", "utils/GraphUtils.cpp", "utils/Utils.cpp",
+                                                     "utils/CommonGraphOptions.cpp"])
+    return t, e
+
+
 def test_cpp_validate_rules_host_only():
     exe = build_exe()
     res = subprocess.run([exe, "--validate"], capture_output=True, text=True, timeout=120)
@@ -107,3 +143,22 @@ def test_reference_fixtures_with_the_cuda_triple():
     exe = build_fixture_exe()
     res = subprocess.run([exe], capture_output=True, text=True, timeout=900)
     assert res.returncode == 0, res.stdout + res.stderr
+
+
+@pytest.mark.gpu
+def test_graph_frontend_on_the_cuda_backend():
+    """A reduced ResNet built with the reference's graph frontend runs on the CUDA backend and matches the oracle."""
+    exe, _ = build_graph_exes()
+    res = subprocess.run([exe], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout + res.stderr
+
+
+@pytest.mark.gpu
+def test_reference_graph_resnet50_example_runs_unmodified():
+    """examples/graph_resnet50.cpp of the reference, compiled as it is, in its synthetic QASYMM8 mode (random weights,
+    no data files): --target=CL selects the CUDA backend in a build without OpenCL."""
+    _, exe = build_graph_exes()
+    res = subprocess.run([exe, "--target=CL", "--type=QASYMM8", "--layout=NHWC", "--batches=4"], capture_output=True, text=True,
+                         timeout=900)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-2000:]
+    assert "Test passed" in res.stdout or res.returncode == 0
