@@ -16,6 +16,9 @@
 #include "arm_compute/runtime/OffsetLifetimeManager.h"
 #include "arm_compute/runtime/PoolManager.h"
 
+#include <cstdio>
+#include <cstdlib>
+
 namespace arm_compute
 {
 namespace graph
@@ -31,9 +34,24 @@ void CUDeviceBackend::initialize_backend()
     _initialized = true;
 }
 
+namespace
+{
+// CU_GRAPH_MEMORY_MANAGER=0 leaves every tensor and workspace with an allocation of its own (to measure what the
+// lifetime managers save); CU_GRAPH_REPORT_MEMORY=1 prints the peak of device bytes held when a graph is released.
+bool env_flag(const char *name, bool otherwise)
+{
+    const char *v = std::getenv(name);
+    return v == nullptr ? otherwise : (v[0] != '0' && v[0] != '\0');
+}
+} // namespace
+
 void CUDeviceBackend::release_backend_context(GraphContext &ctx)
 {
     ARM_COMPUTE_UNUSED(ctx);
+    if (env_flag("CU_GRAPH_REPORT_MEMORY", false))
+    {
+        std::printf("CUDA graph backend: peak device bytes held by tensors and workspaces: %zu\n", CUAllocator::peak_bytes());
+    }
 }
 
 void CUDeviceBackend::setup_backend_context(GraphContext &ctx)
@@ -47,8 +65,9 @@ void CUDeviceBackend::setup_backend_context(GraphContext &ctx)
     {
         MemoryManagerContext mm_ctx;
         mm_ctx.target      = CUDATarget;
-        mm_ctx.intra_mm    = create_memory_manager(MemoryManagerAffinity::Buffer);
-        mm_ctx.cross_mm    = create_memory_manager(MemoryManagerAffinity::Buffer);
+        const bool managed = env_flag("CU_GRAPH_MEMORY_MANAGER", true);
+        mm_ctx.intra_mm    = managed ? create_memory_manager(MemoryManagerAffinity::Buffer) : nullptr;
+        mm_ctx.cross_mm    = managed ? create_memory_manager(MemoryManagerAffinity::Buffer) : nullptr;
         mm_ctx.cross_group = std::make_shared<MemoryGroup>(mm_ctx.cross_mm);
         mm_ctx.allocator   = &_allocator;
         ctx.insert_memory_management_ctx(std::move(mm_ctx));
