@@ -147,6 +147,8 @@ _SIGNATURES = {
     "cugl_conv2d_plan_launches": (C.c_int, [_vp]),
     "cugl_conv2d_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_conv2d_plan_allow_implicit": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_allow_tma_im2col": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_uses_tma_im2col": (C.c_int, [_vp]),
     "cugl_conv2d_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
@@ -519,7 +521,7 @@ class GemmPlan:
     def set_saturating_pack(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_saturating_pack(self.handle, int(on)))
 
-    def set_paired_drain(self, on: bool = True):
+    def set_paired_drain(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_paired_drain(self.handle, int(on)))
 
     def set_channel_major(self, mode: int):
@@ -638,7 +640,7 @@ class ConvPlan:
     def set_saturating_pack(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_saturating_pack(self.handle, int(on)))
 
-    def set_paired_drain(self, on: bool = True):
+    def set_paired_drain(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_paired_drain(self.handle, int(on)))
 
     def set_channel_major(self, mode: int):
@@ -646,6 +648,13 @@ class ConvPlan:
 
     def allow_implicit(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_implicit(self.handle, int(on)))
+
+    def allow_tma_im2col(self, on: bool = True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_tma_im2col(self.handle, int(on)))
+
+    @property
+    def uses_tma_im2col(self) -> bool:
+        return bool(self.ctx.lib.cugl_conv2d_plan_uses_tma_im2col(self.handle))
 
     @property
     def temp_bytes(self) -> int:

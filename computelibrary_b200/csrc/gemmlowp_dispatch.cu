@@ -64,6 +64,11 @@ bool pair_fills_the_device(const cugl_context *ctx, const GemmOperands &op)
 }
 } // namespace
 
+bool gemmlowp_conv_tma_supported(const GemmOperands &op)
+{
+    return gemmlowp_conv_tma_supported_epi4(op);
+}
+
 bool gemmlowp_tcgen05_supported(const GemmOperands &op)
 {
     return gemmlowp_tcgen05_supported_epi4(op);

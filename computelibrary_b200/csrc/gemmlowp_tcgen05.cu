@@ -127,6 +127,20 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
                  : "memory");
 }
 
+// Im2col-mode tile load (NHWC tensor map made by cuTensorMapEncodeIm2col): BLOCK_M window origins starting at
+// (w, h, n) and walking w, then h, then n inside the map's bounding box, channels [c, c + 128) of the pixel at
+// origin + (off_w, off_h); pixels outside the image and origins beyond the last image read as zero.
+__device__ __forceinline__ void tma_load_im2col(uint32_t dst, const CUtensorMap *map, int c, int w, int h, int n,
+                                                uint16_t off_w, uint16_t off_h, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+                 :
+                 : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(off_w),
+                   "h"(off_h)
+                 : "memory");
+}
+
 // ---- tcgen05 -------------------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before()
 {
@@ -175,6 +189,15 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, uint32_t (&v)[32])
                    "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]),
                    "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]),
                    "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld_x16(uint32_t taddr, uint32_t (&v)[16])
+{
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                   "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                  : "r"(taddr)
                  : "memory");
 }
@@ -283,6 +306,11 @@ struct TileParams
     int32_t *status;
     int      raw_f32, raw_accumulate; // stage NONE: float destination / dst += result (EpilogueParams::out_f32, accumulate)
     float    raw_scale;               // dequantization scale of a float destination
+    // Implicit convolution (conv_c != 0): tmap_a is an im2col-mode map of the NHWC input with 128 channels per load, a
+    // tile row is an output pixel and the K axis runs over (ky, kx, c).  Exact for an input zero point of 0 only (the
+    // fill value of out-of-image taps), and for C a multiple of 128.
+    int      conv_c, conv_kw, conv_wo, conv_ho, conv_sx, conv_sy, conv_pl, conv_pt, conv_dx, conv_dy;
+    FastDiv  conv_div_wo, conv_div_ho;
     long long spin_limit;             // clock64 ticks a wait on a barrier may last before the kernel gives up
     int      withhold_kb;             // >= 0: CTA 0 leaves out the copies of this k-block ordinal (test instrument
                                       // of the give-up path, cugl_context_withhold_copy_once); -1 otherwise
@@ -792,69 +820,211 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
     }
 }
 
-// Two accumulator buffers that hold tiles of the same column block (rows ma and mb of this thread) drained
-// together, kStageWide encoding only.  Every lane of a warp needs the 16-byte term of every column, so the
-// per-element term read from shared memory is what the load/store pipe spends most of a short-K epilogue on
-// (802816 x 256 x 64: 235 us, 134 us with one term read per 32 columns instead of 32).  Here a term is read
-// once for two elements; both residual rows are requested together, after the arithmetic (requesting them while the
-// tensor-memory loads travel measured slower: block-1 conv3 + add 238 -> 284 us).
+// 32 packed output bytes of one row to global memory; cols: valid columns from o on (>= 32: a whole chunk).
+__device__ __forceinline__ void store_row32(uint8_t *o, const uint32_t *v, int cols, int vec_ok)
+{
+    if (o == nullptr)
+    {
+        return;
+    }
+    if (cols >= 32 && (vec_ok & 2))
+    {
+        asm volatile("st.global.v8.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8};" ::"l"(o), "r"(v[0]), "r"(v[1]),
+                     "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7])
+                     : "memory");
+    }
+    else if (cols >= 32 && vec_ok)
+    {
+        *reinterpret_cast<uint4 *>(o)      = make_uint4(v[0], v[1], v[2], v[3]);
+        *reinterpret_cast<uint4 *>(o + 16) = make_uint4(v[4], v[5], v[6], v[7]);
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+        {
+            if (j < cols) o[j] = static_cast<uint8_t>(v[j >> 2] >> (8 * (j & 3)));
+        }
+    }
+}
+__device__ __forceinline__ void load_row32(uint32_t (&r)[8], const uint8_t *p, int cols, int vec_ok)
+{
+    if (p == nullptr)
+    {
+        return;
+    }
+    if (cols >= 32 && (vec_ok & 2))
+    {
+        asm volatile("ld.global.nc.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+                     : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+                     : "l"(p));
+    }
+    else if (cols >= 32 && vec_ok)
+    {
+        const uint4 r0 = __ldg(reinterpret_cast<const uint4 *>(p));
+        const uint4 r1 = __ldg(reinterpret_cast<const uint4 *>(p + 16));
+        r[0] = r0.x, r[1] = r0.y, r[2] = r0.z, r[3] = r0.w, r[4] = r1.x, r[5] = r1.y, r[6] = r1.z, r[7] = r1.w;
+    }
+    else
+    {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            uint32_t v = 0;
+            for (int b = 0; b < 4; ++b)
+            {
+                if (4 * j + b < cols) v |= static_cast<uint32_t>(p[4 * j + b]) << (8 * b);
+            }
+            r[j] = v;
+        }
+    }
+}
+
+// Everything the paired drain needs, by value: the function is a call of its own (its register allocation is then
+// independent of the rest of the kernel, which matters in the sixteen-warp build with 96 registers per thread).
+struct PairDrain
+{
+    uint32_t       t_a, t_b;       // tensor-memory addresses of the two buffers (lane quarter and first column applied)
+    const int4    *col;            // terms of the first column
+    uint8_t       *dst_a, *dst_b;  // output rows at the first column; nullptr: the row lies outside the matrix
+    const uint8_t *res_a, *res_b;  // residual rows at the first column; nullptr: no residual (or no row)
+    int            cols;           // valid columns from the first column on
+    int            vec_ok;
+    uint32_t       res_floor4, res_cap4;
+    int32_t        offset, lo, hi; // wide encoding only
+    AccRelease     rel;
+    int            lane;
+};
+
+template <int G, int kMode>
+__device__ __forceinline__ void requant_columns_pair(const uint32_t *a, const uint32_t *b, const int4 *col,
+                                                     const PairDrain &d, uint32_t *wa, uint32_t *wb)
+{
+#pragma unroll
+    for (int h = 0; h < G / 4; ++h)
+    {
+        int32_t ra[4], rb[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+        {
+            const int4 q = col[4 * h + j];
+            ra[j]        = requant_one<kMode>(a[4 * h + j], q, 0, d.offset, d.lo, d.hi);
+            rb[j]        = requant_one<kMode>(b[4 * h + j], q, 0, d.offset, d.lo, d.hi);
+        }
+        if (kMode == kStagePack || kMode == kStagePackS)
+        {
+            wa[h] = pack4_sat<kMode == kStagePackS>(ra[0], ra[1], ra[2], ra[3]);
+            wb[h] = pack4_sat<kMode == kStagePackS>(rb[0], rb[1], rb[2], rb[3]);
+        }
+        else
+        {
+            wa[h] = __byte_perm(__byte_perm(static_cast<uint32_t>(ra[0]), static_cast<uint32_t>(ra[1]), 0x0040),
+                                __byte_perm(static_cast<uint32_t>(ra[2]), static_cast<uint32_t>(ra[3]), 0x0040), 0x5410);
+            wb[h] = __byte_perm(__byte_perm(static_cast<uint32_t>(rb[0]), static_cast<uint32_t>(rb[1]), 0x0040),
+                                __byte_perm(static_cast<uint32_t>(rb[2]), static_cast<uint32_t>(rb[3]), 0x0040), 0x5410);
+        }
+    }
+}
+
+__device__ __forceinline__ void finish_chunk_pair(const PairDrain &d, int ch, uint32_t *wa, uint32_t *wb,
+                                                  const uint32_t (&res_a)[8], const uint32_t (&res_b)[8])
+{
+    if (d.res_a != nullptr || d.res_b != nullptr)
+    {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+        {
+            wa[j] = add_clamp_u8x4(wa[j], res_a[j], d.res_floor4, d.res_cap4);
+            wb[j] = add_clamp_u8x4(wb[j], res_b[j], d.res_floor4, d.res_cap4);
+        }
+    }
+    store_row32(d.dst_a != nullptr ? d.dst_a + ch * 32 : nullptr, wa, d.cols - ch * 32, d.vec_ok);
+    store_row32(d.dst_b != nullptr ? d.dst_b + ch * 32 : nullptr, wb, d.cols - ch * 32, d.vec_ok);
+}
+
+// Two accumulator buffers that hold tiles of the same column block drained together (wide / pack encodings).  Every
+// lane of a warp needs the 16-byte term of every column, so the per-element term read from shared memory is what the
+// load/store pipe spends most of a short-K epilogue on; here a term is read once for two elements.
+template <int kMode>
+__device__ __forceinline__ void drain_pair_chunk_x32(const PairDrain &d, int ch, bool last)
+{
+    uint32_t va[32], vb[32];
+    tmem_ld_x32(d.t_a + ch * 32, va);
+    tmem_ld_x32(d.t_b + ch * 32, vb);
+    tmem_ld_wait();
+    if (last)
+    {
+        release_accumulators(d.rel, d.lane);
+    }
+    uint32_t wa[8], wb[8];
+    requant_columns_pair<32, kMode>(va, vb, d.col + ch * 32, d, wa, wb);
+    uint32_t res_a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, res_b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    load_row32(res_a, d.res_a != nullptr ? d.res_a + ch * 32 : nullptr, d.cols - ch * 32, d.vec_ok);
+    load_row32(res_b, d.res_b != nullptr ? d.res_b + ch * 32 : nullptr, d.cols - ch * 32, d.vec_ok);
+    finish_chunk_pair(d, ch, wa, wb, res_a, res_b);
+}
+// the same chunk read as two halves of sixteen columns: half the accumulator registers live at a time
+template <int kMode>
+__device__ __forceinline__ void drain_pair_chunk_x16(const PairDrain &d, int ch, bool last)
+{
+    uint32_t wa[8], wb[8];
+    uint32_t res_a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, res_b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    load_row32(res_a, d.res_a != nullptr ? d.res_a + ch * 32 : nullptr, d.cols - ch * 32, d.vec_ok);
+    load_row32(res_b, d.res_b != nullptr ? d.res_b + ch * 32 : nullptr, d.cols - ch * 32, d.vec_ok);
+#pragma unroll
+    for (int h = 0; h < 2; ++h)
+    {
+        uint32_t va[16], vb[16];
+        tmem_ld_x16(d.t_a + ch * 32 + h * 16, va);
+        tmem_ld_x16(d.t_b + ch * 32 + h * 16, vb);
+        tmem_ld_wait();
+        if (last && h == 1)
+        {
+            release_accumulators(d.rel, d.lane);
+        }
+        requant_columns_pair<16, kMode>(va, vb, d.col + ch * 32 + h * 16, d, wa + 4 * h, wb + 4 * h);
+    }
+    finish_chunk_pair(d, ch, wa, wb, res_a, res_b);
+}
+template <int NCOLS, int kMode>
+__device__ __noinline__ void drain_pair_x16(const PairDrain d)
+{
+#pragma unroll 1
+    for (int ch = 0; ch < NCOLS / 32; ++ch)
+    {
+        drain_pair_chunk_x16<kMode>(d, ch, ch == NCOLS / 32 - 1);
+    }
+}
+template <int NCOLS, int kMode>
+__device__ __noinline__ void drain_pair_x32(const PairDrain d)
+{
+#pragma unroll 1
+    for (int ch = 0; ch < NCOLS / 32; ++ch)
+    {
+        drain_pair_chunk_x32<kMode>(d, ch, ch == NCOLS / 32 - 1);
+    }
+}
+
 template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
                                                        const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
                                                        int n_first, int lane, const AccRelease &rel)
 {
-    const bool    ok_a   = ma < tp.M, ok_b = mb < tp.M;
-    const int64_t off_a  = static_cast<int64_t>(ma) * tp.ldd;
-    const int64_t off_b  = static_cast<int64_t>(mb) * tp.ldd;
-    const bool with_res  = tp.residual != nullptr; // warp-uniform
-    uint32_t   va[32], vb[32];
-#pragma unroll 1
-    for (int ch = 0; ch < NCOLS / 32; ++ch)
-    {
-        const int4 *col = s_col + ch * 32;
-        tmem_ld_x32(t_a + ch * 32, va);
-        tmem_ld_x32(t_b + ch * 32, vb);
-        tmem_ld_wait();
-        if (ch == NCOLS / 32 - 1)
-        {
-            release_accumulators(rel, lane); // both buffers: the MMAs of the next two tiles overlap this last chunk
-        }
-#pragma unroll
-        for (int j = 0; j < 32; j += 4)
-        {
-            int32_t ra[4], rb[4];
-#pragma unroll
-            for (int b = 0; b < 4; ++b)
-            {
-                const int4 q = col[j + b];
-                ra[b]        = requant_one<kMode>(va[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
-                rb[b]        = requant_one<kMode>(vb[j + b], q, 0, ep.result_offset, ep.lo, ep.hi);
-            }
-            if (kMode == kStagePack || kMode == kStagePackS)
-            {
-                va[j >> 2] = pack4_sat<kMode == kStagePackS>(ra[0], ra[1], ra[2], ra[3]);
-                vb[j >> 2] = pack4_sat<kMode == kStagePackS>(rb[0], rb[1], rb[2], rb[3]);
-            }
-            else
-            {
-                va[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(ra[0]), static_cast<uint32_t>(ra[1]), 0x0040),
-                                         __byte_perm(static_cast<uint32_t>(ra[2]), static_cast<uint32_t>(ra[3]), 0x0040), 0x5410);
-                vb[j >> 2] = __byte_perm(__byte_perm(static_cast<uint32_t>(rb[0]), static_cast<uint32_t>(rb[1]), 0x0040),
-                                         __byte_perm(static_cast<uint32_t>(rb[2]), static_cast<uint32_t>(rb[3]), 0x0040), 0x5410);
-            }
-        }
-        const int nc = n_first + ch * 32;
-        if (with_res)
-        {
-            uint32_t res_a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, res_b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-            load_residual(res_a, tp.residual + off_a, nc, ok_a, tp);
-            load_residual(res_b, tp.residual + off_b, nc, ok_b, tp);
-            add_residual(va, res_a, tp);
-            add_residual(vb, res_b, tp);
-        }
-        store_chunk<false>(va, tp.dst + off_a, nc, ok_a, tp);
-        store_chunk<false>(vb, tp.dst + off_b, nc, ok_b, tp);
-    }
+    PairDrain d;
+    d.t_a = t_a, d.t_b = t_b, d.col = s_col;
+    d.dst_a      = ma < tp.M ? tp.dst + static_cast<int64_t>(ma) * tp.ldd + n_first : nullptr;
+    d.dst_b      = mb < tp.M ? tp.dst + static_cast<int64_t>(mb) * tp.ldd + n_first : nullptr;
+    d.res_a      = (tp.residual != nullptr && ma < tp.M) ? tp.residual + static_cast<int64_t>(ma) * tp.ldd + n_first : nullptr;
+    d.res_b      = (tp.residual != nullptr && mb < tp.M) ? tp.residual + static_cast<int64_t>(mb) * tp.ldd + n_first : nullptr;
+    d.cols       = tp.N - n_first;
+    d.vec_ok     = tp.vec_ok;
+    d.res_floor4 = tp.res_floor4, d.res_cap4 = tp.res_cap4;
+    d.offset = ep.result_offset, d.lo = ep.lo, d.hi = ep.hi;
+    d.rel = rel, d.lane = lane;
+    // sixteen epilogue warps (96 registers per thread): sixteen columns at a time (802816 x 256 x 64: 143 against 154 us;
+    // level on the other shapes); eight and four warps measured level or better with whole 32-column loads
+    if (kEpiWarps == 16) drain_pair_x16<NCOLS, kMode>(d);
+    else drain_pair_x32<NCOLS, kMode>(d);
 }
 
 template <int BLOCK_N, int kGroups>
@@ -1369,7 +1539,36 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const int m0   = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
                 const int n0   = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
                 if (kb == 0) trace_event(tp.trace, ti, 0);
-                if (g != tp.withhold_kb || blockIdx.x != 0)
+                if (!kCM && tp.conv_c != 0)
+                {
+                    // window origin of the tile's first output pixel; sub-blocks beyond K are not loaded at all (the
+                    // MMA loop leaves them out as well)
+                    const int t  = fast_div(m0, tp.conv_div_wo);
+                    const int q  = m0 - t * tp.conv_wo;
+                    const int n  = fast_div(t, tp.conv_div_ho);
+                    const int pp = t - n * tp.conv_ho;
+                    const int w0 = q * tp.conv_sx - tp.conv_pl, h0 = pp * tp.conv_sy - tp.conv_pt;
+                    const int left  = (tp.K - kb * KSUB * BLOCK_K + BLOCK_K - 1) / BLOCK_K;
+                    const int valid = left < KSUB ? left : KSUB;
+                    mbar_expect_tx(full_bar(st), valid * (A_STAGE + P::B_SUB));
+#pragma unroll
+                    for (int sub = 0; sub < KSUB; ++sub)
+                    {
+                        if (sub < valid)
+                        {
+                            const int k0  = (kb * KSUB + sub) * BLOCK_K;
+                            const int tap = k0 / tp.conv_c, c0 = k0 - tap * tp.conv_c;
+                            const int ky = tap / tp.conv_kw, kx = tap - ky * tp.conv_kw;
+                            tma_load_im2col(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, c0, w0, h0, n,
+                                            static_cast<uint16_t>(kx * tp.conv_dx), static_cast<uint16_t>(ky * tp.conv_dy),
+                                            full_bar(st));
+                            tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
+                        }
+                    }
+                    issued |= 1u << st;
+                    parities = (parities & ~(1u << st)) | (ph << st);
+                }
+                else if (g != tp.withhold_kb || blockIdx.x != 0)
                 {
                     mbar_expect_tx(full_bar(st), P::STAGE);
 #pragma unroll
@@ -1475,9 +1674,13 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                         for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                         {
-                            umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
-                                    b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
-                                    (kb | sub | k) != 0 ? 1u : 0u);
+                            // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
+                            if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+                            {
+                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                        b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                        (kb | sub | k) != 0 ? 1u : 0u);
+                            }
                         }
                     }
                     umma_commit(empty_bar(s)); // frees the smem stage once these MMAs have read it
@@ -1518,7 +1721,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         // Only the 256-column tiles with their two buffers: with four buffers and two epilogue groups, and in the
         // implicit convolution, pairing measured slower (the MMA warp can no longer run two tiles ahead).
         constexpr int  kStride  = 1;
-        constexpr bool kCanPair = !kCM && !kS32Out && ACC == 2 && kGroups == 1;
+        // Two buffers only: with 128-column tiles in four buffers, pairs (0, 1) and (2, 3) drained by sixteen warps while
+        // the MMA warp fills the other pair, the same layers measured slower (802816 x 256 x 64: 164 against 133 us).
+        constexpr bool kCanPair = !kCM && !kS32Out && kGroups == 1 && ACC == 2;
         int            skip     = -1; // ordinal of a tile already drained as the partner of an earlier one
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti)
         {
@@ -1526,24 +1731,32 @@ __global__ void __launch_bounds__(kThreads, 1)
             {
                 continue;
             }
-            if (!(kGroups == 1 ? epi_barrier_and(ok) : epi_group_barrier_and(ok, group)))
-            {
-                break;
-            }
             const int      as  = ti % ACC;
             const uint32_t aph = static_cast<uint32_t>(ti / ACC) & 1u;
             const int      m0  = (kCM ? tile / num_n_blocks : tile % num_m_blocks) * BLOCK_M;
             const int      n0  = (kCM ? tile % num_n_blocks : tile / num_m_blocks) * BLOCK_N;
-            if (!kCM && n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
+            // The warps of a group meet only where the column terms change (tiles are ordered m-fastest, so the terms
+            // usually carry over): between such points every warp waits for its accumulator, drains its share and hands
+            // it back on its own, and a slow warp holds nobody up.  A warp whose wait ran out keeps walking the tile
+            // list without working, so that the barrier counts stay whole until all leave together.
+            if (!kCM && n0 != filled_n0)
             {
+                if (!(kGroups == 1 ? epi_barrier_and(ok) : epi_group_barrier_and(ok, group)))
+                {
+                    break; // the old terms are no longer read by anyone; someone gave up
+                }
                 fill_column_terms<BLOCK_N>(g_col, et, n0, tp, ep, kEpiThreads / kGroups);
                 filled_n0 = n0;
                 if (kGroups == 1) epi_barrier();
                 else epi_group_barrier(group);
             }
+            if (!ok)
+            {
+                continue;
+            }
             const int tile_b   = tile + kStride * static_cast<int>(gridDim.x);
             bool      pair_now = false;
-            if (kCanPair && tp.pair_drain != 0 && (tp.mode == kStageWide || tp.mode == kStagePack || tp.mode == kStagePackS) && as < kStride)
+            if (kCanPair && tp.pair_drain != 0 && (tp.mode == kStageWide || tp.mode == kStagePack || tp.mode == kStagePackS) && (as & 1) == 0)
             {
                 pair_now = tile_b < num_tiles && tile_b / num_m_blocks == tile / num_m_blocks;
             }
@@ -2104,9 +2317,13 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 #pragma unroll
                         for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                         {
-                            umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
-                                    b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
-                                    (kb | sub | k) != 0 ? 1u : 0u);
+                            // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
+                            if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+                            {
+                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                        b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                        (kb | sub | k) != 0 ? 1u : 0u);
+                            }
                         }
                     }
                     umma_commit(empty_bar(s));
@@ -2265,6 +2482,13 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 #endif // CUGL_TC_FULL_BUILD
 
 // encoding of the output stage for this launch (see requant_pack4)
+// two accumulator buffers of one column block drained together (drain_accumulator_pair): short K, one destination,
+// the wide / pack encodings of the output stage
+inline bool wants_pair_drain(const GemmOperands &op)
+{
+    return op.pair_drain >= 0 && op.K <= 512 && op.n_extra_dst == 0 && op.wide_stage && !op.generic_stage;
+}
+
 int stage_mode(const GemmOperands &op, const EpilogueParams &ep)
 {
     if (op.generic_stage)
@@ -2292,7 +2516,7 @@ void fill_extra_dst(TileParams &tp, const GemmOperands &op)
     tp.n_extra    = op.n_extra_dst;
     // paired drain: where the tile's time is its epilogue (K = 64: 227 -> 173 us, 128: 120 -> 96, 256: 67 -> 61,
     // 512: 43 -> 43); with a longer main loop the MMA of the next tile should overlap the drain instead
-    tp.pair_drain = (op.pair_drain >= 0 && op.K <= 512 && op.n_extra_dst == 0 && op.wide_stage && !op.generic_stage) ? 1 : 0;
+    tp.pair_drain = wants_pair_drain(op) ? 1 : 0;
     for (int i = 0; i < kMaxExtraDst; ++i)
     {
         tp.extra_dst[i] = i < op.n_extra_dst ? static_cast<uint8_t *>(op.extra_dst[i]) : nullptr;
@@ -2354,6 +2578,60 @@ bool encode_operand_map(CUtensorMap *map, const void *base, int rows, int K, int
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+using EncodeIm2colFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                                    const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
+                                    const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                    CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeIm2colFn get_encode_im2col_fn()
+{
+    static EncodeIm2colFn fn = []() -> EncodeIm2colFn {
+        void                           *p = nullptr;
+        cudaDriverEntryPointQueryResult q = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+        {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeIm2colFn>(p);
+    }();
+    return fn;
+}
+
+// Im2col-mode map of an NHWC byte tensor: a load delivers BLOCK_M window origins x 128 channels (128-byte swizzle, the
+// K-major tile the tensor cores read).  The bounding box of the origins runs from -pad to the origin of the last output
+// pixel in each dimension, the traversal stride is the convolution stride; taps outside the image read as zero.
+bool encode_im2col_map(CUtensorMap *map, const ConvOperands &cv)
+{
+    EncodeIm2colFn fn = get_encode_im2col_fn();
+    if (fn == nullptr)
+    {
+        return false;
+    }
+    const cuuint64_t dims[4]    = {static_cast<cuuint64_t>(cv.C), static_cast<cuuint64_t>(cv.W), static_cast<cuuint64_t>(cv.H),
+                                   static_cast<cuuint64_t>(cv.B)};
+    const cuuint64_t strides[3] = {static_cast<cuuint64_t>(cv.C), static_cast<cuuint64_t>(cv.C) * cv.W,
+                                   static_cast<cuuint64_t>(cv.C) * cv.W * cv.H};
+    const int        lower[2]   = {-cv.pad_l, -cv.pad_t};
+    const int        upper[2]   = {(cv.Wo - 1) * cv.sx - cv.pad_l - (cv.W - 1), (cv.Ho - 1) * cv.sy - cv.pad_t - (cv.H - 1)};
+    const cuuint32_t estr[4]    = {1, static_cast<cuuint32_t>(cv.sx), static_cast<cuuint32_t>(cv.sy), 1};
+    return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(cv.src), dims, strides, lower, upper,
+              static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(BLOCK_M), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// what the im2col-mode route needs besides the GEMM conditions
+bool conv_tma_supported(const GemmOperands &op)
+{
+    const ConvOperands &cv = *op.conv;
+    const int           up_w = (cv.Wo - 1) * cv.sx - cv.pad_l - (cv.W - 1), up_h = (cv.Ho - 1) * cv.sy - cv.pad_t - (cv.H - 1);
+    auto                corner_ok = [](int v) { return v >= -128 && v <= 127; };
+    return (cv.C % BLOCK_K) == 0 && (reinterpret_cast<uintptr_t>(cv.src) & 15) == 0 && cv.sx >= 1 && cv.sx <= 8 &&
+           cv.sy >= 1 && cv.sy <= 8 && corner_ok(-cv.pad_l) && corner_ok(-cv.pad_t) && corner_ok(up_w) && corner_ok(up_h) &&
+           (cv.kw - 1) * cv.dil_x < 256 && (cv.kh - 1) * cv.dil_y < 256 && get_encode_im2col_fn() != nullptr;
+}
+
 template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
 cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
 {
@@ -2361,10 +2639,11 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     CUtensorMap map_a, map_b;
-    if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
+    if (!(op.conv != nullptr ? encode_im2col_map(&map_a, *op.conv)
+                             : encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M)) ||
         !encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, BLOCK_N))
     {
-        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncode failed for a GEMM operand");
     }
     auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false, ACC>;
     static bool attr_set[64] = {}; // per instantiation and device
@@ -2384,6 +2663,14 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.conv_c  = 0;
+    if (op.conv != nullptr)
+    {
+        const ConvOperands &cv = *op.conv;
+        tp.conv_c = cv.C, tp.conv_kw = cv.kw, tp.conv_wo = cv.Wo, tp.conv_ho = cv.Ho, tp.conv_sx = cv.sx, tp.conv_sy = cv.sy;
+        tp.conv_pl = cv.pad_l, tp.conv_pt = cv.pad_t, tp.conv_dx = cv.dil_x, tp.conv_dy = cv.dil_y;
+        tp.conv_div_wo = make_fastdiv(cv.Wo), tp.conv_div_ho = make_fastdiv(cv.Ho);
+    }
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
     ctx->withhold_kb = -1;
@@ -2428,6 +2715,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok  = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 7) == 0;
     tp.status  = ctx->d_status;
+    tp.conv_c  = 0;
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
     ctx->withhold_kb = -1;
@@ -2475,6 +2763,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.split_tail = op.split_tail >= 0 ? 1 : 0;
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.conv_c  = 0;
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
     ctx->withhold_kb = -1;
@@ -2532,6 +2821,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.conv_c  = 0;
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
     ctx->withhold_kb = -1;
@@ -2577,6 +2867,17 @@ bool CUGL_TC_NAME(gemmlowp_tcgen05_supported)(const GemmOperands &op)
     return (bits & 15) == 0 && get_encode_fn() != nullptr;
 }
 
+// implicit convolution through im2col-mode loads (op.conv set): the weights as for the GEMM, the input tensor as above
+bool CUGL_TC_NAME(gemmlowp_conv_tma_supported)(const GemmOperands &op)
+{
+    if (op.conv == nullptr || op.M <= 0 || op.N <= 0 || op.K <= 0 || (op.K % BLOCK_K) != 0)
+    {
+        return false;
+    }
+    const uint64_t bits = reinterpret_cast<uintptr_t>(op.bt) | static_cast<uint64_t>(op.ldbt);
+    return (bits & 15) == 0 && get_encode_fn() != nullptr && conv_tma_supported(op);
+}
+
 // The SM-pair kernel pays off once a tile spans both halves: more than 128 rows and more than 128 columns.
 bool CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(const GemmOperands &op)
 {
@@ -2588,12 +2889,12 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
 {
     const bool s32 = ep.stage == CUGL_STAGE_NONE;
     // channel-major accumulators: no row-sum term (it would be a per-column quantity there) and one destination
-    if (op.channel_major > 0 && ep.rowsum == nullptr && op.n_extra_dst == 0)
+    if (op.channel_major > 0 && ep.rowsum == nullptr && op.n_extra_dst == 0 && op.conv == nullptr)
     {
         return s32 ? launch_variant_cm<256, 4, 1, true>(ctx, op, ep) : launch_variant_cm<256, 4, 1, false>(ctx, op, ep);
     }
 #if CUGL_TC_FULL_BUILD
-    if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
+    if (allow_pair && op.conv == nullptr && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
     {
         return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);
     }
@@ -2606,10 +2907,15 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
         return s32 ? launch_variant<256, 4, 1, true>(ctx, op, ep) : launch_variant<256, 4, 1, false>(ctx, op, ep);
     }
 #if CUGL_TC_FULL_BUILD
+    // K of at most one 128-byte block: a tile is a single stage, so one-block stages and a ring twice as deep keep
+    // twice as many tiles' operands in flight (the loads of such layers are bound by latency, not by bandwidth)
+    const bool one_block = op.K <= BLOCK_K && !s32;
     if (block_n > 64)
     {
+        if (one_block) return launch_variant<128, 6, 1, false>(ctx, op, ep);
         return s32 ? launch_variant<128, 3, 2, true>(ctx, op, ep) : launch_variant<128, 3, 2, false>(ctx, op, ep);
     }
+    if (one_block) return launch_variant<64, 8, 1, false>(ctx, op, ep);
     return s32 ? launch_variant<64, 4, 2, true>(ctx, op, ep) : launch_variant<64, 4, 2, false>(ctx, op, ep);
 #endif
 }

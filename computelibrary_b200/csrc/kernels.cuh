@@ -32,6 +32,7 @@ cugl_status launch_im2col_nhwc(cugl_context *ctx, const void *d_src, void *d_dst
 
 // Operand description shared by both GEMM kernels.  B is always given K-major ("Bt": N rows of K
 // contiguous bytes), which is what prepare() produces.
+struct ConvOperands;
 struct GemmOperands
 {
     const void *a;   // [M][lda]   K contiguous
@@ -63,6 +64,10 @@ struct GemmOperands
     // one-CTA tensor-core kernels with 256-column tiles: < 0 drains every accumulator buffer on its own; otherwise two
     // tiles of one column block are drained together wherever the output stage allows (see drain_accumulator_pair)
     int         pair_drain;
+    // one-CTA row-major tensor-core kernels: not nullptr = implicit convolution, the A operand is read from the NHWC
+    // tensor conv->src by im2col-mode TMA loads (a is ignored; M = B*Ho*Wo, K = kh*kw*C, C a multiple of 128, input
+    // zero point 0)
+    const ConvOperands *conv;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).
@@ -87,6 +92,8 @@ cugl_status launch_gemmlowp_conv_tcgen05_epi4(cugl_context *ctx, const GemmOpera
 cugl_status launch_gemmlowp_conv_tcgen05_epi8(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                               const ConvOperands &cv);
 bool        gemmlowp_tcgen05_supported_epi4(const GemmOperands &op);
+bool        gemmlowp_conv_tma_supported_epi4(const GemmOperands &op); // op.conv set: im2col-mode route possible
+bool        gemmlowp_conv_tma_supported(const GemmOperands &op);
 bool        gemmlowp_tcgen05_supported_epi8(const GemmOperands &op);
 bool        gemmlowp_tcgen05_uses_pair_epi4(const GemmOperands &op);
 bool        gemmlowp_tcgen05_uses_pair_epi8(const GemmOperands &op);

@@ -913,6 +913,7 @@ struct cugl_conv_plan
     bool                 skip_im2col = false;
     bool                 implicit    = false;   // gather the patches inside the GEMM kernel, no im2col matrix
     bool                 allow_implicit = true;
+    bool                 allow_tma_im2col = true; // implicit lowering: im2col-mode TMA loads where they are exact
     uint8_t             *d_cols      = nullptr; // [M][Kp] im2col matrix (allocated on first explicit run)
     uint8_t             *d_pad       = nullptr; // kConvPadBytes of the input zero point: source of out-of-image taps
     // Geometry the lowerings work on: the descriptor's own, or -- stride 2 with at most four channels -- the
@@ -1277,6 +1278,19 @@ extern "C"
             cv.dil_y  = d.dil_y;
             cv.Wo     = plan->Wo;
             cv.Ho     = plan->Ho;
+            // Input zero point 0 and whole 128-channel blocks: the TMA unit builds the patch tiles itself (im2col-mode
+            // tensor map, out-of-image taps read as zero = the zero point) and the GEMM kernels run unchanged; else
+            // the gather kernel, whose out-of-image taps copy any zero point from the pad buffer.
+            if (plan->allow_tma_im2col && d.src_zero_point == 0)
+            {
+                GemmOperands ot  = op;
+                ot.conv          = &cv;
+                ot.channel_major = -1;
+                if (gemmlowp_conv_tma_supported(ot))
+                {
+                    return launch_gemmlowp_tcgen05(plan->ctx, ot, c.epilogue(d.has_bias ? d_bias : nullptr, 0), false);
+                }
+            }
             if (gemmlowp_conv_tcgen05_supported(op, cv))
             {
                 return launch_gemmlowp_conv_tcgen05(plan->ctx, op, c.epilogue(d.has_bias ? d_bias : nullptr, 0), cv);
@@ -1403,6 +1417,25 @@ extern "C"
         }
         plan->core.pair_drain = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_allow_tma_im2col(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_allow_tma_im2col: NULL plan");
+        }
+        plan->allow_tma_im2col = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    int cugl_conv2d_plan_uses_tma_im2col(const cugl_conv_plan *plan)
+    {
+        // the conditions the plan can see; the run adds the alignment of the source pointer (16 bytes)
+        return plan != nullptr && plan->implicit && plan->allow_implicit && !plan->core.force_simt && plan->allow_tma_im2col &&
+                       plan->desc.src_zero_point == 0 && (plan->eC % 128) == 0
+                   ? 1
+                   : 0;
     }
 
     const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan)

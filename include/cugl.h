@@ -397,6 +397,13 @@ CUGL_API int  cugl_conv2d_plan_launches(const cugl_conv_plan *plan);
 CUGL_API const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan);
 /* on = 0 forces the explicit im2col lowering (testing aid: both lowerings must agree bit for bit). */
 CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on);
+/* The implicit lowering has two ways of forming the patch tiles: im2col-mode TMA loads (the copy engine walks the
+ * window origins itself; used when the input zero point is 0 -- the value out-of-image taps read as -- and the
+ * channel count is a multiple of 128) and a gather by eight warps of 16-byte asynchronous copies (any zero point,
+ * channels a multiple of 16).  on = 0 keeps the plan on the gather (testing aid: both must agree bit for bit);
+ * cugl_conv2d_plan_uses_tma_im2col tells which one the plan's next run takes (1 / 0). */
+CUGL_API cugl_status cugl_conv2d_plan_allow_tma_im2col(cugl_conv_plan *plan, int on);
+CUGL_API int         cugl_conv2d_plan_uses_tma_im2col(const cugl_conv_plan *plan);
 /* as cugl_gemmlowp_plan_set_epilogue_warps / cugl_gemmlowp_plan_set_channel_major (the latter acts on the
  * lowerings that run the plain GEMM kernel: 1x1 convolutions and the explicit im2col path) */
 CUGL_API cugl_status cugl_conv2d_plan_set_epilogue_warps(cugl_conv_plan *plan, int warps);

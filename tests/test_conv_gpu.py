@@ -14,7 +14,7 @@ CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
 
 
 def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1),
-             implicit=True, want_kernel=None, tile_columns=0, paired_drain=True):
+             implicit=True, want_kernel=None, tile_columns=0, paired_drain=True, tma_im2col=True, want_tma=None):
     import torch
     B, H, W, Cc = src.shape
     OFM, kh, kw, _ = weights.shape
@@ -32,6 +32,10 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
         plan.set_tile_columns(tile_columns)
     if not paired_drain:
         plan.set_paired_drain(False)
+    if not tma_im2col:
+        plan.allow_tma_im2col(False)
+    if want_tma is not None:
+        assert plan.uses_tma_im2col == want_tma
     if want_kernel is not None:
         assert plan.kernel == want_kernel, plan.kernel
     wo, ho = plan.out_dims()
@@ -198,13 +202,16 @@ def test_fused_residual_addition(ctx, port, geom):
     plan.close()
 
 
+@pytest.mark.parametrize("OFM", [256, 384])
 @pytest.mark.parametrize("paired", [True, False])
-def test_fused_residual_addition_many_tiles(ctx, port, paired):
-    """1x1 convolution 64 -> 256 with a fused residual on 39200 output rows: 307 tiles of 128 x 256 for 148 CTAs,
-    so the paired drain of the epilogue (two tiles, one term read) runs with the residual rows of both tiles."""
+def test_short_k_many_tiles_with_and_without_residual(ctx, port, paired, OFM):
+    """1x1 convolution 64 -> 256 / 384 on 39200 output rows, with and without a fused residual: 307 row blocks for 148
+    CTAs, so every CTA drains pairs of tiles and some a single one, the last row block is ragged, and with 384
+    channels the second column block is half empty.  paired: two tiles of a column block drained together (one term
+    read for two elements) or every tile on its own."""
     import torch
-    rng = np.random.default_rng(99)
-    B, H, W, Cc, OFM = 8, 70, 70, 64, 256
+    rng = np.random.default_rng(99 + OFM)
+    B, H, W, Cc = 8, 70, 70, 64
     src = q8_uniform(rng, (B, H, W, Cc), np.uint8)
     wgt = q8_uniform(rng, (OFM, 1, 1, Cc), np.int8, -127, 127)
     bias = rng.integers(-3000, 3001, OFM).astype(np.int32)
@@ -216,16 +223,24 @@ def test_fused_residual_addition_many_tiles(ctx, port, paired):
     want = port.activation_qasymm8(port.add_qasymm8(conv, res, q, q, q), "relu", 0.0, 0.0, q, q)
     desc, keep = capi.make_conv_desc(B, H, W, Cc, OFM, 1, 1, (1, 1), (0, 0, 0, 0), (1, 1), capi.U8, capi.S8, q[1], 0,
                                      multipliers=mult, shifts=shift, dst_zp=q[1], min_bound=0, max_bound=255)
+    d_src, d_bias = torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda()
     plan = capi.ConvPlan(ctx, desc, keep)
-    plan.set_residual(q[0], q, q, act=capi.ACT_RELU, act_a=0.0)
     plan.set_paired_drain(paired)
+    plan.set_channel_major(-1)
     plan.prepare(torch.from_numpy(wgt.view(np.uint8)).cuda())
+    d_dst = torch.full(conv.shape, 0xA5, dtype=torch.uint8, device="cuda")
+    for _ in range(2):
+        plan.run(d_src, d_bias, d_dst)
+    ctx.sync()
+    assert np.array_equal(d_dst.cpu().numpy(), conv)
+    plan.set_residual(q[0], q, q, act=capi.ACT_RELU, act_a=0.0)
     d_res = torch.from_numpy(res).cuda()
-    d_dst = torch.empty(conv.shape, dtype=torch.uint8, device="cuda")
-    plan.run_residual(torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda(), d_res, d_dst)
+    d_dst.fill_(0x5A)
+    for _ in range(2):
+        plan.run_residual(d_src, d_bias, d_res, d_dst)
     ctx.sync()
     assert np.array_equal(d_dst.cpu().numpy(), want)
-    plan.run_residual(torch.from_numpy(src).cuda(), torch.from_numpy(bias).cuda(), d_res, d_res)  # in place
+    plan.run_residual(d_src, d_bias, d_res, d_res)  # in place
     ctx.sync()
     assert np.array_equal(d_res.cpu().numpy(), want)
     plan.close()
@@ -278,3 +293,41 @@ def test_transpose_batched_is_the_nchw_nhwc_permute(ctx):
     ctx.transpose_batched(d_x, d_y, 37, 11 * 13, 3)
     ctx.sync()
     assert np.array_equal(d_y.cpu().numpy(), x.transpose(0, 2, 1))
+
+
+@pytest.mark.parametrize("geom", [(3, 1, 1, 1, 128, 64, 14, 14), (3, 2, 1, 1, 128, 128, 28, 28), (3, 1, 1, 1, 256, 256, 14, 14),
+                                  (3, 1, 1, 1, 512, 96, 7, 7), (3, 1, 2, 2, 128, 130, 19, 23), (5, 2, 2, 1, 128, 40, 21, 17),
+                                  (1, 2, 0, 1, 256, 64, 19, 23), (3, 2, (0, 1, 0, 1), 1, 128, 64, 16, 18)])
+@pytest.mark.parametrize("batch", [1, 5])
+def test_tma_im2col_conv_vs_oracle(ctx, port, geom, batch):
+    """The im2col-mode TMA route of the implicit lowering (input zero point 0, channels a multiple of 128) on the 3x3
+    layer shapes of ResNet-50 (stride 1 and 2), dilated, 5x5 / 2, strided 1x1 and asymmetric padding: against the oracle,
+    against the gather route, and with every tile width.  batch 5 makes tiles straddle image boundaries and leaves a
+    ragged last tile (rows beyond the last image must read as zero and are never stored)."""
+    k, s, p, d, Cc, OFM, H, W = geom
+    pad = p if isinstance(p, tuple) else (p, p, p, p)
+    rng = np.random.default_rng(k * 1000 + s * 100 + Cc + batch)
+    src = q8_uniform(rng, (batch, H, W, Cc), np.uint8)
+    wgt = q8_uniform(rng, (OFM, k, k, Cc), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, OFM).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.03, ws, 0.05 * k)
+    want = port.conv2d_nhwc(src, wgt, bias, (s, s), pad, 0, 0, mult, shift, 3, 0, 255, dilation=(d, d))
+    gather = gpu_conv(ctx, src, wgt, bias, (s, s), pad, 0, 0, mult, shift, 3, 0, 255, dilation=(d, d), want_kernel="implicit",
+                      tma_im2col=False, want_tma=False)
+    assert np.array_equal(gather, want)
+    for cols in (0, 256, 128, 64):
+        got = gpu_conv(ctx, src, wgt, bias, (s, s), pad, 0, 0, mult, shift, 3, 0, 255, dilation=(d, d), want_kernel="implicit",
+                       tile_columns=cols, want_tma=True)
+        assert np.array_equal(got, want), (cols, np.argwhere(got != want)[:5])
+
+
+def test_tma_im2col_is_not_used_where_it_is_inexact(ctx):
+    """A non-zero input zero point (out-of-image taps would read 0 instead of it) or a channel count that is not a
+    multiple of 128 keep the plan on the gather."""
+    for Cc, zp, want in ((128, 0, True), (128, 3, False), (64, 0, False)):
+        desc, keep = capi.make_conv_desc(1, 8, 8, Cc, 16, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1), capi.U8, capi.S8, zp, 0,
+                                         multiplier=1 << 30, shift=8, dst_zp=0, min_bound=0, max_bound=255)
+        plan = capi.ConvPlan(ctx, desc, keep)
+        assert plan.uses_tma_im2col == want
+        plan.close()
