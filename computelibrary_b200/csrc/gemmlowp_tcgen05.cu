@@ -141,6 +141,18 @@ __device__ __forceinline__ void tma_load_im2col(uint32_t dst, const CUtensorMap 
                  : "memory");
 }
 
+// the same load in a cta_group::2 pipeline: the bytes are credited to the barrier at bar_cluster_addr in the leader CTA
+__device__ __forceinline__ void tma_load_im2col_pair(uint32_t dst, const CUtensorMap *map, int c, int w, int h, int n,
+                                                     uint16_t off_w, uint16_t off_h, uint32_t bar_cluster_addr)
+{
+    asm volatile("cp.async.bulk.tensor.4d.cta_group::2.shared::cluster.global.im2col.mbarrier::complete_tx::bytes "
+                 "[%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+                 :
+                 : "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c), "r"(w), "r"(h), "r"(n),
+                   "h"(off_w), "h"(off_h)
+                 : "memory");
+}
+
 // ---- tcgen05 -------------------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before()
 {
@@ -1960,18 +1972,52 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (kb == 0) trace_event(tp.trace, ti, 0);
                 const uint32_t leader_full = map_to_cta(full_bar(st), 0);
                 const bool     withheld    = g == tp.withhold_kb && blockIdx.x == 0; // the leader of cluster 0
-                if (leader && !withheld)
+                if (tp.conv_c != 0)
                 {
-                    // the bytes of both CTAs
-                    mbar_expect_tx(full_bar(st), half < 0 ? 2 * P::STAGE : 2 * (P::A_STAGE_K + P::B_STAGE / 2));
-                }
+                    // implicit convolution: im2col-mode loads of this CTA's 128 output pixels; K sub-blocks beyond K are
+                    // neither loaded nor multiplied
+                    const int t  = fast_div(m0, tp.conv_div_wo);
+                    const int q  = m0 - t * tp.conv_wo;
+                    const int n  = fast_div(t, tp.conv_div_ho);
+                    const int pp = t - n * tp.conv_ho;
+                    const int w0 = q * tp.conv_sx - tp.conv_pl, h0 = pp * tp.conv_sy - tp.conv_pt;
+                    const int left  = (tp.K - kb * KSUB * BLOCK_K + BLOCK_K - 1) / BLOCK_K;
+                    const int valid = left < KSUB ? left : KSUB;
+                    if (leader)
+                    {
+                        mbar_expect_tx(full_bar(st), 2 * valid * (A_STAGE + (half < 0 ? P::B_SUB : P::B_SUB / 2)));
+                    }
 #pragma unroll
-                for (int sub = 0; sub < KSUB && !withheld; ++sub)
+                    for (int sub = 0; sub < KSUB; ++sub)
+                    {
+                        if (sub < valid)
+                        {
+                            const int k0  = (kb * KSUB + sub) * BLOCK_K;
+                            const int tap = k0 / tp.conv_c, c0 = k0 - tap * tp.conv_c;
+                            const int ky = tap / tp.conv_kw, kx = tap - ky * tp.conv_kw;
+                            tma_load_im2col_pair(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, c0, w0, h0, n,
+                                                 static_cast<uint16_t>(kx * tp.conv_dx),
+                                                 static_cast<uint16_t>(ky * tp.conv_dy), leader_full);
+                            tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, half < 0 ? &tmap_b : &tmap_bh, k0, n0,
+                                             leader_full);
+                        }
+                    }
+                }
+                else
                 {
-                    const int k0 = (kb * KSUB + sub) * BLOCK_K;
-                    tma_load_2d_pair(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, leader_full);
-                    tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, half < 0 ? &tmap_b : &tmap_bh, k0, n0,
-                                     leader_full);
+                    if (leader && !withheld)
+                    {
+                        // the bytes of both CTAs
+                        mbar_expect_tx(full_bar(st), half < 0 ? 2 * P::STAGE : 2 * (P::A_STAGE_K + P::B_STAGE / 2));
+                    }
+#pragma unroll
+                    for (int sub = 0; sub < KSUB && !withheld; ++sub)
+                    {
+                        const int k0 = (kb * KSUB + sub) * BLOCK_K;
+                        tma_load_2d_pair(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, k0, m0, leader_full);
+                        tma_load_2d_pair(sB + st * P::B_STAGE + sub * P::B_SUB, half < 0 ? &tmap_b : &tmap_bh, k0, n0,
+                                         leader_full);
+                    }
                 }
                 kb += kProdLanes;
                 while (kb >= num_kb)
@@ -2044,9 +2090,12 @@ __global__ void __launch_bounds__(kThreads, 1)
 #pragma unroll
                         for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                         {
-                            umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
-                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, idesc,
-                                         (kb | sub | k) != 0 ? 1u : 0u);
+                            if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K) // beyond K: zero fill, or not loaded at all
+                            {
+                                umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                             b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, idesc,
+                                             (kb | sub | k) != 0 ? 1u : 0u);
+                            }
                         }
                     }
                     umma_commit_pair(empty_bar(s)); // frees this stage in both CTAs
@@ -2508,6 +2557,18 @@ int stage_mode(const GemmOperands &op, const EpilogueParams &ep)
     return kStageWide;
 }
 
+void fill_conv_params(TileParams &tp, const GemmOperands &op)
+{
+    tp.conv_c = 0;
+    if (op.conv != nullptr)
+    {
+        const ConvOperands &cv = *op.conv;
+        tp.conv_c = cv.C, tp.conv_kw = cv.kw, tp.conv_wo = cv.Wo, tp.conv_ho = cv.Ho, tp.conv_sx = cv.sx, tp.conv_sy = cv.sy;
+        tp.conv_pl = cv.pad_l, tp.conv_pt = cv.pad_t, tp.conv_dx = cv.dil_x, tp.conv_dy = cv.dil_y;
+        tp.conv_div_wo = make_fastdiv(cv.Wo), tp.conv_div_ho = make_fastdiv(cv.Ho);
+    }
+}
+
 void fill_extra_dst(TileParams &tp, const GemmOperands &op)
 {
     tp.residual   = static_cast<const uint8_t *>(op.residual);
@@ -2663,14 +2724,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
-    tp.conv_c  = 0;
-    if (op.conv != nullptr)
-    {
-        const ConvOperands &cv = *op.conv;
-        tp.conv_c = cv.C, tp.conv_kw = cv.kw, tp.conv_wo = cv.Wo, tp.conv_ho = cv.Ho, tp.conv_sx = cv.sx, tp.conv_sy = cv.sy;
-        tp.conv_pl = cv.pad_l, tp.conv_pt = cv.pad_t, tp.conv_dx = cv.dil_x, tp.conv_dy = cv.dil_y;
-        tp.conv_div_wo = make_fastdiv(cv.Wo), tp.conv_div_ho = make_fastdiv(cv.Ho);
-    }
+    fill_conv_params(tp, op);
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
     ctx->withhold_kb = -1;
@@ -2737,7 +2791,8 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     using P = SmemPlan2<STAGES, KSUB>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     CUtensorMap map_a, map_b, map_bh;
-    if (!encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M) ||
+    if (!(op.conv != nullptr ? encode_im2col_map(&map_a, *op.conv)
+                             : encode_operand_map(&map_a, op.a, op.M, op.K, op.lda, BLOCK_M)) ||
         !encode_operand_map(&map_b, op.bt, op.N, op.K, op.ldbt, P::BLOCK_N / 2) ||
         !encode_operand_map(&map_bh, op.bt, op.N, op.K, op.ldbt, P::BLOCK_N / 4))
     {
@@ -2763,7 +2818,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.split_tail = op.split_tail >= 0 ? 1 : 0;
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
-    tp.conv_c  = 0;
+    fill_conv_params(tp, op);
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
     ctx->withhold_kb = -1;
@@ -2894,7 +2949,7 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
         return s32 ? launch_variant_cm<256, 4, 1, true>(ctx, op, ep) : launch_variant_cm<256, 4, 1, false>(ctx, op, ep);
     }
 #if CUGL_TC_FULL_BUILD
-    if (allow_pair && op.conv == nullptr && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
+    if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
     {
         return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);
     }

@@ -1288,7 +1288,7 @@ extern "C"
                 ot.channel_major = -1;
                 if (gemmlowp_conv_tma_supported(ot))
                 {
-                    return launch_gemmlowp_tcgen05(plan->ctx, ot, c.epilogue(d.has_bias ? d_bias : nullptr, 0), false);
+                    return launch_gemmlowp_tcgen05(plan->ctx, ot, c.epilogue(d.has_bias ? d_bias : nullptr, 0), c.allow_pair);
                 }
             }
             if (gemmlowp_conv_tcgen05_supported(op, cv))

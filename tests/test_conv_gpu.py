@@ -331,3 +331,25 @@ def test_tma_im2col_is_not_used_where_it_is_inexact(ctx):
         plan = capi.ConvPlan(ctx, desc, keep)
         assert plan.uses_tma_im2col == want
         plan.close()
+
+
+@pytest.mark.parametrize("geom", [(26, 28, 128, 256, 1), (27, 30, 128, 320, 1), (50, 39, 256, 256, 2)])
+def test_tma_im2col_on_the_sm_pair_kernel(ctx, port, geom):
+    """Convolutions with at least one 256 x 256 tile per SM pair run the im2col-mode route on the cta_group::2 kernel
+    (each CTA loads the patches of its own 128 output pixels): against the gather route on the whole output, against
+    the oracle on the first and last images; ragged M, ragged N (320 channels) and stride 2."""
+    B, H, Cc, OFM, s = geom
+    rng = np.random.default_rng(B * 10 + s)
+    src = q8_uniform(rng, (B, H, H, Cc), np.uint8)
+    wgt = q8_uniform(rng, (OFM, 3, 3, Cc), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, OFM).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.03, ws, 0.15)
+    tma = gpu_conv(ctx, src, wgt, bias, (s, s), (1, 1, 1, 1), 0, 0, mult, shift, 3, 0, 255, want_kernel="implicit", want_tma=True)
+    gather = gpu_conv(ctx, src, wgt, bias, (s, s), (1, 1, 1, 1), 0, 0, mult, shift, 3, 0, 255, want_kernel="implicit",
+                      tma_im2col=False, want_tma=False)
+    assert np.array_equal(tma, gather), np.argwhere(tma != gather)[:5]
+    for sl in (slice(0, 1), slice(B - 1, B)):
+        want = port.conv2d_nhwc(src[sl], wgt, bias, (s, s), (1, 1, 1, 1), 0, 0, mult, shift, 3, 0, 255)
+        assert np.array_equal(tma[sl], want)
+    assert 0.01 < (tma == 0).mean() < 0.99 and 0.01 < (tma == 255).mean() + (tma < 255).mean()
