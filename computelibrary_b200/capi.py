@@ -116,6 +116,7 @@ _SIGNATURES = {
     "cugl_gemmlowp_plan_kernel": (C.c_char_p, [_vp]),
     "cugl_gemmlowp_plan_force_simt": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_allow_pair_kernel": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_set_host_pipeline": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_launches": (C.c_int, [_vp]),
     "cugl_gemmlowp_run_noalloc": (C.c_int, [_vp, C.POINTER(GemmDesc), _vp, _vp, _vp, _vp, _vp, _vp]),
     "cugl_gemmlowp_noalloc_status": (C.c_int, [_vp]),
@@ -530,6 +531,9 @@ class GemmPlan:
     def set_tail_split(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_tail_split(self.handle, int(on)))
 
+    def set_host_pipeline(self, blocks: int):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_host_pipeline(self.handle, int(blocks)))
+
     def allow_pair_kernel(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_allow_pair_kernel(self.handle, int(on)))
 
@@ -649,7 +653,7 @@ class ConvPlan:
     def allow_implicit(self, on: bool = True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_implicit(self.handle, int(on)))
 
-    def allow_tma_im2col(self, on: bool = True):
+    def allow_tma_im2col(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_allow_tma_im2col(self.handle, int(on)))
 
     @property

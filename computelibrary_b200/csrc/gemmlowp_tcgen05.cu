@@ -232,6 +232,19 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr)
     return d;
 }
 
+// The same for rows of 64 bytes in the 64-byte swizzle (the patch tiles of a 64-channel convolution: one filter tap per
+// tile): 8-row groups 512 bytes apart, layout type 4.
+__device__ __forceinline__ uint64_t make_kmajor_sw64_desc(uint32_t smem_addr)
+{
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr & 0x3ffff) >> 4);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(512 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(4) << 61;
+    return d;
+}
+
 // Optional tracing: event e of the i-th tile this CTA processes, as a %globaltimer value (ns).
 // Layout: trace[(cta * kTraceTiles + i) * kTraceEvents + e].  Events: 0 producer issued the first copy,
 // 1 MMA issuer owns an accumulator, 2 first operand stage has landed, 3 last MMA issued, 4 epilogue sees the
@@ -1562,19 +1575,51 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const int w0 = q * tp.conv_sx - tp.conv_pl, h0 = pp * tp.conv_sy - tp.conv_pt;
                     const int left  = (tp.K - kb * KSUB * BLOCK_K + BLOCK_K - 1) / BLOCK_K;
                     const int valid = left < KSUB ? left : KSUB;
-                    mbar_expect_tx(full_bar(st), valid * (A_STAGE + P::B_SUB));
-#pragma unroll
-                    for (int sub = 0; sub < KSUB; ++sub)
+                    if (tp.conv_c == 64)
                     {
-                        if (sub < valid)
+                        // 64 channels: a 128-byte K block is two filter taps, loaded as two tiles of 128 pixels x 64 bytes
+                        // (64-byte swizzle) one behind the other; the last block of an odd tap count holds one
+                        const int taps_left = (tp.K >> 6) - 2 * kb * KSUB;
+                        const int taps      = taps_left < 2 * KSUB ? taps_left : 2 * KSUB;
+                        mbar_expect_tx(full_bar(st), taps * (A_STAGE / 2) + valid * P::B_SUB);
+#pragma unroll
+                        for (int j = 0; j < 2 * KSUB; ++j)
                         {
-                            const int k0  = (kb * KSUB + sub) * BLOCK_K;
-                            const int tap = k0 / tp.conv_c, c0 = k0 - tap * tp.conv_c;
-                            const int ky = tap / tp.conv_kw, kx = tap - ky * tp.conv_kw;
-                            tma_load_im2col(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, c0, w0, h0, n,
-                                            static_cast<uint16_t>(kx * tp.conv_dx), static_cast<uint16_t>(ky * tp.conv_dy),
+                            if (j < taps)
+                            {
+                                const int tap = 2 * kb * KSUB + j;
+                                const int ky = tap / tp.conv_kw, kx = tap - ky * tp.conv_kw;
+                                tma_load_im2col(sA + st * P::A_STAGE_K + j * (A_STAGE / 2), &tmap_a, 0, w0, h0, n,
+                                                static_cast<uint16_t>(kx * tp.conv_dx),
+                                                static_cast<uint16_t>(ky * tp.conv_dy), full_bar(st));
+                            }
+                        }
+#pragma unroll
+                        for (int sub = 0; sub < KSUB; ++sub)
+                        {
+                            if (sub < valid)
+                            {
+                                tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, (kb * KSUB + sub) * BLOCK_K, n0,
                                             full_bar(st));
-                            tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
+                            }
+                        }
+                    }
+                    else
+                    {
+                        mbar_expect_tx(full_bar(st), valid * (A_STAGE + P::B_SUB));
+#pragma unroll
+                        for (int sub = 0; sub < KSUB; ++sub)
+                        {
+                            if (sub < valid)
+                            {
+                                const int k0  = (kb * KSUB + sub) * BLOCK_K;
+                                const int tap = k0 / tp.conv_c, c0 = k0 - tap * tp.conv_c;
+                                const int ky = tap / tp.conv_kw, kx = tap - ky * tp.conv_kw;
+                                tma_load_im2col(sA + st * P::A_STAGE_K + sub * A_STAGE, &tmap_a, c0, w0, h0, n,
+                                                static_cast<uint16_t>(kx * tp.conv_dx),
+                                                static_cast<uint16_t>(ky * tp.conv_dy), full_bar(st));
+                                tma_load_2d(sB + st * P::B_STAGE + sub * P::B_SUB, &tmap_b, k0, n0, full_bar(st));
+                            }
                         }
                     }
                     issued |= 1u << st;
@@ -1640,7 +1685,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             uint32_t ph = 0, aph = 0;
             bool     ok = true, have = false; // have: the current stage's operands are known to have landed
             int      ti = 0;
-            const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
+            // 64-channel convolution through im2col-mode loads: the A stage holds 64-byte rows, a filter tap per 8 KB
+            const bool     a_sw64  = !kCM && tp.conv_c == 64;
+            const uint64_t a_desc0 = a_sw64 ? make_kmajor_sw64_desc(sA) : make_kmajor_sw128_desc(sA);
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
             for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++ti)
             {
@@ -1689,7 +1736,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                             // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
                             if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
                             {
-                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                // 32 bytes on inside the swizzled row: + 2; 64-byte rows: the next tap's tile after two steps
+                                const uint32_t a_k = a_sw64 ? static_cast<uint32_t>((k >> 1) * ((A_STAGE / 2) >> 4) + 2 * (k & 1))
+                                                            : 2u * k;
+                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + a_k,
                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
                                         (kb | sub | k) != 0 ? 1u : 0u);
                             }
@@ -2676,10 +2726,11 @@ bool encode_im2col_map(CUtensorMap *map, const ConvOperands &cv)
     const int        lower[2]   = {-cv.pad_l, -cv.pad_t};
     const int        upper[2]   = {(cv.Wo - 1) * cv.sx - cv.pad_l - (cv.W - 1), (cv.Ho - 1) * cv.sy - cv.pad_t - (cv.H - 1)};
     const cuuint32_t estr[4]    = {1, static_cast<cuuint32_t>(cv.sx), static_cast<cuuint32_t>(cv.sy), 1};
+    const bool       narrow     = cv.C == 64; // one tap = 64 bytes: 64-byte rows in the 64-byte swizzle
     return fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void *>(cv.src), dims, strides, lower, upper,
-              static_cast<cuuint32_t>(BLOCK_K), static_cast<cuuint32_t>(BLOCK_M), estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-              CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+              static_cast<cuuint32_t>(narrow ? 64 : BLOCK_K), static_cast<cuuint32_t>(BLOCK_M), estr,
+              CU_TENSOR_MAP_INTERLEAVE_NONE, narrow ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
+              CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // what the im2col-mode route needs besides the GEMM conditions
@@ -2688,7 +2739,7 @@ bool conv_tma_supported(const GemmOperands &op)
     const ConvOperands &cv = *op.conv;
     const int           up_w = (cv.Wo - 1) * cv.sx - cv.pad_l - (cv.W - 1), up_h = (cv.Ho - 1) * cv.sy - cv.pad_t - (cv.H - 1);
     auto                corner_ok = [](int v) { return v >= -128 && v <= 127; };
-    return (cv.C % BLOCK_K) == 0 && (reinterpret_cast<uintptr_t>(cv.src) & 15) == 0 && cv.sx >= 1 && cv.sx <= 8 &&
+    return ((cv.C % BLOCK_K) == 0 || cv.C == 64) && (reinterpret_cast<uintptr_t>(cv.src) & 15) == 0 && cv.sx >= 1 && cv.sx <= 8 &&
            cv.sy >= 1 && cv.sy <= 8 && corner_ok(-cv.pad_l) && corner_ok(-cv.pad_t) && corner_ok(up_w) && corner_ok(up_h) &&
            (cv.kw - 1) * cv.dil_x < 256 && (cv.kh - 1) * cv.dil_y < 256 && get_encode_im2col_fn() != nullptr;
 }
@@ -2925,7 +2976,7 @@ bool CUGL_TC_NAME(gemmlowp_tcgen05_supported)(const GemmOperands &op)
 // implicit convolution through im2col-mode loads (op.conv set): the weights as for the GEMM, the input tensor as above
 bool CUGL_TC_NAME(gemmlowp_conv_tma_supported)(const GemmOperands &op)
 {
-    if (op.conv == nullptr || op.M <= 0 || op.N <= 0 || op.K <= 0 || (op.K % BLOCK_K) != 0)
+    if (op.conv == nullptr || op.M <= 0 || op.N <= 0 || op.K <= 0 || (op.K % (op.conv->C == 64 ? 64 : BLOCK_K)) != 0)
     {
         return false;
     }
@@ -2949,7 +3000,7 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
         return s32 ? launch_variant_cm<256, 4, 1, true>(ctx, op, ep) : launch_variant_cm<256, 4, 1, false>(ctx, op, ep);
     }
 #if CUGL_TC_FULL_BUILD
-    if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op))
+    if (allow_pair && CUGL_TC_NAME(gemmlowp_tcgen05_uses_pair)(op) && !(op.conv != nullptr && op.conv->C == 64)) // (64-byte-swizzle tiles: one-CTA kernels)
     {
         return s32 ? launch_variant_2cta<3, 2, true>(ctx, op, ep) : launch_variant_2cta<3, 2, false>(ctx, op, ep);
     }

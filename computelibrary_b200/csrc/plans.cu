@@ -361,12 +361,14 @@ struct cugl_gemm_plan
     // cugl_gemmlowp_run_host pipelines row blocks over three streams: copies in, GEMM (the context's stream),
     // copies out
     cudaStream_t             s_in = nullptr, s_out = nullptr;
+    int                      host_blocks = 0; // row blocks of the host-buffer pipeline, 0 = default
     std::vector<cudaEvent_t> ev_in, ev_done;
 };
 
 namespace
 {
-constexpr int kHostPipelineBlocks = 8;
+constexpr int kHostPipelineBlocks    = 8;  // default number of row blocks of the host-buffer pipeline
+constexpr int kMaxHostPipelineBlocks = 32;
 
 void apply_quant_fields(cugl_gemm_plan *p, const cugl_gemm_desc *d)
 {
@@ -590,19 +592,46 @@ extern "C"
         // block i is multiplied and block i-1 travels back (PCIe is full duplex), so the call costs about the
         // longer of the two copies instead of copy + GEMM + copy.  Pinned host buffers are needed for the overlap;
         // pageable ones still work, serialised by the driver.
-        const int rows_per = static_cast<int>(round_up((d.M + kHostPipelineBlocks - 1) / kHostPipelineBlocks, 256));
-        if (d.batch == 1 && d.M >= 2048 && d.M > rows_per)
+        // Row blocks of the pipeline.  The call costs about (first block in) + (all blocks out) or (all blocks in) +
+        // (last block out), whichever is longer, and large copies run nearer the link rate than small ones: so the
+        // default schedule is tapered -- 1/16, 1/8, 1/4, 1/4, 1/8, 1/8, 1/16 of the rows -- small blocks at both ends,
+        // large ones in the middle.  Measured on 4096 x 4096 x 4096 (16.8 MB each way, 55 GB/s per direction alone):
+        // 0.68 ms unpipelined, 0.61 ms with eight equal blocks, 0.55 ms with three equal blocks or this schedule;
+        // copies in both directions with no dependency between them take 0.39 ms.
+        std::vector<int> block_rows;
+        if (d.batch == 1 && d.M >= 2048)
+        {
+            if (plan->host_blocks > 0)
+            {
+                const int rows_per = static_cast<int>(round_up((d.M + plan->host_blocks - 1) / plan->host_blocks, 256));
+                for (int r0 = 0; r0 < d.M; r0 += rows_per) block_rows.push_back(d.M - r0 < rows_per ? d.M - r0 : rows_per);
+            }
+            else
+            {
+                static const int sixteenths[] = {1, 2, 4, 4, 2, 2, 1};
+                int              r0          = 0;
+                for (int f : sixteenths)
+                {
+                    int rows = static_cast<int>(round_up(static_cast<int64_t>(d.M) * f / 16, 256));
+                    rows     = d.M - r0 < rows ? d.M - r0 : rows;
+                    if (rows > 0) block_rows.push_back(rows);
+                    r0 += rows;
+                }
+                if (r0 < d.M) block_rows.push_back(d.M - r0);
+            }
+        }
+        if (block_rows.size() > 1)
         {
             if (plan->s_in == nullptr)
             {
                 CUGL_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&plan->s_in, cudaStreamNonBlocking));
                 CUGL_CUDA_TRY(ctx, cudaStreamCreateWithFlags(&plan->s_out, cudaStreamNonBlocking));
-                plan->ev_in.resize(kHostPipelineBlocks + 1);
-                plan->ev_done.resize(kHostPipelineBlocks + 1);
+                plan->ev_in.resize(kMaxHostPipelineBlocks + 1);
+                plan->ev_done.resize(kMaxHostPipelineBlocks + 1);
                 for (cudaEvent_t &e : plan->ev_in) CUGL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
                 for (cudaEvent_t &e : plan->ev_done) CUGL_CUDA_TRY(ctx, cudaEventCreateWithFlags(&e, cudaEventDisableTiming));
             }
-            const int      n_blocks = (d.M + rows_per - 1) / rows_per;
+            const int      n_blocks = static_cast<int>(block_rows.size());
             const uint8_t *ha       = static_cast<const uint8_t *>(h_a);
             uint8_t       *da       = static_cast<uint8_t *>(plan->d_a_stage);
             uint8_t       *dd       = static_cast<uint8_t *>(plan->d_dst_stage);
@@ -613,18 +642,16 @@ extern "C"
                 CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(plan->d_bias_stage, h_bias, sizeof(int32_t) * d.N, cudaMemcpyHostToDevice,
                                                    plan->s_in));
             }
-            for (int i = 0; i < n_blocks; ++i)
+            for (int i = 0, r0 = 0; i < n_blocks; r0 += block_rows[i], ++i)
             {
-                const int    r0   = i * rows_per;
-                const size_t rows = static_cast<size_t>(d.M - r0 < rows_per ? d.M - r0 : rows_per);
+                const size_t rows = static_cast<size_t>(block_rows[i]);
                 CUGL_CUDA_TRY(ctx, cudaMemcpyAsync(da + static_cast<size_t>(r0) * d.lda, ha + static_cast<size_t>(r0) * d.lda,
                                                    rows * d.lda, cudaMemcpyHostToDevice, plan->s_in));
                 CUGL_CUDA_TRY(ctx, cudaEventRecord(plan->ev_in[i], plan->s_in));
             }
-            for (int i = 0; i < n_blocks; ++i)
+            for (int i = 0, r0 = 0; i < n_blocks; r0 += block_rows[i], ++i)
             {
-                const int r0   = i * rows_per;
-                const int rows = d.M - r0 < rows_per ? d.M - r0 : rows_per;
+                const int rows = block_rows[i];
                 CUGL_CUDA_TRY(ctx, cudaStreamWaitEvent(ctx->stream, plan->ev_in[i], 0));
                 CUGL_TRY(plan->core.gemm(da + static_cast<size_t>(r0) * d.lda, d.lda, rows, dd + static_cast<size_t>(r0) * d.ldd,
                                          d.ldd, d.has_bias ? plan->d_bias_stage : nullptr, 0, r0));
@@ -760,6 +787,17 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_allow_pair_kernel: NULL plan");
         }
         plan->core.allow_pair = on != 0;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_gemmlowp_plan_set_host_pipeline(cugl_gemm_plan *plan, int blocks)
+    {
+        if (plan == nullptr || blocks < 0 || blocks > kMaxHostPipelineBlocks)
+        {
+            return fail(plan ? plan->ctx : nullptr, CUGL_INVALID_ARGUMENT,
+                        "cugl_gemmlowp_plan_set_host_pipeline: NULL plan or more than 32 blocks");
+        }
+        plan->host_blocks = blocks;
         return CUGL_SUCCESS;
     }
 
@@ -913,7 +951,8 @@ struct cugl_conv_plan
     bool                 skip_im2col = false;
     bool                 implicit    = false;   // gather the patches inside the GEMM kernel, no im2col matrix
     bool                 allow_implicit = true;
-    bool                 allow_tma_im2col = true; // implicit lowering: im2col-mode TMA loads where they are exact
+    int                  allow_tma_im2col = 1; // implicit lowering, im2col-mode TMA loads: 0 never, 1 where they are exact and
+                                               // measured at least level with the gather (128-channel blocks), 2 wherever exact (64 channels too)
     uint8_t             *d_cols      = nullptr; // [M][Kp] im2col matrix (allocated on first explicit run)
     uint8_t             *d_pad       = nullptr; // kConvPadBytes of the input zero point: source of out-of-image taps
     // Geometry the lowerings work on: the descriptor's own, or -- stride 2 with at most four channels -- the
@@ -1281,7 +1320,7 @@ extern "C"
             // Input zero point 0 and whole 128-channel blocks: the TMA unit builds the patch tiles itself (im2col-mode
             // tensor map, out-of-image taps read as zero = the zero point) and the GEMM kernels run unchanged; else
             // the gather kernel, whose out-of-image taps copy any zero point from the pad buffer.
-            if (plan->allow_tma_im2col && d.src_zero_point == 0)
+            if (plan->allow_tma_im2col != 0 && d.src_zero_point == 0 && (plan->eC != 64 || plan->allow_tma_im2col > 1))
             {
                 GemmOperands ot  = op;
                 ot.conv          = &cv;
@@ -1425,15 +1464,15 @@ extern "C"
         {
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_allow_tma_im2col: NULL plan");
         }
-        plan->allow_tma_im2col = on != 0;
+        plan->allow_tma_im2col = on < 0 ? 0 : (on > 2 ? 2 : on);
         return CUGL_SUCCESS;
     }
 
     int cugl_conv2d_plan_uses_tma_im2col(const cugl_conv_plan *plan)
     {
         // the conditions the plan can see; the run adds the alignment of the source pointer (16 bytes)
-        return plan != nullptr && plan->implicit && plan->allow_implicit && !plan->core.force_simt && plan->allow_tma_im2col &&
-                       plan->desc.src_zero_point == 0 && (plan->eC % 128) == 0
+        return plan != nullptr && plan->implicit && plan->allow_implicit && !plan->core.force_simt && plan->allow_tma_im2col != 0 &&
+                       plan->desc.src_zero_point == 0 && ((plan->eC % 128) == 0 || (plan->eC == 64 && plan->allow_tma_im2col > 1))
                    ? 1
                    : 0;
     }

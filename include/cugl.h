@@ -232,6 +232,9 @@ CUGL_API const char *cugl_gemmlowp_plan_kernel(const cugl_gemm_plan *plan);
 CUGL_API cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on);
 /* on = 0 keeps the plan to the one-CTA tensor-core kernels (testing aid). */
 CUGL_API cugl_status cugl_gemmlowp_plan_allow_pair_kernel(cugl_gemm_plan *plan, int on);
+/* cugl_gemmlowp_run_host splits a large product into row blocks that travel in, are multiplied and travel out as a
+ * pipeline; blocks = how many (1: no pipeline, 0: the default, at most 32).  Tuning aid; results do not depend on it. */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_host_pipeline(cugl_gemm_plan *plan, int blocks);
 /* Number of kernels one cugl_gemmlowp_run of this plan launches. */
 CUGL_API int cugl_gemmlowp_plan_launches(const cugl_gemm_plan *plan);
 /* The tensor-core kernels exist with four, eight and (256-column one-CTA tiles only) sixteen epilogue warps; the
@@ -398,10 +401,12 @@ CUGL_API const char *cugl_conv2d_plan_kernel(const cugl_conv_plan *plan);
 /* on = 0 forces the explicit im2col lowering (testing aid: both lowerings must agree bit for bit). */
 CUGL_API cugl_status cugl_conv2d_plan_allow_implicit(cugl_conv_plan *plan, int on);
 /* The implicit lowering has two ways of forming the patch tiles: im2col-mode TMA loads (the copy engine walks the
- * window origins itself; used when the input zero point is 0 -- the value out-of-image taps read as -- and the
- * channel count is a multiple of 128) and a gather by eight warps of 16-byte asynchronous copies (any zero point,
- * channels a multiple of 16).  on = 0 keeps the plan on the gather (testing aid: both must agree bit for bit);
- * cugl_conv2d_plan_uses_tma_im2col tells which one the plan's next run takes (1 / 0). */
+ * window origins itself; exact when the input zero point is 0 -- the value out-of-image taps read as) and a gather by
+ * eight warps of 16-byte asynchronous copies (any zero point, channels a multiple of 16).  on = 1 (default): TMA loads
+ * for channel counts that are multiples of 128, where they measured level with the gather; on = 2: also for exactly
+ * 64 channels (one filter tap per 64-byte-swizzle tile; correct, but measured slower than the gather); on = 0: never
+ * (testing aid: the routes must agree bit for bit).  cugl_conv2d_plan_uses_tma_im2col tells which one the plan's next
+ * run takes (1 / 0). */
 CUGL_API cugl_status cugl_conv2d_plan_allow_tma_im2col(cugl_conv_plan *plan, int on);
 CUGL_API int         cugl_conv2d_plan_uses_tma_im2col(const cugl_conv_plan *plan);
 /* as cugl_gemmlowp_plan_set_epilogue_warps / cugl_gemmlowp_plan_set_channel_major (the latter acts on the

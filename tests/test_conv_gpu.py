@@ -32,8 +32,8 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
         plan.set_tile_columns(tile_columns)
     if not paired_drain:
         plan.set_paired_drain(False)
-    if not tma_im2col:
-        plan.allow_tma_im2col(False)
+    if tma_im2col is not True:
+        plan.allow_tma_im2col(int(tma_im2col))  # 0: the gather; 2: TMA loads for 64-channel inputs too
     if want_tma is not None:
         assert plan.uses_tma_im2col == want_tma
     if want_kernel is not None:
@@ -297,10 +297,13 @@ def test_transpose_batched_is_the_nchw_nhwc_permute(ctx):
 
 @pytest.mark.parametrize("geom", [(3, 1, 1, 1, 128, 64, 14, 14), (3, 2, 1, 1, 128, 128, 28, 28), (3, 1, 1, 1, 256, 256, 14, 14),
                                   (3, 1, 1, 1, 512, 96, 7, 7), (3, 1, 2, 2, 128, 130, 19, 23), (5, 2, 2, 1, 128, 40, 21, 17),
-                                  (1, 2, 0, 1, 256, 64, 19, 23), (3, 2, (0, 1, 0, 1), 1, 128, 64, 16, 18)])
+                                  (1, 2, 0, 1, 256, 64, 19, 23), (3, 2, (0, 1, 0, 1), 1, 128, 64, 16, 18),
+                                  (3, 1, 1, 1, 64, 64, 14, 14), (3, 2, 1, 1, 64, 96, 28, 28), (5, 1, 2, 1, 64, 40, 13, 11),
+                                  (3, 1, 1, 1, 64, 300, 10, 12), (2, 1, (0, 1, 0, 1), 1, 64, 64, 9, 9)])
 @pytest.mark.parametrize("batch", [1, 5])
 def test_tma_im2col_conv_vs_oracle(ctx, port, geom, batch):
-    """The im2col-mode TMA route of the implicit lowering (input zero point 0, channels a multiple of 128) on the 3x3
+    """The im2col-mode TMA route of the implicit lowering (input zero point 0, channels a multiple of 128, or 64 channels
+    as 64-byte-swizzle tiles of one filter tap each: odd and even tap counts) on the 3x3
     layer shapes of ResNet-50 (stride 1 and 2), dilated, 5x5 / 2, strided 1x1 and asymmetric padding: against the oracle,
     against the gather route, and with every tile width.  batch 5 makes tiles straddle image boundaries and leaves a
     ragged last tile (rows beyond the last image must read as zero and are never stored)."""
@@ -318,18 +321,20 @@ def test_tma_im2col_conv_vs_oracle(ctx, port, geom, batch):
     assert np.array_equal(gather, want)
     for cols in (0, 256, 128, 64):
         got = gpu_conv(ctx, src, wgt, bias, (s, s), pad, 0, 0, mult, shift, 3, 0, 255, dilation=(d, d), want_kernel="implicit",
-                       tile_columns=cols, want_tma=True)
+                       tile_columns=cols, tma_im2col=2 if Cc == 64 else True, want_tma=True)
         assert np.array_equal(got, want), (cols, np.argwhere(got != want)[:5])
 
 
 def test_tma_im2col_is_not_used_where_it_is_inexact(ctx):
     """A non-zero input zero point (out-of-image taps would read 0 instead of it) or a channel count that is not a
-    multiple of 128 keep the plan on the gather."""
-    for Cc, zp, want in ((128, 0, True), (128, 3, False), (64, 0, False)):
+    multiple of 128 keep the plan on the gather; 64 channels take the TMA route only on request."""
+    for Cc, zp, want in ((128, 0, True), (64, 0, False), (128, 3, False), (32, 0, False), (192, 0, False)):
         desc, keep = capi.make_conv_desc(1, 8, 8, Cc, 16, 3, 3, (1, 1), (1, 1, 1, 1), (1, 1), capi.U8, capi.S8, zp, 0,
                                          multiplier=1 << 30, shift=8, dst_zp=0, min_bound=0, max_bound=255)
         plan = capi.ConvPlan(ctx, desc, keep)
         assert plan.uses_tma_im2col == want
+        plan.allow_tma_im2col(2)
+        assert plan.uses_tma_im2col == (zp == 0 and Cc in (64, 128))
         plan.close()
 
 
