@@ -311,7 +311,7 @@ def run_ours(args):
     if e2e is not None:
         e2e["h2d_gbs_per_rank"] = e2e["h2d_bytes_per_step"] / (e2e["ms_per_step"] * 1e-3) / 1e9
         e2e["d2h_gbs_per_rank"] = e2e["d2h_bytes_per_step"] / (e2e["ms_per_step"] * 1e-3) / 1e9
-        e2e["note"] = ("copies in and out overlap the GEMM in eight row blocks; the step costs about the longer copy, "
+        e2e["note"] = ("copies in and out overlap the GEMM in row blocks (small at both ends, large in the middle); the step costs about the longer copy, "
                        "so the rate above is what one rank's PCIe / host-memory path delivered with all ranks active")
     if rank != 0:
         plan.close()
