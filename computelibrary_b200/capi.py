@@ -153,6 +153,8 @@ _SIGNATURES = {
     "cugl_conv2d_plan_set_epilogue_warps": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_tma_store": (C.c_int, [_vp, C.c_int]),
+    "cugl_gemmlowp_plan_set_tma_store": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_residual": (C.c_int, [_vp, C.c_float, C.c_float, _i32, C.c_float, _i32, _i32, C.c_float,
@@ -525,6 +527,9 @@ class GemmPlan:
     def set_paired_drain(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_paired_drain(self.handle, int(on)))
 
+    def set_tma_store(self, on=True):
+        self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_tma_store(self.handle, int(on)))
+
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_gemmlowp_plan_set_channel_major(self.handle, int(mode)))
 
@@ -646,6 +651,9 @@ class ConvPlan:
 
     def set_paired_drain(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_paired_drain(self.handle, int(on)))
+
+    def set_tma_store(self, on=True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_tma_store(self.handle, int(on)))
 
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_channel_major(self.handle, int(mode)))

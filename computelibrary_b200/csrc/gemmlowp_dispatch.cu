@@ -100,7 +100,10 @@ cugl_status launch_gemmlowp_tcgen05(cugl_context *ctx, const GemmOperands &op, c
         // with a fused residual too: 50176 x 1024 x 256 + residual 69 us against 79 us row-major, 12544 x 2048 x 512
         // 43 / 53; below K = 256 the two are level with a residual (200704 x 512 x 128: 125 / 128) and the row-major
         // kernel is ahead without one (102 / 94)
-        o.channel_major = (o.K >= 256 && o.K <= kShortK && o.N >= 256) ? 1 : -1;
+        // since the row-major epilogue stores through the TMA unit the two were measured again (batch 256, row-major /
+        // channel-major): 256 -> 1024 at 14 x 14 45 / 45 us (with a residual 64 / 60), 256 -> 512 at 28 x 28 74 / 84,
+        // 1024 -> 256 27 / 29, 512 -> 1024 53 / 49, 512 -> 2048 at 7 x 7 37 / 31, 1024 -> 2048 41 / 37
+        o.channel_major = (o.K >= 512 && o.K <= kShortK && o.N >= 1024) ? 1 : -1;
     }
     const int widest = o.N > 128 ? 256 : (o.N > 64 ? 128 : 64);
     if (o.block_n < widest)

@@ -153,6 +153,33 @@ __device__ __forceinline__ void tma_load_im2col_pair(uint32_t dst, const CUtenso
                  : "memory");
 }
 
+// Tile store: a shared-memory box (written by ordinary stores, then fence_proxy_async_smem and a warp barrier) to global
+// memory through the TMA unit; rows and columns beyond the tensor's extent are clipped.  Bulk-group completion: commit,
+// then wait until the group's shared-memory reads (tma_store_wait_read) or all of it (tma_store_wait_all) are done.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int c0, int c1)
+{
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+                 :
+                 : "l"(reinterpret_cast<uint64_t>(map)), "r"(src), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void tma_store_commit()
+{
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_read()
+{
+    asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+}
+__device__ __forceinline__ void tma_store_wait_all()
+{
+    asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+}
+__device__ __forceinline__ void fence_proxy_async_smem()
+{
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
 // ---- tcgen05 -------------------------------------------------------------------------------------
 __device__ __forceinline__ void tc_fence_before()
 {
@@ -336,6 +363,7 @@ struct TileParams
     // fill value of out-of-image taps), and for C a multiple of 128.
     int      conv_c, conv_kw, conv_wo, conv_ho, conv_sx, conv_sy, conv_pl, conv_pt, conv_dx, conv_dy;
     FastDiv  conv_div_wo, conv_div_ho;
+    int      tma_store;               // one-CTA row-major kernels: staged groups leave as bulk tensor stores (tmap_out)
     long long spin_limit;             // clock64 ticks a wait on a barrier may last before the kernel gives up
     int      withhold_kb;             // >= 0: CTA 0 leaves out the copies of this k-block ordinal (test instrument
                                       // of the give-up path, cugl_context_withhold_copy_once); -1 otherwise
@@ -620,16 +648,24 @@ constexpr int kCmPitchWords  = 36;                // channel-major transpose sta
 constexpr int kCmStageBytes  = 8 * kCmPitchWords * 4;
 constexpr int kOutStageBytes = 32 * kOutRowBytes > kCmStageBytes ? 32 * kOutRowBytes : kCmStageBytes;
 
-__device__ __forceinline__ void stage_chunk(uint8_t *stage, const uint32_t *w, int group_chunk, int lane)
+// Swizzle of the staged rows.  The library's own flush reads the stage back with any conflict-free pattern (row & mask);
+// a stage the TMA unit stores must follow the tensor map's swizzle: the 16-byte piece index XORed with address bits
+// 7.. of the row, i.e. with row, row >> 1 or row >> 2 for rows of 128, 64 or 32 bytes.
+constexpr int kOutSwShift = kOutRowBytes == 128 ? 0 : (kOutRowBytes == 64 ? 1 : 2);
+__device__ __forceinline__ int stage_sw(int r, bool tma)
+{
+    return (tma ? (r >> kOutSwShift) : r) & (kOutPieces - 1);
+}
+__device__ __forceinline__ void stage_chunk(uint8_t *stage, const uint32_t *w, int group_chunk, int lane, bool tma = false)
 {
     uint8_t *row = stage + lane * kOutRowBytes;
-    const int sw = lane & (kOutPieces - 1);
+    const int sw = stage_sw(lane, tma);
     *reinterpret_cast<uint4 *>(row + (((2 * group_chunk) ^ sw) << 4))     = make_uint4(w[0], w[1], w[2], w[3]);
     *reinterpret_cast<uint4 *>(row + (((2 * group_chunk + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
 }
 
 __device__ __forceinline__ void flush_stage(const uint8_t *stage, const TileParams &tp, int m_base, int n_group,
-                                            int ncols_group, int lane)
+                                            int ncols_group, int lane, bool tma = false)
 {
     __syncwarp();
     const int p = lane & (kOutPieces - 1);
@@ -641,7 +677,7 @@ __device__ __forceinline__ void flush_stage(const uint8_t *stage, const TilePara
         const int n = n_group + p * 16;
         if (p * 16 < ncols_group && m < tp.M && n < tp.N)
         {
-            const uint4   val = *reinterpret_cast<const uint4 *>(stage + r * kOutRowBytes + ((p ^ (r & (kOutPieces - 1))) << 4));
+            const uint4   val = *reinterpret_cast<const uint4 *>(stage + r * kOutRowBytes + ((p ^ stage_sw(r, tma)) << 4));
             const int64_t off = static_cast<int64_t>(m) * tp.ldd + n;
             if (n + 16 <= tp.N && tp.vec_ok)
             {
@@ -665,6 +701,30 @@ __device__ __forceinline__ void flush_stage(const uint8_t *stage, const TilePara
                 }
             }
         }
+    }
+    __syncwarp();
+}
+
+// The same staged group (32 rows x kOutRowBytes, all of it valid) handed to the TMA unit: one bulk tensor store per
+// warp and group instead of one row-strided store per lane, which keeps the warp off the load/store pipe and does
+// not make it wait for the stores to be accepted.  The caller waits for the previous group's reads (stage_reuse_wait)
+// before it writes into the stage again.
+__device__ __forceinline__ void flush_stage_tma(const uint8_t *stage, const CUtensorMap *omap, int m_base, int n_group,
+                                                int lane)
+{
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0)
+    {
+        tma_store_2d(omap, smem_u32(stage), n_group, m_base);
+        tma_store_commit();
+    }
+}
+__device__ __forceinline__ void stage_reuse_wait(int lane)
+{
+    if (lane == 0)
+    {
+        tma_store_wait_read();
     }
     __syncwarp();
 }
@@ -760,12 +820,37 @@ __device__ __forceinline__ void release_accumulators(const AccRelease &r, int la
 template <int NCOLS, bool kS32Out, int kMode>
 __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s_col, const TileParams &tp,
                                                   const EpilogueParams &ep, int m, int n_first, int32_t row_term,
-                                                  uint8_t *stage, int lane, const AccRelease &rel)
+                                                  uint8_t *stage, int lane, const AccRelease &rel,
+                                                  const CUtensorMap *omap = nullptr)
 {
     const bool row_ok = m < tp.M;
     const int64_t row_off = static_cast<int64_t>(m) * tp.ldd;
     uint8_t      *drow    = tp.dst + row_off;
-    const bool    staged  = !kS32Out && tp.n_extra > 0; // warp-uniform
+    // omap: the warp's 32 rows x kOutRowBytes leave as one bulk tensor store from its staging area (one destination)
+    const bool    tma     = !kS32Out && omap != nullptr && tp.n_extra == 0; // warp-uniform
+    const bool    staged  = !kS32Out && (tp.n_extra > 0 || tma);            // warp-uniform
+    // chunk c of the warp's columns into the stage; the group goes out when it is complete
+    auto stage_and_flush = [&](const uint32_t *v, int c) {
+        const int gc = c & (kOutChunks - 1);
+        if (tma && gc == 0)
+        {
+            stage_reuse_wait(lane); // the previous group's store has read the stage
+        }
+        stage_chunk(stage, v, gc, lane, tma);
+        if (gc == kOutChunks - 1 || c + 1 >= NCOLS / 32)
+        {
+            const int first = c & ~(kOutChunks - 1); // first chunk of this staged group
+            const int ncols = (c + 1 - first) * 32;
+            if (tma && ncols == kOutRowBytes)
+            {
+                flush_stage_tma(stage, omap, m - lane, n_first + first * 32, lane);
+            }
+            else
+            {
+                flush_stage(stage, tp, m - lane, n_first + first * 32, ncols, lane, tma);
+            }
+        }
+    };
     uint32_t   va[32], vb[32];
     tmem_ld_x32(t_addr, va);
 #pragma unroll 1
@@ -792,11 +877,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         }
         if (staged)
         {
-            stage_chunk(stage, va, ch & (kOutChunks - 1), lane);
-            if (NCOLS / 32 == 1 || kOutChunks == 1) // a staged group holds one chunk only
-            {
-                flush_stage(stage, tp, m - lane, n_first + ch * 32, 32, lane);
-            }
+            stage_and_flush(va, ch);
         }
         else
         {
@@ -826,12 +907,7 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
             }
             if (staged)
             {
-                stage_chunk(stage, vb, (ch + 1) & (kOutChunks - 1), lane);
-                if (((ch + 1) & (kOutChunks - 1)) == kOutChunks - 1 || ch + 2 >= NCOLS / 32)
-                {
-                    const int first = (ch + 1) & ~(kOutChunks - 1); // first chunk of this staged group
-                    flush_stage(stage, tp, m - lane, n_first + first * 32, (ch + 2 - first) * 32, lane);
-                }
+                stage_and_flush(vb, ch + 1);
             }
             else
             {
@@ -919,7 +995,14 @@ struct PairDrain
     int32_t        offset, lo, hi; // wide encoding only
     AccRelease     rel;
     int            lane;
+    // Output through the TMA unit (sixteen-warp build, 64 columns per warp): stage = shared-memory address of this warp's
+    // staging area, two tiles of 32 rows x 64 bytes in the 64-byte swizzle (0: per-lane global stores); the two boxes go
+    // to (n_first, row_a) and (n_first, row_b) of the output map
+    uint32_t           stage;
+    const CUtensorMap *omap;
+    int                n_first, row_a, row_b;
 };
+constexpr int kPairStageBytes = 2 * 32 * 64; // per warp
 
 template <int G, int kMode>
 __device__ __forceinline__ void requant_columns_pair(const uint32_t *a, const uint32_t *b, const int4 *col,
@@ -962,6 +1045,32 @@ __device__ __forceinline__ void finish_chunk_pair(const PairDrain &d, int ch, ui
             wa[j] = add_clamp_u8x4(wa[j], res_a[j], d.res_floor4, d.res_cap4);
             wb[j] = add_clamp_u8x4(wb[j], res_b[j], d.res_floor4, d.res_cap4);
         }
+    }
+    if (d.stage != 0)
+    {
+        // 64-byte rows, 16-byte piece p of row r at piece p ^ ((r >> 1) & 3): the tensor map's 64-byte swizzle
+        if (ch == 0)
+        {
+            stage_reuse_wait(d.lane); // the previous pair's stores have read the stage
+        }
+        const uint32_t row = d.stage + d.lane * 64, sw = (d.lane >> 1) & 3;
+        const uint32_t p0 = ((2u * ch) ^ sw) << 4, p1 = ((2u * ch + 1u) ^ sw) << 4;
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + p0), "r"(wa[0]), "r"(wa[1]), "r"(wa[2]), "r"(wa[3]) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + p1), "r"(wa[4]), "r"(wa[5]), "r"(wa[6]), "r"(wa[7]) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + 2048 + p0), "r"(wb[0]), "r"(wb[1]), "r"(wb[2]), "r"(wb[3]) : "memory");
+        asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + 2048 + p1), "r"(wb[4]), "r"(wb[5]), "r"(wb[6]), "r"(wb[7]) : "memory");
+        if (ch == 1) // 64 columns per warp: the boxes are complete
+        {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (d.lane == 0)
+            {
+                tma_store_2d(d.omap, d.stage, d.n_first, d.row_a);
+                tma_store_2d(d.omap, d.stage + 2048, d.n_first, d.row_b);
+                tma_store_commit();
+            }
+        }
+        return;
     }
     store_row32(d.dst_a != nullptr ? d.dst_a + ch * 32 : nullptr, wa, d.cols - ch * 32, d.vec_ok);
     store_row32(d.dst_b != nullptr ? d.dst_b + ch * 32 : nullptr, wb, d.cols - ch * 32, d.vec_ok);
@@ -1012,7 +1121,7 @@ __device__ __forceinline__ void drain_pair_chunk_x16(const PairDrain &d, int ch,
     finish_chunk_pair(d, ch, wa, wb, res_a, res_b);
 }
 template <int NCOLS, int kMode>
-__device__ __noinline__ void drain_pair_x16(const PairDrain d)
+__device__ __forceinline__ void drain_pair_x16(const PairDrain d)
 {
 #pragma unroll 1
     for (int ch = 0; ch < NCOLS / 32; ++ch)
@@ -1033,9 +1142,11 @@ __device__ __noinline__ void drain_pair_x32(const PairDrain d)
 template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
                                                        const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
-                                                       int n_first, int lane, const AccRelease &rel)
+                                                       int n_first, int lane, const AccRelease &rel, uint32_t stage = 0,
+                                                       const CUtensorMap *omap = nullptr)
 {
     PairDrain d;
+    d.stage = NCOLS == 64 ? stage : 0u, d.omap = omap, d.n_first = n_first, d.row_a = ma - lane, d.row_b = mb - lane;
     d.t_a = t_a, d.t_b = t_b, d.col = s_col;
     d.dst_a      = ma < tp.M ? tp.dst + static_cast<int64_t>(ma) * tp.ldd + n_first : nullptr;
     d.dst_b      = mb < tp.M ? tp.dst + static_cast<int64_t>(mb) * tp.ldd + n_first : nullptr;
@@ -1055,7 +1166,8 @@ __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_
 template <int BLOCK_N, int kGroups>
 __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_t tmem_b, const int4 *s_col,
                                                         const TileParams &tp, const EpilogueParams &ep, int warp,
-                                                        int lane, int m0a, int m0b, int n0, const AccRelease &rel)
+                                                        int lane, int m0a, int m0b, int n0, const AccRelease &rel,
+                                                        uint32_t stage = 0, const CUtensorMap *omap = nullptr)
 {
     constexpr int  NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
     const int      quad  = warp & 3;                                      // tensor-memory lane quarter this warp may read
@@ -1065,19 +1177,19 @@ __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_
     {
         drain_accumulator_pair<NCOLS, kStagePack>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                  n0 + half * NCOLS, lane, rel);
+                                                  n0 + half * NCOLS, lane, rel, stage, omap);
     }
     else if (tp.mode == kStagePackS)
     {
         drain_accumulator_pair<NCOLS, kStagePackS>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                    s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                   n0 + half * NCOLS, lane, rel);
+                                                   n0 + half * NCOLS, lane, rel, stage, omap);
     }
     else
     {
         drain_accumulator_pair<NCOLS, kStageWide>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                  n0 + half * NCOLS, lane, rel);
+                                                  n0 + half * NCOLS, lane, rel, stage, omap);
     }
 }
 
@@ -1408,7 +1520,8 @@ __device__ __forceinline__ void epilogue_warp_tile_cm(uint32_t tmem_acc, const T
 template <int BLOCK_N, bool kS32Out, int kGroups = 1>
 __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4 *s_col, const TileParams &tp,
                                                    const EpilogueParams &ep, int warp, int lane, int m0, int n0,
-                                                   uint8_t *out_stage, const AccRelease &rel)
+                                                   uint8_t *out_stage, const AccRelease &rel,
+                                                   const CUtensorMap *omap = nullptr)
 {
     constexpr int NCOLS    = BLOCK_N * kGroups / (kEpiWarps / 4);
     uint8_t      *stage    = out_stage + (warp - kFirstEpi) * kOutStageBytes;
@@ -1420,27 +1533,27 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
     if (tp.mode == kStagePack && !kS32Out)
     {
         drain_accumulator<NCOLS, kS32Out, kStagePack>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                      stage, lane, rel);
+                                                      stage, lane, rel, omap);
     }
     else if (tp.mode == kStagePackS && !kS32Out)
     {
         drain_accumulator<NCOLS, kS32Out, kStagePackS>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                       stage, lane, rel);
+                                                       stage, lane, rel, omap);
     }
     else if (tp.mode == kStageWide && !kS32Out)
     {
         drain_accumulator<NCOLS, kS32Out, kStageWide>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                      stage, lane, rel);
+                                                      stage, lane, rel, omap);
     }
     else if (tp.mode == kStageGeneric)
     {
         drain_accumulator<NCOLS, kS32Out, kStageGeneric>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS,
-                                                         row_term, stage, lane, rel);
+                                                         row_term, stage, lane, rel, omap);
     }
     else
     {
         drain_accumulator<NCOLS, kS32Out, kStageFast>(t_addr, s_col + half * NCOLS, tp, ep, m, n0 + half * NCOLS, row_term,
-                                                      stage, lane, rel);
+                                                      stage, lane, rel, omap);
     }
 }
 
@@ -1448,7 +1561,7 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
 // issuing thread about 550 clocks whatever it covers, more than the 512 clocks four MMAs keep the tensor
 // cores busy, so a stage carries two sub-blocks (eight MMAs) wherever shared memory leaves room for three
 // such stages.
-template <int BLOCK_N, int STAGES, int KSUB, int ACC = 2>
+template <int BLOCK_N, int STAGES, int KSUB, int ACC = 2, bool kPairTma = false>
 struct SmemPlan
 {
     static constexpr int ACC_STAGES = ACC; // accumulator buffers in tensor memory (ACC * BLOCK_N <= 512 columns)
@@ -1464,8 +1577,10 @@ struct SmemPlan
     static constexpr int EPI_GROUPS = (kEpiWarps == 8 && BLOCK_N <= 128) ? 2 : 1; // see epilogue_warp_tile
     static constexpr int OFF_BAR    = OFF_COL + EPI_GROUPS * BLOCK_N * 16; // full[S], empty[S], tfull[ACC], tempty[ACC]
     static constexpr int OFF_MISC   = OFF_BAR + (2 * STAGES + 2 * ACC) * 8; // tmem base, abort flag
-    static constexpr int OFF_OUT    = OFF_MISC + 16;              // per epilogue warp: 32 rows x 128 bytes of output
-    static constexpr int TOTAL      = OFF_OUT + kEpiWarps * kOutStageBytes;
+    // per epilogue warp: 32 rows x kOutRowBytes of output staging, 1024-byte aligned (a swizzled source of TMA stores)
+    static constexpr int OFF_OUT    = ((OFF_MISC + 16 + 1023) / 1024) * 1024;
+    // kPairTma: the paired drain stages two tiles of 32 rows x 64 bytes per warp for its bulk tensor stores
+    static constexpr int TOTAL      = OFF_OUT + kEpiWarps * (kPairTma ? kPairStageBytes : kOutStageBytes);
     static constexpr int DYN_BYTES  = TOTAL + 1024;               // slack to align the base to 1024
     static constexpr int TMEM_COLS  = ACC * BLOCK_N;
 };
@@ -1474,12 +1589,13 @@ struct SmemPlan
 // activation matrix, tp.M the number of output channels and tp.N the number of output rows -- so the
 // accumulator holds the transposed output tile and epilogue_warp_tile_cm writes it (see there).  Tiles are then
 // ordered n-fastest, i.e. all row blocks of one channel block in turn.
-template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kCM, int ACC>
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kCM, int ACC, bool kPairTma = false>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ TileParams tp, const EpilogueParams ep)
+                            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ TileParams tp,
+                            const EpilogueParams ep)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, kPairTma>;
     extern __shared__ uint8_t smem_raw[];
     // the 1024-byte aligned start of the dynamic shared memory, derived by pointer arithmetic on the __shared__ array
     // itself: a pointer rebuilt from an integer loses its address space and every access through it becomes a
@@ -1853,13 +1969,19 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 else if (kCanPair && pair_now)
                 {
+                    // kPairTma: the warp's share of both tiles leaves as two bulk tensor stores from its staging area
+                    const uint32_t pair_stage =
+                        (kPairTma && tp.tma_store != 0)
+                            ? smem_u32(smem + P::OFF_OUT) + static_cast<uint32_t>(warp - kFirstEpi) * kPairStageBytes
+                            : 0u;
                     epilogue_warp_tile_pair<BLOCK_N, kGroups>(tmem_base + as * BLOCK_N, tmem_base + (as + kStride) * BLOCK_N,
-                                                              g_col, tp, ep, warp, lane, m0, m0b, n0, rel);
+                                                              g_col, tp, ep, warp, lane, m0, m0b, n0, rel, pair_stage, &tmap_out);
                 }
                 else
                 {
                     epilogue_warp_tile<BLOCK_N, kS32Out, kGroups>(tmem_base + as * BLOCK_N, g_col, tp, ep, warp, lane,
-                                                                  m0, n0, smem + P::OFF_OUT, rel);
+                                                                  m0, n0, smem + P::OFF_OUT, rel,
+                                                                  (tp.tma_store != 0 && !kPairTma) ? &tmap_out : nullptr);
                 }
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
@@ -1868,6 +1990,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                     skip = ti + kStride;
                 }
             }
+        }
+        if (tp.tma_store != 0 && lane == 0)
+        {
+            tma_store_wait_all(); // this warp's bulk stores: shared memory stays valid until they have read it
         }
     }
 
@@ -2271,8 +2397,8 @@ constexpr int kConvThreads  = kThreads + 32 * kGatherWarps;
 
 template <int BLOCK_N, int STAGES, int KSUB, int ACC>
 __global__ void __launch_bounds__(kConvThreads, 1)
-    gemmlowp_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ TileParams tp,
-                                 const EpilogueParams ep, const ConvGeom cg)
+    gemmlowp_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_out,
+                                 const __grid_constant__ TileParams tp, const EpilogueParams ep, const ConvGeom cg)
 {
     using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
     extern __shared__ uint8_t smem_raw[];
@@ -2481,10 +2607,14 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 if (et == 0) trace_event(tp.trace, ti, 4);
                 const AccRelease rel{tempty_bar(as), 0u, false};
                 epilogue_warp_tile<BLOCK_N, false, kGroups>(tmem_base + as * BLOCK_N, g_col, tp, ep, warp, lane, m0, n0,
-                                                            smem + P::OFF_OUT, rel);
+                                                            smem + P::OFF_OUT, rel, tp.tma_store != 0 ? &tmap_out : nullptr);
                 if (et == 0) trace_event(tp.trace, ti, 5);
                 __syncwarp();
             }
+        }
+        if (tp.tma_store != 0 && lane == 0)
+        {
+            tma_store_wait_all(); // this warp's bulk stores: shared memory stays valid until they have read it
         }
     }
     else
@@ -2689,6 +2819,30 @@ bool encode_operand_map(CUtensorMap *map, const void *base, int rows, int K, int
               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Output through bulk tensor stores from the warps' staging areas (drain_accumulator): the eight- and four-warp builds,
+// one 8-bit destination, 16-byte aligned base and pitch.  Box = 32 rows x kOutRowBytes in the swizzle the staging
+// uses.  *use says whether the launch may use the map; false is returned only when the encoding itself failed.
+bool encode_out_map(const GemmOperands &op, CUtensorMap *map, bool *use, int row_bytes = kOutRowBytes,
+                    bool any_build = false)
+{
+    *use = (kEpiWarps <= 8 || any_build) && op.tma_store >= 0 && op.n_extra_dst == 0 &&
+           ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0;
+    if (!*use)
+    {
+        return true;
+    }
+    EncodeTiledFn    fn         = get_encode_fn();
+    const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(op.N), static_cast<cuuint64_t>(op.M)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(op.ldd)};
+    const cuuint32_t box[2]     = {static_cast<cuuint32_t>(row_bytes), 32};
+    const cuuint32_t estr[2]    = {1, 1};
+    return fn != nullptr &&
+           fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, op.dst, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+              row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B
+                               : (row_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B),
+              CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 using EncodeIm2colFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                                     const cuuint64_t *, const int *, const int *, cuuint32_t, cuuint32_t,
                                     const cuuint32_t *, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -2744,11 +2898,11 @@ bool conv_tma_supported(const GemmOperands &op)
            (cv.kw - 1) * cv.dil_x < 256 && (cv.kh - 1) * cv.dil_y < 256 && get_encode_im2col_fn() != nullptr;
 }
 
-template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out>
+template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kPairTma = false>
 cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep)
 {
     constexpr int ACC = BLOCK_N <= 128 ? 4 : 2; // narrow tiles: four accumulator buffers in the 512 columns
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, kPairTma>;
     static_assert(P::DYN_BYTES <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     CUtensorMap map_a, map_b;
     if (!(op.conv != nullptr ? encode_im2col_map(&map_a, *op.conv)
@@ -2757,7 +2911,13 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncode failed for a GEMM operand");
     }
-    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false, ACC>;
+    CUtensorMap map_out   = map_a; // placeholder when unused
+    bool        tma_store = false;
+    if (!kS32Out && !(kPairTma ? encode_out_map(op, &map_out, &tma_store, 64, true) : encode_out_map(op, &map_out, &tma_store)))
+    {
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the output tiles");
+    }
+    auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false, ACC, kPairTma>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
     {
@@ -2775,6 +2935,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.tma_store = 0;
     fill_conv_params(tp, op);
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
@@ -2786,7 +2947,8 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     tp.split_tail = 0;
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, tp, ep);
+    tp.tma_store = tma_store ? 1 : 0;
+    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, map_out, tp, ep);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel");
 }
 
@@ -2820,6 +2982,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok  = ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op)) & 7) == 0;
     tp.status  = ctx->d_status;
+    tp.tma_store = 0;
     tp.conv_c  = 0;
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
@@ -2831,7 +2994,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
     tp.split_tail = 0;
     const int tiles = ((op.N + BLOCK_M - 1) / BLOCK_M) * ((op.M + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_w, map_x, tp, ep);
+    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_w, map_x, map_w, tp, ep); // (no bulk stores on this path)
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel (channel-major)");
 }
 
@@ -2869,6 +3032,7 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     tp.split_tail = op.split_tail >= 0 ? 1 : 0;
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.tma_store = 0;
     fill_conv_params(tp, op);
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
@@ -2909,6 +3073,12 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the weights operand");
     }
+    CUtensorMap map_out   = map_b; // placeholder when unused
+    bool        tma_store = false;
+    if (!encode_out_map(op, &map_out, &tma_store))
+    {
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the output tiles");
+    }
     auto        kernel = gemmlowp_conv_tcgen05_kernel<BLOCK_N, STAGES, KSUB, ACC>;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63])
@@ -2927,6 +3097,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
                (static_cast<uint32_t>(BLOCK_N >> 3) << 17) | (static_cast<uint32_t>(BLOCK_M >> 4) << 24);
     tp.vec_ok = vector_flags(reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd) | extra_dst_bits(op));
     tp.status  = ctx->d_status;
+    tp.tma_store = 0;
     tp.conv_c  = 0;
     tp.spin_limit  = ctx->spin_limit;
     tp.withhold_kb = ctx->withhold_kb;
@@ -2956,7 +3127,8 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     cg.div_ho = make_fastdiv(cv.Ho);
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kernel<<<grid, kConvThreads, kDynBytes, ctx->stream>>>(map_b, tp, ep, cg);
+    tp.tma_store = tma_store ? 1 : 0;
+    kernel<<<grid, kConvThreads, kDynBytes, ctx->stream>>>(map_b, map_out, tp, ep, cg);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_conv_tcgen05_kernel");
 }
 #endif // CUGL_TC_FULL_BUILD
@@ -3008,6 +3180,15 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
     (void)allow_pair;
 #endif
     const int block_n = op.block_n > 0 ? op.block_n : (op.N > 128 ? 256 : (op.N > 64 ? 128 : 64));
+#if !CUGL_TC_FULL_BUILD
+    // sixteen epilogue warps with a paired drain: a ring of three stages leaves room for the staging areas of its
+    // bulk tensor stores
+    if (!s32 && wants_pair_drain(op) && op.tma_store >= 0 && op.n_extra_dst == 0 &&
+        ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0)
+    {
+        return launch_variant<256, 3, 1, false, true>(ctx, op, ep);
+    }
+#endif
     if (block_n > 128 || !CUGL_TC_FULL_BUILD)
     {
         return s32 ? launch_variant<256, 4, 1, true>(ctx, op, ep) : launch_variant<256, 4, 1, false>(ctx, op, ep);

@@ -68,6 +68,9 @@ struct GemmOperands
     // tensor conv->src by im2col-mode TMA loads (a is ignored; M = B*Ho*Wo, K = kh*kw*C, C a multiple of 128, input
     // zero point 0)
     const ConvOperands *conv;
+    // one-CTA row-major kernels, eight- and four-warp builds: < 0 keeps the epilogue on per-lane global stores; otherwise
+    // a warp's 32 rows leave as one bulk tensor store from shared memory where the destination allows it
+    int tma_store;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).

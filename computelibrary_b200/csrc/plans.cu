@@ -62,6 +62,7 @@ struct GemmCore
     int           split_tail    = 0;     // < 0: the SM-pair kernel keeps the tiles of a short last wave whole
     int           block_n       = 0;     // 64 / 128 / 256 force that tile width of the one-CTA kernels, 0 = automatic
     int           pair_drain    = 0;     // < 0: every accumulator buffer is drained on its own
+    int           tma_store     = 0;     // < 0: no bulk tensor stores in the epilogue
 
     // bytes of the row-sum vector as a share of a temporary workspace (none without a B offset)
     size_t rowsum_bytes() const
@@ -237,6 +238,7 @@ struct GemmCore
         op.split_tail    = split_tail;
         op.block_n       = block_n;
         op.pair_drain    = pair_drain;
+        op.tma_store     = tma_store;
         op.n_extra_dst   = n_extra;
         op.residual      = d_residual;
         op.res_floor     = res_floor;
@@ -770,6 +772,16 @@ extern "C"
         return CUGL_SUCCESS;
     }
 
+    cugl_status cugl_gemmlowp_plan_set_tma_store(cugl_gemm_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_gemmlowp_plan_set_tma_store: NULL plan");
+        }
+        plan->core.tma_store = on != 0 ? 0 : -1;
+        return CUGL_SUCCESS;
+    }
+
     cugl_status cugl_gemmlowp_plan_force_simt(cugl_gemm_plan *plan, int on)
     {
         if (plan == nullptr)
@@ -1296,6 +1308,7 @@ extern "C"
             op.channel_major = c.channel_major;
             op.block_n       = c.block_n;
             op.pair_drain    = c.pair_drain;
+            op.tma_store     = c.tma_store;
             op.n_extra_dst   = 0;
             op.residual      = d_residual;
             op.res_floor     = plan->res_floor;
@@ -1455,6 +1468,16 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_paired_drain: NULL plan");
         }
         plan->core.pair_drain = on != 0 ? 0 : -1;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_tma_store(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_tma_store: NULL plan");
+        }
+        plan->core.tma_store = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
     }
 

@@ -262,6 +262,10 @@ CUGL_API cugl_status cugl_gemmlowp_plan_set_tile_columns(cugl_gemm_plan *plan, i
  * output-stage term is read from shared memory once for two elements (on by default).  on = 0 drains every
  * tile on its own.  Testing / measurement aid: the results are identical. */
 CUGL_API cugl_status cugl_gemmlowp_plan_set_paired_drain(cugl_gemm_plan *plan, int on);
+/* The one-CTA kernels with four or eight epilogue warps send a warp's 32 output rows off as one bulk tensor store from
+ * shared memory where the destination allows it (8-bit output, one destination, 16-byte aligned base and pitch);
+ * on = 0 keeps them on per-lane global stores (testing aid: results do not depend on it). */
+CUGL_API cugl_status cugl_gemmlowp_plan_set_tma_store(cugl_gemm_plan *plan, int on);
 
 /* Output stages whose clamp bounds are the whole range of the 8-bit output type (every shift in [2, 31], or [2, 22]
  * with a non-zero output offset; non-negative multipliers; no B offset) fold the offset into the per-column constant
@@ -417,6 +421,8 @@ CUGL_API cugl_status cugl_conv2d_plan_set_channel_major(cugl_conv_plan *plan, in
 CUGL_API cugl_status cugl_conv2d_plan_set_tile_columns(cugl_conv_plan *plan, int columns);
 /* as cugl_gemmlowp_plan_set_paired_drain, for the lowerings that run the plain GEMM kernel */
 CUGL_API cugl_status cugl_conv2d_plan_set_paired_drain(cugl_conv_plan *plan, int on);
+/* as cugl_gemmlowp_plan_set_tma_store */
+CUGL_API cugl_status cugl_conv2d_plan_set_tma_store(cugl_conv_plan *plan, int on);
 /* NEGEMMConvolutionLayer::update_quantization_parameters (src/runtime/NEON/functions/NEGEMMConvolutionLayer.cpp:129-131,
  * src/cpu/operators/CpuGemmConv2d.cpp:858-908): re-reads the zero points, the multipliers / shifts, the output zero
  * point and the clamp bounds of desc; geometry and types must be unchanged.  The prepared weights stay valid. */
