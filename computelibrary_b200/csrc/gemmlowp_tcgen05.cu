@@ -1001,6 +1001,13 @@ struct PairDrain
     uint32_t           stage;
     const CUtensorMap *omap;
     int                n_first, row_a, row_b;
+    // A fused residual arrives the same way: before the warp's first tensor-memory load one lane requests the two
+    // residual boxes into the stage (bulk tensor loads completing on the warp's own barrier res_bar, phase res_parity);
+    // every lane adds its pieces in place before the boxes go out again.  rmap == nullptr: no residual this way.
+    const CUtensorMap *rmap;
+    uint32_t           res_bar, res_parity;
+    volatile int      *abort_flag;
+    long long          spin_limit;
 };
 constexpr int kPairStageBytes = 2 * 32 * 64; // per warp
 
@@ -1049,12 +1056,30 @@ __device__ __forceinline__ void finish_chunk_pair(const PairDrain &d, int ch, ui
     if (d.stage != 0)
     {
         // 64-byte rows, 16-byte piece p of row r at piece p ^ ((r >> 1) & 3): the tensor map's 64-byte swizzle
-        if (ch == 0)
+        if (ch == 0 && d.rmap == nullptr)
         {
-            stage_reuse_wait(d.lane); // the previous pair's stores have read the stage
+            stage_reuse_wait(d.lane); // the previous pair's stores have read the stage (with a residual: see drain_pair_x16)
         }
         const uint32_t row = d.stage + d.lane * 64, sw = (d.lane >> 1) & 3;
         const uint32_t p0 = ((2u * ch) ^ sw) << 4, p1 = ((2u * ch + 1u) ^ sw) << 4;
+        if (d.rmap != nullptr)
+        {
+            if (ch == 0)
+            {
+                (void)mbar_wait(d.res_bar, d.res_parity, d.abort_flag, DEV_TIMEOUT_EPILOGUE, d.spin_limit); // gives up: flag set
+            }
+            uint32_t ra[8], rb[8];
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(ra[0]), "=r"(ra[1]), "=r"(ra[2]), "=r"(ra[3]) : "r"(row + p0) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(ra[4]), "=r"(ra[5]), "=r"(ra[6]), "=r"(ra[7]) : "r"(row + p1) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(rb[0]), "=r"(rb[1]), "=r"(rb[2]), "=r"(rb[3]) : "r"(row + 2048 + p0) : "memory");
+            asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(rb[4]), "=r"(rb[5]), "=r"(rb[6]), "=r"(rb[7]) : "r"(row + 2048 + p1) : "memory");
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+            {
+                wa[j] = add_clamp_u8x4(wa[j], ra[j], d.res_floor4, d.res_cap4);
+                wb[j] = add_clamp_u8x4(wb[j], rb[j], d.res_floor4, d.res_cap4);
+            }
+        }
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + p0), "r"(wa[0]), "r"(wa[1]), "r"(wa[2]), "r"(wa[3]) : "memory");
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + p1), "r"(wa[4]), "r"(wa[5]), "r"(wa[6]), "r"(wa[7]) : "memory");
         asm volatile("st.shared.v4.u32 [%0], {%1, %2, %3, %4};" ::"r"(row + 2048 + p0), "r"(wb[0]), "r"(wb[1]), "r"(wb[2]), "r"(wb[3]) : "memory");
@@ -1123,6 +1148,16 @@ __device__ __forceinline__ void drain_pair_chunk_x16(const PairDrain &d, int ch,
 template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_pair_x16(const PairDrain d)
 {
+    if (d.stage != 0 && d.rmap != nullptr)
+    {
+        stage_reuse_wait(d.lane); // the previous pair's stores have read the stage
+        if (d.lane == 0)
+        {
+            mbar_expect_tx(d.res_bar, kPairStageBytes);
+            tma_load_2d(d.stage, d.rmap, d.n_first, d.row_a, d.res_bar);
+            tma_load_2d(d.stage + 2048, d.rmap, d.n_first, d.row_b, d.res_bar);
+        }
+    }
 #pragma unroll 1
     for (int ch = 0; ch < NCOLS / 32; ++ch)
     {
@@ -1143,15 +1178,19 @@ template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_accumulator_pair(uint32_t t_a, uint32_t t_b, const int4 *s_col,
                                                        const TileParams &tp, const EpilogueParams &ep, int ma, int mb,
                                                        int n_first, int lane, const AccRelease &rel, uint32_t stage = 0,
-                                                       const CUtensorMap *omap = nullptr)
+                                                       const CUtensorMap *omap = nullptr, const CUtensorMap *rmap = nullptr,
+                                                       uint32_t res_bar = 0, uint32_t res_parity = 0,
+                                                       volatile int *abort_flag = nullptr)
 {
     PairDrain d;
     d.stage = NCOLS == 64 ? stage : 0u, d.omap = omap, d.n_first = n_first, d.row_a = ma - lane, d.row_b = mb - lane;
+    d.rmap  = (d.stage != 0 && tp.residual != nullptr) ? rmap : nullptr;
+    d.res_bar = res_bar, d.res_parity = res_parity, d.abort_flag = abort_flag, d.spin_limit = tp.spin_limit;
     d.t_a = t_a, d.t_b = t_b, d.col = s_col;
     d.dst_a      = ma < tp.M ? tp.dst + static_cast<int64_t>(ma) * tp.ldd + n_first : nullptr;
     d.dst_b      = mb < tp.M ? tp.dst + static_cast<int64_t>(mb) * tp.ldd + n_first : nullptr;
-    d.res_a      = (tp.residual != nullptr && ma < tp.M) ? tp.residual + static_cast<int64_t>(ma) * tp.ldd + n_first : nullptr;
-    d.res_b      = (tp.residual != nullptr && mb < tp.M) ? tp.residual + static_cast<int64_t>(mb) * tp.ldd + n_first : nullptr;
+    d.res_a      = (tp.residual != nullptr && d.rmap == nullptr && ma < tp.M) ? tp.residual + static_cast<int64_t>(ma) * tp.ldd + n_first : nullptr;
+    d.res_b      = (tp.residual != nullptr && d.rmap == nullptr && mb < tp.M) ? tp.residual + static_cast<int64_t>(mb) * tp.ldd + n_first : nullptr;
     d.cols       = tp.N - n_first;
     d.vec_ok     = tp.vec_ok;
     d.res_floor4 = tp.res_floor4, d.res_cap4 = tp.res_cap4;
@@ -1167,7 +1206,9 @@ template <int BLOCK_N, int kGroups>
 __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_t tmem_b, const int4 *s_col,
                                                         const TileParams &tp, const EpilogueParams &ep, int warp,
                                                         int lane, int m0a, int m0b, int n0, const AccRelease &rel,
-                                                        uint32_t stage = 0, const CUtensorMap *omap = nullptr)
+                                                        uint32_t stage = 0, const CUtensorMap *omap = nullptr,
+                                                        const CUtensorMap *rmap = nullptr, uint32_t res_bar = 0,
+                                                        uint32_t res_parity = 0, volatile int *abort_flag = nullptr)
 {
     constexpr int  NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
     const int      quad  = warp & 3;                                      // tensor-memory lane quarter this warp may read
@@ -1177,19 +1218,19 @@ __device__ __forceinline__ void epilogue_warp_tile_pair(uint32_t tmem_a, uint32_
     {
         drain_accumulator_pair<NCOLS, kStagePack>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                  n0 + half * NCOLS, lane, rel, stage, omap);
+                                                  n0 + half * NCOLS, lane, rel, stage, omap, rmap, res_bar, res_parity, abort_flag);
     }
     else if (tp.mode == kStagePackS)
     {
         drain_accumulator_pair<NCOLS, kStagePackS>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                    s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                   n0 + half * NCOLS, lane, rel, stage, omap);
+                                                   n0 + half * NCOLS, lane, rel, stage, omap, rmap, res_bar, res_parity, abort_flag);
     }
     else
     {
         drain_accumulator_pair<NCOLS, kStageWide>(tmem_a + lanes + half * NCOLS, tmem_b + lanes + half * NCOLS,
                                                   s_col + half * NCOLS, tp, ep, m0a + quad * 32 + lane, m0b + quad * 32 + lane,
-                                                  n0 + half * NCOLS, lane, rel, stage, omap);
+                                                  n0 + half * NCOLS, lane, rel, stage, omap, rmap, res_bar, res_parity, abort_flag);
     }
 }
 
@@ -1578,7 +1619,8 @@ struct SmemPlan
     static constexpr int OFF_BAR    = OFF_COL + EPI_GROUPS * BLOCK_N * 16; // full[S], empty[S], tfull[ACC], tempty[ACC]
     static constexpr int OFF_MISC   = OFF_BAR + (2 * STAGES + 2 * ACC) * 8; // tmem base, abort flag
     // per epilogue warp: 32 rows x kOutRowBytes of output staging, 1024-byte aligned (a swizzled source of TMA stores)
-    static constexpr int OFF_OUT    = ((OFF_MISC + 16 + 1023) / 1024) * 1024;
+    static constexpr int OFF_RESBAR = OFF_MISC + 16;              // kPairTma: one barrier per epilogue warp (residual boxes)
+    static constexpr int OFF_OUT    = ((OFF_RESBAR + 8 * kEpiWarps + 1023) / 1024) * 1024;
     // kPairTma: the paired drain stages two tiles of 32 rows x 64 bytes per warp for its bulk tensor stores
     static constexpr int TOTAL      = OFF_OUT + kEpiWarps * (kPairTma ? kPairStageBytes : kOutStageBytes);
     static constexpr int DYN_BYTES  = TOTAL + 1024;               // slack to align the base to 1024
@@ -1592,8 +1634,8 @@ struct SmemPlan
 template <int BLOCK_N, int STAGES, int KSUB, bool kS32Out, bool kCM, int ACC, bool kPairTma = false>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ TileParams tp,
-                            const EpilogueParams ep)
+                            const __grid_constant__ CUtensorMap tmap_out, const __grid_constant__ CUtensorMap tmap_res,
+                            const __grid_constant__ TileParams tp, const EpilogueParams ep)
 {
     using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, kPairTma>;
     extern __shared__ uint8_t smem_raw[];
@@ -1632,6 +1674,13 @@ __global__ void __launch_bounds__(kThreads, 1)
         {
             mbar_init(tfull_bar(a), 1);
             mbar_init(tempty_bar(a), kEpiWarps / (kCM ? 1 : P::EPI_GROUPS)); // the warps of the group that drains it
+        }
+        if (kPairTma)
+        {
+            for (int w = 0; w < kEpiWarps; ++w)
+            {
+                mbar_init(smem_u32(smem + P::OFF_RESBAR) + 8u * w, 1); // the warp's residual boxes have landed
+            }
         }
         *s_abort = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -1903,6 +1952,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         // the MMA warp fills the other pair, the same layers measured slower (802816 x 256 x 64: 164 against 133 us).
         constexpr bool kCanPair = !kCM && !kS32Out && kGroups == 1 && ACC == 2;
         int            skip     = -1; // ordinal of a tile already drained as the partner of an earlier one
+        uint32_t       n_res_pairs = 0; // kPairTma: pairs whose residual this warp has fetched (phase of its barrier)
         for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++ti)
         {
             if ((kGroups > 1 && (ti & 1) != group) || ti == skip)
@@ -1974,8 +2024,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                         (kPairTma && tp.tma_store != 0)
                             ? smem_u32(smem + P::OFF_OUT) + static_cast<uint32_t>(warp - kFirstEpi) * kPairStageBytes
                             : 0u;
+                    const bool     res_tma = pair_stage != 0 && tp.residual != nullptr; // residual boxes through the TMA unit
+                    const uint32_t res_bar = smem_u32(smem + P::OFF_RESBAR) + 8u * static_cast<uint32_t>(warp - kFirstEpi);
                     epilogue_warp_tile_pair<BLOCK_N, kGroups>(tmem_base + as * BLOCK_N, tmem_base + (as + kStride) * BLOCK_N,
-                                                              g_col, tp, ep, warp, lane, m0, m0b, n0, rel, pair_stage, &tmap_out);
+                                                              g_col, tp, ep, warp, lane, m0, m0b, n0, rel, pair_stage, &tmap_out,
+                                                              &tmap_res, res_bar, n_res_pairs & 1u, s_abort);
+                    if (res_tma)
+                    {
+                        if (*s_abort != 0) // a wait was given up: let this warp's residual boxes land before anything else
+                        {
+                            const long long t0 = clock64();
+                            while (!mbar_try_wait(res_bar, n_res_pairs & 1u) && clock64() - t0 < tp.spin_limit)
+                            {
+                            }
+                        }
+                        ++n_res_pairs;
+                    }
                 }
                 else
                 {
@@ -2917,6 +2981,17 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the output tiles");
     }
+    CUtensorMap map_res = map_out; // the same geometry over the residual matrix (paired drain through the TMA unit)
+    if (kPairTma && tma_store && op.residual != nullptr)
+    {
+        GemmOperands r = op;
+        r.dst          = const_cast<void *>(op.residual);
+        bool use       = false;
+        if ((reinterpret_cast<uintptr_t>(op.residual) & 15) != 0 || !encode_out_map(r, &map_res, &use, 64, true) || !use)
+        {
+            return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the residual tiles");
+        }
+    }
     auto kernel = gemmlowp_tcgen05_kernel<BLOCK_N, STAGES, KSUB, kS32Out, false, ACC, kPairTma>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
@@ -2948,7 +3023,7 @@ cugl_status launch_variant(cugl_context *ctx, const GemmOperands &op, const Epil
     const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     tp.tma_store = tma_store ? 1 : 0;
-    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, map_out, tp, ep);
+    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_a, map_b, map_out, map_res, tp, ep);
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel");
 }
 
@@ -2994,7 +3069,7 @@ cugl_status launch_variant_cm(cugl_context *ctx, const GemmOperands &op, const E
     tp.split_tail = 0;
     const int tiles = ((op.N + BLOCK_M - 1) / BLOCK_M) * ((op.M + BLOCK_N - 1) / BLOCK_N);
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
-    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_w, map_x, map_w, tp, ep); // (no bulk stores on this path)
+    kernel<<<grid, kThreads, P::DYN_BYTES, ctx->stream>>>(map_w, map_x, map_w, map_w, tp, ep); // (no bulk stores on this path)
     return check_cuda(ctx, cudaGetLastError(), "gemmlowp_tcgen05_kernel (channel-major)");
 }
 
@@ -3184,7 +3259,7 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
     // sixteen epilogue warps with a paired drain: a ring of three stages leaves room for the staging areas of its
     // bulk tensor stores
     if (!s32 && wants_pair_drain(op) && op.tma_store >= 0 && op.n_extra_dst == 0 &&
-        ((reinterpret_cast<uintptr_t>(op.dst) | static_cast<uint64_t>(op.ldd)) & 15) == 0)
+        ((reinterpret_cast<uintptr_t>(op.dst) | reinterpret_cast<uintptr_t>(op.residual) | static_cast<uint64_t>(op.ldd)) & 15) == 0)
     {
         return launch_variant<256, 3, 1, false, true>(ctx, op, ep);
     }
