@@ -1892,21 +1892,40 @@ __global__ void __launch_bounds__(kThreads, 1)
                     // stage offset in 16-byte units; advancing K by 32 bytes inside the swizzle row: +2
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
-#pragma unroll
-                    for (int sub = 0; sub < KSUB; ++sub)
+                    // A stage wholly inside K and 128-byte-swizzle operands (the common case): the MMAs back to back with
+                    // nothing to test on the issuing thread's critical path.  Else the K steps beyond K are left out (zero
+                    // fill, or with im2col-mode loads not loaded at all) and 64-byte-swizzle A tiles are addressed tap by tap.
+                    if ((kb + 1) * KSUB * BLOCK_K <= tp.K && !a_sw64)
                     {
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        for (int sub = 0; sub < KSUB; ++sub)
                         {
-                            // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
-                            if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                             {
-                                // 32 bytes on inside the swizzled row: + 2; 64-byte rows: the next tap's tile after two steps
-                                const uint32_t a_k = a_sw64 ? static_cast<uint32_t>((k >> 1) * ((A_STAGE / 2) >> 4) + 2 * (k & 1))
-                                                            : 2u * k;
-                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + a_k,
+                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
                                         (kb | sub | k) != 0 ? 1u : 0u);
+                            }
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int sub = 0; sub < KSUB; ++sub)
+                        {
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                            {
+                                if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+                                {
+                                    // 32 bytes on inside the swizzled row: + 2; 64-byte rows: the next tap's tile after two steps
+                                    const uint32_t a_k = a_sw64 ? static_cast<uint32_t>((k >> 1) * ((A_STAGE / 2) >> 4) + 2 * (k & 1))
+                                                                : 2u * k;
+                                    umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + a_k,
+                                            b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                            (kb | sub | k) != 0 ? 1u : 0u);
+                                }
                             }
                         }
                     }
@@ -2099,7 +2118,7 @@ struct SmemPlan2
     static constexpr int OFF_COL   = STAGES * STAGE;
     static constexpr int OFF_BAR   = OFF_COL + BLOCK_N * 16;
     static constexpr int OFF_MISC  = OFF_BAR + (2 * STAGES + 4) * 8;
-    static constexpr int OFF_OUT   = OFF_MISC + 16;
+    static constexpr int OFF_OUT   = ((OFF_MISC + 16 + 1023) / 1024) * 1024; // staging: a swizzled source of TMA stores
     static constexpr int TOTAL     = OFF_OUT + kEpiWarps * kOutStageBytes;
     static constexpr int DYN_BYTES = TOTAL + 1024;
     static constexpr int TMEM_COLS = 2 * BLOCK_N;
@@ -2109,8 +2128,8 @@ template <int STAGES, int KSUB, bool kS32Out>
 __global__ void __launch_bounds__(kThreads, 1)
     gemmlowp_tcgen05_2cta_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                  const __grid_constant__ CUtensorMap tmap_b,
-                                 const __grid_constant__ CUtensorMap tmap_bh, const __grid_constant__ TileParams tp,
-                                 const EpilogueParams ep)
+                                 const __grid_constant__ CUtensorMap tmap_bh, const __grid_constant__ CUtensorMap tmap_out,
+                                 const __grid_constant__ TileParams tp, const EpilogueParams ep)
 {
     using P               = SmemPlan2<STAGES, KSUB>;
     constexpr int BLOCK_N = P::BLOCK_N;
@@ -2324,17 +2343,37 @@ __global__ void __launch_bounds__(kThreads, 1)
                     if (kb == 0) trace_event(tp.trace, ti, 2);
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
-#pragma unroll
-                    for (int sub = 0; sub < KSUB; ++sub)
+                    // a stage that lies wholly inside K (all but the last one): the MMAs back to back, nothing to test on the
+                    // issuing thread's critical path; the last stage leaves out the K steps beyond K (zero fill, or with
+                    // im2col-mode loads not loaded at all)
+                    if ((kb + 1) * KSUB * BLOCK_K <= tp.K)
                     {
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        for (int sub = 0; sub < KSUB; ++sub)
                         {
-                            if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K) // beyond K: zero fill, or not loaded at all
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                             {
                                 umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
                                              b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, idesc,
                                              (kb | sub | k) != 0 ? 1u : 0u);
+                            }
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int sub = 0; sub < KSUB; ++sub)
+                        {
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                            {
+                                if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+                                {
+                                    umma_i8_pair(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                                 b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, idesc,
+                                                 (kb | sub | k) != 0 ? 1u : 0u);
+                                }
                             }
                         }
                     }
@@ -2390,12 +2429,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (half < 0)
                 {
                     epilogue_warp_tile<BLOCK_N, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                         smem + P::OFF_OUT, rel);
+                                                         smem + P::OFF_OUT, rel, tp.tma_store != 0 ? &tmap_out : nullptr);
                 }
                 else
                 {
                     epilogue_warp_tile<BLOCK_N / 2, kS32Out>(tmem_base + as * BLOCK_N, s_col, tp, ep, warp, lane, m0, n0,
-                                                             smem + P::OFF_OUT, rel);
+                                                             smem + P::OFF_OUT, rel, tp.tma_store != 0 ? &tmap_out : nullptr);
                 }
                 __syncwarp();
                 if (et == 0) trace_event(tp.trace, ti, 5);
@@ -2405,6 +2444,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                 as = 0;
                 aph ^= 1;
             }
+        }
+        if (tp.tma_store != 0 && lane == 0)
+        {
+            tma_store_wait_all(); // this warp's bulk stores: shared memory stays valid until they have read it
         }
     }
 
@@ -3087,6 +3130,12 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for a GEMM operand");
     }
+    CUtensorMap map_out   = map_a; // placeholder when unused
+    bool        tma_store = false;
+    if (!kS32Out && !encode_out_map(op, &map_out, &tma_store))
+    {
+        return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the output tiles");
+    }
     auto kernel = gemmlowp_tcgen05_2cta_kernel<STAGES, KSUB, kS32Out>;
     static bool attr_set[64] = {}; // per instantiation and device
     if (!attr_set[ctx->device & 63])
@@ -3131,7 +3180,8 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     attr[0].val.clusterDim.z = 1;
     cfg.attrs                = attr;
     cfg.numAttrs             = 1;
-    CUGL_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_bh, tp, ep));
+    tp.tma_store = tma_store ? 1 : 0;
+    CUGL_CUDA_TRY(ctx, cudaLaunchKernelEx(&cfg, kernel, map_a, map_b, map_bh, map_out, tp, ep));
     return CUGL_SUCCESS;
 }
 
