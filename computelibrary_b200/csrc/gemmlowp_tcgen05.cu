@@ -841,7 +841,11 @@ __device__ __forceinline__ void drain_accumulator(uint32_t t_addr, const int4 *s
         {
             const int first = c & ~(kOutChunks - 1); // first chunk of this staged group
             const int ncols = (c + 1 - first) * 32;
-            if (tma && ncols == kOutRowBytes)
+            // A bulk tensor store clips at the tensor's edge in whole 16-byte units (measured: a 64-byte box over the
+            // ragged end of a 200-byte row wrote bytes 200..207 too), so a group that crosses N leaves through the
+            // lanes unless N itself ends on such a unit.
+            const int n_group = n_first + first * 32;
+            if (tma && ncols == kOutRowBytes && (n_group + kOutRowBytes <= tp.N || (tp.N & 15) == 0))
             {
                 flush_stage_tma(stage, omap, m - lane, n_first + first * 32, lane);
             }
@@ -3308,7 +3312,7 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_tcgen05)(cugl_context *ctx, const GemmO
 #if !CUGL_TC_FULL_BUILD
     // sixteen epilogue warps with a paired drain: a ring of three stages leaves room for the staging areas of its
     // bulk tensor stores
-    if (!s32 && wants_pair_drain(op) && op.tma_store >= 0 && op.n_extra_dst == 0 &&
+    if (!s32 && wants_pair_drain(op) && op.tma_store >= 0 && op.n_extra_dst == 0 && (op.N & 15) == 0 &&
         ((reinterpret_cast<uintptr_t>(op.dst) | reinterpret_cast<uintptr_t>(op.residual) | static_cast<uint64_t>(op.ldd)) & 15) == 0)
     {
         return launch_variant<256, 3, 1, false, true>(ctx, op, ep);

@@ -23,7 +23,7 @@ def f32_mults(port, i_scale, w_scales, o_scale):
 def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out_dtype, force_simt=False,
                  b_constant=True, runs=1, ldd_pad=0, pair=True, epi_warps=0, channel_major=0, integer_stage=False,
                  tile_columns=0, paired_drain=True, accumulate=False, dequantize_scale=0.0, dst_init=None,
-                 temp_workspace=False, saturating_pack=True):
+                 temp_workspace=False, saturating_pack=True, tma_store=True):
     """Fused NEGEMMLowpMatrixMultiplyCore through the C ABI.  mult/shift scalars -> per-tensor; arrays ->
     per-channel.  out_dtype np.int32 -> output stage NONE.  Returns (numpy result, kernel name)."""
     import torch
@@ -67,6 +67,8 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
             plan.set_paired_drain(False)
         if not saturating_pack:
             plan.set_saturating_pack(False)
+        if not tma_store:
+            plan.set_tma_store(False)
         da = torch.from_numpy(a.view(np.uint8)).cuda()
         db = torch.from_numpy(b.view(np.uint8)).cuda()
         dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.int32)).cuda() if bias is not None else None
@@ -82,7 +84,8 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
         ctx.sync()
         raw = dd.cpu().numpy().reshape(batch, M, ldd)
         if ldd_pad:
-            assert (raw[:, :, N * dsz:] == canary).all(), "kernel wrote into the row padding"
+            bad = np.argwhere(raw[:, :, N * dsz:] != canary)
+            assert bad.size == 0, f"kernel wrote into the row padding: {len(bad)} bytes, first (batch, row, byte) {bad[:4].tolist()}, bytes past the row {np.unique(bad[:, 2]).tolist()[:32]}"
         out = np.ascontiguousarray(raw[:, :, :N * dsz]).view(out_dtype).reshape(batch, M, N)
         kernel = plan.kernel
         if ws is not None:

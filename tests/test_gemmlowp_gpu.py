@@ -485,3 +485,27 @@ def test_saturating_pack_encoding(ctx, port, out_dtype, offset, M, N, K, epi):
         got, _ = gpu_gemmlowp(ctx, a, b, bias, 3, 0, mult, shift, offset, lo, hi, out_dtype, **kw)
         ref, _ = gpu_gemmlowp(ctx, a, b, bias, 3, 0, mult, shift, offset, lo, hi, out_dtype, saturating_pack=False, **kw)
         assert np.array_equal(got, want) and np.array_equal(ref, want), max_shift
+
+
+@pytest.mark.parametrize("shape", [(300, 200, 64), (300, 208, 64), (700, 520, 64), (1000, 96, 256), (2049, 333, 1536), (40000, 256, 64),
+                                   (20000, 64, 128)])
+def test_bulk_tensor_stores_against_per_lane_stores(ctx, port, shape):
+    """The epilogue's two ways of writing the output -- a warp's rows as one bulk tensor store from shared memory, or
+    one store per lane -- on ragged M and N, narrow and wide tiles, short and long K: both against the oracle (a row
+    sample for the large cases) and against each other, with a canary pitch that makes the destination rows 16-byte
+    aligned (bulk stores possible) or not (the plan must fall back to per-lane stores by itself)."""
+    M, N, K = shape
+    r = np.random.default_rng(M + N + K)
+    a, b = q8_uniform(r, (M, K), np.uint8), q8_uniform(r, (K, N), np.int8, -127, 127)
+    bias = r.integers(-4000, 4000, N).astype(np.int32)
+    ws = np.exp(r.uniform(np.log(1e-3), np.log(1e-2), N)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.05, ws, 0.05 * max(1, K // 64))
+    rows = np.unique(np.concatenate([np.arange(0, min(M, 300)), np.arange(max(0, M - 300), M)]))
+    want = port.gemmlowp_fused(a[rows], b, bias, -3, 0, mult, shift, 5, 0, 255, np.uint8)
+    outs = []
+    for tma, pad in ((True, 0), (False, 0), (True, 16 - N % 16 if N % 16 else 16), (True, 3)):
+        out, _ = gpu_gemmlowp(ctx, a, b, bias, -3, 0, mult, shift, 5, 0, 255, np.uint8, ldd_pad=pad, tma_store=tma)
+        assert np.array_equal(out[rows], want), (tma, pad)
+        outs.append(out)
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
