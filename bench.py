@@ -896,8 +896,18 @@ def run_bandwidth(args):
     ctx.close()
 
 
+def json_only_stdout():
+    """Keeps stdout for the JSON line alone: file descriptor 1 is pointed at stderr, where native libraries that print
+    there end up (NCCL's version banner on several GPUs), and Python's sys.stdout keeps the original descriptor."""
+    sys.stdout.flush()
+    keep = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(keep, "w")
+
+
 def main():
     args = parse_args()
+    json_only_stdout()
     _, world, _ = dist_env()
     if args.impl == "reference":
         run_reference(args)
