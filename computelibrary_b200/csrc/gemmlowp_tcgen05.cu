@@ -91,6 +91,21 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
                  : "memory");
     return ok != 0;
 }
+// The barrier's state without waiting: try_wait may suspend the thread for a hardware-chosen time when the phase is not
+// complete, which a look-ahead that has other work to issue must not do.
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity)
+{
+    uint32_t ok;
+    asm volatile("{\n\t"
+                 ".reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t"
+                 "}"
+                 : "=r"(ok)
+                 : "r"(bar), "r"(parity)
+                 : "memory");
+    return ok != 0;
+}
 // Bounded wait.  Returns false when the limit ran out or another role already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int *abort_flag, int code, long long limit)
 {
@@ -1890,7 +1905,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         sn = 0;
                         phn ^= 1;
                     }
-                    have = mbar_try_wait(full_bar(sn), phn);
+                    have = mbar_test_wait(full_bar(sn), phn);
                     tc_fence_after();
                     if (kb == 0) trace_event(tp.trace, ti, 2);
                     // stage offset in 16-byte units; advancing K by 32 bytes inside the swizzle row: +2
@@ -2342,7 +2357,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         sn = 0;
                         phn ^= 1;
                     }
-                    have = mbar_try_wait(full_bar(sn), phn);
+                    have = mbar_test_wait(full_bar(sn), phn);
                     tc_fence_after();
                     if (kb == 0) trace_event(tp.trace, ti, 2);
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
@@ -2641,7 +2656,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                         sn = 0;
                         phn ^= 1;
                     }
-                    have = mbar_try_wait(full_bar(sn), phn);
+                    have = mbar_test_wait(full_bar(sn), phn);
                     tc_fence_after();
                     // the A rows were written by cp.async (generic proxy); the MMA reads through the async proxy
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");

@@ -73,7 +73,10 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
         db = torch.from_numpy(b.view(np.uint8)).cuda()
         dbias = torch.from_numpy(np.ascontiguousarray(bias, dtype=np.int32)).cuda() if bias is not None else None
         canary = 0xA5
-        dd = torch.full((batch * M * ldd,), canary, dtype=torch.uint8, device="cuda")
+        # guard regions of canary bytes on both sides of the destination: a store outside the matrix shows up
+        guard = 4096
+        whole = torch.full((guard + batch * M * ldd + guard,), canary, dtype=torch.uint8, device="cuda")
+        dd = whole[guard:guard + batch * M * ldd]
         if dst_init is not None:  # accumulation starts from these values
             init = np.ascontiguousarray(dst_init, dtype=out_dtype).reshape(batch * M, N).view(np.uint8)
             dd.view(batch * M, ldd)[:, :N * dsz] = torch.from_numpy(init).cuda()
@@ -82,7 +85,10 @@ def gpu_gemmlowp(ctx, a, b, bias, a_off, b_off, mult, shift, offset, lo, hi, out
         for _ in range(runs):
             plan.run(da, None if b_constant else db, dbias, dd)
         ctx.sync()
-        raw = dd.cpu().numpy().reshape(batch, M, ldd)
+        everything = whole.cpu().numpy()
+        assert (everything[:guard] == canary).all() and (everything[-guard:] == canary).all(), \
+            "kernel wrote outside the destination matrix"
+        raw = everything[guard:-guard].reshape(batch, M, ldd)
         if ldd_pad:
             bad = np.argwhere(raw[:, :, N * dsz:] != canary)
             assert bad.size == 0, f"kernel wrote into the row padding: {len(bad)} bytes, first (batch, row, byte) {bad[:4].tolist()}, bytes past the row {np.unique(bad[:, 2]).tolist()[:32]}"

@@ -42,15 +42,20 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
     d_src = torch.from_numpy(src.view(np.uint8)).cuda()
     d_w = torch.from_numpy(weights.view(np.uint8)).cuda()
     d_b = torch.from_numpy(bias).cuda() if bias is not None else None
-    d_dst = torch.empty((B, ho, wo, OFM), dtype=torch.uint8, device="cuda")
+    # guard regions of canary bytes on both sides of the destination: a store outside the tensor shows up
+    guard, n_out = 4096, B * ho * wo * OFM
+    whole = torch.full((guard + n_out + guard,), 0xA5, dtype=torch.uint8, device="cuda")
+    d_dst = whole[guard:guard + n_out].view(B, ho, wo, OFM)
     plan.prepare(d_w)
     del d_w  # weights may be released after prepare()
     plan.run(d_src, d_b, d_dst)
     plan.run(d_src, d_b, d_dst)
     ctx.sync()
-    out = d_dst.cpu().numpy().view(src.dtype)
+    everything = whole.cpu().numpy()
     plan.close()
-    return out
+    assert (everything[:guard] == 0xA5).all() and (everything[-guard:] == 0xA5).all(), \
+        "kernel wrote outside the destination tensor"
+    return np.ascontiguousarray(everything[guard:-guard]).view(src.dtype).reshape(B, ho, wo, OFM)
 
 
 def test_conv_golden(ctx, port):
