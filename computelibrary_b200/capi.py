@@ -154,6 +154,7 @@ _SIGNATURES = {
     "cugl_conv2d_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_tma_store": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_resident_weights": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_tma_store": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
@@ -654,6 +655,9 @@ class ConvPlan:
 
     def set_tma_store(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_tma_store(self.handle, int(on)))
+
+    def set_resident_weights(self, on=True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_resident_weights(self.handle, int(on)))
 
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_channel_major(self.handle, int(mode)))

@@ -1621,7 +1621,9 @@ __device__ __forceinline__ void epilogue_warp_tile(uint32_t tmem_acc, const int4
 // issuing thread about 550 clocks whatever it covers, more than the 512 clocks four MMAs keep the tensor
 // cores busy, so a stage carries two sub-blocks (eight MMAs) wherever shared memory leaves room for three
 // such stages.
-template <int BLOCK_N, int STAGES, int KSUB, int ACC = 2, bool kPairTma = false>
+// RESB > 0 (implicit convolution with one column block): the whole B operand stays in RESB bytes of shared memory for
+// the life of the CTA and the ring holds A stages only.
+template <int BLOCK_N, int STAGES, int KSUB, int ACC = 2, bool kPairTma = false, int RESB = 0>
 struct SmemPlan
 {
     static constexpr int ACC_STAGES = ACC; // accumulator buffers in tensor memory (ACC * BLOCK_N <= 512 columns)
@@ -1630,10 +1632,11 @@ struct SmemPlan
     static constexpr int B_SUB      = BLOCK_N * BLOCK_K;          // one K sub-block of the B tile
     static constexpr int A_STAGE_K  = KSUB * A_STAGE;
     static constexpr int B_STAGE    = KSUB * B_SUB;
-    static constexpr int STAGE      = A_STAGE_K + B_STAGE;
+    static_assert(RESB % 1024 == 0, "the resident operand keeps the 1024-byte alignment of what follows");
+    static constexpr int STAGE      = A_STAGE_K + (RESB != 0 ? 0 : B_STAGE);
     static constexpr int OFF_A      = 0;
-    static constexpr int OFF_B      = STAGES * A_STAGE_K;
-    static constexpr int OFF_COL    = STAGES * STAGE;             // int4 per column
+    static constexpr int OFF_B      = STAGES * A_STAGE_K;         // the B slots of the ring, or the resident B operand
+    static constexpr int OFF_COL    = STAGES * STAGE + RESB;      // int4 per column
     static constexpr int EPI_GROUPS = (kEpiWarps == 8 && BLOCK_N <= 128) ? 2 : 1; // see epilogue_warp_tile
     static constexpr int OFF_BAR    = OFF_COL + EPI_GROUPS * BLOCK_N * 16; // full[S], empty[S], tfull[ACC], tempty[ACC]
     static constexpr int OFF_MISC   = OFF_BAR + (2 * STAGES + 2 * ACC) * 8; // tmem base, abort flag
@@ -2521,12 +2524,15 @@ static_assert(kConvPadBytes >= 16 * 32 * kGatherWarps, "one pad piece per gather
 constexpr int kFirstGather  = kFirstEpi + kEpiWarps;
 constexpr int kConvThreads  = kThreads + 32 * kGatherWarps;
 
-template <int BLOCK_N, int STAGES, int KSUB, int ACC>
+// RESB > 0: a convolution with a single column block (N <= BLOCK_N) whose weights fit into RESB bytes.  Every tile of
+// every CTA multiplies by the same B operand, so the producer thread loads it once and the ring carries patches only:
+// a third less traffic from L2 into shared memory for 64 output channels, and a deeper ring in the space set free.
+template <int BLOCK_N, int STAGES, int KSUB, int ACC, int RESB = 0>
 __global__ void __launch_bounds__(kConvThreads, 1)
     gemmlowp_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_out,
                                  const __grid_constant__ TileParams tp, const EpilogueParams ep, const ConvGeom cg)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, false, RESB>;
     extern __shared__ uint8_t smem_raw[];
     // the 1024-byte aligned start of the dynamic shared memory, derived by pointer arithmetic on the __shared__ array
     // itself: a pointer rebuilt from an integer loses its address space and every access through it becomes a
@@ -2544,6 +2550,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     uint32_t      *s_tmem     = reinterpret_cast<uint32_t *>(smem + P::OFF_MISC);
     volatile int  *s_abort    = reinterpret_cast<volatile int *>(smem + P::OFF_MISC + 4);
     TapEntry      *s_taps     = reinterpret_cast<TapEntry *>(smem + P::TOTAL);
+    const uint32_t bres_bar   = smem_u32(smem + P::OFF_MISC + 8); // RESB: the resident B operand has landed
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -2570,9 +2577,11 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     {
         for (int s = 0; s < STAGES; ++s)
         {
-            mbar_init(full_bar(s), 1 + 32 * kGatherWarps); // B copy (expect_tx arrive) + one deferred arrival per gather thread
+            // B copy (expect_tx arrive; none with a resident B) + one deferred arrival per gather thread
+            mbar_init(full_bar(s), (RESB != 0 ? 0 : 1) + 32 * kGatherWarps);
             mbar_init(empty_bar(s), 1);
         }
+        mbar_init(bres_bar, 1);
         for (int a = 0; a < ACC; ++a)
         {
             mbar_init(tfull_bar(a), 1);
@@ -2593,7 +2602,21 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     if (warp < kProdWarps)
     {
         // ---------------------------------------------------------------- TMA producer: weights only
-        if (warp == 0 && lane == 0)
+        if (RESB != 0)
+        {
+            if (warp == 0 && lane == 0)
+            {
+                // the whole operand once: K sub-blocks of BLOCK_N rows x 128 bytes (zero fill beyond K and N)
+                const int n_sub = (tp.K + BLOCK_K - 1) / BLOCK_K;
+                mbar_expect_tx(bres_bar, n_sub * P::B_SUB);
+                for (int sub = 0; sub < n_sub; ++sub)
+                {
+                    tma_load_2d(sB + sub * P::B_SUB, &tmap_b, sub * BLOCK_K, 0, bres_bar);
+                }
+                (void)mbar_wait(bres_bar, 0, s_abort, DEV_TIMEOUT_PRODUCER, tp.spin_limit); // landed before the CTA may leave
+            }
+        }
+        else if (warp == 0 && lane == 0)
         {
             int      st = 0;
             uint32_t ph = 0;
@@ -2634,6 +2657,10 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             bool     ok = true, have = false;
             const uint64_t a_desc0 = make_kmajor_sw128_desc(sA);
             const uint64_t b_desc0 = make_kmajor_sw128_desc(sB);
+            if (RESB != 0)
+            {
+                ok = mbar_wait(bres_bar, 0, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
+            }
             for (int ti = 0; ti < my_tiles && ok; ++ti)
             {
                 ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
@@ -2661,7 +2688,8 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                     // the A rows were written by cp.async (generic proxy); the MMA reads through the async proxy
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
-                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((s * P::B_STAGE) >> 4);
+                    // the ring slot, or this stage's K sub-blocks of the resident operand
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((RESB != 0 ? kb : s) * P::B_STAGE) >> 4);
 #pragma unroll
                     for (int sub = 0; sub < KSUB; ++sub)
                     {
@@ -3204,12 +3232,14 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     return CUGL_SUCCESS;
 }
 
-template <int BLOCK_N, int STAGES, int KSUB, int ACC>
+template <int BLOCK_N, int STAGES, int KSUB, int ACC, int RESB = 0>
 cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                 const ConvOperands &cv)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC>;
-    constexpr int kDynBytes = P::DYN_BYTES + kConvMaxPieces * static_cast<int>(sizeof(TapEntry));
+    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, false, RESB>;
+    // the tap table: one entry per 16 bytes of K; with a resident B operand K is at most RESB / BLOCK_N bytes
+    constexpr int kTapEntries = RESB != 0 ? RESB / BLOCK_N / 16 : kConvMaxPieces;
+    constexpr int kDynBytes   = P::DYN_BYTES + kTapEntries * static_cast<int>(sizeof(TapEntry));
     static_assert(kDynBytes <= 227 * 1024, "shared memory plan exceeds the sm_100 limit");
     static_assert(P::TOTAL % 8 == 0, "the tap table follows the plan");
     CUtensorMap map_b;
@@ -3223,7 +3253,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the output tiles");
     }
-    auto        kernel = gemmlowp_conv_tcgen05_kernel<BLOCK_N, STAGES, KSUB, ACC>;
+    auto        kernel = gemmlowp_conv_tcgen05_kernel<BLOCK_N, STAGES, KSUB, ACC, RESB>;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63])
     {
@@ -3384,6 +3414,11 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_conv_tcgen05)(cugl_context *ctx, const 
     }
     // narrow tiles: four accumulator buffers keep more tiles in flight (56x56x64 -> 64, batch 256: 131 -> 115 us;
     // eight one-block stages instead of four two-block stages measured slower: 129 us)
+    constexpr int kResidentB = 40 * 1024; // K <= 640: the weights of a 3x3 x 64 or a folded 7x7 x 3 filter bank
+    if (op.resident_b >= 0 && op.N <= 64 && ((op.K + BLOCK_K - 1) / BLOCK_K) * 64 * BLOCK_K <= kResidentB)
+    {
+        return launch_conv_variant<64, 5, 2, 4, kResidentB>(ctx, op, ep, cv);
+    }
     return launch_conv_variant<64, 4, 2, 4>(ctx, op, ep, cv);
 }
 } // namespace cugl

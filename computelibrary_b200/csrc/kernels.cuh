@@ -71,6 +71,9 @@ struct GemmOperands
     // one-CTA row-major kernels, eight- and four-warp builds: < 0 keeps the epilogue on per-lane global stores; otherwise
     // a warp's 32 rows leave as one bulk tensor store from shared memory where the destination allows it
     int tma_store;
+    // implicit convolution (gather): < 0 reloads the weights with every tile; otherwise they stay in shared memory for
+    // the life of a CTA where one column block covers N and they fit beside the ring
+    int resident_b;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).

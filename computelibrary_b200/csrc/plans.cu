@@ -63,6 +63,7 @@ struct GemmCore
     int           block_n       = 0;     // 64 / 128 / 256 force that tile width of the one-CTA kernels, 0 = automatic
     int           pair_drain    = 0;     // < 0: every accumulator buffer is drained on its own
     int           tma_store     = 0;     // < 0: no bulk tensor stores in the epilogue
+    int           resident_b    = 0;     // < 0: the implicit convolution reloads the weights with every tile
 
     // bytes of the row-sum vector as a share of a temporary workspace (none without a B offset)
     size_t rowsum_bytes() const
@@ -239,6 +240,7 @@ struct GemmCore
         op.block_n       = block_n;
         op.pair_drain    = pair_drain;
         op.tma_store     = tma_store;
+        op.resident_b    = resident_b;
         op.n_extra_dst   = n_extra;
         op.residual      = d_residual;
         op.res_floor     = res_floor;
@@ -1309,6 +1311,7 @@ extern "C"
             op.block_n       = c.block_n;
             op.pair_drain    = c.pair_drain;
             op.tma_store     = c.tma_store;
+            op.resident_b    = c.resident_b;
             op.n_extra_dst   = 0;
             op.residual      = d_residual;
             op.res_floor     = plan->res_floor;
@@ -1478,6 +1481,16 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_tma_store: NULL plan");
         }
         plan->core.tma_store = on != 0 ? 0 : -1;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_resident_weights(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_resident_weights: NULL plan");
+        }
+        plan->core.resident_b = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
     }
 

@@ -423,6 +423,10 @@ CUGL_API cugl_status cugl_conv2d_plan_set_tile_columns(cugl_conv_plan *plan, int
 CUGL_API cugl_status cugl_conv2d_plan_set_paired_drain(cugl_conv_plan *plan, int on);
 /* as cugl_gemmlowp_plan_set_tma_store */
 CUGL_API cugl_status cugl_conv2d_plan_set_tma_store(cugl_conv_plan *plan, int on);
+/* Implicit lowering with at most 64 output channels and K = kh * kw * C <= 640: the weight operand is loaded into shared
+ * memory once per thread block and stays there (on by default); 0 reloads it with every tile as for larger filters.
+ * For tests and measurements; results do not depend on it. */
+CUGL_API cugl_status cugl_conv2d_plan_set_resident_weights(cugl_conv_plan *plan, int on);
 /* NEGEMMConvolutionLayer::update_quantization_parameters (src/runtime/NEON/functions/NEGEMMConvolutionLayer.cpp:129-131,
  * src/cpu/operators/CpuGemmConv2d.cpp:858-908): re-reads the zero points, the multipliers / shifts, the output zero
  * point and the clamp bounds of desc; geometry and types must be unchanged.  The prepared weights stay valid. */

@@ -14,7 +14,8 @@ CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
 
 
 def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1),
-             implicit=True, want_kernel=None, tile_columns=0, paired_drain=True, tma_im2col=True, want_tma=None):
+             implicit=True, want_kernel=None, tile_columns=0, paired_drain=True, tma_im2col=True, want_tma=None,
+             resident_weights=True):
     import torch
     B, H, W, Cc = src.shape
     OFM, kh, kw, _ = weights.shape
@@ -34,6 +35,8 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
         plan.set_paired_drain(False)
     if tma_im2col is not True:
         plan.allow_tma_im2col(int(tma_im2col))  # 0: the gather; 2: TMA loads for 64-channel inputs too
+    if not resident_weights:
+        plan.set_resident_weights(False)
     if want_tma is not None:
         assert plan.uses_tma_im2col == want_tma
     if want_kernel is not None:
@@ -363,3 +366,26 @@ def test_tma_im2col_on_the_sm_pair_kernel(ctx, port, geom):
         want = port.conv2d_nhwc(src[sl], wgt, bias, (s, s), (1, 1, 1, 1), 0, 0, mult, shift, 3, 0, 255)
         assert np.array_equal(tma[sl], want)
     assert 0.01 < (tma == 0).mean() < 0.99 and 0.01 < (tma == 255).mean() + (tma < 255).mean()
+
+
+@pytest.mark.parametrize("geom", [((3, 3), 1, 1, 64, 64, 30, 28, 128), ((3, 3), 2, 1, 64, 40, 29, 31, 7), ((7, 7), 2, 3, 3, 64, 61, 64, 128),
+                                  ((2, 5), 1, 0, 64, 64, 17, 19, 0), ((1, 3), 1, 0, 16, 24, 40, 33, 250),
+                                  ((3, 3), 1, 1, 80, 64, 20, 20, 128), ((3, 3), 1, 1, 64, 72, 20, 20, 128)])
+@pytest.mark.parametrize("batch", [1, 7])
+def test_resident_weights_conv_vs_oracle(ctx, port, geom, batch):
+    """Gather convolutions with at most 64 output channels and K <= 640 keep the weight operand in shared memory for the
+    life of a thread block: the 3x3 x 64 and folded 7x7 x 3 layers of ResNet-50, K exactly 640, a ragged K (48) and N
+    (24, 40), many tiles per block (batch 7) -- against the oracle and against the per-tile reload; K = 720 and 72
+    output channels lie past the limits and must come out the same through the reloading kernel."""
+    (kh, kw), s, p, Cc, OFM, H, W, in_zp = geom
+    rng = np.random.default_rng(kh * 1000 + kw * 100 + Cc + OFM + batch)
+    src = q8_uniform(rng, (batch, H, W, Cc), np.uint8)
+    wgt = q8_uniform(rng, (OFM, kh, kw, Cc), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, OFM).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.03, ws, 0.05 * max(kh, kw))
+    want = port.conv2d_nhwc(src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255)
+    for resident in (True, False):
+        got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, want_kernel="implicit",
+                       tma_im2col=False, resident_weights=resident)
+        assert np.array_equal(got, want), (resident, np.argwhere(got != want)[:5])
