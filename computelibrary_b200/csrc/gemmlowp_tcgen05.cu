@@ -2690,18 +2690,37 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     // the ring slot, or this stage's K sub-blocks of the resident operand
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((RESB != 0 ? kb : s) * P::B_STAGE) >> 4);
-#pragma unroll
-                    for (int sub = 0; sub < KSUB; ++sub)
+                    // a stage that lies wholly inside K: the MMAs back to back, nothing to test on the issuing thread's
+                    // path (it shares its scheduler with epilogue and gather warps, so every instruction it saves counts)
+                    if ((kb + 1) * KSUB * BLOCK_K <= tp.K)
                     {
 #pragma unroll
-                        for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        for (int sub = 0; sub < KSUB; ++sub)
                         {
-                            // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
-                            if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                             {
                                 umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
                                         b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
                                         (kb | sub | k) != 0 ? 1u : 0u);
+                            }
+                        }
+                    }
+                    else
+                    {
+#pragma unroll
+                        for (int sub = 0; sub < KSUB; ++sub)
+                        {
+#pragma unroll
+                            for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                            {
+                                // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
+                                if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
+                                {
+                                    umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
+                                            b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                            (kb | sub | k) != 0 ? 1u : 0u);
+                                }
                             }
                         }
                     }
