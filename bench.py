@@ -45,7 +45,7 @@ def parse_args():
     p.add_argument("--steps", type=int, default=2000)
     p.add_argument("--warmup", type=int, default=200)
     p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "bw"])
+    p.add_argument("--workload", default="c2", choices=["c1", "c2", "c3", "c4", "c5", "bw", "tcgen05_rates"])
     p.add_argument("--only", default="", help="bw: run only the kernels whose name contains this text")
     p.add_argument("--small", action="store_true", help="bw: the reduced sizes used for ncu captures (a few hundred MB)")
     p.add_argument("--batch", type=int, default=256, help="global batch of c4 (split over the ranks)")
@@ -896,6 +896,22 @@ def run_bandwidth(args):
     ctx.close()
 
 
+def run_issue_rate_probe(args):
+    """What the thread that issues tensor-core work pays per instruction on an otherwise idle SM (clocks per tcgen05.mma
+    for N = 16 .. 256, per commit, per barrier operation): the stand-alone program built beside the library.  These
+    figures are the tile-shape rooflines the design notes quote; nothing of the library runs here."""
+    from computelibrary_b200 import build as cuda_build
+    exe = cuda_build.PROBE_PATH
+    if not os.path.exists(exe):
+        raise SystemExit(f"{exe} is missing: run __graft_entry__.build() first")
+    out = subprocess.run([exe], capture_output=True, text=True, timeout=120)
+    if out.returncode != 0:
+        raise SystemExit(f"probe failed: {out.stderr.strip()}")
+    line = {"metric": "tcgen05_issue_rates", "n_gpus": 1, "data": "none", "config": {"workload": "one CTA, one issuing thread"}}
+    line.update(json.loads(out.stdout))
+    print(json.dumps(line), flush=True)
+
+
 def json_only_stdout():
     """Keeps stdout for the JSON line alone: file descriptor 1 is pointed at stderr, where native libraries that print
     there end up (NCCL's version banner on several GPUs), and Python's sys.stdout keeps the original descriptor."""
@@ -912,7 +928,9 @@ def main():
     if args.impl == "reference":
         run_reference(args)
         return
-    if args.workload == "bw":
+    if args.workload == "tcgen05_rates":
+        run_issue_rate_probe(args)
+    elif args.workload == "bw":
         run_bandwidth(args)
     elif args.workload == "c3":
         run_conv(args)

@@ -82,5 +82,23 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB_PATH
 
 
+PROBE_PATH = os.path.join(LIB_DIR, "probe_tcgen05_rates")
+
+
+def build_probe(force: bool = False) -> str:
+    """The stand-alone program that measures tcgen05 issue rates (bench.py --workload tcgen05_rates runs it)."""
+    src = os.path.join(CSRC, "probe_tcgen05_rates.cu")
+    os.makedirs(LIB_DIR, exist_ok=True)
+    if not force and os.path.exists(PROBE_PATH) and os.path.getmtime(src) <= os.path.getmtime(PROBE_PATH):
+        return PROBE_PATH
+    cmd = [_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17", "-cudart", "static",
+           "-ccbin", shutil.which("g++") or "g++", src, "-o", PROBE_PATH]
+    res = subprocess.run(cmd, capture_output=True, text=True)
+    if res.returncode != 0:
+        sys.stderr.write(res.stdout + res.stderr)
+        raise RuntimeError("nvcc failed on probe_tcgen05_rates.cu")
+    return PROBE_PATH
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
