@@ -883,7 +883,7 @@ def run_bandwidth(args):
     pd = capi.make_pool_desc(B, 112, 112, 64, capi.POOL_MAX, (3, 3), (2, 2), (0, 1, 0, 1), (0.05, 0), (0.05, 0))
     wo, ho = capi.pool_out_dims(pd)
     src, dst = rnd8(B, 112, 112, 64), torch.empty((B, ho, wo, 64), dtype=torch.uint8, device="cuda")
-    case("maxpool_kernel", B * 64 * (112 * 112 + ho * wo), lambda: ctx.pool2d_nhwc(pd, src, dst),
+    case("maxpool_window_kernel", B * 64 * (112 * 112 + ho * wo), lambda: ctx.pool2d_nhwc(pd, src, dst),
          f"batch {B}, 112x112x64, 3x3 s2")
     del src, dst
     n = (256 // sc) * 56 * 56 * 256

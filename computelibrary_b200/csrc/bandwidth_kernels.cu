@@ -428,6 +428,10 @@ __global__ void __launch_bounds__(kThreads) im2col_nhwc_kernel(const uint8_t *__
 // convolution over 16 channels whose folded weights are zero wherever the original kernel has no tap:
 // the sums are the same integers.  fold_input_kernel: dst[b][Y][X][(dy*2+dx)*4 + c] = src[b][2Y+dy][2X+dx][c];
 // pixels beyond an odd edge and the padding channels hold the zero point (their weights are zero).
+// One thread per folded pixel (16 output bytes).  kFast: three channels, an even image width and a 2-byte aligned
+// tensor -- the two pixels of a row of the block are six contiguous bytes on a 2-byte boundary and come in as three
+// 16-bit loads -- and fewer than 2^31 folded pixels, so that the index arithmetic is 32-bit.
+template <bool kFast>
 __global__ void __launch_bounds__(kThreads) fold_input_kernel(const uint8_t *__restrict__ src, uint8_t *__restrict__ dst,
                                                               int B, int H, int W, int C, int H2, int W2, uint32_t zp)
 {
@@ -435,25 +439,60 @@ __global__ void __launch_bounds__(kThreads) fold_input_kernel(const uint8_t *__r
     for (int64_t i = blockIdx.x * static_cast<int64_t>(kThreads) + threadIdx.x; i < total;
          i += static_cast<int64_t>(gridDim.x) * kThreads)
     {
-        const int     X = static_cast<int>(i % W2);
-        const int     Y = static_cast<int>((i / W2) % H2);
-        const int64_t b = i / (static_cast<int64_t>(W2) * H2);
-        uint32_t      w[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
+        int     X, Y;
+        int64_t b;
+        if (kFast)
         {
-            const int y = 2 * Y + (q >> 1), x = 2 * X + (q & 1);
-            uint32_t  v = zp * 0x01010101u;
-            if (y < H && x < W)
+            uint32_t q = static_cast<uint32_t>(i);
+            X          = static_cast<int>(q % static_cast<uint32_t>(W2));
+            q /= static_cast<uint32_t>(W2);
+            Y = static_cast<int>(q % static_cast<uint32_t>(H2));
+            b = q / static_cast<uint32_t>(H2);
+        }
+        else
+        {
+            X = static_cast<int>(i % W2);
+            Y = static_cast<int>((i / W2) % H2);
+            b = i / (static_cast<int64_t>(W2) * H2);
+        }
+        uint32_t w[4];
+        if (kFast)
+        {
+            // W is even: the block's two columns both lie inside the image
+#pragma unroll
+            for (int dy = 0; dy < 2; ++dy)
             {
-                const uint8_t *p = src + ((b * H + y) * W + x) * C;
-                v                = 0;
-                for (int c = 0; c < 4; ++c)
+                const int y = 2 * Y + dy;
+                uint32_t  p0 = zp * 0x01010101u, p1 = p0;
+                if (y < H)
                 {
-                    v |= (c < C ? static_cast<uint32_t>(p[c]) : zp) << (8 * c);
+                    const uint16_t *p = reinterpret_cast<const uint16_t *>(src + ((b * H + y) * W + 2 * X) * 3);
+                    const uint32_t  h0 = __ldg(p), h1 = __ldg(p + 1), h2 = __ldg(p + 2); // c0 c1 | c2 c0' | c1' c2'
+                    p0 = h0 | ((h1 & 0xffu) << 16) | (zp << 24);
+                    p1 = (h1 >> 8) | (h2 << 8) | (zp << 24);
                 }
+                w[2 * dy]     = p0;
+                w[2 * dy + 1] = p1;
             }
-            w[q] = v;
+        }
+        else
+        {
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+            {
+                const int y = 2 * Y + (q >> 1), x = 2 * X + (q & 1);
+                uint32_t  v = zp * 0x01010101u;
+                if (y < H && x < W)
+                {
+                    const uint8_t *p = src + ((b * H + y) * W + x) * C;
+                    v                = 0;
+                    for (int c = 0; c < 4; ++c)
+                    {
+                        v |= (c < C ? static_cast<uint32_t>(p[c]) : zp) << (8 * c);
+                    }
+                }
+                w[q] = v;
+            }
         }
         reinterpret_cast<uint4 *>(dst)[i] = make_uint4(w[0], w[1], w[2], w[3]);
     }
@@ -657,9 +696,20 @@ cugl_status launch_fold_input(cugl_context *ctx, const void *d_src, void *d_dst,
                               int W2, int zero_point)
 {
     const int blocks = grid_for(static_cast<int64_t>(B) * H2 * W2, ctx->sm_count);
-    fold_input_kernel<<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_src),
-                                                            static_cast<uint8_t *>(d_dst), B, H, W, C, H2, W2,
-                                                            static_cast<uint32_t>(zero_point) & 0xffu);
+    const bool fast = C == 3 && (W & 1) == 0 && (reinterpret_cast<uintptr_t>(d_src) & 1) == 0 &&
+                      static_cast<int64_t>(B) * H2 * W2 <= 0x7fffffff;
+    if (fast)
+    {
+        fold_input_kernel<true><<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_src),
+                                                                      static_cast<uint8_t *>(d_dst), B, H, W, C, H2, W2,
+                                                                      static_cast<uint32_t>(zero_point) & 0xffu);
+    }
+    else
+    {
+        fold_input_kernel<false><<<blocks, kThreads, 0, ctx->stream>>>(static_cast<const uint8_t *>(d_src),
+                                                                       static_cast<uint8_t *>(d_dst), B, H, W, C, H2, W2,
+                                                                       static_cast<uint32_t>(zero_point) & 0xffu);
+    }
     return check_cuda(ctx, cudaGetLastError(), "fold_input_kernel");
 }
 

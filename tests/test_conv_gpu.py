@@ -150,7 +150,7 @@ def test_implicit_conv_vs_oracle(ctx, port, geom, in_zp):
 
 
 @pytest.mark.parametrize("geom", [(7, 3, 3, 20, 22), (7, 3, 3, 19, 23), (3, 1, 4, 17, 18), (5, 2, 1, 9, 11), (3, 0, 3, 12, 15),
-                                  (2, 1, 2, 10, 10), (4, 2, 4, 21, 16)])
+                                  (2, 1, 2, 10, 10), (4, 2, 4, 21, 16), (3, 1, 3, 17, 18), (7, 3, 3, 19, 24)])
 @pytest.mark.parametrize("in_zp", [0, 77])
 def test_folded_stride2_conv_vs_oracle(ctx, port, geom, in_zp):
     """Stride-2 convolutions over at most four channels (the 7x7 / 2 stem of ResNet-50 on RGB images) run as a

@@ -116,3 +116,20 @@ def test_softmax_golden(ctx, golden):
         ctx.sync()
         diff = np.abs(dst.cpu().numpy().astype(np.int32) - golden[c["key"]].astype(np.int32))
         assert diff.max() <= 1, (c["key"], int(diff.max()))
+
+
+@pytest.mark.parametrize("window", [((3, 3), (2, 2), (0, 1, 0, 1)), ((3, 3), (2, 2), (1, 1, 1, 1)), ((3, 3), (1, 1), (1, 1, 1, 1)),
+                                    ((3, 3), (2, 3), (2, 0, 1, 2)), ((2, 2), (2, 2), (0, 0, 0, 0)), ((2, 2), (1, 2), (1, 1, 0, 1)),
+                                    ((1, 1), (2, 2), (0, 0, 0, 0)), ((1, 1), (1, 1), (0, 0, 0, 0)), ((3, 2), (2, 2), (1, 0, 0, 1)),
+                                    ((5, 5), (3, 3), (2, 2, 2, 2))])
+@pytest.mark.parametrize("quant", [((0.05, 0), (0.05, 0)), ((0.05, 3), (0.05, 3)), ((0.05, 3), (0.07, 10)), ((0.11, 0), (0.02, 128))])
+def test_max_pool_windows(ctx, port, window, quant):
+    """MAX pooling over the unrolled window kernels (3x3, 2x2, 1x1; 16 channels per thread) and the general one (3x2, 5x5
+    and 24 channels): padded borders on every side, odd image sizes, strides that differ in x and y, and both the
+    identity table (equal quantization: bytes stored as they are) and a real requantisation, against the oracle."""
+    size, stride, pad = window
+    r = np.random.default_rng(size[0] * 100 + size[1] * 10 + stride[0] + pad[0])
+    for shape in ((3, 23, 17, 32), (2, 9, 14, 64), (1, 12, 11, 24)):
+        c = dict(src=r.integers(0, 256, shape, dtype=np.uint8), geom=("max", size, stride, pad, False, False),
+                 in_q=quant[0], out_q=quant[1])
+        np.testing.assert_array_equal(gpu_pool(ctx, c), pool_with(port, c), err_msg=str((shape, window, quant)))
