@@ -404,11 +404,17 @@ __global__ void __launch_bounds__(kThreads)
         float sum[kVec];
 #pragma unroll
         for (int k = 0; k < kVec; ++k) sum[k] = 0.f;
-        for (int y = hs; y < he; ++y)
+        // the additions stay in window order (the float sum must round as the reference's does); the loads of a window
+        // row are independent of them, so the row is walked by pointer and unrolled to keep several loads in flight
+        // (a window as wide as the image, e.g. the global pool, is one run of pixels)
+        const bool whole_rows = ws == 0 && we == g.W;
+        const int  y_end = whole_rows ? hs + 1 : he, run = whole_rows ? (he - hs) * g.W : we - ws;
+        for (int y = hs; y < y_end; ++y)
         {
-            for (int x = ws; x < we; ++x)
+            const uint8_t *px = src + ((static_cast<int64_t>(b) * g.H + y) * g.W + ws) * g.C + c;
+#pragma unroll 8
+            for (int x = 0; x < run; ++x, px += g.C)
             {
-                const uint8_t *px = src + ((static_cast<int64_t>(b) * g.H + y) * g.W + x) * g.C + c;
                 if (kVec == 4)
                 {
                     const uint32_t v = __ldg(reinterpret_cast<const uint32_t *>(px));
@@ -420,7 +426,7 @@ __global__ void __launch_bounds__(kThreads)
                 }
                 else
                 {
-                    sum[0] = __fadd_rn(sum[0], dequantize(px[0], in.scale, in.zp));
+                    sum[0] = __fadd_rn(sum[0], dequantize(__ldg(px), in.scale, in.zp));
                 }
             }
         }
