@@ -407,12 +407,12 @@ __global__ void __launch_bounds__(kThreads)
         // the additions stay in window order (the float sum must round as the reference's does); the loads of a window
         // row are independent of them, so the row is walked by pointer and unrolled to keep several loads in flight
         // (a window as wide as the image, e.g. the global pool, is one run of pixels)
-        const bool whole_rows = ws == 0 && we == g.W;
+        const bool whole_rows = kVec == 4 && ws == 0 && we == g.W; // (one channel per thread: measured slower that way)
         const int  y_end = whole_rows ? hs + 1 : he, run = whole_rows ? (he - hs) * g.W : we - ws;
         for (int y = hs; y < y_end; ++y)
         {
             const uint8_t *px = src + ((static_cast<int64_t>(b) * g.H + y) * g.W + ws) * g.C + c;
-#pragma unroll 8
+#pragma unroll(kVec == 4 ? 8 : 1)
             for (int x = 0; x < run; ++x, px += g.C)
             {
                 if (kVec == 4)
@@ -714,9 +714,9 @@ extern "C"
             }
             return check_cuda(ctx, cudaGetLastError(), "maxpool_kernel");
         }
-        // four channels per thread once that still leaves every SM a few hundred threads (batch 256, 2048 channels:
-        // 32 -> 22 us); below that the one-channel form has the parallelism (batch 64 under ncu: 16 us against 22 us)
-        const bool vec4 = (g.C % 4) == 0 && pixels * (g.C / 4) >= static_cast<int64_t>(ctx->sm_count) * 512 &&
+        // four channels per thread once that still leaves every SM a hundred threads or more (global pool of
+        // 7 x 7 x 2048: batch 256 32 -> 18 us, batch 64 21 -> 14 us); below that the one-channel form has the parallelism
+        const bool vec4 = (g.C % 4) == 0 && pixels * (g.C / 4) >= static_cast<int64_t>(ctx->sm_count) * 128 &&
                           ((reinterpret_cast<uintptr_t>(d_src) | reinterpret_cast<uintptr_t>(d_dst)) & 3) == 0;
         if (vec4)
         {
