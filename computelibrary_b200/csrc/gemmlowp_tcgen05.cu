@@ -1077,7 +1077,7 @@ __device__ __forceinline__ void finish_chunk_pair(const PairDrain &d, int ch, ui
         // 64-byte rows, 16-byte piece p of row r at piece p ^ ((r >> 1) & 3): the tensor map's 64-byte swizzle
         if (ch == 0 && d.rmap == nullptr)
         {
-            stage_reuse_wait(d.lane); // the previous pair's stores have read the stage (with a residual: see drain_pair_x16)
+            stage_reuse_wait(d.lane); // the previous pair's stores have read the stage (with a residual: request_residual_boxes)
         }
         const uint32_t row = d.stage + d.lane * 64, sw = (d.lane >> 1) & 3;
         const uint32_t p0 = ((2u * ch) ^ sw) << 4, p1 = ((2u * ch + 1u) ^ sw) << 4;
@@ -1164,19 +1164,26 @@ __device__ __forceinline__ void drain_pair_chunk_x16(const PairDrain &d, int ch,
     }
     finish_chunk_pair(d, ch, wa, wb, res_a, res_b);
 }
+// Paired drain with a fused residual: the warp's two residual boxes (32 rows x 64 bytes of each tile) into its staging
+// area, completion on the warp's own barrier.  Called before the wait for the accumulators, so that the boxes travel
+// while the pair's MMAs are still being issued; the previous pair's bulk stores must have read the stage first.
+__device__ __forceinline__ void request_residual_boxes(const CUtensorMap *rmap, uint32_t stage, uint32_t res_bar, int n_first,
+                                                       int row_a, int row_b, int lane)
+{
+    stage_reuse_wait(lane);
+    if (lane == 0)
+    {
+        mbar_expect_tx(res_bar, kPairStageBytes);
+        tma_load_2d(stage, rmap, n_first, row_a, res_bar);
+        tma_load_2d(stage + 2048, rmap, n_first, row_b, res_bar);
+    }
+}
+
 template <int NCOLS, int kMode>
 __device__ __forceinline__ void drain_pair_x16(const PairDrain d)
 {
-    if (d.stage != 0 && d.rmap != nullptr)
-    {
-        stage_reuse_wait(d.lane); // the previous pair's stores have read the stage
-        if (d.lane == 0)
-        {
-            mbar_expect_tx(d.res_bar, kPairStageBytes);
-            tma_load_2d(d.stage, d.rmap, d.n_first, d.row_a, d.res_bar);
-            tma_load_2d(d.stage + 2048, d.rmap, d.n_first, d.row_b, d.res_bar);
-        }
-    }
+    // (with a fused residual the caller has requested the warp's two residual boxes into the stage before it waited
+    // for the accumulators: request_residual_boxes)
 #pragma unroll 1
     for (int ch = 0; ch < NCOLS / 32; ++ch)
     {
@@ -2030,7 +2037,22 @@ __global__ void __launch_bounds__(kThreads, 1)
                 pair_now = tile_b < num_tiles && tile_b / num_m_blocks == tile / num_m_blocks;
             }
             const int m0b = kCanPair ? (tile_b % num_m_blocks) * BLOCK_M : 0;
-            if (!kCM && !kS32Out && tp.residual != nullptr)
+            // kPairTma: the warp's share of both tiles leaves as two bulk tensor stores from its staging area, and a fused
+            // residual arrives there as two bulk tensor loads, requested here, ahead of the accumulators
+            const uint32_t pair_stage =
+                (kPairTma && kCanPair && pair_now && tp.tma_store != 0)
+                    ? smem_u32(smem + P::OFF_OUT) + static_cast<uint32_t>(warp - kFirstEpi) * kPairStageBytes
+                    : 0u;
+            const bool     res_tma = pair_stage != 0 && tp.residual != nullptr;
+            const uint32_t res_bar = smem_u32(smem + P::OFF_RESBAR) + 8u * static_cast<uint32_t>(warp - kFirstEpi);
+            if (res_tma)
+            {
+                constexpr int NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
+                const int     first = n0 + (kGroups == 1 ? (warp - kFirstEpi) >> 2 : 0) * NCOLS;
+                request_residual_boxes(&tmap_res, pair_stage, res_bar, first, m0 + (warp & 3) * 32, m0b + (warp & 3) * 32, lane);
+                // (asking the pair after this one into L2 as well, a drain ahead, measured slower: 142 against 135 us)
+            }
+            else if (!kCM && !kS32Out && tp.residual != nullptr)
             {
                 constexpr int NCOLS = BLOCK_N * kGroups / (kEpiWarps / 4);
                 const int     row   = (warp & 3) * 32 + lane;
@@ -2060,27 +2082,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 else if (kCanPair && pair_now)
                 {
-                    // kPairTma: the warp's share of both tiles leaves as two bulk tensor stores from its staging area
-                    const uint32_t pair_stage =
-                        (kPairTma && tp.tma_store != 0)
-                            ? smem_u32(smem + P::OFF_OUT) + static_cast<uint32_t>(warp - kFirstEpi) * kPairStageBytes
-                            : 0u;
-                    const bool     res_tma = pair_stage != 0 && tp.residual != nullptr; // residual boxes through the TMA unit
-                    const uint32_t res_bar = smem_u32(smem + P::OFF_RESBAR) + 8u * static_cast<uint32_t>(warp - kFirstEpi);
                     epilogue_warp_tile_pair<BLOCK_N, kGroups>(tmem_base + as * BLOCK_N, tmem_base + (as + kStride) * BLOCK_N,
                                                               g_col, tp, ep, warp, lane, m0, m0b, n0, rel, pair_stage, &tmap_out,
                                                               &tmap_res, res_bar, n_res_pairs & 1u, s_abort);
-                    if (res_tma)
-                    {
-                        if (*s_abort != 0) // a wait was given up: let this warp's residual boxes land before anything else
-                        {
-                            const long long t0 = clock64();
-                            while (!mbar_try_wait(res_bar, n_res_pairs & 1u) && clock64() - t0 < tp.spin_limit)
-                            {
-                            }
-                        }
-                        ++n_res_pairs;
-                    }
                 }
                 else
                 {
@@ -2094,6 +2098,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                 {
                     skip = ti + kStride;
                 }
+            }
+            if (res_tma)
+            {
+                if (*s_abort != 0) // a wait was given up: let this warp's residual boxes land before anything else
+                {
+                    const long long t0 = clock64();
+                    while (!mbar_try_wait(res_bar, n_res_pairs & 1u) && clock64() - t0 < tp.spin_limit)
+                    {
+                    }
+                }
+                ++n_res_pairs;
             }
         }
         if (tp.tma_store != 0 && lane == 0)
