@@ -88,6 +88,7 @@ _SIGNATURES = {
     "cugl_context_sm_count": (C.c_int, [_vp]),
     "cugl_context_set_trace_buffer": (C.c_int, [_vp, _vp]),
     "cugl_context_set_wait_limit_us": (C.c_int, [_vp, C.c_uint64]),
+    "cugl_context_set_dependent_launch": (C.c_int, [_vp, C.c_int]),
     "cugl_context_withhold_copy_once": (C.c_int, [_vp, C.c_int]),
     "cugl_malloc": (C.c_int, [_vp, C.c_size_t, C.POINTER(_vp)]),
     "cugl_free": (C.c_int, [_vp, _vp]),
@@ -272,6 +273,10 @@ class Context:
 
     def set_trace_buffer(self, buf):
         self.check(self.lib.cugl_context_set_trace_buffer(self.handle, _dptr(buf)))
+
+    def set_dependent_launch(self, on: bool = True):
+        """Programmatic stream serialization of the tensor-core kernels (on by default)."""
+        self.check(self.lib.cugl_context_set_dependent_launch(self.handle, int(on)))
 
     def set_wait_limit_us(self, microseconds: int):
         """Bound of every device-side barrier wait of the tensor-core kernels (0: the two-second default)."""

@@ -21,6 +21,7 @@ struct cugl_context
     long long   *d_trace     = nullptr; // optional event-timestamp buffer for the tensor-core GEMM kernels
     long long    spin_limit  = 4000000000ll; // clock64 ticks a device-side wait may last (about two seconds)
     int          withhold_kb = -1;      // one-shot test instrument, see cugl_context_withhold_copy_once
+    int          dependent_launch = 1;  // tensor-core kernels launch with programmatic stream serialization
     std::string  last_error;
 };
 

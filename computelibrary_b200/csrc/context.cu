@@ -318,6 +318,16 @@ extern "C"
         return CUGL_SUCCESS;
     }
 
+    cugl_status cugl_context_set_dependent_launch(cugl_context *ctx, int on)
+    {
+        if (ctx == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_context_set_dependent_launch: NULL context");
+        }
+        ctx->dependent_launch = on != 0 ? 1 : 0;
+        return CUGL_SUCCESS;
+    }
+
     // ---- peer access to another process's device buffer (CUDA IPC) --------------------------------
     cugl_status cugl_ipc_get_handle(cugl_context *ctx, void *d_ptr, void *handle64)
     {

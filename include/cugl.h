@@ -108,6 +108,13 @@ CUGL_API cugl_status cugl_context_set_wait_limit_us(cugl_context *ctx, uint64_t 
  * producer of CTA 0 leaves out the operand copies of k-block ordinal `k_block` (counted over the CTA's tile
  * sequence), so that the wait for them runs out.  One shot: the launch after it is normal again. */
 CUGL_API cugl_status cugl_context_withhold_copy_once(cugl_context *ctx, int k_block);
+/* The tensor-core kernels are launched with programmatic stream serialization (on by default): a kernel lets the next
+ * one in the stream start its prologue (barrier set-up, tensor-memory allocation) while its own last tiles finish, and
+ * every kernel waits for its predecessor's completion (griddepcontrol.wait) before its first access to global memory.
+ * A stream that is being captured into a CUDA graph gets plain launches (measured faster there).  0 restores plain
+ * stream order everywhere.  No
+ * reference counterpart (the NE scheduler runs its kernels back to back on the host threads). */
+CUGL_API cugl_status cugl_context_set_dependent_launch(cugl_context *ctx, int on);
 
 /* IAllocator::allocate / free (arm_compute/runtime/IAllocator.h:39-61): device regions, 256-byte aligned. */
 CUGL_API cugl_status cugl_malloc(cugl_context *ctx, size_t bytes, void **d_ptr);

@@ -509,3 +509,47 @@ def test_bulk_tensor_stores_against_per_lane_stores(ctx, port, shape):
         outs.append(out)
     for o in outs[1:]:
         assert np.array_equal(o, outs[0])
+
+
+@pytest.mark.parametrize("widths", [(256, 256, 256), (64, 320, 128), (1024, 64, 512)])
+def test_chained_launches_with_and_without_dependent_launch(ctx, port, widths):
+    """A chain of three GEMMs, each reading what the one before it wrote, launched back to back twenty times over the
+    same buffers (so that a kernel also overwrites what its predecessor is still reading unless it waits for it): with
+    programmatic stream serialization (the default outside graph capture) and with plain stream order the chain ends
+    in the same bytes, equal to the oracle's."""
+    import torch
+    M, K0 = 3000, 128
+    r = np.random.default_rng(sum(widths))
+    a = q8_uniform(r, (M, K0), np.uint8)
+    dims = (K0,) + widths
+    layers, want = [], a
+    for k, n in zip(dims[:-1], dims[1:]):
+        b = q8_uniform(r, (k, n), np.int8, -127, 127)
+        bias = r.integers(-3000, 3000, n).astype(np.int32)
+        ws = np.exp(r.uniform(np.log(1e-3), np.log(4e-3), n)).astype(np.float32)
+        mult, shift = f32_mults(port, 0.05, ws, 0.05 * max(1, k // 128))
+        want = port.gemmlowp_fused(want, b, bias, -2, 0, mult, shift, 4, 0, 255, np.uint8)
+        layers.append((k, n, b, bias, mult, shift))
+    results = {}
+    try:
+        for dependent in (True, False):
+            ctx.set_dependent_launch(dependent)
+            plans, bufs = [], [torch.from_numpy(a).cuda()]
+            for k, n, b, bias, mult, shift in layers:
+                desc, keep = capi.make_gemm_desc(M, n, k, capi.U8, capi.S8, capi.U8, -2, 0, multipliers=mult, shifts=shift,
+                                                 offset=4, min_bound=0, max_bound=255, has_bias=True)
+                plan = capi.GemmPlan(ctx, desc, keep)
+                plan.prepare(torch.from_numpy(b.view(np.uint8)).cuda())
+                plans.append((plan, torch.from_numpy(bias).cuda()))
+                bufs.append(torch.zeros((M, n), dtype=torch.uint8, device="cuda"))
+            for _ in range(20):
+                for i, (plan, d_bias) in enumerate(plans):
+                    plan.run(bufs[i], None, d_bias, bufs[i + 1])
+            ctx.sync()
+            results[dependent] = bufs[-1].cpu().numpy()
+            for plan, _ in plans:
+                plan.close()
+    finally:
+        ctx.set_dependent_launch(True)
+    assert np.array_equal(results[True], want)
+    assert np.array_equal(results[False], want)
