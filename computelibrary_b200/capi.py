@@ -156,6 +156,7 @@ _SIGNATURES = {
     "cugl_conv2d_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_tma_store": (C.c_int, [_vp, C.c_int]),
     "cugl_conv2d_plan_set_resident_weights": (C.c_int, [_vp, C.c_int]),
+    "cugl_conv2d_plan_set_double_tile": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_tma_store": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_paired_drain": (C.c_int, [_vp, C.c_int]),
     "cugl_gemmlowp_plan_set_tile_columns": (C.c_int, [_vp, C.c_int]),
@@ -663,6 +664,9 @@ class ConvPlan:
 
     def set_resident_weights(self, on=True):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_resident_weights(self.handle, int(on)))
+
+    def set_double_tile(self, on=True):
+        self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_double_tile(self.handle, int(on)))
 
     def set_channel_major(self, mode: int):
         self.ctx.check(self.ctx.lib.cugl_conv2d_plan_set_channel_major(self.handle, int(mode)))

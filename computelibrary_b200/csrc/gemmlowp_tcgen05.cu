@@ -2559,12 +2559,18 @@ constexpr int kConvThreads  = kThreads + 32 * kGatherWarps;
 // RESB > 0: a convolution with a single column block (N <= BLOCK_N) whose weights fit into RESB bytes.  Every tile of
 // every CTA multiplies by the same B operand, so the producer thread loads it once and the ring carries patches only:
 // a third less traffic from L2 into shared memory for 64 output channels, and a deeper ring in the space set free.
-template <int BLOCK_N, int STAGES, int KSUB, int ACC, int RESB = 0>
+// MT = 2 (with a resident B operand, four accumulator buffers and two epilogue groups): a unit of work is 256 output
+// pixels, two 128-row tiles that share every hand-over -- one stage barrier, one commit and one accumulator-ready signal
+// for both, where a 64-column tile is bound by exactly those (the tensor pipe is busy a quarter of the time).  A stage
+// holds the patches of both tiles for one K step; epilogue group g drains tile g of every unit.
+template <int BLOCK_N, int STAGES, int KSUB, int ACC, int RESB = 0, int MT = 1>
 __global__ void __launch_bounds__(kConvThreads, 1)
     gemmlowp_conv_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_b, const __grid_constant__ CUtensorMap tmap_out,
                                  const __grid_constant__ TileParams tp, const EpilogueParams ep, const ConvGeom cg)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, false, RESB>;
+    using P = SmemPlan<BLOCK_N, STAGES, MT * KSUB, ACC, false, RESB>; // the A ring: MT x KSUB sub-tiles per stage
+    static_assert(MT == 1 || (MT == 2 && RESB != 0 && ACC == 4 && P::EPI_GROUPS == 2), "double tiles: resident B, four buffers, two groups");
+    constexpr int UNIT_M = MT * BLOCK_M;
     extern __shared__ uint8_t smem_raw[];
     // the 1024-byte aligned start of the dynamic shared memory, derived by pointer arithmetic on the __shared__ array
     // itself: a pointer rebuilt from an integer loses its address space and every access through it becomes a
@@ -2587,7 +2593,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const int num_m_blocks = (tp.M + BLOCK_M - 1) / BLOCK_M;
+    const int num_m_blocks = (tp.M + UNIT_M - 1) / UNIT_M; // units (MT tiles each) along M
     const int num_n_blocks = (tp.N + BLOCK_N - 1) / BLOCK_N;
     const int num_tiles    = num_m_blocks * num_n_blocks;
     const int num_kb       = (tp.K + KSUB * BLOCK_K - 1) / (KSUB * BLOCK_K);
@@ -2698,10 +2704,14 @@ __global__ void __launch_bounds__(kConvThreads, 1)
             for (int ti = 0; ti < my_tiles && ok; ++ti)
             {
                 ok = mbar_wait(tempty_bar(as), aph ^ 1, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
+                if (MT == 2 && ok)
+                {
+                    ok = mbar_wait(tempty_bar(as + 1), aph ^ 1, s_abort, DEV_TIMEOUT_MMA, tp.spin_limit);
+                }
                 if (!ok) break;
                 tc_fence_after();
                 trace_event(tp.trace, ti, 1);
-                const uint32_t d_tmem = tmem_base + as * BLOCK_N;
+                const uint32_t d_tmem = tmem_base + as * BLOCK_N; // (MT == 2: tile 1 of the unit in the next buffer)
                 for (int kb = 0; kb < num_kb; ++kb)
                 {
                     if (!have)
@@ -2723,7 +2733,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>((s * P::A_STAGE_K) >> 4);
                     // the ring slot, or this stage's K sub-blocks of the resident operand
-                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((RESB != 0 ? kb : s) * P::B_STAGE) >> 4);
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((RESB != 0 ? kb : s) * KSUB * P::B_SUB) >> 4);
                     // a stage that lies wholly inside K: the MMAs back to back, nothing to test on the issuing thread's
                     // path (it shares its scheduler with epilogue and gather warps, so every instruction it saves counts)
                     if ((kb + 1) * KSUB * BLOCK_K <= tp.K)
@@ -2734,9 +2744,14 @@ __global__ void __launch_bounds__(kConvThreads, 1)
 #pragma unroll
                             for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
                             {
-                                umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
-                                        b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
-                                        (kb | sub | k) != 0 ? 1u : 0u);
+#pragma unroll
+                                for (int mt = 0; mt < MT; ++mt) // the two tiles alternate: independent accumulators
+                                {
+                                    umma_i8(d_tmem + mt * BLOCK_N,
+                                            a_desc + static_cast<uint64_t>(((mt * KSUB + sub) * A_STAGE) >> 4) + 2u * k,
+                                            b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                            (kb | sub | k) != 0 ? 1u : 0u);
+                                }
                             }
                         }
                     }
@@ -2751,9 +2766,14 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                                 // a K step that lies wholly beyond K multiplies zero fill: left out (short K)
                                 if ((kb * KSUB + sub) * BLOCK_K + k * UMMA_K < tp.K)
                                 {
-                                    umma_i8(d_tmem, a_desc + static_cast<uint64_t>((sub * A_STAGE) >> 4) + 2u * k,
-                                            b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
-                                            (kb | sub | k) != 0 ? 1u : 0u);
+#pragma unroll
+                                    for (int mt = 0; mt < MT; ++mt)
+                                    {
+                                        umma_i8(d_tmem + mt * BLOCK_N,
+                                                a_desc + static_cast<uint64_t>(((mt * KSUB + sub) * A_STAGE) >> 4) + 2u * k,
+                                                b_desc + static_cast<uint64_t>((sub * P::B_SUB) >> 4) + 2u * k, tp.idesc,
+                                                (kb | sub | k) != 0 ? 1u : 0u);
+                                    }
                                 }
                             }
                         }
@@ -2767,7 +2787,8 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                     trace_event(tp.trace, ti, 3);
                     umma_commit(tfull_bar(as));
                 }
-                if (++as == ACC)
+                as += MT; // one accumulator-ready signal per unit: on the barrier of its first buffer
+                if (as == ACC)
                 {
                     as = 0;
                     aph ^= 1;
@@ -2787,18 +2808,20 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         int           filled_n0 = -1;
         for (int ti = 0; ti < my_tiles; ++ti)
         {
-            if (kGroups > 1 && (ti & 1) != group)
+            if (MT == 1 && kGroups > 1 && (ti & 1) != group)
             {
-                continue;
+                continue; // (MT == 2: every group works on every unit, group g on its tile g)
             }
             if (!(kGroups == 1 ? epi_barrier_and(ok) : epi_group_barrier_and(ok, group)))
             {
                 break;
             }
-            const int      as   = ti % ACC;
-            const uint32_t aph  = static_cast<uint32_t>(ti / ACC) & 1u;
+            // buffer of this group's tile, and the buffer whose barrier announces the unit's accumulators
+            const int      as_first = MT == 1 ? ti % ACC : MT * (ti % (ACC / MT));
+            const int      as       = MT == 1 ? as_first : as_first + group;
+            const uint32_t aph  = static_cast<uint32_t>(ti / (ACC / MT)) & 1u;
             const int      tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
-            const int      m0   = (tile % num_m_blocks) * BLOCK_M;
+            const int      m0   = (tile % num_m_blocks) * UNIT_M + (MT == 1 ? 0 : group * BLOCK_M);
             const int      n0   = (tile / num_m_blocks) * BLOCK_N;
             if (n0 != filled_n0) // tiles are ordered m-fastest: the column terms usually carry over
             {
@@ -2807,7 +2830,7 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                 if (kGroups == 1) epi_barrier();
                 else epi_group_barrier(group);
             }
-            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as), aph, s_abort, DEV_TIMEOUT_EPILOGUE, tp.spin_limit));
+            ok = __all_sync(0xffffffffu, mbar_wait(tfull_bar(as_first), aph, s_abort, DEV_TIMEOUT_EPILOGUE, tp.spin_limit));
             if (ok)
             {
                 tc_fence_after();
@@ -2841,13 +2864,14 @@ __global__ void __launch_bounds__(kConvThreads, 1)
         for (int ti = 0; ti < my_tiles && ok; ++ti)
         {
             const int tile = static_cast<int>(blockIdx.x) + ti * static_cast<int>(gridDim.x);
-            const int m0   = (tile % num_m_blocks) * BLOCK_M;
-            int            yi0[kRowsPerThread], xi0[kRowsPerThread];
-            const uint8_t *base[kRowsPerThread];
+            const int m0   = (tile % num_m_blocks) * UNIT_M;
+            int            yi0[MT * kRowsPerThread], xi0[MT * kRowsPerThread];
+            const uint8_t *base[MT * kRowsPerThread];
 #pragma unroll
-            for (int i = 0; i < kRowsPerThread; ++i)
+            for (int i = 0; i < MT * kRowsPerThread; ++i)
             {
-                const int m  = min(m0 + row0 + 32 * i, tp.M - 1); // rows beyond M repeat the last pixel (never stored)
+                // rows beyond M repeat the last pixel (never stored); i / kRowsPerThread is the tile of the unit
+                const int m  = min(m0 + (i / kRowsPerThread) * BLOCK_M + row0 + 32 * (i % kRowsPerThread), tp.M - 1);
                 const int q  = fast_div(m, cg.div_wo), xo = m - q * cg.Wo;
                 const int bi = fast_div(q, cg.div_ho), yo = q - bi * cg.Ho;
                 yi0[i]       = yo * cg.sy - cg.pad_t;
@@ -2877,13 +2901,14 @@ __global__ void __launch_bounds__(kConvThreads, 1)
                     const TapEntry e  = s_taps[(kb * KSUB + sub) * 8 + piece];
                     const int      dy = static_cast<int>(e.dydx >> 16), dx = static_cast<int>(e.dydx & 0xffffu);
 #pragma unroll
-                    for (int i = 0; i < kRowsPerThread; ++i)
+                    for (int i = 0; i < MT * kRowsPerThread; ++i)
                     {
                         const bool     in  = static_cast<unsigned>(yi0[i] + dy) < static_cast<unsigned>(cg.H) &&
                                         static_cast<unsigned>(xi0[i] + dx) < static_cast<unsigned>(cg.W);
                         const uint8_t *src = in ? base[i] + e.offset : pad_src;
-                        const int      r   = row0 + 32 * i;
-                        const uint32_t dst = sA + st * P::A_STAGE_K + sub * A_STAGE + r * 128 + ((piece ^ (r & 7)) << 4);
+                        const int      r   = row0 + 32 * (i % kRowsPerThread);
+                        const uint32_t dst = sA + st * P::A_STAGE_K + ((i / kRowsPerThread) * KSUB + sub) * A_STAGE + r * 128 +
+                                             ((piece ^ (r & 7)) << 4);
                         // .cg: through L2 only -- measured 5 to 20 % faster than .ca on every layer shape (an L1 miss
                         // of .ca lands in shared memory sector by sector)
                         asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
@@ -3323,11 +3348,11 @@ cugl_status launch_variant_2cta(cugl_context *ctx, const GemmOperands &op, const
     return CUGL_SUCCESS;
 }
 
-template <int BLOCK_N, int STAGES, int KSUB, int ACC, int RESB = 0>
+template <int BLOCK_N, int STAGES, int KSUB, int ACC, int RESB = 0, int MT = 1>
 cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const EpilogueParams &ep,
                                 const ConvOperands &cv)
 {
-    using P = SmemPlan<BLOCK_N, STAGES, KSUB, ACC, false, RESB>;
+    using P = SmemPlan<BLOCK_N, STAGES, MT * KSUB, ACC, false, RESB>;
     // the tap table: one entry per 16 bytes of K; with a resident B operand K is at most RESB / BLOCK_N bytes
     constexpr int kTapEntries = RESB != 0 ? RESB / BLOCK_N / 16 : kConvMaxPieces;
     constexpr int kDynBytes   = P::DYN_BYTES + kTapEntries * static_cast<int>(sizeof(TapEntry));
@@ -3344,7 +3369,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     {
         return fail(ctx, CUGL_RUNTIME_ERROR, "cuTensorMapEncodeTiled failed for the output tiles");
     }
-    auto        kernel = gemmlowp_conv_tcgen05_kernel<BLOCK_N, STAGES, KSUB, ACC, RESB>;
+    auto        kernel = gemmlowp_conv_tcgen05_kernel<BLOCK_N, STAGES, KSUB, ACC, RESB, MT>;
     static bool attr_set[64] = {};
     if (!attr_set[ctx->device & 63])
     {
@@ -3390,7 +3415,7 @@ cugl_status launch_conv_variant(cugl_context *ctx, const GemmOperands &op, const
     cg.Ho    = cv.Ho;
     cg.div_wo = make_fastdiv(cv.Wo);
     cg.div_ho = make_fastdiv(cv.Ho);
-    const int tiles = ((op.M + BLOCK_M - 1) / BLOCK_M) * ((op.N + BLOCK_N - 1) / BLOCK_N);
+    const int tiles = ((op.M + MT * BLOCK_M - 1) / (MT * BLOCK_M)) * ((op.N + BLOCK_N - 1) / BLOCK_N); // units of MT tiles
     const int grid  = tiles < ctx->sm_count ? tiles : ctx->sm_count;
     tp.tma_store = tma_store ? 1 : 0;
     CUGL_CUDA_TRY(ctx, launch_dependent(ctx, kernel, grid, kConvThreads, kDynBytes, map_b, map_out, tp, ep, cg));
@@ -3508,6 +3533,15 @@ cugl_status CUGL_TC_NAME(launch_gemmlowp_conv_tcgen05)(cugl_context *ctx, const 
     constexpr int kResidentB = 40 * 1024; // K <= 640: the weights of a 3x3 x 64 or a folded 7x7 x 3 filter bank
     if (op.resident_b >= 0 && op.N <= 64 && ((op.K + BLOCK_K - 1) / BLOCK_K) * 64 * BLOCK_K <= kResidentB)
     {
+        if constexpr (kEpiWarps == 8) // (two epilogue groups: one per tile of a unit)
+        {
+            // enough output for a 256-row unit on every SM, and more than two K blocks per tile (802816 x 64 x 576:
+            // 93.6 -> 87.4 us; with K = 256, two hand-overs per tile either way, the folded stem measured slower: 231 -> 246)
+            if (op.double_tile >= 0 && op.M > 2 * BLOCK_M * ctx->sm_count && op.K > 2 * BLOCK_K)
+            {
+                return launch_conv_variant<64, 5, 1, 4, kResidentB, 2>(ctx, op, ep, cv);
+            }
+        }
         return launch_conv_variant<64, 5, 2, 4, kResidentB>(ctx, op, ep, cv);
     }
     return launch_conv_variant<64, 4, 2, 4>(ctx, op, ep, cv);

@@ -74,6 +74,9 @@ struct GemmOperands
     // implicit convolution (gather): < 0 reloads the weights with every tile; otherwise they stay in shared memory for
     // the life of a CTA where one column block covers N and they fit beside the ring
     int resident_b;
+    // the same kernels: < 0 keeps 128-row units of work; otherwise 256-row units (two tiles per hand-over) where the
+    // output is large enough
+    int double_tile;
 };
 
 // Geometry of an NHWC 8-bit convolution whose A operand is gathered on the fly (implicit GEMM).

@@ -64,6 +64,7 @@ struct GemmCore
     int           pair_drain    = 0;     // < 0: every accumulator buffer is drained on its own
     int           tma_store     = 0;     // < 0: no bulk tensor stores in the epilogue
     int           resident_b    = 0;     // < 0: the implicit convolution reloads the weights with every tile
+    int           double_tile   = 0;     // < 0: the implicit convolution keeps 128-row units of work
 
     // bytes of the row-sum vector as a share of a temporary workspace (none without a B offset)
     size_t rowsum_bytes() const
@@ -241,6 +242,7 @@ struct GemmCore
         op.pair_drain    = pair_drain;
         op.tma_store     = tma_store;
         op.resident_b    = resident_b;
+        op.double_tile   = double_tile;
         op.n_extra_dst   = n_extra;
         op.residual      = d_residual;
         op.res_floor     = res_floor;
@@ -1312,6 +1314,7 @@ extern "C"
             op.pair_drain    = c.pair_drain;
             op.tma_store     = c.tma_store;
             op.resident_b    = c.resident_b;
+            op.double_tile   = c.double_tile;
             op.n_extra_dst   = 0;
             op.residual      = d_residual;
             op.res_floor     = plan->res_floor;
@@ -1491,6 +1494,16 @@ extern "C"
             return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_resident_weights: NULL plan");
         }
         plan->core.resident_b = on != 0 ? 0 : -1;
+        return CUGL_SUCCESS;
+    }
+
+    cugl_status cugl_conv2d_plan_set_double_tile(cugl_conv_plan *plan, int on)
+    {
+        if (plan == nullptr)
+        {
+            return fail(nullptr, CUGL_INVALID_ARGUMENT, "cugl_conv2d_plan_set_double_tile: NULL plan");
+        }
+        plan->core.double_tile = on != 0 ? 0 : -1;
         return CUGL_SUCCESS;
     }
 

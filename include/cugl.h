@@ -434,6 +434,10 @@ CUGL_API cugl_status cugl_conv2d_plan_set_tma_store(cugl_conv_plan *plan, int on
  * memory once per thread block and stays there (on by default); 0 reloads it with every tile as for larger filters.
  * For tests and measurements; results do not depend on it. */
 CUGL_API cugl_status cugl_conv2d_plan_set_resident_weights(cugl_conv_plan *plan, int on);
+/* The same layers (resident weights) with more than 256 output pixels per SM: a thread block works on units of 256
+ * output pixels, two 128-row tiles that share every barrier hand-over (on by default); 0 keeps 128-row units.  For tests
+ * and measurements; results do not depend on it. */
+CUGL_API cugl_status cugl_conv2d_plan_set_double_tile(cugl_conv_plan *plan, int on);
 /* NEGEMMConvolutionLayer::update_quantization_parameters (src/runtime/NEON/functions/NEGEMMConvolutionLayer.cpp:129-131,
  * src/cpu/operators/CpuGemmConv2d.cpp:858-908): re-reads the zero points, the multipliers / shifts, the output zero
  * point and the clamp bounds of desc; geometry and types must be unchanged.  The prepared weights stay valid. */

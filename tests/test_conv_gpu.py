@@ -15,7 +15,7 @@ CODE = {np.dtype(np.uint8): capi.U8, np.dtype(np.int8): capi.S8}
 
 def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out_zp, lo, hi, dilation=(1, 1),
              implicit=True, want_kernel=None, tile_columns=0, paired_drain=True, tma_im2col=True, want_tma=None,
-             resident_weights=True):
+             resident_weights=True, double_tile=True):
     import torch
     B, H, W, Cc = src.shape
     OFM, kh, kw, _ = weights.shape
@@ -37,6 +37,8 @@ def gpu_conv(ctx, src, weights, bias, stride, pad, in_zp, w_zp, mult, shift, out
         plan.allow_tma_im2col(int(tma_im2col))  # 0: the gather; 2: TMA loads for 64-channel inputs too
     if not resident_weights:
         plan.set_resident_weights(False)
+    if not double_tile:
+        plan.set_double_tile(False)
     if want_tma is not None:
         assert plan.uses_tma_im2col == want_tma
     if want_kernel is not None:
@@ -389,3 +391,23 @@ def test_resident_weights_conv_vs_oracle(ctx, port, geom, batch):
         got = gpu_conv(ctx, src, wgt, bias, (s, s), (p, p, p, p), in_zp, 0, mult, shift, 3, 0, 255, want_kernel="implicit",
                        tma_im2col=False, resident_weights=resident)
         assert np.array_equal(got, want), (resident, np.argwhere(got != want)[:5])
+
+
+@pytest.mark.parametrize("geom", [(16, 56, 56, 1, 64, 128), (13, 57, 59, 1, 40, 0), (11, 60, 61, 1, 64, 0), (50, 57, 59, 2, 64, 7)])
+def test_double_tile_conv_vs_oracle(ctx, port, geom):
+    """3x3 x 64 convolutions large enough (more than 256 output pixels per SM) for the gather kernel's 256-pixel units,
+    two tiles per barrier hand-over: a whole number of units, a ragged last unit whose second tile is partly or wholly
+    beyond M, stride 2 and 40 output channels -- against the oracle and against the 128-pixel units."""
+    B, H, W, s, OFM, in_zp = geom
+    rng = np.random.default_rng(B * 100 + H + OFM)
+    src = q8_uniform(rng, (B, H, W, 64), np.uint8)
+    wgt = q8_uniform(rng, (OFM, 3, 3, 64), np.int8, -127, 127)
+    bias = rng.integers(-5000, 5001, OFM).astype(np.int32)
+    ws = np.exp(rng.uniform(np.log(1e-3), np.log(1e-2), OFM)).astype(np.float32)
+    mult, shift = f32_mults(port, 0.03, ws, 0.15)
+    want = port.conv2d_nhwc(src, wgt, bias, (s, s), (1, 1, 1, 1), in_zp, 0, mult, shift, 3, 0, 255)
+    assert want.shape[0] * want.shape[1] * want.shape[2] > 256 * 148
+    for double in (True, False):
+        got = gpu_conv(ctx, src, wgt, bias, (s, s), (1, 1, 1, 1), in_zp, 0, mult, shift, 3, 0, 255, want_kernel="implicit",
+                       tma_im2col=False, double_tile=double)
+        assert np.array_equal(got, want), (double, np.argwhere(got != want)[:5])
